@@ -1,0 +1,105 @@
+"""SpecAugment / SpecCutout on [B, F, T] spectrograms.
+
+Frequency masks and (adaptive) time masks are drawn per utterance and applied in place, fully on
+the device without a host synchronisation: mask start / width tensors are sampled with
+``torch.rand`` for the whole batch and applied as a broadcast comparison.  Reference behaviour:
+``nemo/collections/asr/parts/submodules/spectr_augment.py:25,218`` and the Numba kernel
+``parts/numba/spec_augment/spec_aug_numba.py:27-95`` (time-mask width is ``time_width`` frames, or
+a fraction of the utterance length when ``time_width`` is a float — "adaptive").
+"""
+from __future__ import annotations
+
+from typing import Optional, Union
+
+import torch
+
+from ..core.module import NeuralModule
+from ..core.neural_types import LengthsType, NeuralType, SpectrogramType, typecheck
+
+
+class SpecAugment(torch.nn.Module):
+    def __init__(self, freq_masks=0, time_masks=0, freq_width=10, time_width: Union[int, float] = 10, rng=None,
+                 mask_value=0.0, use_vectorized_code: bool = True):
+        super().__init__()
+        self.freq_masks, self.time_masks = freq_masks, time_masks
+        self.freq_width, self.time_width = freq_width, time_width
+        self.mask_value = mask_value
+        if isinstance(time_width, float) and not (0.0 <= time_width <= 1.0):
+            raise ValueError("If `time_width` is a float value, must be in range [0, 1]")
+        self.adaptive_temporal_width = isinstance(time_width, float)
+
+    @torch.no_grad()
+    def forward(self, input_spec, length):
+        B, F, T = input_spec.shape
+        dev = input_spec.device
+        if length is None:
+            length = torch.full((B,), T, device=dev, dtype=torch.long)
+        fill = torch.zeros(B, F, T, dtype=torch.bool, device=dev)
+        if self.freq_masks > 0:
+            w = torch.randint(0, self.freq_width + 1, (B, self.freq_masks), device=dev)
+            start = (torch.rand(B, self.freq_masks, device=dev) * (F - w + 1).clamp(min=1)).long()
+            f = torch.arange(F, device=dev)[None, None, :]
+            fm = ((f >= start[..., None]) & (f < (start + w)[..., None])).any(dim=1)  # B,F
+            fill |= fm[:, :, None]
+        if self.time_masks > 0:
+            if self.adaptive_temporal_width:
+                tw = (length.float() * self.time_width).long().clamp(min=1)[:, None]
+            else:
+                tw = torch.full((B, 1), int(self.time_width), device=dev)
+            w = (torch.rand(B, self.time_masks, device=dev) * (tw + 1).float()).long()
+            hi = (length[:, None] - w).clamp(min=1)
+            start = (torch.rand(B, self.time_masks, device=dev) * hi.float()).long()
+            t = torch.arange(T, device=dev)[None, None, :]
+            tm = ((t >= start[..., None]) & (t < (start + w)[..., None])).any(dim=1)  # B,T
+            fill |= tm[:, None, :]
+        return input_spec.masked_fill(fill, self.mask_value)
+
+
+class SpecCutout(torch.nn.Module):
+    def __init__(self, rect_masks=0, rect_time=5, rect_freq=20, rng=None):
+        super().__init__()
+        self.rect_masks, self.rect_time, self.rect_freq = rect_masks, rect_time, rect_freq
+
+    @torch.no_grad()
+    def forward(self, input_spec):
+        B, F, T = input_spec.shape
+        dev = input_spec.device
+        if self.rect_masks <= 0:
+            return input_spec
+        fs = (torch.rand(B, self.rect_masks, device=dev) * max(1, F - self.rect_freq)).long()
+        ts = (torch.rand(B, self.rect_masks, device=dev) * max(1, T - self.rect_time)).long()
+        fw = torch.randint(0, self.rect_freq + 1, (B, self.rect_masks), device=dev)
+        tw = torch.randint(0, self.rect_time + 1, (B, self.rect_masks), device=dev)
+        f = torch.arange(F, device=dev)[None, None, :, None]
+        t = torch.arange(T, device=dev)[None, None, None, :]
+        m = ((f >= fs[..., None, None]) & (f < (fs + fw)[..., None, None]) &
+             (t >= ts[..., None, None]) & (t < (ts + tw)[..., None, None])).any(dim=1)
+        return input_spec.masked_fill(m, 0.0)
+
+
+class SpectrogramAugmentation(NeuralModule):
+    def __init__(self, freq_masks=0, time_masks=0, freq_width=10, time_width=10, rect_masks=0, rect_time=5,
+                 rect_freq=20, rng=None, mask_value=0.0, use_vectorized_spec_augment: bool = True,
+                 use_numba_spec_augment: bool = False):
+        super().__init__()
+        self.spec_cutout = SpecCutout(rect_masks, rect_time, rect_freq) if rect_masks > 0 else None
+        self.spec_augment = SpecAugment(freq_masks, time_masks, freq_width, time_width, mask_value=mask_value) \
+            if freq_masks + time_masks > 0 else None
+
+    @property
+    def input_types(self):
+        return {"input_spec": NeuralType(("B", "D", "T"), SpectrogramType()),
+                "length": NeuralType(("B",), LengthsType(), optional=True)}
+
+    @property
+    def output_types(self):
+        return {"augmented_spec": NeuralType(("B", "D", "T"), SpectrogramType())}
+
+    @typecheck()
+    def forward(self, input_spec, length=None):
+        x = input_spec
+        if self.spec_cutout is not None:
+            x = self.spec_cutout(x)
+        if self.spec_augment is not None:
+            x = self.spec_augment(x, length)
+        return x
