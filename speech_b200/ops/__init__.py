@@ -56,12 +56,12 @@ _native = None
 _native_err: Optional[BaseException] = None
 
 
-def native():
+def _nat():
     """The ctypes binding module, loaded on first use."""
     global _native, _native_err
     if _native is None and _native_err is None:
         try:
-            from . import native as _n
+            from . import native as _n  # noqa: F811
 
             _n.load()
             _native = _n
@@ -78,7 +78,7 @@ def native():
 
 def native_available() -> bool:
     try:
-        native()
+        _nat()
         return True
     except RuntimeError:
         return False
@@ -87,7 +87,7 @@ def native_available() -> bool:
 def _use_native(t: torch.Tensor) -> bool:
     if not t.is_cuda or eager_allowed():
         return False
-    native()  # raises loudly when the library is missing on a GPU machine
+    _nat()  # raises loudly when the library is missing on a GPU machine
     return True
 
 
@@ -113,25 +113,25 @@ def lowp(param: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tens
 # ----------------------------------------------------------------------------- dense layers
 def linear(x, weight, bias=None, act: Optional[str] = None, residual=None, alpha: float = 1.0):
     if _use_native(x) and x.dtype == torch.bfloat16:
-        return native().linear(x, weight, bias, act, residual, alpha)
+        return _nat().linear(x, weight, bias, act, residual, alpha)
     return reference.linear(x, weight, bias, act, residual, alpha)
 
 
 def layer_norm(x, weight, bias, eps: float = 1e-5):
     if _use_native(x) and x.dtype == torch.bfloat16:
-        return native().layer_norm(x, weight, bias, eps)
+        return _nat().layer_norm(x, weight, bias, eps)
     return reference.layer_norm(x, weight, bias, eps)
 
 
 def relpos_attention(q, k, v, p, pos_bias_u, pos_bias_v, mask=None, dropout_p: float = 0.0, training: bool = False):
     if _use_native(q) and q.dtype == torch.bfloat16 and not (dropout_p > 0 and training):
-        return native().relpos_attention(q, k, v, p, pos_bias_u, pos_bias_v, mask)
+        return _nat().relpos_attention(q, k, v, p, pos_bias_u, pos_bias_v, mask)
     return reference.relpos_attention(q, k, v, p, pos_bias_u, pos_bias_v, mask, dropout_p, training)
 
 
 def mha_attention(q, k, v, mask=None, dropout_p: float = 0.0, training: bool = False, scale=None):
     if _use_native(q) and q.dtype == torch.bfloat16 and not (dropout_p > 0 and training):
-        return native().mha_attention(q, k, v, mask, scale)
+        return _nat().mha_attention(q, k, v, mask, scale)
     return reference.mha_attention(q, k, v, mask, dropout_p, training, scale)
 
 
@@ -139,7 +139,7 @@ def conv_module_core(g, dw_weight, dw_bias, norm_type, norm_weight, norm_bias, r
                      pad_mask=None, training=False, momentum=0.1, eps=1e-5, left_pad=4, right_pad=4, cache=None,
                      cache_drop_size=0, bn_stats_reduce=None):
     if _use_native(g) and g.dtype == torch.bfloat16 and cache is None and norm_type in ("batch_norm", "layer_norm"):
-        return native().conv_module_core(g, dw_weight, dw_bias, norm_type, norm_weight, norm_bias, running_mean,
+        return _nat().conv_module_core(g, dw_weight, dw_bias, norm_type, norm_weight, norm_bias, running_mean,
                                          running_var, pad_mask, training, momentum, eps, left_pad, right_pad,
                                          bn_stats_reduce)
     return reference.conv_module_core(g, dw_weight, dw_bias, norm_type, norm_weight, norm_bias, running_mean,
@@ -149,7 +149,7 @@ def conv_module_core(g, dw_weight, dw_bias, norm_type, norm_weight, norm_bias, r
 
 def lstm(x, weights, h0=None, c0=None, num_layers=1, dropout=0.0, training=False):
     if _use_native(x) and x.dtype == torch.bfloat16 and not (dropout > 0 and training):
-        return native().lstm(x, weights, h0, c0, num_layers)
+        return _nat().lstm(x, weights, h0, c0, num_layers)
     return reference.lstm(x, weights, h0, c0, num_layers, dropout, training)
 
 
@@ -157,7 +157,7 @@ def lstm(x, weights, h0=None, c0=None, num_layers=1, dropout=0.0, training=False
 def transducer_joint_loss(f, g, w, b, targets, f_len, y_len, blank, durations, sigma, act="relu",
                           fastemit_lambda=0.0, sub_batch=0):
     if _use_native(f) and f.dtype == torch.bfloat16 and act == "relu":
-        return native().transducer_joint_loss(f, g, w, b, targets, f_len, y_len, blank, durations, sigma,
+        return _nat().transducer_joint_loss(f, g, w, b, targets, f_len, y_len, blank, durations, sigma,
                                               fastemit_lambda)
     return reference.transducer_joint_loss(f, g, w, b, targets, f_len, y_len, blank, durations, sigma, act,
                                            fastemit_lambda, sub_batch)
@@ -165,13 +165,13 @@ def transducer_joint_loss(f, g, w, b, targets, f_len, y_len, blank, durations, s
 
 def transducer_loss_from_logits(logits, targets, f_len, y_len, blank, durations, sigma=0.0):
     if _use_native(logits):
-        return native().transducer_loss_from_logits(logits, targets, f_len, y_len, blank, durations, sigma)
+        return _nat().transducer_loss_from_logits(logits, targets, f_len, y_len, blank, durations, sigma)
     return reference.tdt_loss_from_logits(logits, targets, f_len, y_len, blank, durations, sigma)
 
 
 def ctc_loss(log_probs, targets, input_lengths, target_lengths, blank, zero_infinity=True):
     if _use_native(log_probs):
-        return native().ctc_loss(log_probs, targets, input_lengths, target_lengths, blank)
+        return _nat().ctc_loss(log_probs, targets, input_lengths, target_lengths, blank)
     return reference.ctc_loss(log_probs, targets, input_lengths, target_lengths, blank, zero_infinity)
 
 
@@ -179,7 +179,7 @@ def ctc_loss(log_probs, targets, input_lengths, target_lengths, blank, zero_infi
 def logmel(x, seq_len, window, fb, n_fft, hop, win_length, preemph=0.97, mag_power=2.0, log_zero_guard=2 ** -24,
            normalize="per_feature", pad_to=0, pad_value=0.0, dither=0.0, log=True):
     if _use_native(x) and normalize in ("per_feature", None) and mag_power == 2.0 and log and n_fft == 512:
-        return native().logmel(x, seq_len, window, fb, n_fft, hop, win_length, preemph, log_zero_guard,
+        return _nat().logmel(x, seq_len, window, fb, n_fft, hop, win_length, preemph, log_zero_guard,
                                normalize, pad_to, pad_value, dither)
     return reference.logmel(x, seq_len, window, fb, n_fft, hop, win_length, preemph, mag_power, log_zero_guard,
                             normalize, pad_to, pad_value, dither, log=log)
@@ -189,7 +189,7 @@ def logmel(x, seq_len, window, fb, n_fft, hop, win_length, preemph=0.97, mag_pow
 def adamw_flat(master, grad, exp_avg, exp_avg_sq, lowp, lr, beta1, beta2, eps, weight_decay, step, scalars):
     """One fused AdamW pass; ``scalars[1]`` (device memory) holds the gradient multiplier (clip x scale)."""
     if _use_native(master):
-        return native().adamw_flat(master, grad, exp_avg, exp_avg_sq, lowp, lr, beta1, beta2, eps, weight_decay, step,
+        return _nat().adamw_flat(master, grad, exp_avg, exp_avg_sq, lowp, lr, beta1, beta2, eps, weight_decay, step,
                                    scalars)
     return reference.adamw_flat(master, grad, exp_avg, exp_avg_sq, lowp, lr, beta1, beta2, eps, weight_decay, step,
                                 clip_coef=scalars[1])
@@ -198,7 +198,7 @@ def adamw_flat(master, grad, exp_avg, exp_avg_sq, lowp, lr, beta1, beta2, eps, w
 def grad_norm_clip_coef(flat_grad, scalars, max_norm: float, grad_scale: float = 1.0):
     """scalars[0] <- ||grad * grad_scale||_2, scalars[1] <- grad_scale * min(1, max_norm / (norm + 1e-6))."""
     if _use_native(flat_grad):
-        return native().grad_norm_clip_coef(flat_grad, scalars, max_norm, grad_scale)
+        return _nat().grad_norm_clip_coef(flat_grad, scalars, max_norm, grad_scale)
     norm = flat_grad.float().norm() * grad_scale
     scalars[0] = norm
     scalars[1] = grad_scale * torch.clamp(max_norm / (norm + 1e-6), max=1.0)

@@ -1,0 +1,529 @@
+// Persistent bf16 GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma with TMEM accumulators -> fused epilogue.
+//
+//   D[b] = epilogue( alpha * A[b] (M x K) * B[b]^T (K x N) )          fp32 accumulation
+//
+// Each operand may be stored K-major ("row" of the logical matrix is contiguous in K: A as [M,K], B as [N,K],
+// i.e. nn.Linear's weight) or MN-major (stored transposed: A as [K,M], B as [K,N]); the four combinations cover
+// forward (x W^T), input-gradient (dy W) and weight-gradient (dy^T x) GEMMs without any transposition pass.
+// Batched problems (attention scores per (batch, head)) use two batch indices with arbitrary strides.
+//
+// CTA layout (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor memory and issues the MMAs,
+// warps 2-5 run the epilogue (each owns 32 TMEM lanes).  The CTA is persistent over output tiles; two
+// accumulators (2 x 128 TMEM columns) let the epilogue of tile i overlap the MMAs of tile i+1.
+// Shared-memory stages hold a 128x64 A tile and a 128x64 B tile in the 128-byte swizzled layout that both
+// TMA and the tcgen05 shared-memory descriptors understand.
+//
+// Epilogue (all optional, applied in this order): v = acc + bias[n]; store pre-activation (bf16);
+// v = alpha * act(v); v *= act'(aux[m,n]); v += residual[m,n]; v += beta * D_old[m,n] (fp32 D only); store D as bf16 or fp32.
+//
+// Every mbarrier wait is bounded (see common.cuh): on a timeout the kernel records a status code and all roles
+// fall through to the common exit where tensor memory is released.
+#include "common.cuh"
+#include <cuda.h>
+#include <stdio.h>
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_N = 128;
+constexpr int BLOCK_K = 64;  // 64 bf16 = 128 bytes = one swizzle atom row
+constexpr int UMMA_K = 16;
+constexpr int NUM_STAGES = 6;
+constexpr int NUM_ACC = 2;
+constexpr int TILE_BYTES = BLOCK_M * BLOCK_K * 2;  // 16 KiB per operand tile
+constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+constexpr int SMEM_BYTES = NUM_STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = NUM_ACC * BLOCK_N;  // 256
+
+struct EpilogueArgs {
+  void* D;
+  const float* bias_f32;
+  const __nv_bfloat16* bias_bf16;
+  const __nv_bfloat16* residual;
+  const __nv_bfloat16* aux;
+  __nv_bfloat16* D_pre;
+  long long ldd, ldr, ldx, ldp;
+  long long d_bs0, d_bs1, r_bs0, r_bs1, x_bs0, x_bs1, p_bs0, p_bs1;
+  float alpha, beta;
+  int act;       // 0 none, 1 relu, 2 swish, 3 gelu
+  int dact;      // 0 none, 1 relu', 2 swish', 3 gelu'  (multiplies by act'(aux))
+  int d_is_f32;  // output dtype
+};
+
+struct GemmParams {
+  int M, N, K;
+  int batch0, batch1;
+  int tiles_m, tiles_n;
+  long long num_tiles;
+  EpilogueArgs ep;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false after SB_WAIT_CYCLES, with the status word set.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > SB_WAIT_CYCLES || sb_failed(status)) {
+      sb_set_status(status, code, (int)parity);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tmap, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor (tcgen05): 128-byte swizzle, version 1.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == 1) return fmaxf(v, 0.f);
+  if (act == 2) return sb_swish(v);
+  if (act == 3) return sb_gelu(v);
+  return v;
+}
+__device__ __forceinline__ float apply_dact(float g, float z, int dact) {
+  if (dact == 1) return z > 0.f ? g : 0.f;
+  if (dact == 2) return g * sb_dswish(z);
+  if (dact == 3) return g * sb_dgelu(z);
+  return g;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t bar_base = base + NUM_STAGES * STAGE_BYTES;
+  // barrier slots (8 bytes each): full[S], empty[S], tmem_full[2], tmem_empty[2]; then the TMEM address word
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (NUM_STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * NUM_STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * NUM_STAGES + NUM_ACC + a); };
+  volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem + NUM_STAGES * STAGE_BYTES + 8 * (2 * NUM_STAGES + 2 * NUM_ACC));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NUM_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < NUM_ACC; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      long long it = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        const int batch = (int)(tile / ((long long)p.tiles_m * p.tiles_n));
+        const int rem = (int)(tile % ((long long)p.tiles_m * p.tiles_n));
+        const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
+        const int b0 = batch % p.batch0, b1 = batch / p.batch0;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = (int)(it % NUM_STAGES);
+          const uint32_t ph = (uint32_t)((it / NUM_STAGES) & 1);
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, SB_TIMEOUT_SMEM_EMPTY)) { ok = false; break; }
+          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          const uint32_t sa = base + s * STAGE_BYTES, sb = sa + TILE_BYTES;
+          if (A_MN) {
+            tma_load_4d(sa, &tmap_a, full_bar(s), tm * BLOCK_M, kb * BLOCK_K, b0, b1);
+            tma_load_4d(sa + TILE_BYTES / 2, &tmap_a, full_bar(s), tm * BLOCK_M + 64, kb * BLOCK_K, b0, b1);
+          } else {
+            tma_load_4d(sa, &tmap_a, full_bar(s), kb * BLOCK_K, tm * BLOCK_M, b0, b1);
+          }
+          if (B_MN) {
+            tma_load_4d(sb, &tmap_b, full_bar(s), tn * BLOCK_N, kb * BLOCK_K, b0, b1);
+            tma_load_4d(sb + TILE_BYTES / 2, &tmap_b, full_bar(s), tn * BLOCK_N + 64, kb * BLOCK_K, b0, b1);
+          } else {
+            tma_load_4d(sb, &tmap_b, full_bar(s), kb * BLOCK_K, tn * BLOCK_N, b0, b1);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                             ((uint32_t)(BLOCK_N >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
+      long long it = 0;
+      long long tcount = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++tcount) {
+        const int acc = (int)(tcount % NUM_ACC);
+        const uint32_t aph = (uint32_t)((tcount / NUM_ACC) & 1);
+        if (!mbar_wait(tempty_bar(acc), aph ^ 1u, p.status, SB_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = (int)(it % NUM_STAGES);
+          const uint32_t ph = (uint32_t)((it / NUM_STAGES) & 1);
+          if (!mbar_wait(full_bar(s), ph, p.status, SB_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + s * STAGE_BYTES, sb = sa + TILE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            // K-major: advance 32 bytes inside the swizzle atom; MN-major: advance 16 rows of 128 bytes.
+            const uint64_t ad = A_MN ? make_desc(sa + k * (UMMA_K * 128), BLOCK_K * 128, 1024)
+                                     : make_desc(sa + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t bd = B_MN ? make_desc(sb + k * (UMMA_K * 128), BLOCK_K * 128, 1024)
+                                     : make_desc(sb + k * (UMMA_K * 2), 16, 1024);
+            umma_bf16(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+        }
+        if (ok) umma_commit(tfull_bar(acc));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;  // TMEM lane quarter owned by this warp
+    const EpilogueArgs& e = p.ep;
+    long long tcount = 0;
+    bool ok = true;
+    for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++tcount) {
+      const int batch = (int)(tile / ((long long)p.tiles_m * p.tiles_n));
+      const int rem = (int)(tile % ((long long)p.tiles_m * p.tiles_n));
+      const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
+      const int b0 = batch % p.batch0, b1 = batch / p.batch0;
+      const int acc = (int)(tcount % NUM_ACC);
+      const uint32_t aph = (uint32_t)((tcount / NUM_ACC) & 1);
+      // the decision to go on must be warp-uniform: tcgen05.ld below is a warp-collective instruction
+      ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(acc), aph, p.status, SB_TIMEOUT_TMEM_FULL) ? 1 : 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+      const int row = tm * BLOCK_M + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const long long d_off = (long long)b0 * e.d_bs0 + (long long)b1 * e.d_bs1 + (long long)row * e.ldd;
+      const long long r_off = (long long)b0 * e.r_bs0 + (long long)b1 * e.r_bs1 + (long long)row * e.ldr;
+      const long long x_off = (long long)b0 * e.x_bs0 + (long long)b1 * e.x_bs1 + (long long)row * e.ldx;
+      const long long p_off = (long long)b0 * e.p_bs0 + (long long)b1 * e.p_bs1 + (long long)row * e.ldp;
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BLOCK_N + c * 32);
+        tmem_ld32(taddr, r);
+        tmem_ld_wait();
+        const int col0 = tn * BLOCK_N + c * 32;
+        if (row_ok && col0 < p.N) {
+          const bool full = (col0 + 32 <= p.N);
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (e.bias_f32) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full || col0 + j < p.N) v[j] += __ldg(e.bias_f32 + col0 + j);
+          } else if (e.bias_bf16) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full || col0 + j < p.N) v[j] += __bfloat162float(e.bias_bf16[col0 + j]);
+          }
+          if (e.D_pre) {
+            __nv_bfloat16* dp = e.D_pre + p_off + col0;
+            if (full && ((((uintptr_t)dp) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                __align__(16) __nv_bfloat162 t[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) t[u] = __floats2bfloat162_rn(v[j + 2 * u], v[j + 2 * u + 1]);
+                *reinterpret_cast<uint4*>(dp + j) = *reinterpret_cast<uint4*>(t);
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dp[j] = __float2bfloat16(v[j]);
+            }
+          }
+          if (e.act) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], e.act);
+          }
+          if (e.alpha != 1.f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= e.alpha;
+          }
+          if (e.dact) {
+            const __nv_bfloat16* xp = e.aux + x_off + col0;
+            if (full && ((((uintptr_t)xp) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 raw4 = *reinterpret_cast<const uint4*>(xp + j);
+                const __nv_bfloat162* t = reinterpret_cast<const __nv_bfloat162*>(&raw4);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  float2 z = __bfloat1622float2(t[u]);
+                  v[j + 2 * u] = apply_dact(v[j + 2 * u], z.x, e.dact);
+                  v[j + 2 * u + 1] = apply_dact(v[j + 2 * u + 1], z.y, e.dact);
+                }
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) v[j] = apply_dact(v[j], __bfloat162float(xp[j]), e.dact);
+            }
+          }
+          if (e.residual) {
+            const __nv_bfloat16* rp = e.residual + r_off + col0;
+            if (full && ((((uintptr_t)rp) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 raw4 = *reinterpret_cast<const uint4*>(rp + j);
+                const __nv_bfloat162* t = reinterpret_cast<const __nv_bfloat162*>(&raw4);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  float2 z = __bfloat1622float2(t[u]);
+                  v[j + 2 * u] += z.x;
+                  v[j + 2 * u + 1] += z.y;
+                }
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
+            }
+          }
+          if (e.d_is_f32) {
+            float* dp = reinterpret_cast<float*>(e.D) + d_off + col0;
+            if (full && ((((uintptr_t)dp) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (e.beta != 0.f) {
+                  float4 old = *reinterpret_cast<const float4*>(dp + j);
+                  o.x += e.beta * old.x; o.y += e.beta * old.y; o.z += e.beta * old.z; o.w += e.beta * old.w;
+                }
+                *reinterpret_cast<float4*>(dp + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dp[j] = v[j] + (e.beta != 0.f ? e.beta * dp[j] : 0.f);
+            }
+          } else {
+            __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(e.D) + d_off + col0;
+            if (full && ((((uintptr_t)dp) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                __align__(16) __nv_bfloat162 t[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) t[u] = __floats2bfloat162_rn(v[j + 2 * u], v[j + 2 * u + 1]);
+                *reinterpret_cast<uint4*>(dp + j) = *reinterpret_cast<uint4*>(t);
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dp[j] = __float2bfloat16(v[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  // ------------------------------------------------------------------ common exit
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+// Operand as a 4-D tensor (inner, outer, batch0, batch1) with a {64, box_outer, 1, 1} box.
+int make_operand_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long ld, int batch0,
+                     int batch1, long long bs0, long long bs1, int box_outer) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return -100;
+  if ((((uintptr_t)ptr) & 15) != 0 || (ld * 2) % 16 != 0) return -101;
+  if ((batch0 > 1 && (bs0 * 2) % 16 != 0) || (batch1 > 1 && (bs1 * 2) % 16 != 0)) return -102;
+  cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)batch0, (cuuint64_t)batch1};
+  const cuuint64_t safe = (cuuint64_t)ld * 2;
+  cuuint64_t strides[3] = {(cuuint64_t)ld * 2, batch0 > 1 ? (cuuint64_t)bs0 * 2 : safe, batch1 > 1 ? (cuuint64_t)bs1 * 2 : safe};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_outer, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(200 + (int)r);
+}
+
+bool g_attr_set[4] = {false, false, false, false};
+
+}  // namespace
+
+struct SbGemmArgs {
+  const void* A;
+  const void* B;
+  int M, N, K;
+  int a_mn_major, b_mn_major;
+  long long lda, ldb;
+  int batch0, batch1;
+  long long a_bs0, a_bs1, b_bs0, b_bs1;
+  void* D;
+  int d_is_f32;
+  long long ldd, d_bs0, d_bs1;
+  const void* bias;
+  int bias_is_f32;
+  const void* residual;
+  long long ldr, r_bs0, r_bs1;
+  const void* aux;
+  long long ldx, x_bs0, x_bs1;
+  void* D_pre;
+  long long ldp, p_bs0, p_bs1;
+  float alpha, beta;
+  int act, dact;
+  int max_ctas;  // 0 = one per SM
+};
+
+// Returns 0 on success, a negative code for invalid arguments, or a positive cudaError_t.
+SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batch0 <= 0 || a->batch1 <= 0) return -1;
+  CUtensorMap ta, tb;
+  int rc;
+  if (a->a_mn_major)
+    rc = make_operand_map(&ta, a->A, a->M, a->K, a->lda, a->batch0, a->batch1, a->a_bs0, a->a_bs1, BLOCK_K);
+  else
+    rc = make_operand_map(&ta, a->A, a->K, a->M, a->lda, a->batch0, a->batch1, a->a_bs0, a->a_bs1, BLOCK_M);
+  if (rc) return rc;
+  if (a->b_mn_major)
+    rc = make_operand_map(&tb, a->B, a->N, a->K, a->ldb, a->batch0, a->batch1, a->b_bs0, a->b_bs1, BLOCK_K);
+  else
+    rc = make_operand_map(&tb, a->B, a->K, a->N, a->ldb, a->batch0, a->batch1, a->b_bs0, a->b_bs1, BLOCK_N);
+  if (rc) return rc - 1000;
+  GemmParams p;
+  p.M = a->M; p.N = a->N; p.K = a->K;
+  p.batch0 = a->batch0; p.batch1 = a->batch1;
+  p.tiles_m = (a->M + BLOCK_M - 1) / BLOCK_M;
+  p.tiles_n = (a->N + BLOCK_N - 1) / BLOCK_N;
+  p.num_tiles = (long long)p.tiles_m * p.tiles_n * a->batch0 * a->batch1;
+  p.status = sb_status_ptr();
+  if (!p.status) return -2;
+  EpilogueArgs& e = p.ep;
+  e.D = a->D; e.d_is_f32 = a->d_is_f32; e.ldd = a->ldd; e.d_bs0 = a->d_bs0; e.d_bs1 = a->d_bs1;
+  e.bias_f32 = (a->bias && a->bias_is_f32) ? (const float*)a->bias : nullptr;
+  e.bias_bf16 = (a->bias && !a->bias_is_f32) ? (const __nv_bfloat16*)a->bias : nullptr;
+  e.residual = (const __nv_bfloat16*)a->residual; e.ldr = a->ldr; e.r_bs0 = a->r_bs0; e.r_bs1 = a->r_bs1;
+  e.aux = (const __nv_bfloat16*)a->aux; e.ldx = a->ldx; e.x_bs0 = a->x_bs0; e.x_bs1 = a->x_bs1;
+  e.D_pre = (__nv_bfloat16*)a->D_pre; e.ldp = a->ldp; e.p_bs0 = a->p_bs0; e.p_bs1 = a->p_bs1;
+  e.alpha = a->alpha; e.beta = a->beta; e.act = a->act; e.dact = (a->aux ? a->dact : 0);
+  int grid = sb_num_sms();
+  if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
+  if ((long long)grid > p.num_tiles) grid = (int)p.num_tiles;
+  const int variant = (a->a_mn_major ? 2 : 0) | (a->b_mn_major ? 1 : 0);
+  void (*kern)(const CUtensorMap, const CUtensorMap, const GemmParams) = nullptr;
+  switch (variant) {
+    case 0: kern = gemm_bf16_kernel<false, false>; break;
+    case 1: kern = gemm_bf16_kernel<false, true>; break;
+    case 2: kern = gemm_bf16_kernel<true, false>; break;
+    default: kern = gemm_bf16_kernel<true, true>; break;
+  }
+  if (!g_attr_set[variant]) {
+    cudaError_t ae = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (ae != cudaSuccess) return (int)ae;
+    g_attr_set[variant] = true;
+  }
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,48 @@
+// Device status word shared by all kernels of the library, plus host accessors.
+#include "common.cuh"
+#include <stdio.h>
+
+#define SB_MAX_DEVICES 16
+static __device__ int g_sb_status[4];
+static int* g_status_ptr[SB_MAX_DEVICES] = {nullptr};
+
+SB_API int* sb_status_ptr() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= SB_MAX_DEVICES) return nullptr;
+  if (g_status_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_sb_status) != cudaSuccess) return nullptr;
+    g_status_ptr[dev] = (int*)p;
+  }
+  return g_status_ptr[dev];
+}
+
+// Copies the 4-int status word to the host (synchronises the stream) and clears it when `clear` is set.
+SB_API int sb_read_status(int* out4, int clear, cudaStream_t stream) {
+  int* p = sb_status_ptr();
+  if (!p) return -1;
+  cudaError_t e = cudaMemcpyAsync(out4, p, 4 * sizeof(int), cudaMemcpyDeviceToHost, stream);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return (int)e;
+  if (clear && out4[0] != 0) {
+    e = cudaMemsetAsync(p, 0, 4 * sizeof(int), stream);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+
+SB_API const char* sb_status_string(int code) {
+  switch (code) {
+    case SB_OK: return "ok";
+    case SB_TIMEOUT_SMEM_EMPTY: return "timeout waiting for a free shared-memory stage";
+    case SB_TIMEOUT_SMEM_FULL: return "timeout waiting for a TMA load to land";
+    case SB_TIMEOUT_TMEM_EMPTY: return "timeout waiting for the epilogue to release an accumulator";
+    case SB_TIMEOUT_TMEM_FULL: return "timeout waiting for the tensor core to finish a tile";
+    case SB_TIMEOUT_PEER_FLAG: return "timeout waiting for a peer rank's flag";
+    case SB_BAD_ARGUMENT: return "bad argument";
+    default: return "unknown";
+  }
+}
+
+SB_API int sb_last_cuda_error() { return (int)cudaGetLastError(); }

@@ -1,0 +1,137 @@
+"""tcgen05 GEMM against an fp32 PyTorch reference: all four operand layouts, tails, batching, fused epilogues."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _native():
+    from speech_b200.ops import native
+
+    native.load()
+    return native
+
+
+def _ref(a, b, a_mn, b_mn):
+    A = a.float().transpose(-1, -2) if a_mn else a.float()
+    B = b.float().transpose(-1, -2) if b_mn else b.float()
+    return A @ B.transpose(-1, -2)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 384, 512), (250, 1032, 640), (3750, 1024, 1024), (77, 130, 200)])
+def test_gemm_layouts(a_mn, b_mn, M, N, K):
+    nat = _native()
+    torch.manual_seed(0)
+    Mp, Np, Kp = (M + 7) // 8 * 8, (N + 7) // 8 * 8, (K + 7) // 8 * 8
+    a = torch.randn((K, Mp) if a_mn else (M, Kp), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((K, Np) if b_mn else (N, Kp), device="cuda", dtype=torch.bfloat16)
+    av = a[:, :M] if a_mn else a[:, :K]
+    bv = b[:, :N] if b_mn else b[:, :K]
+    out = torch.full((M, Np), float("nan"), device="cuda", dtype=torch.float32)
+    nat.gemm(a, b, out, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, lda=a.stride(0), ldb=b.stride(0), ldd=Np)
+    nat.check_status()
+    ref = _ref(av, bv, a_mn, b_mn)
+    err = (out[:, :N] - ref).abs().max().item()
+    assert err <= 2e-2 * (K ** 0.5), f"max abs err {err}"
+    assert torch.isnan(out[:, N:]).all()
+
+
+def test_gemm_epilogue_bias_act_residual_pre():
+    nat = _native()
+    torch.manual_seed(1)
+    M, N, K = 300, 512, 256
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=torch.float32)
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    pre = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    nat.gemm(x, w, out, M=M, N=N, K=K, bias=bias, act="swish", residual=res, out_pre=pre, alpha=0.5)
+    nat.check_status()
+    z = (x.float() @ w.float().t()) + bias
+    ref = 0.5 * torch.nn.functional.silu(z) + res.float()
+    assert (pre.float() - z).abs().max() < 0.05
+    assert (out.float() - ref).abs().max() < 0.06
+
+
+def test_gemm_batched_strided():
+    nat = _native()
+    torch.manual_seed(2)
+    B, H, T, dk = 3, 4, 100, 64
+    q = torch.randn(B, T, H, dk, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(B, T, H, dk, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(B, H, T, T, device="cuda", dtype=torch.float32)
+    Tp = T
+    nat.gemm(q, k, out, M=T, N=T, K=dk, lda=H * dk, ldb=H * dk, ldd=T, batch=(H, B), a_bs=(dk, T * H * dk),
+             b_bs=(dk, T * H * dk), d_bs=(T * T, H * T * T))
+    nat.check_status()
+    ref = torch.einsum("bthd,bshd->bhts", q.float(), k.float())
+    assert (out - ref).abs().max() < 0.2
+
+
+def test_gemm_beta_accumulate_and_dact():
+    nat = _native()
+    torch.manual_seed(3)
+    M, N, K = 256, 256, 128
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.ones(M, N, device="cuda", dtype=torch.float32)
+    nat.gemm(a, b, out, M=M, N=N, K=K, beta=1.0)
+    ref = a.float() @ b.float().t() + 1.0
+    assert (out - ref).abs().max() < 0.3
+    aux = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    o2 = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    nat.gemm(a, b, o2, M=M, N=N, K=K, aux=aux, dact="relu")
+    ref2 = (a.float() @ b.float().t()) * (aux.float() > 0)
+    assert (o2.float() - ref2).abs().max() < 0.3
+    nat.check_status()
+
+
+def test_linear_layernorm_autograd_matches_reference():
+    from speech_b200 import ops
+    from speech_b200.ops import reference
+
+    torch.manual_seed(4)
+    M, K, N = 200, 256, 384
+    x = torch.randn(2, M // 2, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = torch.nn.Parameter(torch.randn(N, K, device="cuda") * 0.05)
+    b = torch.nn.Parameter(torch.randn(N, device="cuda") * 0.1)
+    g = torch.nn.Parameter(torch.rand(K, device="cuda") + 0.5)
+    be = torch.nn.Parameter(torch.randn(K, device="cuda") * 0.1)
+    y = ops.linear(ops.layer_norm(x, g, be), w, b, act="swish", alpha=0.5)
+    y.float().square().mean().backward()
+    got = [t.grad.float().clone() for t in (x, w, b, g, be)]
+    for t in (x, w, b, g, be):
+        t.grad = None
+    xr = x.detach().float().requires_grad_(True)
+    yr = reference.linear(reference.layer_norm(xr, g, be), w, b, act="swish", alpha=0.5)
+    yr.square().mean().backward()
+    ref = [xr.grad, w.grad, b.grad, g.grad, be.grad]
+    assert (y.float() - yr).abs().max() < 0.05
+    for name, a_, r_ in zip("x w b gamma beta".split(), got, ref):
+        denom = r_.abs().max().clamp(min=1e-6)
+        assert ((a_ - r_).abs().max() / denom) < 0.05, name
+    ops.native.check_status()
+
+
+def test_fused_adamw_matches_torch():
+    from speech_b200.core.optim.fused_adamw import FusedAdamW
+
+    torch.manual_seed(5)
+    ps = [torch.nn.Parameter(torch.randn(257, 33, device="cuda")), torch.nn.Parameter(torch.randn(1000, device="cuda"))]
+    ref = [torch.nn.Parameter(p.detach().clone()) for p in ps]
+    opt = FusedAdamW(ps, lr=1e-2, betas=(0.9, 0.98), weight_decay=0.01, max_grad_norm=1.0)
+    topt = torch.optim.AdamW(ref, lr=1e-2, betas=(0.9, 0.98), weight_decay=0.01)
+    for _ in range(3):
+        gs = [torch.randn_like(p) for p in ps]
+        opt.zero_grad()
+        for p, r, g in zip(ps, ref, gs):
+            p.grad.copy_(g)
+            r.grad = g.clone()
+        torch.nn.utils.clip_grad_norm_(ref, 1.0)
+        opt.step()
+        topt.step()
+    for p, r in zip(ps, ref):
+        assert (p - r).abs().max() < 1e-5
+        assert (p._lowp.float() - r).abs().max() < 2e-2
