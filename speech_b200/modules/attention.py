@@ -128,7 +128,9 @@ class MultiHeadAttention(nn.Module):
         if fused is not None:
             w, b = fused
             qkv = ops.linear(query, w, b).view(B, -1, 3, self.h, self.d_k)
+            self._last_qkv = qkv
             return qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        self._last_qkv = None
         q = ops.linear(query, self.linear_q.weight, self.linear_q.bias).view(B, -1, self.h, self.d_k)
         k = ops.linear(key, self.linear_k.weight, self.linear_k.bias).view(B, -1, self.h, self.d_k)
         v = ops.linear(value, self.linear_v.weight, self.linear_v.bias).view(B, -1, self.h, self.d_k)
@@ -198,7 +200,9 @@ class RelPositionMultiHeadAttention(MultiHeadAttention):
         q, k, v = self._qkv(query, key, value)
         nb = pos_emb.size(0)
         p = ops.linear(pos_emb.to(q.dtype), self.linear_pos.weight, None).view(nb, -1, self.h, self.d_k)
-        ctx = ops.relpos_attention(q, k, v, p, self.pos_bias_u, self.pos_bias_v, mask, self.dropout_rate, self.training)
+        ctx = ops.relpos_attention(q, k, v, p, self.pos_bias_u, self.pos_bias_v, mask, self.dropout_rate, self.training,
+                                   qkv=self._last_qkv)
+        self._last_qkv = None
         out = ops.linear(ctx, self.linear_out.weight, self.linear_out.bias, residual=residual)
         return out if cache is None else (out, cache)
 

@@ -123,15 +123,16 @@ def layer_norm(x, weight, bias, eps: float = 1e-5):
     return reference.layer_norm(x, weight, bias, eps)
 
 
-def relpos_attention(q, k, v, p, pos_bias_u, pos_bias_v, mask=None, dropout_p: float = 0.0, training: bool = False):
-    if _use_native(q) and q.dtype == torch.bfloat16 and not (dropout_p > 0 and training):
-        return _nat().relpos_attention(q, k, v, p, pos_bias_u, pos_bias_v, mask)
+def relpos_attention(q, k, v, p, pos_bias_u, pos_bias_v, mask=None, dropout_p: float = 0.0, training: bool = False,
+                     qkv=None):
+    if _use_native(q) and q.dtype == torch.bfloat16:
+        return _nat().relpos_attention(q, k, v, p, pos_bias_u, pos_bias_v, mask, dropout_p, training, qkv=qkv)
     return reference.relpos_attention(q, k, v, p, pos_bias_u, pos_bias_v, mask, dropout_p, training)
 
 
 def mha_attention(q, k, v, mask=None, dropout_p: float = 0.0, training: bool = False, scale=None):
-    if _use_native(q) and q.dtype == torch.bfloat16 and not (dropout_p > 0 and training):
-        return _nat().mha_attention(q, k, v, mask, scale)
+    if _use_native(q) and q.dtype == torch.bfloat16:
+        return _nat().mha_attention(q, k, v, mask, scale, dropout_p, training)
     return reference.mha_attention(q, k, v, mask, dropout_p, training, scale)
 
 
@@ -148,7 +149,7 @@ def conv_module_core(g, dw_weight, dw_bias, norm_type, norm_weight, norm_bias, r
 
 
 def lstm(x, weights, h0=None, c0=None, num_layers=1, dropout=0.0, training=False):
-    if _use_native(x) and x.dtype == torch.bfloat16 and not (dropout > 0 and training):
+    if _use_native(x) and x.dtype == torch.bfloat16 and not (dropout > 0 and training) and hasattr(_nat(), "lstm"):
         return _nat().lstm(x, weights, h0, c0, num_layers)
     return reference.lstm(x, weights, h0, c0, num_layers, dropout, training)
 
@@ -170,7 +171,7 @@ def transducer_loss_from_logits(logits, targets, f_len, y_len, blank, durations,
 
 
 def ctc_loss(log_probs, targets, input_lengths, target_lengths, blank, zero_infinity=True):
-    if _use_native(log_probs):
+    if _use_native(log_probs) and hasattr(_nat(), "ctc_loss"):
         return _nat().ctc_loss(log_probs, targets, input_lengths, target_lengths, blank)
     return reference.ctc_loss(log_probs, targets, input_lengths, target_lengths, blank, zero_infinity)
 
@@ -178,7 +179,7 @@ def ctc_loss(log_probs, targets, input_lengths, target_lengths, blank, zero_infi
 # ----------------------------------------------------------------------------- front-end
 def logmel(x, seq_len, window, fb, n_fft, hop, win_length, preemph=0.97, mag_power=2.0, log_zero_guard=2 ** -24,
            normalize="per_feature", pad_to=0, pad_value=0.0, dither=0.0, log=True):
-    if _use_native(x) and normalize in ("per_feature", None) and mag_power == 2.0 and log and n_fft == 512:
+    if _use_native(x) and normalize in ("per_feature", None) and mag_power == 2.0 and log and n_fft == 512 and hasattr(_nat(), "logmel"):
         return _nat().logmel(x, seq_len, window, fb, n_fft, hop, win_length, preemph, log_zero_guard,
                                normalize, pad_to, pad_value, dither)
     return reference.logmel(x, seq_len, window, fb, n_fft, hop, win_length, preemph, mag_power, log_zero_guard,

@@ -86,11 +86,13 @@ __global__ void glu_dwconv_fwd_kernel(const __nv_bfloat16* __restrict__ g, const
 }
 
 // mean / rstd per channel from sums (training) or running statistics (evaluation); also the running-stat update.
-__global__ void bn_finalize_kernel(const float* __restrict__ stats, float count, float* __restrict__ mean_rstd,
+__global__ void bn_finalize_kernel(const float* __restrict__ stats, float count_arg, const float* __restrict__ count_ptr,
+                                   float* __restrict__ mean_rstd,
                                    float* __restrict__ running_mean, float* __restrict__ running_var, int C, float eps,
                                    float momentum, int training) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
+  const float count = count_ptr ? *count_ptr : count_arg;
   float mean, var;
   if (training) {
     mean = stats[c] / count;
@@ -174,14 +176,15 @@ __global__ void dwconv_glu_bwd_kernel(const __nv_bfloat16* __restrict__ ds, cons
                                       const __nv_bfloat16* __restrict__ g, const uint8_t* __restrict__ pad,
                                       const float* __restrict__ w, const float* __restrict__ mean_rstd,
                                       const float* __restrict__ gamma, const float* __restrict__ beta,
-                                      const float* __restrict__ sums, float count, int training,
-                                      __nv_bfloat16* __restrict__ dg, float* __restrict__ dw, float* __restrict__ dbias, int T,
+                                      const float* __restrict__ sums, float count_arg,
+                                      const float* __restrict__ count_ptr, int training, __nv_bfloat16* __restrict__ dg, float* __restrict__ dw, float* __restrict__ dbias, int T,
                                       int C, int left) {
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (c >= C) return;
   const int b = blockIdx.z;
   const int t0 = blockIdx.y * TT;
   const int right = K - 1 - left;
+  const float count = count_ptr ? *count_ptr : count_arg;
   float wk[K][4], mu[4], rs[4], ga[4], be[4], m1[4], m2[4];
 #pragma unroll
   for (int k = 0; k < K; ++k)
@@ -284,13 +287,13 @@ int launch_fwd(const void* g, const uint8_t* pad, const float* w, const float* b
 }
 template <int K>
 int launch_bwd(const void* ds, const void* y, const void* g, const uint8_t* pad, const float* w, const float* mean_rstd,
-               const float* gamma, const float* beta, const float* sums, float count, int training, void* dg, float* dw,
-               float* dbias, int B, int T, int C, int left, cudaStream_t stream) {
+               const float* gamma, const float* beta, const float* sums, float count, const float* count_ptr, int training,
+               void* dg, float* dw, float* dbias, int B, int T, int C, int left, cudaStream_t stream) {
   const int threads = 128;
   dim3 grid((C / 4 + threads - 1) / threads, (T + TT - 1) / TT, B);
   dwconv_glu_bwd_kernel<K><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)ds, (const __nv_bfloat16*)y,
                                                         (const __nv_bfloat16*)g, pad, w, mean_rstd, gamma, beta, sums, count,
-                                                        training, (__nv_bfloat16*)dg, dw, dbias, T, C, left);
+                                                        count_ptr, training, (__nv_bfloat16*)dg, dw, dbias, T, C, left);
   return (int)cudaGetLastError();
 }
 
@@ -307,10 +310,10 @@ SB_API int sb_glu_dwconv_fwd(const void* g, const uint8_t* pad, const float* w, 
   }
 }
 
-SB_API int sb_bn_finalize(const float* stats, float count, float* mean_rstd, float* running_mean, float* running_var, int C,
-                          float eps, float momentum, int training, cudaStream_t stream) {
-  bn_finalize_kernel<<<(C + 255) / 256, 256, 0, stream>>>(stats, count, mean_rstd, running_mean, running_var, C, eps, momentum,
-                                                         training);
+SB_API int sb_bn_finalize(const float* stats, float count, const float* count_ptr, float* mean_rstd, float* running_mean,
+                          float* running_var, int C, float eps, float momentum, int training, cudaStream_t stream) {
+  bn_finalize_kernel<<<(C + 255) / 256, 256, 0, stream>>>(stats, count, count_ptr, mean_rstd, running_mean, running_var, C, eps,
+                                                         momentum, training);
   return (int)cudaGetLastError();
 }
 
@@ -340,13 +343,13 @@ SB_API int sb_bn_silu_bwd_stats(const void* ds, const void* y, const float* mean
 
 SB_API int sb_dwconv_glu_bwd(const void* ds, const void* y, const void* g, const uint8_t* pad, const float* w,
                              const float* mean_rstd, const float* gamma, const float* beta, const float* sums, float count,
-                             int training, void* dg, float* dw, float* dbias, int B, int T, int C, int K, int left,
+                             const float* count_ptr, int training, void* dg, float* dw, float* dbias, int B, int T, int C, int K, int left,
                              cudaStream_t stream) {
   if (C % 4 != 0 || B <= 0 || T <= 0) return -1;
   switch (K) {
-    case 5: return launch_bwd<5>(ds, y, g, pad, w, mean_rstd, gamma, beta, sums, count, training, dg, dw, dbias, B, T, C, left, stream);
-    case 9: return launch_bwd<9>(ds, y, g, pad, w, mean_rstd, gamma, beta, sums, count, training, dg, dw, dbias, B, T, C, left, stream);
-    case 15: return launch_bwd<15>(ds, y, g, pad, w, mean_rstd, gamma, beta, sums, count, training, dg, dw, dbias, B, T, C, left, stream);
+    case 5: return launch_bwd<5>(ds, y, g, pad, w, mean_rstd, gamma, beta, sums, count, count_ptr, training, dg, dw, dbias, B, T, C, left, stream);
+    case 9: return launch_bwd<9>(ds, y, g, pad, w, mean_rstd, gamma, beta, sums, count, count_ptr, training, dg, dw, dbias, B, T, C, left, stream);
+    case 15: return launch_bwd<15>(ds, y, g, pad, w, mean_rstd, gamma, beta, sums, count, count_ptr, training, dg, dw, dbias, B, T, C, left, stream);
     default: return -2;
   }
 }

@@ -7,11 +7,11 @@
 // forward (x W^T), input-gradient (dy W) and weight-gradient (dy^T x) GEMMs without any transposition pass.
 // Batched problems (attention scores per (batch, head)) use two batch indices with arbitrary strides.
 //
-// CTA layout (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor memory and issues the MMAs,
-// warps 2-5 run the epilogue (each owns 32 TMEM lanes).  The CTA is persistent over output tiles; two
-// accumulators (2 x 128 TMEM columns) let the epilogue of tile i overlap the MMAs of tile i+1.
-// Shared-memory stages hold a 128x64 A tile and a 128x64 B tile in the 128-byte swizzled layout that both
-// TMA and the tcgen05 shared-memory descriptors understand.
+// CTA layout (320 threads): warp 0 issues TMA loads, warp 1 allocates tensor memory and issues the MMAs,
+// warps 2-9 run the epilogue (two warps per 32-lane TMEM quarter, each draining half of the columns).  The CTA is
+// persistent over output tiles; two accumulators (2 x BN TMEM columns) let the epilogue of tile i overlap the MMAs
+// of tile i+1.  Shared-memory stages hold a 128x64 A tile and a BNx64 B tile (BN = 128 or 256) in the 128-byte
+// swizzled layout that both TMA and the tcgen05 shared-memory descriptors understand.
 //
 // Epilogue (all optional, applied in this order): v = acc + bias[n]; store pre-activation (bf16);
 // v = alpha * act(v); v *= act'(aux[m,n]); v += residual[m,n]; v += beta * D_old[m,n] (fp32 D only); store D as bf16 or fp32.
@@ -25,16 +25,15 @@
 namespace {
 
 constexpr int BLOCK_M = 128;
-constexpr int BLOCK_N = 128;
 constexpr int BLOCK_K = 64;  // 64 bf16 = 128 bytes = one swizzle atom row
 constexpr int UMMA_K = 16;
-constexpr int NUM_STAGES = 6;
 constexpr int NUM_ACC = 2;
 constexpr int TILE_BYTES = BLOCK_M * BLOCK_K * 2;  // 16 KiB per operand tile
-constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-constexpr int SMEM_BYTES = NUM_STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-constexpr int NUM_THREADS = 192;
-constexpr int TMEM_COLS = NUM_ACC * BLOCK_N;  // 256
+constexpr int NUM_THREADS = 320;  // warp 0: TMA, warp 1: MMA, warps 2-9: epilogue (two per TMEM lane quarter)
+// Tile width BN is a template parameter: 128 (6 stages) or 256 (4 stages; halves shared-memory traffic per flop).
+constexpr int num_stages(int bn) { return bn == 256 ? 4 : 6; }
+constexpr int stage_bytes(int bn) { return TILE_BYTES + bn * BLOCK_K * 2; }
+constexpr int smem_bytes(int bn) { return num_stages(bn) * stage_bytes(bn) + 1024 /*align*/ + 256 /*barriers*/; }
 
 struct EpilogueArgs {
   void* D;
@@ -54,6 +53,7 @@ struct EpilogueArgs {
 struct GemmParams {
   int M, N, K;
   int batch0, batch1;
+  int kfold;  // > 1: the K loop also runs over this many batch1 entries (sum over batch1 into one output)
   int tiles_m, tiles_n;
   long long num_tiles;
   EpilogueArgs ep;
@@ -153,10 +153,14 @@ __device__ __forceinline__ float apply_dact(float g, float z, int dact) {
   return g;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
+  constexpr int BLOCK_N = BN;
+  constexpr int NUM_STAGES = num_stages(BN);
+  constexpr int STAGE_BYTES = stage_bytes(BN);
+  constexpr int TMEM_COLS = NUM_ACC * BN;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
@@ -171,7 +175,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+  const int num_kb1 = (p.K + BLOCK_K - 1) / BLOCK_K;
+  const int num_kb = num_kb1 * p.kfold;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NUM_STAGES; ++s) {
@@ -180,7 +185,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);
+      mbar_init(tempty_bar(a), 8);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -205,8 +210,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int batch = (int)(tile / ((long long)p.tiles_m * p.tiles_n));
         const int rem = (int)(tile % ((long long)p.tiles_m * p.tiles_n));
         const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
-        const int b0 = batch % p.batch0, b1 = batch / p.batch0;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int b0 = batch % p.batch0;
+        for (int kbt = 0; kbt < num_kb; ++kbt, ++it) {
+          const int kb = kbt % num_kb1;
+          const int b1 = p.kfold > 1 ? kbt / num_kb1 : batch / p.batch0;
           const int s = (int)(it % NUM_STAGES);
           const uint32_t ph = (uint32_t)((it / NUM_STAGES) & 1);
           if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, SB_TIMEOUT_SMEM_EMPTY)) { ok = false; break; }
@@ -219,8 +226,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tma_load_4d(sa, &tmap_a, full_bar(s), kb * BLOCK_K, tm * BLOCK_M, b0, b1);
           }
           if (B_MN) {
-            tma_load_4d(sb, &tmap_b, full_bar(s), tn * BLOCK_N, kb * BLOCK_K, b0, b1);
-            tma_load_4d(sb + TILE_BYTES / 2, &tmap_b, full_bar(s), tn * BLOCK_N + 64, kb * BLOCK_K, b0, b1);
+#pragma unroll
+            for (int j = 0; j < BLOCK_N / 64; ++j)
+              tma_load_4d(sb + j * (TILE_BYTES / 2), &tmap_b, full_bar(s), tn * BLOCK_N + 64 * j, kb * BLOCK_K, b0, b1);
           } else {
             tma_load_4d(sb, &tmap_b, full_bar(s), kb * BLOCK_K, tn * BLOCK_N, b0, b1);
           }
@@ -263,7 +271,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
-    const int q = warp & 3;  // TMEM lane quarter owned by this warp
+    const int q = warp & 3;            // TMEM lane quarter owned by this warp
+    const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
     const EpilogueArgs& e = p.ep;
     long long tcount = 0;
     bool ok = true;
@@ -285,7 +294,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const long long x_off = (long long)b0 * e.x_bs0 + (long long)b1 * e.x_bs1 + (long long)row * e.ldx;
       const long long p_off = (long long)b0 * e.p_bs0 + (long long)b1 * e.p_bs1 + (long long)row * e.ldp;
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
+      for (int c = half * (BLOCK_N / 64); c < (half + 1) * (BLOCK_N / 64); ++c) {
         uint32_t r[32];
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BLOCK_N + c * 32);
         tmem_ld32(taddr, r);
@@ -449,7 +458,7 @@ int make_operand_map(CUtensorMap* map, const void* ptr, long long inner, long lo
   return r == CUDA_SUCCESS ? 0 : -(200 + (int)r);
 }
 
-bool g_attr_set[4] = {false, false, false, false};
+bool g_attr_set[8] = {false, false, false, false, false, false, false, false};
 
 }  // namespace
 
@@ -475,11 +484,20 @@ struct SbGemmArgs {
   float alpha, beta;
   int act, dact;
   int max_ctas;  // 0 = one per SM
+  int fold_batch1;  // 1: sum over batch1 inside the K loop; D then has no batch1 dimension
+  int tile_n;       // 128 or 256 to force the tile width, anything else = automatic
 };
 
 // Returns 0 on success, a negative code for invalid arguments, or a positive cudaError_t.
 SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   if (a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batch0 <= 0 || a->batch1 <= 0) return -1;
+  // 256-wide tiles when the problem has enough of them to fill the machine, else 128-wide
+  int bn = a->tile_n;
+  if (bn != 128 && bn != 256) {
+    const long long t256 = (long long)((a->M + BLOCK_M - 1) / BLOCK_M) * ((a->N + 255) / 256) * a->batch0 *
+                           (a->fold_batch1 ? 1 : a->batch1);
+    bn = (a->N >= 256 && t256 >= (long long)sb_num_sms() * 3 / 4) ? 256 : 128;
+  }
   CUtensorMap ta, tb;
   int rc;
   if (a->a_mn_major)
@@ -490,14 +508,15 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   if (a->b_mn_major)
     rc = make_operand_map(&tb, a->B, a->N, a->K, a->ldb, a->batch0, a->batch1, a->b_bs0, a->b_bs1, BLOCK_K);
   else
-    rc = make_operand_map(&tb, a->B, a->K, a->N, a->ldb, a->batch0, a->batch1, a->b_bs0, a->b_bs1, BLOCK_N);
+    rc = make_operand_map(&tb, a->B, a->K, a->N, a->ldb, a->batch0, a->batch1, a->b_bs0, a->b_bs1, bn);
   if (rc) return rc - 1000;
   GemmParams p;
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.batch0 = a->batch0; p.batch1 = a->batch1;
   p.tiles_m = (a->M + BLOCK_M - 1) / BLOCK_M;
-  p.tiles_n = (a->N + BLOCK_N - 1) / BLOCK_N;
-  p.num_tiles = (long long)p.tiles_m * p.tiles_n * a->batch0 * a->batch1;
+  p.tiles_n = (a->N + bn - 1) / bn;
+  p.kfold = a->fold_batch1 ? a->batch1 : 1;
+  p.num_tiles = (long long)p.tiles_m * p.tiles_n * a->batch0 * (a->fold_batch1 ? 1 : a->batch1);
   p.status = sb_status_ptr();
   if (!p.status) return -2;
   EpilogueArgs& e = p.ep;
@@ -511,19 +530,24 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   int grid = sb_num_sms();
   if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
   if ((long long)grid > p.num_tiles) grid = (int)p.num_tiles;
-  const int variant = (a->a_mn_major ? 2 : 0) | (a->b_mn_major ? 1 : 0);
+  const int variant = (a->a_mn_major ? 2 : 0) | (a->b_mn_major ? 1 : 0) | (bn == 256 ? 4 : 0);
   void (*kern)(const CUtensorMap, const CUtensorMap, const GemmParams) = nullptr;
   switch (variant) {
-    case 0: kern = gemm_bf16_kernel<false, false>; break;
-    case 1: kern = gemm_bf16_kernel<false, true>; break;
-    case 2: kern = gemm_bf16_kernel<true, false>; break;
-    default: kern = gemm_bf16_kernel<true, true>; break;
+    case 0: kern = gemm_bf16_kernel<false, false, 128>; break;
+    case 1: kern = gemm_bf16_kernel<false, true, 128>; break;
+    case 2: kern = gemm_bf16_kernel<true, false, 128>; break;
+    case 3: kern = gemm_bf16_kernel<true, true, 128>; break;
+    case 4: kern = gemm_bf16_kernel<false, false, 256>; break;
+    case 5: kern = gemm_bf16_kernel<false, true, 256>; break;
+    case 6: kern = gemm_bf16_kernel<true, false, 256>; break;
+    default: kern = gemm_bf16_kernel<true, true, 256>; break;
   }
+  const int smem = smem_bytes(bn);
   if (!g_attr_set[variant]) {
-    cudaError_t ae = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t ae = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (ae != cudaSuccess) return (int)ae;
     g_attr_set[variant] = true;
   }
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  kern<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, p);
   return (int)cudaGetLastError();
 }

@@ -36,7 +36,7 @@ class SbGemmArgs(ctypes.Structure):
         ("aux", ctypes.c_void_p), ("ldx", ctypes.c_longlong), ("x_bs0", ctypes.c_longlong), ("x_bs1", ctypes.c_longlong),
         ("D_pre", ctypes.c_void_p), ("ldp", ctypes.c_longlong), ("p_bs0", ctypes.c_longlong), ("p_bs1", ctypes.c_longlong),
         ("alpha", ctypes.c_float), ("beta", ctypes.c_float), ("act", ctypes.c_int), ("dact", ctypes.c_int),
-        ("max_ctas", ctypes.c_int),
+        ("max_ctas", ctypes.c_int), ("fold_batch1", ctypes.c_int), ("tile_n", ctypes.c_int),
     ]
 
 
@@ -96,7 +96,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
          ldr: Optional[int] = None, r_bs: Tuple[int, int] = (0, 0), aux: Optional[torch.Tensor] = None, dact: Optional[str] = None,
          ldx: Optional[int] = None, x_bs: Tuple[int, int] = (0, 0), out_pre: Optional[torch.Tensor] = None,
          ldp: Optional[int] = None, p_bs: Tuple[int, int] = (0, 0), alpha: float = 1.0, beta: float = 0.0,
-         max_ctas: int = 0) -> torch.Tensor:
+         max_ctas: int = 0, fold_batch1: bool = False, tile_n: int = 0) -> torch.Tensor:
     """``out = epilogue(alpha * A @ B^T)`` on raw strided bf16 operands (see csrc/gemm_tcgen05.cu).
 
     ``a_mn`` / ``b_mn``: the operand is stored transposed (A as [K, M], B as [K, N]).  ``lda`` / ``ldb`` are the row
@@ -139,6 +139,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
         g.p_bs0, g.p_bs1 = p_bs
     g.alpha, g.beta, g.act = alpha, beta, ACT[act]
     g.max_ctas = max_ctas
+    g.fold_batch1 = int(fold_batch1)
+    g.tile_n = int(tile_n)
     _check(lib().sb_gemm_bf16(ctypes.byref(g), _stream()), "sb_gemm_bf16")
     return out
 
@@ -331,3 +333,7 @@ def adamw_flat(master, grad, exp_avg, exp_avg_sq, lowp, lr, beta1, beta2, eps, w
     _check(lib().sb_adamw(_ptr(master), _ptr(grad), _ptr(exp_avg), _ptr(exp_avg_sq), _ptr(lowp), ctypes.c_longlong(master.numel()),
                           ctypes.c_float(lr), ctypes.c_float(beta1), ctypes.c_float(beta2), ctypes.c_float(eps),
                           ctypes.c_float(weight_decay), ctypes.c_int(step), _ptr(scalars), _stream()), "sb_adamw")
+
+
+from .native_blocks import conv_module_core, mha_attention, relpos_attention  # noqa: E402,F401
+from .native_transducer import transducer_joint_loss, transducer_loss_from_logits  # noqa: E402,F401

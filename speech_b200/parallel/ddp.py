@@ -134,6 +134,9 @@ class GradSync:
             for p in b["params"]:
                 self._bucket_of[id(p)] = bi
         self._hooks = []
+        if self.arena is not None:
+            # kernels that write a gradient straight into the arena report it here (autograd hooks do not fire for them)
+            self.arena.grad_ready = self.mark_ready
         for p in self.params:
             self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(p)))
 
@@ -145,7 +148,7 @@ class GradSync:
 
     # ------------------------------------------------------------------ step protocol
     def begin_step(self):
-        self._pending = [len(b["params"]) for b in self.buckets]
+        self._pending = [{id(p) for p in b["params"]} for b in self.buckets]
         self._launched = [False] * len(self.buckets)
         self._works = []
 
@@ -165,8 +168,8 @@ class GradSync:
         bi = self._bucket_of.get(id(param))
         if bi is None or self._launched[bi]:
             return
-        self._pending[bi] -= 1
-        if self._pending[bi] <= 0:
+        self._pending[bi].discard(id(param))
+        if not self._pending[bi]:
             self._launch(bi)
 
     def _launch(self, bi: int):

@@ -1,0 +1,186 @@
+"""CPU tests of the core layer: config tree, instantiation allow-list, neural types, schedulers, optimizers."""
+import math
+import os
+
+import pytest
+import torch
+
+from speech_b200.core.config import DictConfig, MissingMandatoryValue, OmegaConf, apply_overrides, hydra_runner, open_dict
+from speech_b200.core.instantiate import instantiate, locate
+from speech_b200.core.neural_types import (AcousticEncodedRepresentation, AudioSignal, ChannelType, LengthsType, NeuralType,
+                                           NeuralTypeComparisonResult, SpectrogramType, MelSpectrogramType, typecheck)
+from speech_b200.core.optim import lr_scheduler as S
+from speech_b200.core.optim.optimizers import AVAILABLE_OPTIMIZERS, get_optimizer, parse_optimizer_args
+
+
+def test_config_interpolation_and_resolvers():
+    cfg = OmegaConf.create({"a": {"b": 4, "c": "${a.b}"}, "d": "${multiply:${a.b},3}", "e": "x_${a.c}", "f": "${sum:1,2,3}",
+                            "lst": [1, {"k": "${a.b}"}]})
+    assert cfg.a.c == 4 and cfg.d == 12 and cfg.e == "x_4" and cfg.f == 6
+    assert cfg.lst[1].k == 4
+    plain = OmegaConf.to_container(cfg, resolve=True)
+    assert plain["d"] == 12 and plain["lst"][1]["k"] == 4
+    y = OmegaConf.to_yaml(cfg)
+    again = OmegaConf.create(y)
+    assert again.a.c == 4
+
+
+def test_config_struct_missing_and_overrides(tmp_path):
+    cfg = OmegaConf.create({"model": {"lr": 1e-3, "name": "???"}, "trainer": {"devices": 1}})
+    with pytest.raises(MissingMandatoryValue):
+        _ = cfg.model.name
+    OmegaConf.set_struct(cfg, True)
+    with pytest.raises(Exception):
+        cfg.model.new_key = 1
+    with open_dict(cfg):
+        cfg.model.new_key = 1
+    apply_overrides(cfg, ["model.lr=0.5", "+model.extra.k=[1,2]", "trainer.devices=8", "~model.new_key", "model.name=abc"])
+    assert cfg.model.lr == 0.5 and cfg.model.extra.k == [1, 2] and cfg.trainer.devices == 8 and "new_key" not in cfg.model
+    assert cfg.model.name == "abc"
+    p = tmp_path / "c.yaml"
+    OmegaConf.save(cfg, str(p))
+    assert OmegaConf.load(str(p)) == cfg
+    merged = OmegaConf.merge(cfg, {"model": {"lr": 2.0}, "z": 1})
+    assert merged.model.lr == 2.0 and merged.z == 1 and merged.model.name == "abc"
+
+
+def test_yaml_float_exponent():
+    assert OmegaConf.create("lr: 1e-3").lr == pytest.approx(1e-3)
+
+
+def test_hydra_runner(tmp_path):
+    (tmp_path / "conf.yaml").write_text("model:\n  dim: 8\n  scale: ${multiply:${model.dim},2}\n")
+    seen = {}
+
+    @hydra_runner(config_path=str(tmp_path), config_name="conf")
+    def main(cfg):
+        seen["cfg"] = cfg
+        return cfg.model.scale
+
+    assert main(argv=["model.dim=16"]) == 32
+    assert seen["cfg"].model.dim == 16
+
+
+def test_instantiate_allow_list_and_alias():
+    enc = instantiate({"_target_": "nemo.collections.asr.modules.ConvASRDecoder", "feat_in": 16, "num_classes": 5,
+                       "vocabulary": list("abcde")})
+    assert type(enc).__name__ == "ConvASRDecoder" and enc.num_classes_with_blank == 6
+    with pytest.raises(ValueError):
+        instantiate({"_target_": "os.system", "command": "true"})
+    assert locate("torch.nn.Linear") is torch.nn.Linear
+
+
+def test_neural_types_and_typecheck():
+    a = NeuralType(("B", "D", "T"), SpectrogramType())
+    b = NeuralType(("B", "D", "T"), MelSpectrogramType())
+    assert a.compare(b) == NeuralTypeComparisonResult.GREATER and b.compare(a) == NeuralTypeComparisonResult.LESS
+    assert a.compare(NeuralType(("B", "T", "D"), SpectrogramType())) == NeuralTypeComparisonResult.TRANSPOSE_SAME
+    assert NeuralType(("B", "T"), AudioSignal(16000)).compare(NeuralType(("B", "T"), AudioSignal(8000))) == \
+        NeuralTypeComparisonResult.SAME_TYPE_INCOMPATIBLE_PARAMS
+
+    class M(torch.nn.Module):
+        @property
+        def input_types(self):
+            return {"x": NeuralType(("B", "T"), ChannelType()), "n": NeuralType(("B",), LengthsType(), optional=True)}
+
+        @property
+        def output_types(self):
+            return {"y": NeuralType(("B", "T"), ChannelType())}
+
+        @typecheck()
+        def forward(self, x, n=None):
+            return x * 2
+
+    m = M()
+    out = m(x=torch.ones(2, 3))
+    assert out.neural_type.elements_type.__class__ is ChannelType
+    with pytest.raises(TypeError):
+        m(torch.ones(2, 3))
+    with pytest.raises(TypeError):
+        m(x=torch.ones(2, 3, 4))
+    with typecheck.disable_checks():
+        m(torch.ones(2, 3))
+
+
+def test_noam_and_cosine_schedules():
+    p = [torch.nn.Parameter(torch.zeros(1))]
+    opt = torch.optim.SGD(p, lr=2.0)
+    sch = S.NoamAnnealing(opt, d_model=256, warmup_steps=100, min_lr=1e-6)
+    lrs = []
+    for _ in range(300):
+        opt.step()
+        sch.step()
+        lrs.append(opt.param_groups[0]["lr"])
+    step = 150
+    expect = 2.0 * 256 ** -0.5 * min(step ** -0.5, step * 100 ** -1.5)
+    assert lrs[step - 1] == pytest.approx(expect, rel=1e-6)
+    assert max(lrs) == pytest.approx(2.0 * 256 ** -0.5 * 100 ** -0.5, rel=1e-6)
+    opt = torch.optim.SGD(p, lr=1.0)
+    cos = S.CosineAnnealing(opt, max_steps=100, warmup_steps=10, min_lr=0.1)
+    vals = []
+    for _ in range(100):
+        opt.step()
+        cos.step()
+        vals.append(opt.param_groups[0]["lr"])
+    assert vals[9] == pytest.approx(1.0, rel=1e-6)
+    assert vals[-1] == pytest.approx(0.1, abs=1e-6)
+    assert all(x >= y - 1e-9 for x, y in zip(vals[10:], vals[11:]))
+
+
+def test_scheduler_registry_and_prepare():
+    names = ["WarmupPolicy", "WarmupHoldPolicy", "SquareAnnealing", "CosineAnnealing", "NoamAnnealing", "NoamHoldAnnealing",
+             "WarmupAnnealing", "InverseSquareRootAnnealing", "T5InverseSquareRootAnnealing", "SquareRootAnnealing",
+             "PolynomialDecayAnnealing", "PolynomialHoldDecayAnnealing", "StepLR", "ExponentialLR", "ReduceLROnPlateau", "CyclicLR",
+             "WarmupHoldAnnealOneMinusSquareRoot", "WarmupHoldAnnealLinear"]
+    for n in names:
+        assert n in S.AVAILABLE_SCHEDULERS
+    opt = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=1.0)
+    out = S.prepare_lr_scheduler(opt, {"name": "CosineAnnealing", "warmup_steps": 2, "max_steps": 10, "min_lr": 0.0})
+    assert out["interval"] == "step" and isinstance(out["scheduler"], S.CosineAnnealing)
+
+
+def test_optimizer_registry():
+    for n in ["sgd", "adam", "adamw", "adadelta", "adamax", "adagrad", "rmsprop", "rprop", "novograd", "adafactor", "adan",
+              "fused_adam"]:
+        assert n in AVAILABLE_OPTIMIZERS
+    kw = parse_optimizer_args("adamw", {"name": "adamw", "lr": 1e-3, "betas": [0.9, 0.98], "sched": {"name": "x"}})
+    assert kw == {"lr": 1e-3, "betas": (0.9, 0.98)}
+    w = torch.nn.Parameter(torch.tensor([1.0, -2.0, 3.0]))
+    for name in ("novograd", "adan", "adafactor"):
+        kwargs = {"lr": 0.05} if name != "adafactor" else {"lr": 0.05, "relative_step": False, "scale_parameter": False}
+        q = torch.nn.Parameter(w.detach().clone())
+        opt = get_optimizer(name)([q], **kwargs)
+        first = None
+        for _ in range(30):
+            opt.zero_grad()
+            loss = (q ** 2).sum()
+            first = first if first is not None else float(loss)
+            loss.backward()
+            opt.step()
+        assert float((q ** 2).sum()) < first, name
+
+
+def test_fused_adamw_cpu_matches_torch_and_fusion_views():
+    from speech_b200.core.optim.fused_adamw import FusedAdamW
+
+    torch.manual_seed(0)
+    a, b, c = (torch.nn.Parameter(torch.randn(128, 16)) for _ in range(3))
+    other = torch.nn.Parameter(torch.randn(7))
+    ref = [torch.nn.Parameter(p.detach().clone()) for p in (a, other, b, c)]
+    opt = FusedAdamW([a, other, b, c], lr=1e-2, betas=(0.9, 0.98), weight_decay=0.1, fusion_groups=[[a, b, c]])
+    fused = opt.arena.fuse([a, b, c])
+    assert fused is not None and fused.shape == (384, 16)
+    assert fused.data_ptr() == a.data_ptr()
+    topt = torch.optim.AdamW(ref, lr=1e-2, betas=(0.9, 0.98), weight_decay=0.1)
+    for _ in range(4):
+        opt.zero_grad()
+        for p, r in zip((a, other, b, c), ref):
+            g = torch.randn_like(p)
+            p.grad.copy_(g)
+            r.grad = g.clone()
+        opt.step()
+        topt.step()
+    for p, r in zip((a, other, b, c), ref):
+        assert torch.allclose(p, r, atol=1e-6)
+    sd = opt.state_dict()
+    opt.load_state_dict(sd)
