@@ -203,3 +203,6 @@ def grad_norm_clip_coef(flat_grad, scalars, max_norm: float, grad_scale: float =
     norm = flat_grad.float().norm() * grad_scale
     scalars[0] = norm
     scalars[1] = grad_scale * torch.clamp(max_norm / (norm + 1e-6), max=1.0)
+
+
+from . import native  # noqa: E402,F401  (binding module; the shared library itself is loaded on first use)

@@ -337,3 +337,6 @@ def adamw_flat(master, grad, exp_avg, exp_avg_sq, lowp, lr, beta1, beta2, eps, w
 
 from .native_blocks import conv_module_core, mha_attention, relpos_attention  # noqa: E402,F401
 from .native_transducer import transducer_joint_loss, transducer_loss_from_logits  # noqa: E402,F401
+from .native_lstm import lstm  # noqa: E402,F401
+from .native_ctc import ctc_loss  # noqa: E402,F401
+from .native_logmel import logmel  # noqa: E402,F401

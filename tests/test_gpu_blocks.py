@@ -5,8 +5,10 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _rel_err(a, b):
-    return ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp(min=1e-6)).item()
+def _rel_err(a, b, floor=5e-3):
+    """Max abs error relative to the reference's largest magnitude; gradients that are analytically zero (a bias in
+    front of a train-mode BatchNorm, the key bias of a softmax) only have to be small in absolute terms."""
+    return ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp(min=floor)).item()
 
 
 @pytest.mark.parametrize("fused", [False, True])
