@@ -50,12 +50,12 @@ def _install_default_aliases() -> None:
     a("nemo.collections.asr.modules.StatelessTransducerDecoder", M + "rnnt.StatelessTransducerDecoder")
     a("nemo.collections.asr.modules.SampledRNNTJoint", M + "rnnt.SampledRNNTJoint")
     a("nemo.collections.asr.modules.HATJoint", M + "rnnt.HATJoint")
-    a("nemo.collections.asr.modules.transformer.get_nemo_transformer", M + "transformer.get_transformer")
-    a("nemo.collections.asr.modules.transformer.transformer.TransformerDecoderNM", M + "transformer.TransformerDecoderNM")
-    a("nemo.collections.asr.modules.transformer.TransformerDecoderNM", M + "transformer.TransformerDecoderNM")
-    a("nemo.collections.asr.modules.transformer.TransformerEncoderNM", M + "transformer.TransformerEncoderNM")
-    a("nemo.collections.asr.parts.submodules.token_classifier.TokenClassifier", M + "transformer.TokenClassifier")
-    a("nemo.collections.common.parts.MultiLayerPerceptron", M + "transformer.MultiLayerPerceptron")
+    a("nemo.collections.asr.modules.transformer.get_nemo_transformer", M + "transformer_nm.get_transformer")
+    a("nemo.collections.asr.modules.transformer.transformer.TransformerDecoderNM", M + "transformer_nm.TransformerDecoderNM")
+    a("nemo.collections.asr.modules.transformer.TransformerDecoderNM", M + "transformer_nm.TransformerDecoderNM")
+    a("nemo.collections.asr.modules.transformer.TransformerEncoderNM", M + "transformer_nm.TransformerEncoderNM")
+    a("nemo.collections.asr.parts.submodules.token_classifier.TokenClassifier", M + "transformer_nm.TokenClassifier")
+    a("nemo.collections.common.parts.MultiLayerPerceptron", M + "transformer_nm.MultiLayerPerceptron")
     a("nemo.collections.asr.modules.SortformerModules", M + "sortformer.SortformerModules")
     a("nemo.collections.asr.modules.transformer.transformer_encoders.TransformerEncoder", M + "transformer.TransformerEncoder")
     a("nemo.collections.asr.losses.ctc.CTCLoss", "speech_b200.losses.ctc.CTCLoss")

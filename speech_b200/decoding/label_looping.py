@@ -131,11 +131,17 @@ class GreedyBatchedLabelLoopingComputer:
                  ) -> Tuple[BatchedHyps, None, LabelLoopingState]:
         """x: [B, T, D_enc] encoder output; out_len: [B].  Returns (hyps, alignments, state)."""
         use_graph = (x.is_cuda and self.allow_cuda_graphs and self.cuda_graphs_mode != "no_graphs"
-                     and not self.fusion_models and not ops.eager_allowed() and ops.native_available())
+                     and not self.fusion_models and not ops.eager_allowed() and ops.native_available()
+                     and self._graph_supported())
         with torch.autocast(x.device.type, enabled=False), ops.compute_dtype(None):
             if use_graph:
                 return self._graph_impl(x, out_len, prev_batched_state)
             return self.torch_impl(x, out_len, prev_batched_state)
+
+    def _graph_supported(self) -> bool:
+        from ..ops import native
+
+        return hasattr(native, "LabelLoopingGraph") and native.LabelLoopingGraph.supports(self)
 
     def _graph_impl(self, x, out_len, prev):
         from ..ops import native

@@ -1,0 +1,34 @@
+// C interface of the tcgen05 GEMM (implemented in gemm_tcgen05.cu); used by the Python bindings and by other kernels' host
+// drivers in this library (the LSTM recurrence issues one small GEMM per time step).
+#pragma once
+#include "common.cuh"
+
+struct SbGemmArgs {
+  const void* A;
+  const void* B;
+  int M, N, K;
+  int a_mn_major, b_mn_major;
+  long long lda, ldb;
+  int batch0, batch1;
+  long long a_bs0, a_bs1, b_bs0, b_bs1;
+  void* D;
+  int d_is_f32;
+  long long ldd, d_bs0, d_bs1;
+  const void* bias;
+  int bias_is_f32;
+  const void* residual;
+  long long ldr, r_bs0, r_bs1;
+  const void* aux;
+  long long ldx, x_bs0, x_bs1;
+  void* D_pre;
+  long long ldp, p_bs0, p_bs1;
+  float alpha, beta;
+  int act, dact;
+  int max_ctas;  // 0 = one per SM
+  int fold_batch1;  // 1: sum over batch1 inside the K loop; D then has no batch1 dimension
+  int tile_n;       // 128 or 256 to force the tile width, anything else = automatic
+};
+
+
+// Returns 0 on success, a negative code for invalid arguments, or a positive cudaError_t.
+SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream);

@@ -19,6 +19,7 @@
 // Every mbarrier wait is bounded (see common.cuh): on a timeout the kernel records a status code and all roles
 // fall through to the common exit where tensor memory is released.
 #include "common.cuh"
+#include "gemm_api.h"
 #include <cuda.h>
 #include <stdio.h>
 
@@ -461,32 +462,6 @@ int make_operand_map(CUtensorMap* map, const void* ptr, long long inner, long lo
 bool g_attr_set[8] = {false, false, false, false, false, false, false, false};
 
 }  // namespace
-
-struct SbGemmArgs {
-  const void* A;
-  const void* B;
-  int M, N, K;
-  int a_mn_major, b_mn_major;
-  long long lda, ldb;
-  int batch0, batch1;
-  long long a_bs0, a_bs1, b_bs0, b_bs1;
-  void* D;
-  int d_is_f32;
-  long long ldd, d_bs0, d_bs1;
-  const void* bias;
-  int bias_is_f32;
-  const void* residual;
-  long long ldr, r_bs0, r_bs1;
-  const void* aux;
-  long long ldx, x_bs0, x_bs1;
-  void* D_pre;
-  long long ldp, p_bs0, p_bs1;
-  float alpha, beta;
-  int act, dact;
-  int max_ctas;  // 0 = one per SM
-  int fold_batch1;  // 1: sum over batch1 inside the K loop; D then has no batch1 dimension
-  int tile_n;       // 128 or 256 to force the tile width, anything else = automatic
-};
 
 // Returns 0 on success, a negative code for invalid arguments, or a positive cudaError_t.
 SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {

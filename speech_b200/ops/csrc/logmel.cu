@@ -60,7 +60,7 @@ __global__ void logmel_frames_kernel(const float* __restrict__ wave, long long w
       const int wi = i - woff;
       if (wi >= 0 && wi < win_len) {
         float cur = sample_at(x, n, len, dither, seed, nbase);
-        if (preemph != 0.f && n > 0) cur -= preemph * sample_at(x, n - 1, len, dither, seed, nbase);
+        if (preemph != 0.f && n > 0 && n < len) cur -= preemph * sample_at(x, n - 1, len, dither, seed, nbase);
         v = cur * window[wi];
       }
       const int r = __brev((unsigned)i) >> 23;  // 9-bit reversal

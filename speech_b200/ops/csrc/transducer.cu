@@ -274,28 +274,34 @@ __global__ void joint_dlogits_kernel(const float* __restrict__ z, int ldz, const
   }
 }
 
-// df[b,t,:] = sum_u dh[(b,t,u),:]; dg[b,u,:] = sum_t dh[(b,t,u),:]   (dh bf16 [nb*T*U1, Hj], outputs fp32 accumulators)
+// df[b,t,:] = sum_u dh[(b,t,u),:]; dg[b,u,:] = sum_t dh[(b,t,u),:]   (dh bf16 [nb*T*U1, Hj], outputs fp32).
+// One block per output row (a (b,t) pair for df, a (b,u) pair for dg); a thread owns two adjacent channels.
 __global__ void joint_reduce_dh_kernel(const __nv_bfloat16* __restrict__ dh, float* __restrict__ df, float* __restrict__ dg,
                                        int b0, int nb, int T, int U1, int Hj) {
-  // grid.x over channel groups (blockDim threads x 1 channel), grid.y over (b_local): each thread loops t,u
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = 2 * (blockIdx.y * blockDim.x + threadIdx.x);
   if (c >= Hj) return;
-  const int bl = blockIdx.y;
-  const int which = blockIdx.z;  // 0: df (loop u inside t), 1: dg (loop t inside u)
-  const __nv_bfloat16* base = dh + (long long)bl * T * U1 * Hj + c;
-  const int b = b0 + bl;
-  if (which == 0) {
-    for (int t = 0; t < T; ++t) {
-      float s = 0.f;
-      for (int u = 0; u < U1; ++u) s += __bfloat162float(base[((long long)t * U1 + u) * Hj]);
-      df[((long long)b * T + t) * Hj + c] = s;
-    }
-  } else {
+  const int n_df = nb * T;
+  int row = blockIdx.x;
+  float s0 = 0.f, s1 = 0.f;
+  if (row < n_df) {
+    const int bl = row / T, t = row % T;
+    const __nv_bfloat16* p = dh + ((long long)bl * T + t) * U1 * Hj + c;
     for (int u = 0; u < U1; ++u) {
-      float s = 0.f;
-      for (int t = 0; t < T; ++t) s += __bfloat162float(base[((long long)t * U1 + u) * Hj]);
-      dg[((long long)b * U1 + u) * Hj + c] = s;
+      const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + (long long)u * Hj));
+      s0 += v.x; s1 += v.y;
     }
+    float* o = df + ((long long)(b0 + bl) * T + t) * Hj + c;
+    o[0] = s0; o[1] = s1;
+  } else {
+    row -= n_df;
+    const int bl = row / U1, u = row % U1;
+    const __nv_bfloat16* p = dh + ((long long)bl * T * U1 + u) * Hj + c;
+    for (int t = 0; t < T; ++t) {
+      const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + (long long)t * U1 * Hj));
+      s0 += v.x; s1 += v.y;
+    }
+    float* o = dg + ((long long)(b0 + bl) * U1 + u) * Hj + c;
+    o[0] = s0; o[1] = s1;
   }
 }
 
@@ -368,7 +374,9 @@ SB_API int sb_joint_dlogits(const float* z, int ldz, const long long* targets, i
 }
 
 SB_API int sb_joint_reduce_dh(const void* dh, float* df, float* dg, int b0, int nb, int T, int U1, int Hj, cudaStream_t stream) {
-  dim3 grid((Hj + 127) / 128, nb, 2);
-  joint_reduce_dh_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)dh, df, dg, b0, nb, T, U1, Hj);
+  if (Hj % 2 != 0) return -1;
+  const int threads = 128;
+  dim3 grid(nb * T + nb * U1, (Hj / 2 + threads - 1) / threads);
+  joint_reduce_dh_kernel<<<grid, threads, 0, stream>>>((const __nv_bfloat16*)dh, df, dg, b0, nb, T, U1, Hj);
   return (int)cudaGetLastError();
 }

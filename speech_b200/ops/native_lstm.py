@@ -33,14 +33,13 @@ class _LSTMFn(torch.autograd.Function):
             N.gemm(inp.view(U * B, In), wih, xproj, M=U * B, N=4 * H, K=In, bias=bias)
             acts = torch.empty((U, B, 4 * H), dtype=torch.float32, device=dev)
             c_all = torch.empty((U, B, H), dtype=torch.float32, device=dev)
-            h_all = torch.empty((U, B, H), dtype=torch.float32, device=dev)
             y = torch.empty((U, B, H), dtype=torch.bfloat16, device=dev)
-            h0l = h0[l].float().contiguous() if h0 is not None else None
+            h0l = h0[l].to(torch.bfloat16).contiguous() if h0 is not None else None
             c0l = c0[l].float().contiguous() if c0 is not None else None
             N._check(N.lib().sb_lstm_forward(N._ptr(xproj), N._ptr(h0l), N._ptr(c0l), N._ptr(whh), N._ptr(acts), N._ptr(c_all),
-                                             N._ptr(h_all), N._ptr(y), _i(U), _i(B), _i(H), N._stream()), "sb_lstm_forward")
+                                             N._ptr(y), _i(U), _i(B), _i(H), N._stream()), "sb_lstm_forward")
             saved.append((inp, acts, c_all, y, h0l, c0l))
-            hn.append(h_all[-1])
+            hn.append(y[-1])
             cn.append(c_all[-1])
             inp = y
         ctx.layers = saved
@@ -66,13 +65,12 @@ class _LSTMFn(torch.autograd.Function):
             In = wih.shape[1]
             dh_rec = torch.zeros((B, H), dtype=torch.float32, device=dev)
             dc_rec = torch.zeros((B, H), dtype=torch.float32, device=dev)
-            dG = torch.empty((U, B, 4 * H), dtype=torch.float32, device=dev)
             dGb = torch.empty((U, B, 4 * H), dtype=torch.bfloat16, device=dev)
             N._check(N.lib().sb_lstm_backward(N._ptr(dcur), N._ptr(dh_rec), N._ptr(dc_rec), N._ptr(acts), N._ptr(c_all), N._ptr(c0l),
-                                              N._ptr(whh), N._ptr(dG), N._ptr(dGb), _i(U), _i(B), _i(H), N._stream()),
+                                              N._ptr(whh), N._ptr(dGb), _i(U), _i(B), _i(H), N._stream()),
                      "sb_lstm_backward")
             dG2 = dGb.view(U * B, 4 * H)
-            first = h0l.to(torch.bfloat16).unsqueeze(0) if h0l is not None else torch.zeros((1, B, H), dtype=torch.bfloat16, device=dev)
+            first = h0l.unsqueeze(0) if h0l is not None else torch.zeros((1, B, H), dtype=torch.bfloat16, device=dev)
             hprev = torch.cat([first, y[:-1]], dim=0).view(U * B, H)
             x2 = inp.view(U * B, In)
             grads[4 * l + 1] = N._write_param_grad(w_hh, lambda out, beta: N.gemm(dG2, hprev, out, M=4 * H, N=H, K=U * B, a_mn=True,

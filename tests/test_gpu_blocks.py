@@ -85,6 +85,10 @@ def test_conv_module_core_fwd_bwd(training):
     (sr * w).sum().backward()
     exp = [sr.detach(), g32.grad, dw.grad, db.grad, ga.grad, be.grad]
     for name, a, b in zip(["s", "dg", "ddw", "ddb", "dgamma", "dbeta"], got, exp):
+        if name == "ddb" and training:
+            # a bias in front of a train-mode BatchNorm has zero gradient; what remains is bf16 storage noise of y
+            assert a.abs().max() < 0.05 * max(1.0, float(got[2].abs().max()))
+            continue
         assert _rel_err(a, b) < 0.06, f"{name}: {_rel_err(a, b)}"
     if training:
         assert (rm - rm2).abs().max() < 2e-2 and (rv - rv2).abs().max() < 2e-2
@@ -127,7 +131,13 @@ def test_conformer_layer_native_vs_eager():
     assert _rel_err(y, yr) < 0.05
     assert _rel_err(gx, x32.grad) < 0.1
     bad = []
+    scale = max(float(p.grad.abs().max()) for p in ref_layer.parameters())
     for n, p in ref_layer.named_parameters():
+        if float(p.grad.abs().max()) < 1e-4 * scale:
+            # analytically zero gradients (key bias under a softmax, bias before a train-mode BatchNorm): absolute check
+            if float(grads[n].abs().max()) > 0.02 * scale:
+                bad.append((n, float(grads[n].abs().max())))
+            continue
         e = _rel_err(grads[n], p.grad)
         if e > 0.12:
             bad.append((n, e))
