@@ -1,0 +1,200 @@
+// Gradient all-reduce over NVLink peer memory in ONE kernel per bucket: cast + scale, reduce-scatter by peer loads,
+// all-gather by peer stores, unpack.  Replaces the c10d reducer + NCCL all-reduce of the reference's DDP strategy for
+// buckets of the flat gradient arena.
+//
+// Every rank owns one symmetric buffer laid out as  [ flags | send (bf16) | recv (bf16) ]  and knows the base address of
+// every peer's buffer (plain P2P pointers: ordinary loads and stores, no TMA, no multicast).  All ranks launch this kernel
+// for the same bucket in the same order.  CTA b of rank r:
+//   phase 0  casts its sub-chunk b of EVERY slice p of the local fp32 gradient (times `scale`) to bf16 in the local send
+//            buffer, then raises flag (b, r) = 2*epoch+1 in every peer's flag block;
+//   wait     until flags (b, q) >= 2*epoch+1 for all peers q                       (their sub-chunk b is ready);
+//   phase A  sums sub-chunk b of slice r over all ranks' send buffers in fp32, rounds to bf16 once and stores the result into
+//            EVERY rank's recv buffer (so all ranks hold bit-identical values), then raises flag (b, r) = 2*epoch+2;
+//   wait     until flags (b, q) >= 2*epoch+2 for all peers q;
+//   phase B  converts sub-chunk b of every slice of the local recv buffer to fp32 in the gradient arena.
+// CTA b only ever waits for CTA b of the peers, so no CTA depends on another CTA of its own GPU and the grid needs no
+// co-residency.  Flags only grow (epoch = launch counter, identical on all ranks), so they are never reset; a rank that is
+// one bucket ahead cannot touch a buffer a slower rank still uses because each phase is gated by the slower rank's flag.
+// Every wait is bounded: after SB_WAIT_CYCLES the CTA records SB_TIMEOUT_PEER_FLAG in the status word and returns
+// without touching peer memory again.
+#include "common.cuh"
+
+#define SB_PEER_MAX_WORLD 16
+#define SB_PEER_MAX_CTAS 128
+
+struct SbPeerArgs {
+  float* grad;                 // local fp32 gradient bucket [n], reduced in place
+  void* const* buffers;        // device array [world]: base address of each rank's symmetric buffer
+  long long flags_off;         // byte offsets inside a symmetric buffer
+  long long send_off;
+  long long recv_off;
+  long long n;                 // elements in the bucket
+  long long slice;             // elements per rank slice (multiple of 8, slice * world >= n)
+  long long chunk;             // elements per CTA sub-chunk (multiple of 8, chunk * ctas >= slice)
+  int rank, world, ctas;
+  unsigned int epoch;          // launch counter, starts at 1
+  float scale;
+  int* status;                 // device status word (filled in by sb_peer_allreduce)
+};
+
+namespace {
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Thread q < world waits for peer q's flag; everyone gets the verdict.  Returns false after a timeout.
+__device__ bool wait_peers(const unsigned int* my_flags, int b, int world, int rank, unsigned int want, int* s_fail) {
+  if (threadIdx.x < world && threadIdx.x != rank) {
+    const unsigned int* f = my_flags + (long long)b * SB_PEER_MAX_WORLD + threadIdx.x;
+    const long long t0 = clock64();
+    while ((int)(ld_acquire_sys(f) - want) < 0) {
+      if (clock64() - t0 > SB_WAIT_CYCLES) {
+        atomicExch(s_fail, 1);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  return *s_fail == 0;
+}
+
+__device__ void signal_peers(const SbPeerArgs& a, int b, unsigned int value) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < a.world && threadIdx.x != a.rank) {
+    unsigned int* f = reinterpret_cast<unsigned int*>((char*)a.buffers[threadIdx.x] + a.flags_off) +
+                      (long long)b * SB_PEER_MAX_WORLD + a.rank;
+    st_release_sys(f, value);
+  }
+}
+
+__device__ __forceinline__ void add8(float* acc, const uint4& v) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    acc[2 * i] += f.x;
+    acc[2 * i + 1] += f.y;
+  }
+}
+
+__global__ void __launch_bounds__(512) peer_allreduce_kernel(SbPeerArgs a) {
+  __shared__ int s_fail;
+  const int b = blockIdx.x;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  char* my_base = (char*)a.buffers[a.rank];
+  __nv_bfloat16* my_send = reinterpret_cast<__nv_bfloat16*>(my_base + a.send_off);
+  __nv_bfloat16* my_recv = reinterpret_cast<__nv_bfloat16*>(my_base + a.recv_off);
+  const unsigned int* my_flags = reinterpret_cast<const unsigned int*>(my_base + a.flags_off);
+  const long long c0 = (long long)b * a.chunk;                 // sub-chunk range inside a slice
+  const long long c1 = min(a.slice, c0 + a.chunk);
+
+  // ---- phase 0: local cast of sub-chunk b of every slice
+  for (int p = 0; p < a.world; ++p) {
+    const long long base = (long long)p * a.slice;
+    for (long long i = c0 + (long long)threadIdx.x * 8; i < c1; i += (long long)blockDim.x * 8) {
+      const long long e = base + i;
+      __align__(16) __nv_bfloat162 o[4];
+      if (e + 8 <= a.n) {
+        const float4 x = *reinterpret_cast<const float4*>(a.grad + e);
+        const float4 y = *reinterpret_cast<const float4*>(a.grad + e + 4);
+        o[0] = __floats2bfloat162_rn(x.x * a.scale, x.y * a.scale);
+        o[1] = __floats2bfloat162_rn(x.z * a.scale, x.w * a.scale);
+        o[2] = __floats2bfloat162_rn(y.x * a.scale, y.y * a.scale);
+        o[3] = __floats2bfloat162_rn(y.z * a.scale, y.w * a.scale);
+      } else {
+        float t[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t[k] = (e + k < a.n) ? a.grad[e + k] * a.scale : 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(t[2 * k], t[2 * k + 1]);
+      }
+      *reinterpret_cast<uint4*>(my_send + e) = *reinterpret_cast<const uint4*>(o);
+    }
+  }
+  signal_peers(a, b, 2u * a.epoch + 1u);
+  if (!wait_peers(my_flags, b, a.world, a.rank, 2u * a.epoch + 1u, &s_fail)) {
+    if (threadIdx.x == 0) sb_set_status(a.status, SB_TIMEOUT_PEER_FLAG, 1);
+    return;
+  }
+
+  // ---- phase A: reduce my slice's sub-chunk over all ranks, broadcast the rounded result
+  {
+    const long long base = (long long)a.rank * a.slice;
+    for (long long i = c0 + (long long)threadIdx.x * 8; i < c1; i += (long long)blockDim.x * 8) {
+      const long long e = base + i;
+      if (e >= a.n) break;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int q = 0; q < a.world; ++q) {
+        const uint4 v = *reinterpret_cast<const uint4*>((const char*)a.buffers[q] + a.send_off + e * 2);
+        add8(acc, v);
+      }
+      __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+      const uint4 r = *reinterpret_cast<const uint4*>(o);
+      for (int q = 0; q < a.world; ++q) *reinterpret_cast<uint4*>((char*)a.buffers[q] + a.recv_off + e * 2) = r;
+    }
+  }
+  signal_peers(a, b, 2u * a.epoch + 2u);
+  if (!wait_peers(my_flags, b, a.world, a.rank, 2u * a.epoch + 2u, &s_fail)) {
+    if (threadIdx.x == 0) sb_set_status(a.status, SB_TIMEOUT_PEER_FLAG, 2);
+    return;
+  }
+
+  // ---- phase B: unpack sub-chunk b of every slice into the fp32 arena
+  for (int p = 0; p < a.world; ++p) {
+    const long long base = (long long)p * a.slice;
+    for (long long i = c0 + (long long)threadIdx.x * 8; i < c1; i += (long long)blockDim.x * 8) {
+      const long long e = base + i;
+      if (e >= a.n) break;
+      const uint4 v = *reinterpret_cast<const uint4*>(my_recv + e);
+      float t[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      add8(t, v);
+      if (e + 8 <= a.n) {
+        *reinterpret_cast<float4*>(a.grad + e) = make_float4(t[0], t[1], t[2], t[3]);
+        *reinterpret_cast<float4*>(a.grad + e + 4) = make_float4(t[4], t[5], t[6], t[7]);
+      } else {
+        for (int k = 0; k < 8 && e + k < a.n; ++k) a.grad[e + k] = t[k];
+      }
+    }
+  }
+}
+
+}  // namespace
+
+// Bytes of the flag block at the start of a symmetric buffer.
+SB_API long long sb_peer_flags_bytes() { return (long long)SB_PEER_MAX_CTAS * SB_PEER_MAX_WORLD * sizeof(unsigned int); }
+
+// Fills the derived fields (slice, chunk) and launches.  `grad` must be 16-byte aligned; the send / recv regions must hold
+// slice * world bf16 elements.  Returns 0, a negative code for bad arguments or a positive cudaError_t.
+SB_API int sb_peer_allreduce(SbPeerArgs* a, cudaStream_t stream) {
+  if (a->world < 1 || a->world > SB_PEER_MAX_WORLD || a->rank < 0 || a->rank >= a->world) return -1;
+  if (a->ctas < 1 || a->ctas > SB_PEER_MAX_CTAS || a->n <= 0 || a->epoch == 0) return -1;
+  if ((reinterpret_cast<unsigned long long>(a->grad) & 15ull) || (a->send_off & 15) || (a->recv_off & 15) || (a->flags_off & 3)) return -2;
+  long long slice = (a->n + a->world - 1) / a->world;
+  slice = (slice + 7) / 8 * 8;
+  long long chunk = (slice + a->ctas - 1) / a->ctas;
+  chunk = (chunk + 7) / 8 * 8;
+  a->status = sb_status_ptr();
+  if (a->status == nullptr) return -3;
+  a->slice = slice;
+  a->chunk = chunk;
+  peer_allreduce_kernel<<<a->ctas, 512, 0, stream>>>(*a);
+  return (int)cudaGetLastError();
+}
+
+// Capacity (elements) the send and recv regions need for a bucket of n elements.
+SB_API long long sb_peer_padded_elems(long long n, int world) {
+  long long slice = (n + world - 1) / world;
+  slice = (slice + 7) / 8 * 8;
+  return slice * world;
+}

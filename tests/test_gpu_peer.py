@@ -1,0 +1,99 @@
+"""Peer-memory gradient all-reduce kernel (csrc/peer_allreduce.cu): arithmetic and indexing on one GPU with a one-rank
+"world", and the real multi-rank protocol as torchrun child processes when the machine has at least two GPUs."""
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import textwrap
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("n,ctas", [(8, 1), (1000, 3), (1_000_003, 32), (40_000_000, 64)])
+def test_one_rank_world_rounds_through_bf16(n, ctas):
+    from speech_b200.ops import native
+    from speech_b200.parallel.symm import SbPeerArgs, padded_elems
+
+    lib = native.lib()
+    lib.sb_peer_flags_bytes.restype = ctypes.c_longlong
+    dev = torch.device("cuda:0")
+    torch.manual_seed(n)
+    g = torch.randn(n, device=dev)
+    want = (g * 0.5).to(torch.bfloat16).float()
+    flags = int(lib.sb_peer_flags_bytes())
+    region = -(-padded_elems(n, 1) * 2 // 256) * 256
+    buf = torch.zeros(flags + 2 * region, dtype=torch.uint8, device=dev)
+    ptrs = torch.tensor([buf.data_ptr()], dtype=torch.int64, device=dev)
+    for epoch in (1, 2):  # the second launch reuses flags and regions
+        x = g.clone()
+        a = SbPeerArgs(x.data_ptr(), ptrs.data_ptr(), 0, flags, flags + region, n, 0, 0, 0, 1, ctas, epoch, 0.5, None)
+        assert lib.sb_peer_allreduce(ctypes.byref(a), native._stream()) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(x, want)
+    native.check_status()
+
+
+def test_bad_arguments_are_rejected():
+    from speech_b200.ops import native
+    from speech_b200.parallel.symm import SbPeerArgs
+
+    lib = native.lib()
+    dev = torch.device("cuda:0")
+    x = torch.zeros(64, device=dev)
+    buf = torch.zeros(1 << 16, dtype=torch.uint8, device=dev)
+    ptrs = torch.tensor([buf.data_ptr()], dtype=torch.int64, device=dev)
+    bad_world = SbPeerArgs(x.data_ptr(), ptrs.data_ptr(), 0, 8192, 16384, 64, 0, 0, 0, 17, 4, 1, 1.0, None)
+    assert lib.sb_peer_allreduce(ctypes.byref(bad_world), native._stream()) == -1
+    misaligned = SbPeerArgs(x.data_ptr() + 4, ptrs.data_ptr(), 0, 8192, 16384, 32, 0, 0, 0, 1, 4, 1, 1.0, None)
+    assert lib.sb_peer_allreduce(ctypes.byref(misaligned), native._stream()) == -2
+
+
+PEER_SCRIPT = textwrap.dedent("""
+    import os, sys, json, torch, torch.distributed as dist
+    sys.path.insert(0, {repo!r})
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from speech_b200.ops import native
+    from speech_b200.parallel.symm import PeerAllReduce
+    red = PeerAllReduce(3_000_017, dev)
+    worst = 0.0
+    for it, n in enumerate([3_000_017, 8, 1_234_567, 3_000_017]):
+        torch.manual_seed(100 * it + rank)
+        x = torch.randn(n, device=dev)
+        mine = (x / world).to(torch.bfloat16).float()
+        ref = mine.clone()
+        dist.all_reduce(ref)                       # fp32 sum of the bf16-rounded contributions
+        ref = ref.to(torch.bfloat16).float()
+        red(x, 1.0 / world)
+        torch.cuda.synchronize()
+        worst = max(worst, float((x - ref).abs().max() / ref.abs().max()))
+        same = x.clone(); dist.broadcast(same, 0)
+        assert torch.equal(same, x), "ranks disagree"
+    native.check_status()
+    print("RESULT", json.dumps({{"rank": rank, "worst": worst}}))
+    dist.destroy_process_group()
+""")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_or_more_ranks_match_nccl(tmp_path):
+    script = tmp_path / "peer.py"
+    script.write_text(PEER_SCRIPT.format(repo=REPO))
+    n = min(torch.cuda.device_count(), 4)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                          "--master-addr", "127.0.0.1", "--master-port", "29741", str(script)],
+                         capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, (out.stdout[-2000:], out.stderr[-3000:])
+    import re
+
+    res = [json.loads(m) for m in re.findall(r"RESULT (\{[^{}]*\})", out.stdout)]
+    assert len(res) == n
+    assert max(r["worst"] for r in res) < 8e-3  # one bf16 ulp of the result
