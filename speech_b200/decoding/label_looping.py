@@ -138,6 +138,19 @@ class GreedyBatchedLabelLoopingComputer:
                 return self._graph_impl(x, out_len, prev_batched_state)
             return self.torch_impl(x, out_len, prev_batched_state)
 
+    @torch.no_grad()
+    def initial_state(self, batch_size: int, device) -> LabelLoopingState:
+        """Decoder state of streams that have not emitted anything yet (prediction net fed with the start symbol)."""
+        dt = torch.float32
+        with torch.autocast(torch.device(device).type, enabled=False), ops.compute_dtype(None):
+            dec_out, state = self.decoder.predict(None, state=None, add_sos=False, batch_size=batch_size)
+            dec_proj = self.joint.project_prednet(dec_out.to(dt))
+        return LabelLoopingState(
+            predictor_state=tuple(state) if state is not None else None, predictor_output=dec_proj,
+            labels=torch.full((batch_size,), self._blank_index, device=device, dtype=torch.long),
+            decoded_lengths=torch.zeros(batch_size, device=device, dtype=torch.long),
+            time_jumps=torch.zeros(batch_size, device=device, dtype=torch.long), fusion_states=None)
+
     def _graph_supported(self) -> bool:
         from ..ops import native
 

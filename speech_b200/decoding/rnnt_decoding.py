@@ -290,8 +290,18 @@ class GreedyBatchedRNNTInfer:
         """encoder_output: [B, D, T].  ``partial_hypotheses`` carry the decoder state for streaming continuation."""
         x = encoder_output.transpose(1, 2)
         prev = None
-        if partial_hypotheses is not None and all(h is not None and h.dec_state is not None for h in partial_hypotheses):
-            prev = merge_states([h.dec_state for h in partial_hypotheses])
+        if partial_hypotheses is not None and any(h is not None and h.dec_state is not None for h in partial_hypotheses):
+            # streams that join a running batch start from the prediction net's start-symbol state
+            fresh = None
+            states = []
+            for h in partial_hypotheses:
+                if h is not None and h.dec_state is not None:
+                    states.append(h.dec_state)
+                else:
+                    if fresh is None:
+                        fresh = self.decoding_computer.initial_state(1, x.device)
+                    states.append(fresh)
+            prev = merge_states(states)
         hyps, _, state = self.decoding_computer(x, encoded_lengths.to(x.device), prev)
         out = batched_hyps_to_hypotheses(hyps, None, batch_size=x.shape[0])
         states = split_state(state, x.shape[0])

@@ -1,0 +1,108 @@
+"""Slot allocator for cache-aware streaming encoder state.
+
+All live streams share three resident tensors (``[L, num_slots, cache, d]`` attention cache, ``[L, num_slots, d, k-1]``
+convolution cache, ``[num_slots]`` valid cache length); a stream owns one slot for its lifetime.  A batch step gathers the
+slots of the streams in the batch, runs the encoder chunk and scatters the updated caches back; finished streams have
+their slot zeroed and returned to the free list (reference behaviour: ``inference/utils/context_manager.py:45-197``).
+
+The gather and scatter are single ``index_select`` / ``index_copy_`` calls on the resident tensors, so the per-step cost is
+one read and one write of the batch's cache rows and no allocation beyond the gathered batch.
+"""
+from __future__ import annotations
+
+from collections import deque
+from typing import Dict, List, Tuple
+
+import torch
+
+
+class CacheAwareContext:
+    """Per-batch view of the caches: what the encoder step consumes and produces."""
+
+    def __init__(self, cache_last_channel=None, cache_last_time=None, cache_last_channel_len=None):
+        self.cache_last_channel = cache_last_channel
+        self.cache_last_time = cache_last_time
+        self.cache_last_channel_len = cache_last_channel_len
+
+    def as_tuple(self):
+        return self.cache_last_channel, self.cache_last_time, self.cache_last_channel_len
+
+
+class CacheAwareContextManager:
+    def __init__(self, cache_aware_model, num_slots: int, use_cache: bool = True, dtype=torch.float32, device=None):
+        """``cache_aware_model`` exposes ``get_initial_cache_state(batch_size)`` (an encoder or a model wrapper)."""
+        self.model = cache_aware_model
+        self.num_slots = int(num_slots)
+        self.use_cache = use_cache
+        self.dtype, self.device = dtype, device
+        self.reset()
+
+    def reset(self) -> None:
+        self.streamidx2slotidx: Dict[int, int] = {}
+        self.slotidx2streamidx: Dict[int, int] = {}
+        self.free_slots = deque(range(self.num_slots))
+        if self.use_cache:
+            clc, clt, clcl = self.model.get_initial_cache_state(batch_size=self.num_slots)
+            if self.device is not None:
+                clc, clt, clcl = clc.to(self.device), clt.to(self.device), clcl.to(self.device)
+            self.cache_last_channel = clc.to(self.dtype)
+            self.cache_last_time = clt.to(self.dtype)
+            self.cache_last_channel_len = clcl
+            self.device = self.cache_last_channel.device
+        else:
+            self.cache_last_channel = self.cache_last_time = self.cache_last_channel_len = None
+
+    # ------------------------------------------------------------------ slots
+    def num_free_slots(self) -> int:
+        return len(self.free_slots)
+
+    def _slot_of(self, stream_id: int) -> int:
+        s = self.streamidx2slotidx.get(stream_id)
+        if s is None:
+            if not self.free_slots:
+                raise RuntimeError(f"no free cache slot for stream {stream_id} ({self.num_slots} slots in use)")
+            s = self.free_slots.popleft()
+            self.streamidx2slotidx[stream_id] = s
+            self.slotidx2streamidx[s] = stream_id
+        return s
+
+    def reset_slots(self, stream_ids: List[int], eos_flags: List[bool]) -> None:
+        """Zero and free the slots of streams that have ended."""
+        ended = [self.streamidx2slotidx[s] for s, e in zip(stream_ids, eos_flags) if e and s in self.streamidx2slotidx]
+        if not ended:
+            return
+        if self.use_cache:
+            idx = torch.tensor(ended, device=self.device, dtype=torch.long)
+            self.cache_last_channel.index_fill_(1, idx, 0)
+            self.cache_last_time.index_fill_(1, idx, 0)
+            self.cache_last_channel_len.index_fill_(0, idx, 0)
+        for slot in ended:
+            sid = self.slotidx2streamidx.pop(slot)
+            del self.streamidx2slotidx[sid]
+            self.free_slots.append(slot)
+
+    # ------------------------------------------------------------------ gather / scatter
+    def get_context(self, stream_ids: List[int]) -> Tuple[CacheAwareContext, Dict[int, int]]:
+        """Caches of the given streams in batch order, plus ``{stream_id: slot}``."""
+        slots = [self._slot_of(s) for s in stream_ids]
+        mapping = dict(zip(stream_ids, slots))
+        if not self.use_cache:
+            return CacheAwareContext(), mapping
+        idx = torch.tensor(slots, device=self.device, dtype=torch.long)
+        return CacheAwareContext(self.cache_last_channel.index_select(1, idx), self.cache_last_time.index_select(1, idx),
+                                 self.cache_last_channel_len.index_select(0, idx)), mapping
+
+    def update_cache(self, stream_ids: List[int], new_context: CacheAwareContext, mapping: Dict[int, int]) -> None:
+        if not self.use_cache:
+            return
+        idx = torch.tensor([mapping[s] for s in stream_ids], device=self.device, dtype=torch.long)
+        clc = new_context.cache_last_channel
+        keep = self.cache_last_channel.shape[2]
+        if clc.shape[2] != keep:  # the encoder may return a shorter / longer window than the resident one
+            if clc.shape[2] > keep:
+                clc = clc[:, :, -keep:]
+            else:
+                clc = torch.nn.functional.pad(clc, (0, 0, keep - clc.shape[2], 0))
+        self.cache_last_channel.index_copy_(1, idx, clc.to(self.dtype))
+        self.cache_last_time.index_copy_(1, idx, new_context.cache_last_time.to(self.dtype))
+        self.cache_last_channel_len.index_copy_(0, idx, new_context.cache_last_channel_len)

@@ -1,0 +1,122 @@
+"""Streaming inference on CPU: slot allocator, continuous batching, cache-aware and buffered pipelines.
+
+The cache-aware check follows the reference's own oracle: chunk-by-chunk decoding with caches must give the same tokens as
+the offline encoder run with the same limited-context mask."""
+import numpy as np
+import pytest
+import torch
+
+from speech_b200.core.config import open_dict
+from speech_b200.inference.context_manager import CacheAwareContextManager
+from speech_b200.inference.framing import ContinuousBatchedRequestStreamer, RequestType
+from speech_b200.inference.pipelines import PipelineBuilder
+from speech_b200.inference.state import GreedyEndpointing, StreamingState, TokenTextAssembler
+from speech_b200.models import EncDecCTCModelBPE, EncDecRNNTBPEModel
+from speech_b200.models.configs import fastconformer_ctc_config, fastconformer_transducer_config
+
+
+def _streaming_overrides(cfg):
+    with open_dict(cfg):
+        cfg.preprocessor.normalize = "NA"
+        cfg.preprocessor.dither = 0.0
+        cfg.preprocessor.pad_to = 0
+    return cfg
+
+
+def _audio(n, seed):
+    g = np.random.default_rng(seed)
+    return (g.standard_normal(n) * 0.1).astype(np.float32)
+
+
+def test_streamer_keeps_batch_full_and_orders_chunks():
+    s = ContinuousBatchedRequestStreamer(n_frames_per_stream=1000, batch_size=2, sample_rate=16000)
+    s.set_audio_filepaths([_audio(2500, 0), _audio(900, 1), _audio(1800, 2)])
+    steps = [[(f.stream_id, f.is_first, f.is_last, f.valid_size) for f in batch] for batch in s]
+    assert steps[0] == [(0, True, False, 1000), (1, True, True, 900)]
+    assert steps[1] == [(0, False, False, 1000), (2, True, False, 1000)]   # stream 2 joined as soon as stream 1 ended
+    assert steps[2] == [(0, False, True, 500), (2, False, True, 800)]
+    assert len(steps) == 3
+
+
+class _FakeEncoder:
+    def get_initial_cache_state(self, batch_size=1):
+        return torch.zeros(2, batch_size, 4, 3), torch.zeros(2, batch_size, 3, 2), torch.zeros(batch_size, dtype=torch.long)
+
+
+def test_context_manager_slots_gather_scatter_and_reuse():
+    cm = CacheAwareContextManager(_FakeEncoder(), num_slots=3)
+    ctx, mp = cm.get_context([10, 11])
+    assert ctx.cache_last_channel.shape == (2, 2, 4, 3) and cm.num_free_slots() == 1
+    ctx.cache_last_channel = torch.ones(2, 2, 4, 3) * torch.tensor([1.0, 2.0]).view(1, 2, 1, 1)
+    ctx.cache_last_time = torch.ones(2, 2, 3, 2)
+    ctx.cache_last_channel_len = torch.tensor([4, 2])
+    cm.update_cache([10, 11], ctx, mp)
+    again, _ = cm.get_context([11, 10])
+    assert float(again.cache_last_channel[0, 0, 0, 0]) == 2.0 and again.cache_last_channel_len.tolist() == [2, 4]
+    cm.reset_slots([10, 11], [True, False])
+    assert cm.num_free_slots() == 2
+    fresh, _ = cm.get_context([12])
+    assert float(fresh.cache_last_channel.abs().sum()) == 0.0       # the freed slot was zeroed
+    with pytest.raises(RuntimeError):
+        cm.get_context([13, 14, 15])
+
+
+def test_endpointing_and_word_assembly():
+    toks = {1: "▁he", 2: "llo", 3: "▁wor", 4: "ld"}
+    asm = TokenTextAssembler(lambda ids: [toks[i] for i in ids],
+                             lambda ids: "".join(toks[i] for i in ids).replace("▁", " ").strip(), seconds_per_frame=0.08)
+    ws = asm.words([1, 2, 3, 4], [0, 2, 10, 11], [0.9, 0.7, 1.0, 0.5])
+    assert [w.text for w in ws] == ["hello", "world"]
+    assert ws[0].start == 0.0 and abs(ws[0].end - 0.24) < 1e-9 and abs(ws[0].conf - 0.8) < 1e-9
+    st = StreamingState(0)
+    ep = GreedyEndpointing(ms_per_frame=80.0, stop_history_eou_ms=400)
+    st.append_tokens([1, 2], [0, 1])
+    st.advance(4)
+    assert not ep.detect_eou(st)
+    st.advance(4)                      # 6 silent frames >= 5
+    assert ep.detect_eou(st) and ep.detect_eou(StreamingState(1), is_last=True)
+
+
+@pytest.mark.parametrize("kind", ["ctc", "rnnt"])
+def test_cache_aware_pipeline_matches_offline_limited_context(kind):
+    torch.manual_seed(0)
+    enc_over = dict(n_layers=2, causal=True, att_context_size=[8, 1], att_context_style="chunked_limited",
+                    conv_norm_type="layer_norm")
+    if kind == "ctc":
+        model = EncDecCTCModelBPE(_streaming_overrides(fastconformer_ctc_config("small", vocab_size=32, **enc_over)))
+    else:
+        model = EncDecRNNTBPEModel(_streaming_overrides(fastconformer_transducer_config(
+            "small", vocab_size=32, loss="rnnt", dropout=0.0, sched=None, lr=1e-3, **enc_over)))
+    model.eval()
+    audios = [_audio(16000 * 2 + 320, 1), _audio(16000 + 4000, 2), _audio(16000 * 3, 3)]
+    pipe = PipelineBuilder.build_pipeline({"pipeline_type": "cache_aware",
+                                           "streaming": {"batch_size": 2, "num_slots": 4},
+                                           "endpointing": {"stop_history_eou": 100000}}, asr_model=model)
+    out = pipe.run(audios)
+    assert sorted(out) == [0, 1, 2]
+    offline = model.transcribe(audios, batch_size=1)
+    off_text = [h.text if hasattr(h, "text") else h for h in offline]
+    # same limited-context encoder offline and online: identical token streams, except that the ragged final chunk may
+    # cover one encoder frame less than the offline pass (at most max_symbols = 10 tokens of an untrained model)
+    for i in range(3):
+        on, off = out[i].text.split(), off_text[i].split()
+        n = min(len(on), len(off))
+        assert n > 0 or len(off) <= 10
+        assert on[:n] == off[:n], (i, on, off)
+        assert abs(len(on) - len(off)) <= 10
+    assert pipe.rtfx() > 0
+
+
+def test_buffered_ctc_pipeline_runs_and_times_words():
+    torch.manual_seed(0)
+    model = EncDecCTCModelBPE(_streaming_overrides(fastconformer_ctc_config("small", vocab_size=32, n_layers=1)))
+    model.eval()
+    pipe = PipelineBuilder.build_pipeline({"pipeline_type": "buffered",
+                                           "streaming": {"batch_size": 2, "chunk_size": 0.8, "left_padding_size": 0.8,
+                                                         "right_padding_size": 0.4}}, asr_model=model)
+    out = pipe.run([_audio(16000 * 2, 5), _audio(12000, 6)])
+    assert sorted(out) == [0, 1]
+    for o in out.values():
+        assert isinstance(o.text, str)
+        for w in o.words:
+            assert 0.0 <= w.start <= w.end
