@@ -5,6 +5,11 @@
 * ``BatchedCacheFeatureBufferer`` — audio ring buffers for a batch of streams; every update recomputes log-mel features of
   the windows in ONE preprocessor call and returns, per stream, the feature frames of the newest chunk preceded by the
   pre-encode cache frames the subsampling convolutions need.
+
+Feature frames are bit-compatible with an offline pass over the whole recording: a frame is only released once its whole
+analysis window lies inside the buffer, which costs ``lookahead_frames`` (= ceil(n_fft / 2 / hop), 2 frames = 20 ms for the
+default front-end) of extra audio in the first chunk of a stream; afterwards every chunk releases exactly ``chunk_frames``
+frames.  The stream's last chunk releases whatever is left up to the offline frame count.
 Reference: ``inference/streaming/buffering/{audio_bufferer,cache_feature_bufferer}.py`` and the legacy
 ``CacheAwareStreamingAudioBuffer`` (``parts/utils/streaming_utils.py``).
 """
@@ -55,21 +60,40 @@ class AudioBufferer:
 
 class BatchedCacheFeatureBufferer:
     def __init__(self, sample_rate: int, buffer_size_in_secs: float, chunk_size_in_secs: float, preprocessor, device=None,
-                 pre_encode_cache_frames: int = 0, right_pad_features: bool = False):
-        self.audio = AudioBufferer(sample_rate, buffer_size_in_secs)
+                 pre_encode_cache_frames: int = 0, first_chunk_frames: Optional[int] = None, right_pad_features: bool = False):
         self.preprocessor = preprocessor
         self.device = device
         feat = getattr(preprocessor, "featurizer", preprocessor)
+        self.featurizer = feat
         self.hop = int(getattr(feat, "hop_length", int(0.01 * sample_rate)))
+        n_fft = int(getattr(feat, "n_fft", 512))
+        self.lookahead_frames = int(math.ceil((n_fft // 2) / self.hop))
         self.chunk_samples = int(round(chunk_size_in_secs * sample_rate))
         self.chunk_frames = int(math.ceil(self.chunk_samples / self.hop))
+        self.first_chunk_frames = int(first_chunk_frames) if first_chunk_frames else self.chunk_frames
         self.cache_frames = int(pre_encode_cache_frames)
+        need = (max(self.chunk_frames, self.first_chunk_frames) + self.cache_frames + self.lookahead_frames + 1) * self.hop
+        self.audio = AudioBufferer(sample_rate, max(buffer_size_in_secs, need / sample_rate))
         self.right_pad_features = right_pad_features
-        if self.chunk_samples + self.cache_frames * self.hop > self.audio.buffer_size:
-            raise ValueError("the audio buffer must cover one chunk plus the pre-encode cache")
+        self.delivered: Dict[int, int] = {}
+
+    # geometry the streamer needs to cut the audio so that every update releases whole chunks
+    def first_frame_samples(self) -> int:
+        return (self.first_chunk_frames + self.lookahead_frames) * self.hop
+
+    def tail_padding_samples(self) -> int:
+        return (self.lookahead_frames + 1) * self.hop
 
     def set_pre_encode_cache(self, frames: int) -> None:
         self.cache_frames = int(frames)
+        need = (max(self.chunk_frames, self.first_chunk_frames) + self.cache_frames + self.lookahead_frames + 1) * self.hop
+        if need > self.audio.buffer_size:
+            self.audio = AudioBufferer(self.audio.sample_rate, need / self.audio.sample_rate)
+
+    def _offline_frames(self, n_samples: int) -> int:
+        if hasattr(self.featurizer, "get_seq_len"):
+            return int(self.featurizer.get_seq_len(torch.tensor([n_samples]))[0])
+        return n_samples // self.hop + 1
 
     @torch.no_grad()
     def update(self, frames: List[Frame]) -> List[FeatureBuffer]:
@@ -83,19 +107,32 @@ class BatchedCacheFeatureBufferer:
         feats, _ = self.preprocessor(input_signal=windows, length=lens)  # [B, F, T]
         if was_training:
             self.preprocessor.train()
-        T = (windows.shape[1] // self.hop)  # frames fully inside the window (the trailing centre-padded frame is dropped)
-        want = self.chunk_frames + self.cache_frames
+        # window frame j is centred on window sample j*hop; frames up to `end` have their analysis window inside the buffer
+        end = windows.shape[1] // self.hop - self.lookahead_frames
         out = []
         for i, f in enumerate(frames):
-            x = feats[i, :, max(0, T - want):T]
-            if x.shape[1] < want:
-                x = torch.nn.functional.pad(x, (want - x.shape[1], 0))
-            valid_chunk = int(math.ceil(f.valid_size / self.hop))
-            length = self.cache_frames + valid_chunk
-            if f.is_first and self.cache_frames:
-                # nothing precedes the first chunk: drop the cache part so the encoder sees exactly the chunk
-                x = x[:, self.cache_frames:]
-                length = valid_chunk
-            out.append(FeatureBuffer(features=x, stream_id=f.stream_id, is_first=f.is_first, is_last=f.is_last, length=length,
-                                     options=f.options))
+            if f.is_first:
+                self.delivered[f.stream_id] = 0
+            new = self.first_chunk_frames if f.is_first else self.chunk_frames
+            cache = 0 if f.is_first else self.cache_frames
+            if f.is_last:
+                # the tail is zero-padded audio, exactly what the offline front-end sees beyond the end of the recording
+                end_i = windows.shape[1] // self.hop + 1
+                total = self._offline_frames(f.total_samples if f.total_samples >= 0 else 0)
+                remaining = max(0, total - self.delivered.get(f.stream_id, 0))
+                # frames of this (padded) chunk start where the previous release stopped
+                lo = end - new
+                x = feats[i, :, max(0, lo - cache):min(end_i, lo + max(new, remaining))]
+                valid_new = min(remaining, x.shape[1] - cache)
+            else:
+                lo = end - new
+                x = feats[i, :, max(0, lo - cache):end]
+                valid_new = new
+            if x.shape[1] < cache + new:
+                x = torch.nn.functional.pad(x, (0, cache + new - x.shape[1]))
+            self.delivered[f.stream_id] = self.delivered.get(f.stream_id, 0) + valid_new
+            if f.is_last:
+                self.delivered.pop(f.stream_id, None)
+            out.append(FeatureBuffer(features=x, stream_id=f.stream_id, is_first=f.is_first, is_last=f.is_last,
+                                     length=cache + valid_new, options=f.options))
         return out

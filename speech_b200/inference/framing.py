@@ -47,6 +47,7 @@ class Frame:
     is_last: bool = False
     length: int = -1                 # valid samples (<= len(samples)); -1 = all
     options: Optional[ASRRequestOptions] = None
+    total_samples: int = -1          # on the last frame: length of the whole stream without tail padding
 
     @property
     def size(self) -> int:
@@ -83,9 +84,13 @@ class MonoStream:
     """One audio source cut into chunks of ``frame_size`` samples; the last chunk is zero-padded when ``pad_last_frame``."""
 
     def __init__(self, samples: torch.Tensor, stream_id: int, frame_size: int, pad_last_frame: bool = True,
-                 options: Optional[ASRRequestOptions] = None):
+                 options: Optional[ASRRequestOptions] = None, first_frame_size: Optional[int] = None, tail_padding: int = 0):
         self.samples = samples.reshape(-1).float()
+        self.true_length = int(self.samples.shape[0])
+        if tail_padding:
+            self.samples = torch.nn.functional.pad(self.samples, (0, int(tail_padding)))
         self.stream_id, self.frame_size, self.pad_last = stream_id, int(frame_size), pad_last_frame
+        self.first_frame_size = int(first_frame_size) if first_frame_size else self.frame_size
         self.options = options
         self.pos = 0
         self.n = int(self.samples.shape[0])
@@ -94,14 +99,16 @@ class MonoStream:
         return self.pos >= self.n and self.pos > 0
 
     def next_frame(self) -> Frame:
-        s, e = self.pos, min(self.n, self.pos + self.frame_size)
+        size = self.first_frame_size if self.pos == 0 else self.frame_size
+        s, e = self.pos, min(self.n, self.pos + size)
         chunk = self.samples[s:e]
         valid = e - s
-        if valid < self.frame_size and self.pad_last:
-            chunk = torch.nn.functional.pad(chunk, (0, self.frame_size - valid))
-        self.pos = s + self.frame_size
-        return Frame(samples=chunk, stream_id=self.stream_id, is_first=(s == 0), is_last=(self.pos >= self.n), length=valid,
-                     options=self.options)
+        if valid < size and self.pad_last:
+            chunk = torch.nn.functional.pad(chunk, (0, size - valid))
+        self.pos = s + size
+        last = self.pos >= self.n
+        return Frame(samples=chunk, stream_id=self.stream_id, is_first=(s == 0), is_last=last, length=valid,
+                     options=self.options, total_samples=self.true_length if last else -1)
 
 
 class ContinuousBatchedRequestStreamer:
@@ -113,16 +120,18 @@ class ContinuousBatchedRequestStreamer:
 
     def __init__(self, n_frames_per_stream: int, batch_size: int, sample_rate: int = 16000,
                  request_type: RequestType = RequestType.FRAME, preprocessor=None, buffer_size_in_secs: Optional[float] = None,
-                 device=None, pad_last_frame: bool = True, right_pad_features: bool = False, tail_padding_in_samples: int = 0):
+                 device=None, pad_last_frame: bool = True, right_pad_features: bool = False, tail_padding_in_samples: int = 0,
+                 first_frame_size: Optional[int] = None, bufferer=None):
         self.frame_size, self.batch_size, self.sample_rate = int(n_frames_per_stream), int(batch_size), sample_rate
+        self.first_frame_size = first_frame_size
         self.request_type, self.device = request_type, device
         self.pad_last_frame = pad_last_frame
         self.tail_padding = int(tail_padding_in_samples)
         self.sources: List[Any] = []
         self.options: List[Optional[ASRRequestOptions]] = []
         self.elapsed_durations: Dict[int, float] = {}
-        self.bufferer = None
-        if request_type is RequestType.FEATURE_BUFFER:
+        self.bufferer = bufferer
+        if request_type is RequestType.FEATURE_BUFFER and bufferer is None:
             from .bufferer import BatchedCacheFeatureBufferer
 
             if preprocessor is None or buffer_size_in_secs is None:
@@ -131,6 +140,10 @@ class ContinuousBatchedRequestStreamer:
                                                         chunk_size_in_secs=self.frame_size / sample_rate,
                                                         preprocessor=preprocessor, device=device,
                                                         right_pad_features=right_pad_features)
+        if self.bufferer is not None:
+            # cut the audio so that every update releases whole chunks of offline-exact feature frames
+            self.first_frame_size = self.first_frame_size or self.bufferer.first_frame_samples()
+            self.tail_padding = self.tail_padding or self.bufferer.tail_padding_samples()
 
     def set_audio_filepaths(self, audio: Sequence[Union[str, np.ndarray, torch.Tensor]],
                             options: Optional[Sequence[Optional[ASRRequestOptions]]] = None) -> None:
@@ -146,10 +159,9 @@ class ContinuousBatchedRequestStreamer:
             x = torch.from_numpy(np.asarray(load_audio(src, target_sr=self.sample_rate), dtype=np.float32))
         else:
             x = torch.as_tensor(src, dtype=torch.float32)
-        if self.tail_padding:
-            x = torch.nn.functional.pad(x.reshape(-1), (0, self.tail_padding))
         self.elapsed_durations[stream_id] = x.numel() / self.sample_rate
-        return MonoStream(x, stream_id, self.frame_size, self.pad_last_frame, self.options[stream_id])
+        return MonoStream(x, stream_id, self.frame_size, self.pad_last_frame, self.options[stream_id],
+                          first_frame_size=self.first_frame_size, tail_padding=self.tail_padding)
 
     def get_audio_durations(self) -> Dict[int, float]:
         return dict(self.elapsed_durations)

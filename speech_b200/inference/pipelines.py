@@ -161,12 +161,15 @@ class _CacheAwarePipeline(BasePipeline):
         self.context_manager.reset()
 
     def get_request_generator(self) -> ContinuousBatchedRequestStreamer:
-        s = ContinuousBatchedRequestStreamer(n_frames_per_stream=self.chunk_samples, batch_size=self.batch_size,
-                                             sample_rate=self.sample_rate, request_type=RequestType.FEATURE_BUFFER,
-                                             preprocessor=self.asr_model.asr_model.preprocessor,
-                                             buffer_size_in_secs=self.buffer_secs, device=self.asr_model.device)
-        s.bufferer.set_pre_encode_cache(self.pre_cache)
-        return s
+        from .bufferer import BatchedCacheFeatureBufferer
+
+        buf = BatchedCacheFeatureBufferer(sample_rate=self.sample_rate, buffer_size_in_secs=self.buffer_secs,
+                                          chunk_size_in_secs=self.chunk_samples / self.sample_rate,
+                                          preprocessor=self.asr_model.asr_model.preprocessor, device=self.asr_model.device,
+                                          pre_encode_cache_frames=self.pre_cache, first_chunk_frames=self.first_chunk_frames)
+        return ContinuousBatchedRequestStreamer(n_frames_per_stream=self.chunk_samples, batch_size=self.batch_size,
+                                                sample_rate=self.sample_rate, request_type=RequestType.FEATURE_BUFFER,
+                                                bufferer=buf)
 
     def _run_group(self, reqs: List[FeatureBuffer], first: bool) -> None:
         ids = [r.stream_id for r in reqs]
