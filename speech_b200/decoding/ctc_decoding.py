@@ -111,7 +111,22 @@ class AbstractCTCDecoding:
         if decoder_lengths is None:
             decoder_lengths = torch.full((decoder_outputs.shape[0],), decoder_outputs.shape[1],
                                          device=decoder_outputs.device, dtype=torch.long)
-        if self.strategy in ("beam", "beam_batch"):
+        if self.strategy == "beam_batch":
+            from .batched_beam import BatchedBeamCTCComputer
+
+            comp = BatchedBeamCTCComputer(self.blank_id, beam_size=self.beam_size,
+                                          beam_beta=cfg_get(cfg_get(self.cfg, "beam", None) or {}, "beam_beta", 0.0),
+                                          fusion_models=getattr(self, "fusion_models", None),
+                                          fusion_models_alpha=getattr(self, "fusion_models_alpha", None))
+            beams = comp(decoder_outputs, decoder_lengths.to(decoder_outputs.device))
+            out = []
+            for nbest in beams.to_hyps_list(score_norm=False):
+                hs = [Hypothesis(score=s, y_sequence=torch.tensor(tok, dtype=torch.long),
+                                 timestamp=torch.tensor(frm, dtype=torch.long)) for tok, frm, s in nbest]
+                hs = hs or [Hypothesis(score=0.0, y_sequence=torch.zeros(0, dtype=torch.long))]
+                out.append(self._finish(hs))
+            return [h[0] for h in out] if self.return_best_hypothesis else [NBestHypotheses(h) for h in out]
+        if self.strategy == "beam":
             hyps = [self._beam(decoder_outputs[b, : int(decoder_lengths[b])].float().cpu())
                     for b in range(decoder_outputs.shape[0])]
             if self.return_best_hypothesis:

@@ -16,6 +16,7 @@ from typing import Any, Dict, List, Optional, Tuple, Union
 
 import torch
 
+from .. import ops
 from ..core.config import DictConfig, OmegaConf, cfg_get
 from .label_looping import BatchedHyps, GreedyBatchedLabelLoopingComputer, LabelLoopingState
 
@@ -319,6 +320,34 @@ class GreedyBatchedRNNTInfer:
         return (out,)
 
 
+class BeamBatchedRNNTInfer:
+    """``malsd_batch`` / ``maes_batch`` strategies: the GPU-resident beam search of ``batched_beam`` behind the decoder
+    interface (reference: ``rnnt_beam_decoding.py`` ``BeamBatchedRNNTInfer`` / ``tdt_beam_decoding.py`` ``BeamBatchedTDTInfer``)."""
+
+    def __init__(self, decoder_model, joint_model, blank_index: int, beam_size: int = 4, durations=None,
+                 max_symbols_per_step=10, score_norm: bool = True, return_best_hypothesis: bool = True,
+                 fusion_models=None, fusion_models_alpha=None, **_):
+        from .batched_beam import ModifiedALSDBatchedComputer
+
+        self.return_best_hypothesis = return_best_hypothesis
+        self.score_norm = score_norm
+        self.decoding_computer = ModifiedALSDBatchedComputer(
+            decoder_model, joint_model, blank_index, beam_size, durations, max_symbols_per_step, fusion_models,
+            fusion_models_alpha, score_norm=score_norm)
+
+    @torch.no_grad()
+    def __call__(self, encoder_output: torch.Tensor, encoded_lengths: torch.Tensor, partial_hypotheses=None):
+        x = encoder_output.transpose(1, 2)
+        with torch.autocast(x.device.type, enabled=False), ops.compute_dtype(None):
+            beams = self.decoding_computer(x, encoded_lengths)
+        out = []
+        for nbest in beams.to_hyps_list(score_norm=self.score_norm):
+            hs = [Hypothesis(score=s, y_sequence=torch.tensor(tok, dtype=torch.long), timestamp=torch.tensor(frm, dtype=torch.long))
+                  for tok, frm, s in nbest] or [Hypothesis(score=0.0, y_sequence=torch.zeros(0, dtype=torch.long))]
+            out.append(hs[0] if self.return_best_hypothesis else NBestHypotheses(hs))
+        return (out,)
+
+
 def split_state(state: LabelLoopingState, B: int) -> List[LabelLoopingState]:
     out = []
     for i in range(B):
@@ -393,8 +422,25 @@ class AbstractRNNTDecoding:
                 use_cuda_graph_decoder=cfg_get(g, "use_cuda_graph_decoder", True),
                 include_duration=bool(self.tdt_include_token_duration), fusion_models=fusion_models,
                 fusion_models_alpha=alphas)
+        elif strategy in ("malsd_batch", "maes_batch"):
+            fusion_models, alphas = [], []
+            if cfg_get(bm, "ngram_lm_model", None):
+                from .ngram_lm import NGramGPULanguageModel
+
+                fusion_models.append(NGramGPULanguageModel.from_file(bm["ngram_lm_model"], vocab_size=blank_id))
+                alphas.append(cfg_get(bm, "ngram_lm_alpha", 0.0))
+            if cfg_get(bm, "boosting_tree", None) is not None and cfg_get(bm, "boosting_tree_alpha", 0.0):
+                bt = bm["boosting_tree"]
+                if hasattr(bt, "advance"):
+                    fusion_models.append(bt)
+                    alphas.append(cfg_get(bm, "boosting_tree_alpha", 0.0))
+            self.decoding = BeamBatchedRNNTInfer(
+                decoder, joint, blank_id, beam_size=cfg_get(bm, "beam_size", 4), durations=self.durations,
+                max_symbols_per_step=cfg_get(bm, "max_symbols_per_step", None) or cfg_get(bm, "max_symbols", 10),
+                score_norm=cfg_get(bm, "score_norm", True), return_best_hypothesis=cfg_get(bm, "return_best_hypothesis", True),
+                fusion_models=fusion_models, fusion_models_alpha=alphas)
         else:
-            st = {"beam": "default", "malsd_batch": "alsd", "maes_batch": "maes"}.get(strategy, strategy)
+            st = {"beam": "default"}.get(strategy, strategy)
             self.decoding = BeamRNNTInfer(
                 decoder, joint, blank_id, beam_size=cfg_get(bm, "beam_size", 4), search_type=st,
                 score_norm=cfg_get(bm, "score_norm", True), return_best_hypothesis=cfg_get(bm, "return_best_hypothesis", True),

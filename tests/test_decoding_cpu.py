@@ -1,0 +1,137 @@
+"""Decoding extras on CPU: n-gram LM automaton, boosting tree, batched CTC prefix beam search, batched MALSD beam."""
+import itertools
+import math
+
+import pytest
+import torch
+
+from speech_b200.decoding.batched_beam import BatchedBeamCTCComputer, ModifiedALSDBatchedComputer
+from speech_b200.decoding.context_biasing import GPUBiasingMultiModel, GPUBoostingTreeModel, ctc_word_spotter
+from speech_b200.decoding.ngram_lm import DEFAULT_TOKEN_OFFSET, NGramGPULanguageModel, write_arpa
+from speech_b200.utils.streaming_utils import lcs_alignment_merge_buffer, longest_common_subsequence_merge
+
+LN10 = math.log(10.0)
+
+
+def _c(i):
+    return chr(i + DEFAULT_TOKEN_OFFSET)
+
+
+def test_ngram_lm_matches_bruteforce_backoff(tmp_path):
+    V = 4
+    grams = {("<s>",): (-99.0, -0.3), ("</s>",): (-1.0, 0.0), ("<unk>",): (-2.0, 0.0)}
+    for i in range(V):
+        grams[(_c(i),)] = (-0.5 - 0.1 * i, -0.2 - 0.05 * i)
+    grams[(_c(0), _c(1))] = (-0.2, -0.4)
+    grams[(_c(1), _c(2))] = (-0.3, -0.1)
+    grams[("<s>", _c(0))] = (-0.25, -0.15)
+    grams[(_c(0), _c(1), _c(2))] = (-0.05, 0.0)
+    grams[(_c(1), _c(2), "</s>")] = (-0.6, 0.0)
+    path = str(tmp_path / "lm.arpa")
+    write_arpa(path, grams)
+    lm = NGramGPULanguageModel.from_arpa(path, vocab_size=V)
+
+    def brute(ctx, w):                       # ctx, w: tuples of ARPA words
+        ctx = ctx[-2:]
+        while True:
+            if ctx + (w,) in grams:
+                return grams[ctx + (w,)][0]
+            if not ctx:
+                return grams[("<unk>",)][0]
+            bo = grams[ctx][1] if ctx in grams else 0.0
+            return bo + brute(ctx[1:], w)
+
+    for seq in itertools.product(range(V), repeat=3):
+        st = lm.get_init_states(1, bos=True)
+        ctx = ("<s>",)
+        for t in seq:
+            sc, nx = lm.advance(st)
+            want = torch.tensor([brute(ctx, _c(v)) * LN10 for v in range(V)])
+            assert torch.allclose(sc[0], want, atol=1e-5), (seq, ctx)
+            st = nx[:, t]
+            ctx = ctx + (_c(t),)
+    lm.save_to(str(tmp_path / "lm.pt"))
+    again = NGramGPULanguageModel.restore_from(str(tmp_path / "lm.pt"))
+    assert abs(again.score_sentence([0, 1, 2]) - lm.score_sentence([0, 1, 2])) < 1e-6
+    # p(0|<s>) + [backoff(<s> 0) + p(1|0)] + p(2|0 1)
+    assert abs(lm.score_sentence([0, 1, 2]) - (-0.25 - 0.15 - 0.2 - 0.05) * LN10) < 1e-5
+
+
+def test_boosting_tree_rewards_complete_phrases_only():
+    tree = GPUBoostingTreeModel(vocab_size=8, phrases=[[1, 2, 3], [2, 4]], context_score=1.0)
+
+    def walk(seq):
+        st = tree.get_init_states(1)
+        total = 0.0
+        for t in seq:
+            sc, nx = tree.advance(st)
+            total += float(sc[0, t])
+            st = nx[:, t]
+        return total + float(tree.get_final(st)[0])
+
+    assert walk([1, 2, 3]) == pytest.approx(3.0)
+    assert walk([1, 2, 5]) == pytest.approx(0.0)         # partial match gives the reward back
+    assert walk([1, 2, 4]) == pytest.approx(2.0)         # falls over to the second phrase through the failure link
+    assert walk([1, 2]) == pytest.approx(0.0)            # unfinished at end of utterance
+    assert walk([5, 2, 4, 6]) == pytest.approx(2.0)
+    multi = GPUBiasingMultiModel(8)
+    a = multi.add_model(tree, alpha=2.0)
+    sc, _ = multi.advance(torch.zeros(2, dtype=torch.long), torch.tensor([a, -1]))
+    assert float(sc[0, 1]) == 2.0 and float(sc[1].abs().sum()) == 0.0
+
+
+def test_batched_ctc_beam_finds_best_labelling():
+    torch.manual_seed(0)
+    B, T, V = 3, 5, 3                                     # 2 labels + blank (index 2)
+    lp = torch.log_softmax(torch.randn(B, T, V) * 2, dim=-1)
+    lens = torch.tensor([5, 4, 3])
+    beams = BatchedBeamCTCComputer(blank_index=2, beam_size=16)(lp, lens)
+    got = beams.to_hyps_list(score_norm=False)
+    for b in range(B):
+        probs = {}
+        for path in itertools.product(range(V), repeat=int(lens[b])):
+            p = sum(float(lp[b, t, s]) for t, s in enumerate(path))
+            lab, prev = [], 2
+            for s in path:
+                if s != prev and s != 2:
+                    lab.append(s)
+                prev = s
+            probs[tuple(lab)] = math.log(math.exp(probs[tuple(lab)]) + math.exp(p)) if tuple(lab) in probs else p
+        best = max(probs, key=probs.get)
+        assert tuple(got[b][0][0]) == best
+        assert got[b][0][2] == pytest.approx(probs[best], abs=1e-2)   # pruned prefixes take a little mass with them
+
+
+def test_malsd_beam_one_equals_greedy_and_wider_beam_is_not_worse():
+    from speech_b200.models import EncDecRNNTBPEModel
+    from speech_b200.models.configs import fastconformer_transducer_config
+
+    torch.manual_seed(1)
+    m = EncDecRNNTBPEModel(fastconformer_transducer_config("small", vocab_size=16, loss="rnnt", dropout=0.0, n_layers=1,
+                                                           sched=None, lr=1e-3))
+    m.eval()
+    enc = torch.randn(2, 7, m.joint.enc.in_features if hasattr(m.joint, "enc") else 176)
+    lens = torch.tensor([7, 5])
+    greedy = m.decoding.rnnt_decoder_predictions_tensor(enc.transpose(1, 2), lens, return_hypotheses=True)
+    blank = m.decoding.blank_id
+    k1 = ModifiedALSDBatchedComputer(m.decoder, m.joint, blank, beam_size=1, max_symbols_per_step=10)(enc, lens)
+    h1 = k1.to_hyps_list(score_norm=False)
+    for b in range(2):
+        assert h1[b][0][0] == greedy[b].y_sequence.tolist()
+    k4 = ModifiedALSDBatchedComputer(m.decoder, m.joint, blank, beam_size=4, max_symbols_per_step=10)(enc, lens)
+    h4 = k4.to_hyps_list(score_norm=False)
+    for b in range(2):
+        assert max(s for _, _, s in h4[b]) >= h1[b][0][2] - 1e-4
+
+
+def test_lcs_merge_and_word_spotter():
+    i, j, n, _ = longest_common_subsequence_merge([5, 6, 7, 8, 9], [8, 9, 10, 11])
+    assert (i, j, n) == (3, 0, 2)
+    assert lcs_alignment_merge_buffer([1, 2, 3, 4, 5], [4, 5, 6, 7], delay=2) == [1, 2, 3, 4, 5, 6, 7]
+    T, V = 12, 5
+    lp = torch.full((T, V), -8.0)
+    lp[:, 4] = -0.05
+    for t, tok in [(3, 1), (4, 1), (6, 2), (7, 3)]:
+        lp[t, 4], lp[t, tok] = -6.0, -0.05
+    hits = ctc_word_spotter(lp, {"abc": [1, 2, 3], "zz": [0, 0]}, blank=4, keyword_threshold=-2.0)
+    assert [h.word for h in hits] == ["abc"] and hits[0].start_frame in (3, 4) and hits[0].end_frame == 7
