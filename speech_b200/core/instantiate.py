@@ -82,6 +82,24 @@ def _install_default_aliases() -> None:
     a("nemo.collections.asr.models.SortformerEncLabelModel", MD + "sortformer_models.SortformerEncLabelModel")
     a("nemo.collections.asr.models.EncDecSpeakerLabelModel", MD + "label_models.EncDecSpeakerLabelModel")
     a("nemo.collections.asr.models.EncDecClassificationModel", MD + "classification_models.EncDecClassificationModel")
+    for name, mod in (("EncDecFrameClassificationModel", "classification_models"), ("EncDecRegressionModel", "classification_models"),
+                      ("SpeechEncDecSelfSupervisedModel", "ssl_models"), ("EncDecMaskedTokenPredModel", "ssl_models"),
+                      ("EncDecDenoiseMaskedTokenPredModel", "ssl_models"), ("EncDecRNNTBPEModelWithPrompt", "asr_variants"),
+                      ("EncDecHybridRNNTCTCBPEModelWithPrompt", "asr_variants"), ("EncDecRNNTBPEEOUModel", "asr_variants"),
+                      ("EncDecHybridRNNTCTCBPEEOUModel", "asr_variants"), ("EncDecMultiTalkerRNNTBPEModel", "asr_variants"),
+                      ("EncDecTransfModelBPE", "asr_variants"), ("ConfidenceEnsembleModel", "asr_variants"),
+                      ("ClusteringDiarizer", "diarizers"), ("OnlineDiarizer", "diarizers")):
+        a("nemo.collections.asr.models." + name, MD + mod + "." + name)
+    for name in ("ConvASRDecoderReconstruction", "ECAPAEncoder", "ParallelConvASREncoder"):
+        a("nemo.collections.asr.modules." + name, M + "conv_asr." + name)
+    for name in ("RandomProjectionVectorQuantizer", "RandomBlockMasking", "MultiSoftmaxDecoder"):
+        a("nemo.collections.asr.modules." + name, MD + "ssl_models." + name)
+    a("nemo.collections.asr.losses.angularloss.AngularSoftmaxLoss", "speech_b200.losses.misc.AngularSoftmaxLoss")
+    a("nemo.collections.asr.losses.AngularSoftmaxLoss", "speech_b200.losses.misc.AngularSoftmaxLoss")
+    a("nemo.collections.asr.losses.bce_loss.BCELoss", "speech_b200.losses.misc.BCELoss")
+    a("nemo.collections.asr.losses.ssl_losses.contrastive.ContrastiveLoss", "speech_b200.losses.misc.ContrastiveLoss")
+    a("nemo.collections.asr.losses.ssl_losses.mlm.MLMLoss", "speech_b200.losses.misc.MLMLoss")
+    a("nemo.collections.asr.losses.ssl_losses.mlm.MultiMLMLoss", "speech_b200.losses.misc.MultiMLMLoss")
     a("nemo.collections.speechlm2.models.SALM", "speech_b200.speechlm.salm.SALM")
     a("nemo.collections.tts.models.MagpieTTSModel", "speech_b200.tts.magpietts.MagpieTTSModel")
     a("nemo.collections.tts.models.AudioCodecModel", "speech_b200.tts.audio_codec.AudioCodecModel")

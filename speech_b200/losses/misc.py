@@ -146,6 +146,8 @@ class MLMLoss(Loss):
         """decoder_outputs: log-probs [B, T, V]; targets: [B, T]; masks: [B, D, T*c] or [B, T] (1 = masked)."""
         m = masks if masks is not None else spec_masks
         B, T, V = decoder_outputs.shape
+        T = min(T, targets.shape[1])          # the quantiser floors T / combine_time_steps, the encoder may round up
+        decoder_outputs = decoder_outputs[:, :T]
         if m is None:
             sel = torch.ones((B, T), dtype=torch.bool, device=decoder_outputs.device)
         elif m.dim() == 3:

@@ -1,0 +1,190 @@
+"""Model families beyond CTC / transducer ASR, exercised on CPU with synthetic data: a few optimisation steps must run,
+the loss must be finite (and fall where the task is learnable), and the inference entry points must work."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from speech_b200.core.config import OmegaConf
+from speech_b200.core.trainer import Trainer
+from speech_b200.models import (ClusteringDiarizer, ConfidenceEnsembleModel, EncDecClassificationModel, EncDecCTCModelBPE,
+                                EncDecMaskedTokenPredModel, EncDecMultiTalkerRNNTBPEModel, EncDecRNNTBPEModelWithPrompt,
+                                EncDecSpeakerLabelModel, SortformerEncLabelModel, SpeechEncDecSelfSupervisedModel)
+from speech_b200.models.asr_variants import entropy_confidence, evaluate_eou
+from speech_b200.models.configs import (encoder_cfg, fastconformer_ctc_config, fastconformer_transducer_config,
+                                        preprocessor_cfg)
+from speech_b200.models.diarizers import cosine_affinity, nme_spectral_clustering
+from speech_b200.models.sortformer_models import find_segments, get_ats_targets, get_pil_targets
+
+JASPER = [{"filters": 32, "repeat": 1, "kernel": [11], "stride": [1], "dilation": [1], "dropout": 0.0, "residual": False,
+           "separable": True},
+          {"filters": 32, "repeat": 2, "kernel": [13], "stride": [1], "dilation": [1], "dropout": 0.0, "residual": True,
+           "separable": True, "se": True},
+          {"filters": 48, "repeat": 1, "kernel": [1], "stride": [1], "dilation": [1], "dropout": 0.0, "residual": False}]
+
+
+def _label_cfg(decoder):
+    return OmegaConf.create({
+        "sample_rate": 16000, "labels": ["a", "b", "c"], "preprocessor": {**preprocessor_cfg(32), "dither": 0.0},
+        "encoder": {"_target_": "speech_b200.modules.conv_asr.ConvASREncoder", "feat_in": 32, "activation": "relu",
+                    "conv_mask": True, "jasper": JASPER},
+        "decoder": decoder,
+        "train_ds": {"synthetic": {"num_samples": 48, "num_classes": 3}, "batch_size": 8, "shuffle": True},
+        "optim": {"name": "adamw", "lr": 3e-3, "weight_decay": 0.0}})
+
+
+def _fit(model, steps):
+    tr = Trainer(max_steps=steps, accelerator="cpu", log_every_n_steps=1, enable_checkpointing=False, logger=False)
+    tr.fit(model)
+    return tr
+
+
+def test_classification_model_learns_tones():
+    torch.manual_seed(0)
+    m = EncDecClassificationModel(_label_cfg({"_target_": "speech_b200.modules.conv_asr.ConvASRDecoderClassification",
+                                              "feat_in": None, "num_classes": 3}))
+    tr = _fit(m, 30)
+    assert float(tr.callback_metrics["train_loss"]) < 0.8
+    assert m.transcribe([np.zeros(8000, dtype=np.float32)])[0] in ("a", "b", "c")
+
+
+def test_speaker_model_embeddings_and_verification():
+    torch.manual_seed(0)
+    m = EncDecSpeakerLabelModel(_label_cfg({"_target_": "speech_b200.modules.conv_asr.SpeakerDecoder", "feat_in": None,
+                                            "num_classes": 3, "emb_sizes": 16, "pool_mode": "attention", "angular": True}))
+    tr = _fit(m, 10)
+    assert math.isfinite(float(tr.callback_metrics["train_loss"]))
+    x = np.random.default_rng(0).standard_normal(16000).astype(np.float32)
+    assert m.get_embedding(x).shape == (1, 16)
+    assert m.verify_speakers(x, x)
+
+
+def test_nme_spectral_clustering_separates_two_speakers():
+    g = np.random.default_rng(0)
+    a = g.standard_normal(16)
+    b = g.standard_normal(16)
+    emb = np.stack([a + 0.05 * g.standard_normal(16) for _ in range(12)] + [b + 0.05 * g.standard_normal(16) for _ in range(9)])
+    labels = nme_spectral_clustering(cosine_affinity(emb), max_num_speakers=4)
+    assert len(set(labels[:12])) == 1 and len(set(labels[12:])) == 1 and labels[0] != labels[-1]
+
+
+def test_sortformer_trains_and_streams():
+    torch.manual_seed(0)
+    cfg = OmegaConf.create({
+        "sample_rate": 16000, "max_num_of_spks": 3, "preprocessor": {**preprocessor_cfg(32), "dither": 0.0, "normalize": "NA"},
+        "encoder": encoder_cfg("small", 32, 0.0, 0.0, n_layers=1),
+        "sortformer_modules": {"_target_": "speech_b200.models.sortformer_models.SortformerModules", "num_spks": 3,
+                               "dropout_rate": 0.0, "fc_d_model": 176, "tf_d_model": 64, "spkcache_len": 24, "fifo_len": 6,
+                               "chunk_len": 10, "spkcache_sil_frames_per_spk": 1},
+        "transformer_encoder": {"_target_": "speech_b200.modules.transformer.TransformerEncoder", "num_layers": 1,
+                                "hidden_size": 64, "inner_size": 128, "num_attention_heads": 4},
+        "train_ds": {"synthetic": {"num_samples": 8}, "batch_size": 4, "shuffle": True},
+        "optim": {"name": "adamw", "lr": 1e-3, "weight_decay": 0.0}})
+    m = SortformerEncLabelModel(cfg)
+    tr = _fit(m, 3)
+    assert math.isfinite(float(tr.callback_metrics["train_loss"]))
+    x = [np.random.default_rng(1).standard_normal(16000 * 3).astype(np.float32)]
+    _, offline = m.diarize(x, include_tensor_outputs=True)
+    m.streaming_mode = True
+    _, online = m.diarize(x, include_tensor_outputs=True)
+    assert offline[0].shape == online[0].shape == (38, 3)
+    lab = torch.zeros(1, 6, 3)
+    lab[0, 3:, 0] = 1
+    lab[0, 1:4, 2] = 1
+    ats = get_ats_targets(lab, lab, m.speaker_permutations)
+    assert ats[0, :, 0].tolist() == [0, 1, 1, 1, 0, 0] and ats[0, :, 1].tolist() == [0, 0, 0, 1, 1, 1]
+    pil = get_pil_targets(lab, ats, m.speaker_permutations)
+    assert torch.equal(pil, ats)
+    assert find_segments(np.array([0, .9, .9, .2, .9, .9, 0.]), 0.1, min_duration_off=0.15) == [(0.1, 0.6000000000000001)]
+
+
+def test_ssl_models_run():
+    torch.manual_seed(0)
+    enc = encoder_cfg("small", 32, 0.0, 0.0, n_layers=1)
+    ds = {"synthetic": {"num_samples": 8, "vocab_size": 8, "min_duration": 1.0, "max_duration": 1.5}, "batch_size": 4}
+    nest = EncDecMaskedTokenPredModel(OmegaConf.create({
+        "preprocessor": {**preprocessor_cfg(32), "dither": 0.0}, "encoder": enc,
+        "quantizer": {"_target_": "speech_b200.models.ssl_models.RandomProjectionVectorQuantizer", "feat_in": 32, "code_dim": 8,
+                      "num_classes": 64, "num_books": 2, "combine_time_steps": 8},
+        "masking": {"_target_": "speech_b200.models.ssl_models.RandomBlockMasking", "feat_in": 32, "block_size": 16,
+                    "mask_prob": 0.4},
+        "decoder": {"_target_": "speech_b200.models.ssl_models.MultiSoftmaxDecoder", "feat_in": 176, "num_classes": 64,
+                    "num_decoders": 2},
+        "loss": {"_target_": "speech_b200.losses.misc.MultiMLMLoss", "combine_time_steps": 8, "num_decoders": 2},
+        "train_ds": ds, "optim": {"name": "adamw", "lr": 1e-3}}))
+    assert math.isfinite(float(_fit(nest, 2).callback_metrics["train_loss"]))
+    con = SpeechEncDecSelfSupervisedModel(OmegaConf.create({
+        "preprocessor": {**preprocessor_cfg(32), "dither": 0.0}, "encoder": enc,
+        "spec_augment": {"_target_": "speech_b200.modules.spec_augment.SpectrogramAugmentation", "freq_masks": 0,
+                         "time_masks": 4, "time_width": 20},
+        "decoder": {"_target_": "speech_b200.modules.conv_asr.ConvASRDecoderReconstruction", "feat_in": 176, "feat_hidden": 32,
+                    "feat_out": 16, "stride_layers": 0, "non_stride_layers": 0},
+        "loss": {"_target_": "speech_b200.losses.misc.ContrastiveLoss", "in_dim": 32, "proj_dim": 16, "combine_time_steps": 8,
+                 "num_negatives": 5, "quantized_targets": True, "codebook_size": 16, "num_groups": 2},
+        "train_ds": ds, "optim": {"name": "adamw", "lr": 1e-3}}))
+    assert math.isfinite(float(_fit(con, 2).callback_metrics["train_loss"]))
+
+
+def test_prompt_and_multitalker_variants_step():
+    torch.manual_seed(0)
+    cfg = fastconformer_transducer_config("small", vocab_size=16, loss="rnnt", dropout=0.0, n_layers=1, sched=None, lr=1e-3)
+    audio = torch.randn(2, 16000)
+    alen = torch.tensor([16000, 12000])
+    txt = torch.randint(0, 16, (2, 5))
+    tlen = torch.tensor([5, 3])
+    pm = EncDecRNNTBPEModelWithPrompt(cfg)
+    pm.train()
+    out = pm.training_step((audio, alen, txt, tlen, torch.tensor([3, 7])), 0)
+    out["loss"].backward()
+    assert pm.prompt_kernel[0].weight.grad is not None and torch.isfinite(out["loss"])
+    mt = EncDecMultiTalkerRNNTBPEModel(cfg)
+    mt.train()
+    act = (torch.rand(2, 13) > 0.5).float()
+    out = mt.training_step((audio, alen, txt, tlen, act, 1 - act), 0)
+    out["loss"].backward()
+    assert mt.spk_kernels["0"].ff[0].weight.grad.abs().sum() > 0
+
+
+def test_eou_metrics_and_confidence():
+    r = evaluate_eou([{"start_time": 1.9, "end_time": 2.1, "eou_pred": True}, {"start_time": 0.4, "end_time": 0.5, "eou_pred": True}],
+                     [{"start_time": 0.0, "end_time": 2.0}], collar=0.0)
+    assert r.true_positives == 1 and r.latency == [pytest.approx(0.1)] and len(r.early_cutoff) == 1
+    flat = torch.full((1, 4, 8), math.log(1 / 8))
+    peaked = torch.log_softmax(torch.tensor([[[20.0] + [0.0] * 7] * 4]), -1)
+    for kind in ("tsallis", "renyi", "gibbs", "max_prob"):
+        assert float(entropy_confidence(flat, 0.5, kind).mean()) == pytest.approx(0.0, abs=1e-5)
+        assert float(entropy_confidence(peaked, 0.5, kind).mean()) > 0.99
+
+
+def test_confidence_ensemble_picks_a_model():
+    torch.manual_seed(0)
+    a = EncDecCTCModelBPE(fastconformer_ctc_config("small", vocab_size=16, n_layers=1))
+    b = EncDecCTCModelBPE(fastconformer_ctc_config("small", vocab_size=16, n_layers=1))
+    ens = ConfidenceEnsembleModel(OmegaConf.create({}), models=[a, b])
+    ens.eval()
+    out = ens.transcribe([np.random.default_rng(0).standard_normal(16000).astype(np.float32)])
+    assert len(out) == 1 and isinstance(out[0], str)
+
+
+def test_clustering_diarizer_end_to_end(tmp_path):
+    class FakeSpk:
+        def batch_inference(self, chunks, batch_size=64):
+            # "embedding" = normalised magnitude spectrum pooled to 16 bins
+            e = []
+            for c in chunks:
+                s = np.abs(np.fft.rfft(np.asarray(c), n=2048))[:512].reshape(16, 32).mean(1)
+                e.append(s / (np.linalg.norm(s) + 1e-8))
+            return torch.tensor(np.stack(e), dtype=torch.float32), None
+
+    sr = 16000
+    t = np.arange(sr * 2) / sr
+    x = np.concatenate([0.3 * np.sin(2 * np.pi * 220 * t), np.zeros(sr // 2), 0.3 * np.sin(2 * np.pi * 1800 * t)]).astype(np.float32)
+    d = ClusteringDiarizer({"diarizer": {"out_dir": str(tmp_path)}}, speaker_model=FakeSpk())
+    segs = d.diarize([x])["session_0"]
+    spk = {s[2] for s in segs}
+    assert len(spk) == 2
+    first = [s for s in segs if s[1] <= 2.1]
+    last = [s for s in segs if s[0] >= 2.4]
+    assert first and last and {s[2] for s in first} != {s[2] for s in last}
+    assert (tmp_path / "pred_rttms" / "session_0.rttm").exists()
