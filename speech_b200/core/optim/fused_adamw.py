@@ -29,7 +29,7 @@ class ParamArena:
     """Owns the flat buffers and points ``param.data`` / ``param.grad`` / ``param._lowp`` into them."""
 
     def __init__(self, groups: List[List[torch.nn.Parameter]], lowp_dtype: Optional[torch.dtype] = torch.bfloat16,
-                 fusion_groups: Optional[List[List[torch.nn.Parameter]]] = None):
+                 fusion_groups: Optional[List[List[torch.nn.Parameter]]] = None, pad_multiple: int = 1):
         groups = [self._reorder(g, fusion_groups or []) for g in groups]
         params = [p for g in groups for p in g]
         if not params:
@@ -51,6 +51,8 @@ class ParamArena:
                 self.offsets[id(p)] = (off, n)
                 off += (n + ALIGN - 1) // ALIGN * ALIGN
             self.group_ranges.append((start, off))
+        self.used_numel = off
+        off = (off + pad_multiple - 1) // pad_multiple * pad_multiple   # sharded optimizers want equal slices per rank
         self.numel = off
         self.master = torch.zeros(off, dtype=torch.float32, device=dev)
         self.grad = torch.zeros(off, dtype=torch.float32, device=dev)
@@ -136,7 +138,7 @@ class FusedAdamW(Optimizer):
 
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 1e-2,
                  max_grad_norm: float = 0.0, lowp_dtype: Optional[torch.dtype] = torch.bfloat16, amsgrad: bool = False,
-                 fusion_groups=None, **_unused):
+                 fusion_groups=None, arena_pad_multiple: int = 1, **_unused):
         if amsgrad:
             raise ValueError("FusedAdamW does not implement amsgrad")
         defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
@@ -144,15 +146,19 @@ class FusedAdamW(Optimizer):
         self.max_grad_norm = float(max_grad_norm or 0.0)
         groups = [[p for p in g["params"] if p.requires_grad] for g in self.param_groups]
         self._nonempty = [i for i, g in enumerate(groups) if g]
-        self.arena = ParamArena([groups[i] for i in self._nonempty], lowp_dtype=lowp_dtype, fusion_groups=fusion_groups)
+        self.arena = ParamArena([groups[i] for i in self._nonempty], lowp_dtype=lowp_dtype, fusion_groups=fusion_groups,
+                                pad_multiple=arena_pad_multiple)
         a = self.arena
-        self.exp_avg = torch.zeros_like(a.master)
-        self.exp_avg_sq = torch.zeros_like(a.master)
+        self._alloc_state()
         self._step = 0
         # device scalars: [0] = sum of squares / grad norm, [1] = clip coefficient, [2] = found-inf flag
         self._scalars = torch.zeros(4, dtype=torch.float32, device=a.device)
         self._scalars[1] = 1.0
         self.grad_scale: float = 1.0  # extra multiplier applied to gradients (e.g. 1/accumulation)
+
+    def _alloc_state(self) -> None:
+        self.exp_avg = torch.zeros_like(self.arena.master)
+        self.exp_avg_sq = torch.zeros_like(self.arena.master)
 
     # ------------------------------------------------------------------
     def zero_grad(self, set_to_none: bool = False) -> None:

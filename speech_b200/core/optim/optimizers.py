@@ -235,6 +235,12 @@ def _fused_adamw(*args, **kwargs):
     return FusedAdamW(*args, **kwargs)
 
 
+def _sharded_adamw(*args, **kwargs):
+    from ...parallel.fsdp import ShardedFusedAdamW
+
+    return ShardedFusedAdamW(*args, **kwargs)
+
+
 AVAILABLE_OPTIMIZERS: Dict[str, Any] = {
     "sgd": optim.SGD,
     "adam": optim.Adam,
@@ -249,7 +255,8 @@ AVAILABLE_OPTIMIZERS: Dict[str, Any] = {
     "adan": Adan,
     "fused_adam": _fused_adamw,
     "fused_adamw": _fused_adamw,
-    "distributed_fused_adam": _fused_adamw,
+    "distributed_fused_adam": _sharded_adamw,
+    "sharded_adamw": _sharded_adamw,
 }
 
 

@@ -233,7 +233,8 @@ class Trainer:
             torch.cuda.set_device(self.device)
         model.to(self.device)
         for cb in self.callbacks:
-            cb.setup(self, model, stage)
+            if hasattr(cb, "setup"):
+                cb.setup(self, model, stage)
 
     def _configure_optimizers(self):
         out = self.model.configure_optimizers()
@@ -500,7 +501,7 @@ class Trainer:
         if not weights_only:
             ckpt["optimizer_states"] = [_cpu_tree(o.state_dict()) for o in self.optimizers]
             ckpt["lr_schedulers"] = [sc["scheduler"].state_dict() for sc in self.lr_scheduler_configs]
-            ckpt["callbacks"] = {type(cb).__name__: cb.state_dict() for cb in self.callbacks}
+            ckpt["callbacks"] = {type(cb).__name__: cb.state_dict() for cb in self.callbacks if hasattr(cb, "state_dict")}
         self._call("on_save_checkpoint", ckpt)
         return ckpt
 
@@ -530,7 +531,7 @@ class Trainer:
             sc["scheduler"].load_state_dict(s)
         cb_states = ckpt.get("callbacks", {})
         for cb in self.callbacks:
-            if type(cb).__name__ in cb_states:
+            if type(cb).__name__ in cb_states and hasattr(cb, "load_state_dict"):
                 cb.load_state_dict(cb_states[type(cb).__name__])
         self._call("on_load_checkpoint", ckpt)
         logging.info(f"Restored trainer state from {path} at global_step={self.global_step}")

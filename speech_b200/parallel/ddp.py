@@ -229,6 +229,10 @@ def build_grad_sync(model, optimizers, strategy_spec, world_size: int, device: t
             except Exception as e:  # noqa: BLE001
                 logging.warning(f"peer-memory gradient exchange unavailable ({e}); using NCCL all-reduce")
         return GradSync(model, optimizers, world_size, device, sync_batchnorm=sync_batchnorm)
+    if kind in ("fsdp", "fsdp2", "zero", "sharded"):
+        from .fsdp import ShardedGradSync
+
+        return ShardedGradSync(model, optimizers, world_size, device, sync_batchnorm=sync_batchnorm)
     if hasattr(strategy_spec, "build_grad_sync"):
         return strategy_spec.build_grad_sync(model, optimizers, world_size, device)
     raise ValueError(f"unknown strategy {strategy_spec}")

@@ -1,0 +1,212 @@
+"""Tensor and sequence parallelism for transformer blocks.
+
+Column-parallel projections (q / k / v / gate / up) keep a slice of the output features, row-parallel projections (o / down)
+a slice of the input features; one reduction per attention / MLP block restores the full activation.  With sequence
+parallelism the residual stream is sharded over the sequence between blocks: the block input is all-gathered and the block
+output reduce-scattered instead of all-reduced (the plan of the reference's ``salm.py:491-504``: ``SequenceParallel`` norms,
+``ColwiseParallel`` q/k/v/gate/up, ``RowwiseParallel`` o/down).
+
+The collectives are differentiable autograd functions over ``torch.distributed`` groups (NCCL on GPUs, gloo in CPU tests).
+``PipelinedRowParallel`` overlaps a row-parallel GEMM with its reduction by splitting the rows into chunks: chunk ``i`` is
+reduced on the communication stream (by the peer-memory kernel when a symmetric buffer is available) while chunk ``i+1`` is
+still in the GEMM.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+def _all_reduce(x: torch.Tensor, group) -> torch.Tensor:
+    x = x.contiguous()
+    dist.all_reduce(x, group=group)
+    return x
+
+
+class CopyToTP(torch.autograd.Function):
+    """Identity forward, all-reduce backward (input of a column-parallel region)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return _all_reduce(g.clone(), ctx.group), None
+
+
+class ReduceFromTP(torch.autograd.Function):
+    """All-reduce forward, identity backward (output of a row-parallel region)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        return _all_reduce(x.clone(), group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class GatherFromSP(torch.autograd.Function):
+    """All-gather along the sequence dim forward, reduce-scatter backward."""
+
+    @staticmethod
+    def forward(ctx, x, group, dim):
+        ctx.group, ctx.dim = group, dim
+        ws = dist.get_world_size(group)
+        parts = [torch.empty_like(x) for _ in range(ws)]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        return torch.cat(parts, dim=dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        ws, r = dist.get_world_size(ctx.group), dist.get_rank(ctx.group)
+        g = _all_reduce(g.clone(), ctx.group)
+        return g.chunk(ws, dim=ctx.dim)[r].contiguous(), None, None
+
+
+class ReduceScatterToSP(torch.autograd.Function):
+    """Reduce-scatter along the sequence dim forward, all-gather backward."""
+
+    @staticmethod
+    def forward(ctx, x, group, dim):
+        ctx.group, ctx.dim = group, dim
+        ws, r = dist.get_world_size(group), dist.get_rank(group)
+        x = _all_reduce(x.clone(), group)
+        return x.chunk(ws, dim=dim)[r].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        ws = dist.get_world_size(ctx.group)
+        parts = [torch.empty_like(g) for _ in range(ws)]
+        dist.all_gather(parts, g.contiguous(), group=ctx.group)
+        return torch.cat(parts, dim=ctx.dim), None, None
+
+
+def _shard_linear(lin: nn.Linear, dim: int, rank: int, ws: int) -> None:
+    """Keep this rank's slice of the weight (dim 0 = output features / column-parallel, 1 = input features / row-parallel)."""
+    w = lin.weight.data
+    if w.shape[dim] % ws:
+        raise ValueError(f"cannot split dimension of size {w.shape[dim]} over {ws} ranks")
+    lin.weight = nn.Parameter(w.chunk(ws, dim=dim)[rank].clone(), requires_grad=lin.weight.requires_grad)
+    if dim == 0:
+        lin.out_features = lin.weight.shape[0]
+        if lin.bias is not None:
+            lin.bias = nn.Parameter(lin.bias.data.chunk(ws, dim=0)[rank].clone(), requires_grad=lin.bias.requires_grad)
+    else:
+        lin.in_features = lin.weight.shape[1]
+        if lin.bias is not None and rank != 0:
+            lin.bias.data.zero_()            # the bias is added once, by rank 0's partial sum
+
+
+def apply_tensor_parallel_llm(llm, group, sequence_parallel: bool = False) -> None:
+    """Shard every decoder layer of ``speechlm.llm.CausalLM`` over ``group`` in place."""
+    ws, r = dist.get_world_size(group), dist.get_rank(group)
+    if ws == 1:
+        return
+    cfg = llm.config
+    if cfg.num_attention_heads % ws or cfg.num_key_value_heads % ws:
+        raise ValueError(f"heads ({cfg.num_attention_heads} / {cfg.num_key_value_heads}) are not divisible by tp={ws}")
+    for layer in llm.model.layers:
+        att, mlp = layer.self_attn, layer.mlp
+        for lin in (att.q_proj, att.k_proj, att.v_proj, mlp.gate_proj, mlp.up_proj):
+            _shard_linear(getattr(lin, "base", lin), 0, r, ws)
+        for lin in (att.o_proj, mlp.down_proj):
+            _shard_linear(getattr(lin, "base", lin), 1, r, ws)
+        att.n_q, att.n_kv = cfg.num_attention_heads // ws, cfg.num_key_value_heads // ws
+        layer.tp_reduce = (lambda x, g=group: ReduceFromTP.apply(x, g))
+        _wrap_inputs(layer, group)
+
+
+def _wrap_inputs(layer, group) -> None:
+    """Mark the (replicated) normalised activations entering the column-parallel projections so that their gradients are
+    summed over the group."""
+    for norm in (layer.input_layernorm, layer.post_attention_layernorm):
+        fwd = norm.forward
+        norm.forward = (lambda x, f=fwd, g=group: CopyToTP.apply(f(x), g))
+
+
+class ColumnParallelLinear(nn.Module):
+    def __init__(self, in_features: int, out_features: int, group, bias: bool = True, gather_output: bool = False):
+        super().__init__()
+        ws = dist.get_world_size(group)
+        self.group, self.gather_output = group, gather_output
+        self.linear = nn.Linear(in_features, out_features // ws, bias=bias)
+
+    def forward(self, x):
+        y = self.linear(CopyToTP.apply(x, self.group))
+        return GatherFromSP.apply(y, self.group, -1) if self.gather_output else y
+
+
+class RowParallelLinear(nn.Module):
+    def __init__(self, in_features: int, out_features: int, group, bias: bool = True):
+        super().__init__()
+        ws = dist.get_world_size(group)
+        self.group = group
+        self.linear = nn.Linear(in_features // ws, out_features, bias=False)
+        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+
+    def forward(self, x):
+        y = ReduceFromTP.apply(self.linear(x), self.group)
+        return y + self.bias if self.bias is not None else y
+
+
+def vocab_parallel_cross_entropy(local_logits: torch.Tensor, targets: torch.Tensor, group, ignore_index: int = -100) -> torch.Tensor:
+    """Cross entropy when the vocabulary dimension of the logits is sharded over ``group`` (the reference runs its loss under
+    ``loss_parallel()``, ``salm.py:221-230``).  Per-token losses; ignored positions give 0."""
+    ws, r = dist.get_world_size(group), dist.get_rank(group)
+    Vl = local_logits.shape[-1]
+    lo = r * Vl
+    x = local_logits.float()
+    m = x.max(dim=-1).values.detach()
+    m_all = m.clone()
+    dist.all_reduce(m_all, op=dist.ReduceOp.MAX, group=group)
+    se = torch.exp(x - m_all.unsqueeze(-1)).sum(-1)
+    se = ReduceFromTP.apply(se, group)
+    inside = (targets >= lo) & (targets < lo + Vl)
+    idx = (targets - lo).clamp(min=0, max=Vl - 1)
+    tgt = torch.where(inside, x.gather(-1, idx.unsqueeze(-1)).squeeze(-1), torch.zeros_like(m))
+    tgt = ReduceFromTP.apply(tgt, group)
+    loss = torch.log(se) + m_all - tgt
+    return torch.where(targets == ignore_index, torch.zeros_like(loss), loss)
+
+
+class PipelinedRowParallel:
+    """``y = reduce(x @ W_local^T)`` with the reduction of row-chunk ``i`` overlapping the GEMM of chunk ``i+1``.
+
+    ``reducer(flat_fp32)`` is an in-place all-reduce on the current stream (for instance ``parallel.symm.PeerAllReduce``);
+    without one, NCCL's asynchronous all-reduce is used.  Forward only (inference / frozen layers)."""
+
+    def __init__(self, group, chunks: int = 4, reducer: Optional[Callable[[torch.Tensor], None]] = None):
+        self.group, self.chunks, self.reducer = group, chunks, reducer
+        self.comm = torch.cuda.Stream() if torch.cuda.is_available() else None
+
+    @torch.no_grad()
+    def __call__(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        from .. import ops
+
+        rows = x.reshape(-1, x.shape[-1])
+        outs, works = [], []
+        for part in rows.chunk(self.chunks, dim=0):
+            y = ops.linear(part, weight, None).float()
+            if self.comm is not None and x.is_cuda:
+                self.comm.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self.comm):
+                    if self.reducer is not None:
+                        self.reducer(y.view(-1))
+                    else:
+                        works.append(dist.all_reduce(y, group=self.group, async_op=True))
+                y.record_stream(self.comm)
+            else:
+                dist.all_reduce(y, group=self.group)
+            outs.append(y)
+        for w in works:
+            w.wait()
+        if self.comm is not None and x.is_cuda:
+            torch.cuda.current_stream().wait_stream(self.comm)
+        return torch.cat(outs, dim=0).reshape(*x.shape[:-1], weight.shape[0]).to(x.dtype)

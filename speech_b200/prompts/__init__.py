@@ -80,7 +80,8 @@ class PromptFormatter:
                 raise ValueError(f"Missing slot '{key}' for template '{template}' (got {list(slots)})")
             return str(slots[key])
 
-        return re.sub(r"\|([A-Za-z_0-9]+)\|", sub, template)
+        # slots look like |name|; special tokens such as <|im_start|> are left alone
+        return re.sub(r"(?<!<)\|([A-Za-z_0-9]+)\|(?!>)", sub, template)
 
     def encode_turn(self, prompt_template: str, expected_slots: dict, slot_values: dict) -> List[int]:
         text = prompt_template.replace(BOS_SLOT, "").replace(EOS_SLOT, "")

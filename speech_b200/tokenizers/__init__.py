@@ -188,14 +188,58 @@ class ByteLevelTokenizer(TokenizerSpec):
         self.vocab = [chr(i) for i in range(256)] + list(special_tokens or [])
         self._special = {t: 256 + i for i, t in enumerate(special_tokens or [])}
 
+    @property
+    def vocab_size(self):
+        return len(self.vocab)
+
+    def add_special_tokens(self, special_tokens) -> int:
+        toks = special_tokens.get("additional_special_tokens", []) if isinstance(special_tokens, dict) else list(special_tokens)
+        n = 0
+        for t in toks:
+            if t not in self._special:
+                self._special[t] = len(self.vocab)
+                self.vocab.append(t)
+                n += 1
+        return n
+
+    def token_to_id(self, token):
+        return self._special.get(token, ord(token) if len(token) == 1 and ord(token) < 256 else -1)
+
+    def _special_id(self, name):
+        return self._special.get(name, -1)
+
+    @property
+    def pad_id(self):
+        return self._special_id("<pad>")
+
+    @property
+    def bos_id(self):
+        return self._special_id("<s>")
+
+    @property
+    def eos_id(self):
+        return self._special_id("</s>")
+
     def text_to_ids(self, text):
-        return list(text.encode("utf-8"))
+        """Special tokens that occur verbatim in the text map to their single id, everything else to UTF-8 bytes."""
+        if not self._special:
+            return list(text.encode("utf-8"))
+        import re
+
+        pat = "(" + "|".join(re.escape(t) for t in sorted(self._special, key=len, reverse=True)) + ")"
+        out: List[int] = []
+        for piece in re.split(pat, text):
+            if piece in self._special:
+                out.append(self._special[piece])
+            elif piece:
+                out.extend(piece.encode("utf-8"))
+        return out
 
     def ids_to_text(self, ids):
         return bytes(int(i) for i in ids if int(i) < 256).decode("utf-8", errors="ignore")
 
     def text_to_tokens(self, text):
-        return [chr(b) for b in text.encode("utf-8")]
+        return [self.vocab[i] for i in self.text_to_ids(text)]
 
     def tokens_to_ids(self, tokens):
         return [self._special.get(t, ord(t)) for t in tokens]
@@ -494,3 +538,26 @@ class SyntheticTokenizer(TokenizerSpec):
 
     def tokens_to_text(self, tokens):
         return " ".join(t.lstrip("▁") for t in tokens)
+
+
+def build_tokenizer(cfg) -> TokenizerSpec:
+    """``cfg.type`` ∈ {bpe, spe, wpe, char, byte, hf, auto, synthetic}; mirrors the tokenizer block of model configs
+    (``dir`` holding ``tokenizer.model`` / ``vocab.txt``, or ``model_path`` / ``pretrained_model_name``)."""
+    import os
+
+    get = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: getattr(cfg, k, d))
+    kind = str(get("type", "bpe")).lower()
+    if kind in ("bpe", "spe", "sentencepiece"):
+        path = get("model_path", None) or os.path.join(get("dir"), "tokenizer.model")
+        return SentencePieceTokenizer(path, special_tokens=get("special_tokens", None))
+    if kind == "wpe":
+        return WordPieceVocabTokenizer(get("vocab_file", None) or os.path.join(get("dir"), "vocab.txt"))
+    if kind == "char":
+        return CharTokenizer(get("vocab", None) or get("vocab_file"))
+    if kind == "byte":
+        return ByteLevelTokenizer(special_tokens=list(get("special_tokens", None) or []))
+    if kind in ("hf", "auto", "huggingface"):
+        return AutoTokenizer(get("pretrained_model_name", None) or get("dir"), use_fast=get("use_fast", True))
+    if kind == "synthetic":
+        return SyntheticTokenizer(int(get("vocab_size")))
+    raise ValueError(f"unknown tokenizer type {kind}")

@@ -1,0 +1,81 @@
+"""Parallel strategies on CPU (gloo, two ranks): device mesh, tensor-parallel LLM vs the unsharded model, vocabulary-
+parallel cross entropy, sharded AdamW vs plain AdamW on averaged gradients, world-size independent optimizer checkpoints."""
+import os
+import subprocess
+import sys
+import textwrap
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+SCRIPT = textwrap.dedent("""
+    import os, sys, torch, torch.distributed as dist
+    sys.path.insert(0, {repo!r})
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from speech_b200.parallel.mesh import DeviceMesh
+    from speech_b200.parallel.tp import apply_tensor_parallel_llm, vocab_parallel_cross_entropy
+    from speech_b200.parallel.fsdp import ShardedFusedAdamW
+    from speech_b200.core.optim.fused_adamw import FusedAdamW
+    from speech_b200.speechlm.llm import CausalLM, LLMConfig
+    mesh = DeviceMesh({{"tp": 2, "dp_shard": -1}})
+    assert mesh.size("tp") == 2 and mesh.size("dp") == world // 2
+    torch.manual_seed(0)
+    cfg = LLMConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=8)
+    ref = CausalLM(cfg); tp = CausalLM(cfg); tp.load_state_dict(ref.state_dict())
+    apply_tensor_parallel_llm(tp, mesh.group("tp"))
+    ids = torch.randint(0, 64, (2, 7))
+    a = ref(input_ids=ids)["logits"]; b = tp(input_ids=ids)["logits"]
+    assert torch.allclose(a, b, atol=1e-5), (a-b).abs().max()
+    a.pow(2).mean().backward(); b.pow(2).mean().backward()
+    g_ref = ref.model.layers[0].self_attn.q_proj.weight.grad.chunk(2, 0)[mesh.rank("tp")]
+    assert torch.allclose(g_ref, tp.model.layers[0].self_attn.q_proj.weight.grad, atol=1e-6)
+    assert torch.allclose(ref.model.embed_tokens.weight.grad, tp.model.embed_tokens.weight.grad, atol=1e-6)
+    # vocab-parallel CE
+    lg = torch.randn(3, 5, 64); tg = torch.randint(0, 64, (3, 5)); tg[0, 0] = -100
+    full = torch.nn.functional.cross_entropy(lg.view(-1, 64), tg.view(-1), ignore_index=-100, reduction="none").view(3, 5)
+    dist.broadcast(lg, 0); dist.broadcast(tg, 0)
+    full = torch.nn.functional.cross_entropy(lg.view(-1, 64), tg.view(-1), ignore_index=-100, reduction="none").view(3, 5)
+    part = vocab_parallel_cross_entropy(lg.chunk(2, -1)[rank], tg, None)
+    assert torch.allclose(full, part, atol=1e-5)
+    # sharded AdamW == plain AdamW on averaged grads
+    torch.manual_seed(1)
+    def make():
+        torch.manual_seed(1)
+        return [torch.nn.Parameter(torch.randn(37, 5)), torch.nn.Parameter(torch.randn(300))]
+    p1, p2 = make(), make()
+    o1 = FusedAdamW(p1, lr=1e-2, max_grad_norm=1.0); o2 = ShardedFusedAdamW(p2, lr=1e-2, max_grad_norm=1.0)
+    for it in range(3):
+        torch.manual_seed(10 * it + rank)
+        gs = [torch.randn_like(p) for p in p1]
+        avg = [g.clone() for g in gs]
+        for g in avg: dist.all_reduce(g); g.div_(world)
+        for p, g in zip(p1, avg): p.grad.copy_(g)
+        for p, g in zip(p2, gs): p.grad.copy_(g)
+        o1.step(); o2.step()
+        for a_, b_ in zip(p1, p2):
+            assert torch.allclose(a_, b_, atol=1e-6), (it, (a_-b_).abs().max())
+    sd = o2.state_dict()
+    assert torch.allclose(sd["state"][0]["exp_avg"], o1.state_dict()["state"][0]["exp_avg"], atol=1e-7)
+    o2.load_state_dict(sd)
+    print("RESULT ok", rank)
+    dist.destroy_process_group()
+""")
+
+
+def test_mesh_tp_and_sharded_optimizer_two_ranks(tmp_path):
+    script = tmp_path / "par.py"
+    script.write_text(SCRIPT.format(repo=REPO))
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29762", str(script)],
+                         capture_output=True, text=True, timeout=600, env=dict(os.environ, MASTER_ADDR="127.0.0.1"))
+    assert out.returncode == 0, out.stderr[-3000:]
+    assert out.stdout.count("RESULT ok") == 2
+
+
+def test_mesh_layout_without_process_groups():
+    from speech_b200.parallel.mesh import DeviceMesh
+
+    m = DeviceMesh({"dp_replicate": 2, "dp_shard": 2, "tp": 2}, rank=5, world_size=8, create_groups=False)
+    assert m.coords == {"pp": 0, "dp_replicate": 1, "dp_shard": 0, "cp": 0, "tp": 1}
+    assert m.ranks("tp") == [4, 5] and m.ranks("dp_shard") == [5, 7] and m.ranks("dp") == [1, 3, 5, 7]
+    assert m.size("dp") == 4 and m.rank("dp") == 2 and not m.is_dp_source()

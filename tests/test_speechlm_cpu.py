@@ -1,0 +1,138 @@
+"""Speech-LLM stack on CPU: native decoder-only LM (KV-cache decoding equals full recomputation, HF-directory round trip),
+placeholder splicing, LoRA, SALM training + generation, failure detection on the host."""
+import math
+
+import pytest
+import torch
+
+from speech_b200.core.config import OmegaConf
+from speech_b200.core.trainer import Trainer
+from speech_b200.models.configs import encoder_cfg, preprocessor_cfg
+from speech_b200.parallel.resiliency import FaultToleranceCallback, HeartbeatMonitor, StragglerDetectionCallback
+from speech_b200.speechlm.llm import CausalLM, LLMConfig
+from speech_b200.speechlm.lora import apply_lora, freeze_and_subset, merge_lora
+from speech_b200.speechlm.salm import IGNORE_INDEX, SALM, replace_placeholders_and_build_targets
+from speech_b200.tokenizers import ByteLevelTokenizer
+
+TINY = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+            num_key_value_heads=2, head_dim=16)
+
+
+def test_llm_cache_decode_matches_full_forward_and_left_padding(tmp_path):
+    torch.manual_seed(0)
+    m = CausalLM(LLMConfig(**TINY)).eval()
+    ids = torch.randint(0, 300, (2, 9))
+    full = m(input_ids=ids)["logits"]
+    cache = [dict() for _ in m.model.layers]
+    a = m(input_ids=ids[:, :5], cache=cache)["logits"]
+    outs = [a]
+    for t in range(5, 9):
+        outs.append(m(input_ids=ids[:, t:t + 1], cache=cache)["logits"])
+    assert torch.allclose(torch.cat(outs, 1), full, atol=1e-4)
+    # left padding must not change the logits of the real tokens
+    pad = torch.cat([torch.zeros(2, 3, dtype=torch.long), ids], dim=1)
+    mask = torch.cat([torch.zeros(2, 3, dtype=torch.long), torch.ones(2, 9, dtype=torch.long)], dim=1)
+    padded = m(input_ids=pad, attention_mask=mask)["logits"][:, 3:]
+    assert torch.allclose(padded, full, atol=1e-4)
+    m.save_pretrained(str(tmp_path / "hf"))
+    again = CausalLM.from_pretrained(str(tmp_path / "hf")).eval()
+    assert torch.allclose(again(input_ids=ids)["logits"], full, atol=1e-6)
+    gen = m.generate(input_ids=ids, max_new_tokens=4)
+    assert gen.shape == (2, 4)
+    ref_next = full[:, -1].argmax(-1)
+    assert torch.equal(gen[:, 0], ref_next)
+
+
+def test_placeholder_splicing_targets_and_left_padding():
+    H = 4
+    ids = torch.tensor([[5, 99, 6, 7, 0], [99, 8, 99, 0, 0]])          # 99 = audio placeholder, 0 = padding
+    emb = torch.arange(2 * 5 * H, dtype=torch.float32).view(2, 5, H)
+    tgt = torch.where(ids == 0, torch.full_like(ids, IGNORE_INDEX), ids)
+    aud = [torch.full((3, H), -1.0), torch.full((2, H), -2.0), torch.full((1, H), -3.0)]
+    e, t, m = replace_placeholders_and_build_targets(ids, emb, 0, 99, aud, tgt)
+    assert e.shape == (2, 6, H) and m.sum(1).tolist() == [6, 4]
+    assert t[0].tolist() == [5, -100, -100, -100, 6, 7]
+    assert t[1].tolist() == [-100, -100, -100, -100, 8, -100]            # left padded: 2 pads, 2 audio, token, 1 audio
+    assert float(e[1, 2, 0]) == -2.0 and float(e[1, 5, 0]) == -3.0 and m[1].tolist() == [False, False, True, True, True, True]
+    with pytest.raises(ValueError):
+        replace_placeholders_and_build_targets(ids, emb, 0, 99, aud[:2], tgt)
+
+
+def test_lora_starts_as_identity_trains_only_adapters_and_merges():
+    torch.manual_seed(0)
+    m = CausalLM(LLMConfig(**TINY))
+    ids = torch.randint(0, 300, (1, 6))
+    before = m(input_ids=ids)["logits"].detach()
+    names = apply_lora(m, r=4, lora_alpha=8, target_modules=["q_proj", "v_proj"])
+    assert len(names) == 4
+    assert torch.allclose(m(input_ids=ids)["logits"], before, atol=1e-6)
+    for n, p in m.named_parameters():
+        if ".lora_" not in n:
+            p.requires_grad_(False)
+    trainable = freeze_and_subset(m.named_parameters(), ["^model\\..+$"], [])
+    assert trainable and all(".lora_" in n for n, _ in trainable)
+    m(input_ids=ids)["logits"].pow(2).mean().backward()
+    with torch.no_grad():
+        for _, p in trainable:
+            p.add_(0.05 * torch.randn_like(p))
+    changed = m(input_ids=ids)["logits"].detach()
+    merge_lora(m)
+    assert torch.allclose(m(input_ids=ids)["logits"], changed, atol=1e-4)
+    assert not any(".lora_" in n for n, _ in m.named_parameters())
+
+
+def test_salm_trains_and_generates():
+    torch.manual_seed(0)
+    tok = ByteLevelTokenizer(special_tokens=["<pad>", "<s>", "</s>", "<|im_start|>", "<|im_end|>"])
+    cfg = OmegaConf.create({
+        "audio_locator_tag": "<|audioplaceholder|>", "prompt_format": "qwen", "llm": dict(TINY, tie_word_embeddings=True),
+        "perception": {"preprocessor": {**preprocessor_cfg(32), "dither": 0.0}, "encoder": encoder_cfg("small", 32, 0.0, 0.0, n_layers=1),
+                       "modality_adapter": {"_target_": "speech_b200.speechlm.perception.IdentityConnector", "d_model": 176}},
+        "freeze_params": ["^perception\\.preprocessor\\..+$", "^llm\\..+$"], "prevent_freeze_params": [],
+        "train_ds": {"synthetic": {"num_samples": 16}, "batch_size": 4, "shuffle": True},
+        "optim": {"name": "adamw", "lr": 3e-3, "weight_decay": 0.0}})
+    m = SALM(cfg, tokenizer=tok)
+    assert not any(p.requires_grad for n, p in m.named_parameters() if n.startswith("llm."))
+    assert m.llm.model.embed_tokens is None and m.embed_tokens.num_embeddings >= tok.vocab_size
+    losses = []
+
+    class Rec:
+        def on_train_batch_end(self, trainer, model, outputs, batch, batch_idx):
+            losses.append(float(outputs["loss"]))
+
+    Trainer(max_steps=12, accelerator="cpu", log_every_n_steps=1, enable_checkpointing=False, logger=False, callbacks=[Rec()]).fit(m)
+    assert all(math.isfinite(l) for l in losses) and min(losses[-4:]) < losses[0]
+    m.eval()
+    out = m.generate([[{"role": "user", "content": "Transcribe: <|audioplaceholder|>"}]] * 2, audios=torch.randn(2, 12000),
+                     audio_lens=torch.tensor([12000, 8000]), max_new_tokens=5)
+    assert out.shape[0] == 2 and out.shape[1] <= 5
+
+
+def test_heartbeat_straggler_and_fault_tolerance_on_host(tmp_path):
+    now = [1000.0]
+    hb0 = HeartbeatMonitor(0, 3, timeout=30.0, directory=str(tmp_path), clock=lambda: now[0])
+    hb1 = HeartbeatMonitor(1, 3, timeout=30.0, directory=str(tmp_path), clock=lambda: now[0])
+    hb0.beat(1)
+    hb1.beat(1)
+    assert hb0.dead_ranks() == [2]                    # rank 2 never joined
+    now[0] += 60
+    hb0.beat(2)
+    assert hb0.dead_ranks() == [1, 2]                 # rank 1 stopped beating
+    t = [0.0]
+    sd = StragglerDetectionCallback(report_time_interval=0.0, clock=lambda: t[0], stop_if_detected=True)
+
+    class Tr:
+        callback_metrics = {}
+        should_stop = False
+        global_rank, world_size, global_step, log_dir = 0, 3, 0, str(tmp_path)
+
+    tr = Tr()
+    for dur in (1.0, 1.0, 2.5):
+        sd.on_train_batch_start(tr, None, None, 0)
+        t[0] += dur
+        sd.on_train_batch_end(tr, None, None, None, 0)
+    assert sd.last_report["individual_perf"] == pytest.approx(0.4) and tr.callback_metrics["straggler/individual_perf"] < 0.7
+    ft = FaultToleranceCallback(heartbeat_timeout=30.0, directory=str(tmp_path / "hb"), exit_on_failure=False, save_on_failure=False)
+    ft.setup(tr, None, "fit")
+    ft.on_train_batch_end(tr, None, None, None, 0)
+    assert tr.should_stop and "no heartbeat from ranks [1, 2]" in ft.failures[0]
