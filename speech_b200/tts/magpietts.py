@@ -1,0 +1,376 @@
+"""MagpieTTS: text → audio-codec tokens with an encoder-decoder transformer, decoded to a waveform by a frozen codec.
+
+Structure (reference ``tts/models/magpietts.py``): text embedding + non-causal text encoder; causal decoder with
+cross-attention over the text (optionally with a beta-binomial alignment prior and a CTC forward-sum alignment loss on
+selected cross-attention heads); audio frames enter as the sum of one embedding per codebook (times ``frame_stacking_factor``
+stacked frames) and leave through ``final_proj: d_model → codebooks · stack · tokens`` (``:524-530``); an optional *local
+transformer* refines the codebooks of one step autoregressively (``:532-570``); classifier-free guidance by dropping the
+text condition during training and mixing conditional / unconditional logits at inference; KV-cache autoregressive
+``infer_batch`` (``:2856``) and ``do_tts`` (``:3711``).
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ..core.config import DictConfig, OmegaConf, cfg_get, open_dict
+from ..core.modelpt import ModelPT
+from .audio_codec import AudioCodecModel
+from .transformer_2501 import Transformer
+
+
+def beta_binomial_prior(text_len: int, audio_len: int, scaling: float = 1.0) -> torch.Tensor:
+    """[audio_len, text_len]: row ``t`` is BetaBinomial(n = text_len - 1, a = s·(t+1), b = s·(audio_len - t))."""
+    k = torch.arange(text_len, dtype=torch.float64)
+    n = float(text_len - 1)
+    out = []
+    for t in range(1, audio_len + 1):
+        a, b = scaling * t, scaling * (audio_len + 1 - t)
+        logp = (torch.lgamma(torch.tensor(n + 1)) - torch.lgamma(k + 1) - torch.lgamma(n - k + 1)
+                + torch.lgamma(k + a) + torch.lgamma(n - k + b) - torch.lgamma(torch.tensor(n + a + b))
+                - (torch.lgamma(torch.tensor(a)) + torch.lgamma(torch.tensor(b)) - torch.lgamma(torch.tensor(a + b))))
+        out.append(logp.exp())
+    return torch.stack(out).float()
+
+
+class ForwardSumLoss(nn.Module):
+    """CTC over attention: the text positions are the labels 1..T_text, a constant blank column is prepended."""
+
+    def __init__(self, blank_logprob: float = -1.0):
+        super().__init__()
+        self.blank_logprob = blank_logprob
+
+    def forward(self, attn_logprob: torch.Tensor, in_lens: torch.Tensor, out_lens: torch.Tensor) -> torch.Tensor:
+        """attn_logprob [B, T_audio, T_text] (log-probabilities); in_lens = text lengths, out_lens = audio lengths."""
+        B = attn_logprob.shape[0]
+        x = F.pad(attn_logprob.float(), (1, 0), value=self.blank_logprob)
+        total = attn_logprob.new_zeros((), dtype=torch.float32)
+        for b in range(B):
+            Tt, Ta = int(in_lens[b]), int(out_lens[b])
+            lp = torch.log_softmax(x[b, :Ta, : Tt + 1], dim=-1).unsqueeze(1)
+            tgt = torch.arange(1, Tt + 1).unsqueeze(0)
+            total = total + F.ctc_loss(lp, tgt, torch.tensor([Ta]), torch.tensor([Tt]), blank=0, zero_infinity=True)
+        return total / B
+
+
+class MagpieTTSModel(ModelPT):
+    def __init__(self, cfg: DictConfig, trainer=None, codec: Optional[AudioCodecModel] = None, tokenizer=None):
+        super().__init__(cfg=cfg, trainer=trainer)
+        cfg = self._cfg
+        # ---- codec (frozen)
+        if codec is None:
+            if cfg_get(cfg, "codecmodel_path", None):
+                codec = AudioCodecModel.restore_from(cfg.codecmodel_path)
+            else:
+                codec = AudioCodecModel(cfg.codec)
+        object.__setattr__(self, "_codec", codec)                    # not a sub-module: never trained or check-pointed here
+        codec.eval()
+        for p in codec.parameters():
+            p.requires_grad_(False)
+        self.num_audio_codebooks = codec.num_codebooks
+        self.codebook_size = codec.codebook_size
+        self.audio_bos_id, self.audio_eos_id = self.codebook_size, self.codebook_size + 1
+        self.num_all_tokens_per_codebook = self.codebook_size + cfg_get(cfg, "num_special_audio_tokens", 8)
+        self.frame_stacking_factor = cfg_get(cfg, "frame_stacking_factor", 1)
+        # ---- text
+        if tokenizer is None:
+            from ..tokenizers import build_tokenizer
+
+            tokenizer = build_tokenizer(cfg.text_tokenizer)
+        self.tokenizer = tokenizer
+        n_text = int(tokenizer.vocab_size) + 2
+        self.text_bos_id, self.text_eos_id = n_text - 2, n_text - 1
+        d = cfg_get(cfg, "embedding_dim", 256)
+        self.d_model = d
+        self.text_embedding = nn.Embedding(n_text, d)
+        self.encoder = Transformer(**dict(cfg.encoder))
+        self.decoder = Transformer(**dict(cfg.decoder))
+        C = self.num_audio_codebooks * self.frame_stacking_factor
+        self.audio_embeddings = nn.ModuleList([nn.Embedding(self.num_all_tokens_per_codebook, d) for _ in range(C)])
+        self.final_proj = nn.Linear(d, C * self.num_all_tokens_per_codebook)
+        # ---- optional local transformer over the codebooks of one step
+        self.local_transformer_type = str(cfg_get(cfg, "local_transformer_type", "none")).lower()
+        if self.local_transformer_type != "none":
+            dl = cfg_get(cfg, "local_transformer_hidden_dim", d)
+            self.local_transformer_in_projection = nn.Linear(d, dl)
+            self.local_transformer = Transformer(n_layers=cfg_get(cfg, "local_transformer_n_layers", 1), d_model=dl, d_ffn=dl * 4,
+                                                 sa_n_heads=cfg_get(cfg, "local_transformer_n_heads", 1), kernel_size=1,
+                                                 is_causal=self.local_transformer_type == "autoregressive",
+                                                 max_length_causal_mask=C + 2, use_learnable_pos_emb=True)
+            self.local_transformer_audio_embeddings = nn.ModuleList([nn.Embedding(self.num_all_tokens_per_codebook, dl) for _ in range(C)])
+            self.local_transformer_out_projections = nn.ModuleList([nn.Linear(dl, self.num_all_tokens_per_codebook) for _ in range(C)])
+        # ---- losses / regularisers
+        self.alignment_loss_scale = cfg_get(cfg, "alignment_loss_scale", 0.0)
+        self.alignment_layers = list(cfg_get(cfg, "alignment_decoder_loss_layers", cfg_get(cfg, "prior_layers", [])) or [])
+        self.prior_scaling_factor = cfg_get(cfg, "prior_scaling_factor", None)
+        self.prior_end_step = cfg_get(cfg, "prior_end_step", 0)
+        self.cfg_unconditional_prob = cfg_get(cfg, "cfg_unconditional_prob", 0.0)
+        self.alignment_loss = ForwardSumLoss()
+        self.moe_loss_scale = cfg_get(cfg, "moe_load_balancing_loss_scale", 0.01)
+        if not self._is_model_being_restored and self._train_dl is None:
+            self._setup_dataloaders_from_cfg()
+
+    def _setup_dataloaders_from_cfg(self):
+        if not hasattr(self, "final_proj"):
+            return
+        super()._setup_dataloaders_from_cfg()
+
+    @classmethod
+    def list_available_models(cls):
+        return []
+
+    # ------------------------------------------------------------------ data: (text ids, text len, audio, audio len)
+    def _loader(self, config):
+        if config is None:
+            return None
+        from .data import build_tts_dataloader
+
+        return build_tts_dataloader(config, self.tokenizer, sample_rate=self._codec.sample_rate)
+
+    def setup_training_data(self, c):
+        self._train_dl = self._loader(c)
+
+    def setup_validation_data(self, c):
+        self._validation_dl = self._loader(c)
+
+    # ------------------------------------------------------------------ token plumbing
+    @torch.no_grad()
+    def audio_to_codes(self, audio, audio_len):
+        """→ codes [B, C, T+2] with BOS / EOS added, lengths."""
+        self._codec.to(audio.device)
+        codes, lens = self._codec.encode(audio, audio_len)
+        B, C, T = codes.shape
+        out = torch.full((B, C, T + 2), self.audio_eos_id, dtype=torch.long, device=codes.device)
+        out[:, :, 0] = self.audio_bos_id
+        out[:, :, 1:T + 1] = codes
+        for b in range(B):
+            out[b, :, int(lens[b]) + 1] = self.audio_eos_id
+            out[b, :, int(lens[b]) + 2:] = 0
+        return out, lens + 2
+
+    @torch.no_grad()
+    def codes_to_audio(self, codes, codes_len):
+        self._codec.to(codes.device)
+        codes = codes.clamp(max=self.codebook_size - 1)
+        return self._codec.decode(codes, codes_len)
+
+    def stack_codes(self, codes, lens):
+        S = self.frame_stacking_factor
+        if S == 1:
+            return codes, lens
+        B, C, T = codes.shape
+        pad = (-T) % S
+        codes = F.pad(codes, (0, pad), value=self.audio_eos_id)
+        codes = codes.view(B, C, -1, S).permute(0, 1, 3, 2).reshape(B, C * S, -1)
+        return codes, torch.div(lens + S - 1, S, rounding_mode="floor")
+
+    def unstack_codes(self, codes, lens):
+        S = self.frame_stacking_factor
+        if S == 1:
+            return codes, lens
+        B, CS, T = codes.shape
+        C = CS // S
+        return codes.view(B, C, S, T).permute(0, 1, 3, 2).reshape(B, C, T * S), lens * S
+
+    def embed_audio_tokens(self, codes):
+        """codes [B, C·S, T] → [B, T, d]: mean of the per-codebook embeddings."""
+        x = 0.0
+        for c, emb in enumerate(self.audio_embeddings):
+            x = x + emb(codes[:, c])
+        return x / len(self.audio_embeddings)
+
+    def encode_text(self, text, text_len):
+        mask = torch.arange(text.shape[1], device=text.device)[None] < text_len[:, None]
+        out = self.encoder(self.text_embedding(text), mask)["output"]
+        return out, mask
+
+    # ------------------------------------------------------------------ teacher-forced forward
+    def _priors(self, text_len, audio_len, Ta, Tt, device):
+        if self.prior_scaling_factor is None or (self.prior_end_step and self.global_step >= self.prior_end_step):
+            return None
+        pri = torch.zeros((len(text_len), Ta, Tt), device=device)
+        for b in range(len(text_len)):
+            tl, al = int(text_len[b]), int(audio_len[b])
+            pri[b, :al, :tl] = beta_binomial_prior(tl, al, self.prior_scaling_factor).to(device)
+        return pri
+
+    def forward(self, text, text_len, codes, codes_len, drop_condition: bool = False):
+        """Teacher forcing.  codes [B, C·S, T] (stacked, with BOS / EOS).  Returns logits [B, T-1, C·S, N] and the
+        cross-attention probabilities of the decoder layers."""
+        cond, cond_mask = self.encode_text(text, text_len)
+        if drop_condition:
+            cond = torch.zeros_like(cond)
+        inp, tgt_len = codes[:, :, :-1], codes_len - 1
+        x = self.embed_audio_tokens(inp)
+        xmask = torch.arange(x.shape[1], device=x.device)[None] < tgt_len[:, None]
+        prior = self._priors(text_len, tgt_len, x.shape[1], cond.shape[1], x.device) if self.training else None
+        priors = [prior if i in self.alignment_layers else None for i in range(len(self.decoder.layers))] if prior is not None else None
+        out = self.decoder(x, xmask, cond=cond, cond_mask=cond_mask, attn_prior=priors)
+        h = out["output"]
+        B, T, _ = h.shape
+        logits = ops.linear(h, self.final_proj.weight, self.final_proj.bias).float().view(B, T, len(self.audio_embeddings), -1)
+        return logits, out["attn_probabilities"], h, xmask
+
+    def local_transformer_logits(self, h: torch.Tensor, target_codes: torch.Tensor) -> torch.Tensor:
+        """Teacher-forced local transformer: h [N, d] decoder states, target_codes [N, C] → logits [N, C, V]."""
+        x0 = self.local_transformer_in_projection(h).unsqueeze(1)
+        embs = [self.local_transformer_audio_embeddings[c](target_codes[:, c]).unsqueeze(1) for c in range(target_codes.shape[1] - 1)]
+        seq = torch.cat([x0] + embs, dim=1)
+        mask = torch.ones(seq.shape[:2], dtype=torch.bool, device=seq.device)
+        out = self.local_transformer(seq, mask)["output"]
+        return torch.stack([self.local_transformer_out_projections[c](out[:, c]) for c in range(target_codes.shape[1])], dim=1).float()
+
+    def _loss(self, batch):
+        text, text_len, audio, audio_len = batch[:4]
+        codes, codes_len = self.audio_to_codes(audio, audio_len)
+        codes, codes_len = self.stack_codes(codes, codes_len)
+        drop = self.training and self.cfg_unconditional_prob > 0 and float(torch.rand(())) < self.cfg_unconditional_prob
+        logits, attn, h, xmask = self.forward(text, text_len, codes, codes_len, drop_condition=drop)
+        tgt = codes[:, :, 1:].permute(0, 2, 1)                         # [B, T-1, C·S]
+        ce = F.cross_entropy(logits[xmask].reshape(-1, logits.shape[-1]), tgt[xmask].reshape(-1))
+        logs = {"codebook_loss": ce.detach()}
+        loss = ce
+        if self.local_transformer_type != "none":
+            lt = self.local_transformer_logits(h[xmask].float(), tgt[xmask])
+            lt_loss = F.cross_entropy(lt.reshape(-1, lt.shape[-1]), tgt[xmask].reshape(-1))
+            loss = loss + lt_loss
+            logs["local_transformer_loss"] = lt_loss.detach()
+        if self.alignment_loss_scale > 0 and not drop and self.alignment_layers:
+            al = 0.0
+            for i in self.alignment_layers:
+                p = attn[i]
+                if p is None:
+                    continue
+                al = al + self.alignment_loss(torch.log(p.float().mean(1) + 1e-8), text_len, codes_len - 1)
+            loss = loss + self.alignment_loss_scale * al / max(1, len(self.alignment_layers))
+            logs["alignment_loss"] = torch.as_tensor(al).detach()
+        for k, v in self.decoder.moe_aux_losses().items():
+            if k == "load_balancing_loss":
+                loss = loss + self.moe_loss_scale * v
+                logs["moe_load_balancing_loss"] = v.detach()
+        return loss, logs
+
+    def training_step(self, batch, batch_idx):
+        loss, logs = self._loss(batch)
+        self.log_dict({"train_loss": loss.detach(), **{f"train_{k}": v for k, v in logs.items()}})
+        return {"loss": loss}
+
+    def validation_step(self, batch, batch_idx, dataloader_idx=0):
+        loss, logs = self._loss(batch)
+        return {"val_loss": loss}
+
+    # ------------------------------------------------------------------ inference
+    @staticmethod
+    def _sample(logits: torch.Tensor, temperature: float, topk: int) -> torch.Tensor:
+        if temperature <= 0:
+            return logits.argmax(-1)
+        lg = logits / temperature
+        if topk and topk < lg.shape[-1]:
+            kth = lg.topk(topk, dim=-1).values[..., -1:]
+            lg = lg.masked_fill(lg < kth, float("-inf"))
+        return torch.multinomial(torch.softmax(lg, -1).view(-1, lg.shape[-1]), 1).view(lg.shape[:-1])
+
+    @torch.no_grad()
+    def infer_batch(self, text, text_len, max_decoder_steps: int = 500, temperature: float = 0.7, topk: int = 80,
+                    use_cfg: bool = False, cfg_scale: float = 2.5, min_generated_frames: int = 4):
+        """Autoregressive decoding with KV caches.  Returns (audio [B, n], audio_len, codes [B, C, T], codes_len)."""
+        self.eval()
+        B, dev = text.shape[0], text.device
+        cond, cond_mask = self.encode_text(text, text_len)
+        if use_cfg:
+            cond = torch.cat([cond, torch.zeros_like(cond)], 0)
+            cond_mask = torch.cat([cond_mask, cond_mask], 0)
+        CS = len(self.audio_embeddings)
+        cur = torch.full((B, CS, 1), self.audio_bos_id, dtype=torch.long, device=dev)
+        cache = self.decoder.new_cache()
+        done = torch.zeros(B, dtype=torch.bool, device=dev)
+        end_step = torch.full((B,), max_decoder_steps, dtype=torch.long, device=dev)
+        frames = []
+        for step in range(max_decoder_steps):
+            x = self.embed_audio_tokens(cur)
+            if use_cfg:
+                x = torch.cat([x, x], 0)
+            xmask = torch.ones(x.shape[:2], dtype=torch.bool, device=dev)
+            h = self.decoder(x, xmask, cond=cond, cond_mask=cond_mask, cache=cache, position_offset=step)["output"][:, -1]
+            logits = ops.linear(h, self.final_proj.weight, self.final_proj.bias).float().view(h.shape[0], CS, -1)
+            if use_cfg:
+                logits = logits[B:] + cfg_scale * (logits[:B] - logits[B:])
+            if self.local_transformer_type == "autoregressive":
+                nxt = self._local_ar(h[:B].float(), temperature, topk, uncond=h[B:].float() if use_cfg else None, cfg_scale=cfg_scale)
+            else:
+                logits[..., self.audio_bos_id] = float("-inf")
+                logits[..., self.audio_eos_id + 1:] = float("-inf")
+                if step < min_generated_frames:
+                    logits[..., self.audio_eos_id] = float("-inf")
+                nxt = self._sample(logits, temperature, topk)
+            is_eos = (nxt == self.audio_eos_id).any(dim=1)
+            newly = is_eos & ~done
+            end_step = torch.where(newly, torch.full_like(end_step, step), end_step)
+            done = done | is_eos
+            frames.append(nxt)
+            cur = nxt.unsqueeze(-1)
+            if bool(done.all()):
+                break
+        codes = torch.stack(frames, dim=-1)                               # [B, C·S, T]
+        lens = end_step.clamp(max=codes.shape[-1])
+        codes, lens = self.unstack_codes(codes, lens)
+        lens = lens.clamp(min=1)
+        audio, audio_len = self.codes_to_audio(codes, lens)
+        return audio, audio_len, codes, lens
+
+    def _local_ar(self, h, temperature, topk, uncond=None, cfg_scale=1.0):
+        CS = len(self.audio_embeddings)
+        seq = self.local_transformer_in_projection(h).unsqueeze(1)
+        useq = self.local_transformer_in_projection(uncond).unsqueeze(1) if uncond is not None else None
+        out = []
+        for c in range(CS):
+            m = torch.ones(seq.shape[:2], dtype=torch.bool, device=seq.device)
+            lg = self.local_transformer_out_projections[c](self.local_transformer(seq, m)["output"][:, -1]).float()
+            if useq is not None:
+                ul = self.local_transformer_out_projections[c](self.local_transformer(useq, m)["output"][:, -1]).float()
+                lg = ul + cfg_scale * (lg - ul)
+            lg[..., self.audio_bos_id] = float("-inf")
+            lg[..., self.audio_eos_id + 1:] = float("-inf")
+            tok = self._sample(lg, temperature, topk)
+            out.append(tok)
+            e = self.local_transformer_audio_embeddings[c](tok).unsqueeze(1)
+            seq = torch.cat([seq, e], 1)
+            if useq is not None:
+                useq = torch.cat([useq, e], 1)
+        return torch.stack(out, dim=1)
+
+    def tokenize(self, transcript: str) -> torch.Tensor:
+        ids = [self.text_bos_id] + list(self.tokenizer.text_to_ids(transcript)) + [self.text_eos_id]
+        return torch.tensor(ids, dtype=torch.long)
+
+    @torch.no_grad()
+    def do_tts(self, transcript: str, **kw) -> Tuple[torch.Tensor, torch.Tensor]:
+        ids = self.tokenize(transcript).unsqueeze(0).to(self.device)
+        audio, alen, _, _ = self.infer_batch(ids, torch.tensor([ids.shape[1]], device=self.device), **kw)
+        return audio, alen
+
+    @torch.no_grad()
+    def generate_speech(self, transcript: str, max_chars_per_chunk: int = 200, **kw) -> torch.Tensor:
+        """Long-form synthesis: split at sentence boundaries, synthesise chunk by chunk, concatenate."""
+        import re
+
+        sents = [s.strip() for s in re.split(r"(?<=[.!?])\s+", transcript) if s.strip()]
+        chunks, cur = [], ""
+        for s in sents:
+            if cur and len(cur) + len(s) + 1 > max_chars_per_chunk:
+                chunks.append(cur)
+                cur = s
+            else:
+                cur = (cur + " " + s).strip()
+        if cur:
+            chunks.append(cur)
+        outs = []
+        for c in chunks:
+            a, n = self.do_tts(c, **kw)
+            outs.append(a[0, : int(n[0])])
+        return torch.cat(outs) if outs else torch.zeros(0)
