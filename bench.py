@@ -160,6 +160,11 @@ class _Timed:
         self.audio = 0.0
         self.losses = []
         self.d2h_bytes = 0
+        # loss read-back is pipelined by one step: step i's loss is copied to pinned memory asynchronously and read on the
+        # host at the end of step i+1 (the last one at the end of the timed region), so the host never drains the GPU
+        # queue in the middle of the run
+        self._pending = None
+        self._host = torch.zeros(2, dtype=torch.float32).pin_memory()
 
     # the Trainer calls every hook by name; unknown hooks are simply absent
     def setup(self, trainer, model, stage): ...
@@ -179,11 +184,23 @@ class _Timed:
         import torch.distributed as dist
 
         loss = outputs["loss"].detach().float()
-        self.losses.append(float(loss.item()))  # device -> host read of the step's result
+        if self._pending is not None:
+            slot, ev = self._pending
+            ev.synchronize()
+            self.losses.append(float(self._host[slot]))  # device -> host read of the previous step's result
+        slot = batch_idx % 2
+        self._host[slot].copy_(loss, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._pending = (slot, ev)
         self.d2h_bytes = 4
         if self.warmup <= batch_idx < self.warmup + self.steps:
             self.audio += self.durations[batch_idx % len(self.durations)]
         if batch_idx == self.warmup + self.steps - 1:
+            slot, ev = self._pending
+            ev.synchronize()
+            self.losses.append(float(self._host[slot]))
+            self._pending = None
             self.t1.record()
             torch.cuda.synchronize()
             if dist.is_initialized():

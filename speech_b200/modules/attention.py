@@ -143,14 +143,14 @@ class MultiHeadAttention(nn.Module):
             cache = torch.cat([cache[:, q_keep_size:, :], query[:, :q_keep_size, :].to(cache.dtype)], dim=1)
         return key, value, query, cache
 
-    def forward(self, query, key, value, mask=None, pos_emb=None, cache=None, residual=None):
+    def forward(self, query, key, value, mask=None, pos_emb=None, cache=None, residual=None, out_dropout: float = 0.0):
         same = query is key and key is value
         key, value, query, cache = self.update_cache(key, value, query, cache)
         if same and cache is None:
             key = value = query
         q, k, v = self._qkv(query, key, value)
         ctx = ops.mha_attention(q, k, v, mask, self.dropout_rate, self.training)
-        out = ops.linear(ctx, self.linear_out.weight, self.linear_out.bias, residual=residual)
+        out = ops.linear(ctx, self.linear_out.weight, self.linear_out.bias, residual=residual, dropout_p=out_dropout)
         return out if cache is None else (out, cache)
 
 
@@ -192,7 +192,7 @@ class RelPositionMultiHeadAttention(MultiHeadAttention):
         else:
             self.pos_bias_u, self.pos_bias_v = pos_bias_u, pos_bias_v
 
-    def forward(self, query, key, value, mask=None, pos_emb=None, cache=None, residual=None):
+    def forward(self, query, key, value, mask=None, pos_emb=None, cache=None, residual=None, out_dropout: float = 0.0):
         same = query is key and key is value
         key, value, query, cache = self.update_cache(key, value, query, cache)
         if same and cache is None:
@@ -203,7 +203,7 @@ class RelPositionMultiHeadAttention(MultiHeadAttention):
         ctx = ops.relpos_attention(q, k, v, p, self.pos_bias_u, self.pos_bias_v, mask, self.dropout_rate, self.training,
                                    qkv=self._last_qkv)
         self._last_qkv = None
-        out = ops.linear(ctx, self.linear_out.weight, self.linear_out.bias, residual=residual)
+        out = ops.linear(ctx, self.linear_out.weight, self.linear_out.bias, residual=residual, dropout_p=out_dropout)
         return out if cache is None else (out, cache)
 
 
@@ -221,7 +221,7 @@ class RelPositionMultiHeadAttentionLongformer(RelPositionMultiHeadAttention):
         self.att_context_size = tuple(att_context_size)
         self.global_tokens, self.global_tokens_spacing = global_tokens, global_tokens_spacing
 
-    def forward(self, query, key, value, pad_mask=None, pos_emb=None, cache=None, residual=None, mask=None):
+    def forward(self, query, key, value, pad_mask=None, pos_emb=None, cache=None, residual=None, mask=None, out_dropout: float = 0.0):
         B, T, _ = query.shape
         q, k, v = self._qkv(query, key, value)
         left, right = self.att_context_size
@@ -251,5 +251,5 @@ class RelPositionMultiHeadAttentionLongformer(RelPositionMultiHeadAttention):
         attn = torch.softmax(scores, dim=-1).masked_fill(hidden[:, None], 0.0)
         attn = torch.nn.functional.dropout(attn, self.dropout_rate, self.training)
         ctx = torch.matmul(attn, v.float().transpose(1, 2)).transpose(1, 2).reshape(B, T, -1).to(query.dtype)
-        out = ops.linear(ctx, self.linear_out.weight, self.linear_out.bias, residual=residual)
+        out = ops.linear(ctx, self.linear_out.weight, self.linear_out.bias, residual=residual, dropout_p=out_dropout)
         return out if cache is None else (out, cache)

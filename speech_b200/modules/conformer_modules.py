@@ -58,12 +58,9 @@ class ConformerFeedForward(nn.Module):
 
     def forward(self, x, residual=None, alpha: float = 1.0):
         """``residual + alpha * FF(x)``; dropout (if any) is applied between the two GEMMs and on the output."""
-        h = ops.linear(x, self.linear1.weight, self.linear1.bias, act="swish")
-        h = self.dropout(h)
-        if self.training and self.dropout.p > 0:
-            y = self.dropout(ops.linear(h, self.linear2.weight, self.linear2.bias))
-            return residual + alpha * y if residual is not None else alpha * y
-        return ops.linear(h, self.linear2.weight, self.linear2.bias, residual=residual, alpha=alpha)
+        p = self.dropout.p if self.training else 0.0
+        h = ops.linear(x, self.linear1.weight, self.linear1.bias, act="swish", dropout_p=p)
+        return ops.linear(h, self.linear2.weight, self.linear2.bias, residual=residual, alpha=alpha, dropout_p=p)
 
     def reset_parameters_ff(self):
         ffn1_max, ffn2_max = self.d_model ** -0.5, self.d_ff ** -0.5
@@ -105,7 +102,7 @@ class ConformerConvolution(nn.Module):
         self.pointwise_conv2 = nn.Conv1d(dw_in, d_model, kernel_size=1, bias=use_bias)
         self.bn_stats_reduce = None  # set by the data-parallel strategy for synchronised BatchNorm
 
-    def forward(self, x, pad_mask=None, cache=None, residual=None):
+    def forward(self, x, pad_mask=None, cache=None, residual=None, out_dropout: float = 0.0):
         g = ops.linear(x, self.pointwise_conv1.weight.squeeze(-1), self.pointwise_conv1.bias)
         fusable = self.pointwise_activation == "glu_" and self.norm_type in ("batch_norm", "layer_norm")
         if fusable:
@@ -134,7 +131,8 @@ class ConformerConvolution(nn.Module):
                 xt, cache = xt
             xt = self.batch_norm(xt)
             s = self.activation(xt).transpose(1, 2)
-        y = ops.linear(s, self.pointwise_conv2.weight.squeeze(-1), self.pointwise_conv2.bias, residual=residual)
+        y = ops.linear(s, self.pointwise_conv2.weight.squeeze(-1), self.pointwise_conv2.bias, residual=residual,
+                       dropout_p=out_dropout)
         return y if cache is None else (y, cache)
 
     def reset_parameters_conv(self):
@@ -204,27 +202,28 @@ class ConformerLayer(nn.Module, AdapterModuleMixin, AccessMixin):
         return ops.layer_norm(x, ln.weight, ln.bias, ln.eps)
 
     def forward(self, x, att_mask=None, pos_emb=None, pad_mask=None, cache_last_channel=None, cache_last_time=None):
-        drop = self.training and self.dropout.p > 0
+        # dropout on the module outputs is fused into the epilogue of each module's last GEMM: residual + dropout(out)
+        p_out = self.dropout.p if self.training else 0.0
         residual = self.feed_forward1(self._ln(self.norm_feed_forward1, x), residual=x, alpha=self.fc_factor)
         h = self._ln(self.norm_self_att, residual)
-        kw = dict(query=h, key=h, value=h, pos_emb=pos_emb, cache=cache_last_channel)
+        kw = dict(query=h, key=h, value=h, pos_emb=pos_emb, cache=cache_last_channel, out_dropout=p_out)
         if self.self_attention_model == "rel_pos_local_attn":
             kw["pad_mask"] = pad_mask
         else:
             kw["mask"] = att_mask
         if self.self_attention_model == "abs_pos":
             kw.pop("pos_emb")
-        a = self.self_attn(residual=None if drop else residual, **kw)
+        a = self.self_attn(residual=residual, **kw)
         if cache_last_channel is not None:
             a, cache_last_channel = a
-        residual = residual + self.dropout(a) if drop else a
+        residual = a
         if self.is_adapter_available():
             residual = self.forward_enabled_adapters(residual)
         h = self._ln(self.norm_conv, residual)
-        c = self.conv(h, pad_mask=pad_mask, cache=cache_last_time, residual=None if drop else residual)
+        c = self.conv(h, pad_mask=pad_mask, cache=cache_last_time, residual=residual, out_dropout=p_out)
         if cache_last_time is not None:
             c, cache_last_time = c
-        residual = residual + self.dropout(c) if drop else c
+        residual = c
         residual = self.feed_forward2(self._ln(self.norm_feed_forward2, residual), residual=residual, alpha=self.fc_factor)
         out = self._ln(self.norm_out, residual)
         if self.is_access_enabled(getattr(self, "model_guid", None)) and self.access_cfg.get("save_encoder_tensors", False):

@@ -111,10 +111,11 @@ def lowp(param: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tens
 
 
 # ----------------------------------------------------------------------------- dense layers
-def linear(x, weight, bias=None, act: Optional[str] = None, residual=None, alpha: float = 1.0):
+def linear(x, weight, bias=None, act: Optional[str] = None, residual=None, alpha: float = 1.0, dropout_p: float = 0.0):
+    """``residual + alpha * dropout(act(x W^T + b))``; ``dropout_p`` > 0 means "apply dropout now" (callers pass 0 in eval)."""
     if _use_native(x) and x.dtype == torch.bfloat16:
-        return _nat().linear(x, weight, bias, act, residual, alpha)
-    return reference.linear(x, weight, bias, act, residual, alpha)
+        return _nat().linear(x, weight, bias, act, residual, alpha, dropout_p)
+    return reference.linear(x, weight, bias, act, residual, alpha, dropout_p)
 
 
 def layer_norm(x, weight, bias, eps: float = 1e-5):

@@ -35,6 +35,21 @@ __device__ __forceinline__ void sb_set_status(int* status, int code, int detail)
 }
 __device__ __forceinline__ bool sb_failed(const int* status) { return *((volatile const int*)status) != 0; }
 
+// Stateless dropout mask: element `idx` of the tensor drawn with `seed` is kept iff the hash is >= thresh
+// (thresh = p * 2^32).  Forward kernels and the backward kernels that rebuild the mask call this with the same
+// (seed, row * N + col), so no mask tensor is ever stored.
+__device__ __forceinline__ bool sb_dropout_keep(unsigned long long seed, unsigned long long idx, unsigned int thresh) {
+  unsigned int h = (unsigned int)idx * 0x9E3779B1u ^ (unsigned int)(idx >> 32) * 0x85EBCA77u ^ (unsigned int)seed;
+  h ^= h >> 16; h *= 0x7FEB352Du; h ^= h >> 15; h *= 0x846CA68Bu; h ^= h >> 16;
+  h ^= (unsigned int)(seed >> 32); h *= 0x9E3779B1u; h ^= h >> 15; h *= 0x2C1B3C6Du; h ^= h >> 12;
+  return h >= thresh;
+}
+static inline unsigned int sb_dropout_threshold(float p) {
+  if (p <= 0.f) return 0u;
+  double t = (double)p * 4294967296.0;
+  return t >= 4294967295.0 ? 4294967295u : (unsigned int)t;
+}
+
 __device__ __forceinline__ float sb_sigmoid(float x) { return 1.f / (1.f + __expf(-x)); }
 __device__ __forceinline__ float sb_swish(float x) { return x * sb_sigmoid(x); }
 __device__ __forceinline__ float sb_dswish(float z) {

@@ -119,6 +119,91 @@ __global__ void layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const
   }
 }
 
+// Register-resident variant for D = NCH * 256 (NCH <= 4): a lane owns the same 8*NCH columns in every row its warp
+// visits, so x / dy are read once and the dgamma / dbeta partial sums live in registers until the end of the block.
+template <int NCH>
+__global__ void __launch_bounds__(256) layernorm_bwd_reg_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
+    const float* __restrict__ mean, const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma,
+    float* __restrict__ dbeta, int rows, int rows_per_block) {
+  constexpr int D = NCH * 256;
+  __shared__ float sg[D];
+  __shared__ float sb[D];
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    sg[i] = 0.f;
+    sb[i] = 0.f;
+  }
+  __syncthreads();
+  const int warps = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float gam[NCH][8], ag[NCH][8], ab[NCH][8];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j)
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      gam[j][u] = gamma[j * 256 + lane * 8 + u];
+      ag[j][u] = 0.f;
+      ab[j][u] = 0.f;
+    }
+  const int row0 = blockIdx.x * rows_per_block;
+  const int row1 = min(rows, row0 + rows_per_block);
+  for (int row = row0 + w; row < row1; row += warps) {
+    const __nv_bfloat16* xr = x + (long long)row * D;
+    const __nv_bfloat16* gr = dy + (long long)row * D;
+    const float mu = mean[row], rs = rstd[row];
+    float xh[NCH][8], g[NCH][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const uint4 rx = *reinterpret_cast<const uint4*>(xr + j * 256 + lane * 8);
+      const uint4 rg = *reinterpret_cast<const uint4*>(gr + j * 256 + lane * 8);
+      const __nv_bfloat162* hx = reinterpret_cast<const __nv_bfloat162*>(&rx);
+      const __nv_bfloat162* hg = reinterpret_cast<const __nv_bfloat162*>(&rg);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 fx = __bfloat1622float2(hx[u]), fg = __bfloat1622float2(hg[u]);
+        xh[j][2 * u] = (fx.x - mu) * rs;
+        xh[j][2 * u + 1] = (fx.y - mu) * rs;
+        g[j][2 * u] = fg.x;
+        g[j][2 * u + 1] = fg.y;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float gg = g[j][u] * gam[j][u];
+        s1 += gg;
+        s2 += gg * xh[j][u];
+        ag[j][u] += g[j][u] * xh[j][u];
+        ab[j][u] += g[j][u];
+      }
+    }
+    s1 = warp_sum(s1) * (1.f / D);
+    s2 = warp_sum(s2) * (1.f / D);
+    __nv_bfloat16* dr = dx + (long long)row * D;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float a = rs * (g[j][2 * u] * gam[j][2 * u] - s1 - xh[j][2 * u] * s2);
+        const float b = rs * (g[j][2 * u + 1] * gam[j][2 * u + 1] - s1 - xh[j][2 * u + 1] * s2);
+        o[u] = __floats2bfloat162_rn(a, b);
+      }
+      *reinterpret_cast<uint4*>(dr + j * 256 + lane * 8) = *reinterpret_cast<const uint4*>(o);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NCH; ++j)
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      atomicAdd(&sg[j * 256 + lane * 8 + u], ag[j][u]);
+      atomicAdd(&sb[j * 256 + lane * 8 + u], ab[j][u]);
+    }
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    atomicAdd(&dgamma[i], sg[i]);
+    if (dbeta) atomicAdd(&dbeta[i], sb[i]);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ AdamW
 // scalars[1] = gradient multiplier (clip coefficient x loss scale), read from device memory.
 __global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
@@ -246,6 +331,17 @@ SB_API int sb_layernorm_bwd(const void* dy, const void* x, const float* gamma, c
   const int blocks = min(rows, 2 * sb_num_sms());
   const int rpb = (rows + blocks - 1) / blocks;
   const int nblocks = (rows + rpb - 1) / rpb;
+  if (D % 256 == 0 && D <= 1024) {
+    const __nv_bfloat16 *gdy = (const __nv_bfloat16*)dy, *gx = (const __nv_bfloat16*)x;
+    __nv_bfloat16* gdx = (__nv_bfloat16*)dx;
+    switch (D / 256) {
+      case 1: layernorm_bwd_reg_kernel<1><<<nblocks, 256, 0, stream>>>(gdy, gx, gamma, mean, rstd, gdx, dgamma, dbeta, rows, rpb); break;
+      case 2: layernorm_bwd_reg_kernel<2><<<nblocks, 256, 0, stream>>>(gdy, gx, gamma, mean, rstd, gdx, dgamma, dbeta, rows, rpb); break;
+      case 3: layernorm_bwd_reg_kernel<3><<<nblocks, 256, 0, stream>>>(gdy, gx, gamma, mean, rstd, gdx, dgamma, dbeta, rows, rpb); break;
+      default: layernorm_bwd_reg_kernel<4><<<nblocks, 256, 0, stream>>>(gdy, gx, gamma, mean, rstd, gdx, dgamma, dbeta, rows, rpb); break;
+    }
+    return (int)cudaGetLastError();
+  }
   layernorm_bwd_kernel<<<nblocks, 256, 2 * D * sizeof(float), stream>>>(
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, mean, rstd, (__nv_bfloat16*)dx, dgamma, dbeta, rows, D, rpb);
   return (int)cudaGetLastError();
@@ -301,14 +397,16 @@ SB_API int sb_cast_f32_bf16(const float* in, void* out, long long n, float scale
 }
 
 namespace {
-// dz = alpha * dy * act'(z) for bf16 [rows, N] (dy may have a row stride; z and dz are dense).
+// dz = alpha * mask * dy * act'(z) for bf16 [rows, N] (dy may have a row stride; z (optional) and dz are dense).  The
+// dropout mask (thresh != 0) is rebuilt from (seed, r * N + c), matching the GEMM epilogue that applied it.
 __global__ void scale_dact_kernel(const __nv_bfloat16* __restrict__ dy, long long ld_dy, const __nv_bfloat16* __restrict__ z,
-                                  __nv_bfloat16* __restrict__ dz, int rows, int N, int act, float alpha) {
+                                  __nv_bfloat16* __restrict__ dz, int rows, int N, int act, float alpha, unsigned int thresh,
+                                  float drop_scale, unsigned long long seed) {
   const long long total8 = (long long)rows * (N / 8);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (long long)gridDim.x * blockDim.x) {
     const int r = (int)(i / (N / 8)), c = (int)(i % (N / 8)) * 8;
     uint4 rg = *reinterpret_cast<const uint4*>(dy + (long long)r * ld_dy + c);
-    uint4 rz = *reinterpret_cast<const uint4*>(z + (long long)r * N + c);
+    uint4 rz = z ? *reinterpret_cast<const uint4*>(z + (long long)r * N + c) : make_uint4(0, 0, 0, 0);
     const __nv_bfloat162* hg = reinterpret_cast<const __nv_bfloat162*>(&rg);
     const __nv_bfloat162* hz = reinterpret_cast<const __nv_bfloat162*>(&rz);
     __align__(16) __nv_bfloat162 o[4];
@@ -320,6 +418,11 @@ __global__ void scale_dact_kernel(const __nv_bfloat16* __restrict__ dy, long lon
       else if (act == 2) { d0 = sb_dswish(zz.x); d1 = sb_dswish(zz.y); }
       else if (act == 3) { d0 = sb_dgelu(zz.x); d1 = sb_dgelu(zz.y); }
       else { d0 = d1 = 1.f; }
+      if (thresh) {
+        const unsigned long long idx = (unsigned long long)r * N + c + 2 * u;
+        d0 = sb_dropout_keep(seed, idx, thresh) ? d0 * drop_scale : 0.f;
+        d1 = sb_dropout_keep(seed, idx + 1, thresh) ? d1 * drop_scale : 0.f;
+      }
       o[u] = __floats2bfloat162_rn(alpha * g.x * d0, alpha * g.y * d1);
     }
     *reinterpret_cast<uint4*>(dz + (long long)r * N + c) = *reinterpret_cast<uint4*>(o);
@@ -327,14 +430,24 @@ __global__ void scale_dact_kernel(const __nv_bfloat16* __restrict__ dy, long lon
 }
 }  // namespace
 
+SB_API int sb_scale_dact_dropout(const void* dy, long long ld_dy, const void* z, void* dz, int rows, int N, int act, float alpha,
+                                 float drop_p, unsigned long long seed, cudaStream_t stream);
+
 SB_API int sb_scale_dact(const void* dy, long long ld_dy, const void* z, void* dz, int rows, int N, int act, float alpha,
                          cudaStream_t stream) {
+  return sb_scale_dact_dropout(dy, ld_dy, z, dz, rows, N, act, alpha, 0.f, 0ull, stream);
+}
+
+SB_API int sb_scale_dact_dropout(const void* dy, long long ld_dy, const void* z, void* dz, int rows, int N, int act, float alpha,
+                                 float drop_p, unsigned long long seed, cudaStream_t stream) {
   if (N % 8 != 0 || rows <= 0) return -1;
+  if (z == nullptr) act = 0;
   long long total8 = (long long)rows * (N / 8);
   long long blocks = (total8 + 255) / 256;
   const long long cap = (long long)sb_num_sms() * 16;
   if (blocks > cap) blocks = cap;
   scale_dact_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)dy, ld_dy, (const __nv_bfloat16*)z,
-                                                    (__nv_bfloat16*)dz, rows, N, act, alpha);
+                                                    (__nv_bfloat16*)dz, rows, N, act, alpha, sb_dropout_threshold(drop_p),
+                                                    drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f, seed);
   return (int)cudaGetLastError();
 }

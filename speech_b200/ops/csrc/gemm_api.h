@@ -27,6 +27,8 @@ struct SbGemmArgs {
   int max_ctas;  // 0 = one per SM
   int fold_batch1;  // 1: sum over batch1 inside the K loop; D then has no batch1 dimension
   int tile_n;       // 128 or 256 to force the tile width, anything else = automatic
+  float drop_p;     // > 0: dropout applied to act(acc + bias) before alpha / residual; mask = sb_dropout_keep(seed, m * N + n)
+  unsigned long long drop_seed;
 };
 
 

@@ -49,6 +49,9 @@ struct EpilogueArgs {
   int act;       // 0 none, 1 relu, 2 swish, 3 gelu
   int dact;      // 0 none, 1 relu', 2 swish', 3 gelu'  (multiplies by act'(aux))
   int d_is_f32;  // output dtype
+  unsigned int drop_thresh;  // 0 = no dropout; otherwise keep iff sb_dropout_keep(seed, batch*M*N + m*N + n, thresh)
+  float drop_scale;          // 1 / (1 - p)
+  unsigned long long drop_seed;
 };
 
 struct GemmParams {
@@ -334,6 +337,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], e.act);
           }
+          if (e.drop_thresh) {
+            const unsigned long long base = ((unsigned long long)batch * p.M + row) * (unsigned long long)p.N + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = sb_dropout_keep(e.drop_seed, base + j, e.drop_thresh) ? v[j] * e.drop_scale : 0.f;
+          }
           if (e.alpha != 1.f) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] *= e.alpha;
@@ -502,6 +510,9 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   e.aux = (const __nv_bfloat16*)a->aux; e.ldx = a->ldx; e.x_bs0 = a->x_bs0; e.x_bs1 = a->x_bs1;
   e.D_pre = (__nv_bfloat16*)a->D_pre; e.ldp = a->ldp; e.p_bs0 = a->p_bs0; e.p_bs1 = a->p_bs1;
   e.alpha = a->alpha; e.beta = a->beta; e.act = a->act; e.dact = (a->aux ? a->dact : 0);
+  e.drop_thresh = sb_dropout_threshold(a->drop_p);
+  e.drop_scale = a->drop_p > 0.f ? 1.f / (1.f - a->drop_p) : 1.f;
+  e.drop_seed = a->drop_seed;
   int grid = sb_num_sms();
   if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
   if ((long long)grid > p.num_tiles) grid = (int)p.num_tiles;

@@ -37,6 +37,7 @@ class SbGemmArgs(ctypes.Structure):
         ("D_pre", ctypes.c_void_p), ("ldp", ctypes.c_longlong), ("p_bs0", ctypes.c_longlong), ("p_bs1", ctypes.c_longlong),
         ("alpha", ctypes.c_float), ("beta", ctypes.c_float), ("act", ctypes.c_int), ("dact", ctypes.c_int),
         ("max_ctas", ctypes.c_int), ("fold_batch1", ctypes.c_int), ("tile_n", ctypes.c_int),
+        ("drop_p", ctypes.c_float), ("drop_seed", ctypes.c_ulonglong),
     ]
 
 
@@ -59,7 +60,14 @@ def lib():
     return _LIB if _LIB is not None else load()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_cur_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream(t: Optional[torch.Tensor] = None) -> ctypes.c_void_p:
+    """Handle of the current CUDA stream of the current device (one C call; this runs once per kernel launch)."""
+    if _raw_stream is not None and _cur_device is not None:
+        return ctypes.c_void_p(_raw_stream(_cur_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -96,7 +104,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
          ldr: Optional[int] = None, r_bs: Tuple[int, int] = (0, 0), aux: Optional[torch.Tensor] = None, dact: Optional[str] = None,
          ldx: Optional[int] = None, x_bs: Tuple[int, int] = (0, 0), out_pre: Optional[torch.Tensor] = None,
          ldp: Optional[int] = None, p_bs: Tuple[int, int] = (0, 0), alpha: float = 1.0, beta: float = 0.0,
-         max_ctas: int = 0, fold_batch1: bool = False, tile_n: int = 0) -> torch.Tensor:
+         max_ctas: int = 0, fold_batch1: bool = False, tile_n: int = 0, drop_p: float = 0.0, drop_seed: int = 0) -> torch.Tensor:
     """``out = epilogue(alpha * A @ B^T)`` on raw strided bf16 operands (see csrc/gemm_tcgen05.cu).
 
     ``a_mn`` / ``b_mn``: the operand is stored transposed (A as [K, M], B as [K, N]).  ``lda`` / ``ldb`` are the row
@@ -141,6 +149,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
     g.max_ctas = max_ctas
     g.fold_batch1 = int(fold_batch1)
     g.tile_n = int(tile_n)
+    if drop_p > 0.0:
+        g.drop_p, g.drop_seed = float(drop_p), int(drop_seed)
     _check(lib().sb_gemm_bf16(ctypes.byref(g), _stream()), "sb_gemm_bf16")
     return out
 
@@ -182,10 +192,11 @@ def _write_param_grad(param: torch.Tensor, compute, shape) -> Optional[torch.Ten
 
 # ------------------------------------------------------------------------------------------------ linear
 class _LinearFn(torch.autograd.Function):
-    """y = residual + alpha * act(x W^T + b); saves x and (when needed) the pre-activation for backward."""
+    """y = residual + alpha * dropout(act(x W^T + b)); saves x and (when needed) the pre-activation for backward.  The
+    dropout mask is a hash of (seed, element index): the backward pass rebuilds it instead of storing it."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, residual, act, alpha):
+    def forward(ctx, x, weight, bias, residual, act, alpha, drop_p=0.0):
         x2 = _as_2d(x)
         M, K = x2.shape
         wl = _lowp_weight(weight)
@@ -194,8 +205,10 @@ class _LinearFn(torch.autograd.Function):
         need_pre = act is not None and ctx.needs_input_grad[0] | ctx.needs_input_grad[1]
         pre = torch.empty_like(y) if need_pre else None
         r2 = _as_2d(residual) if residual is not None else None
+        seed = _next_dropout_seed() if drop_p > 0.0 else 0
         gemm(x2, wl, y, M=M, N=N, K=K, lda=x2.stride(0), bias=bias, act=act, residual=r2,
-             ldr=(r2.stride(0) if r2 is not None else None), out_pre=pre, alpha=alpha)
+             ldr=(r2.stride(0) if r2 is not None else None), out_pre=pre, alpha=alpha, drop_p=drop_p, drop_seed=seed)
+        ctx.drop_p, ctx.drop_seed = drop_p, seed
         ctx.save_for_backward(x2, pre)
         ctx.weight, ctx.bias = weight, bias
         ctx.act, ctx.alpha = act, alpha
@@ -212,9 +225,9 @@ class _LinearFn(torch.autograd.Function):
         N = dy2.shape[1]
         wl = _lowp_weight(weight)
         # gradient w.r.t. the pre-activation z: dz = alpha * dy * act'(z)
-        if ctx.act is not None:
+        if ctx.act is not None or ctx.drop_p > 0.0:
             dz = torch.empty((M, N), dtype=torch.bfloat16, device=dy.device)
-            lib_call_scale_dact(dy2, pre, dz, ctx.act, ctx.alpha)
+            lib_call_scale_dact(dy2, pre if ctx.act is not None else None, dz, ctx.act, ctx.alpha, ctx.drop_p, ctx.drop_seed)
         elif ctx.alpha != 1.0:
             dz = dy2 * ctx.alpha
         else:
@@ -232,13 +245,23 @@ class _LinearFn(torch.autograd.Function):
         if bias is not None and ctx.needs_input_grad[2]:
             db = _write_param_grad(bias, lambda out, beta: colsum(dz, out, accumulate=beta != 0.0), (N,))
         dres = dy if ctx.has_res and ctx.needs_input_grad[3] else None
-        return dx, dw, db, dres, None, None
+        return dx, dw, db, dres, None, None, None
 
 
-def lib_call_scale_dact(dy2, pre, dz, act, alpha):
-    _check(lib().sb_scale_dact(_ptr(dy2), ctypes.c_longlong(dy2.stride(0)), _ptr(pre), _ptr(dz), ctypes.c_int(dy2.shape[0]),
-                               ctypes.c_int(dy2.shape[1]), ctypes.c_int(ACT[act]), ctypes.c_float(alpha), _stream()),
-           "sb_scale_dact")
+_dropout_counter = [0x5EED5EED]
+
+
+def _next_dropout_seed() -> int:
+    """A fresh 64-bit seed per dropout site and step (host counter mixed with torch's seed, so runs are reproducible)."""
+    _dropout_counter[0] = (_dropout_counter[0] * 6364136223846793005 + 1442695040888963407) & 0xFFFFFFFFFFFFFFFF
+    return (_dropout_counter[0] ^ (torch.initial_seed() & 0xFFFFFFFFFFFFFFFF)) & 0xFFFFFFFFFFFFFFFF
+
+
+def lib_call_scale_dact(dy2, pre, dz, act, alpha, drop_p: float = 0.0, drop_seed: int = 0):
+    _check(lib().sb_scale_dact_dropout(_ptr(dy2), ctypes.c_longlong(dy2.stride(0)), _ptr(pre), _ptr(dz), ctypes.c_int(dy2.shape[0]),
+                                       ctypes.c_int(dy2.shape[1]), ctypes.c_int(ACT[act]), ctypes.c_float(alpha),
+                                       ctypes.c_float(drop_p), ctypes.c_ulonglong(drop_seed), _stream()),
+           "sb_scale_dact_dropout")
 
 
 def colsum(x2: torch.Tensor, out: torch.Tensor, accumulate: bool = False):
@@ -249,13 +272,13 @@ def colsum(x2: torch.Tensor, out: torch.Tensor, accumulate: bool = False):
     return out
 
 
-def linear(x, weight, bias=None, act=None, residual=None, alpha: float = 1.0):
+def linear(x, weight, bias=None, act=None, residual=None, alpha: float = 1.0, dropout_p: float = 0.0):
     K = x.shape[-1]
-    if K % 8 != 0 or x.numel() == 0:
+    if K % 8 != 0 or x.numel() == 0 or (dropout_p > 0.0 and weight.shape[0] % 8 != 0):
         from . import reference
 
-        return reference.linear(x, weight, bias, act, residual, alpha)
-    return _LinearFn.apply(x, weight, bias, residual, act, alpha)
+        return reference.linear(x, weight, bias, act, residual, alpha, dropout_p)
+    return _LinearFn.apply(x, weight, bias, residual, act, alpha, float(dropout_p))
 
 
 # ------------------------------------------------------------------------------------------------ layer norm

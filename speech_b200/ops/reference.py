@@ -22,10 +22,12 @@ def act_fn(name: Optional[str]):
             "sigmoid": torch.sigmoid}[name]
 
 
-def linear(x, weight, bias=None, act=None, residual=None, alpha: float = 1.0):
-    """``residual + alpha * act(x @ W^T + b)``."""
+def linear(x, weight, bias=None, act=None, residual=None, alpha: float = 1.0, dropout_p: float = 0.0):
+    """``residual + alpha * dropout(act(x @ W^T + b))``."""
     y = F.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
     y = act_fn(act)(y)
+    if dropout_p > 0.0:
+        y = F.dropout(y, dropout_p, training=True)
     if alpha != 1.0:
         y = y * alpha
     if residual is not None:

@@ -135,3 +135,43 @@ def test_fused_adamw_matches_torch():
     for p, r in zip(ps, ref):
         assert (p - r).abs().max() < 1e-5
         assert (p._lowp.float() - r).abs().max() < 2e-2
+
+
+def test_linear_fused_dropout_mask_is_consistent_between_forward_and_backward():
+    """Dropout lives in the GEMM epilogue as a hash of (seed, index); backward must rebuild exactly the same mask.
+    The bias keeps every pre-activation far from zero, so the mask can be read off the output exactly."""
+    from speech_b200 import ops
+
+    torch.manual_seed(0)
+    dev = torch.device("cuda")
+    M, K, N, p = 300, 256, 512, 0.3
+    x = torch.randn(M, K, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.nn.Parameter(torch.randn(N, K, device=dev) * 0.02)
+    b = torch.nn.Parameter(torch.full((N,), 6.0, device=dev))
+    y = ops.linear(x, w, b, act="swish", alpha=0.5, dropout_p=p)
+    z = torch.nn.functional.linear(x.float(), w.float().to(torch.bfloat16).float(), b.float())
+    assert z.min().item() > 3.0
+    keep = (y != 0).float()
+    assert abs(keep.mean().item() - (1 - p)) < 0.02
+    want = keep * 0.5 * torch.nn.functional.silu(z) / (1 - p)
+    assert ((y.float() - want).abs() / want.abs().clamp(min=1.0)).max().item() < 0.02
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    s = torch.sigmoid(z)
+    dz = 0.5 * keep / (1 - p) * dy.float() * (s + z * s * (1 - s))
+    dx_ref, dw_ref, db_ref = dz @ w.float(), dz.t() @ x.float(), dz.sum(0)
+    for got, ref in ((x.grad, dx_ref), (w.grad, dw_ref), (b.grad, db_ref)):
+        assert (got.float() - ref).abs().max().item() / ref.abs().max().item() < 0.03
+    # a second call draws a different mask; without dropout the op is deterministic
+    y2 = ops.linear(x.detach(), w, b, act="swish", alpha=0.5, dropout_p=p)
+    assert ((y2 != 0) != (y != 0)).float().mean().item() > 0.2
+    assert torch.equal(ops.linear(x.detach(), w, b, act="swish"), ops.linear(x.detach(), w, b, act="swish"))
+    # output-side dropout with a residual (the pattern at the end of every conformer sub-module)
+    res = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+    x2 = x.detach().clone().requires_grad_(True)
+    y4 = ops.linear(x2, w, b, residual=res, dropout_p=p)
+    keep4 = ((y4.float() - res.float()).abs() > 0.5).float()           # |z| / (1-p) > 4 wherever it was kept
+    assert abs(keep4.mean().item() - (1 - p)) < 0.02
+    y4.backward(dy)
+    ref4 = (keep4 / (1 - p) * dy.float()) @ w.float()
+    assert (x2.grad.float() - ref4).abs().max().item() / ref4.abs().max().item() < 0.03
