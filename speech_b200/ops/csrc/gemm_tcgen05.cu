@@ -34,7 +34,12 @@ constexpr int NUM_THREADS = 320;  // warp 0: TMA, warp 1: MMA, warps 2-9: epilog
 // Tile width BN is a template parameter: 128 (6 stages) or 256 (4 stages; halves shared-memory traffic per flop).
 constexpr int num_stages(int bn) { return bn == 256 ? 4 : 6; }
 constexpr int stage_bytes(int bn) { return TILE_BYTES + bn * BLOCK_K * 2; }
-constexpr int smem_bytes(int bn) { return num_stages(bn) * stage_bytes(bn) + 1024 /*align*/ + 256 /*barriers*/; }
+constexpr int EPI_WARPS = 8;
+constexpr int EPI_ROW_BYTES = 80;   // 32 bf16 (64 B) + 16 B pad: conflict-free 16-byte writes by row and reads by 4-lane groups
+constexpr int EPI_STAGE_BYTES = 32 * EPI_ROW_BYTES;
+constexpr int smem_bytes(int bn) {
+  return num_stages(bn) * stage_bytes(bn) + 1024 /*align*/ + 256 /*barriers*/ + EPI_WARPS * EPI_STAGE_BYTES /*store staging*/;
+}
 
 struct EpilogueArgs {
   void* D;
@@ -49,6 +54,8 @@ struct EpilogueArgs {
   int act;       // 0 none, 1 relu, 2 swish, 3 gelu
   int dact;      // 0 none, 1 relu', 2 swish', 3 gelu'  (multiplies by act'(aux))
   int d_is_f32;  // output dtype
+  int stage_d;   // 1: bf16 D rows are 16-byte aligned at every 32-column block: store through the shared-memory transpose
+  int stage_p;   // same for D_pre
   unsigned int drop_thresh;  // 0 = no dropout; otherwise keep iff sb_dropout_keep(seed, batch*M*N + m*N + n, thresh)
   float drop_scale;          // 1 / (1 - p)
   unsigned long long drop_seed;
@@ -155,6 +162,28 @@ __device__ __forceinline__ float apply_dact(float g, float z, int dact) {
   if (dact == 2) return g * sb_dswish(z);
   if (dact == 3) return g * sb_dgelu(z);
   return g;
+}
+
+// Warp-level store of a 32 x 32 bf16 block: lane l holds row l (32 values); the block is transposed through shared
+// memory so that every store instruction writes 8 rows x 64 contiguous bytes instead of 32 rows x 16 bytes.
+__device__ __forceinline__ void stage_store_32x32(uint8_t* st, int lane, const float* v, __nv_bfloat16* dst_row0, long long ld,
+                                                  int rows_valid) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __align__(16) __nv_bfloat162 t[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) t[u] = __floats2bfloat162_rn(v[8 * j + 2 * u], v[8 * j + 2 * u + 1]);
+    *reinterpret_cast<uint4*>(st + lane * EPI_ROW_BYTES + j * 16) = *reinterpret_cast<const uint4*>(t);
+  }
+  __syncwarp();
+  const int ch = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = i * 8 + (lane >> 2);
+    const uint4 val = *reinterpret_cast<const uint4*>(st + r * EPI_ROW_BYTES + ch * 16);
+    if (r < rows_valid) *reinterpret_cast<uint4*>(dst_row0 + (long long)r * ld + ch * 8) = val;
+  }
+  __syncwarp();
 }
 
 template <bool A_MN, bool B_MN, int BN>
@@ -278,6 +307,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int q = warp & 3;            // TMEM lane quarter owned by this warp
     const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
     const EpilogueArgs& e = p.ep;
+    uint8_t* stage = smem + NUM_STAGES * STAGE_BYTES + 256 + (warp - 2) * EPI_STAGE_BYTES;
     long long tcount = 0;
     bool ok = true;
     for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++tcount) {
@@ -304,21 +334,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tmem_ld32(taddr, r);
         tmem_ld_wait();
         const int col0 = tn * BLOCK_N + c * 32;
-        if (row_ok && col0 < p.N) {
-          const bool full = (col0 + 32 <= p.N);
-          float v[32];
+        const bool full = (col0 + 32 <= p.N);
+        const int row_base = tm * BLOCK_M + q * 32;               // first row of this warp's 32-row slab
+        const int rows_valid = min(32, p.M - row_base);           // warp-uniform
+        const long long slab_d = (long long)b0 * e.d_bs0 + (long long)b1 * e.d_bs1 + (long long)row_base * e.ldd;
+        const long long slab_p = (long long)b0 * e.p_bs0 + (long long)b1 * e.p_bs1 + (long long)row_base * e.ldp;
+        const bool st_d = e.stage_d && full && rows_valid > 0;    // warp-uniform decisions
+        const bool st_p = e.stage_p && full && rows_valid > 0 && e.D_pre != nullptr;
+        float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        // the bias depends on the column only: add it once, for all lanes, before the stores and the activation
+        if (col0 < p.N) {
           if (e.bias_f32) {
+            if (full && ((((uintptr_t)(e.bias_f32 + col0)) & 15) == 0)) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (full || col0 + j < p.N) v[j] += __ldg(e.bias_f32 + col0 + j);
+              for (int j = 0; j < 8; ++j) {
+                const float4 bv = __ldg(reinterpret_cast<const float4*>(e.bias_f32 + col0) + j);
+                v[4 * j] += bv.x; v[4 * j + 1] += bv.y; v[4 * j + 2] += bv.z; v[4 * j + 3] += bv.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (full || col0 + j < p.N) v[j] += __ldg(e.bias_f32 + col0 + j);
+            }
           } else if (e.bias_bf16) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (full || col0 + j < p.N) v[j] += __bfloat162float(e.bias_bf16[col0 + j]);
           }
-          if (e.D_pre) {
+        }
+        // pre-activation (acc + bias) stored coalesced: all lanes take part, rows beyond M are masked in the helper
+        if (st_p) stage_store_32x32(stage, lane, v, e.D_pre + slab_p + col0, e.ldp, rows_valid);
+        if (row_ok && col0 < p.N) {
+          if (e.D_pre && !st_p) {
             __nv_bfloat16* dp = e.D_pre + p_off + col0;
             if (full && ((((uintptr_t)dp) & 15) == 0)) {
 #pragma unroll
@@ -329,13 +378,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 *reinterpret_cast<uint4*>(dp + j) = *reinterpret_cast<uint4*>(t);
               }
             } else {
+#pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (col0 + j < p.N) dp[j] = __float2bfloat16(v[j]);
             }
           }
-          if (e.act) {
+          if (e.act == 2) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], e.act);
+            for (int j = 0; j < 32; ++j) v[j] = sb_swish(v[j]);
+          } else if (e.act == 1) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+          } else if (e.act == 3) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = sb_gelu(v[j]);
           }
           if (e.drop_thresh) {
             const unsigned long long base = ((unsigned long long)batch * p.M + row) * (unsigned long long)p.N + col0;
@@ -361,6 +417,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
               }
             } else {
+#pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (col0 + j < p.N) v[j] = apply_dact(v[j], __bfloat162float(xp[j]), e.dact);
             }
@@ -380,6 +437,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
               }
             } else {
+#pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
             }
@@ -397,10 +455,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 *reinterpret_cast<float4*>(dp + j) = o;
               }
             } else {
+#pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (col0 + j < p.N) dp[j] = v[j] + (e.beta != 0.f ? e.beta * dp[j] : 0.f);
             }
-          } else {
+          } else if (!st_d) {
             __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(e.D) + d_off + col0;
             if (full && ((((uintptr_t)dp) & 15) == 0)) {
 #pragma unroll
@@ -411,11 +470,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 *reinterpret_cast<uint4*>(dp + j) = *reinterpret_cast<uint4*>(t);
               }
             } else {
+#pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (col0 + j < p.N) dp[j] = __float2bfloat16(v[j]);
             }
           }
         }
+        if (st_d) stage_store_32x32(stage, lane, v, reinterpret_cast<__nv_bfloat16*>(e.D) + slab_d + col0, e.ldd, rows_valid);
       }
       tc_fence_before();
       __syncwarp();
@@ -510,6 +571,9 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   e.aux = (const __nv_bfloat16*)a->aux; e.ldx = a->ldx; e.x_bs0 = a->x_bs0; e.x_bs1 = a->x_bs1;
   e.D_pre = (__nv_bfloat16*)a->D_pre; e.ldp = a->ldp; e.p_bs0 = a->p_bs0; e.p_bs1 = a->p_bs1;
   e.alpha = a->alpha; e.beta = a->beta; e.act = a->act; e.dact = (a->aux ? a->dact : 0);
+  auto al8 = [](long long x) { return (x % 8) == 0; };
+  e.stage_d = (!a->d_is_f32 && a->beta == 0.f && (((uintptr_t)a->D) & 15) == 0 && al8(a->ldd) && al8(a->d_bs0) && al8(a->d_bs1)) ? 1 : 0;
+  e.stage_p = (a->D_pre && (((uintptr_t)a->D_pre) & 15) == 0 && al8(a->ldp) && al8(a->p_bs0) && al8(a->p_bs1)) ? 1 : 0;
   e.drop_thresh = sb_dropout_threshold(a->drop_p);
   e.drop_scale = a->drop_p > 0.f ? 1.f / (1.f - a->drop_p) : 1.f;
   e.drop_seed = a->drop_seed;
