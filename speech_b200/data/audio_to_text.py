@@ -96,8 +96,9 @@ def write_manifest(path: str, items: List[Dict[str, Any]]) -> None:
 
 def load_audio(path: str, target_sr: int = 16000, offset: float = 0.0, duration: Optional[float] = None,
                channel_selector: Union[int, str, None] = None) -> np.ndarray:
-    """PCM WAV (8/16/24/32-bit int or 32-bit float) or ``.npy`` -> float32 mono at ``target_sr``."""
-    if path.endswith(".npy"):
+    """PCM WAV (8/16/24/32-bit int or 32-bit float) or ``.npy`` -> float32 mono at ``target_sr``.  ``path`` may also be a
+    binary file object holding a WAV (members of tarred datasets)."""
+    if isinstance(path, str) and path.endswith(".npy"):
         x, sr = np.load(path).astype(np.float32), target_sr
     else:
         try:

@@ -141,11 +141,16 @@ class ASRModel(ModelPT):
             labels = cfg_get(config, "labels", None) or cfg_get(self._cfg, "labels", None)
             if labels is None and hasattr(self, "decoder") and getattr(self.decoder, "vocabulary", None):
                 labels = self.decoder.vocabulary
+        rank = self.global_rank if self._trainer is not None else int(os.environ.get("RANK", 0))
+        ws = self.world_size if self._trainer is not None else int(os.environ.get("WORLD_SIZE", 1))
+        if cfg_get(config, "synthetic", None) is None and (cfg_get(config, "use_lhotse", False) or
+                                                           cfg_get(config, "input_cfg", None) is not None):
+            from ..data.cuts import get_dataloader_from_cuts_config
+
+            return get_dataloader_from_cuts_config(config, rank, ws, tokenizer=tok, labels=list(labels) if labels is not None else None)
         ds = _data.build_speech_dataset(config, tokenizer=tok, labels=list(labels) if labels is not None else None)
         if ds is None:
             return None
-        rank = self.global_rank if self._trainer is not None else int(os.environ.get("RANK", 0))
-        ws = self.world_size if self._trainer is not None else int(os.environ.get("WORLD_SIZE", 1))
         return _data.get_dataloader_from_config(config, ds, rank, ws)
 
     def setup_training_data(self, train_data_config):

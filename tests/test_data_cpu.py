@@ -1,0 +1,133 @@
+"""Cut-based data pipeline on CPU: manifests and tarred shards, input_cfg mux, filters, speed perturbation, bucketing
+(1-D, 2-D, token budget), noise / RIR augmentation, multi-config fusion, rank sharding."""
+import io
+import json
+import os
+import tarfile
+
+import numpy as np
+import pytest
+import torch
+
+from speech_b200.data.audio_to_text import save_wav
+from speech_b200.data.cuts import (Cut, CutSet, NoiseMixer, RIRConvolver, determine_bucket_duration_bins,
+                                   get_dataloader_from_cuts_config, parse_input_cfg, read_nemo_manifest, speed_perturb)
+from speech_b200.tokenizers import CharTokenizer
+
+TOK = CharTokenizer(list("abcdefghijklmnopqrstuvwxyz "))
+
+
+def _corpus(tmp_path, n=12, name="m"):
+    g = np.random.default_rng(0)
+    items = []
+    for i in range(n):
+        d = 0.2 + 0.1 * i
+        p = str(tmp_path / f"{name}{i}.wav")
+        save_wav(p, (0.1 * g.standard_normal(int(16000 * d))).astype(np.float32))
+        items.append({"audio_filepath": p, "duration": d, "text": "ab " * (1 + i % 4), "lang": "en"})
+    man = str(tmp_path / f"{name}.json")
+    with open(man, "w") as f:
+        for it in items:
+            f.write(json.dumps(it) + "\n")
+    return man, items
+
+
+def test_manifest_filters_buckets_and_rank_sharding(tmp_path):
+    man, items = _corpus(tmp_path)
+    cfg = {"manifest_filepath": man, "use_lhotse": True, "batch_duration": 2.0, "num_buckets": 2, "min_duration": 0.3,
+           "max_duration": 1.2, "shuffle": True, "seed": 1, "perturb_speed": False}
+    seen = []
+    for rank in range(2):
+        dl = get_dataloader_from_cuts_config(cfg, rank, 2, tokenizer=TOK)
+        for audio, alen, tok, tlen in dl:
+            assert audio.shape[0] == alen.numel() and float(alen.max()) / 16000 * len(alen) <= 2.0 + 1e-6
+            seen.append(sorted(alen.tolist()))
+    flat = sorted(x for b in seen for x in b)
+    kept = [int(16000 * it["duration"]) for it in items if 0.3 <= it["duration"] <= 1.2]
+    assert len(flat) <= len(kept) and set(flat) <= set(kept)
+    assert len(seen) % 2 == 0                        # both ranks got the same number of batches
+
+
+def test_input_cfg_mux_weights_tags_and_speed_perturbation(tmp_path):
+    m1, _ = _corpus(tmp_path, 6, "a")
+    m2, _ = _corpus(tmp_path, 6, "b")
+    cuts = parse_input_cfg([{"type": "nemo", "manifest_filepath": m1, "weight": 0.9, "tags": {"src": "a"}},
+                            {"type": "group", "weight": 0.1, "input_cfg": [{"type": "nemo", "manifest_filepath": m2, "tags": {"src": "b"}}]}],
+                           seed=3)
+    srcs = [c.custom["src"] for c in cuts]
+    assert sorted(srcs) == ["a"] * 6 + ["b"] * 6 and srcs[:4].count("a") >= 3
+    c = next(iter(read_nemo_manifest(m1)))
+    fast = c.with_speed(1.1)
+    assert abs(fast.duration - c.duration / 1.1) < 1e-9 and abs(len(fast.load_audio()) - len(c.load_audio()) / 1.1) <= 2
+    x = np.sin(np.arange(1600) * 0.1).astype(np.float32)
+    assert len(speed_perturb(x, 0.9)) == round(1600 / 0.9)
+    dl = get_dataloader_from_cuts_config({"input_cfg": [{"type": "nemo", "manifest_filepath": m1}], "batch_size": 4,
+                                          "perturb_speed": [0.9, 1.1]}, tokenizer=TOK)
+    assert sum(b[0].shape[0] for b in dl) == 18
+
+
+def test_two_dim_buckets_token_budget_and_duration_bins(tmp_path):
+    man, items = _corpus(tmp_path)
+    dl = get_dataloader_from_cuts_config({"manifest_filepath": man, "use_lhotse": True,
+                                          "bucket_duration_bins": [[0.6, 6], [0.6, 12], [1.4, 6], [1.4, 12]],
+                                          "bucket_batch_size": [4, 3, 2, 1]}, tokenizer=TOK)
+    for audio, alen, tok, tlen in dl:
+        d, t = float(alen.max()) / 16000, int(tlen.max())
+        limit = 4 if (d <= 0.6 and t <= 6) else 3 if d <= 0.6 else 2 if t <= 6 else 1
+        assert audio.shape[0] <= limit
+    dl2 = get_dataloader_from_cuts_config({"manifest_filepath": man, "use_lhotse": True, "batch_tokens": 40,
+                                           "token_equivalent_duration": 0.08}, tokenizer=TOK)
+    for audio, alen, tok, tlen in dl2:
+        assert (float(alen.max()) / 16000 / 0.08 + int(tlen.max())) * audio.shape[0] <= 40 + 13
+    bins = determine_bucket_duration_bins([1.0] * 10 + [5.0] * 2, 2)
+    assert bins == [1.0] or bins == [5.0]
+
+
+def test_tarred_shards_and_multi_config(tmp_path):
+    man, items = _corpus(tmp_path, 8, "t")
+    tars = []
+    for s in range(2):
+        tp = str(tmp_path / f"audio_{s}.tar")
+        with tarfile.open(tp, "w") as tf:
+            for it in items[s::2]:
+                tf.add(it["audio_filepath"], arcname=os.path.basename(it["audio_filepath"]))
+        tars.append(tp)
+    cfg = {"manifest_filepath": man, "tarred_audio_filepaths": str(tmp_path / "audio__OP_0..1_CL_.tar"), "batch_size": 2}
+    n0 = sum(b[0].shape[0] for b in get_dataloader_from_cuts_config(cfg, 0, 2, tokenizer=TOK))
+    n1 = sum(b[0].shape[0] for b in get_dataloader_from_cuts_config(cfg, 1, 2, tokenizer=TOK))
+    assert n0 == 4 and n1 == 4
+    m2, _ = _corpus(tmp_path, 4, "u")
+    fused = get_dataloader_from_cuts_config({"multi_config": True, "sampler_fusion": "round_robin",
+                                             "a": {"manifest_filepath": man, "use_lhotse": True, "batch_size": 4},
+                                             "b": {"manifest_filepath": m2, "use_lhotse": True, "batch_size": 2}}, tokenizer=TOK)
+    sizes = [b[0].shape[0] for b in fused]
+    assert sizes == [4, 2, 4, 2]
+
+
+def test_noise_and_rir_augmentation_keep_length_and_change_signal():
+    x = (0.3 * np.sin(np.arange(8000) * 0.05)).astype(np.float32)
+    noise = [Cut("n", (0.1 * np.random.default_rng(0).standard_normal(3000)).astype(np.float32), 3000 / 16000)]
+    y = NoiseMixer(noise, snr=10.0, prob=1.0)(x)
+    snr = 10 * np.log10((x ** 2).mean() / ((y - x) ** 2).mean())
+    assert y.shape == x.shape and abs(snr - 10.0) < 0.5
+    z = RIRConvolver(prob=1.0, seed=1)(x)
+    assert z.shape == x.shape and not np.allclose(z, x) and abs(np.abs(z).max() - np.abs(x).max()) < 1e-5
+
+
+def test_model_trains_from_cuts_config(tmp_path):
+    from speech_b200.core.config import open_dict
+    from speech_b200.core.trainer import Trainer
+    from speech_b200.models import EncDecCTCModel
+    from speech_b200.models.configs import fastconformer_ctc_config
+
+    man, _ = _corpus(tmp_path, 8, "z")
+    cfg = fastconformer_ctc_config("small", vocab_size=28, n_layers=1)
+    with open_dict(cfg):
+        del cfg["tokenizer"]
+        cfg.labels = list("abcdefghijklmnopqrstuvwxyz ") + ["'"]
+        cfg.decoder.vocabulary = cfg.labels
+        cfg.train_ds = {"use_lhotse": True, "manifest_filepath": man, "batch_duration": 3.0, "num_buckets": 2, "shuffle": True}
+    m = EncDecCTCModel(cfg)
+    tr = Trainer(max_steps=2, accelerator="cpu", log_every_n_steps=1, enable_checkpointing=False, logger=False)
+    tr.fit(m)
+    assert torch.isfinite(torch.as_tensor(float(tr.callback_metrics["train_loss"])))
