@@ -338,3 +338,12 @@ from .native_transducer import transducer_joint_loss, transducer_loss_from_logit
 from .native_lstm import lstm  # noqa: E402,F401
 from .native_ctc import ctc_loss  # noqa: E402,F401
 from .native_logmel import logmel  # noqa: E402,F401
+
+
+def __getattr__(name):
+    # decode graph builder lives with the decoders; exposed here because callers look it up next to the kernels
+    if name == "LabelLoopingGraph":
+        from ..decoding.label_looping_graph import LabelLoopingGraph
+
+        return LabelLoopingGraph
+    raise AttributeError(name)
