@@ -1,0 +1,16 @@
+"""Train a character-vocabulary CTC model.
+
+Usage: python examples/asr/asr_ctc/speech_to_text_ctc.py [--config-path DIR] [--config-name NAME] key=value ...
+(reference script: ``examples/asr/asr_ctc/speech_to_text_ctc.py``)."""
+from speech_b200.core.config import hydra_runner
+from speech_b200.models import EncDecCTCModel
+from speech_b200.utils.launch import run_training
+
+
+@hydra_runner(config_path="../conf/fastconformer", config_name="fast-conformer_ctc_char")
+def main(cfg):
+    run_training(EncDecCTCModel, cfg)
+
+
+if __name__ == "__main__":
+    main()
