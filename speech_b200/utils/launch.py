@@ -24,7 +24,10 @@ def run_training(model_cls: Type, cfg: DictConfig, model_key: str = "model", tes
     logging.info(f"Config:\n{OmegaConf.to_yaml(cfg)}")
     trainer = build_trainer(cfg)
     exp_manager(trainer, cfg.get("exp_manager", None))
-    model = model_cls(cfg=cfg[model_key], trainer=trainer)
+    # interpolations such as ${model.sample_rate} or ${trainer.max_steps} refer to the root config: resolve them while the
+    # model block is still attached to it
+    model_cfg = OmegaConf.create(to_container(cfg[model_key], resolve=True))
+    model = model_cls(cfg=model_cfg, trainer=trainer)
     if hasattr(model, "maybe_init_from_pretrained_checkpoint"):
         model.maybe_init_from_pretrained_checkpoint(cfg)
     trainer.fit(model)

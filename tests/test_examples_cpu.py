@@ -1,0 +1,50 @@
+"""The example scripts run end to end: train a tiny CTC model from the shipped YAML, then transcribe with the saved .nemo,
+then stream the same files through the buffered pipeline script."""
+import glob
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(script, args, cwd):
+    env = dict(os.environ, PYTHONPATH=REPO + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    out = subprocess.run([sys.executable, os.path.join(REPO, script)] + args, cwd=cwd, env=env, capture_output=True, text=True, timeout=900)
+    assert out.returncode == 0, out.stderr[-3000:]
+    return out.stdout + out.stderr
+
+
+def test_train_transcribe_and_stream_examples(tmp_path):
+    from speech_b200.data.audio_to_text import save_wav
+
+    g = np.random.default_rng(0)
+    man = tmp_path / "test.json"
+    with open(man, "w") as f:
+        for i in range(3):
+            p = str(tmp_path / f"a{i}.wav")
+            save_wav(p, (0.1 * g.standard_normal(16000 + 3000 * i)).astype(np.float32))
+            f.write(json.dumps({"audio_filepath": p, "duration": 1.0 + 0.1875 * i, "text": "w1 w2"}) + "\n")
+    exp = tmp_path / "exp"
+    _run("examples/asr/asr_ctc/speech_to_text_ctc_bpe.py", [
+        "model.tokenizer.type=synthetic", "+model.tokenizer.vocab_size=32", "model.tokenizer.dir=null",
+        "+model.train_ds.synthetic={num_samples: 8, vocab_size: 32, min_duration: 1.0, max_duration: 1.5}",
+        "model.train_ds.manifest_filepath=null", "model.validation_ds.manifest_filepath=null", "model.train_ds.batch_size=4",
+        "model.train_ds.num_workers=0", "model.encoder.n_layers=1", "model.encoder.d_model=64", "model.encoder.n_heads=4",
+        "trainer.max_steps=2", "trainer.max_epochs=null", "trainer.accelerator=cpu", "trainer.devices=1", "trainer.precision=32",
+        "trainer.strategy=auto", f"exp_manager.exp_dir={exp}", "exp_manager.create_tensorboard_logger=false"], str(tmp_path))
+    nemo = glob.glob(str(exp / "**" / "*.nemo"), recursive=True)
+    assert nemo
+    out_json = tmp_path / "out.json"
+    log = _run("examples/asr/transcribe_speech.py", [f"model_path={nemo[0]}", f"dataset_manifest={man}", f"output_filename={out_json}",
+                                                     "batch_size=2", "cuda=-1", "calculate_rtfx=true"], str(tmp_path))
+    recs = [json.loads(l) for l in open(out_json)]
+    assert len(recs) == 3 and all("pred_text" in r for r in recs) and "RTFx" in log
+    log = _run("examples/asr/asr_streaming_inference/asr_streaming_infer.py", [
+        "--config-name", "buffered_ctc", f"asr.model_name={nemo[0]}", "asr.device=cpu", "asr.compute_dtype=float32", f"audio_file={man}",
+        f"output_filename={tmp_path / 'stream.json'}", "streaming.batch_size=2", "streaming.chunk_size=0.4",
+        "streaming.left_padding_size=0.4", "streaming.right_padding_size=0.2"], str(tmp_path))
+    assert "RTFx" in log and len(open(tmp_path / "stream.json").read().splitlines()) == 3
