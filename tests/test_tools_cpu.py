@@ -1,0 +1,96 @@
+"""Command-line helpers: duration bins, tarred conversion, n-gram LM training, forced alignment, checkpoint averaging,
+tokenizer building, batch-size search."""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from speech_b200.data import tools
+from speech_b200.data.audio_to_text import read_manifest, save_wav
+from speech_b200.decoding.forced_aligner import viterbi_ctc_alignment
+from speech_b200.decoding.ngram_lm import NGramGPULanguageModel, write_arpa
+from speech_b200.decoding.train_ngram_lm import train_ngram
+from speech_b200.utils.checkpoint_averaging import average_state_dicts
+from speech_b200.utils.oomptimizer import find_max_batch
+
+
+def _corpus(tmp_path, n=10):
+    g = np.random.default_rng(0)
+    man = str(tmp_path / "m.json")
+    with open(man, "w") as f:
+        for i in range(n):
+            p = str(tmp_path / f"a{i}.wav")
+            save_wav(p, (0.1 * g.standard_normal(1600 * (i + 1))).astype(np.float32))
+            f.write(json.dumps({"audio_filepath": p, "duration": 0.1 * (i + 1), "text": "hello world " * (1 + i % 3)}) + "\n")
+    return man
+
+
+def test_duration_bins_weights_and_tarred_conversion(tmp_path):
+    man = _corpus(tmp_path)
+    bins = tools.estimate_duration_bins([man], 3)
+    assert len(bins) == 2 and bins == sorted(bins) and 0.1 < bins[0] < bins[1] < 1.0
+    w = tools.estimate_data_weights({"a": man, "b": man}, temperature=0.5)
+    assert abs(w["a"] - 0.5) < 1e-9
+    meta = tools.convert_to_tarred(man, str(tmp_path / "tar"), num_shards=3, seed=1)
+    assert meta["num_samples_per_shard"] == 3 and meta["dropped"] == 1
+    from speech_b200.data.cuts import read_nemo_tarred
+
+    cuts = list(read_nemo_tarred(str(tmp_path / "tar" / "tarred_audio_manifest.json"), str(tmp_path / "tar" / "audio__OP_0..2_CL_.tar")))
+    assert len(cuts) == 9 and all(abs(len(c.audio) / 16000 - c.duration) < 1e-3 for c in cuts)
+    tools.main(["filter-manifest", man, str(tmp_path / "f.json"), "--max-duration", "0.5"])
+    assert len(read_manifest(str(tmp_path / "f.json"))) == 5
+
+
+def test_ngram_training_normalises_and_prefers_seen_sequences(tmp_path):
+    sents = [[0, 1, 2], [0, 1, 3], [0, 1, 2], [4, 1, 2]] * 5
+    grams = train_ngram(sents, order=3, vocab_size=5)
+    arpa = str(tmp_path / "lm.arpa")
+    write_arpa(arpa, grams)
+    lm = NGramGPULanguageModel.from_arpa(arpa, vocab_size=5)
+    st = lm.get_init_states(1, bos=True)
+    sc, nx = lm.advance(st)
+    total = float(torch.logsumexp(torch.cat([sc[0], lm.get_final(st)]), 0))
+    assert abs(total) < 0.05                                    # p(. | <s>) sums to ~1 over tokens + </s> (unk mass aside)
+    assert lm.score_sentence([0, 1, 2]) > lm.score_sentence([2, 1, 0]) + 2.0
+    st = nx[:, 0]
+    sc, nx = lm.advance(st)
+    assert int(sc[0].argmax()) == 1
+
+
+def test_viterbi_alignment_finds_the_planted_path():
+    T, V, blank = 12, 5, 4
+    lp = torch.full((T, V), -6.0)
+    lp[:, blank] = -0.5
+    for t, tok in [(2, 1), (3, 1), (6, 2), (9, 1)]:
+        lp[t, tok], lp[t, blank] = -0.05, -5.0
+    spans = viterbi_ctc_alignment(lp, [1, 2, 1], blank)
+    assert [(a, b) for a, b, _ in spans] == [(2, 3), (6, 6), (9, 9)]
+    assert viterbi_ctc_alignment(lp, [], blank) == []
+    with pytest.raises(ValueError):
+        viterbi_ctc_alignment(lp[:2], [1, 2, 1], blank)
+
+
+def test_checkpoint_averaging_and_batch_search():
+    a = {"w": torch.tensor([1.0, 3.0]), "n": torch.tensor(5)}
+    b = {"w": torch.tensor([3.0, 5.0]), "n": torch.tensor(9)}
+    avg = average_state_dicts([a, b])
+    assert avg["w"].tolist() == [2.0, 4.0] and int(avg["n"]) == 5
+    calls = []
+    assert find_max_batch(lambda n: (calls.append(n) or n <= 37), start=1, limit=4096) in range(35, 38)
+    assert find_max_batch(lambda n: False) == 0 and find_max_batch(lambda n: True, limit=64) == 64
+
+
+def test_tokenizer_builder(tmp_path):
+    from speech_b200.tokenizers import SentencePieceTokenizer, WordPieceVocabTokenizer
+    from speech_b200.tokenizers.process_asr_text_tokenizer import main
+
+    man = _corpus(tmp_path, 6)
+    main(["--manifest", man, "--data_root", str(tmp_path / "tok"), "--vocab_size", "20", "--tokenizer", "spe", "--spe_type", "bpe"])
+    tok = SentencePieceTokenizer(str(tmp_path / "tok" / "tokenizer_spe_bpe_v20" / "tokenizer.model"))
+    assert tok.ids_to_text(tok.text_to_ids("hello world")) == "hello world"
+    main(["--manifest", man, "--data_root", str(tmp_path / "tok"), "--vocab_size", "30", "--tokenizer", "wpe"])
+    wp = WordPieceVocabTokenizer(str(tmp_path / "tok" / "tokenizer_wpe_v30" / "vocab.txt"))
+    assert wp.ids_to_text(wp.text_to_ids("hello world")) == "hello world"
