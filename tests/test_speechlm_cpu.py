@@ -136,3 +136,38 @@ def test_heartbeat_straggler_and_fault_tolerance_on_host(tmp_path):
     ft.setup(tr, None, "fit")
     ft.on_train_batch_end(tr, None, None, None, 0)
     assert tr.should_stop and "no heartbeat from ranks [1, 2]" in ft.failures[0]
+
+
+def test_packed_sequences_cp_partition_chunking_and_metrics():
+    from speech_b200.speechlm import parts
+
+    e = [torch.randn(5, 4), torch.randn(8, 4)]
+    t = [torch.arange(5), torch.arange(8)]
+    p = parts.pack_sequences(e, t, cp_size=2, tp_size=3)
+    assert p.cu_seqlens.tolist() == [0, 4, 12, 12] or p.cu_seqlens.tolist()[-1] % 3 == 0
+    assert p.input_embeds.shape[1] == p.target_ids.shape[1] == int(p.cu_seqlens[-1]) and p.input_embeds.shape[1] % 3 == 0
+    assert p.target_ids[0, :4].tolist() == [1, 2, 3, 4] and p.position_ids[0, 4:7].tolist() == [0, 1, 2]
+    # the packed row attends block-diagonally: logits equal the per-sequence logits
+    m = CausalLM(LLMConfig(**TINY)).eval()
+    a, b = torch.randn(1, 4, 64), torch.randn(1, 6, 64)
+    row = torch.cat([a, b], dim=1)
+    seq = torch.tensor([[0] * 4 + [1] * 6])
+    pos = torch.tensor([[0, 1, 2, 3, 0, 1, 2, 3, 4, 5]])
+    packed = m(inputs_embeds=row, position_ids=pos, seq_ids=seq)["logits"]
+    assert torch.allclose(packed[:, :4], m(inputs_embeds=a)["logits"], atol=1e-4)
+    assert torch.allclose(packed[:, 4:], m(inputs_embeds=b)["logits"], atol=1e-4)
+    idx0 = parts.thd_partition_indices(torch.tensor([0, 8, 16]), cp_size=2, cp_rank=0)
+    idx1 = parts.thd_partition_indices(torch.tensor([0, 8, 16]), cp_size=2, cp_rank=1)
+    assert sorted(idx0.tolist() + idx1.tolist()) == list(range(16)) and idx0.tolist()[:4] == [0, 1, 6, 7]
+    aud = torch.randn(2, 1000)
+    ch, cl, owner = parts.chunk_audio(aud, torch.tensor([1000, 450]), 400)
+    assert ch.shape == (5, 400) and cl.tolist() == [400, 400, 200, 400, 50] and owner.tolist() == [0, 0, 0, 1, 1]
+    emb, lens = parts.recombine_chunk_embeddings(torch.ones(5, 3, 2), torch.tensor([3, 3, 2, 3, 1]), owner, 2)
+    assert lens.tolist() == [8, 4] and emb.shape == (2, 8, 2)
+    a0, l0, real0 = parts.split_audio_for_cp(aud, torch.tensor([1000, 450]), cp_size=4, cp_rank=3)
+    assert real0 == 0 and a0.shape == (1, 1000) and l0.tolist() == [1]
+    assert parts.bleu(["the cat sat on the mat"], ["the cat sat on the mat"]) == pytest.approx(100.0)
+    assert parts.bleu(["a b c d e"], ["v w x y z"]) == 0.0
+    lg = torch.zeros(1, 3, 5)
+    lg[0, 0, 2] = lg[0, 1, 1] = lg[0, 2, 0] = 5.0
+    assert parts.token_accuracy(lg, torch.tensor([[2, 4, -100]])) == 0.5
