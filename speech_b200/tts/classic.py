@@ -1,0 +1,379 @@
+"""Classic two-stage TTS: FastPitch (text → mel with explicit duration / pitch), HiFi-GAN vocoder (mel → waveform), the
+alignment model (text ↔ mel attention trained with the forward-sum loss) and dictionary grapheme-to-phoneme conversion.
+
+Reference: ``tts/models/fastpitch.py`` + ``modules/fastpitch.py`` / ``modules/transformer.py`` (FFTransformer),
+``tts/models/hifigan.py``, ``tts/models/aligner.py`` + ``modules/aligner.py``, ``tts/g2p/models/en_us_arpabet.py`` /
+``i18n_ipa.py``; monotonic alignment search ``tts/parts/utils/helpers.py:192-260`` (``binarize_attention``).
+"""
+from __future__ import annotations
+
+import math
+import re
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..core.config import DictConfig, cfg_get
+from ..core.modelpt import ModelPT
+from .audio_codec import Discriminator, HiFiGANDecoder, MelLoss, discriminator_loss, feature_matching_loss, generator_adv_loss
+from .magpietts import ForwardSumLoss, beta_binomial_prior
+from .transformer_2501 import Transformer
+
+
+# ---------------------------------------------------------------------------------------------- G2P
+class DictG2p:
+    """Word → phoneme lookup with a CMUdict-style dictionary (``WORD  P1 P2 ...``); unknown words fall back to graphemes
+    (or are spelled with ``oov_fn``).  ``phoneme_probability`` < 1 mixes graphemes in during training, as the reference does."""
+
+    PUNCT = ",.!?;:'\"()-"
+
+    def __init__(self, phoneme_dict, phoneme_probability: Optional[float] = None, apply_to_oov_word=None, ignore_ambiguous_words: bool = True,
+                 seed: int = 0, grapheme_prefix: str = ""):
+        self.dict: Dict[str, List[List[str]]] = {}
+        if isinstance(phoneme_dict, dict):
+            for w, p in phoneme_dict.items():
+                self.dict[w.lower()] = [list(x) for x in p] if p and isinstance(p[0], (list, tuple)) else [list(p)]
+        else:
+            with open(phoneme_dict, encoding="latin-1") as f:
+                for line in f:
+                    if not line.strip() or line.startswith(";;;"):
+                        continue
+                    parts = line.split()
+                    w = re.sub(r"\(\d+\)$", "", parts[0]).lower()
+                    self.dict.setdefault(w, []).append(parts[1:])
+        self.p, self.oov_fn, self.ignore_ambiguous = phoneme_probability, apply_to_oov_word, ignore_ambiguous_words
+        self.rng = np.random.default_rng(seed)
+        self.grapheme_prefix = grapheme_prefix
+
+    def __call__(self, text: str) -> List[str]:
+        out: List[str] = []
+        for tok in re.findall(r"[\w']+|[^\w\s]|\s+", text):
+            if tok.isspace():
+                out.append(" ")
+                continue
+            w = tok.lower()
+            prons = self.dict.get(w)
+            use_phon = prons is not None and (self.p is None or self.rng.random() < self.p) and \
+                not (self.ignore_ambiguous and len(prons) > 1)
+            if use_phon:
+                out.extend(prons[0])
+            elif prons is None and self.oov_fn is not None and tok not in self.PUNCT:
+                out.extend(self.oov_fn(w))
+            else:
+                out.extend(self.grapheme_prefix + ch for ch in w)
+        return out
+
+
+class PhonemeTokenizer:
+    def __init__(self, g2p: DictG2p, symbols: Optional[Sequence[str]] = None, pad: str = "<pad>", blank: str = "<blank>", oov: str = "<oov>"):
+        syms = list(symbols) if symbols is not None else sorted({p for prons in g2p.dict.values() for pr in prons for p in pr})
+        chars = list("abcdefghijklmnopqrstuvwxyz' ") + list(DictG2p.PUNCT)
+        self.tokens = [pad, blank, oov] + [s for s in dict.fromkeys(syms + chars)]
+        self._t2i = {t: i for i, t in enumerate(self.tokens)}
+        self.g2p, self.pad, self.blank, self.oov = g2p, 0, 1, 2
+
+    @property
+    def vocab_size(self):
+        return len(self.tokens)
+
+    def text_to_ids(self, text: str) -> List[int]:
+        return [self._t2i.get(p, self.oov) for p in self.g2p(text)]
+
+    encode = text_to_ids
+
+    def ids_to_tokens(self, ids):
+        return [self.tokens[int(i)] for i in ids]
+
+
+# ---------------------------------------------------------------------------------------------- alignment utilities
+def binarize_attention(attn: torch.Tensor, in_lens: torch.Tensor, out_lens: torch.Tensor) -> torch.Tensor:
+    """Monotonic alignment search: hard 0/1 path [B, T_out, T_in] maximising the sum of log attention."""
+    B = attn.shape[0]
+    out = torch.zeros_like(attn)
+    la = torch.log(attn.detach().float().clamp(min=1e-12)).cpu().numpy()
+    for b in range(B):
+        T, N = int(out_lens[b]), int(in_lens[b])
+        a = la[b, :T, :N]
+        Q = np.full((T, N), -np.inf)
+        Q[0, 0] = a[0, 0]
+        for t in range(1, T):
+            for n in range(min(N, t + 1)):
+                prev = Q[t - 1, n] if n == 0 else max(Q[t - 1, n], Q[t - 1, n - 1])
+                Q[t, n] = prev + a[t, n]
+        n = N - 1
+        for t in range(T - 1, -1, -1):
+            out[b, t, n] = 1.0
+            if t > 0 and n > 0 and (n == t or Q[t - 1, n - 1] >= Q[t - 1, n]):
+                n -= 1
+    return out
+
+
+def regulate_len(durations: torch.Tensor, enc: torch.Tensor, pace: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Repeat every encoder step ``round(duration / pace)`` times.  durations [B, N], enc [B, N, D] → ([B, T, D], lens)."""
+    reps = torch.round(durations.float() / pace).long().clamp(min=0)
+    lens = reps.sum(1)
+    T = int(lens.max()) if lens.numel() else 0
+    out = enc.new_zeros((enc.shape[0], T, enc.shape[2]))
+    for b in range(enc.shape[0]):
+        r = torch.repeat_interleave(enc[b], reps[b], dim=0)
+        out[b, : r.shape[0]] = r
+    return out, lens
+
+
+class ConvAttention(nn.Module):
+    """Aligner attention: conv-encoded text keys and mel queries, distance-based soft attention (+ optional prior)."""
+
+    def __init__(self, n_mel: int = 80, n_text: int = 256, n_att: int = 80, temperature: float = 0.0005):
+        super().__init__()
+        self.temperature = temperature
+        self.key_proj = nn.Sequential(nn.Conv1d(n_text, n_text * 2, 3, padding=1), nn.ReLU(), nn.Conv1d(n_text * 2, n_att, 1))
+        self.query_proj = nn.Sequential(nn.Conv1d(n_mel, n_mel * 2, 3, padding=1), nn.ReLU(), nn.Conv1d(n_mel * 2, n_mel, 1), nn.ReLU(),
+                                        nn.Conv1d(n_mel, n_att, 1))
+
+    def forward(self, queries, keys, mask=None, attn_prior=None):
+        """queries [B, n_mel, T], keys [B, n_text, N], mask [B, N] True at padding → (soft attention [B, 1, T, N], log-probs)."""
+        k, q = self.key_proj(keys), self.query_proj(queries)
+        d = ((q.unsqueeze(3) - k.unsqueeze(2)) ** 2).sum(1, keepdim=True)
+        logp = -self.temperature * d
+        if attn_prior is not None:
+            logp = torch.log_softmax(logp, dim=3) + torch.log(attn_prior.unsqueeze(1) + 1e-8)
+        if mask is not None:
+            logp = logp.masked_fill(mask.unsqueeze(1).unsqueeze(1), -float("inf"))
+        return torch.softmax(logp, dim=3), logp
+
+
+class TemporalPredictor(nn.Module):
+    def __init__(self, d_in: int, d_hidden: int = 256, kernel: int = 3, dropout: float = 0.1, n_layers: int = 2):
+        super().__init__()
+        layers, c = [], d_in
+        for _ in range(n_layers):
+            layers.append(nn.ModuleList([nn.Conv1d(c, d_hidden, kernel, padding=kernel // 2), nn.LayerNorm(d_hidden), nn.Dropout(dropout)]))
+            c = d_hidden
+        self.layers = nn.ModuleList(layers)
+        self.fc = nn.Linear(d_hidden, 1)
+
+    def forward(self, x, mask):
+        """x [B, N, D], mask [B, N] True at valid positions → [B, N]."""
+        h = x * mask.unsqueeze(-1)
+        for conv, ln, dr in self.layers:
+            h = dr(ln(F.relu(conv(h.transpose(1, 2)).transpose(1, 2))))
+        return self.fc(h).squeeze(-1) * mask
+
+
+class FastPitchModel(ModelPT):
+    def __init__(self, cfg: DictConfig, trainer=None, tokenizer=None):
+        super().__init__(cfg=cfg, trainer=trainer)
+        cfg = self._cfg
+        self.tokenizer = tokenizer
+        n_sym = cfg_get(cfg, "n_symbols", tokenizer.vocab_size if tokenizer is not None else 128)
+        d = cfg_get(cfg, "symbols_embedding_dim", 384)
+        self.n_mel = cfg_get(cfg, "n_mel_channels", 80)
+        self.embedding = nn.Embedding(n_sym, d, padding_idx=0)
+        tf = dict(d_model=d, d_ffn=cfg_get(cfg, "d_inner", 1536), sa_n_heads=cfg_get(cfg, "n_heads", 1), kernel_size=3, p_dropout=0.1,
+                  is_causal=False, use_learnable_pos_emb=True, max_length_causal_mask=2048)
+        self.encoder = Transformer(n_layers=cfg_get(cfg, "encoder_layers", 6), **tf)
+        self.decoder = Transformer(n_layers=cfg_get(cfg, "decoder_layers", 6), **tf)
+        self.duration_predictor = TemporalPredictor(d)
+        self.pitch_predictor = TemporalPredictor(d)
+        self.pitch_emb = nn.Conv1d(1, d, 3, padding=1)
+        self.proj = nn.Linear(d, self.n_mel)
+        self.aligner = ConvAttention(self.n_mel, d)
+        self.forward_sum = ForwardSumLoss()
+        n_spk = cfg_get(cfg, "n_speakers", 1)
+        self.speaker_emb = nn.Embedding(n_spk, d) if n_spk > 1 else None
+        self.mel = MelLoss(cfg_get(cfg, "sample_rate", 22050), self.n_mel, cfg_get(cfg, "n_fft", 1024), cfg_get(cfg, "hop_length", 256),
+                           cfg_get(cfg, "win_length", 1024))
+        self.w = {"dur": cfg_get(cfg, "dur_loss_scale", 0.1), "pitch": cfg_get(cfg, "pitch_loss_scale", 0.1), "align": cfg_get(cfg, "align_loss_scale", 1.0)}
+        self.bin_loss_start = cfg_get(cfg, "bin_loss_warmup_epochs", 100)
+
+    @classmethod
+    def list_available_models(cls):
+        return []
+
+    def setup_training_data(self, c):
+        from .data import build_tts_dataloader
+
+        self._train_dl = build_tts_dataloader(c, self.tokenizer, cfg_get(self._cfg, "sample_rate", 22050)) if c is not None else None
+
+    def setup_validation_data(self, c):
+        self._validation_dl = None
+
+    @staticmethod
+    def estimate_pitch(audio: torch.Tensor, hop: int, sr: int, fmin: float = 60.0, fmax: float = 400.0) -> torch.Tensor:
+        """Frame-wise f0 by autocorrelation peak picking (0 where unvoiced)."""
+        B, n = audio.shape
+        win = 4 * hop
+        T = n // hop + 1
+        x = F.pad(audio, (win // 2, win // 2 + hop))
+        fr = x.unfold(1, win, hop)[:, :T]
+        fr = fr - fr.mean(-1, keepdim=True)
+        spec = torch.fft.rfft(fr, 2 * win)
+        ac = torch.fft.irfft(spec.abs() ** 2)[..., :win]
+        lo, hi = int(sr / fmax), min(win - 1, int(sr / fmin))
+        seg = ac[..., lo:hi]
+        peak, idx = seg.max(-1)
+        f0 = sr / (idx + lo).float()
+        return torch.where(peak > 0.3 * ac[..., 0].clamp(min=1e-8), f0, torch.zeros_like(f0))
+
+    def forward(self, text, text_len, mel=None, mel_len=None, pitch=None, speaker=None, pace: float = 1.0):
+        mask = torch.arange(text.shape[1], device=text.device)[None] < text_len[:, None]
+        x = self.embedding(text)
+        if self.speaker_emb is not None and speaker is not None:
+            x = x + self.speaker_emb(speaker).unsqueeze(1)
+        enc = self.encoder(x, mask)["output"].float()
+        log_dur = self.duration_predictor(enc, mask)
+        pitch_pred = self.pitch_predictor(enc, mask)
+        attn_soft = attn_logp = attn_hard = None
+        if mel is not None:
+            T = mel.shape[2]
+            prior = torch.zeros((text.shape[0], T, text.shape[1]), device=text.device)
+            for b in range(text.shape[0]):
+                prior[b, : int(mel_len[b]), : int(text_len[b])] = beta_binomial_prior(int(text_len[b]), int(mel_len[b])).to(text.device)
+            attn_soft, attn_logp = self.aligner(mel, x.transpose(1, 2).float(), ~mask, prior)
+            attn_hard = binarize_attention(attn_soft.squeeze(1), text_len, mel_len)
+            dur = attn_hard.sum(1)
+            pitch_tok = (torch.bmm(attn_hard.transpose(1, 2), pitch.unsqueeze(-1)).squeeze(-1) / dur.clamp(min=1)) if pitch is not None else pitch_pred
+        else:
+            dur = torch.clamp(torch.exp(log_dur) - 1, min=0) * mask
+            pitch_tok = pitch_pred
+        enc = enc + self.pitch_emb(pitch_tok.unsqueeze(1)).transpose(1, 2)
+        frames, flen = regulate_len(dur, enc, pace)
+        fmask = torch.arange(frames.shape[1], device=text.device)[None] < flen[:, None]
+        dec = self.decoder(frames, fmask)["output"].float()
+        return {"mel": self.proj(dec).transpose(1, 2), "mel_len": flen, "log_dur": log_dur, "pitch_pred": pitch_pred, "dur": dur,
+                "pitch_tok": pitch_tok, "attn_soft": attn_soft, "attn_logp": attn_logp, "attn_hard": attn_hard, "mask": mask}
+
+    def training_step(self, batch, batch_idx):
+        text, text_len, audio, audio_len = batch[:4]
+        hop = self.mel.hop
+        with torch.no_grad():
+            mel = self.mel.mel(audio)
+            mel_len = torch.div(audio_len, hop, rounding_mode="floor") + 1
+            pitch = self.estimate_pitch(audio, hop, cfg_get(self._cfg, "sample_rate", 22050))[:, : mel.shape[2]]
+            pitch = F.pad(pitch, (0, mel.shape[2] - pitch.shape[1])) / 100.0
+        o = self.forward(text, text_len, mel, mel_len, pitch)
+        T = min(o["mel"].shape[2], mel.shape[2])
+        fm = (torch.arange(T, device=mel.device)[None] < mel_len[:, None]).unsqueeze(1)
+        mel_loss = ((o["mel"][..., :T] - mel[..., :T]) ** 2 * fm).sum() / (fm.sum() * self.n_mel).clamp(min=1)
+        m = o["mask"]
+        dur_loss = ((o["log_dur"] - torch.log(o["dur"] + 1)) ** 2 * m).sum() / m.sum()
+        pitch_loss = ((o["pitch_pred"] - o["pitch_tok"].detach()) ** 2 * m).sum() / m.sum()
+        align = self.forward_sum(o["attn_logp"].squeeze(1), text_len, mel_len)
+        loss = mel_loss + self.w["dur"] * dur_loss + self.w["pitch"] * pitch_loss + self.w["align"] * align
+        if self.current_epoch >= self.bin_loss_start:
+            loss = loss - (o["attn_hard"] * torch.log(o["attn_soft"].squeeze(1).clamp(min=1e-12))).sum() / o["attn_hard"].sum().clamp(min=1)
+        self.log_dict({"train_loss": loss.detach(), "mel_loss": mel_loss.detach(), "dur_loss": dur_loss.detach(), "align_loss": align.detach()})
+        return {"loss": loss}
+
+    @torch.no_grad()
+    def generate_spectrogram(self, tokens: torch.Tensor, speaker=None, pace: float = 1.0) -> torch.Tensor:
+        self.eval()
+        lens = torch.tensor([tokens.shape[1]] * tokens.shape[0], device=tokens.device)
+        return self.forward(tokens, lens, speaker=speaker, pace=pace)["mel"]
+
+    def parse(self, text: str) -> torch.Tensor:
+        return torch.tensor([self.tokenizer.text_to_ids(text)], dtype=torch.long, device=self.device)
+
+
+class HifiGanModel(ModelPT):
+    """Vocoder: mel spectrogram → waveform (generator = ``HiFiGANDecoder``; multi-period + STFT discriminators)."""
+
+    def __init__(self, cfg: DictConfig, trainer=None):
+        super().__init__(cfg=cfg, trainer=trainer)
+        cfg = self._cfg
+        self.sample_rate = cfg_get(cfg, "sample_rate", 22050)
+        g = dict(cfg_get(cfg, "generator", {}) or {})
+        self.n_mel = g.pop("input_dim", 80)
+        self.generator = HiFiGANDecoder(input_dim=self.n_mel, **g)
+        self.discriminator = Discriminator(**dict(cfg_get(cfg, "discriminator", {}) or {}))
+        self.mel = MelLoss(self.sample_rate, self.n_mel, **dict(cfg_get(cfg, "mel", {}) or {}))
+        self.l1_factor = cfg_get(cfg, "l1_loss_factor", 45.0)
+
+    @classmethod
+    def list_available_models(cls):
+        return []
+
+    def setup_training_data(self, c):
+        self._train_dl = None
+
+    def setup_validation_data(self, c):
+        self._validation_dl = None
+
+    def forward(self, spec: torch.Tensor) -> torch.Tensor:
+        lens = torch.full((spec.shape[0],), spec.shape[2], device=spec.device, dtype=torch.long)
+        return self.generator(spec, lens)[0]
+
+    convert_spectrogram_to_audio = forward
+
+    def configure_optimizers(self):
+        lr = cfg_get(cfg_get(self._cfg, "optim", {}), "lr", 2e-4)
+        self._optimizers = [torch.optim.AdamW(self.generator.parameters(), lr=lr, betas=(0.8, 0.99)),
+                            torch.optim.AdamW(self.discriminator.parameters(), lr=lr, betas=(0.8, 0.99))]
+        return self._optimizers
+
+    def training_step(self, batch, batch_idx):
+        audio, audio_len = batch[0], batch[1]
+        with torch.no_grad():
+            mel = self.mel.mel(audio)
+        gen = self.forward(mel)
+        n = min(gen.shape[-1], audio.shape[-1])
+        audio, gen = audio[..., :n], gen[..., :n]
+        opts = getattr(self, "_optimizers", None)
+        if opts is not None:
+            sr, sg, _, _ = self.discriminator(audio, gen.detach())
+            d = discriminator_loss(sr, sg)
+            opts[1].zero_grad()
+            d.backward()
+            opts[1].step()
+        sr, sg, fr, fg = self.discriminator(audio, gen)
+        loss = self.l1_factor * self.mel(audio, gen, audio_len) + generator_adv_loss(sg) + 2.0 * feature_matching_loss(fr, fg)
+        self.log_dict({"train_loss": loss.detach()})
+        return {"loss": loss}
+
+
+class AlignerModel(ModelPT):
+    """Learns text ↔ mel alignments alone (used to extract durations for other models)."""
+
+    def __init__(self, cfg: DictConfig, trainer=None, tokenizer=None):
+        super().__init__(cfg=cfg, trainer=trainer)
+        cfg = self._cfg
+        self.tokenizer = tokenizer
+        d = cfg_get(cfg, "symbols_embedding_dim", 256)
+        self.n_mel = cfg_get(cfg, "n_mel_channels", 80)
+        self.embed = nn.Embedding(cfg_get(cfg, "n_symbols", tokenizer.vocab_size if tokenizer is not None else 128), d)
+        self.alignment_encoder = ConvAttention(self.n_mel, d)
+        self.forward_sum = ForwardSumLoss()
+        self.mel = MelLoss(cfg_get(cfg, "sample_rate", 22050), self.n_mel)
+
+    @classmethod
+    def list_available_models(cls):
+        return []
+
+    def setup_training_data(self, c):
+        self._train_dl = None
+
+    def setup_validation_data(self, c):
+        self._validation_dl = None
+
+    def forward(self, spec, spec_len, text, text_len, attn_prior=None):
+        mask = torch.arange(text.shape[1], device=text.device)[None] >= text_len[:, None]
+        soft, logp = self.alignment_encoder(spec, self.embed(text).transpose(1, 2), mask, attn_prior)
+        return soft, logp
+
+    def training_step(self, batch, batch_idx):
+        text, text_len, audio, audio_len = batch[:4]
+        with torch.no_grad():
+            spec = self.mel.mel(audio)
+            spec_len = torch.div(audio_len, self.mel.hop, rounding_mode="floor") + 1
+        soft, logp = self.forward(spec, spec_len, text, text_len)
+        loss = self.forward_sum(logp.squeeze(1), text_len, spec_len)
+        self.log_dict({"train_loss": loss.detach()})
+        return {"loss": loss}
+
+    @torch.no_grad()
+    def durations(self, spec, spec_len, text, text_len) -> torch.Tensor:
+        soft, _ = self.forward(spec, spec_len, text, text_len)
+        return binarize_attention(soft.squeeze(1), text_len, spec_len).sum(1)

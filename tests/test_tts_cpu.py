@@ -108,3 +108,51 @@ def test_magpie_trains_and_synthesises():
     assert audio.shape[0] == 1 and 0 < int(alen[0]) <= audio.shape[1]
     long = m.generate_speech("ab. cd! ef?", max_chars_per_chunk=4, max_decoder_steps=3)
     assert long.numel() > 0
+
+
+def test_classic_tts_g2p_alignment_fastpitch_vocoder_aligner():
+    from speech_b200.tts.classic import (AlignerModel, DictG2p, FastPitchModel, HifiGanModel, PhonemeTokenizer, binarize_attention,
+                                         regulate_len)
+
+    g2p = DictG2p({"hello": [["HH", "AH0", "L", "OW1"]], "read": [["R", "IY1", "D"], ["R", "EH1", "D"]]})
+    assert g2p("Hello, read xyz") == ["HH", "AH0", "L", "OW1", ",", " ", "r", "e", "a", "d", " ", "x", "y", "z"]
+    tok = PhonemeTokenizer(g2p)
+    ids = tok.text_to_ids("hello world")
+    assert tok.ids_to_tokens(ids)[:4] == ["HH", "AH0", "L", "OW1"] and tok.oov not in ids
+    # monotonic alignment search: a diagonal-dominant soft attention gives a staircase that covers every text position once
+    T, N = 9, 3
+    soft = torch.full((1, T, N), 0.05)
+    for t in range(T):
+        soft[0, t, t * N // T] = 0.9
+    hard = binarize_attention(soft, torch.tensor([N]), torch.tensor([T]))
+    assert hard.sum(2).tolist() == [[1.0] * T] and hard.sum(1).tolist() == [[3.0, 3.0, 3.0]]
+    out, lens = regulate_len(torch.tensor([[2.0, 0.0, 3.0]]), torch.arange(3.0).view(1, 3, 1))
+    assert lens.tolist() == [5] and out[0, :, 0].tolist() == [0.0, 0.0, 2.0, 2.0, 2.0]
+    torch.manual_seed(0)
+    cfg = OmegaConf.create({"n_symbols": tok.vocab_size, "symbols_embedding_dim": 32, "d_inner": 64, "encoder_layers": 1, "decoder_layers": 1,
+                            "n_mel_channels": 20, "sample_rate": 8000, "n_fft": 256, "hop_length": 64, "win_length": 256, "bin_loss_warmup_epochs": 0})
+    fp = FastPitchModel(cfg, tokenizer=tok)
+    text = torch.tensor([ids + [0] * 2, tok.text_to_ids("hello") + [0] * (len(ids) - 2)])
+    text_len = torch.tensor([len(ids), 4])
+    t = torch.arange(4000) / 8000.0
+    audio = torch.stack([torch.sin(2 * math.pi * 150 * t), torch.sin(2 * math.pi * 220 * t)]) * 0.5
+    f0 = FastPitchModel.estimate_pitch(audio, 64, 8000)
+    assert abs(float(f0[0, 10:40].median()) - 150) < 8 and abs(float(f0[1, 10:40].median()) - 220) < 12
+    loss = fp.training_step((text, text_len, audio, torch.tensor([4000, 3000])), 0)["loss"]
+    loss.backward()
+    assert math.isfinite(float(loss)) and fp.duration_predictor.fc.weight.grad is not None
+    mel = fp.generate_spectrogram(fp.parse("hello"))
+    assert mel.shape[:2] == (1, 20)
+    voc = HifiGanModel(OmegaConf.create({"sample_rate": 8000, "generator": {"input_dim": 20, "up_sample_rates": [4, 4, 4], "base_channels": 32,
+                                                                          "resblock_kernel_sizes": [3]},
+                                         "discriminator": {"periods": [2, 3], "stft_resolutions": [[256, 64, 256]]},
+                                         "mel": {"n_fft": 256, "hop": 64, "win": 256}}))
+    voc.configure_optimizers()
+    wav = voc.convert_spectrogram_to_audio(torch.randn(1, 20, 10))
+    assert wav.shape == (1, 640)
+    vl = voc.training_step((audio[:, :2048], torch.tensor([2048, 2048])), 0)["loss"]
+    assert math.isfinite(float(vl))
+    al = AlignerModel(OmegaConf.create({"n_symbols": tok.vocab_size, "symbols_embedding_dim": 16, "n_mel_channels": 80, "sample_rate": 8000}), tokenizer=tok)
+    l2 = al.training_step((text, text_len, audio, torch.tensor([4000, 3000])), 0)["loss"]
+    l2.backward()
+    assert math.isfinite(float(l2))
