@@ -110,6 +110,9 @@ class ParamArena:
             return None
         shape = (sum(p.shape[0] for p in params),) + tail
         view = self.master[start:start + total].view(shape)
+        # autograd must see the stacked weight as a trainable leaf, or custom Functions skip its gradient (needs_input_grad);
+        # the gradient itself is written by the kernels into ``_grad_view``, never into ``view.grad``
+        view.requires_grad_(any(p.requires_grad for p in params))
         view._grad_view = self.grad[start:start + total].view(shape)
         if self.lowp is not None:
             view._lowp = self.lowp[start:start + total].view(shape)

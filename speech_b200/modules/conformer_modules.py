@@ -202,6 +202,11 @@ class ConformerLayer(nn.Module, AdapterModuleMixin, AccessMixin):
         return ops.layer_norm(x, ln.weight, ln.bias, ln.eps)
 
     def forward(self, x, att_mask=None, pos_emb=None, pad_mask=None, cache_last_channel=None, cache_last_time=None):
+        if cache_last_channel is None and cache_last_time is None and x.is_cuda and not self.is_adapter_available() \
+                and not self.is_access_enabled(getattr(self, "model_guid", None)):
+            out = ops.conformer_layer(self, x, att_mask, pos_emb, pad_mask)   # one native call for the whole layer
+            if out is not None:
+                return out
         # dropout on the module outputs is fused into the epilogue of each module's last GEMM: residual + dropout(out)
         p_out = self.dropout.p if self.training else 0.0
         residual = self.feed_forward1(self._ln(self.norm_feed_forward1, x), residual=x, alpha=self.fc_factor)

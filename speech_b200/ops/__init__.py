@@ -156,6 +156,16 @@ def conv_module_core(g, dw_weight, dw_bias, norm_type, norm_weight, norm_bias, r
                                       cache_drop_size, bn_stats_reduce)
 
 
+def conformer_layer(layer, x, att_mask=None, pos_emb=None, pad_mask=None):
+    """Whole Conformer layer (forward and backward each issued by one native call); ``None`` when the layer's configuration
+    or this call is outside the executor's envelope and the caller should run the per-op path."""
+    if not _use_native(x) or x.dtype != torch.bfloat16:
+        return None
+    from . import native_layer
+
+    return native_layer.conformer_layer(layer, x, att_mask, pos_emb, pad_mask)
+
+
 def lstm(x, weights, h0=None, c0=None, num_layers=1, dropout=0.0, training=False):
     if _use_native(x) and x.dtype == torch.bfloat16 and not (dropout > 0 and training) and hasattr(_nat(), "lstm"):
         return _nat().lstm(x, weights, h0, c0, num_layers)

@@ -59,7 +59,7 @@ __global__ void layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const
                                      const float* __restrict__ gamma, const float* __restrict__ mean,
                                      const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx,
                                      float* __restrict__ dgamma, float* __restrict__ dbeta, int rows, int D,
-                                     int rows_per_block) {
+                                     int rows_per_block, const __nv_bfloat16* __restrict__ dres) {
   extern __shared__ float sh[];  // [2*D]
   float* sg = sh;
   float* sb = sh + D;
@@ -97,13 +97,17 @@ __global__ void layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const
       const __nv_bfloat162* hx = reinterpret_cast<const __nv_bfloat162*>(&rx);
       const __nv_bfloat162* hg = reinterpret_cast<const __nv_bfloat162*>(&rg);
       __align__(16) __nv_bfloat162 o[4];
+      uint4 rr = make_uint4(0u, 0u, 0u, 0u);  // bf16 zeros
+      if (dres) rr = *reinterpret_cast<const uint4*>(dres + (long long)row * D + i);
+      const __nv_bfloat162* hr = reinterpret_cast<const __nv_bfloat162*>(&rr);
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         float2 fx = __bfloat1622float2(hx[u]), fg = __bfloat1622float2(hg[u]);
+        const float2 fr = __bfloat1622float2(hr[u]);
         const int c = i + 2 * u;
         float xh0 = (fx.x - mu) * rs, xh1 = (fx.y - mu) * rs;
         float g0 = fg.x * gamma[c], g1 = fg.y * gamma[c + 1];
-        o[u] = __floats2bfloat162_rn(rs * (g0 - s1 - xh0 * s2), rs * (g1 - s1 - xh1 * s2));
+        o[u] = __floats2bfloat162_rn(rs * (g0 - s1 - xh0 * s2) + fr.x, rs * (g1 - s1 - xh1 * s2) + fr.y);
         atomicAdd(&sg[c], fg.x * xh0);
         atomicAdd(&sg[c + 1], fg.y * xh1);
         atomicAdd(&sb[c], fg.x);
@@ -125,7 +129,7 @@ template <int NCH>
 __global__ void __launch_bounds__(256) layernorm_bwd_reg_kernel(
     const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
     const float* __restrict__ mean, const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma,
-    float* __restrict__ dbeta, int rows, int rows_per_block) {
+    float* __restrict__ dbeta, int rows, int rows_per_block, const __nv_bfloat16* __restrict__ dres) {
   constexpr int D = NCH * 256;
   __shared__ float sg[D];
   __shared__ float sb[D];
@@ -181,10 +185,14 @@ __global__ void __launch_bounds__(256) layernorm_bwd_reg_kernel(
 #pragma unroll
     for (int j = 0; j < NCH; ++j) {
       __align__(16) __nv_bfloat162 o[4];
+      uint4 rr = make_uint4(0u, 0u, 0u, 0u);  // bf16 zeros
+      if (dres) rr = *reinterpret_cast<const uint4*>(dres + (long long)row * D + j * 256 + lane * 8);
+      const __nv_bfloat162* hr = reinterpret_cast<const __nv_bfloat162*>(&rr);
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const float a = rs * (g[j][2 * u] * gam[j][2 * u] - s1 - xh[j][2 * u] * s2);
-        const float b = rs * (g[j][2 * u + 1] * gam[j][2 * u + 1] - s1 - xh[j][2 * u + 1] * s2);
+        const float2 fr = __bfloat1622float2(hr[u]);
+        const float a = rs * (g[j][2 * u] * gam[j][2 * u] - s1 - xh[j][2 * u] * s2) + fr.x;
+        const float b = rs * (g[j][2 * u + 1] * gam[j][2 * u + 1] - s1 - xh[j][2 * u + 1] * s2) + fr.y;
         o[u] = __floats2bfloat162_rn(a, b);
       }
       *reinterpret_cast<uint4*>(dr + j * 256 + lane * 8) = *reinterpret_cast<const uint4*>(o);
@@ -325,8 +333,9 @@ SB_API int sb_layernorm_fwd(const void* x, const float* gamma, const float* beta
   return (int)cudaGetLastError();
 }
 
-SB_API int sb_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd, void* dx,
-                            float* dgamma, float* dbeta, int rows, int D, cudaStream_t stream) {
+// dx = LayerNorm backward (+ dres when given: the gradient that reaches the same tensor through the residual branch).
+SB_API int sb_layernorm_bwd_res(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd, void* dx,
+                                float* dgamma, float* dbeta, const void* dres, int rows, int D, cudaStream_t stream) {
   if (D % 8 != 0 || rows <= 0 || D > 5632) return -1;  // 2*D floats of shared memory
   const int blocks = min(rows, 2 * sb_num_sms());
   const int rpb = (rows + blocks - 1) / blocks;
@@ -334,17 +343,24 @@ SB_API int sb_layernorm_bwd(const void* dy, const void* x, const float* gamma, c
   if (D % 256 == 0 && D <= 1024) {
     const __nv_bfloat16 *gdy = (const __nv_bfloat16*)dy, *gx = (const __nv_bfloat16*)x;
     __nv_bfloat16* gdx = (__nv_bfloat16*)dx;
+    const __nv_bfloat16* gres = (const __nv_bfloat16*)dres;
     switch (D / 256) {
-      case 1: layernorm_bwd_reg_kernel<1><<<nblocks, 256, 0, stream>>>(gdy, gx, gamma, mean, rstd, gdx, dgamma, dbeta, rows, rpb); break;
-      case 2: layernorm_bwd_reg_kernel<2><<<nblocks, 256, 0, stream>>>(gdy, gx, gamma, mean, rstd, gdx, dgamma, dbeta, rows, rpb); break;
-      case 3: layernorm_bwd_reg_kernel<3><<<nblocks, 256, 0, stream>>>(gdy, gx, gamma, mean, rstd, gdx, dgamma, dbeta, rows, rpb); break;
-      default: layernorm_bwd_reg_kernel<4><<<nblocks, 256, 0, stream>>>(gdy, gx, gamma, mean, rstd, gdx, dgamma, dbeta, rows, rpb); break;
+      case 1: layernorm_bwd_reg_kernel<1><<<nblocks, 256, 0, stream>>>(gdy, gx, gamma, mean, rstd, gdx, dgamma, dbeta, rows, rpb, gres); break;
+      case 2: layernorm_bwd_reg_kernel<2><<<nblocks, 256, 0, stream>>>(gdy, gx, gamma, mean, rstd, gdx, dgamma, dbeta, rows, rpb, gres); break;
+      case 3: layernorm_bwd_reg_kernel<3><<<nblocks, 256, 0, stream>>>(gdy, gx, gamma, mean, rstd, gdx, dgamma, dbeta, rows, rpb, gres); break;
+      default: layernorm_bwd_reg_kernel<4><<<nblocks, 256, 0, stream>>>(gdy, gx, gamma, mean, rstd, gdx, dgamma, dbeta, rows, rpb, gres); break;
     }
     return (int)cudaGetLastError();
   }
   layernorm_bwd_kernel<<<nblocks, 256, 2 * D * sizeof(float), stream>>>(
-      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, mean, rstd, (__nv_bfloat16*)dx, dgamma, dbeta, rows, D, rpb);
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, mean, rstd, (__nv_bfloat16*)dx, dgamma, dbeta, rows, D, rpb,
+      (const __nv_bfloat16*)dres);
   return (int)cudaGetLastError();
+}
+
+SB_API int sb_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd, void* dx,
+                            float* dgamma, float* dbeta, int rows, int D, cudaStream_t stream) {
+  return sb_layernorm_bwd_res(dy, x, gamma, mean, rstd, dx, dgamma, dbeta, nullptr, rows, D, stream);
 }
 
 SB_API int sb_adamw(float* p, const float* g, float* m, float* v, void* lowp, long long n, float lr, float beta1, float beta2,

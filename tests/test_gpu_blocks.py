@@ -143,3 +143,94 @@ def test_conformer_layer_native_vs_eager():
             bad.append((n, e))
     assert not bad, bad
     ops.native.check_status()
+
+
+def _arena_layer(d, H, dropout, seed=5):
+    from speech_b200.core.optim.fused_adamw import FusedAdamW
+    from speech_b200.modules.conformer_modules import ConformerLayer
+
+    torch.manual_seed(seed)
+    layer = ConformerLayer(d_model=d, d_ff=4 * d, n_heads=H, conv_kernel_size=9, dropout=dropout, dropout_att=dropout).cuda()
+    with torch.no_grad():
+        layer.self_attn.pos_bias_u.normal_(std=0.1)
+        layer.self_attn.pos_bias_v.normal_(std=0.1)
+    fusion = [fg for m in layer.modules() if hasattr(m, "arena_fusion_groups") for fg in m.arena_fusion_groups()]
+    opt = FusedAdamW(layer.parameters(), lr=1e-3, fusion_groups=fusion)
+    return layer.train(), opt
+
+
+@pytest.mark.parametrize("dropout", [0.0, 0.1])
+def test_conformer_layer_executor_matches_per_op_path_and_fp32_reference(dropout, monkeypatch):
+    """The one-call-per-layer executor against (a) the per-op kernel path with identical dropout seeds and (b) fp32 eager math."""
+    import copy
+
+    from speech_b200 import ops
+    from speech_b200.modules.attention import RelPositionalEncoding
+    from speech_b200.ops import native as N
+    from speech_b200.ops import native_blocks as NB
+    from speech_b200.ops import native_layer
+
+    d, H, T, B = 256, 4, 61, 3
+    layer, opt = _arena_layer(d, H, dropout)
+    pe = RelPositionalEncoding(d, 0.0)
+    pe.extend_pe(T, "cuda")
+    x = torch.randn(B, T, d, device="cuda")
+    _, pos = pe(x)
+    lens = torch.tensor([T, T - 9, T - 20], device="cuda")
+    pad = torch.arange(T, device="cuda")[None, :] >= lens[:, None]
+    att = pad[:, None, :] | pad[:, :, None]
+    wr = torch.randn(B, T, d, device="cuda")
+
+    def run(executor: bool):
+        monkeypatch.setenv("SPEECH_B200_LAYER_EXECUTOR", "1" if executor else "0")
+        N._dropout_counter[0], NB._seed_counter[0] = 0x5EED5EED, 0x1234567
+        layer.conv.batch_norm.reset_running_stats()
+        opt.zero_grad()
+        xb = x.to(torch.bfloat16).requires_grad_(True)
+        before = N.launch_count
+        with ops.compute_dtype(torch.bfloat16):
+            y = layer(xb, att_mask=att, pos_emb=pos, pad_mask=pad)
+        (y.float() * wr).sum().backward()
+        torch.cuda.synchronize()
+        return (y.detach().float(), xb.grad.float().clone(), {n: p.grad.clone() for n, p in layer.named_parameters()},
+                layer.conv.batch_norm.running_var.clone(), N.launch_count - before)
+
+    y0, gx0, g0, rv0, _ = run(False)
+    y1, gx1, g1, rv1, launches = run(True)
+    assert native_layer._packs.get(layer) is not None and launches > 40, "the executor did not run"
+    # same kernels, order and dropout seeds; BatchNorm statistics are accumulated with atomics, so equality is to rounding
+    assert _rel_err(y1, y0) < 0.01
+    assert torch.allclose(rv0, rv1)
+    assert _rel_err(gx1, gx0) < 0.02
+    scale = max(float(g.abs().max()) for g in g0.values())
+    # analytically-zero gradients (key bias under the softmax) are rounding noise in both paths: absolute floor of 1% of the largest
+    bad = [(n, _rel_err(g1[n], g0[n], floor=1e-2 * scale)) for n in g0 if _rel_err(g1[n], g0[n], floor=1e-2 * scale) > 0.03]
+    assert not bad, bad
+    if dropout == 0.0:
+        ref_layer = copy.deepcopy(layer).float()
+        ref_layer.conv.batch_norm.reset_running_stats()
+        ref_layer.zero_grad()
+        x32 = x.to(torch.bfloat16).float().requires_grad_(True)
+        with ops.eager_mode():
+            yr = ref_layer(x32, att_mask=att, pos_emb=pos, pad_mask=pad)
+        (yr * wr).sum().backward()
+        assert _rel_err(y1, yr) < 0.05 and _rel_err(gx1, x32.grad) < 0.1
+        rscale = max(float(p.grad.abs().max()) for p in ref_layer.parameters())
+        bad = []
+        for n, p in ref_layer.named_parameters():
+            if float(p.grad.abs().max()) < 1e-4 * rscale:
+                if float(g1[n].abs().max()) > 0.02 * rscale:
+                    bad.append((n, float(g1[n].abs().max())))
+            elif _rel_err(g1[n], p.grad) > 0.12:
+                bad.append((n, _rel_err(g1[n], p.grad)))
+        assert not bad, bad
+    # inference through the executor equals the per-op path in eval mode
+    layer.eval()
+    with torch.no_grad(), ops.compute_dtype(torch.bfloat16):
+        monkeypatch.setenv("SPEECH_B200_LAYER_EXECUTOR", "0")
+        e0 = layer(x.to(torch.bfloat16), att_mask=att, pos_emb=pos, pad_mask=pad)
+        monkeypatch.setenv("SPEECH_B200_LAYER_EXECUTOR", "1")
+        e1 = layer(x.to(torch.bfloat16), att_mask=att, pos_emb=pos, pad_mask=pad)
+    assert torch.equal(e0, e1)
+    ops.native.check_status()
+    assert native_layer.enabled()
