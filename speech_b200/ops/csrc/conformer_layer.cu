@@ -14,6 +14,7 @@
 #include "gemm_api.h"
 
 #include <cstdint>
+#include <cstdio>
 #include <cstring>
 
 SB_API int sb_layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd, int rows,
@@ -99,6 +100,11 @@ struct SbConformerLayerArgs {
   // backward only
   const void* dout;    // [B*T, d] bf16
   void* dx;            // [B*T, d] bf16 (null: the input needs no gradient)
+  // profiling (host memory, optional): when prof_ms is set, the call records a CUDA event after every launch, waits for the
+  // last one and stores the device time of launch i in prof_ms[i] (milliseconds); at most prof_cap entries
+  float* prof_ms;
+  int prof_cap;
+  int pad_;
 };
 
 namespace {
@@ -211,16 +217,53 @@ SbGemmArgs gemm_defaults() {
   return g;
 }
 
+constexpr int kMaxProf = 160;
+char g_prof_names[kMaxProf][40];   // names of the launches of the last profiled call (profiling is a single-threaded debug aid)
+
 struct Exec {
   cudaStream_t stream;
   int launches = 0;
   int step = 0;     // index of the call that failed, for the error code
   int rc = 0;
+  bool prof = false;
+  cudaEvent_t ev[kMaxProf + 1];
+  int nev = 0;
+  const char* tag = "";   // name of the layer part being issued (profile labels only)
+  const char* sub = "";
+  void begin(bool profile) {
+    prof = profile;
+    if (prof && cudaEventCreate(&ev[0]) == cudaSuccess) {
+      cudaEventRecord(ev[0], stream);
+      nev = 1;
+    } else {
+      prof = false;
+    }
+  }
   bool run(int code) {
     ++step;
     ++launches;
+    if (prof && nev <= kMaxProf && cudaEventCreate(&ev[nev]) == cudaSuccess) {
+      cudaEventRecord(ev[nev], stream);
+      snprintf(g_prof_names[nev - 1], sizeof(g_prof_names[0]), "%s%s", tag, sub);
+      ++nev;
+    }
+    sub = "";
     if (code != 0 && rc == 0) rc = code < 0 ? -(step * 1000 - code) : -(step * 1000 + 999);
     return rc == 0;
+  }
+  void finish(float* out_ms, int cap) {
+    if (!prof) return;
+    if (nev > 1) cudaEventSynchronize(ev[nev - 1]);
+    for (int i = 1; i < nev; ++i) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, ev[i - 1], ev[i]);
+      if (out_ms && i - 1 < cap) out_ms[i - 1] = ms;
+    }
+    for (int i = 0; i < nev; ++i) cudaEventDestroy(ev[i]);
+  }
+  bool named(const char* label, int code) {
+    sub = label;
+    return run(code);
   }
   // y[M, N] = epilogue(x[M, K] @ w[N, K]^T)
   bool linear(const bf16* x, long long ldx, const SbLinearParams& p, bf16* y, int M, int N, int K, int act, bf16* pre,
@@ -233,36 +276,50 @@ struct Exec {
     g.D_pre = pre; g.ldp = pre ? N : 0;
     g.alpha = alpha; g.act = act;
     g.drop_p = drop_p; g.drop_seed = drop_p > 0.f ? seed : 0ull;
+    char label[32];
+    snprintf(label, sizeof(label), ".linear %dx%d", N, K);
+    sub = label;
     return run(sb_gemm_bf16(&g, stream));
   }
   // dx[M, K] = dz[M, N] @ w[N, K];  gw[N, K] += dz^T x;  gb[N] += column sums of dz
   bool linear_bwd(const bf16* dz, long long ld_dz, const bf16* x, long long ldx, const SbLinearParams& p, bf16* dx, int M, int N,
                   int K) {
+    char label[32];
     if (dx) {
       SbGemmArgs g = gemm_defaults();
       g.A = dz; g.B = p.w; g.M = M; g.N = K; g.K = N; g.lda = ld_dz; g.b_mn_major = 1; g.ldb = K;
       g.D = dx; g.ldd = K;
+      snprintf(label, sizeof(label), ".dgrad %dx%d", N, K);
+      sub = label;
       if (!run(sb_gemm_bf16(&g, stream))) return false;
     }
     if (p.gw) {
       SbGemmArgs g = gemm_defaults();
       g.A = dz; g.B = x; g.M = N; g.N = K; g.K = M; g.a_mn_major = 1; g.lda = ld_dz; g.b_mn_major = 1; g.ldb = ldx;
       g.D = p.gw; g.d_is_f32 = 1; g.ldd = K; g.beta = 1.f;
+      snprintf(label, sizeof(label), ".wgrad %dx%d", N, K);
+      sub = label;
       if (!run(sb_gemm_bf16(&g, stream))) return false;
     }
-    if (p.gb && !run(sb_colsum_bf16(dz, ld_dz, M, N, p.gb, stream))) return false;
+    if (p.gb) {
+      sub = ".bgrad";
+      if (!run(sb_colsum_bf16(dz, ld_dz, M, N, p.gb, stream))) return false;
+    }
     return true;
   }
   bool ln(const bf16* x, const SbNormParams& p, bf16* y, float* mean, float* rstd, int rows, int D) {
+    sub = ".ln";
     return run(sb_layernorm_fwd(x, p.w, p.b, y, mean, rstd, rows, D, p.eps, stream));
   }
   bool ln_bwd(const bf16* dy, const bf16* x, const SbNormParams& p, const float* mean, const float* rstd, bf16* dx,
               const bf16* dres, int rows, int D) {
+    sub = ".ln_bwd";
     return run(sb_layernorm_bwd_res(dy, x, p.w, mean, rstd, dx, p.gw, p.gb, dres, rows, D, stream));
   }
-  bool zero(void* ptr, size_t bytes) { return run((int)cudaMemsetAsync(ptr, 0, bytes, stream)); }
+  bool zero(void* ptr, size_t bytes) { sub = ".memset"; return run((int)cudaMemsetAsync(ptr, 0, bytes, stream)); }
   bool accum(float* out, const float* a, float ca, const float* b, float cb, int n) {
     axpby_accum_kernel<<<(n + 255) / 256, 256, 0, stream>>>(out, a, ca, b, cb, n);
+    sub = ".accum";
     return run((int)cudaGetLastError());
   }
 };
@@ -289,6 +346,9 @@ SB_API int sb_conformer_layer_sizes(const SbConformerLayerArgs* a, long long* sa
   return 0;
 }
 
+// Label of launch i of the most recent profiled call ("" beyond its end).
+SB_API const char* sb_conformer_layer_prof_name(int i) { return (i >= 0 && i < kMaxProf) ? g_prof_names[i] : ""; }
+
 SB_API int sb_conformer_layer_args_size() { return (int)sizeof(SbConformerLayerArgs); }
 
 SB_API int sb_conformer_layer_fwd(SbConformerLayerArgs* a, cudaStream_t stream) {
@@ -299,6 +359,7 @@ SB_API int sb_conformer_layer_fwd(SbConformerLayerArgs* a, cudaStream_t stream) 
   if (layout_fwd_scratch(*a, a->scratch, f) > a->scratch_bytes || !a->scratch) return -3;
   Exec e;
   e.stream = stream;
+  e.begin(a->prof_ms != nullptr);
   const int B = a->B, T = a->T, P = a->P, d = a->d, F = a->dff, H = a->H, dk = d / H;
   const int R = B * T;
   const bool tr = a->training != 0;
@@ -308,29 +369,31 @@ SB_API int sb_conformer_layer_fwd(SbConformerLayerArgs* a, cudaStream_t stream) 
   const long long HD = d, QS = 3LL * d;
   bool ok = true;
   // ---- feed-forward 1
+  e.tag = "ff1";
   ok = ok && e.ln(x, a->ln_ff1, s.h1, s.mean[0], s.rstd[0], R, d);
   ok = ok && e.linear(s.h1, d, a->ff1a, s.a1, R, F, d, /*swish*/ 2, s.pre1, nullptr, 1.f, p_ff, a->seeds[0]);
   ok = ok && e.linear(s.a1, F, a->ff1b, s.res1, R, d, F, 0, nullptr, x, a->fc_factor, p_ff, a->seeds[1]);
   // ---- self-attention
+  e.tag = "att";
   ok = ok && e.ln(s.res1, a->ln_att, s.h2, s.mean[1], s.rstd[1], R, d);
   ok = ok && e.linear(s.h2, d, a->qkv, s.qkv, R, 3 * d, d, 0, nullptr, nullptr, 1.f, 0.f, 0);
   ok = ok && e.linear((const bf16*)a->pos_emb, d, a->pos, s.p, P, d, d, 0, nullptr, nullptr, 1.f, 0.f, 0);
-  ok = ok && e.run(sb_add_pos_bias(s.qkv, QS, a->pos_u, a->pos_v, s.qu, s.qv, R, d, stream));
+  ok = ok && e.named(".add_pos_bias", sb_add_pos_bias(s.qkv, QS, a->pos_u, a->pos_v, s.qu, s.qv, R, d, stream));
   if (ok) {  // AC = (q + u) k^T
     SbGemmArgs g = gemm_defaults();
     g.A = s.qu; g.B = s.qkv + d; g.M = T; g.N = T; g.K = dk; g.lda = HD; g.ldb = QS;
     g.batch0 = H; g.batch1 = B; g.a_bs0 = dk; g.a_bs1 = (long long)T * HD; g.b_bs0 = dk; g.b_bs1 = (long long)T * QS;
     g.D = f.AC; g.d_is_f32 = 1; g.ldd = ldac; g.d_bs0 = (long long)T * ldac; g.d_bs1 = (long long)H * T * ldac;
-    ok = e.run(sb_gemm_bf16(&g, stream));
+    ok = e.named(".gemm_AC", sb_gemm_bf16(&g, stream));
   }
   if (ok) {  // BD = (q + v) p^T
     SbGemmArgs g = gemm_defaults();
     g.A = s.qv; g.B = s.p; g.M = T; g.N = P; g.K = dk; g.lda = HD; g.ldb = HD;
     g.batch0 = H; g.batch1 = B; g.a_bs0 = dk; g.a_bs1 = (long long)T * HD; g.b_bs0 = dk; g.b_bs1 = 0;
     g.D = f.BD; g.d_is_f32 = 1; g.ldd = ldbd; g.d_bs0 = (long long)T * ldbd; g.d_bs1 = (long long)H * T * ldbd;
-    ok = e.run(sb_gemm_bf16(&g, stream));
+    ok = e.named(".gemm_BD", sb_gemm_bf16(&g, stream));
   }
-  ok = ok && e.run(sb_relpos_softmax_fwd(f.AC, f.BD, a->att_mask, a->att_mask_bstride, s.Pm, p_att > 0.f ? s.Pd : nullptr, B, H, T,
+  ok = ok && e.named(".relpos_softmax_fwd", sb_relpos_softmax_fwd(f.AC, f.BD, a->att_mask, a->att_mask_bstride, s.Pm, p_att > 0.f ? s.Pd : nullptr, B, H, T,
                                          T, ldac, ldbd, ldp, 1.f / sqrtf((float)dk), p_att, a->seeds[2], stream));
   if (ok) {  // ctx = P v
     const bf16* Pu = (p_att > 0.f) ? s.Pd : s.Pm;
@@ -339,24 +402,28 @@ SB_API int sb_conformer_layer_fwd(SbConformerLayerArgs* a, cudaStream_t stream) 
     g.batch0 = H; g.batch1 = B; g.a_bs0 = (long long)T * ldp; g.a_bs1 = (long long)H * T * ldp; g.b_bs0 = dk;
     g.b_bs1 = (long long)T * QS;
     g.D = s.ctx; g.ldd = HD; g.d_bs0 = dk; g.d_bs1 = (long long)T * HD;
-    ok = e.run(sb_gemm_bf16(&g, stream));
+    ok = e.named(".gemm_ctx", sb_gemm_bf16(&g, stream));
   }
   ok = ok && e.linear(s.ctx, d, a->out_proj, s.res2, R, d, d, 0, nullptr, s.res1, 1.f, p_out, a->seeds[3]);
   // ---- convolution module
+  e.tag = "conv";
   ok = ok && e.ln(s.res2, a->ln_conv, s.h3, s.mean[2], s.rstd[2], R, d);
   ok = ok && e.linear(s.h3, d, a->pw1, s.g, R, 2 * d, d, 0, nullptr, nullptr, 1.f, 0.f, 0);
   if (tr) ok = ok && e.zero(f.stats, (2 * d + 1) * sizeof(float));
-  ok = ok && e.run(sb_glu_dwconv_fwd(s.g, a->pad_mask, a->dw_w, a->dw_b, s.y, tr ? f.stats : nullptr, B, T, d, a->conv_k,
+  ok = ok && e.named(".glu_dwconv_fwd", sb_glu_dwconv_fwd(s.g, a->pad_mask, a->dw_w, a->dw_b, s.y, tr ? f.stats : nullptr, B, T, d, a->conv_k,
                                      a->conv_left, stream));
-  ok = ok && e.run(sb_bn_finalize(tr ? f.stats : nullptr, (float)R, nullptr, s.mean_rstd, a->bn_mean, a->bn_var, d, a->bn_eps,
+  ok = ok && e.named(".bn_finalize", sb_bn_finalize(tr ? f.stats : nullptr, (float)R, nullptr, s.mean_rstd, a->bn_mean, a->bn_var, d, a->bn_eps,
                                   a->bn_momentum, tr ? 1 : 0, stream));
-  ok = ok && e.run(sb_bn_silu_fwd(s.y, s.mean_rstd, a->bn_w, a->bn_b, s.s, R, d, stream));
+  ok = ok && e.named(".bn_silu_fwd", sb_bn_silu_fwd(s.y, s.mean_rstd, a->bn_w, a->bn_b, s.s, R, d, stream));
   ok = ok && e.linear(s.s, d, a->pw2, s.res3, R, d, d, 0, nullptr, s.res2, 1.f, p_out, a->seeds[4]);
   // ---- feed-forward 2 and the output norm
+  e.tag = "ff2";
   ok = ok && e.ln(s.res3, a->ln_ff2, s.h4, s.mean[3], s.rstd[3], R, d);
   ok = ok && e.linear(s.h4, d, a->ff2a, s.a2, R, F, d, 2, s.pre2, nullptr, 1.f, p_ff, a->seeds[5]);
   ok = ok && e.linear(s.a2, F, a->ff2b, s.res4, R, d, F, 0, nullptr, s.res3, a->fc_factor, p_ff, a->seeds[6]);
+  e.tag = "out";
   ok = ok && e.ln(s.res4, a->ln_out, (bf16*)a->out, s.mean[4], s.rstd[4], R, d);
+  e.finish(a->prof_ms, a->prof_cap);
   a->launches = e.launches;
   return e.rc;
 }
@@ -370,6 +437,7 @@ SB_API int sb_conformer_layer_bwd(SbConformerLayerArgs* a, cudaStream_t stream) 
   if (!a->dout) return -4;
   Exec e;
   e.stream = stream;
+  e.begin(a->prof_ms != nullptr);
   const int B = a->B, T = a->T, P = a->P, d = a->d, F = a->dff, H = a->H, dk = d / H;
   const int R = B * T;
   const bool tr = a->training != 0;
@@ -384,31 +452,34 @@ SB_API int sb_conformer_layer_bwd(SbConformerLayerArgs* a, cudaStream_t stream) 
   auto ff_bwd = [&](const bf16* G_in, bf16* G_out, const bf16* res_in, const bf16* h, const bf16* pre, const bf16* act_out,
                     const SbNormParams& norm, const SbLinearParams& la, const SbLinearParams& lb, const float* mean,
                     const float* rstd, unsigned long long seed_inner, unsigned long long seed_out) {
-    bool k = e.run(sb_scale_dact_dropout(G_in, d, nullptr, w.dzd, R, d, 0, a->fc_factor, p_ff, seed_out, stream));
+    bool k = e.named(".scale_dact_dropout", sb_scale_dact_dropout(G_in, d, nullptr, w.dzd, R, d, 0, a->fc_factor, p_ff, seed_out, stream));
     k = k && e.linear_bwd(w.dzd, d, act_out, F, lb, w.big, R, d, F);
-    k = k && e.run(sb_scale_dact_dropout(w.big, F, pre, w.big, R, F, 2, 1.f, p_ff, seed_inner, stream));
+    k = k && e.named(".scale_dact_dropout", sb_scale_dact_dropout(w.big, F, pre, w.big, R, F, 2, 1.f, p_ff, seed_inner, stream));
     k = k && e.linear_bwd(w.big, F, h, d, la, w.dh, R, F, d);
     k = k && e.ln_bwd(w.dh, res_in, norm, mean, rstd, G_out, G_in, R, d);
     return k;
   };
 
   // ---- output norm and feed-forward 2
+  e.tag = "out";
   ok = ok && e.ln_bwd((const bf16*)a->dout, s.res4, a->ln_out, s.mean[4], s.rstd[4], w.GA, nullptr, R, d);
+  e.tag = "ff2";
   ok = ok && ff_bwd(w.GA, w.GB, s.res3, s.h4, s.pre2, s.a2, a->ln_ff2, a->ff2a, a->ff2b, s.mean[3], s.rstd[3], a->seeds[5],
                     a->seeds[6]);
   // ---- convolution module: gradient of res3 is in GB
+  e.tag = "conv";
   {
     const bf16* dz = w.GB;
     if (p_out > 0.f) {
-      ok = ok && e.run(sb_scale_dact_dropout(w.GB, d, nullptr, w.dzd, R, d, 0, 1.f, p_out, a->seeds[4], stream));
+      ok = ok && e.named(".scale_dact_dropout", sb_scale_dact_dropout(w.GB, d, nullptr, w.dzd, R, d, 0, 1.f, p_out, a->seeds[4], stream));
       dz = w.dzd;
     }
     bf16* ds = w.dh;
     ok = ok && e.linear_bwd(dz, d, s.s, d, a->pw2, ds, R, d, d);
     ok = ok && e.zero(w.sums, 2 * d * sizeof(float));
-    ok = ok && e.run(sb_bn_silu_bwd_stats(ds, s.y, s.mean_rstd, a->bn_w, a->bn_b, w.sums, R, d, stream));
+    ok = ok && e.named(".bn_silu_bwd_stats", sb_bn_silu_bwd_stats(ds, s.y, s.mean_rstd, a->bn_w, a->bn_b, w.sums, R, d, stream));
     bf16* dg = w.big;
-    ok = ok && e.run(sb_dwconv_glu_bwd(ds, s.y, s.g, a->pad_mask, a->dw_w, s.mean_rstd, a->bn_w, a->bn_b, w.sums, (float)R, nullptr,
+    ok = ok && e.named(".dwconv_glu_bwd", sb_dwconv_glu_bwd(ds, s.y, s.g, a->pad_mask, a->dw_w, s.mean_rstd, a->bn_w, a->bn_b, w.sums, (float)R, nullptr,
                                        tr ? 1 : 0, dg, a->g_dw_w, a->g_dw_b, B, T, d, a->conv_k, a->conv_left, stream));
     if (a->g_bn_w) ok = ok && e.accum(a->g_bn_w, w.sums + d, 1.f, nullptr, 0.f, d);
     if (a->g_bn_b) ok = ok && e.accum(a->g_bn_b, w.sums, 1.f, nullptr, 0.f, d);
@@ -416,10 +487,11 @@ SB_API int sb_conformer_layer_bwd(SbConformerLayerArgs* a, cudaStream_t stream) 
     ok = ok && e.ln_bwd(w.dzd, s.res2, a->ln_conv, s.mean[2], s.rstd[2], w.GA, w.GB, R, d);
   }
   // ---- self-attention: gradient of res2 is in GA
+  e.tag = "att";
   {
     const bf16* dz = w.GA;
     if (p_out > 0.f) {
-      ok = ok && e.run(sb_scale_dact_dropout(w.GA, d, nullptr, w.dzd, R, d, 0, 1.f, p_out, a->seeds[3], stream));
+      ok = ok && e.named(".scale_dact_dropout", sb_scale_dact_dropout(w.GA, d, nullptr, w.dzd, R, d, 0, 1.f, p_out, a->seeds[3], stream));
       dz = w.dzd;
     }
     bf16* dctx = w.dh;
@@ -434,30 +506,30 @@ SB_API int sb_conformer_layer_bwd(SbConformerLayerArgs* a, cudaStream_t stream) 
       g.A = Pu; g.B = dctx; g.M = T; g.N = dk; g.K = T; g.a_mn_major = 1; g.lda = ldp; g.b_mn_major = 1; g.ldb = HD;
       g.batch0 = H; g.batch1 = B; g.a_bs0 = pb0; g.a_bs1 = pb1; g.b_bs0 = dk; g.b_bs1 = (long long)T * HD;
       g.D = dV; g.ldd = QS; g.d_bs0 = dk; g.d_bs1 = (long long)T * QS;
-      ok = e.run(sb_gemm_bf16(&g, stream));
+      ok = e.named(".gemm_dV", sb_gemm_bf16(&g, stream));
     }
     if (ok) {  // dP = dO V^T
       SbGemmArgs g = gemm_defaults();
       g.A = dctx; g.B = vv; g.M = T; g.N = T; g.K = dk; g.lda = HD; g.ldb = QS;
       g.batch0 = H; g.batch1 = B; g.a_bs0 = dk; g.a_bs1 = (long long)T * HD; g.b_bs0 = dk; g.b_bs1 = (long long)T * QS;
       g.D = w.dPd; g.d_is_f32 = 1; g.ldd = lddp; g.d_bs0 = (long long)T * lddp; g.d_bs1 = (long long)H * T * lddp;
-      ok = e.run(sb_gemm_bf16(&g, stream));
+      ok = e.named(".gemm_dP", sb_gemm_bf16(&g, stream));
     }
-    ok = ok && e.run(sb_relpos_softmax_bwd(s.Pm, w.dPd, w.dAC, w.dBD, B, H, T, T, ldp, lddp, ldbd, 1.f / sqrtf((float)dk), p_att,
+    ok = ok && e.named(".relpos_softmax_bwd", sb_relpos_softmax_bwd(s.Pm, w.dPd, w.dAC, w.dBD, B, H, T, T, ldp, lddp, ldbd, 1.f / sqrtf((float)dk), p_att,
                                            a->seeds[2], stream));
     if (ok) {  // dK = dAC^T (q + u)
       SbGemmArgs g = gemm_defaults();
       g.A = w.dAC; g.B = s.qu; g.M = T; g.N = dk; g.K = T; g.a_mn_major = 1; g.lda = ldp; g.b_mn_major = 1; g.ldb = HD;
       g.batch0 = H; g.batch1 = B; g.a_bs0 = pb0; g.a_bs1 = pb1; g.b_bs0 = dk; g.b_bs1 = (long long)T * HD;
       g.D = dK; g.ldd = QS; g.d_bs0 = dk; g.d_bs1 = (long long)T * QS;
-      ok = e.run(sb_gemm_bf16(&g, stream));
+      ok = e.named(".gemm_dK", sb_gemm_bf16(&g, stream));
     }
     if (ok) {  // dQu = dAC K
       SbGemmArgs g = gemm_defaults();
       g.A = w.dAC; g.B = kk; g.M = T; g.N = dk; g.K = T; g.lda = ldp; g.b_mn_major = 1; g.ldb = QS;
       g.batch0 = H; g.batch1 = B; g.a_bs0 = pb0; g.a_bs1 = pb1; g.b_bs0 = dk; g.b_bs1 = (long long)T * QS;
       g.D = w.dQu; g.ldd = HD; g.d_bs0 = dk; g.d_bs1 = (long long)T * HD;
-      ok = e.run(sb_gemm_bf16(&g, stream));
+      ok = e.named(".gemm_dQu", sb_gemm_bf16(&g, stream));
     }
     if (ok) {  // dQ = dBD p + dQu
       SbGemmArgs g = gemm_defaults();
@@ -465,20 +537,20 @@ SB_API int sb_conformer_layer_bwd(SbConformerLayerArgs* a, cudaStream_t stream) 
       g.batch0 = H; g.batch1 = B; g.a_bs0 = bb0; g.a_bs1 = bb1; g.b_bs0 = dk; g.b_bs1 = 0;
       g.D = dQ; g.ldd = QS; g.d_bs0 = dk; g.d_bs1 = (long long)T * QS;
       g.residual = w.dQu; g.ldr = HD; g.r_bs0 = dk; g.r_bs1 = (long long)T * HD;
-      ok = e.run(sb_gemm_bf16(&g, stream));
+      ok = e.named(".gemm_dQ", sb_gemm_bf16(&g, stream));
     }
     if (ok && a->pos.gw) {  // dp = sum over the batch of dBD^T (q + v), then the positional projection's weight gradient
       SbGemmArgs g = gemm_defaults();
       g.A = w.dBD; g.B = s.qv; g.M = P; g.N = dk; g.K = T; g.a_mn_major = 1; g.lda = ldbd; g.b_mn_major = 1; g.ldb = HD;
       g.batch0 = H; g.batch1 = B; g.a_bs0 = bb0; g.a_bs1 = bb1; g.b_bs0 = dk; g.b_bs1 = (long long)T * HD;
       g.D = w.dp; g.ldd = HD; g.d_bs0 = dk; g.d_bs1 = 0; g.fold_batch1 = 1;
-      ok = e.run(sb_gemm_bf16(&g, stream));
+      ok = e.named(".gemm_dp", sb_gemm_bf16(&g, stream));
       ok = ok && e.linear_bwd(w.dp, d, (const bf16*)a->pos_emb, d, a->pos, nullptr, P, d, d);
     }
     if (a->g_pos_u || a->g_pos_v) {  // d(u) = colsum(dQu);  d(v) = colsum(dQ) - colsum(dQu)
       ok = ok && e.zero(w.su, 2 * (size_t)d * sizeof(float));
-      ok = ok && e.run(sb_colsum_bf16(w.dQu, HD, R, d, w.su, stream));
-      ok = ok && e.run(sb_colsum_bf16(dQ, QS, R, d, w.sq, stream));
+      ok = ok && e.named(".colsum_bf16", sb_colsum_bf16(w.dQu, HD, R, d, w.su, stream));
+      ok = ok && e.named(".colsum_bf16", sb_colsum_bf16(dQ, QS, R, d, w.sq, stream));
       if (a->g_pos_u) ok = ok && e.accum(a->g_pos_u, w.su, 1.f, nullptr, 0.f, d);
       if (a->g_pos_v) ok = ok && e.accum(a->g_pos_v, w.sq, 1.f, w.su, -1.f, d);
     }
@@ -486,8 +558,10 @@ SB_API int sb_conformer_layer_bwd(SbConformerLayerArgs* a, cudaStream_t stream) 
     ok = ok && e.ln_bwd(w.dzd, s.res1, a->ln_att, s.mean[1], s.rstd[1], w.GB, w.GA, R, d);
   }
   // ---- feed-forward 1: gradient of res1 is in GB; the layer input's gradient goes to dx (or to scratch when unused)
+  e.tag = "ff1";
   bf16* dx = a->dx ? (bf16*)a->dx : w.GA;
   ok = ok && ff_bwd(w.GB, dx, x, s.h1, s.pre1, s.a1, a->ln_ff1, a->ff1a, a->ff1b, s.mean[0], s.rstd[0], a->seeds[0], a->seeds[1]);
+  e.finish(a->prof_ms, a->prof_cap);
   a->launches = e.launches;
   return e.rc;
 }

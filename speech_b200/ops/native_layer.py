@@ -46,7 +46,7 @@ class SbConformerLayerArgs(ctypes.Structure):
         ("dw_w", _vp), ("dw_b", _vp), ("g_dw_w", _vp), ("g_dw_b", _vp),
         ("bn_w", _vp), ("bn_b", _vp), ("g_bn_w", _vp), ("g_bn_b", _vp), ("bn_mean", _vp), ("bn_var", _vp),
         ("out", _vp), ("saved", _vp), ("saved_bytes", _ll), ("scratch", _vp), ("scratch_bytes", _ll),
-        ("dout", _vp), ("dx", _vp),
+        ("dout", _vp), ("dx", _vp), ("prof_ms", ctypes.POINTER(_f)), ("prof_cap", _i), ("pad_", _i),
     ]
 
 
@@ -84,6 +84,27 @@ class _ConvertCache:
         if len(self.items) > self.n:
             self.items.pop(0)
         return out
+
+
+profile_sink: Optional[list] = None   # set to a list to collect (phase, [(label, ms), ...]) for every executor call
+_PROF_CAP = 160
+
+
+def _prof_begin(a):
+    if profile_sink is None:
+        a.prof_ms, a.prof_cap = None, 0
+        return None
+    buf = (_f * _PROF_CAP)()
+    a.prof_ms, a.prof_cap = ctypes.cast(buf, ctypes.POINTER(_f)), _PROF_CAP
+    return buf
+
+
+def _prof_end(phase: str, a, buf):
+    if buf is None:
+        return
+    name = _lib().sb_conformer_layer_prof_name
+    name.restype = ctypes.c_char_p
+    profile_sink.append((phase, [(name(i).decode(), float(buf[i])) for i in range(min(a.launches, _PROF_CAP))]))
 
 
 _masks = _ConvertCache()
@@ -256,7 +277,9 @@ class _ConformerLayerFn(torch.autograd.Function):
         a.out, a.saved, a.saved_bytes = out.data_ptr(), saved.data_ptr(), sv
         a.scratch, a.scratch_bytes = scratch.data_ptr(), scratch.numel()
         a.dout = a.dx = None
+        prof = _prof_begin(a)
         rc = _lib().sb_conformer_layer_fwd(ctypes.byref(a), N._stream())
+        _prof_end("forward", a, prof)
         N.launch_count += a.launches
         if rc != 0:
             raise RuntimeError(f"sb_conformer_layer_fwd failed with code {rc} (step {(-rc) // 1000}, code {(-rc) % 1000})")
@@ -286,7 +309,9 @@ class _ConformerLayerFn(torch.autograd.Function):
         a.saved, a.saved_bytes = ctx.saved_buf.data_ptr(), sv
         a.scratch, a.scratch_bytes = scratch.data_ptr(), scratch.numel()
         a.dout, a.dx, a.out = dout.data_ptr(), _ptr(dx), None
+        prof = _prof_begin(a)
         rc = _lib().sb_conformer_layer_bwd(ctypes.byref(a), N._stream())
+        _prof_end("backward", a, prof)
         N.launch_count += a.launches
         if rc != 0:
             raise RuntimeError(f"sb_conformer_layer_bwd failed with code {rc} (step {(-rc) // 1000}, code {(-rc) % 1000})")
@@ -312,8 +337,11 @@ def conformer_layer(layer, x: torch.Tensor, att_mask, pos_emb, pad_mask) -> Opti
     if pos_emb.shape[1] != 2 * T - 1 or B * T == 0:
         return None
     training = layer.training
-    need_grad = torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in layer.parameters()))
-    if need_grad and not all(p.requires_grad for p in layer.parameters()):
+    cached = _packs.get(layer)
+    params = cached.params if cached is not None else list(layer.parameters())   # walking the module tree costs ~50 us
+    trainable = sum(1 for p in params if p.requires_grad)
+    need_grad = torch.is_grad_enabled() and (x.requires_grad or trainable > 0)
+    if need_grad and trainable != len(params):
         return None
     pack = _get_pack(layer, need_grad)
     if pack is None:
