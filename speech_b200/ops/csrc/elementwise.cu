@@ -53,6 +53,63 @@ __global__ void layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const 
   }
 }
 
+// Register-resident forward for D = NCH * 256 (NCH <= 4): the row is read once, gamma / beta come in as float4.
+template <int NCH>
+__global__ void __launch_bounds__(256) layernorm_fwd_reg_kernel(
+    const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+    __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, float eps) {
+  constexpr int D = NCH * 256;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + (long long)row * D;
+  float v[NCH][8];
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(xr + j * 256 + lane * 8);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float2 f = __bfloat1622float2(h[u]);
+      v[j][2 * u] = f.x;
+      v[j][2 * u + 1] = f.y;
+      s += f.x + f.y;
+    }
+  }
+  const float mean = warp_sum(s) * (1.f / D);
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NCH; ++j)
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      v[j][u] -= mean;
+      ss += v[j][u] * v[j][u];
+    }
+  const float rstd = rsqrtf(warp_sum(ss) * (1.f / D) + eps);
+  if (lane == 0) {
+    if (mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  __nv_bfloat16* yr = y + (long long)row * D;
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int c = j * 256 + lane * 8;
+    const float4 g0 = *reinterpret_cast<const float4*>(gamma + c), g1 = *reinterpret_cast<const float4*>(gamma + c + 4);
+    float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
+    if (beta) {
+      b0 = *reinterpret_cast<const float4*>(beta + c);
+      b1 = *reinterpret_cast<const float4*>(beta + c + 4);
+    }
+    __align__(16) __nv_bfloat162 o[4];
+    o[0] = __floats2bfloat162_rn(v[j][0] * rstd * g0.x + b0.x, v[j][1] * rstd * g0.y + b0.y);
+    o[1] = __floats2bfloat162_rn(v[j][2] * rstd * g0.z + b0.z, v[j][3] * rstd * g0.w + b0.w);
+    o[2] = __floats2bfloat162_rn(v[j][4] * rstd * g1.x + b1.x, v[j][5] * rstd * g1.y + b1.y);
+    o[3] = __floats2bfloat162_rn(v[j][6] * rstd * g1.z + b1.z, v[j][7] * rstd * g1.w + b1.w);
+    *reinterpret_cast<uint4*>(yr + c) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
 // dx for one row per warp; per-block partial dgamma/dbeta accumulated in shared memory then atomically added
 // to fp32 [D] outputs (which the caller zeroes or which already hold earlier gradient contributions).
 __global__ void layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
@@ -328,6 +385,18 @@ SB_API int sb_layernorm_fwd(const void* x, const float* gamma, const float* beta
                             int D, float eps, cudaStream_t stream) {
   if (D % 8 != 0 || rows <= 0) return -1;
   const int warps = 8;
+  if (D % 256 == 0 && D <= 1024 && (reinterpret_cast<uintptr_t>(gamma) & 15) == 0 && (!beta || (reinterpret_cast<uintptr_t>(beta) & 15) == 0)) {
+    const int nb = (rows + warps - 1) / warps;
+    const __nv_bfloat16* gx = (const __nv_bfloat16*)x;
+    __nv_bfloat16* gy = (__nv_bfloat16*)y;
+    switch (D / 256) {
+      case 1: layernorm_fwd_reg_kernel<1><<<nb, warps * 32, 0, stream>>>(gx, gamma, beta, gy, mean, rstd, rows, eps); break;
+      case 2: layernorm_fwd_reg_kernel<2><<<nb, warps * 32, 0, stream>>>(gx, gamma, beta, gy, mean, rstd, rows, eps); break;
+      case 3: layernorm_fwd_reg_kernel<3><<<nb, warps * 32, 0, stream>>>(gx, gamma, beta, gy, mean, rstd, rows, eps); break;
+      default: layernorm_fwd_reg_kernel<4><<<nb, warps * 32, 0, stream>>>(gx, gamma, beta, gy, mean, rstd, rows, eps); break;
+    }
+    return (int)cudaGetLastError();
+  }
   layernorm_fwd_kernel<8><<<(rows + warps - 1) / warps, warps * 32, 0, stream>>>(
       (const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, rstd, rows, D, eps);
   return (int)cudaGetLastError();
@@ -337,10 +406,12 @@ SB_API int sb_layernorm_fwd(const void* x, const float* gamma, const float* beta
 SB_API int sb_layernorm_bwd_res(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd, void* dx,
                                 float* dgamma, float* dbeta, const void* dres, int rows, int D, cudaStream_t stream) {
   if (D % 8 != 0 || rows <= 0 || D > 5632) return -1;  // 2*D floats of shared memory
-  const int blocks = min(rows, 2 * sb_num_sms());
+  // the register-resident kernel runs one 256-thread block per SM (246 registers at D = 1024): exactly one wave of blocks
+  const bool reg_path = D % 256 == 0 && D <= 1024;
+  const int blocks = min(rows, (reg_path ? 1 : 2) * sb_num_sms());
   const int rpb = (rows + blocks - 1) / blocks;
   const int nblocks = (rows + rpb - 1) / rpb;
-  if (D % 256 == 0 && D <= 1024) {
+  if (reg_path) {
     const __nv_bfloat16 *gdy = (const __nv_bfloat16*)dy, *gx = (const __nv_bfloat16*)x;
     __nv_bfloat16* gdx = (__nv_bfloat16*)dx;
     const __nv_bfloat16* gres = (const __nv_bfloat16*)dres;

@@ -29,6 +29,8 @@ struct SbGemmArgs {
   int tile_n;       // 128 or 256 to force the tile width, anything else = automatic
   float drop_p;     // > 0: dropout applied to act(acc + bias) before alpha / residual; mask = sb_dropout_keep(seed, m * N + n)
   unsigned long long drop_seed;
+  int ksplit;       // 0 = automatic, -1 = never split K, > 1 = that many K slices (only honoured for D(fp32) += alpha * A B^T)
+  int pad_;
 };
 
 

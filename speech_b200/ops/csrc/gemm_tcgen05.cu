@@ -67,6 +67,10 @@ struct GemmParams {
   int kfold;  // > 1: the K loop also runs over this many batch1 entries (sum over batch1 into one output)
   int tiles_m, tiles_n;
   long long num_tiles;
+  // split-K: every output tile is computed by `ksplit` work items of `kb_per` K blocks each, which add their partial sums to
+  // the fp32 output with vector reductions (only for plain accumulating epilogues: D += alpha * A B^T)
+  int ksplit, kb_per;
+  long long num_work;  // num_tiles * ksplit
   EpilogueArgs ep;
   int* status;
 };
@@ -239,12 +243,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (lane == 0) {
       long long it = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      for (long long w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
+        const long long tile = p.ksplit > 1 ? w / p.ksplit : w;
+        const int kb_begin = p.ksplit > 1 ? (int)(w % p.ksplit) * p.kb_per : 0;
+        const int kb_end = p.ksplit > 1 ? min(num_kb, kb_begin + p.kb_per) : num_kb;
         const int batch = (int)(tile / ((long long)p.tiles_m * p.tiles_n));
         const int rem = (int)(tile % ((long long)p.tiles_m * p.tiles_n));
         const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
         const int b0 = batch % p.batch0;
-        for (int kbt = 0; kbt < num_kb; ++kbt, ++it) {
+        for (int kbt = kb_begin; kbt < kb_end; ++kbt, ++it) {
           const int kb = kbt % num_kb1;
           const int b1 = p.kfold > 1 ? kbt / num_kb1 : batch / p.batch0;
           const int s = (int)(it % NUM_STAGES);
@@ -276,13 +283,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       long long it = 0;
       long long tcount = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++tcount) {
+      for (long long w = blockIdx.x; w < p.num_work && ok; w += gridDim.x, ++tcount) {
+        const int kb_begin = p.ksplit > 1 ? (int)(w % p.ksplit) * p.kb_per : 0;
+        const int kb_end = p.ksplit > 1 ? min(num_kb, kb_begin + p.kb_per) : num_kb;
         const int acc = (int)(tcount % NUM_ACC);
         const uint32_t aph = (uint32_t)((tcount / NUM_ACC) & 1);
         if (!mbar_wait(tempty_bar(acc), aph ^ 1u, p.status, SB_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const int s = (int)(it % NUM_STAGES);
           const uint32_t ph = (uint32_t)((it / NUM_STAGES) & 1);
           if (!mbar_wait(full_bar(s), ph, p.status, SB_TIMEOUT_SMEM_FULL)) { ok = false; break; }
@@ -295,7 +304,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                      : make_desc(sa + k * (UMMA_K * 2), 16, 1024);
             const uint64_t bd = B_MN ? make_desc(sb + k * (UMMA_K * 128), BLOCK_K * 128, 1024)
                                      : make_desc(sb + k * (UMMA_K * 2), 16, 1024);
-            umma_bf16(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(d_tmem, ad, bd, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
         }
@@ -310,7 +319,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint8_t* stage = smem + NUM_STAGES * STAGE_BYTES + 256 + (warp - 2) * EPI_STAGE_BYTES;
     long long tcount = 0;
     bool ok = true;
-    for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++tcount) {
+    for (long long w = blockIdx.x; w < p.num_work && ok; w += gridDim.x, ++tcount) {
+      const long long tile = p.ksplit > 1 ? w / p.ksplit : w;
       const int batch = (int)(tile / ((long long)p.tiles_m * p.tiles_n));
       const int rem = (int)(tile % ((long long)p.tiles_m * p.tiles_n));
       const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
@@ -442,7 +452,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
             }
           }
-          if (e.d_is_f32) {
+          if (e.d_is_f32 && p.ksplit > 1) {
+            // partial sum of one K slice: D += v (the host only splits K for epilogues of exactly this form)
+            float* dp = reinterpret_cast<float*>(e.D) + d_off + col0;
+            if (full && ((((uintptr_t)dp) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dp + j), "f"(v[j]), "f"(v[j + 1]), "f"(v[j + 2]),
+                             "f"(v[j + 3])
+                             : "memory");
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) atomicAdd(dp + j, v[j]);
+            }
+          } else if (e.d_is_f32) {
             float* dp = reinterpret_cast<float*>(e.D) + d_off + col0;
             if (full && ((((uintptr_t)dp) & 15) == 0)) {
 #pragma unroll
@@ -536,8 +560,13 @@ bool g_attr_set[8] = {false, false, false, false, false, false, false, false};
 SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   if (a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batch0 <= 0 || a->batch1 <= 0) return -1;
   // 256-wide tiles when the problem has enough of them to fill the machine, else 128-wide
+  // split-K is possible when the epilogue is exactly D(fp32) += alpha * A B^T: weight gradients (long K, few output tiles)
+  const bool can_split = a->d_is_f32 && a->beta == 1.f && !a->bias && !a->residual && !a->aux && !a->D_pre && a->act == 0 &&
+                         a->drop_p <= 0.f && !a->fold_batch1 && a->ksplit >= 0;
   int bn = a->tile_n;
-  if (bn != 128 && bn != 256) {
+  if (bn != 128 && bn != 256 && can_split && a->N >= 256 && a->K >= 24 * BLOCK_K) {
+    bn = 256;  // K slices restore the parallelism that wide tiles give up
+  } else if (bn != 128 && bn != 256) {
     const long long t256 = (long long)((a->M + BLOCK_M - 1) / BLOCK_M) * ((a->N + 255) / 256) * a->batch0 *
                            (a->fold_batch1 ? 1 : a->batch1);
     bn = (a->N >= 256 && t256 >= (long long)sb_num_sms() * 3 / 4) ? 256 : 128;
@@ -561,6 +590,28 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   p.tiles_n = (a->N + bn - 1) / bn;
   p.kfold = a->fold_batch1 ? a->batch1 : 1;
   p.num_tiles = (long long)p.tiles_m * p.tiles_n * a->batch0 * (a->fold_batch1 ? 1 : a->batch1);
+  p.ksplit = 1;
+  {
+    const int num_kb = (a->K + BLOCK_K - 1) / BLOCK_K;
+    const int sms = sb_num_sms();
+    if (a->ksplit > 1 && can_split) {
+      p.ksplit = a->ksplit < num_kb ? a->ksplit : num_kb;
+    } else if (can_split && a->ksplit == 0 && p.num_tiles < (long long)sms * 3 / 4) {
+      // pick the split whose work-item count fills whole waves best; a slice keeps at least 12 K blocks (768 elements)
+      double best = (double)p.num_tiles / sms;  // efficiency of one partial wave
+      for (int s = 2; s <= 8 && num_kb / s >= 12; ++s) {
+        const long long items = p.num_tiles * s;
+        const double eff = (double)items / ((double)((items + sms - 1) / sms) * sms) - 0.02 * (s - 1);
+        if (eff > best + 1e-9) {
+          best = eff;
+          p.ksplit = s;
+        }
+      }
+    }
+    p.kb_per = (num_kb + p.ksplit - 1) / p.ksplit;
+    p.ksplit = (num_kb + p.kb_per - 1) / p.kb_per;  // no empty slices
+    p.num_work = p.num_tiles * p.ksplit;
+  }
   p.status = sb_status_ptr();
   if (!p.status) return -2;
   EpilogueArgs& e = p.ep;
@@ -579,7 +630,7 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   e.drop_seed = a->drop_seed;
   int grid = sb_num_sms();
   if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
-  if ((long long)grid > p.num_tiles) grid = (int)p.num_tiles;
+  if ((long long)grid > p.num_work) grid = (int)p.num_work;
   const int variant = (a->a_mn_major ? 2 : 0) | (a->b_mn_major ? 1 : 0) | (bn == 256 ? 4 : 0);
   void (*kern)(const CUtensorMap, const CUtensorMap, const GemmParams) = nullptr;
   switch (variant) {

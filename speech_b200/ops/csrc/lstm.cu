@@ -67,6 +67,7 @@ SbGemmArgs small_gemm(const void* A, const void* Bm, void* D, int M, int N, int 
   a.D = D; a.d_is_f32 = 1; a.ldd = N;
   a.alpha = 1.f; a.beta = beta;
   a.tile_n = 128;
+  a.ksplit = -1;  // the recurrence GEMMs are tiny; never slice K
   return a;
 }
 

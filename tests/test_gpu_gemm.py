@@ -175,3 +175,48 @@ def test_linear_fused_dropout_mask_is_consistent_between_forward_and_backward():
     y4.backward(dy)
     ref4 = (keep4 / (1 - p) * dy.float()) @ w.float()
     assert (x2.grad.float() - ref4).abs().max().item() / ref4.abs().max().item() < 0.03
+
+
+@pytest.mark.parametrize("ksplit", [0, 3, -1])
+@pytest.mark.parametrize("M,N,K", [(1024, 1024, 3760), (2048, 1024, 3752), (1000, 520, 1800)])
+def test_gemm_split_k_weight_gradient(ksplit, M, N, K):
+    """D(fp32) += A^T B with both operands stored [K, *] (the weight-gradient form): K slices add into D with reductions."""
+    nat = _native()
+    torch.manual_seed(1)
+    a = torch.randn((K, M), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((K, N), device="cuda", dtype=torch.bfloat16)
+    d0 = torch.randn((M, N), device="cuda", dtype=torch.float32)
+    out = d0.clone()
+    nat.gemm(a, b, out, M=M, N=N, K=K, a_mn=True, b_mn=True, lda=M, ldb=N, ldd=N, beta=1.0, alpha=0.5, ksplit=ksplit)
+    nat.check_status()
+    ref = d0 + 0.5 * (a.float().t() @ b.float())
+    err = (out - ref).abs().max().item()
+    assert err <= 2e-2 * (K ** 0.5), f"max abs err {err}"
+
+
+def test_layernorm_forward_register_path_and_backward_residual():
+    nat = _native()
+    import ctypes
+
+    torch.manual_seed(2)
+    for rows, D in ((3760, 1024), (33, 512), (50, 264)):
+        x = torch.randn(rows, D, device="cuda").to(torch.bfloat16)
+        g = torch.randn(D, device="cuda")
+        b = torch.randn(D, device="cuda")
+        y = nat.layer_norm(x, g, b, 1e-5)
+        ref = torch.nn.functional.layer_norm(x.float(), (D,), g, b, 1e-5)
+        assert (y.float() - ref).abs().max().item() < 0.05
+        dy = torch.randn(rows, D, device="cuda").to(torch.bfloat16)
+        dres = torch.randn(rows, D, device="cuda").to(torch.bfloat16)
+        mean = x.float().mean(-1)
+        rstd = (x.float().var(-1, unbiased=False) + 1e-5).rsqrt()
+        dx = torch.empty_like(x)
+        dg, db = torch.zeros(D, device="cuda"), torch.zeros(D, device="cuda")
+        rc = nat.lib().sb_layernorm_bwd_res(nat._ptr(dy), nat._ptr(x), nat._ptr(g), nat._ptr(mean), nat._ptr(rstd), nat._ptr(dx), nat._ptr(dg),
+                                            nat._ptr(db), nat._ptr(dres), ctypes.c_int(rows), ctypes.c_int(D), nat._stream())
+        assert rc == 0
+        x32 = x.float().requires_grad_(True)
+        g32, b32 = g.clone().requires_grad_(True), b.clone().requires_grad_(True)
+        torch.nn.functional.layer_norm(x32, (D,), g32, b32, 1e-5).backward(dy.float())
+        assert (dx.float() - (x32.grad + dres.float())).abs().max().item() < 0.08
+        assert (dg - g32.grad).abs().max().item() < 0.02 * rows ** 0.5 and (db - b32.grad).abs().max().item() < 0.02 * rows ** 0.5
