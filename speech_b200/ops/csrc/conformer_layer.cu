@@ -282,13 +282,19 @@ struct Exec {
     return run(sb_gemm_bf16(&g, stream));
   }
   // dx[M, K] = dz[M, N] @ w[N, K];  gw[N, K] += dz^T x;  gb[N] += column sums of dz
+  // The input gradient can leave its GEMM already multiplied by the previous activation's derivative and dropout mask:
+  // dx = dropout(dz @ w) * act'(dx_pre)  (dx_pre = that activation's saved input, dx_seed = its forward dropout seed).
   bool linear_bwd(const bf16* dz, long long ld_dz, const bf16* x, long long ldx, const SbLinearParams& p, bf16* dx, int M, int N,
-                  int K) {
+                  int K, const bf16* dx_pre = nullptr, int dx_dact = 0, float dx_drop = 0.f, unsigned long long dx_seed = 0) {
     char label[32];
     if (dx) {
       SbGemmArgs g = gemm_defaults();
       g.A = dz; g.B = p.w; g.M = M; g.N = K; g.K = N; g.lda = ld_dz; g.b_mn_major = 1; g.ldb = K;
       g.D = dx; g.ldd = K;
+      if (dx_pre) {
+        g.aux = dx_pre; g.ldx = K; g.dact = dx_dact;
+      }
+      g.drop_p = dx_drop; g.drop_seed = dx_drop > 0.f ? dx_seed : 0ull;
       snprintf(label, sizeof(label), ".dgrad %dx%d", N, K);
       sub = label;
       if (!run(sb_gemm_bf16(&g, stream))) return false;
@@ -453,6 +459,8 @@ SB_API int sb_conformer_layer_bwd(SbConformerLayerArgs* a, cudaStream_t stream) 
                     const SbNormParams& norm, const SbLinearParams& la, const SbLinearParams& lb, const float* mean,
                     const float* rstd, unsigned long long seed_inner, unsigned long long seed_out) {
     bool k = e.named(".scale_dact_dropout", sb_scale_dact_dropout(G_in, d, nullptr, w.dzd, R, d, 0, a->fc_factor, p_ff, seed_out, stream));
+    // (folding swish'(pre) and the inner dropout into this dgrad GEMM's epilogue was measured slower: with K = d the GEMM is
+    // epilogue-bound and the per-row loads of `pre` more than double it; the separate pass below runs at HBM speed)
     k = k && e.linear_bwd(w.dzd, d, act_out, F, lb, w.big, R, d, F);
     k = k && e.named(".scale_dact_dropout", sb_scale_dact_dropout(w.big, F, pre, w.big, R, F, 2, 1.f, p_ff, seed_inner, stream));
     k = k && e.linear_bwd(w.big, F, h, d, la, w.dh, R, F, d);
