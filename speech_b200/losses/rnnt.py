@@ -25,6 +25,7 @@ RNNT_LOSS_RESOLVER = {
     "default": "rnnt", "warprnnt": "rnnt", "warprnnt_numba": "rnnt", "pytorch": "rnnt", "rnnt": "rnnt",
     "tdt": "tdt", "tdt_pytorch": "tdt",
     "multiblank_rnnt": "multiblank", "multiblank_rnnt_pytorch": "multiblank",
+    "graph_rnnt": "graph_rnnt", "graph_w_transducer": "graph_w",
 }
 
 
@@ -51,6 +52,16 @@ class RNNTLoss(Loss):
         self.sigma = float(kw.get("sigma", 0.0))
         self.omega = float(kw.get("omega", 0.0))
         self.big_blank_durations: List[int] = list(kw.get("big_blank_durations", [])) if self.kind == "multiblank" else []
+        self._graph_loss = None
+        if self.kind in ("graph_rnnt", "graph_w"):
+            from .graph_transducer import GraphRnntLoss, GraphWTransducerLoss
+
+            gk = {k: v for k, v in kw.items() if k in ("double_scores", "cast_to_float32", "use_grid_implementation", "connect_composed")}
+            if self.kind == "graph_w":
+                self._graph_loss = GraphWTransducerLoss(num_classes, eps_weight=float(kw.get("eps_weight", 0.0)),
+                                                        last_blank_mode=str(kw.get("last_blank_mode", "force_final")), **gk)
+            else:
+                self._graph_loss = GraphRnntLoss(num_classes, **gk)
         if self.kind == "tdt" and not self.durations:
             raise ValueError("TDT loss needs `durations` in loss_kwargs")
         if self.kind == "multiblank" and not self.big_blank_durations:
@@ -95,6 +106,8 @@ class RNNTLoss(Loss):
             acts = acts.narrow(2, 0, max_u + 1)
         labels = labels[:, :max_u]
         act_lens, label_lens = act_lens.long(), label_lens.long()
+        if self._graph_loss is not None:
+            return self._graph_loss(acts, labels, act_lens, label_lens)
         if self.kind == "tdt":
             if self._use_plain_rnnt_this_call():
                 loss = ops.transducer_loss_from_logits(acts[..., : -len(self.durations)].contiguous(), labels, act_lens,

@@ -140,3 +140,61 @@ def test_gloo_data_parallel_keeps_ranks_in_sync(tmp_path):
     assert len(res) == 2
     assert abs(res[0]["sum"] - res[1]["sum"]) < 1e-6 * max(1.0, abs(res[0]["sum"]))
     assert res[0]["loss"] != res[1]["loss"]  # each rank saw its own shard of the data
+
+
+def test_graph_rnnt_and_w_transducer_losses_match_explicit_lattice_dp():
+    import math as _m
+
+    from speech_b200.losses.graph_transducer import GraphRnntLoss, GraphWTransducerLoss
+    from speech_b200.ops import reference
+
+    torch.manual_seed(0)
+    B, T, U, V = 3, 7, 4, 6
+    blank = V - 1
+    logits = torch.randn(B, T, U + 1, V, dtype=torch.float64, requires_grad=True)
+    labels = torch.randint(0, V - 1, (B, U))
+    act_lens, label_lens = torch.tensor([7, 5, 6]), torch.tensor([4, 2, 3])
+    loss = GraphRnntLoss(blank, double_scores=True)(logits, labels, act_lens, label_lens)
+    ref = reference.tdt_loss_from_logits(logits.detach().float(), labels, act_lens, label_lens, blank, [], 0.0)
+    assert torch.allclose(loss, ref.float(), atol=1e-3)
+    loss.sum().backward()
+    assert torch.isfinite(logits.grad).all() and float(logits.grad[1, 5:].abs().sum()) == 0.0     # frames past the length carry no gradient
+
+    def lattice(lp, y, Tn, Un, eps, mode):
+        """Plain-Python forward algorithm over the W-Transducer grid with explicit skip arcs."""
+        NEG = -1e30
+        lae = lambda a, b: max(a, b) + _m.log1p(_m.exp(-abs(a - b))) if min(a, b) > NEG / 2 else max(a, b)  # noqa: E731
+        al = [[NEG] * (Un + 1) for _ in range(Tn)]
+        for t in range(Tn):
+            for u in range(Un + 1):
+                s = 0.0 if (t == 0 and u == 0) else NEG
+                if t > 0 and u == 0 and eps is not None:
+                    s = lae(s, eps)                                   # start state -> (t, 0)
+                if t > 0:
+                    s = lae(s, al[t - 1][u] + lp[t - 1][u][blank])
+                if u > 0:
+                    s = lae(s, al[t][u - 1] + lp[t][u - 1][y[u - 1]])
+                al[t][u] = s
+        end = al[Tn - 1][Un]
+        skipped = NEG
+        if eps is not None:
+            for t in range(Tn - 1):
+                skipped = lae(skipped, al[t][Un] + eps)               # (t, U) -> last frame
+        if mode == "force_final":
+            return lae(end, skipped) + lp[Tn - 1][Un][blank]
+        return lae(end + lp[Tn - 1][Un][blank], skipped)
+
+    lp = torch.log_softmax(logits.detach(), -1).tolist()
+    for mode in ("force_final", "allow_ignore"):
+        for eps in (0.0, -1.5):
+            got = GraphWTransducerLoss(blank, eps_weight=eps, last_blank_mode=mode, double_scores=True)(logits, labels, act_lens, label_lens)
+            exp = [-lattice(lp[b], labels[b].tolist(), int(act_lens[b]), int(label_lens[b]), eps, mode) for b in range(B)]
+            assert torch.allclose(got.double(), torch.tensor(exp, dtype=torch.float64), atol=1e-4), (mode, eps, got, exp)
+            assert (got <= loss.detach() + 1e-5).all()                # extra paths can only raise the likelihood
+    from speech_b200.losses.rnnt import RNNTLoss
+
+    via = RNNTLoss(num_classes=blank, loss_name="graph_w_transducer", loss_kwargs={"eps_weight": -1.5, "last_blank_mode": "force_final"},
+                   reduction="none")
+    v = via(log_probs=logits.detach().float(), targets=labels, input_lengths=act_lens, target_lengths=label_lens)
+    exp = [-lattice(lp[b], labels[b].tolist(), int(act_lens[b]), int(label_lens[b]), -1.5, "force_final") for b in range(B)]
+    assert torch.allclose(v, torch.tensor(exp, dtype=torch.float32), atol=1e-3)
