@@ -12,6 +12,7 @@
 // Swish convolution module, final LayerNorm).
 #include "common.cuh"
 #include "gemm_api.h"
+#include "peer_small.h"
 
 #include <cstdint>
 #include <cstdio>
@@ -100,6 +101,14 @@ struct SbConformerLayerArgs {
   // backward only
   const void* dout;    // [B*T, d] bf16
   void* dx;            // [B*T, d] bf16 (null: the input needs no gradient)
+  // synchronised BatchNorm (training on several GPUs): the layer's batch statistics are summed over all ranks with the
+  // small-vector peer all-reduce; sync_world <= 1 keeps them local.  The forward call uses epoch sync_epoch, and so does the
+  // backward call (the caller advances the counter once per call, identically on every rank).
+  void* const* sync_buffers;
+  long long sync_base_off;
+  int sync_rank, sync_world;
+  unsigned int sync_epoch;
+  int pad2_;
   // profiling (host memory, optional): when prof_ms is set, the call records a CUDA event after every launch, waits for the
   // last one and stores the device time of launch i in prof_ms[i] (milliseconds); at most prof_cap entries
   float* prof_ms;
@@ -130,6 +139,7 @@ struct Saved {
   bf16 *h2, *qkv, *p, *qu, *qv, *Pm, *Pd, *ctx, *res2;
   bf16 *h3, *g, *y, *s, *res3;
   float* mean_rstd;
+  float* gcount;   // number of (frame, batch) positions behind the BatchNorm statistics, summed over ranks
   bf16 *h4, *pre2, *a2, *res4;
 };
 
@@ -159,6 +169,7 @@ long long layout_saved(const SbConformerLayerArgs& a, char* base, Saved& s) {
   s.s = m.take<bf16>(R * d);
   s.res3 = m.take<bf16>(R * d);
   s.mean_rstd = m.take<float>(2 * d);
+  s.gcount = m.take<float>(1);
   s.h4 = m.take<bf16>(R * d);
   s.pre2 = m.take<bf16>(R * F);
   s.a2 = m.take<bf16>(R * F);
@@ -359,6 +370,7 @@ SB_API int sb_conformer_layer_args_size() { return (int)sizeof(SbConformerLayerA
 
 SB_API int sb_conformer_layer_fwd(SbConformerLayerArgs* a, cudaStream_t stream) {
   if (!shapes_ok(*a)) return -1;
+  if (a->sync_world > 1 && 2 * a->d + 1 > SB_SMALL_MAX) return -5;
   Saved s;
   FwdScratch f;
   if (layout_saved(*a, a->saved, s) > a->saved_bytes || !a->saved) return -2;
@@ -418,8 +430,17 @@ SB_API int sb_conformer_layer_fwd(SbConformerLayerArgs* a, cudaStream_t stream) 
   if (tr) ok = ok && e.zero(f.stats, (2 * d + 1) * sizeof(float));
   ok = ok && e.named(".glu_dwconv_fwd", sb_glu_dwconv_fwd(s.g, a->pad_mask, a->dw_w, a->dw_b, s.y, tr ? f.stats : nullptr, B, T, d, a->conv_k,
                                      a->conv_left, stream));
-  ok = ok && e.named(".bn_finalize", sb_bn_finalize(tr ? f.stats : nullptr, (float)R, nullptr, s.mean_rstd, a->bn_mean, a->bn_var, d, a->bn_eps,
-                                  a->bn_momentum, tr ? 1 : 0, stream));
+  const bool sync_bn = tr && a->sync_world > 1 && a->sync_buffers;
+  if (sync_bn) {  // batch statistics and element count summed over all ranks
+    SbPeerSmallArgs sa;
+    memset(&sa, 0, sizeof(sa));
+    sa.data = f.stats; sa.buffers = a->sync_buffers; sa.base_off = a->sync_base_off; sa.n = 2 * d; sa.has_extra = 1; sa.extra = (float)R;
+    sa.rank = a->sync_rank; sa.world = a->sync_world; sa.epoch = a->sync_epoch;
+    ok = ok && e.named(".peer_small_allreduce", sb_peer_small_allreduce(&sa, stream));
+    ok = ok && e.named(".copy_count", (int)cudaMemcpyAsync(s.gcount, f.stats + 2 * d, sizeof(float), cudaMemcpyDeviceToDevice, stream));
+  }
+  ok = ok && e.named(".bn_finalize", sb_bn_finalize(tr ? f.stats : nullptr, (float)R, sync_bn ? f.stats + 2 * d : nullptr, s.mean_rstd,
+                                                    a->bn_mean, a->bn_var, d, a->bn_eps, a->bn_momentum, tr ? 1 : 0, stream));
   ok = ok && e.named(".bn_silu_fwd", sb_bn_silu_fwd(s.y, s.mean_rstd, a->bn_w, a->bn_b, s.s, R, d, stream));
   ok = ok && e.linear(s.s, d, a->pw2, s.res3, R, d, d, 0, nullptr, s.res2, 1.f, p_out, a->seeds[4]);
   // ---- feed-forward 2 and the output norm
@@ -436,6 +457,7 @@ SB_API int sb_conformer_layer_fwd(SbConformerLayerArgs* a, cudaStream_t stream) 
 
 SB_API int sb_conformer_layer_bwd(SbConformerLayerArgs* a, cudaStream_t stream) {
   if (!shapes_ok(*a)) return -1;
+  if (a->sync_world > 1 && 2 * a->d + 1 > SB_SMALL_MAX) return -5;
   Saved s;
   BwdScratch w;
   if (layout_saved(*a, a->saved, s) > a->saved_bytes || !a->saved) return -2;
@@ -487,10 +509,21 @@ SB_API int sb_conformer_layer_bwd(SbConformerLayerArgs* a, cudaStream_t stream) 
     ok = ok && e.zero(w.sums, 2 * d * sizeof(float));
     ok = ok && e.named(".bn_silu_bwd_stats", sb_bn_silu_bwd_stats(ds, s.y, s.mean_rstd, a->bn_w, a->bn_b, w.sums, R, d, stream));
     bf16* dg = w.big;
-    ok = ok && e.named(".dwconv_glu_bwd", sb_dwconv_glu_bwd(ds, s.y, s.g, a->pad_mask, a->dw_w, s.mean_rstd, a->bn_w, a->bn_b, w.sums, (float)R, nullptr,
-                                       tr ? 1 : 0, dg, a->g_dw_w, a->g_dw_b, B, T, d, a->conv_k, a->conv_left, stream));
+    // the affine gradients are the LOCAL sums (the data-parallel gradient exchange adds the ranks up later) ...
     if (a->g_bn_w) ok = ok && e.accum(a->g_bn_w, w.sums + d, 1.f, nullptr, 0.f, d);
     if (a->g_bn_b) ok = ok && e.accum(a->g_bn_b, w.sums, 1.f, nullptr, 0.f, d);
+    // ... while the input gradient of a synchronised BatchNorm needs the sums over all ranks
+    const bool sync_bn = tr && a->sync_world > 1 && a->sync_buffers;
+    if (sync_bn) {
+      SbPeerSmallArgs sa;
+      memset(&sa, 0, sizeof(sa));
+      sa.data = w.sums; sa.buffers = a->sync_buffers; sa.base_off = a->sync_base_off; sa.n = 2 * d;
+      sa.rank = a->sync_rank; sa.world = a->sync_world; sa.epoch = a->sync_epoch;
+      ok = ok && e.named(".peer_small_allreduce", sb_peer_small_allreduce(&sa, stream));
+    }
+    ok = ok && e.named(".dwconv_glu_bwd", sb_dwconv_glu_bwd(ds, s.y, s.g, a->pad_mask, a->dw_w, s.mean_rstd, a->bn_w, a->bn_b, w.sums, (float)R,
+                                                            sync_bn ? s.gcount : nullptr, tr ? 1 : 0, dg, a->g_dw_w, a->g_dw_b, B, T, d,
+                                                            a->conv_k, a->conv_left, stream));
     ok = ok && e.linear_bwd(dg, 2 * d, s.h3, d, a->pw1, w.dzd, R, 2 * d, d);
     ok = ok && e.ln_bwd(w.dzd, s.res2, a->ln_conv, s.mean[2], s.rstd[2], w.GA, w.GB, R, d);
   }

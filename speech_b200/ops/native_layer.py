@@ -46,7 +46,9 @@ class SbConformerLayerArgs(ctypes.Structure):
         ("dw_w", _vp), ("dw_b", _vp), ("g_dw_w", _vp), ("g_dw_b", _vp),
         ("bn_w", _vp), ("bn_b", _vp), ("g_bn_w", _vp), ("g_bn_b", _vp), ("bn_mean", _vp), ("bn_var", _vp),
         ("out", _vp), ("saved", _vp), ("saved_bytes", _ll), ("scratch", _vp), ("scratch_bytes", _ll),
-        ("dout", _vp), ("dx", _vp), ("prof_ms", ctypes.POINTER(_f)), ("prof_cap", _i), ("pad_", _i),
+        ("dout", _vp), ("dx", _vp),
+        ("sync_buffers", _vp), ("sync_base_off", _ll), ("sync_rank", _i), ("sync_world", _i), ("sync_epoch", ctypes.c_uint), ("pad2_", _i),
+        ("prof_ms", ctypes.POINTER(_f)), ("prof_cap", _i), ("pad_", _i),
     ]
 
 
@@ -257,12 +259,21 @@ def _sizes_for(a: SbConformerLayerArgs) -> Tuple[int, int, int]:
     return s
 
 
+def _set_sync(a, sync) -> None:
+    """Synchronised BatchNorm: hand the executor the peer buffers and this call's epoch (one per call, same on all ranks)."""
+    if sync is None or not a.training:
+        a.sync_buffers, a.sync_world, a.sync_epoch = None, 0, 0
+        return
+    a.sync_buffers, a.sync_base_off = sync.ptrs_dev, 0
+    a.sync_rank, a.sync_world, a.sync_epoch = sync.rank, sync.world, sync.next_epoch()
+
+
 class _ConformerLayerFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, anchor, pack, dyn):
         a: SbConformerLayerArgs = pack.args
         B, T, d = x.shape
-        pos, m8, mbs, pad8, training, drops, seeds = dyn
+        pos, m8, mbs, pad8, training, drops, seeds, sync = dyn
         a.B, a.T, a.P = B, T, pos.shape[0]
         a.training = int(training)
         a.drop_ff, a.drop_att, a.drop_out = drops
@@ -270,6 +281,7 @@ class _ConformerLayerFn(torch.autograd.Function):
             a.seeds[i] = s
         a.x, a.pos_emb = x.data_ptr(), pos.data_ptr()
         a.att_mask, a.att_mask_bstride, a.pad_mask = _ptr(m8), mbs, _ptr(pad8)
+        _set_sync(a, sync)
         sv, fs, bs = _sizes_for(a)
         saved = torch.empty(sv, dtype=torch.uint8, device=x.device)
         scratch = _scratch_for(x.device, max(fs, bs))
@@ -294,7 +306,7 @@ class _ConformerLayerFn(torch.autograd.Function):
         pack = ctx.pack
         a: SbConformerLayerArgs = pack.args
         B, T, d = ctx.dims
-        pos, m8, mbs, pad8, training, drops, seeds = ctx.dyn
+        pos, m8, mbs, pad8, training, drops, seeds, sync = ctx.dyn
         a.B, a.T, a.P = B, T, pos.shape[0]
         a.training = int(training)
         a.drop_ff, a.drop_att, a.drop_out = drops
@@ -302,6 +314,7 @@ class _ConformerLayerFn(torch.autograd.Function):
             a.seeds[i] = s
         a.x, a.pos_emb = x.data_ptr(), pos.data_ptr()
         a.att_mask, a.att_mask_bstride, a.pad_mask = _ptr(m8), mbs, _ptr(pad8)
+        _set_sync(a, sync)
         sv, fs, bs = _sizes_for(a)
         scratch = _scratch_for(x.device, max(fs, bs))
         dout = dout if dout.is_contiguous() else dout.contiguous()
@@ -331,8 +344,14 @@ def conformer_layer(layer, x: torch.Tensor, att_mask, pos_emb, pad_mask) -> Opti
     ok = getattr(layer, "_exec_static_ok", None)
     if ok is None:
         ok = layer._exec_static_ok = _static_ok(layer)
-    if not ok or layer.conv.bn_stats_reduce is not None or pos_emb is None or pos_emb.shape[0] != 1:
+    if not ok or pos_emb is None or pos_emb.shape[0] != 1:
         return None
+    sync = None
+    if layer.conv.bn_stats_reduce is not None:
+        # synchronised BatchNorm: only with the peer-memory reducer, which the executor can call between its kernels
+        sync = getattr(layer.conv, "bn_peer_sync", None)
+        if sync is None or 2 * x.shape[2] + 1 > sync.max_elems:
+            return None
     B, T, d = x.shape
     if pos_emb.shape[1] != 2 * T - 1 or B * T == 0:
         return None
@@ -363,7 +382,7 @@ def conformer_layer(layer, x: torch.Tensor, att_mask, pos_emb, pad_mask) -> Opti
     seeds = (nd() if p_ff > 0 else 0, nd() if p_ff > 0 else 0, ns() if p_att > 0 else 0, nd() if p_out > 0 else 0,
              nd() if p_out > 0 else 0, nd() if p_ff > 0 else 0, nd() if p_ff > 0 else 0)
     xc = x if x.is_contiguous() else x.contiguous()
-    dyn = (pos, m8, mbs, pad8, training, (p_ff, p_att, p_out), seeds)
+    dyn = (pos, m8, mbs, pad8, training, (p_ff, p_att, p_out), seeds, sync)
     if need_grad:
         out = _ConformerLayerFn.apply(xc, layer.norm_out.weight, pack, dyn)
     else:

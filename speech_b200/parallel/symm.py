@@ -95,6 +95,51 @@ class PeerAllReduce:
             raise RuntimeError(f"sb_peer_allreduce failed with code {rc}")
 
 
+class SbPeerSmallArgs(ctypes.Structure):
+    _fields_ = [("data", ctypes.c_void_p), ("buffers", ctypes.c_void_p), ("base_off", ctypes.c_longlong), ("n", ctypes.c_int),
+                ("has_extra", ctypes.c_int), ("extra", ctypes.c_float), ("rank", ctypes.c_int), ("world", ctypes.c_int),
+                ("epoch", ctypes.c_uint), ("status", ctypes.c_void_p)]
+
+
+class PeerSmallAllReduce:
+    """Sum of a small fp32 vector over all ranks by one single-CTA kernel over peer memory (``csrc/peer_small_allreduce.cu``).
+
+    Every use — a direct call here or one made by the Conformer layer executor with ``ptrs_dev`` / ``next_epoch()`` — consumes
+    one epoch; all ranks must make the same sequence of uses."""
+
+    def __init__(self, device: torch.device, group=None):
+        from ..ops import native
+
+        self.native = native
+        self.lib = native.lib()
+        self.lib.sb_peer_small_bytes.restype = ctypes.c_longlong
+        self.max_elems = int(self.lib.sb_peer_small_max())
+        self.buf = SymmetricBuffer(int(self.lib.sb_peer_small_bytes()), device, group)
+        self.rank, self.world, self.ptrs_dev = self.buf.rank, self.buf.world, self.buf.ptrs_dev
+        self.epoch = 0
+
+    def __deepcopy__(self, memo):
+        return self   # process-wide communication state: modules that point here may be deep-copied (EMA, averaging)
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    def __call__(self, t: torch.Tensor, extra: Optional[float] = None) -> torch.Tensor:
+        """In-place sum of ``t`` (fp32, contiguous) over ranks; with ``extra`` the tensor must have one spare element at the end
+        that receives the sum of the ranks' ``extra`` values."""
+        n = t.numel() - (1 if extra is not None else 0)
+        if t.dtype != torch.float32 or not t.is_contiguous() or n <= 0 or t.numel() > self.max_elems:
+            raise ValueError(f"small peer all-reduce takes contiguous fp32 vectors of at most {self.max_elems} elements")
+        a = SbPeerSmallArgs(t.data_ptr(), self.ptrs_dev, 0, n, int(extra is not None), float(extra or 0.0), self.rank, self.world,
+                            self.next_epoch(), None)
+        rc = self.lib.sb_peer_small_allreduce(ctypes.byref(a), self.native._stream())
+        self.native.launch_count += 1
+        if rc != 0:
+            raise RuntimeError(f"sb_peer_small_allreduce failed with code {rc}")
+        return t
+
+
 class PeerGradSync(GradSync):
     """``GradSync`` whose buckets are reduced by the peer-memory kernel instead of an NCCL all-reduce."""
 
@@ -109,6 +154,14 @@ class PeerGradSync(GradSync):
         self.reducer = PeerAllReduce(biggest, device)
         logging.info(f"peer-memory gradient exchange: {len(self.buckets)} buckets, largest {biggest * 4 / 2**20:.1f} MB, "
                      f"{self.reducer.ctas} CTAs per bucket")
+
+    def enable_sync_batchnorm(self):
+        """BatchNorm statistics also travel through peer memory: the layer executor issues the small all-reduce itself."""
+        super().enable_sync_batchnorm()
+        self.small_reducer = PeerSmallAllReduce(self.device)
+        for m in self.model.modules():
+            if hasattr(m, "bn_stats_reduce"):
+                m.bn_peer_sync = self.small_reducer
 
     def _reduce_flat(self, flat: torch.Tensor):
         cur = torch.cuda.current_stream(self.device)

@@ -97,3 +97,104 @@ def test_two_or_more_ranks_match_nccl(tmp_path):
     res = [json.loads(m) for m in re.findall(r"RESULT (\{[^{}]*\})", out.stdout)]
     assert len(res) == n
     assert max(r["worst"] for r in res) < 8e-3  # one bf16 ulp of the result
+
+
+def test_small_allreduce_one_rank_world_and_extra_element():
+    from speech_b200.ops import native
+    from speech_b200.parallel.symm import SbPeerSmallArgs
+
+    lib = native.lib()
+    lib.sb_peer_small_bytes.restype = ctypes.c_longlong
+    dev = torch.device("cuda:0")
+    buf = torch.zeros(int(lib.sb_peer_small_bytes()), dtype=torch.uint8, device=dev)
+    ptrs = torch.tensor([buf.data_ptr()], dtype=torch.int64, device=dev)
+    x = torch.randn(2049, device=dev)
+    want = x.clone()
+    want[2048] = 77.0
+    for epoch in (1, 2, 3):
+        a = SbPeerSmallArgs(x.data_ptr(), ptrs.data_ptr(), 0, 2048, 1, 77.0, 0, 1, epoch, None)
+        assert lib.sb_peer_small_allreduce(ctypes.byref(a), native._stream()) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(x, want)
+    too_long = SbPeerSmallArgs(x.data_ptr(), ptrs.data_ptr(), 0, 5000, 0, 0.0, 0, 1, 4, None)
+    assert lib.sb_peer_small_allreduce(ctypes.byref(too_long), native._stream()) == -2
+    native.check_status()
+
+
+SYNC_BN_SCRIPT = textwrap.dedent("""
+    import os, sys, json, torch, torch.distributed as dist
+    sys.path.insert(0, {repo!r})
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from speech_b200 import ops
+    from speech_b200.ops import native, native_blocks, native_layer
+    from speech_b200.core.optim.fused_adamw import FusedAdamW
+    from speech_b200.modules.attention import RelPositionalEncoding
+    from speech_b200.modules.conformer_modules import ConformerLayer
+    from speech_b200.parallel.symm import PeerGradSync, PeerSmallAllReduce
+
+    # 1. the small all-reduce against NCCL, several calls in a row (both halves of the slots get reused)
+    small = PeerSmallAllReduce(dev)
+    worst = 0.0
+    for it, n in enumerate([2049, 7, 4096, 513, 2049]):
+        torch.manual_seed(10 * it + rank)
+        t = torch.randn(n, device=dev)
+        ref = t.clone(); ref[-1] = float(rank + 1); dist.all_reduce(ref)
+        small(t, extra=float(rank + 1))
+        torch.cuda.synchronize()
+        worst = max(worst, float((t - ref).abs().max()))
+    # 2. a Conformer layer with synchronised BatchNorm: executor (peer all-reduce inside) vs per-op path (NCCL all-reduce)
+    torch.manual_seed(5)
+    d, H, T, B = 256, 4, 40 + 8 * rank, 2
+    layer = ConformerLayer(d_model=d, d_ff=4 * d, n_heads=H, conv_kernel_size=9, dropout=0.0, dropout_att=0.0).cuda().train()
+    fusion = [fg for m in layer.modules() if hasattr(m, "arena_fusion_groups") for fg in m.arena_fusion_groups()]
+    opt = FusedAdamW(layer.parameters(), lr=1e-3, fusion_groups=fusion)
+    sync = PeerGradSync(layer, [opt], world, dev, sync_batchnorm=True)
+    pe = RelPositionalEncoding(d, 0.0); pe.extend_pe(T, dev)
+    torch.manual_seed(100 + rank)
+    x = torch.randn(B, T, d, device=dev); _, pos = pe(x)
+    wr = torch.randn(B, T, d, device=dev)
+    res = []
+    for executor in (False, True):
+        os.environ["SPEECH_B200_LAYER_EXECUTOR"] = "1" if executor else "0"
+        layer.conv.batch_norm.reset_running_stats(); opt.zero_grad()
+        xb = x.to(torch.bfloat16).requires_grad_(True)
+        before = native.launch_count
+        with ops.compute_dtype(torch.bfloat16), sync.no_sync():
+            y = layer(xb, att_mask=None, pos_emb=pos, pad_mask=None)
+        (y.float() * wr).sum().backward()
+        torch.cuda.synchronize()
+        res.append((y.detach().float(), xb.grad.float().clone(), layer.conv.batch_norm.running_mean.clone(),
+                    layer.conv.pointwise_conv1.weight.grad.clone(), native.launch_count - before))
+    def rel(a, b): return float((a - b).abs().max() / b.abs().max().clamp(min=1e-3))
+    assert native_layer._packs.get(layer) is not None
+    out = dict(rank=rank, small=worst, y=rel(res[1][0], res[0][0]), gx=rel(res[1][1], res[0][1]), rm=rel(res[1][2], res[0][2]),
+               gw=rel(res[1][3], res[0][3]), launches=res[1][4])
+    # running statistics are global: identical on all ranks
+    rm = res[1][2].clone(); dist.broadcast(rm, 0)
+    out["rm_same"] = bool(torch.allclose(rm, res[1][2], atol=1e-6))
+    native.check_status()
+    print("RESULT", json.dumps(out))
+    dist.destroy_process_group()
+""")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sync_batchnorm_through_peer_memory_in_layer_executor(tmp_path):
+    script = tmp_path / "syncbn.py"
+    script.write_text(SYNC_BN_SCRIPT.format(repo=REPO))
+    n = min(torch.cuda.device_count(), 4)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                          "--master-addr", "127.0.0.1", "--master-port", "29743", str(script)],
+                         capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, (out.stdout[-2000:], out.stderr[-3000:])
+    import re
+
+    res = [json.loads(m) for m in re.findall(r"RESULT (\{[^{}]*\})", out.stdout)]
+    assert len(res) == n
+    for r in res:
+        assert r["small"] < 1e-4 and r["y"] < 0.01 and r["gx"] < 0.03 and r["rm"] < 1e-3 and r["gw"] < 0.03 and r["rm_same"], r
+        assert r["launches"] > 40

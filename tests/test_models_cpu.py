@@ -188,3 +188,48 @@ def test_clustering_diarizer_end_to_end(tmp_path):
     last = [s for s in segs if s[0] >= 2.4]
     assert first and last and {s[2] for s in first} != {s[2] for s in last}
     assert (tmp_path / "pred_rttms" / "session_0.rttm").exists()
+
+
+def test_extra_encoders_rnn_transformer_wav2vec_parallel_expert():
+    from speech_b200.modules.conformer_encoder import ConformerEncoder
+    from speech_b200.modules.extra_encoders import (ConvFeatureEncoder, LSTMDecoder, ParallelExpertEncoder, RNNEncoder, TransformerEncoder,
+                                                    Wav2VecTransformerEncoder)
+
+    torch.manual_seed(0)
+    feats, lens = torch.randn(2, 32, 64), torch.tensor([64, 40])
+    rnn = RNNEncoder(32, n_layers=2, d_model=48, proj_size=32, subsampling="stacking", subsampling_factor=4)
+    y, yl = rnn(audio_signal=feats, length=lens)
+    assert y.shape == (2, 32, 16) and yl.tolist() == [16, 10]
+    dec = LSTMDecoder(32, num_classes=5, lstm_hidden_size=24, vocabulary=list("abcde"), bidirectional=True)
+    lp = dec(encoder_output=y)
+    assert lp.shape == (2, 16, 6) and torch.allclose(lp.exp().sum(-1), torch.ones(2, 16), atol=1e-5)
+    for sam, mode in (("rel_pos", "full"), ("abs_pos", "causal"), ("no_pos", "full")):
+        enc = TransformerEncoder(feat_in=32, d_model=64, n_heads=4, n_layers=2, subsampling="striding", subsampling_factor=4,
+                                 subsampling_conv_channels=16, self_attention_model=sam, attn_mode=mode, qk_norm=(sam == "no_pos"), drop_rate=0.0,
+                                 dropout_pre_encoder=0.0).eval()
+        out, ol = enc(audio_signal=feats, length=lens)
+        assert out.shape == (2, 64, 16) and ol.tolist() == [16, 10]
+        # padding of the shorter utterance must not leak into its valid frames
+        out2, _ = enc(audio_signal=torch.cat([feats[1:, :, :40], torch.randn(1, 32, 24)], dim=2), length=lens[1:])
+        assert torch.allclose(out[1, :, :10], out2[0, :, :10], atol=1e-4)
+        if mode == "causal":   # the future must not influence the past
+            f2 = feats.clone()
+            f2[0, :, 48:] += 1.0
+            o3, _ = enc(audio_signal=f2, length=lens)
+            assert torch.allclose(o3[0, :, :8], out[0, :, :8], atol=1e-4) and not torch.allclose(o3[0, :, 12:], out[0, :, 12:], atol=1e-4)
+    conv = ConvFeatureEncoder([{"emb_dim": 16, "kernel_size": 10, "stride": 5}, {"emb_dim": 16, "kernel_size": 3, "stride": 2}], embedding_dim=32)
+    wav, wl = torch.randn(2, 1600), torch.tensor([1600, 1000])
+    f, fl = conv(input_signal=wav, length=wl)
+    assert f.shape[:2] == (2, 32) and fl.tolist() == [159, 99] and f.shape[2] == 159
+    w2v = Wav2VecTransformerEncoder(embedding_dim=32, num_layers=2, num_heads=4, inner_size=64, pos_kernel_size=8, pos_groups=4).eval()
+    o, _ = w2v(audio_signal=f, length=fl)
+    assert o.shape == f.shape
+    asr = ConformerEncoder(feat_in=32, n_layers=1, d_model=32, n_heads=4, subsampling_factor=4, subsampling_conv_channels=16, conv_kernel_size=5)
+    pe = ParallelExpertEncoder(asr, None, n_spk=4).eval()
+    base, bl = pe(feats, lens)
+    spk = torch.zeros(2, 16, 4)
+    spk[:, :, 1] = 1.0
+    fused, _ = pe(feats, lens, spk_targets=spk)
+    assert fused.shape == base.shape and not torch.allclose(fused, base)
+    expect = pe.asr_norm(base.transpose(1, 2)) + pe.diar_norm(spk) @ pe.diar_kernel
+    assert torch.allclose(fused.transpose(1, 2), expect, atol=1e-5)
