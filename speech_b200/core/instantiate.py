@@ -50,6 +50,11 @@ def _install_default_aliases() -> None:
     a("nemo.collections.asr.modules.StatelessTransducerDecoder", M + "rnnt.StatelessTransducerDecoder")
     a("nemo.collections.asr.modules.SampledRNNTJoint", M + "rnnt.SampledRNNTJoint")
     a("nemo.collections.asr.modules.HATJoint", M + "rnnt.HATJoint")
+    for ref, name in (("rnn_encoder.", "RNNEncoder"), ("lstm_decoder.", "LSTMDecoder"), ("transformer_encoder.", "TransformerEncoder"),
+                      ("wav2vec_modules.", "ConvFeatureEncoder"), ("wav2vec_modules.", "Wav2VecTransformerEncoder"),
+                      ("parallel_expert_encoder.", "ParallelExpertEncoder")):
+        a("nemo.collections.asr.modules." + name, M + "extra_encoders." + name)
+        a("nemo.collections.asr.modules." + ref + name, M + "extra_encoders." + name)
     a("nemo.collections.asr.modules.transformer.get_nemo_transformer", M + "transformer_nm.get_transformer")
     a("nemo.collections.asr.modules.transformer.transformer.TransformerDecoderNM", M + "transformer_nm.TransformerDecoderNM")
     a("nemo.collections.asr.modules.transformer.TransformerDecoderNM", M + "transformer_nm.TransformerDecoderNM")

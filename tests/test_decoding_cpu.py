@@ -135,3 +135,60 @@ def test_lcs_merge_and_word_spotter():
         lp[t, 4], lp[t, tok] = -6.0, -0.05
     hits = ctc_word_spotter(lp, {"abc": [1, 2, 3], "zz": [0, 0]}, blank=4, keyword_threshold=-2.0)
     assert [h.word for h in hits] == ["abc"] and hits[0].start_frame in (3, 4) and hits[0].end_frame == 7
+
+
+def test_streaming_aed_waitk_and_alignatt_policies():
+    from speech_b200.decoding.aed_streaming import AEDStreamingDecodingConfig, GreedyBatchedStreamingAEDComputer
+    from speech_b200.modules.transformer_nm import GreedySequenceGenerator, TokenClassifier, TransformerDecoderNM
+
+    torch.manual_seed(0)
+    V, D, EOS = 20, 32, 2
+    dec = TransformerDecoderNM(vocab_size=V, hidden_size=D, num_layers=2, inner_size=64, num_attention_heads=4, max_sequence_length=64).eval()
+    cls = TokenClassifier(D, V).eval()
+    enc = torch.randn(2, 40, D)
+    enc_len = torch.tensor([40, 32])
+    prompt = torch.tensor([[1, 5], [1, 6]])
+    # offline greedy result with the full audio (per stream: streams have different lengths)
+    gen = GreedySequenceGenerator(dec.embedding, dec.decoder, cls, pad=0, bos=1, eos=EOS, max_sequence_length=24, max_delta_length=100)
+    offline = []
+    for b in range(2):
+        ids = gen(decoder_input_ids=prompt[b:b + 1], encoder_hidden_states=enc[b:b + 1, : int(enc_len[b])],
+                  encoder_input_mask=torch.ones(1, int(enc_len[b]), dtype=torch.bool))[0, 2:].tolist()
+        offline.append([t for t in (ids[: ids.index(EOS)] if EOS in ids else ids) if t != 0])
+    # wait-k fed with the whole audio in one last chunk equals offline greedy decoding
+    cfg = AEDStreamingDecodingConfig(streaming_policy="waitk", waitk_lagging=2, max_generation_length=24, frame_chunk_size=8,
+                                     hallucinations_detector=False)
+    comp = GreedyBatchedStreamingAEDComputer(dec.embedding, dec.decoder, cls, EOS, cfg)
+    st = comp(enc, enc_len, torch.tensor([True, True]), comp.init_state(prompt))
+    cut = lambda hyps: [h[:21] for h in hyps]      # an untrained decoder never emits EOS: both runs end at their length limits  # noqa: E731
+    assert cut(st.hypotheses(EOS)) == cut(offline) and not bool(st.active_samples.any())
+    # chunk by chunk: nothing during the initial lag, then one token per chunk, the rest at the end
+    st = comp.init_state(prompt)
+    counts = []
+    for c in range(1, 6):
+        n = torch.minimum(torch.tensor([8 * c, 8 * c]), enc_len)
+        st = comp(enc[:, : int(n.max())], n, n >= enc_len, st)
+        counts.append((st.current_context_lengths - st.prompt_lengths).tolist())
+    assert counts[0] == [0, 0] and counts[1] == [1, 1] and counts[2] == [2, 2]
+    assert not bool(st.active_samples.any())
+    assert int(st.tokens_frame_alignment[0, 2]) == 16 and int(st.tokens_frame_alignment[0, 3]) == 24
+    laal = comp.compute_laal(st, enc_len, 0.08)
+    assert len(laal) == 2 and all(l == l for l in laal)
+    # AlignAtt: a huge threshold withholds every token until the last chunk; threshold 0 lets tokens out early
+    strict = GreedyBatchedStreamingAEDComputer(dec.embedding, dec.decoder, cls, EOS, AEDStreamingDecodingConfig(
+        streaming_policy="alignatt", waitk_lagging=1, alignatt_thr=1000, max_generation_length=24, frame_chunk_size=8, hallucinations_detector=False))
+    st = strict.init_state(prompt)
+    st = strict(enc[:, :16], torch.tensor([16, 16]), torch.tensor([False, False]), st)
+    assert (st.current_context_lengths - st.prompt_lengths).tolist() == [0, 0]
+    st = strict(enc, enc_len, torch.tensor([True, True]), st)
+    assert cut(st.hypotheses(EOS)) == cut(offline)
+    loose = GreedyBatchedStreamingAEDComputer(dec.embedding, dec.decoder, cls, EOS, AEDStreamingDecodingConfig(
+        streaming_policy="alignatt", waitk_lagging=1, alignatt_thr=0, max_tokens_per_alignatt_step=3, max_generation_length=24, frame_chunk_size=8,
+        hallucinations_detector=False))
+    st = loose(enc[:, :16], torch.tensor([16, 16]), torch.tensor([False, False]), loose.init_state(prompt))
+    assert all(0 < n <= 3 for n in (st.current_context_lengths - st.prompt_lengths).tolist())
+    strict.close(), loose.close()
+    # repeated n-gram tails are flagged
+    st.pred_tokens_ids[0, 2:10] = torch.tensor([7, 8, 7, 8, 7, 8, 7, 8])
+    st.current_context_lengths[0] = 10
+    assert bool(loose.detect_hallucinations(st)[0])
