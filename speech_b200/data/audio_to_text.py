@@ -459,3 +459,18 @@ def build_speech_dataset(config, tokenizer=None, labels=None, global_rank=0, wor
         return AudioToBPEDataset(c["manifest_filepath"], tokenizer, use_start_end_token=c.get("use_start_end_token", False), **common)
     return AudioToCharDataset(c["manifest_filepath"], labels=labels or c.get("labels"), normalize=c.get("normalize_transcripts", False)
                               or c.get("normalize", False), unk_index=c.get("unk_index", -1), **common)
+
+
+def load_audio_file(path) -> Tuple[np.ndarray, int]:
+    """Samples at the file's own rate: float32 ``[n]`` (mono) or ``[n, channels]``, and the sample rate."""
+    if isinstance(path, str) and path.endswith(".npy"):
+        return np.load(path).astype(np.float32), 16000
+    from scipy.io import wavfile
+
+    sr, data = wavfile.read(path)
+    x = data.astype(np.float32)
+    if data.dtype.kind == "i":
+        x /= float(np.iinfo(data.dtype).max) + 1.0
+    elif data.dtype.kind == "u":
+        x = (x - 128.0) / 128.0
+    return x, int(sr)

@@ -131,3 +131,64 @@ def test_model_trains_from_cuts_config(tmp_path):
     tr = Trainer(max_steps=2, accelerator="cpu", log_every_n_steps=1, enable_checkpointing=False, logger=False)
     tr.fit(m)
     assert torch.isfinite(torch.as_tensor(float(tr.callback_metrics["train_loss"])))
+
+
+def test_audio_segment_and_perturbations(tmp_path):
+    import numpy as np
+    from scipy.io import wavfile
+
+    from speech_b200.data.perturb import (AudioAugmentor, AudioSegment, GainPerturbation, ImpulsePerturbation, NoisePerturbation, ShiftPerturbation,
+                                          SilencePerturbation, SpeedPerturbation, TimeStretchPerturbation, TranscodePerturbation,
+                                          WhiteNoisePerturbation, process_augmentations)
+
+    sr = 16000
+    t = np.arange(sr) / sr
+    tone = (0.3 * np.sin(2 * np.pi * 440 * t)).astype(np.float32)
+    wavfile.write(str(tmp_path / "a.wav"), sr, (tone * 32767).astype(np.int16))
+    seg = AudioSegment.from_file(str(tmp_path / "a.wav"), target_sr=8000, offset=0.25, duration=0.5)
+    assert seg.sample_rate == 8000 and abs(seg.num_samples - 4000) <= 2 and abs(seg.rms_db - 20 * np.log10(0.3 / np.sqrt(2))) < 0.5
+    win = AudioSegment.segment_from_file(str(tmp_path / "a.wav"), n_segments=20000)
+    assert win.num_samples == 20000 and float(np.abs(win.samples[16000:]).max()) == 0.0
+    base = AudioSegment(tone, sr)
+    s = AudioSegment(tone, sr)
+    SpeedPerturbation(sr, min_speed_rate=1.25, max_speed_rate=1.25, num_rates=1).perturb(s)
+    assert abs(s.num_samples - sr / 1.25) <= 2
+    spec = np.abs(np.fft.rfft(s.samples))
+    assert abs(np.argmax(spec) * sr / s.num_samples - 550) < 5           # pitch moves with speed
+    s = AudioSegment(tone, sr)
+    TimeStretchPerturbation(min_speed_rate=1.25, max_speed_rate=1.25, num_rates=1).perturb(s)
+    spec = np.abs(np.fft.rfft(s.samples))
+    assert abs(s.num_samples - sr / 1.25) < 600 and abs(np.argmax(spec) * sr / s.num_samples - 440) < 8   # tempo changes, pitch stays
+    s = AudioSegment(tone, sr)
+    GainPerturbation(6, 6).perturb(s)
+    assert abs(s.rms_db - base.rms_db - 6) < 1e-3
+    s = AudioSegment(tone, sr)
+    noise = np.random.RandomState(0).randn(sr // 2).astype(np.float32)
+    NoisePerturbation(noise_items=[{"samples": noise, "sample_rate": sr}], min_snr_db=10, max_snr_db=10, rng=0).perturb(s)
+    resid = s.samples - tone
+    assert abs(10 * np.log10((tone ** 2).mean() / (resid ** 2).mean()) - 10) < 0.5
+    s = AudioSegment(tone, sr)
+    h = np.zeros(400, np.float32)
+    h[0], h[200] = 1.0, 0.5
+    ImpulsePerturbation(impulse_items=[{"samples": h, "sample_rate": sr}], rng=0).perturb(s)
+    expect = tone.copy()
+    expect[200:] += 0.5 * tone[:-200]
+    expect = expect / np.abs(expect).max() * np.abs(tone).max()
+    assert np.abs(s.samples - expect).max() < 1e-3
+    s = AudioSegment(tone, sr)
+    ShiftPerturbation(10, 10).perturb(s)
+    assert float(np.abs(s.samples[:160]).max()) == 0.0 and np.allclose(s.samples[160:], tone[:-160])
+    s = AudioSegment(tone, sr)
+    SilencePerturbation(0.1, 0.1, 0.2, 0.2).perturb(s)
+    assert s.num_samples == sr + 1600 + 3200
+    s = AudioSegment(tone, sr)
+    TranscodePerturbation(["g711"]).perturb(s)
+    assert s.num_samples == sr and 0.5 < np.corrcoef(s.samples, tone)[0, 1] <= 1.0
+    s = AudioSegment(tone, sr)
+    WhiteNoisePerturbation(-40, -39, rng=0).perturb(s)
+    assert 1e-3 < np.abs(s.samples - tone).std() < 2e-2
+    aug = process_augmentations({"gain": {"prob": 1.0, "min_gain_dbfs": -6, "max_gain_dbfs": -6}, "shift": {"prob": 0.0}})
+    out = aug(tone, sr)
+    assert isinstance(aug, AudioAugmentor) and abs(20 * np.log10(np.abs(out).max() / 0.3) + 6) < 0.1
+    with pytest.raises(ValueError):
+        process_augmentations({"pitch_magic": {"prob": 1.0}})
