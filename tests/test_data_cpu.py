@@ -192,3 +192,52 @@ def test_audio_segment_and_perturbations(tmp_path):
     assert isinstance(aug, AudioAugmentor) and abs(20 * np.log10(np.abs(out).max() / 0.3) + 6) < 0.1
     with pytest.raises(ValueError):
         process_augmentations({"pitch_magic": {"prob": 1.0}})
+
+
+def test_feature_datasets_hf_rows_and_multispeaker_simulator(tmp_path):
+    import json
+
+    import numpy as np
+
+    from speech_b200.data.extra_datasets import (AudioToCharDALIDataset, FeatureToLabelDataset, FeatureToTextDataset, HFAudioToTextDataset,
+                                                 MultiSpeakerSimulator, TextToTextDataset)
+    from speech_b200.tokenizers import CharTokenizer
+
+    feats = []
+    for k, T in enumerate((30, 50)):
+        np.save(tmp_path / f"f{k}.npy", np.random.randn(8, T).astype(np.float32))
+        feats.append(str(tmp_path / f"f{k}.npy"))
+    (tmp_path / "lab.json").write_text("\n".join(json.dumps({"feature_file": f, "label": l}) for f, l in zip(feats, ("speech", "noise"))))
+    ds = FeatureToLabelDataset(str(tmp_path / "lab.json"), labels=["noise", "speech"])
+    x, xl, y, yl = ds.collate_fn([ds[0], ds[1]])
+    assert x.shape == (2, 8, 50) and xl.tolist() == [30, 50] and y[:, 0].tolist() == [1, 0] and float(x[0, 0, 40]) == pytest.approx(-16.635)
+    (tmp_path / "seq.json").write_text(json.dumps({"feature_file": feats[0], "label": "0 1 1 0"}))
+    y = FeatureToLabelDataset(str(tmp_path / "seq.json"), delimiter=" ")[0][2]
+    assert y.tolist() == [0, 1, 1, 0]
+    (tmp_path / "a.rttm").write_text("SPEAKER a 1 0.10 0.10 <NA> <NA> s <NA> <NA>\n")
+    (tmp_path / "txt.json").write_text(json.dumps({"feature_file": feats[0], "text": "ab a", "rttm_file": str(tmp_path / "a.rttm")}))
+    tok = CharTokenizer(list(" ab"))
+    ft = FeatureToTextDataset(str(tmp_path / "txt.json"), tokenizer=tok, use_rttm=True, rttm_mode="mask", feat_mask_val=-9.0)
+    f, fl, t, tl = ft[0]
+    assert int(tl) == 4 and float(f[0, 5]) == -9.0 and float(f[0, 15]) != -9.0
+    dropped = FeatureToTextDataset(str(tmp_path / "txt.json"), tokenizer=tok, use_rttm=True, rttm_mode="drop")[0][0]
+    assert dropped.shape[-1] == 11
+    (tmp_path / "t.txt").write_text("ab\nba ab\n")
+    tt = TextToTextDataset(str(tmp_path / "t.txt"), tok)
+    s, sl, g, gl = tt.collate_fn([tt[0], tt[1]])
+    assert s.shape == (2, 5) and sl.tolist() == [2, 5] and torch.equal(s, g)
+    rows = [{"audio": {"array": np.random.randn(800).astype(np.float32), "sampling_rate": 8000}, "text": "AB a!"}]
+    hf = HFAudioToTextDataset(data=rows, tokenizer=tok, sample_rate=16000, normalize_text=True)
+    a, al, t, tl = hf[0]
+    assert int(al) == 1600 and tok.ids_to_text(t.tolist()) == "ab a"
+    with pytest.raises(ImportError):
+        AudioToCharDALIDataset()
+    items = [{"samples": np.full(8000, 0.1 * (k + 1), np.float32), "speaker_id": f"s{k % 3}", "text": f"w{k}"} for k in range(9)]
+    sim = MultiSpeakerSimulator(items, sample_rate=8000, num_speakers=2, session_length=10.0, overlap_prob=0.5, seed=1)
+    out = sim.generate_sessions(1, output_dir=str(tmp_path / "sim"))[0]
+    assert out["audio"].shape == (80000,) and len(out["speakers"]) == 2 and len(out["rttm"]) >= 5
+    assert {s["speaker"] for s in out["segments"]} <= set(out["speakers"]) and all(s["end"] <= 10.0 + 1e-6 for s in out["segments"])
+    overlaps = sum(1 for a, b in zip(out["segments"], out["segments"][1:]) if b["start"] < a["end"])
+    assert overlaps >= 1
+    man = json.loads(open(tmp_path / "sim" / "manifest.json").read().strip())
+    assert man["num_speakers"] == 2 and man["rttm_filepath"].endswith(".rttm")
