@@ -79,7 +79,89 @@ def rnn(input_size, hidden_size, num_layers, norm=None, forget_gate_bias=1.0, dr
     if norm is None:
         return LSTMDropout(input_size, hidden_size, num_layers, dropout, forget_gate_bias, t_max, weights_init_scale,
                            hidden_hidden_bias_scale, proj_size)
-    raise NotImplementedError("batch / layer normalised LSTM variants are not provided; use norm=None")
+    if norm == "batch":
+        return BNRNNSum(input_size, hidden_size, rnn_layers=num_layers, batch_norm=True, dropout=dropout, forget_gate_bias=forget_gate_bias,
+                        norm_first_rnn=bool(norm_first_rnn), t_max=t_max, weights_init_scale=weights_init_scale,
+                        hidden_hidden_bias_scale=hidden_hidden_bias_scale, proj_size=proj_size)
+    return LayerNormLSTM(input_size, hidden_size, num_layers, dropout, forget_gate_bias, t_max, weights_init_scale, hidden_hidden_bias_scale)
+
+
+class BNRNNSum(nn.Module):
+    """Stack of single-layer LSTMs with BatchNorm over the features in front of each layer (optionally the first too); state
+    is threaded per layer.  Reference: ``common/parts/rnn.py:287`` (``BNRNNSum`` / ``StackTime``-free variant)."""
+
+    def __init__(self, input_size, hidden_size, rnn_layers=1, batch_norm=True, dropout=0.0, forget_gate_bias=1.0, norm_first_rnn=False,
+                 t_max=None, weights_init_scale=1.0, hidden_hidden_bias_scale=0.0, proj_size=0):
+        super().__init__()
+        self.rnn_layers = rnn_layers
+        self.layers = nn.ModuleList()
+        for i in range(rnn_layers):
+            in_size = input_size if i == 0 else (proj_size or hidden_size)
+            bn = nn.BatchNorm1d(in_size) if batch_norm and (i > 0 or norm_first_rnn) else None
+            self.layers.append(nn.ModuleDict({"bn": bn if bn is not None else nn.Identity(),
+                                              "rnn": LSTMDropout(in_size, hidden_size, 1, dropout if i + 1 < rnn_layers else 0.0, forget_gate_bias, t_max,
+                                                                 weights_init_scale, hidden_hidden_bias_scale, proj_size)}))
+
+    def forward(self, x, hx=None):
+        """x [T, B, D]; hx = (h [L, B, H], c [L, B, H]) or None."""
+        hs, cs = [], []
+        for i, l in enumerate(self.layers):
+            if isinstance(l["bn"], nn.BatchNorm1d):
+                x = l["bn"](x.permute(1, 2, 0).float()).permute(2, 0, 1).to(x.dtype)
+            st = None if hx is None else (hx[0][i:i + 1].contiguous(), hx[1][i:i + 1].contiguous())
+            x, (h, c) = l["rnn"](x, st)
+            hs.append(h)
+            cs.append(c)
+        return x, (torch.cat(hs, 0), torch.cat(cs, 0))
+
+
+class LayerNormLSTM(nn.Module):
+    """LSTM whose gate pre-activations (input and recurrent parts separately) and cell state are layer-normalised
+    (``common/parts/rnn.py:407`` ``ln_lstm``).  The recurrence is a Python loop over time: a training-quality variant for the
+    prediction network, where sequences are short."""
+
+    def __init__(self, input_size, hidden_size, num_layers, dropout=0.0, forget_gate_bias=1.0, t_max=None, weights_init_scale=1.0,
+                 hidden_hidden_bias_scale=0.0):
+        super().__init__()
+        self.num_layers, self.hidden_size = num_layers, hidden_size
+        self.cells = nn.ModuleList()
+        for i in range(num_layers):
+            d = input_size if i == 0 else hidden_size
+            cell = nn.ModuleDict({"ih": nn.Linear(d, 4 * hidden_size), "hh": nn.Linear(hidden_size, 4 * hidden_size),
+                                  "ln_i": nn.LayerNorm(4 * hidden_size), "ln_h": nn.LayerNorm(4 * hidden_size), "ln_c": nn.LayerNorm(hidden_size)})
+            with torch.no_grad():
+                if forget_gate_bias is not None:
+                    cell["ih"].bias[hidden_size:2 * hidden_size].fill_(forget_gate_bias)
+                    cell["hh"].bias[hidden_size:2 * hidden_size].mul_(float(hidden_hidden_bias_scale))
+                for p in (cell["ih"].weight, cell["hh"].weight, cell["ih"].bias, cell["hh"].bias):
+                    p.mul_(float(weights_init_scale))
+            self.cells.append(cell)
+        self.dropout = nn.Dropout(dropout) if dropout else None
+
+    def forward(self, x, hx=None):
+        T, B, _ = x.shape
+        H = self.hidden_size
+        x = x.float()
+        hs, cs = [], []
+        for i, cell in enumerate(self.cells):
+            h = x.new_zeros(B, H) if hx is None else hx[0][i].float()
+            c = x.new_zeros(B, H) if hx is None else hx[1][i].float()
+            gi_all = cell["ln_i"](cell["ih"](x))
+            outs = []
+            for t in range(T):
+                g = gi_all[t] + cell["ln_h"](cell["hh"](h))
+                i_g, f_g, g_g, o_g = g.chunk(4, dim=-1)
+                c = cell["ln_c"](torch.sigmoid(f_g) * c + torch.sigmoid(i_g) * torch.tanh(g_g))
+                h = torch.sigmoid(o_g) * torch.tanh(c)
+                outs.append(h)
+            x = torch.stack(outs)
+            if self.dropout is not None and i + 1 < self.num_layers:
+                x = self.dropout(x)
+            hs.append(h)
+            cs.append(c)
+        if self.dropout is not None:
+            x = self.dropout(x)
+        return x, (torch.stack(hs), torch.stack(cs))
 
 
 def label_collate(labels, device=None):

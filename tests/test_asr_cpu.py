@@ -198,3 +198,21 @@ def test_graph_rnnt_and_w_transducer_losses_match_explicit_lattice_dp():
     v = via(log_probs=logits.detach().float(), targets=labels, input_lengths=act_lens, target_lengths=label_lens)
     exp = [-lattice(lp[b], labels[b].tolist(), int(act_lens[b]), int(label_lens[b]), -1.5, "force_final") for b in range(B)]
     assert torch.allclose(v, torch.tensor(exp, dtype=torch.float32), atol=1e-3)
+
+
+def test_normalised_lstm_variants_thread_state():
+    from speech_b200.modules.rnnt import BNRNNSum, LayerNormLSTM, rnn
+
+    torch.manual_seed(0)
+    for norm, cls in (("batch", BNRNNSum), ("layer", LayerNormLSTM)):
+        m = rnn(16, 24, 2, norm=norm, dropout=0.0, norm_first_rnn=True).eval()
+        assert isinstance(m, cls)
+        x = torch.randn(7, 3, 16)
+        y, (h, c) = m(x)
+        y1, st = m(x[:4])
+        y2, _ = m(x[4:], st)
+        assert y.shape == (7, 3, 24) and h.shape == c.shape == (2, 3, 24)
+        assert torch.allclose(torch.cat([y1, y2]), y, atol=1e-6)
+        y.sum().backward()
+    with pytest.raises(ValueError):
+        rnn(16, 24, 1, norm="instance")
