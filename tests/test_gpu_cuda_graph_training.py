@@ -1,0 +1,49 @@
+"""Whole-iteration CUDA-graph training callback: replayed iterations follow the eager loss trajectory."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(with_graph: bool, steps: int = 8):
+    from speech_b200.core.config import open_dict
+    from speech_b200.core.trainer import Trainer
+    from speech_b200.models import EncDecCTCModelBPE
+    from speech_b200.models.configs import fastconformer_ctc_config
+    from speech_b200.utils.callbacks_extra import CUDAGraphCallback
+
+    torch.manual_seed(0)
+    cfg = fastconformer_ctc_config("small", vocab_size=128, n_layers=2, dropout=0.0) if "dropout" in fastconformer_ctc_config.__code__.co_varnames \
+        else fastconformer_ctc_config("small", vocab_size=128, n_layers=2)
+    with open_dict(cfg):
+        cfg.train_ds = {"synthetic": {"num_samples": 4, "vocab_size": 128, "min_duration": 2.0, "max_duration": 2.0, "max_tokens_frac_of_frames": 0.5,
+                                      "token_low": 0, "fixed_tokens": 8}, "batch_size": 4, "shuffle": False}
+        cfg.spec_augment = None
+    model = EncDecCTCModelBPE(cfg)
+    for m in model.modules():
+        if isinstance(m, torch.nn.Dropout):
+            m.p = 0.0
+        for attr in ("dropout_rate",):
+            if hasattr(m, attr):
+                setattr(m, attr, 0.0)
+    losses = []
+
+    class Rec:
+        def on_train_batch_end(self, trainer, m, out, batch, idx):
+            losses.append(float(out["loss"]))
+
+    cb = CUDAGraphCallback(warmup_steps=2, max_graphs=2)
+    tr = Trainer(max_steps=steps, accelerator="gpu", precision="bf16-mixed", callbacks=[Rec()] + ([cb] if with_graph else []), log_every_n_steps=10 ** 9,
+                 enable_checkpointing=False, logger=False)
+    tr.fit(model)
+    return losses, cb
+
+
+def test_graph_replay_follows_the_eager_trajectory():
+    eager, _ = _run(False)
+    graphed, cb = _run(True)
+    assert cb.replays >= 4 and len(cb.graphs) == 1
+    assert len(eager) == len(graphed) == 8
+    assert all(l == l for l in graphed) and graphed[-1] < graphed[0]
+    # bf16 training with atomically accumulated BatchNorm statistics is not bit-reproducible: compare loosely
+    assert max(abs(a - b) / max(abs(a), 1.0) for a, b in zip(eager, graphed)) < 0.05

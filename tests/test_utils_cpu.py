@@ -83,3 +83,78 @@ def test_sharded_checkpoint_io_sync_and_async(tmp_path):
     back = io_.load(str(tmp_path / "ck"))
     assert back["step"] == 3 and torch.equal(back["exp_avg"], torch.arange(4.0))
     assert len(io_.load_all(str(tmp_path / "ck"))) == 1
+
+
+def test_callback_group_object_store_io_and_hf_directory(tmp_path):
+    import torch
+
+    from speech_b200.core.config import OmegaConf
+    from speech_b200.utils.callbacks_extra import (CallbackGroup, EventRecorder, HuggingFaceFileIO, NsightProfiling, ObjectStoreCheckpointIO,
+                                                   StaticBufferLoader, hook_class_init_with_callbacks)
+
+    group = CallbackGroup.get_instance()
+    group.clear()
+    rec = EventRecorder(clock=iter(range(100)).__next__)
+    group.register(rec)
+    assert CallbackGroup.get_instance() is group
+
+    class Thing:
+        def __init__(self, v):
+            self.v = v
+
+    hook_class_init_with_callbacks(Thing, "on_model_init_start", "on_model_init_end")
+    assert Thing(3).v == 3
+    group.on_save_checkpoint_start(iteration=1)
+    group.some_event_nobody_handles()
+    assert [e for e, _ in rec.events] == ["on_model_init_start", "on_model_init_end", "on_save_checkpoint_start"]
+    group.clear()
+
+    class FakeS3:
+        def __init__(self):
+            self.store = {}
+
+        def upload_file(self, local, bucket, key):
+            self.store[(bucket, key)] = open(local, "rb").read()
+
+        def download_file(self, bucket, key, local):
+            open(local, "wb").write(self.store[(bucket, key)])
+
+        def delete_object(self, Bucket, Key):
+            del self.store[(Bucket, Key)]
+
+    s3 = FakeS3()
+    io = ObjectStoreCheckpointIO(client=s3, staging_dir=str(tmp_path / "stage"), async_checkpointing=True)
+    io.save_checkpoint({"w": torch.arange(4)}, "s3://bucket/run/step=4.ckpt")
+    io.wait()
+    assert ("bucket", "run/step=4.ckpt") in s3.store and not os.listdir(tmp_path / "stage")
+    assert torch.equal(io.load_checkpoint("s3://bucket/run/step=4.ckpt")["w"], torch.arange(4))
+    io.remove_checkpoint("s3://bucket/run/step=4.ckpt")
+    assert not s3.store
+    io.save_checkpoint({"w": torch.ones(2)}, str(tmp_path / "local" / "a.ckpt"))
+    assert torch.equal(io.load_checkpoint(str(tmp_path / "local" / "a.ckpt"))["w"], torch.ones(2))
+    with pytest.raises(ImportError):
+        ObjectStoreCheckpointIO(staging_dir=str(tmp_path / "stage")).load_checkpoint("s3://b/k")
+
+    from speech_b200.core.instantiate import allow_prefix
+
+    allow_prefix("test_utils_cpu.")
+    global _TinyHF
+
+    class _TinyHF(torch.nn.Module, HuggingFaceFileIO):
+        def __init__(self, cfg):
+            super().__init__()
+            self.cfg = cfg
+            self.lin = torch.nn.Linear(cfg.d, cfg.d)
+
+    m = _TinyHF(OmegaConf.create({"d": 3}))
+    m.save_pretrained(str(tmp_path / "hf"))
+    again = _TinyHF.from_pretrained(str(tmp_path / "hf"))
+    assert torch.equal(again.lin.weight, m.lin.weight)
+    with pytest.raises((FileNotFoundError, Exception)):
+        _TinyHF.from_pretrained(str(tmp_path / "missing"))
+    loader = StaticBufferLoader(torch.device("cpu"))
+    a = loader.load((torch.ones(2, 3), {"k": torch.zeros(4)}))
+    b = loader.load((torch.full((2, 3), 5.0), {"k": torch.ones(4)}))
+    assert a[0] is b[0] and float(b[0][0, 0]) == 5.0 and len(loader.buffers) == 1
+    with pytest.raises(ValueError):
+        NsightProfiling(5, 2)
