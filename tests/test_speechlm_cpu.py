@@ -171,3 +171,46 @@ def test_packed_sequences_cp_partition_chunking_and_metrics():
     lg = torch.zeros(1, 3, 5)
     lg[0, 0, 2] = lg[0, 1, 1] = lg[0, 2, 0] = 5.0
     assert parts.token_accuracy(lg, torch.tensor([[2, 4, -100]])) == 0.5
+
+
+def test_duplex_models_and_salm_variants():
+    from speech_b200.speechlm.duplex import DuplexS2SModel, DuplexSTTModel, SALMAutomodel, SALMWithAsrDecoder
+
+    torch.manual_seed(0)
+    pc = {"preprocessor": {**preprocessor_cfg(32), "dither": 0.0}, "encoder": encoder_cfg("small", 32, 0.0, 0.0, n_layers=1),
+          "modality_adapter": {"_target_": "speech_b200.speechlm.perception.IdentityConnector", "d_model": 176}}
+    cfg = OmegaConf.create({"llm": dict(TINY), "perception": pc, "codebook_size": 10, "num_codebooks": 2, "optim": {"name": "adamw", "lr": 1e-3}})
+    audio, lens = torch.randn(2, 16000), torch.tensor([16000, 12000])
+    stt = DuplexSTTModel(cfg)
+    T = 30
+    tgt = torch.randint(3, 50, (2, T))
+    loss = stt.training_step({"source_audio": audio, "source_audio_lens": lens, "target_tokens": tgt}, 0)["loss"]
+    loss.backward()
+    assert math.isfinite(float(loss)) and stt.embed_tokens.weight.grad is not None
+    res = stt.offline_inference(audio, lens)
+    assert res["tokens"].shape[0] == 2 and res["tokens"].shape[1] == int(res["lengths"].max()) and len(res["text"]) == 2
+    # incremental frame-by-frame decoding equals teacher-forced decoding on its own outputs
+    inp_prev = torch.cat([torch.full((2, 1), stt.text_pad_id), res["tokens"][:, :-1]], dim=1)
+    emb, _ = stt.perception(input_signal=audio, input_signal_length=lens)
+    full = stt(stt._frame_inputs(emb, inp_prev))["text_logits"].argmax(-1)
+    assert torch.equal(full, res["tokens"])
+    s2s = DuplexS2SModel(cfg)
+    codes = torch.randint(0, 10, (2, T, 2))
+    l = s2s.training_step({"source_audio": audio, "source_audio_lens": lens, "target_tokens": tgt, "target_codes": codes}, 0)["loss"]
+    l.backward()
+    assert math.isfinite(float(l)) and s2s.audio_head.weight.grad is not None and s2s.speech_vocab_size == 13
+    out = s2s.offline_inference(audio, lens, decode_audio=False)
+    assert out["codes"].shape == (2, out["tokens"].shape[1], 2) and int(out["codes"].max()) < 13
+    tok = ByteLevelTokenizer(special_tokens=["<pad>", "<s>", "</s>", "<|im_start|>", "<|im_end|>"])
+    scfg = OmegaConf.create({"audio_locator_tag": "<|audioplaceholder|>", "prompt_format": "qwen", "llm": dict(TINY, tie_word_embeddings=True), "perception": pc,
+                             "freeze_params": [], "prevent_freeze_params": [], "asr_weight": 0.5, "optim": {"name": "adamw", "lr": 1e-3}})
+    m = SALMWithAsrDecoder(scfg, tokenizer=tok)
+    emb, el = m.perception(input_signal=audio, input_signal_length=lens)
+    aux = m.asr_loss(emb, el, torch.randint(5, 200, (2, 6)), torch.tensor([6, 4]))
+    aux.backward()
+    assert math.isfinite(float(aux)) and m.asr_head.weight.grad is not None
+    hyp = m.transcribe_with_asr_head(audio, lens)
+    assert len(hyp) == 2 and all(isinstance(h, list) for h in hyp)
+    auto = SALMAutomodel(scfg, tokenizer=tok)
+    auto.configure_model(None)
+    assert auto.device_mesh is None
