@@ -158,3 +158,44 @@ def test_callback_group_object_store_io_and_hf_directory(tmp_path):
     assert a[0] is b[0] and float(b[0][0, 0]) == 5.0 and len(loader.buffers) == 1
     with pytest.raises(ValueError):
         NsightProfiling(5, 2)
+
+
+def test_extra_tokenizers_and_chat_template():
+    from speech_b200.tokenizers import ByteLevelTokenizer
+    from speech_b200.tokenizers.extra import (ChatTemplateMixin, ChineseCharsTokenizer, EnJaProcessor, MosesProcessor, NullTokenizer, RegExTokenizer,
+                                              TiktokenTokenizer, WordTokenizer)
+
+    w = WordTokenizer(vocab=["hello", "world"], bos_token="<s>", eos_token="</s>")
+    assert w.text_to_ids("hello there world") == [4, w.unk_id, 5] and w.ids_to_text([4, 5]) == "hello world" and w.vocab_size == 6
+    r = RegExTokenizer()
+    r.build_vocab_from_text(["CC(=O)Cl", "[NH4+]Br"])
+    ids = r.text_to_ids("CC(=O)Cl")
+    assert r.ids_to_text(ids) == "CC(=O)Cl" and r.text_to_tokens("[NH4+]Br") == ["[NH4+]", "Br"]
+    n = NullTokenizer(100)
+    assert n.text_to_ids("3 14 15") == [3, 14, 15] and n.ids_to_text([9, 2]) == "9 2" and n.vocab_size == 100
+    c = ChineseCharsTokenizer(vocab=list("你好世界") + ["ok"])
+    toks = c.text_to_tokens("你好 ok 世界")
+    assert toks == ["你", "好", "ok", "世", "界"] and c.tokens_to_text(toks) == "你好ok世界" and c.tokens_to_text(["ok", "go", "你"]) == "ok go你"
+    mp = MosesProcessor("en")
+    t = mp.tokenize("Hello, world! It's fine.")
+    assert t == "Hello , world ! It 's fine ." and mp.detokenize(t.split()) == "Hello, world! It's fine."
+    assert EnJaProcessor("ja").detokenize(EnJaProcessor("ja").tokenize("こんにちは").split()) == "こんにちは"
+    try:
+        import tiktoken  # noqa: F401
+        have = True
+    except ImportError:
+        have = False
+    if not have:
+        with pytest.raises(ImportError):
+            TiktokenTokenizer("missing.json")
+
+    class Tok(ByteLevelTokenizer, ChatTemplateMixin):
+        pass
+
+    tk = Tok()
+    msgs = [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "yo"}]
+    s = tk.apply_chat_template(msgs, add_generation_prompt=True)
+    assert s == "<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\nyo<|im_end|>\n<|im_start|>assistant\n"
+    enc = tk.apply_chat_template(msgs, tokenize=True)
+    assert len(enc["input_ids"]) == len(enc["assistant_mask"]) and 0 < sum(enc["assistant_mask"]) < len(enc["input_ids"])
+    assert tk.apply_chat_template(msgs, template="llama3").startswith("<|begin_of_text|><|start_header_id|>user")
