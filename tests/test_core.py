@@ -184,3 +184,50 @@ def test_fused_adamw_cpu_matches_torch_and_fusion_views():
         assert torch.allclose(p, r, atol=1e-6)
     sd = opt.state_dict()
     opt.load_state_dict(sd)
+
+
+def test_ema_optimizer_and_main_params_wrapper():
+    import torch
+
+    from speech_b200.core.optim.wrappers import EMAOptimizer, MainParamsOptimizerWrapper
+
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(4, 3)
+    opt = EMAOptimizer(torch.optim.SGD(lin.parameters(), lr=0.5), decay=0.5)
+    w0 = lin.weight.detach().clone()
+    lin(torch.ones(2, 4)).sum().backward()
+    opt.step()
+    w1 = lin.weight.detach().clone()
+    assert torch.allclose(opt.ema_params[0], w1)            # first step: the average starts at the weights
+    opt.zero_grad()
+    lin(torch.ones(2, 4)).sum().backward()
+    opt.step()
+    w2 = lin.weight.detach().clone()
+    assert torch.allclose(opt.ema_params[0], 0.5 * w1 + 0.5 * w2, atol=1e-6) and not torch.equal(w0, w2)
+    with opt.swap_ema_weights():
+        assert torch.allclose(lin.weight, 0.5 * w1 + 0.5 * w2, atol=1e-6)
+    assert torch.equal(lin.weight, w2)
+    sd = opt.state_dict()
+    opt2 = EMAOptimizer(torch.optim.SGD(lin.parameters(), lr=0.5), decay=0.9)
+    opt2.load_state_dict(sd)
+    assert opt2.decay == 0.5 and opt2.current_step == 2 and torch.equal(opt2.ema_params[0], opt.ema_params[0])
+    # bf16 model, fp32 main weights: tiny updates are not lost to bf16 rounding
+    m = torch.nn.Linear(8, 8, bias=False).to(torch.bfloat16)
+    with torch.no_grad():
+        m.weight.fill_(1.0)
+    wrap = MainParamsOptimizerWrapper(m.parameters(), lambda ps: torch.optim.SGD(ps, lr=1e-3), fp32_grad_accum=True)
+    for _ in range(40):
+        wrap.zero_grad()
+        m(torch.ones(1, 8, dtype=torch.bfloat16)).sum().backward()
+        assert m.weight.grad is None and float(wrap.main_params[0].grad.abs().sum()) > 0
+        wrap.step()
+    assert abs(float(wrap.main_params[0][0, 0]) - (1.0 - 40 * 1e-3)) < 1e-5 and abs(float(m.weight[0, 0]) - 0.96) < 0.004
+    naive = torch.nn.Linear(8, 8, bias=False).to(torch.bfloat16)
+    with torch.no_grad():
+        naive.weight.fill_(1.0)
+    o = torch.optim.SGD(naive.parameters(), lr=1e-3)
+    for _ in range(40):
+        o.zero_grad()
+        naive(torch.ones(1, 8, dtype=torch.bfloat16)).sum().backward()
+        o.step()
+    assert float(naive.weight[0, 0]) == 1.0               # every update rounds away in bf16
