@@ -115,3 +115,73 @@ def test_buffered_ctc_pipeline_runs_and_times_words():
         assert isinstance(o.text, str)
         for w in o.words:
             assert 0.0 <= w.start <= w.end
+
+
+def test_inverse_text_normalisation_and_translation_hook():
+    from speech_b200.inference.text_postprocess import InverseTextNormalizer, TranslationHook
+
+    n = InverseTextNormalizer()
+    assert n("i have twenty three apples and one hundred and five pears") == "i have 23 apples and 105 pears"
+    assert n("it costs fifteen dollars or three point one four percent") == "it costs $15 or 3.14%"
+    assert n("the twenty first of may at seven o'clock") == "the 21st of may at 7:00"
+    assert n("two thousand twenty five was the third year") == "2025 was the 3rd year"
+    assert n("one of them came forty-second") == "one of them came 42nd"
+    assert n.normalize_list(["one hundred", "no numbers"]) == ["100", "no numbers"]
+    hook = TranslationHook(lambda xs: [x.upper() for x in xs], batch_size=2)
+    assert hook(["a", "b", "c"]) == ["A", "B", "C"]
+    import pytest
+
+    with pytest.raises(RuntimeError):
+        TranslationHook(lambda xs: xs[:-1])(["a", "b"])
+
+
+def test_voice_agent_pipeline_turns_tools_and_barge_in(tmp_path):
+    import os
+
+    import numpy as np
+
+    from speech_b200.agents.voice_agent import (AudioRawFrame, BotInterruptionFrame, EndFrame, LLMTextFrame, ToolCallFrame, TranscriptionFrame,
+                                                TTSAudioFrame, UserStoppedSpeakingFrame, build_voice_agent)
+
+    heard = []
+
+    def stt(chunk):                       # a stand-in recogniser: one more word per loud chunk
+        if float(np.abs(chunk).mean()) > 0.05:
+            heard.append("word")
+        return " ".join(heard), False
+
+    calls = []
+
+    def llm(messages):
+        calls.append([m["role"] for m in messages])
+        if messages[-1]["role"] == "tool":
+            return "It is 7 degrees. Bring a coat!"
+        return '{"tool": "weather", "arguments": {"city": "Oslo"}}'
+
+    def tts(text):
+        return np.full(800, 0.1, np.float32), 8000
+
+    agent = build_voice_agent(stt, llm, tts, diar_step=lambda a: np.tile(np.array([[0.1, 0.9]]), (4, 1)), log_dir=str(tmp_path),
+                              system_prompt="be brief", tools={"weather": lambda city: {"city": city, "temp_c": 7}}, max_silence=0.3)
+    sr = 16000
+    loud, quiet = np.full(1600, 0.2, np.float32), np.zeros(1600, np.float32)
+    frames = [AudioRawFrame(0.1 * i, loud, sr) for i in range(5)] + [AudioRawFrame(0.5 + 0.1 * i, quiet, sr) for i in range(4)]
+    out = agent.run(frames)
+    kinds = [type(f).__name__ for f in out]
+    assert "UserStartedSpeakingFrame" in kinds and "UserStoppedSpeakingFrame" in kinds
+    finals = [f for f in out if isinstance(f, TranscriptionFrame) and f.is_final]
+    assert len(finals) == 1 and finals[0].text == "word word word word word" and finals[0].speaker == "speaker_1"
+    tool = [f for f in out if isinstance(f, ToolCallFrame)]
+    assert tool and tool[0].result == {"city": "Oslo", "temp_c": 7}
+    reply = [f for f in out if isinstance(f, LLMTextFrame)]
+    assert reply[0].text == "It is 7 degrees. Bring a coat!" and calls[0] == ["system", "user"] and calls[1][-1] == "tool"
+    audio = [f for f in out if isinstance(f, TTSAudioFrame)]
+    assert [a.text for a in audio] == ["It is 7 degrees.", "Bring a coat!"]           # sentence-wise synthesis
+    # barge-in: the user speaks while the bot is talking
+    heard.clear()
+    out2 = agent.run([TTSAudioFrame(2.0, np.zeros(10, np.float32), 8000, "x")] + [AudioRawFrame(2.0 + 0.1 * i, loud, sr) for i in range(3)])
+    assert any(isinstance(f, BotInterruptionFrame) for f in out2)
+    agent.run([EndFrame(9.0)])
+    assert os.path.exists(tmp_path / "session" / "user.wav") and os.path.exists(tmp_path / "session" / "bot.wav")
+    lines = open(tmp_path / "session" / "events.jsonl").read().strip().splitlines()
+    assert any('"LLMTextFrame"' in l for l in lines)
