@@ -274,3 +274,48 @@ class BatchedFrameASRRNNT(FrameBatchASR):
             else:
                 merged.extend(y for y, t in zip(ys, ts) if lo <= t < lo + tpc)
         return self.asr_model.decoding.decode_tokens_to_str(merged)
+
+
+BatchedFrameASRTDT = BatchedFrameASRRNNT   # TDT models decode through the same transducer interface (durations handled by the decoder)
+
+
+class FrameBatchMultiTaskAED:
+    """Chunked inference for attention encoder-decoder models on long recordings: the audio is cut into windows of ``chunk_len``
+    seconds (the final short remainder is merged into the previous window), each window is transcribed with the model's prompt
+    and the texts are joined.  Reference: ``parts/utils/streaming_utils.py`` ``FrameBatchMultiTaskAED`` (window batching +
+    prompt per window, text joined with spaces)."""
+
+    def __init__(self, asr_model, chunk_len: float = 30.0, batch_size: int = 4, min_tail: float = 1.0, sample_rate: Optional[int] = None):
+        self.asr_model, self.chunk_len, self.batch_size, self.min_tail = asr_model, chunk_len, batch_size, min_tail
+        pre = getattr(asr_model, "preprocessor", None)
+        feat = getattr(pre, "featurizer", pre)
+        self.sr = int(sample_rate or getattr(feat, "sample_rate", 16000))
+        self.samples: Optional[torch.Tensor] = None
+        self.meta: dict = {}
+
+    def read_audio_file(self, path_or_array, meta_data: Optional[dict] = None, **_):
+        if isinstance(path_or_array, str):
+            from ..data.audio_to_text import load_audio
+
+            path_or_array = load_audio(path_or_array, target_sr=self.sr)
+        self.samples = torch.as_tensor(path_or_array, dtype=torch.float32).reshape(-1)
+        self.meta = dict(meta_data or {})
+
+    def windows(self) -> List[torch.Tensor]:
+        n = int(self.chunk_len * self.sr)
+        chunks = list(self.samples.split(n))
+        if len(chunks) > 1 and chunks[-1].numel() < int(self.min_tail * self.sr):
+            chunks[-2] = torch.cat([chunks[-2], chunks[-1]])
+            chunks.pop()
+        return chunks
+
+    @torch.no_grad()
+    def transcribe(self, **transcribe_kwargs) -> str:
+        texts: List[str] = []
+        wins = self.windows()
+        for s in range(0, len(wins), self.batch_size):
+            batch = [w.numpy() for w in wins[s:s + self.batch_size]]
+            hyps = self.asr_model.transcribe(batch, batch_size=len(batch), **{**self.meta, **transcribe_kwargs})
+            hyps = hyps[0] if isinstance(hyps, tuple) else hyps
+            texts += [h.text if hasattr(h, "text") else str(h) for h in hyps]
+        return " ".join(t.strip() for t in texts if t and t.strip())

@@ -185,3 +185,15 @@ def test_voice_agent_pipeline_turns_tools_and_barge_in(tmp_path):
     assert os.path.exists(tmp_path / "session" / "user.wav") and os.path.exists(tmp_path / "session" / "bot.wav")
     lines = open(tmp_path / "session" / "events.jsonl").read().strip().splitlines()
     assert any('"LLMTextFrame"' in l for l in lines)
+
+
+def test_chunked_aed_inference_merges_short_tail():
+    from speech_b200.utils.streaming_utils import BatchedFrameASRRNNT, BatchedFrameASRTDT, FrameBatchMultiTaskAED
+
+    class M:
+        def transcribe(self, audio, batch_size=1, **kw):
+            return [f"len{len(a)}" for a in audio]
+
+    f = FrameBatchMultiTaskAED(M(), chunk_len=1.0, batch_size=2, min_tail=0.5, sample_rate=100)
+    f.read_audio_file(torch.zeros(330))
+    assert f.transcribe() == "len100 len100 len130" and BatchedFrameASRTDT is BatchedFrameASRRNNT
