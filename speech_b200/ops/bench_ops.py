@@ -37,7 +37,7 @@ def bench_gemm(a):
     D = [torch.empty(M, N, device=dev, dtype=torch.bfloat16) for _ in range(nv)]
     bias = torch.randn(N, device=dev, dtype=torch.float32) if a.epilogue != "none" else None
     act = "swish" if a.epilogue == "bias_swish" else None
-    ms = _time(lambda i: native.gemm(A[i], B[i], D[i], M=M, N=N, K=K, bias=bias, act=act, tile_n=a.tile_n), nv, a.iters, a.warmup)
+    ms = _time(lambda i: native.gemm(A[i], B[i], D[i], M=M, N=N, K=K, bias=bias, act=act, tile_n=a.tile_n, pair=a.pair), nv, a.iters, a.warmup)
     ms_lib = _time(lambda i: torch.matmul(A[i], B[i].t(), out=D[i]), nv, a.iters, a.warmup)
     native.check_status()
     fl = 2.0 * M * N * K
@@ -96,6 +96,7 @@ def main():
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--epilogue", default="none", choices=["none", "bias", "bias_swish"])
     ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--pair", type=int, default=0, help="1: CTA-pair (cta_group::2) variant, -1: never, 0: default policy")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     a = ap.parse_args()

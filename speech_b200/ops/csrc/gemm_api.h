@@ -30,7 +30,7 @@ struct SbGemmArgs {
   float drop_p;     // > 0: dropout applied to act(acc + bias) before alpha / residual; mask = sb_dropout_keep(seed, m * N + n)
   unsigned long long drop_seed;
   int ksplit;       // 0 = automatic, -1 = never split K, > 1 = that many K slices (only honoured for D(fp32) += alpha * A B^T)
-  int pad_;
+  int pair;         // 0 = default policy, 1 = use CTA pairs (cta_group::2) when the shape allows, -1 = never
 };
 
 

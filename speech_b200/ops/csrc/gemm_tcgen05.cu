@@ -22,6 +22,8 @@
 #include "gemm_api.h"
 #include <cuda.h>
 #include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
 
 namespace {
 
@@ -32,13 +34,15 @@ constexpr int NUM_ACC = 2;
 constexpr int TILE_BYTES = BLOCK_M * BLOCK_K * 2;  // 16 KiB per operand tile
 constexpr int NUM_THREADS = 320;  // warp 0: TMA, warp 1: MMA, warps 2-9: epilogue (two per TMEM lane quarter)
 // Tile width BN is a template parameter: 128 (6 stages) or 256 (4 stages; halves shared-memory traffic per flop).
-constexpr int num_stages(int bn) { return bn == 256 ? 4 : 6; }
-constexpr int stage_bytes(int bn) { return TILE_BYTES + bn * BLOCK_K * 2; }
+// In pair mode (cta_group::2: two CTAs of a cluster compute one 256 x BN tile) a CTA stages its own 128 rows of A and HALF of
+// the B tile, so a stage is 32 KiB at BN = 256 and six of them fit.
+constexpr int num_stages(int bn, bool pair = false) { return pair ? 6 : (bn == 256 ? 4 : 6); }
+constexpr int stage_bytes(int bn, bool pair = false) { return TILE_BYTES + (pair ? bn / 2 : bn) * BLOCK_K * 2; }
 constexpr int EPI_WARPS = 8;
 constexpr int EPI_ROW_BYTES = 80;   // 32 bf16 (64 B) + 16 B pad: conflict-free 16-byte writes by row and reads by 4-lane groups
 constexpr int EPI_STAGE_BYTES = 32 * EPI_ROW_BYTES;
-constexpr int smem_bytes(int bn) {
-  return num_stages(bn) * stage_bytes(bn) + 1024 /*align*/ + 256 /*barriers*/ + EPI_WARPS * EPI_STAGE_BYTES /*store staging*/;
+constexpr int smem_bytes(int bn, bool pair = false) {
+  return num_stages(bn, pair) * stage_bytes(bn, pair) + 1024 /*align*/ + 256 /*barriers*/ + EPI_WARPS * EPI_STAGE_BYTES /*store staging*/;
 }
 
 struct EpilogueArgs {
@@ -71,6 +75,7 @@ struct GemmParams {
   // the fp32 output with vector reductions (only for plain accumulating epilogues: D += alpha * A B^T)
   int ksplit, kb_per;
   long long num_work;  // num_tiles * ksplit
+  int debug;           // diagnostics only (wrong results): 1 = tensor core alone (operands loaded once), 2 = loads alone (no MMAs)
   EpilogueArgs ep;
   int* status;
 };
@@ -99,9 +104,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait: false after SB_WAIT_CYCLES, with the status word set.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  long long t0 = clock64();
+  const long long t0 = clock64();
+  unsigned int probes = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > SB_WAIT_CYCLES || sb_failed(status)) {
+    // The give-up test reads the status word from global memory (several hundred cycles): doing it after every failed probe
+    // put that latency on the critical path of each producer / consumer hand-over.  Every 64th probe is plenty for a bound.
+    if ((++probes & 63u) == 0 && (clock64() - t0 > SB_WAIT_CYCLES || sb_failed(status))) {
       sb_set_status(status, code, (int)parity);
       return false;
     }
@@ -115,6 +123,44 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tma
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+
+// ---- CTA-pair helpers (cta_group::2).  The TMA loads carry no multicast: each CTA fetches its own operand slices and reports
+// the bytes to the LEADER CTA's barrier (a shared::cluster address), which the .cta_group::2 form of the copy permits.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* tmap, uint32_t leader_bar, int c0, int c1, int c2,
+                                                 int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(tmap), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// one arrival on the barrier at `cluster_addr` (own or peer CTA) once all MMAs issued so far have completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 // Shared-memory matrix descriptor (tcgen05): 128-byte swizzle, version 1.
@@ -190,14 +236,21 @@ __device__ __forceinline__ void stage_store_32x32(uint8_t* st, int lane, const f
   __syncwarp();
 }
 
-template <bool A_MN, bool B_MN, int BN>
+// PAIR = true: launched as clusters of two CTAs; CTA pair c works on 256 x BN tiles (CTA rank r owns rows r*128..r*128+127 of
+// the tile in its tensor memory and stages columns r*BN/2.. of B); only rank 0 issues MMAs (tcgen05.mma.cta_group::2).
+template <bool A_MN, bool B_MN, int BN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
   constexpr int BLOCK_N = BN;
-  constexpr int NUM_STAGES = num_stages(BN);
-  constexpr int STAGE_BYTES = stage_bytes(BN);
+  constexpr int NUM_STAGES = num_stages(BN, PAIR);
+  constexpr int STAGE_BYTES = stage_bytes(BN, PAIR);
   constexpr int TMEM_COLS = NUM_ACC * BN;
+  constexpr int TILE_M = PAIR ? 2 * BLOCK_M : BLOCK_M;        // rows of an output tile
+  constexpr int B_ROWS = PAIR ? BN / 2 : BN;                  // rows (= output columns) of B staged by this CTA
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  const long long worker = PAIR ? (long long)(blockIdx.x >> 1) : (long long)blockIdx.x;
+  const long long num_workers = PAIR ? (long long)(gridDim.x >> 1) : (long long)gridDim.x;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
@@ -222,19 +275,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 8);
+      mbar_init(tempty_bar(a), PAIR ? 16 : 8);   // in pair mode the leader's barrier also hears the peer's eight epilogue warps
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // both CTAs' barriers are initialised before either touches the other's
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -243,7 +304,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (lane == 0) {
       long long it = 0;
       bool ok = true;
-      for (long long w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
+      for (long long w = worker; w < p.num_work && ok; w += num_workers) {
         const long long tile = p.ksplit > 1 ? w / p.ksplit : w;
         const int kb_begin = p.ksplit > 1 ? (int)(w % p.ksplit) * p.kb_per : 0;
         const int kb_end = p.ksplit > 1 ? min(num_kb, kb_begin + p.kb_per) : num_kb;
@@ -251,39 +312,64 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int rem = (int)(tile % ((long long)p.tiles_m * p.tiles_n));
         const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
         const int b0 = batch % p.batch0;
+        const int a_row0 = tm * TILE_M + (int)cta_rank * BLOCK_M;      // first A row (output row) staged by this CTA
+        const int b_row0 = tn * BLOCK_N + (int)cta_rank * B_ROWS;      // first B row (output column) staged by this CTA
         for (int kbt = kb_begin; kbt < kb_end; ++kbt, ++it) {
           const int kb = kbt % num_kb1;
           const int b1 = p.kfold > 1 ? kbt / num_kb1 : batch / p.batch0;
           const int s = (int)(it % NUM_STAGES);
           const uint32_t ph = (uint32_t)((it / NUM_STAGES) & 1);
+          if ((p.debug & 15) == 1 && it >= NUM_STAGES) continue;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, SB_TIMEOUT_SMEM_EMPTY)) { ok = false; break; }
-          mbar_expect_tx(full_bar(s), STAGE_BYTES);
           const uint32_t sa = base + s * STAGE_BYTES, sb = sa + TILE_BYTES;
-          if (A_MN) {
-            tma_load_4d(sa, &tmap_a, full_bar(s), tm * BLOCK_M, kb * BLOCK_K, b0, b1);
-            tma_load_4d(sa + TILE_BYTES / 2, &tmap_a, full_bar(s), tm * BLOCK_M + 64, kb * BLOCK_K, b0, b1);
-          } else {
-            tma_load_4d(sa, &tmap_a, full_bar(s), kb * BLOCK_K, tm * BLOCK_M, b0, b1);
-          }
-          if (B_MN) {
+          if (PAIR) {
+            // the leader's barrier counts the bytes of both CTAs; only the leader posts the expectation (and the arrival)
+            const uint32_t lbar = mapa_shared(full_bar(s), 0);
+            if (cta_rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);
+            if (A_MN) {
+              tma_load_4d_pair(sa, &tmap_a, lbar, a_row0, kb * BLOCK_K, b0, b1);
+              tma_load_4d_pair(sa + TILE_BYTES / 2, &tmap_a, lbar, a_row0 + 64, kb * BLOCK_K, b0, b1);
+            } else {
+              tma_load_4d_pair(sa, &tmap_a, lbar, kb * BLOCK_K, a_row0, b0, b1);
+            }
+            if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BLOCK_N / 64; ++j)
-              tma_load_4d(sb + j * (TILE_BYTES / 2), &tmap_b, full_bar(s), tn * BLOCK_N + 64 * j, kb * BLOCK_K, b0, b1);
+              for (int j = 0; j < B_ROWS / 64; ++j)
+                tma_load_4d_pair(sb + j * (TILE_BYTES / 2), &tmap_b, lbar, b_row0 + 64 * j, kb * BLOCK_K, b0, b1);
+            } else {
+              tma_load_4d_pair(sb, &tmap_b, lbar, kb * BLOCK_K, b_row0, b0, b1);
+            }
+          } else if ((p.debug & 15) == 3) {   // diagnostics: A operand only (a third of the bytes), no MMAs
+            mbar_expect_tx(full_bar(s), TILE_BYTES);
+            tma_load_4d(sa, &tmap_a, full_bar(s), kb * BLOCK_K, a_row0, b0, b1);
           } else {
-            tma_load_4d(sb, &tmap_b, full_bar(s), kb * BLOCK_K, tn * BLOCK_N, b0, b1);
+            mbar_expect_tx(full_bar(s), STAGE_BYTES);
+            if (A_MN) {
+              tma_load_4d(sa, &tmap_a, full_bar(s), a_row0, kb * BLOCK_K, b0, b1);
+              tma_load_4d(sa + TILE_BYTES / 2, &tmap_a, full_bar(s), a_row0 + 64, kb * BLOCK_K, b0, b1);
+            } else {
+              tma_load_4d(sa, &tmap_a, full_bar(s), kb * BLOCK_K, a_row0, b0, b1);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BLOCK_N / 64; ++j)
+                tma_load_4d(sb + j * (TILE_BYTES / 2), &tmap_b, full_bar(s), b_row0 + 64 * j, kb * BLOCK_K, b0, b1);
+            } else {
+              tma_load_4d(sb, &tmap_b, full_bar(s), kb * BLOCK_K, b_row0, b0, b1);
+            }
           }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && cta_rank == 0) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
-                             ((uint32_t)(BLOCK_N >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
+                             ((uint32_t)(BLOCK_N >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
       long long it = 0;
       long long tcount = 0;
       bool ok = true;
-      for (long long w = blockIdx.x; w < p.num_work && ok; w += gridDim.x, ++tcount) {
+      for (long long w = worker; w < p.num_work && ok; w += num_workers, ++tcount) {
         const int kb_begin = p.ksplit > 1 ? (int)(w % p.ksplit) * p.kb_per : 0;
         const int kb_end = p.ksplit > 1 ? min(num_kb, kb_begin + p.kb_per) : num_kb;
         const int acc = (int)(tcount % NUM_ACC);
@@ -294,7 +380,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const int s = (int)(it % NUM_STAGES);
           const uint32_t ph = (uint32_t)((it / NUM_STAGES) & 1);
-          if (!mbar_wait(full_bar(s), ph, p.status, SB_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+          if (!((p.debug & 15) == 1 && it >= NUM_STAGES)) {
+            if (!mbar_wait(full_bar(s), ph, p.status, SB_TIMEOUT_SMEM_FULL)) { ok = false; break; }
+          }
           tc_fence_after();
           const uint32_t sa = base + s * STAGE_BYTES, sb = sa + TILE_BYTES;
 #pragma unroll
@@ -304,11 +392,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                      : make_desc(sa + k * (UMMA_K * 2), 16, 1024);
             const uint64_t bd = B_MN ? make_desc(sb + k * (UMMA_K * 128), BLOCK_K * 128, 1024)
                                      : make_desc(sb + k * (UMMA_K * 2), 16, 1024);
-            umma_bf16(d_tmem, ad, bd, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+            if ((p.debug & 15) >= 2) continue;
+            if (PAIR) umma_bf16_pair(d_tmem, ad, bd, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+            else umma_bf16(d_tmem, ad, bd, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
           }
-          umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+          if ((p.debug & 31) == 1) {
+            // stages are never recycled in this mode
+          } else if (PAIR) {  // the stage is free in BOTH CTAs once these MMAs have read it
+            umma_commit_pair(mapa_shared(empty_bar(s), 0));
+            umma_commit_pair(mapa_shared(empty_bar(s), 1));
+          } else {
+            umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+          }
         }
-        if (ok) umma_commit(tfull_bar(acc));
+        if (ok) {
+          if (PAIR) {
+            umma_commit_pair(mapa_shared(tfull_bar(acc), 0));
+            umma_commit_pair(mapa_shared(tfull_bar(acc), 1));
+          } else {
+            umma_commit(tfull_bar(acc));
+          }
+        }
       }
     }
   } else {
@@ -319,19 +423,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint8_t* stage = smem + NUM_STAGES * STAGE_BYTES + 256 + (warp - 2) * EPI_STAGE_BYTES;
     long long tcount = 0;
     bool ok = true;
-    for (long long w = blockIdx.x; w < p.num_work && ok; w += gridDim.x, ++tcount) {
+    for (long long w = worker; w < p.num_work && ok; w += num_workers, ++tcount) {
       const long long tile = p.ksplit > 1 ? w / p.ksplit : w;
       const int batch = (int)(tile / ((long long)p.tiles_m * p.tiles_n));
       const int rem = (int)(tile % ((long long)p.tiles_m * p.tiles_n));
       const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
       const int b0 = batch % p.batch0, b1 = batch / p.batch0;
+      const int tile_row0 = tm * TILE_M + (int)cta_rank * BLOCK_M;   // first output row held in this CTA's tensor memory
       const int acc = (int)(tcount % NUM_ACC);
       const uint32_t aph = (uint32_t)((tcount / NUM_ACC) & 1);
       // the decision to go on must be warp-uniform: tcgen05.ld below is a warp-collective instruction
       ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(acc), aph, p.status, SB_TIMEOUT_TMEM_FULL) ? 1 : 0) != 0;
       if (!ok) break;
       tc_fence_after();
-      const int row = tm * BLOCK_M + q * 32 + lane;
+      const int row = tile_row0 + q * 32 + lane;
       const bool row_ok = row < p.M;
       const long long d_off = (long long)b0 * e.d_bs0 + (long long)b1 * e.d_bs1 + (long long)row * e.ldd;
       const long long r_off = (long long)b0 * e.r_bs0 + (long long)b1 * e.r_bs1 + (long long)row * e.ldr;
@@ -345,7 +450,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tmem_ld_wait();
         const int col0 = tn * BLOCK_N + c * 32;
         const bool full = (col0 + 32 <= p.N);
-        const int row_base = tm * BLOCK_M + q * 32;               // first row of this warp's 32-row slab
+        const int row_base = tile_row0 + q * 32;                  // first row of this warp's 32-row slab
         const int rows_valid = min(32, p.M - row_base);           // warp-uniform
         const long long slab_d = (long long)b0 * e.d_bs0 + (long long)b1 * e.d_bs1 + (long long)row_base * e.ldd;
         const long long slab_p = (long long)b0 * e.p_bs0 + (long long)b1 * e.p_bs1 + (long long)row_base * e.ldp;
@@ -504,16 +609,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(mapa_shared(tempty_bar(acc), 0));   // the leader's MMA warp waits for both CTAs
+        else mbar_arrive(tempty_bar(acc));
+      }
     }
   }
 
   // ------------------------------------------------------------------ common exit
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while its partner may still reach into it
   tc_fence_after();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -552,7 +662,7 @@ int make_operand_map(CUtensorMap* map, const void* ptr, long long inner, long lo
   return r == CUDA_SUCCESS ? 0 : -(200 + (int)r);
 }
 
-bool g_attr_set[8] = {false, false, false, false, false, false, false, false};
+bool g_attr_set[16] = {};
 
 }  // namespace
 
@@ -571,6 +681,10 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
                            (a->fold_batch1 ? 1 : a->batch1);
     bn = (a->N >= 256 && t256 >= (long long)sb_num_sms() * 3 / 4) ? 256 : 128;
   }
+  // CTA pairs (cta_group::2, 256 x 256 tiles, half the B traffic per SM) for large plain-layout problems; opt-in while the path
+  // is being qualified: SbGemmArgs.pair = 1, or the environment variable SPEECH_B200_GEMM_PAIR=1 for every eligible GEMM
+  static const bool env_pair = [] { const char* e = getenv("SPEECH_B200_GEMM_PAIR"); return e && e[0] == '1'; }();
+  const bool pair = bn == 256 && a->M > 128 && (a->pair == 1 || (a->pair == 0 && env_pair));
   CUtensorMap ta, tb;
   int rc;
   if (a->a_mn_major)
@@ -581,19 +695,19 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   if (a->b_mn_major)
     rc = make_operand_map(&tb, a->B, a->N, a->K, a->ldb, a->batch0, a->batch1, a->b_bs0, a->b_bs1, BLOCK_K);
   else
-    rc = make_operand_map(&tb, a->B, a->K, a->N, a->ldb, a->batch0, a->batch1, a->b_bs0, a->b_bs1, bn);
+    rc = make_operand_map(&tb, a->B, a->K, a->N, a->ldb, a->batch0, a->batch1, a->b_bs0, a->b_bs1, pair ? bn / 2 : bn);
   if (rc) return rc - 1000;
   GemmParams p;
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.batch0 = a->batch0; p.batch1 = a->batch1;
-  p.tiles_m = (a->M + BLOCK_M - 1) / BLOCK_M;
+  p.tiles_m = pair ? (a->M + 2 * BLOCK_M - 1) / (2 * BLOCK_M) : (a->M + BLOCK_M - 1) / BLOCK_M;
   p.tiles_n = (a->N + bn - 1) / bn;
   p.kfold = a->fold_batch1 ? a->batch1 : 1;
   p.num_tiles = (long long)p.tiles_m * p.tiles_n * a->batch0 * (a->fold_batch1 ? 1 : a->batch1);
   p.ksplit = 1;
   {
     const int num_kb = (a->K + BLOCK_K - 1) / BLOCK_K;
-    const int sms = sb_num_sms();
+    const int sms = pair ? sb_num_sms() / 2 : sb_num_sms();   // parallel workers: CTA pairs or CTAs
     if (a->ksplit > 1 && can_split) {
       p.ksplit = a->ksplit < num_kb ? a->ksplit : num_kb;
     } else if (can_split && a->ksplit == 0 && p.num_tiles < (long long)sms * 3 / 4) {
@@ -614,6 +728,8 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   }
   p.status = sb_status_ptr();
   if (!p.status) return -2;
+  static const int env_debug = [] { const char* e = getenv("SPEECH_B200_GEMM_DEBUG"); return e ? atoi(e) : 0; }();
+  p.debug = env_debug & 31;
   EpilogueArgs& e = p.ep;
   e.D = a->D; e.d_is_f32 = a->d_is_f32; e.ldd = a->ldd; e.d_bs0 = a->d_bs0; e.d_bs1 = a->d_bs1;
   e.bias_f32 = (a->bias && a->bias_is_f32) ? (const float*)a->bias : nullptr;
@@ -631,23 +747,50 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   int grid = sb_num_sms();
   if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
   if ((long long)grid > p.num_work) grid = (int)p.num_work;
-  const int variant = (a->a_mn_major ? 2 : 0) | (a->b_mn_major ? 1 : 0) | (bn == 256 ? 4 : 0);
+  const int variant = (a->a_mn_major ? 2 : 0) | (a->b_mn_major ? 1 : 0) | (bn == 256 ? 4 : 0) | (pair ? 8 : 0);
   void (*kern)(const CUtensorMap, const CUtensorMap, const GemmParams) = nullptr;
   switch (variant) {
-    case 0: kern = gemm_bf16_kernel<false, false, 128>; break;
-    case 1: kern = gemm_bf16_kernel<false, true, 128>; break;
-    case 2: kern = gemm_bf16_kernel<true, false, 128>; break;
-    case 3: kern = gemm_bf16_kernel<true, true, 128>; break;
-    case 4: kern = gemm_bf16_kernel<false, false, 256>; break;
-    case 5: kern = gemm_bf16_kernel<false, true, 256>; break;
-    case 6: kern = gemm_bf16_kernel<true, false, 256>; break;
-    default: kern = gemm_bf16_kernel<true, true, 256>; break;
+    case 0: kern = gemm_bf16_kernel<false, false, 128, false>; break;
+    case 1: kern = gemm_bf16_kernel<false, true, 128, false>; break;
+    case 2: kern = gemm_bf16_kernel<true, false, 128, false>; break;
+    case 3: kern = gemm_bf16_kernel<true, true, 128, false>; break;
+    case 4: kern = gemm_bf16_kernel<false, false, 256, false>; break;
+    case 5: kern = gemm_bf16_kernel<false, true, 256, false>; break;
+    case 6: kern = gemm_bf16_kernel<true, false, 256, false>; break;
+    case 7: kern = gemm_bf16_kernel<true, true, 256, false>; break;
+    case 12: kern = gemm_bf16_kernel<false, false, 256, true>; break;
+    case 13: kern = gemm_bf16_kernel<false, true, 256, true>; break;
+    case 14: kern = gemm_bf16_kernel<true, false, 256, true>; break;
+    default: kern = gemm_bf16_kernel<true, true, 256, true>; break;
   }
-  const int smem = smem_bytes(bn);
+  const int smem = smem_bytes(bn, pair);
   if (!g_attr_set[variant]) {
     cudaError_t ae = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (ae != cudaSuccess) return (int)ae;
+    if (pair) {
+      ae = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 0);
+      (void)ae;
+    }
     g_attr_set[variant] = true;
+  }
+  if (pair) {
+    int pairs = sb_num_sms() / 2;
+    if (a->max_ctas > 1 && a->max_ctas / 2 < pairs) pairs = a->max_ctas / 2;
+    if ((long long)pairs > p.num_work) pairs = (int)p.num_work;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
   }
   kern<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, p);
   return (int)cudaGetLastError();
