@@ -177,11 +177,11 @@ class LabelLoopingGraph:
         torch.cuda.current_stream(dev).synchronize()
         n = s["length"].clone()
         hyps = BatchedHyps(B, init_length=max(1, int(n.max())), device=dev, store_durations=c.include_duration and len(c.durations) > 0)
-        L = hyps.transcript.shape[1]
-        hyps.transcript.copy_(s["transcript"][:, :L])
-        hyps.timestamps.copy_(s["stamps"][:, :L])
+        L = min(hyps.transcript.shape[1], s["transcript"].shape[1])      # the two buffers round their capacities differently
+        hyps.transcript[:, :L].copy_(s["transcript"][:, :L])
+        hyps.timestamps[:, :L].copy_(s["stamps"][:, :L])
         if hyps.token_durations is not None:
-            hyps.token_durations.copy_(s["durs"][:, :L])
+            hyps.token_durations[:, :L].copy_(s["durs"][:, :L])
         hyps.current_lengths.copy_(n)
         hyps.scores.copy_(s["score"])
         state = LabelLoopingState(predictor_state=tuple(t.clone() for t in s["state"]), predictor_output=s["dec_proj"].clone(),

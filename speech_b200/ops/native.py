@@ -250,7 +250,8 @@ def colsum(x2: torch.Tensor, out: torch.Tensor, accumulate: bool = False):
 
 def linear(x, weight, bias=None, act=None, residual=None, alpha: float = 1.0, dropout_p: float = 0.0):
     K = x.shape[-1]
-    if K % 8 != 0 or x.numel() == 0 or (dropout_p > 0.0 and weight.shape[0] % 8 != 0):
+    # the backward pass feeds dy [M, N] to the tensor core as a K-major operand: N must keep rows 16-byte aligned as well
+    if K % 8 != 0 or x.numel() == 0 or weight.shape[0] % 8 != 0:
         from . import reference
 
         return reference.linear(x, weight, bias, act, residual, alpha, dropout_p)

@@ -16,8 +16,8 @@ def _run(with_graph: bool, steps: int = 8):
     cfg = fastconformer_ctc_config("small", vocab_size=128, n_layers=2, dropout=0.0) if "dropout" in fastconformer_ctc_config.__code__.co_varnames \
         else fastconformer_ctc_config("small", vocab_size=128, n_layers=2)
     with open_dict(cfg):
-        cfg.train_ds = {"synthetic": {"num_samples": 4, "vocab_size": 128, "min_duration": 2.0, "max_duration": 2.0, "max_tokens_frac_of_frames": 0.5,
-                                      "token_low": 0, "fixed_tokens": 8}, "batch_size": 4, "shuffle": False}
+        cfg.train_ds = {"synthetic": {"num_samples": 4, "vocab_size": 128, "min_duration": 2.0, "max_duration": 2.0, "tokens_per_second": 3.0,
+                                      "token_low": 0}, "batch_size": 4, "shuffle": False}
         cfg.spec_augment = None
     model = EncDecCTCModelBPE(cfg)
     for m in model.modules():
