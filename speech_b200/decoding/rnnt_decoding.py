@@ -306,6 +306,7 @@ class GreedyBatchedRNNTInfer:
         hyps, _, state = self.decoding_computer(x, encoded_lengths.to(x.device), prev)
         out = batched_hyps_to_hypotheses(hyps, None, batch_size=x.shape[0])
         states = split_state(state, x.shape[0])
+        enc_lens = encoded_lengths.tolist()           # one device read for the whole batch
         for i, h in enumerate(out):
             h.dec_state = states[i]
             if partial_hypotheses is not None and partial_hypotheses[i] is not None:
@@ -314,9 +315,9 @@ class GreedyBatchedRNNTInfer:
                 h.y_sequence = torch.cat([torch.as_tensor(ph.y_sequence, dtype=torch.long), h.y_sequence])
                 h.timestamp = torch.cat([torch.as_tensor(ph.timestamp, dtype=torch.long), h.timestamp + off])
                 h.score = h.score + ph.score
-                h.last_frame = off + int(encoded_lengths[i])
+                h.last_frame = off + int(enc_lens[i])
             else:
-                h.last_frame = int(encoded_lengths[i])
+                h.last_frame = int(enc_lens[i])
         return (out,)
 
 
@@ -349,18 +350,24 @@ class BeamBatchedRNNTInfer:
 
 
 def split_state(state: LabelLoopingState, B: int) -> List[LabelLoopingState]:
+    """Per-stream states as VIEWS of the batched tensors (no copies, no kernel launches); each remembers its parent and row so
+    that ``merge_states`` can hand the parent back untouched when the same streams meet again in the same order."""
     out = []
     for i in range(B):
-        ps = tuple(s[:, i:i + 1].clone() for s in state.predictor_state) if state.predictor_state is not None else None
-        out.append(LabelLoopingState(predictor_state=ps, predictor_output=state.predictor_output[i:i + 1].clone(),
-                                     labels=state.labels[i:i + 1].clone(),
-                                     decoded_lengths=state.decoded_lengths[i:i + 1].clone(),
-                                     time_jumps=state.time_jumps[i:i + 1].clone(),
-                                     fusion_states=[f[i:i + 1] for f in state.fusion_states] if state.fusion_states else None))
+        ps = tuple(s[:, i:i + 1] for s in state.predictor_state) if state.predictor_state is not None else None
+        st = LabelLoopingState(predictor_state=ps, predictor_output=state.predictor_output[i:i + 1], labels=state.labels[i:i + 1],
+                               decoded_lengths=state.decoded_lengths[i:i + 1], time_jumps=state.time_jumps[i:i + 1],
+                               fusion_states=[f[i:i + 1] for f in state.fusion_states] if state.fusion_states else None)
+        st._batch_ref = (state, i, B)
+        out.append(st)
     return out
 
 
 def merge_states(states: List[LabelLoopingState]) -> LabelLoopingState:
+    ref = getattr(states[0], "_batch_ref", None)
+    if ref is not None and ref[2] == len(states) and all(getattr(s, "_batch_ref", (None, -1, 0))[0] is ref[0] and s._batch_ref[1] == i
+                                                         for i, s in enumerate(states)):
+        return ref[0]                       # the very batch these states were split from, in the same order
     ps = None
     if states[0].predictor_state is not None:
         ps = tuple(torch.cat([s.predictor_state[k] for s in states], dim=1) for k in range(len(states[0].predictor_state)))

@@ -175,7 +175,8 @@ class _CacheAwarePipeline(BasePipeline):
         ids = [r.stream_id for r in reqs]
         states = [self.get_state(r.stream_id, r.options) for r in reqs]
         T = max(r.size for r in reqs)
-        feats = torch.stack([torch.nn.functional.pad(r.features, (0, T - r.size)) for r in reqs])
+        # padding launches a kernel per stream: only for the (rare) streams whose chunk is shorter than the longest one
+        feats = torch.stack([r.features if r.size == T else torch.nn.functional.pad(r.features, (0, T - r.size)) for r in reqs])
         lens = torch.tensor([r.valid_size for r in reqs], dtype=torch.long)
         ctx, mapping = self.context_manager.get_context(ids)
         result = self._decode_group(feats, lens, ctx, states, drop_extra=0 if first else self.drop_extra)

@@ -26,6 +26,7 @@ enum SbStatus : int {
 // The status word lives in status.cu; host code fetches its device address once per device with
 // sb_status_ptr() and passes it to every kernel that can wait.
 SB_API int* sb_status_ptr();
+SB_API int sb_reserved_sms();   // SMs persistent kernels leave to concurrent kernels (status.cu)
 
 __device__ __forceinline__ void sb_set_status(int* status, int code, int detail) {
   if (atomicCAS(&status[0], 0, code) == 0) {

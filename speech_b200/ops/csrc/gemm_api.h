@@ -30,6 +30,8 @@ struct SbGemmArgs {
   float drop_p;     // > 0: dropout applied to act(acc + bias) before alpha / residual; mask = sb_dropout_keep(seed, m * N + n)
   unsigned long long drop_seed;
   int ksplit;       // 0 = automatic, -1 = never split K, > 1 = that many K slices (only honoured for D(fp32) += alpha * A B^T)
+  const void* const* peer_D;  // device array [world] of fp32 output buffers for GEMM + reduce-scatter (see gemm_tcgen05.cu); or null
+  int peer_rows;    // rows of the full output owned by each rank
   int pair;         // 0 = default policy, 1 = use CTA pairs (cta_group::2) when the shape allows, -1 = never
 };
 

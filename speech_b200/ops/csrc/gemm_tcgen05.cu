@@ -63,6 +63,10 @@ struct EpilogueArgs {
   unsigned int drop_thresh;  // 0 = no dropout; otherwise keep iff sb_dropout_keep(seed, batch*M*N + m*N + n, thresh)
   float drop_scale;          // 1 / (1 - p)
   unsigned long long drop_seed;
+  // GEMM + reduce-scatter: output row m belongs to rank m / peer_rows and is ADDED (fp32 reductions over NVLink peer stores)
+  // into that rank's buffer peer_D[rank] at row m % peer_rows.  Null = ordinary local output.
+  float* const* peer_D;
+  int peer_rows;
 };
 
 struct GemmParams {
@@ -438,7 +442,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_after();
       const int row = tile_row0 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      const long long d_off = (long long)b0 * e.d_bs0 + (long long)b1 * e.d_bs1 + (long long)row * e.ldd;
+      const long long d_off = e.peer_D ? (long long)(row % e.peer_rows) * e.ldd
+                                       : (long long)b0 * e.d_bs0 + (long long)b1 * e.d_bs1 + (long long)row * e.ldd;
+      // with a scattered output the owner's buffer replaces D (rows beyond M never store, so the index stays in range)
+      float* const peer_base = (e.peer_D && row_ok) ? e.peer_D[row / e.peer_rows] : nullptr;
       const long long r_off = (long long)b0 * e.r_bs0 + (long long)b1 * e.r_bs1 + (long long)row * e.ldr;
       const long long x_off = (long long)b0 * e.x_bs0 + (long long)b1 * e.x_bs1 + (long long)row * e.ldx;
       const long long p_off = (long long)b0 * e.p_bs0 + (long long)b1 * e.p_bs1 + (long long)row * e.ldp;
@@ -557,9 +564,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
             }
           }
-          if (e.d_is_f32 && p.ksplit > 1) {
-            // partial sum of one K slice: D += v (the host only splits K for epilogues of exactly this form)
-            float* dp = reinterpret_cast<float*>(e.D) + d_off + col0;
+          if (e.d_is_f32 && (p.ksplit > 1 || e.peer_D)) {
+            // partial sum of one K slice (or of one rank's K shard): D += v.  The host only takes this path for epilogues of
+            // exactly this form; with peer_D the destination is another GPU's memory, reached by plain P2P reductions.
+            float* dp = (e.peer_D ? peer_base : reinterpret_cast<float*>(e.D)) + d_off + col0;
             if (full && ((((uintptr_t)dp) & 15) == 0)) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4)
@@ -738,13 +746,20 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   e.aux = (const __nv_bfloat16*)a->aux; e.ldx = a->ldx; e.x_bs0 = a->x_bs0; e.x_bs1 = a->x_bs1;
   e.D_pre = (__nv_bfloat16*)a->D_pre; e.ldp = a->ldp; e.p_bs0 = a->p_bs0; e.p_bs1 = a->p_bs1;
   e.alpha = a->alpha; e.beta = a->beta; e.act = a->act; e.dact = (a->aux ? a->dact : 0);
+  e.peer_D = (float* const*)a->peer_D; e.peer_rows = a->peer_rows;
+  if (a->peer_D) {
+    if (!a->d_is_f32 || a->peer_rows <= 0 || a->bias || a->residual || a->aux || a->D_pre || a->act || a->drop_p > 0.f ||
+        a->batch0 != 1 || a->batch1 != 1 || a->ldd % 4 != 0)
+      return -6;   // the scattered output is a pure accumulation of fp32 partial products
+  }
   auto al8 = [](long long x) { return (x % 8) == 0; };
   e.stage_d = (!a->d_is_f32 && a->beta == 0.f && (((uintptr_t)a->D) & 15) == 0 && al8(a->ldd) && al8(a->d_bs0) && al8(a->d_bs1)) ? 1 : 0;
   e.stage_p = (a->D_pre && (((uintptr_t)a->D_pre) & 15) == 0 && al8(a->ldp) && al8(a->p_bs0) && al8(a->p_bs1)) ? 1 : 0;
   e.drop_thresh = sb_dropout_threshold(a->drop_p);
   e.drop_scale = a->drop_p > 0.f ? 1.f / (1.f - a->drop_p) : 1.f;
   e.drop_seed = a->drop_seed;
-  int grid = sb_num_sms();
+  int grid = sb_num_sms() - sb_reserved_sms();
+  if (grid < 8) grid = 8;
   if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
   if ((long long)grid > p.num_work) grid = (int)p.num_work;
   const int variant = (a->a_mn_major ? 2 : 0) | (a->b_mn_major ? 1 : 0) | (bn == 256 ? 4 : 0) | (pair ? 8 : 0);
@@ -774,7 +789,8 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
     g_attr_set[variant] = true;
   }
   if (pair) {
-    int pairs = sb_num_sms() / 2;
+    int pairs = (sb_num_sms() - sb_reserved_sms()) / 2;
+    if (pairs < 4) pairs = 4;
     if (a->max_ctas > 1 && a->max_ctas / 2 < pairs) pairs = a->max_ctas / 2;
     if ((long long)pairs > p.num_work) pairs = (int)p.num_work;
     cudaLaunchConfig_t cfg;

@@ -97,27 +97,44 @@ __global__ void __launch_bounds__(512) peer_allreduce_kernel(SbPeerArgs a) {
   const long long c0 = (long long)b * a.chunk;                 // sub-chunk range inside a slice
   const long long c1 = min(a.slice, c0 + a.chunk);
 
+  // Every loop below keeps UNR independent 16/32-byte loads in flight per thread: with one load per iteration a 512-thread CTA has
+  // 16 KB outstanding and moves ~17 GB/s, a quarter of what four loads give.
+  constexpr int UNR = 4;
+  const long long step = (long long)blockDim.x * 8;
   // ---- phase 0: local cast of sub-chunk b of every slice
   for (int p = 0; p < a.world; ++p) {
     const long long base = (long long)p * a.slice;
-    for (long long i = c0 + (long long)threadIdx.x * 8; i < c1; i += (long long)blockDim.x * 8) {
-      const long long e = base + i;
-      __align__(16) __nv_bfloat162 o[4];
-      if (e + 8 <= a.n) {
-        const float4 x = *reinterpret_cast<const float4*>(a.grad + e);
-        const float4 y = *reinterpret_cast<const float4*>(a.grad + e + 4);
-        o[0] = __floats2bfloat162_rn(x.x * a.scale, x.y * a.scale);
-        o[1] = __floats2bfloat162_rn(x.z * a.scale, x.w * a.scale);
-        o[2] = __floats2bfloat162_rn(y.x * a.scale, y.y * a.scale);
-        o[3] = __floats2bfloat162_rn(y.z * a.scale, y.w * a.scale);
-      } else {
-        float t[8];
+    for (long long i0 = c0 + (long long)threadIdx.x * 8; i0 < c1; i0 += step * UNR) {
+      float4 x[UNR], y[UNR];
+      bool vec[UNR];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) t[k] = (e + k < a.n) ? a.grad[e + k] * a.scale : 0.f;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(t[2 * k], t[2 * k + 1]);
+      for (int u = 0; u < UNR; ++u) {
+        const long long i = i0 + u * step, e = base + i;
+        vec[u] = i < c1 && e + 8 <= a.n;
+        if (vec[u]) {
+          x[u] = *reinterpret_cast<const float4*>(a.grad + e);
+          y[u] = *reinterpret_cast<const float4*>(a.grad + e + 4);
+        }
       }
-      *reinterpret_cast<uint4*>(my_send + e) = *reinterpret_cast<const uint4*>(o);
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const long long i = i0 + u * step, e = base + i;
+        if (i >= c1) break;
+        __align__(16) __nv_bfloat162 o[4];
+        if (vec[u]) {
+          o[0] = __floats2bfloat162_rn(x[u].x * a.scale, x[u].y * a.scale);
+          o[1] = __floats2bfloat162_rn(x[u].z * a.scale, x[u].w * a.scale);
+          o[2] = __floats2bfloat162_rn(y[u].x * a.scale, y[u].y * a.scale);
+          o[3] = __floats2bfloat162_rn(y[u].z * a.scale, y[u].w * a.scale);
+        } else {
+          float t[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) t[k] = (e + k < a.n) ? a.grad[e + k] * a.scale : 0.f;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(t[2 * k], t[2 * k + 1]);
+        }
+        *reinterpret_cast<uint4*>(my_send + e) = *reinterpret_cast<const uint4*>(o);
+      }
     }
   }
   signal_peers(a, b, 2u * a.epoch + 1u);
@@ -129,19 +146,41 @@ __global__ void __launch_bounds__(512) peer_allreduce_kernel(SbPeerArgs a) {
   // ---- phase A: reduce my slice's sub-chunk over all ranks, broadcast the rounded result
   {
     const long long base = (long long)a.rank * a.slice;
-    for (long long i = c0 + (long long)threadIdx.x * 8; i < c1; i += (long long)blockDim.x * 8) {
-      const long long e = base + i;
-      if (e >= a.n) break;
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int q = 0; q < a.world; ++q) {
-        const uint4 v = *reinterpret_cast<const uint4*>((const char*)a.buffers[q] + a.send_off + e * 2);
-        add8(acc, v);
-      }
-      __align__(16) __nv_bfloat162 o[4];
+    constexpr int UA = 2, QB = 4;   // 2 positions x 4 ranks = 8 independent 16-byte peer reads in flight per thread
+    for (long long i0 = c0 + (long long)threadIdx.x * 8; i0 < c1; i0 += step * UA) {
+      float acc[UA][8];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
-      const uint4 r = *reinterpret_cast<const uint4*>(o);
-      for (int q = 0; q < a.world; ++q) *reinterpret_cast<uint4*>((char*)a.buffers[q] + a.recv_off + e * 2) = r;
+      for (int u = 0; u < UA; ++u)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[u][k] = 0.f;
+      for (int q0 = 0; q0 < a.world; q0 += QB) {
+        uint4 v[UA][QB];
+#pragma unroll
+        for (int u = 0; u < UA; ++u) {
+          const long long i = i0 + u * step, e = base + i;
+#pragma unroll
+          for (int q = 0; q < QB; ++q)
+            if (i < c1 && e < a.n && q0 + q < a.world)
+              v[u][q] = *reinterpret_cast<const uint4*>((const char*)a.buffers[q0 + q] + a.send_off + e * 2);
+        }
+#pragma unroll
+        for (int u = 0; u < UA; ++u) {
+          const long long i = i0 + u * step, e = base + i;
+#pragma unroll
+          for (int q = 0; q < QB; ++q)
+            if (i < c1 && e < a.n && q0 + q < a.world) add8(acc[u], v[u][q]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UA; ++u) {
+        const long long i = i0 + u * step, e = base + i;
+        if (i >= c1 || e >= a.n) break;
+        __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(acc[u][2 * k], acc[u][2 * k + 1]);
+        const uint4 r = *reinterpret_cast<const uint4*>(o);
+        for (int q = 0; q < a.world; ++q) *reinterpret_cast<uint4*>((char*)a.buffers[q] + a.recv_off + e * 2) = r;
+      }
     }
   }
   signal_peers(a, b, 2u * a.epoch + 2u);
@@ -153,17 +192,25 @@ __global__ void __launch_bounds__(512) peer_allreduce_kernel(SbPeerArgs a) {
   // ---- phase B: unpack sub-chunk b of every slice into the fp32 arena
   for (int p = 0; p < a.world; ++p) {
     const long long base = (long long)p * a.slice;
-    for (long long i = c0 + (long long)threadIdx.x * 8; i < c1; i += (long long)blockDim.x * 8) {
-      const long long e = base + i;
-      if (e >= a.n) break;
-      const uint4 v = *reinterpret_cast<const uint4*>(my_recv + e);
-      float t[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      add8(t, v);
-      if (e + 8 <= a.n) {
-        *reinterpret_cast<float4*>(a.grad + e) = make_float4(t[0], t[1], t[2], t[3]);
-        *reinterpret_cast<float4*>(a.grad + e + 4) = make_float4(t[4], t[5], t[6], t[7]);
-      } else {
-        for (int k = 0; k < 8 && e + k < a.n; ++k) a.grad[e + k] = t[k];
+    for (long long i0 = c0 + (long long)threadIdx.x * 8; i0 < c1; i0 += step * UNR) {
+      uint4 v[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const long long i = i0 + u * step, e = base + i;
+        if (i < c1 && e < a.n) v[u] = *reinterpret_cast<const uint4*>(my_recv + e);
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const long long i = i0 + u * step, e = base + i;
+        if (i >= c1 || e >= a.n) break;
+        float t[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        add8(t, v[u]);
+        if (e + 8 <= a.n) {
+          *reinterpret_cast<float4*>(a.grad + e) = make_float4(t[0], t[1], t[2], t[3]);
+          *reinterpret_cast<float4*>(a.grad + e + 4) = make_float4(t[4], t[5], t[6], t[7]);
+        } else {
+          for (int k = 0; k < 8 && e + k < a.n; ++k) a.grad[e + k] = t[k];
+        }
       }
     }
   }

@@ -46,3 +46,9 @@ SB_API const char* sb_status_string(int code) {
 }
 
 SB_API int sb_last_cuda_error() { return (int)cudaGetLastError(); }
+
+// SMs that persistent kernels leave free for kernels running beside them (gradient-exchange kernels on another stream).  A
+// persistent GEMM whose grid exceeds the SMs actually available runs its displaced CTAs as a second wave and takes twice as long.
+static int g_sb_reserved_sms = 0;
+SB_API void sb_set_reserved_sms(int n) { g_sb_reserved_sms = n < 0 ? 0 : n; }
+SB_API int sb_reserved_sms() { return g_sb_reserved_sms; }

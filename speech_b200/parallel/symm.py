@@ -76,7 +76,7 @@ class PeerAllReduce:
         self.recv_off = self.flags_bytes + region
         self.buf = SymmetricBuffer(self.flags_bytes + 2 * region, device, group)
         self.rank, self.world = self.buf.rank, self.buf.world
-        self.ctas = int(ctas or os.environ.get("SPEECH_B200_PEER_CTAS", 32))
+        self.ctas = int(ctas or os.environ.get("SPEECH_B200_PEER_CTAS", 16))
         self.epoch = 0
 
     def __call__(self, flat: torch.Tensor, scale: float = 1.0) -> None:
@@ -152,6 +152,8 @@ class PeerGradSync(GradSync):
             n = b["view"].numel() if b["view"] is not None else sum(p.numel() for p in b["params"])
             biggest = max(biggest, n)
         self.reducer = PeerAllReduce(biggest, device)
+        # persistent GEMMs size their grids to the SMs that are left while a bucket kernel is resident on the other stream
+        self.reducer.lib.sb_set_reserved_sms(ctypes.c_int(self.reducer.ctas))
         logging.info(f"peer-memory gradient exchange: {len(self.buckets)} buckets, largest {biggest * 4 / 2**20:.1f} MB, "
                      f"{self.reducer.ctas} CTAs per bucket")
 

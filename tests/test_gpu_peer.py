@@ -198,3 +198,64 @@ def test_sync_batchnorm_through_peer_memory_in_layer_executor(tmp_path):
     for r in res:
         assert r["small"] < 1e-4 and r["y"] < 0.01 and r["gx"] < 0.03 and r["rm"] < 1e-3 and r["gw"] < 0.03 and r["rm_same"], r
         assert r["launches"] > 40
+
+
+GEMM_RS_SCRIPT = textwrap.dedent("""
+    import os, sys, json, torch, torch.distributed as dist
+    sys.path.insert(0, {repo!r})
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from speech_b200.ops import native
+    from speech_b200.parallel.fused import GemmReduceScatter
+    op = GemmReduceScatter(2048, 1024, dev)
+    worst = 0.0
+    for it, (M, N, K) in enumerate([(512 * world, 1024, 512), (256 * world, 520, 264), (1000 * world, 1024, 2048)]):
+        torch.manual_seed(7 * it + rank)
+        x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        w = (torch.randn(N, K, device=dev) * 0.1).to(torch.bfloat16)
+        got = op(x, w, out_dtype=torch.float32)
+        full = x.float() @ w.float().t()
+        ref = torch.empty(M // world, N, device=dev)
+        dist.reduce_scatter_tensor(ref, full)
+        torch.cuda.synchronize()
+        worst = max(worst, float((got - ref).abs().max() / ref.abs().max()))
+    # timing against GEMM + NCCL reduce-scatter (device events, max over ranks is taken by the test)
+    M, N, K = 1024 * world, 1024, 4096
+    x = torch.randn(M, K, device=dev).to(torch.bfloat16); w = torch.randn(N, K, device=dev).to(torch.bfloat16)
+    def timed(fn, n=20):
+        for _ in range(3): fn()
+        torch.cuda.synchronize(); dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n): fn()
+        b.record(); torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+    out = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
+    def baseline():
+        y = x @ w.t()
+        dist.reduce_scatter_tensor(out, y)
+    t_fused, t_base = timed(lambda: op(x, w)), timed(baseline)
+    native.check_status()
+    print("RESULT", json.dumps({{"rank": rank, "worst": worst, "fused_ms": t_fused, "nccl_ms": t_base}}))
+    dist.destroy_process_group()
+""")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_gemm_reduce_scatter_fused_over_peer_memory(tmp_path):
+    script = tmp_path / "gemm_rs.py"
+    script.write_text(GEMM_RS_SCRIPT.format(repo=REPO))
+    n = min(torch.cuda.device_count(), 4)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                          "--master-addr", "127.0.0.1", "--master-port", "29745", str(script)],
+                         capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, (out.stdout[-1500:], out.stderr[-6000:])
+    import re
+
+    res = [json.loads(m) for m in re.findall(r"RESULT (\{[^{}]*\})", out.stdout)]
+    assert len(res) == n, (out.stdout[-1500:], out.stderr[-1500:])
+    assert max(r["worst"] for r in res) < 2e-2
+    print("gemm+reduce-scatter ms (fused / gemm+nccl):", max(r["fused_ms"] for r in res), max(r["nccl_ms"] for r in res))
