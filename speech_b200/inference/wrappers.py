@@ -96,6 +96,10 @@ class CacheAwareASRInferenceWrapper(ASRInferenceWrapper):
             self.set_default_att_context_size(att_context_size)
         if enc.streaming_cfg is None:
             enc.setup_streaming_params()
+        # the encoder step of a streaming batch repeats its shapes: replay it from CUDA graphs (SPEECH_B200_STREAM_GRAPHS=0 to disable)
+        import os
+
+        enc.stream_cuda_graphs = self.device.type == "cuda" and os.environ.get("SPEECH_B200_STREAM_GRAPHS", "1") != "0"
 
     def set_default_att_context_size(self, att_context_size) -> None:
         self.asr_model.encoder.set_default_att_context_size(list(att_context_size))

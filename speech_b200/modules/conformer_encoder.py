@@ -444,9 +444,58 @@ class ConformerEncoder(NeuralModule, AccessMixin):
         clcl = torch.zeros(batch_size, device=device, dtype=torch.int64)
         return clc, clt, clcl
 
+    # ------------------------------------------------------------------ streaming step under CUDA graphs
+    stream_cuda_graphs = False      # set by the streaming wrappers: replay the whole encoder step from a graph per input signature
+    max_stream_graphs = 8
+
     def cache_aware_stream_step(self, processed_signal, processed_signal_length=None, cache_last_channel=None,
                                 cache_last_time=None, cache_last_channel_len=None, keep_all_outputs=True,
                                 drop_extra_pre_encoded=None, bypass_pre_encode=False):
+        """One chunk through the encoder with caches.  A streaming step is ~1000 small launches whose cost is host time, and its
+        shapes repeat from step to step, so on a GPU the step is captured once per signature (batch, frames, drop, dtypes) and
+        replayed; inputs are copied into the graph's static buffers and the returned tensors are the graph's static outputs
+        (valid until the next step with the same signature: callers store what they keep, as the slot cache manager does)."""
+        if (self.stream_cuda_graphs and processed_signal.is_cuda and not self.training and not torch.is_grad_enabled()
+                and cache_last_channel is not None and processed_signal_length is not None and not bypass_pre_encode
+                and not torch.cuda.is_current_stream_capturing()):
+            return self._stream_step_graphed(processed_signal, processed_signal_length, cache_last_channel, cache_last_time,
+                                             cache_last_channel_len, keep_all_outputs, drop_extra_pre_encoded)
+        return self._stream_step_eager(processed_signal, processed_signal_length, cache_last_channel, cache_last_time,
+                                       cache_last_channel_len, keep_all_outputs, drop_extra_pre_encoded, bypass_pre_encode)
+
+    def _stream_step_graphed(self, sig, length, clc, clt, clcl, keep_all_outputs, drop_extra):
+        from collections import OrderedDict
+
+        graphs = self.__dict__.setdefault("_stream_graphs", OrderedDict())
+        key = (tuple(sig.shape), sig.dtype, tuple(clc.shape), clc.dtype, tuple(clt.shape), bool(keep_all_outputs), drop_extra,
+               ops.get_compute_dtype(), torch.is_autocast_enabled())
+        e = graphs.get(key)
+        if e is None:
+            args = [sig.clone(), length.clone(), clc.clone(), clt.clone(), clcl.clone()]
+            run = lambda: self._stream_step_eager(args[0], args[1], args[2], args[3], args[4], keep_all_outputs, drop_extra, False)  # noqa: E731
+            side = torch.cuda.Stream(device=sig.device)
+            side.wait_stream(torch.cuda.current_stream(sig.device))
+            with torch.cuda.stream(side):
+                for _ in range(2):                      # lazy initialisation (tables, kernel attributes, allocator) outside the capture
+                    run()
+            torch.cuda.current_stream(sig.device).wait_stream(side)
+            torch.cuda.synchronize(sig.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                outs = run()
+            e = graphs[key] = {"graph": g, "args": args, "outs": outs}
+            while len(graphs) > self.max_stream_graphs:
+                graphs.popitem(last=False)
+        else:
+            graphs.move_to_end(key)
+        for dst, src in zip(e["args"], (sig, length, clc, clt, clcl)):
+            dst.copy_(src, non_blocking=True)
+        e["graph"].replay()
+        return e["outs"]
+
+    def _stream_step_eager(self, processed_signal, processed_signal_length=None, cache_last_channel=None,
+                           cache_last_time=None, cache_last_channel_len=None, keep_all_outputs=True,
+                           drop_extra_pre_encoded=None, bypass_pre_encode=False):
         """One chunk through the encoder with caches, then trim (reference: ``parts/mixins/streaming.py:40-76``)."""
         if self.streaming_cfg is None:
             self.setup_streaming_params()
