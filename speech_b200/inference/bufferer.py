@@ -24,38 +24,73 @@ from .framing import FeatureBuffer, Frame
 
 
 class AudioBufferer:
+    """Rows of one ``[capacity, buffer_size]`` tensor hold the streams' windows, so that shifting the new samples of a whole
+    batch of streams in is a handful of batched tensor operations (a per-stream ``cat`` costs more host time than the math)."""
+
     def __init__(self, sample_rate: int, buffer_size_in_secs: float):
         self.sample_rate = sample_rate
         self.buffer_size = int(round(buffer_size_in_secs * sample_rate))
-        self.buffers: Dict[int, torch.Tensor] = {}
+        self.store = torch.zeros((0, self.buffer_size), dtype=torch.float32)
+        self.row: Dict[int, int] = {}
+        self.free: List[int] = []
         self.filled: Dict[int, int] = {}
 
+    @property
+    def buffers(self) -> Dict[int, torch.Tensor]:
+        return {sid: self.store[r] for sid, r in self.row.items()}
+
     def reset(self):
-        self.buffers.clear()
+        self.store = torch.zeros((0, self.buffer_size), dtype=torch.float32)
+        self.row.clear()
+        self.free.clear()
         self.filled.clear()
 
     def rm_stream(self, stream_id: int):
-        self.buffers.pop(stream_id, None)
+        r = self.row.pop(stream_id, None)
+        if r is not None:
+            self.free.append(r)
         self.filled.pop(stream_id, None)
+
+    def _row_for(self, f: Frame) -> int:
+        r = self.row.get(f.stream_id)
+        if r is None:
+            if not self.free:
+                grow = max(16, self.store.shape[0])
+                self.free = list(range(self.store.shape[0], self.store.shape[0] + grow))
+                self.store = torch.cat([self.store, torch.zeros((grow, self.buffer_size), dtype=torch.float32)])
+            r = self.free.pop()
+            self.row[f.stream_id] = r
+            self.store[r].zero_()
+            self.filled[f.stream_id] = 0
+        elif f.is_first:
+            self.store[r].zero_()
+            self.filled[f.stream_id] = 0
+        return r
 
     def update(self, frames: List[Frame]):
         """Shift every frame into its stream's window.  Returns ``(windows [B, buffer_size], left_padding [B])`` where
         left padding counts the samples of the window that precede the start of the stream."""
-        outs, pads = [], []
+        rows = [self._row_for(f) for f in frames]
+        groups: Dict[int, List[int]] = {}
+        for k, f in enumerate(frames):
+            groups.setdefault(min(f.size, self.buffer_size), []).append(k)
+        for n, ks in groups.items():
+            idx = torch.tensor([rows[k] for k in ks], dtype=torch.long)
+            new = torch.stack([frames[k].samples[-n:].to(torch.float32) for k in ks]) if n > 0 else None
+            cur = self.store.index_select(0, idx)
+            if n > 0:
+                cur = torch.cat([cur[:, n:], new.cpu()], dim=1)
+            self.store.index_copy_(0, idx, cur)
+        pads = []
         for f in frames:
-            buf = self.buffers.get(f.stream_id)
-            if buf is None or f.is_first:
-                buf = torch.zeros(self.buffer_size, dtype=torch.float32)
-                self.filled[f.stream_id] = 0
             n = min(f.size, self.buffer_size)
-            buf = torch.cat([buf[n:], f.samples[-n:].to(buf.dtype).cpu()])
-            self.buffers[f.stream_id] = buf
             self.filled[f.stream_id] = min(self.buffer_size, self.filled[f.stream_id] + n)
-            outs.append(buf)
             pads.append(self.buffer_size - self.filled[f.stream_id])
+        out = self.store.index_select(0, torch.tensor(rows, dtype=torch.long))
+        for f in frames:
             if f.is_last:
                 self.rm_stream(f.stream_id)
-        return torch.stack(outs), torch.tensor(pads, dtype=torch.long)
+        return out, torch.tensor(pads, dtype=torch.long)
 
 
 class BatchedCacheFeatureBufferer:

@@ -32,6 +32,9 @@ struct SbGemmArgs {
   int ksplit;       // 0 = automatic, -1 = never split K, > 1 = that many K slices (only honoured for D(fp32) += alpha * A B^T)
   const void* const* peer_D;  // device array [world] of fp32 output buffers for GEMM + reduce-scatter (see gemm_tcgen05.cu); or null
   int peer_rows;    // rows of the full output owned by each rank
+  const void* const* peer_A;  // HOST array [peer_world] of device pointers: rank r's row shard of A (all-gather + GEMM); or null
+  int peer_a_rows;  // rows per shard (multiple of 128)
+  int peer_world;
   int pair;         // 0 = default policy, 1 = use CTA pairs (cta_group::2) when the shape allows, -1 = never
 };
 

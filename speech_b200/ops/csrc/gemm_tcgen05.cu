@@ -79,6 +79,7 @@ struct GemmParams {
   // the fp32 output with vector reductions (only for plain accumulating epilogues: D += alpha * A B^T)
   int ksplit, kb_per;
   long long num_work;  // num_tiles * ksplit
+  int a_peer_rows;     // > 0: all-gather + GEMM: rows [r * a_peer_rows, (r+1) * a_peer_rows) of A live in rank r's memory (peer_a.m[r])
   int debug;           // diagnostics only (wrong results): 1 = tensor core alone (operands loaded once), 2 = loads alone (no MMAs)
   EpilogueArgs ep;
   int* status;
@@ -242,10 +243,16 @@ __device__ __forceinline__ void stage_store_32x32(uint8_t* st, int lane, const f
 
 // PAIR = true: launched as clusters of two CTAs; CTA pair c works on 256 x BN tiles (CTA rank r owns rows r*128..r*128+127 of
 // the tile in its tensor memory and stages columns r*BN/2.. of B); only rank 0 issues MMAs (tcgen05.mma.cta_group::2).
+// Tensor maps of the A operand in every rank's memory (all-gather + GEMM): a tile's rows belong to one rank, and the producer
+// simply loads them through that rank's map — an ordinary TMA tile load whose source happens to be peer memory (no multicast).
+struct PeerMaps {
+  CUtensorMap m[8];
+};
+
 template <bool A_MN, bool B_MN, int BN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const GemmParams p) {
+                 const GemmParams p, const __grid_constant__ PeerMaps peer_a) {
   constexpr int BLOCK_N = BN;
   constexpr int NUM_STAGES = num_stages(BN, PAIR);
   constexpr int STAGE_BYTES = stage_bytes(BN, PAIR);
@@ -351,6 +358,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (A_MN) {
               tma_load_4d(sa, &tmap_a, full_bar(s), a_row0, kb * BLOCK_K, b0, b1);
               tma_load_4d(sa + TILE_BYTES / 2, &tmap_a, full_bar(s), a_row0 + 64, kb * BLOCK_K, b0, b1);
+            } else if (p.a_peer_rows > 0) {
+              const int owner = a_row0 / p.a_peer_rows;
+              tma_load_4d(sa, &peer_a.m[owner], full_bar(s), kb * BLOCK_K, a_row0 - owner * p.a_peer_rows, b0, b1);
             } else {
               tma_load_4d(sa, &tmap_a, full_bar(s), kb * BLOCK_K, a_row0, b0, b1);
             }
@@ -734,6 +744,20 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
     p.ksplit = (num_kb + p.kb_per - 1) / p.kb_per;  // no empty slices
     p.num_work = p.num_tiles * p.ksplit;
   }
+  p.a_peer_rows = 0;
+  static PeerMaps pm_zero;
+  PeerMaps pm = pm_zero;
+  if (a->peer_A) {
+    // all-gather + GEMM: A is row-sharded over `peer_world` ranks; peer_A[r] is rank r's shard [peer_a_rows, K] (K-major)
+    if (pair || a->a_mn_major || a->peer_world < 1 || a->peer_world > 8 || a->peer_a_rows <= 0 || a->peer_a_rows % BLOCK_M != 0 ||
+        (long long)a->peer_a_rows * a->peer_world < a->M || a->batch0 != 1 || a->batch1 != 1)
+      return -7;
+    for (int r = 0; r < a->peer_world; ++r) {
+      rc = make_operand_map(&pm.m[r], a->peer_A[r], a->K, a->peer_a_rows, a->lda, 1, 1, 0, 0, BLOCK_M);
+      if (rc) return rc - 2000;
+    }
+    p.a_peer_rows = a->peer_a_rows;
+  }
   p.status = sb_status_ptr();
   if (!p.status) return -2;
   static const int env_debug = [] { const char* e = getenv("SPEECH_B200_GEMM_DEBUG"); return e ? atoi(e) : 0; }();
@@ -763,7 +787,7 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
   if ((long long)grid > p.num_work) grid = (int)p.num_work;
   const int variant = (a->a_mn_major ? 2 : 0) | (a->b_mn_major ? 1 : 0) | (bn == 256 ? 4 : 0) | (pair ? 8 : 0);
-  void (*kern)(const CUtensorMap, const CUtensorMap, const GemmParams) = nullptr;
+  void (*kern)(const CUtensorMap, const CUtensorMap, const GemmParams, const PeerMaps) = nullptr;
   switch (variant) {
     case 0: kern = gemm_bf16_kernel<false, false, 128, false>; break;
     case 1: kern = gemm_bf16_kernel<false, true, 128, false>; break;
@@ -806,8 +830,8 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
+    return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, p, pm);
   }
-  kern<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, p);
+  kern<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, p, pm);
   return (int)cudaGetLastError();
 }

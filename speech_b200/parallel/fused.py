@@ -8,7 +8,12 @@ separate collective kernel runs; the transfer of tile i overlaps the MMAs of til
 accumulators.  A flag barrier (the small-vector peer all-reduce kernel) before and after the launch orders the zeroing, the
 remote reductions and the consumer's read.
 
-The reference reaches the same result with a cuBLAS GEMM followed by an NCCL reduce-scatter
+``AllGatherGemm`` — the column-parallel linear layer fed by sequence-parallel activations (all-gather, then QKV / up projection)
+as ONE GEMM launch: every rank keeps its row shard of the activations in a symmetric buffer, and the GEMM's TMA producer loads
+each A tile straight from the memory of the rank that owns those rows (one tensor map per rank, plain tiled loads, no multicast).
+The gathered activation matrix never exists in memory.
+
+The reference reaches the same results with a cuBLAS GEMM preceded by an NCCL all-gather / followed by an NCCL reduce-scatter
 (``speechlm2/parts/parallel.py`` tensor-parallel plans over ``torch.distributed.tensor``).
 """
 from __future__ import annotations
@@ -52,3 +57,39 @@ class GemmReduceScatter:
                          peer_rows=rows, ksplit=-1)
         self._sync()                                        # all ranks' contributions have landed
         return acc.to(out_dtype) if out_dtype != torch.float32 else acc.clone()
+
+
+class AllGatherGemm:
+    def __init__(self, max_rows_per_rank: int, max_k: int, device: torch.device, group=None):
+        import ctypes
+
+        from ..ops import native
+
+        self.native, self.ctypes = native, ctypes
+        self.group = group or dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("AllGatherGemm supports up to 8 ranks")
+        self.capacity = int(max_rows_per_rank) * int(max_k)
+        self.buf = SymmetricBuffer(self.capacity * 2, device, self.group)
+        self.peer_ptrs = [int(p) for p in self.buf.handle.buffer_ptrs]
+        self.barrier = PeerSmallAllReduce(device, self.group)
+        self._token = torch.zeros(8, dtype=torch.float32, device=device)
+
+    def _sync(self) -> None:
+        self.barrier(self._token)
+
+    def __call__(self, x_local: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: Optional[str] = None) -> torch.Tensor:
+        """x_local [M/W, K] (bf16, this rank's rows), w [N_local, K] -> act(concat_r(x_r) @ w^T + bias) of shape [M, N_local]."""
+        rows, K = x_local.shape
+        if rows % 128 or rows * K > self.capacity or K % 8:
+            raise ValueError("AllGatherGemm: rows per rank must be a multiple of 128 and fit the buffer; K % 8 == 0")
+        mine = self.buf.tensor[: rows * K * 2].view(torch.bfloat16).view(rows, K)
+        mine.copy_(x_local)
+        self._sync()                                        # every rank's shard is in place before anyone loads it
+        M, N = rows * self.world, w.shape[0]
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x_local.device)
+        arr = (self.ctypes.c_void_p * self.world)(*self.peer_ptrs)
+        self.native.gemm(mine, w, out, M=M, N=N, K=K, lda=K, ldb=w.stride(0), ldd=N, bias=bias, act=act, peer_a=arr, peer_a_rows=rows, pair=-1)
+        self._sync()                                        # nobody overwrites its shard while a peer may still be reading it
+        return out

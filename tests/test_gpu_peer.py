@@ -221,6 +221,21 @@ GEMM_RS_SCRIPT = textwrap.dedent("""
         dist.reduce_scatter_tensor(ref, full)
         torch.cuda.synchronize()
         worst = max(worst, float((got - ref).abs().max() / ref.abs().max()))
+    # all-gather + GEMM: A tiles are TMA-loaded from the owner rank's memory
+    from speech_b200.parallel.fused import AllGatherGemm
+    ag = AllGatherGemm(1024, 2048, dev)
+    for it, (rows, N, K) in enumerate([(256, 512, 512), (1024, 1032, 2048), (128, 256, 72)]):
+        torch.manual_seed(50 + 7 * it + rank)
+        xl = torch.randn(rows, K, device=dev).to(torch.bfloat16)
+        torch.manual_seed(99 + it)
+        w2 = (torch.randn(N, K, device=dev) * 0.1).to(torch.bfloat16)
+        b2 = torch.randn(N, device=dev)
+        got = ag(xl, w2, bias=b2, act="relu").float()
+        parts = [torch.empty_like(xl) for _ in range(world)]
+        dist.all_gather(parts, xl)
+        ref = torch.relu(torch.cat(parts).float() @ w2.float().t() + b2)
+        torch.cuda.synchronize()
+        worst = max(worst, float((got - ref).abs().max() / ref.abs().max()) * 0.1)     # bf16 output: scaled into the fp32 budget below
     # timing against GEMM + NCCL reduce-scatter (device events, max over ranks is taken by the test)
     M, N, K = 1024 * world, 1024, 4096
     x = torch.randn(M, K, device=dev).to(torch.bfloat16); w = torch.randn(N, K, device=dev).to(torch.bfloat16)

@@ -156,3 +156,28 @@ def test_classic_tts_g2p_alignment_fastpitch_vocoder_aligner():
     l2 = al.training_step((text, text_len, audio, torch.tensor([4000, 3000])), 0)["loss"]
     l2.backward()
     assert math.isfinite(float(l2))
+
+
+def test_preference_losses_and_grpo_math():
+    from speech_b200.tts.preference import grpo_advantages, grpo_loss, preference_loss, sequence_logprob
+
+    torch.manual_seed(0)
+    logits = torch.randn(2, 5, 3, 7)
+    tgt = torch.randint(0, 7, (2, 5, 3))
+    mask = torch.tensor([[1.0, 1, 1, 1, 1], [1, 1, 1, 0, 0]])
+    lp = sequence_logprob(logits, tgt, mask)
+    ref = torch.log_softmax(logits, -1).gather(-1, tgt.unsqueeze(-1)).squeeze(-1).sum(-1)
+    assert torch.allclose(lp[1], ref[1, :3].sum()) and torch.allclose(lp[0], ref[0].sum())
+    pc, pr, rc, rr = torch.tensor([-10.0]), torch.tensor([-12.0]), torch.tensor([-11.0]), torch.tensor([-11.0])
+    loss, c, r = preference_loss(pc, pr, rc, rr, beta=0.5, loss_type="dpo")
+    assert torch.allclose(loss, -torch.nn.functional.logsigmoid(torch.tensor(0.5 * 2.0))) and float(c) > float(r)
+    assert float(preference_loss(pc, pr, rc, rr, beta=0.5, loss_type="ipo")[0]) == pytest.approx((2.0 - 1.0) ** 2)
+    assert float(preference_loss(pc, pr, rc, rr, 0.5, "rpo_sq", torch.tensor([1.0]), torch.tensor([0.0]))[0]) == pytest.approx(0.0)
+    with pytest.raises(NotImplementedError):
+        preference_loss(pc, pr, rc, rr, loss_type="xyz")
+    adv = grpo_advantages(torch.tensor([[1.0, 2.0, 3.0], [5.0, 5.0, 5.0]]))
+    assert torch.allclose(adv[0].mean(), torch.tensor(0.0), atol=1e-6) and float(adv[1].abs().max()) == 0.0 and float(adv[0, 2]) > 1.0
+    new = torch.tensor([-5.0, -6.0], requires_grad=True)
+    l = grpo_loss(new, new.detach(), torch.tensor([1.0, -1.0]), ref_logp=torch.tensor([-5.5, -6.0]), kl_beta=0.1, lengths=torch.tensor([5, 5]))
+    l.backward()
+    assert new.grad[0] < 0 < new.grad[1]          # raise the likelihood of the above-average sample, lower the other
