@@ -69,7 +69,7 @@ def main():
     res = {"metric": "cache-aware streaming RTFx", "value": round(float(pipe.rtfx()), 1), "unit": "audio-seconds/s", "n_gpus": 1,
            "streams": args.streams, "seconds_per_stream": args.seconds, "chunk_ms": round(chunk_s * 1e3, 1), "steps": int(steps.size),
            "step_ms_p50": round(float(np.percentile(steps, 50)) * 1e3, 2), "step_ms_p99": round(float(np.percentile(steps, 99)) * 1e3, 2),
-           "step_ms_first": round(float(steps[0]) * 1e3, 2), "step_ms_max_after_first": round(float(steps[1:].max()) * 1e3, 2) if steps.size > 1 else None,
+           "step_ms_first": round(float(steps[0]) * 1e3, 2), "slowest_steps": [int(i) for i in np.argsort(steps)[-3:][::-1]], "step_ms_max_after_first": round(float(steps[1:].max()) * 1e3, 2) if steps.size > 1 else None,
            "real_time": bool(np.percentile(steps, 99) <= chunk_s), "rtfx_wall": round(total_audio / wall, 1), "dtype": "bf16", "data": "synthetic",
            "tokens_emitted": int(sum(len(o.text.split()) for o in out.values())), "blank_bias": args.blank_bias,
            "config": {"model": f"FastConformer-{args.size} cache-aware RNNT, att_context [70,{args.lookahead}]", "batch_size": bs}}

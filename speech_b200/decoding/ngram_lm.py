@@ -3,8 +3,9 @@
 An ARPA model becomes a back-off automaton held in a handful of flat tensors: every n-gram context of length < order is a
 state; ``arcs`` (sorted by ``state * V + token``) carry a log-probability and a destination state, every state has a
 back-off weight and a back-off state.  ``advance(states[B])`` returns ``scores[B, V]`` (natural log) and
-``next_states[B, V]`` for ALL tokens at once: up to ``order`` rounds of a vectorised binary search over the arc keys, adding
-back-off weights for the (state, token) pairs not yet resolved — no host synchronisation, no dense ``S x V`` table.
+``next_states[B, V]`` for ALL tokens at once — no host synchronisation, no dense ``S x V`` table.  On a GPU this is one
+kernel (``ops/csrc/decode_aux.cu``: the back-off chain is walked once per hypothesis, every token then searches the short arc
+range of each level); on the CPU it is up to ``order`` rounds of a vectorised binary search over the arc keys.
 Same contract as the reference's ``NGramGPULanguageModel`` (``parts/submodules/ngram_lm/ngram_lm_batched.py:505``;
 ``advance`` ``:1005-1129``), whose ARPA files store token ids as single characters ``chr(id + 100)``
 (``kenlm_utils.py`` ``DEFAULT_TOKEN_OFFSET``).
@@ -54,24 +55,10 @@ class BackoffGraph(torch.nn.Module):
 
     @torch.no_grad()
     def advance(self, states: torch.Tensor, eos_id: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-        B, V = states.shape[0], self.vocab_size
-        cur = states.view(B, 1).expand(B, V)
-        acc = torch.zeros((B, V), dtype=torch.float32, device=states.device)
-        done = torch.zeros((B, V), dtype=torch.bool, device=states.device)
-        scores = torch.zeros_like(acc)
-        nxt = torch.full((B, V), self.start_state, dtype=torch.long, device=states.device)
-        last = self.arc_keys.shape[0] - 1
-        for _ in range(self.max_depth):
-            key = cur * V + self._tok
-            idx = torch.searchsorted(self.arc_keys, key).clamp(max=last)
-            hit = (self.arc_keys[idx] == key) & ~done
-            scores = torch.where(hit, acc + self.arc_w[idx], scores)
-            nxt = torch.where(hit, self.arc_to[idx], nxt)
-            done = done | hit
-            acc = acc + self.backoff_w[cur]
-            cur = self.backoff_to[cur]
-        scores = torch.where(done, scores, acc + self.default_score)
-        return scores, nxt
+        from .. import ops
+
+        return ops.ngram_advance(states, self.arc_keys, self.arc_w, self.arc_to, self.backoff_w, self.backoff_to, self.vocab_size,
+                                 self.max_depth, self.default_score, self.start_state)
 
     forward = advance
 

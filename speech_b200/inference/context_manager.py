@@ -6,7 +6,11 @@ slots of the streams in the batch, runs the encoder chunk and scatters the updat
 their slot zeroed and returned to the free list (reference behaviour: ``inference/utils/context_manager.py:45-197``).
 
 The gather and scatter are single ``index_select`` / ``index_copy_`` calls on the resident tensors, so the per-step cost is
-one read and one write of the batch's cache rows and no allocation beyond the gathered batch.
+one read and one write of the batch's cache rows and no allocation beyond the gathered batch.  When a batch holds every slot
+in slot order (a server running at its capacity: the steady state of continuous batching) there is nothing to permute: the
+step reads the resident tensors themselves and the new caches are copied back with one contiguous copy; at 256 streams of
+a 24-layer, 1024-wide encoder the attention cache is 0.9 GB, and the indexed gather + scatter cost several times the
+contiguous copy.
 """
 from __future__ import annotations
 
@@ -41,6 +45,7 @@ class CacheAwareContextManager:
         self.streamidx2slotidx: Dict[int, int] = {}
         self.slotidx2streamidx: Dict[int, int] = {}
         self.free_slots = deque(range(self.num_slots))
+        self._identity = list(range(self.num_slots))
         if self.use_cache:
             clc, clt, clcl = self.model.get_initial_cache_state(batch_size=self.num_slots)
             if self.device is not None:
@@ -88,6 +93,8 @@ class CacheAwareContextManager:
         mapping = dict(zip(stream_ids, slots))
         if not self.use_cache:
             return CacheAwareContext(), mapping
+        if slots == self._identity:
+            return CacheAwareContext(self.cache_last_channel, self.cache_last_time, self.cache_last_channel_len), mapping
         idx = torch.tensor(slots, device=self.device, dtype=torch.long)
         return CacheAwareContext(self.cache_last_channel.index_select(1, idx), self.cache_last_time.index_select(1, idx),
                                  self.cache_last_channel_len.index_select(0, idx)), mapping
@@ -95,9 +102,16 @@ class CacheAwareContextManager:
     def update_cache(self, stream_ids: List[int], new_context: CacheAwareContext, mapping: Dict[int, int]) -> None:
         if not self.use_cache:
             return
-        idx = torch.tensor([mapping[s] for s in stream_ids], device=self.device, dtype=torch.long)
+        slots = [mapping[s] for s in stream_ids]
         clc = new_context.cache_last_channel
         keep = self.cache_last_channel.shape[2]
+        if slots == self._identity and clc.shape[2] == keep:
+            for dst, src in ((self.cache_last_channel, clc), (self.cache_last_time, new_context.cache_last_time),
+                             (self.cache_last_channel_len, new_context.cache_last_channel_len)):
+                if dst.data_ptr() != src.data_ptr():
+                    dst.copy_(src)
+            return
+        idx = torch.tensor(slots, device=self.device, dtype=torch.long)
         if clc.shape[2] != keep:  # the encoder may return a shorter / longer window than the resident one
             if clc.shape[2] > keep:
                 clc = clc[:, :, -keep:]

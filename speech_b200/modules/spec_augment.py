@@ -2,7 +2,8 @@
 
 Frequency masks and (adaptive) time masks are drawn per utterance and applied in place, fully on
 the device without a host synchronisation: mask start / width tensors are sampled with
-``torch.rand`` for the whole batch and applied as a broadcast comparison.  Reference behaviour:
+``torch.rand`` for the whole batch; on a GPU one kernel then writes just the masked elements
+(``ops/csrc/decode_aux.cu``), on the CPU they are applied as a broadcast comparison.  Reference behaviour:
 ``nemo/collections/asr/parts/submodules/spectr_augment.py:25,218`` and the Numba kernel
 ``parts/numba/spec_augment/spec_aug_numba.py:27-95`` (time-mask width is ``time_width`` frames, or
 a fraction of the utterance length when ``time_width`` is a float — "adaptive").
@@ -13,6 +14,7 @@ from typing import Optional, Union
 
 import torch
 
+from .. import ops
 from ..core.module import NeuralModule
 from ..core.neural_types import LengthsType, NeuralType, SpectrogramType, typecheck
 
@@ -34,25 +36,19 @@ class SpecAugment(torch.nn.Module):
         dev = input_spec.device
         if length is None:
             length = torch.full((B,), T, device=dev, dtype=torch.long)
-        fill = torch.zeros(B, F, T, dtype=torch.bool, device=dev)
+        f_start = f_w = t_start = t_w = None
         if self.freq_masks > 0:
-            w = torch.randint(0, self.freq_width + 1, (B, self.freq_masks), device=dev)
-            start = (torch.rand(B, self.freq_masks, device=dev) * (F - w + 1).clamp(min=1)).long()
-            f = torch.arange(F, device=dev)[None, None, :]
-            fm = ((f >= start[..., None]) & (f < (start + w)[..., None])).any(dim=1)  # B,F
-            fill |= fm[:, :, None]
+            f_w = torch.randint(0, self.freq_width + 1, (B, self.freq_masks), device=dev)
+            f_start = (torch.rand(B, self.freq_masks, device=dev) * (F - f_w + 1).clamp(min=1)).long()
         if self.time_masks > 0:
             if self.adaptive_temporal_width:
                 tw = (length.float() * self.time_width).long().clamp(min=1)[:, None]
             else:
                 tw = torch.full((B, 1), int(self.time_width), device=dev)
-            w = (torch.rand(B, self.time_masks, device=dev) * (tw + 1).float()).long()
-            hi = (length[:, None] - w).clamp(min=1)
-            start = (torch.rand(B, self.time_masks, device=dev) * hi.float()).long()
-            t = torch.arange(T, device=dev)[None, None, :]
-            tm = ((t >= start[..., None]) & (t < (start + w)[..., None])).any(dim=1)  # B,T
-            fill |= tm[:, None, :]
-        return input_spec.masked_fill(fill, self.mask_value)
+            t_w = (torch.rand(B, self.time_masks, device=dev) * (tw + 1).float()).long()
+            hi = (length[:, None] - t_w).clamp(min=1)
+            t_start = (torch.rand(B, self.time_masks, device=dev) * hi.float()).long()
+        return ops.specaugment(input_spec, f_start, f_w, t_start, t_w, self.mask_value)
 
 
 class SpecCutout(torch.nn.Module):

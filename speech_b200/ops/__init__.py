@@ -117,6 +117,24 @@ def lowp(param: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tens
     return t
 
 
+# ----------------------------------------------------------------------------- augmentation / LM fusion
+def specaugment(x, f_start, f_width, t_start, t_width, mask_value: float = 0.0):
+    """Copy of ``x`` [B, F, T] with the frequency rows ``[f_start, f_start + f_width)`` and the time ranges
+    ``[t_start, t_start + t_width)`` of every utterance set to ``mask_value`` (start / width: integer [B, n] or None)."""
+    if _use_native(x) and x.dtype in (torch.float32, torch.bfloat16) and (t_start is None or t_start.shape[1] <= 32):
+        i32 = lambda t: None if t is None else t.to(torch.int32).contiguous()  # noqa: E731
+        return _nat().specaugment_(x.clone(memory_format=torch.contiguous_format), i32(f_start), i32(f_width), i32(t_start),
+                                   i32(t_width), mask_value)
+    return reference.specaugment(x, f_start, f_width, t_start, t_width, mask_value)
+
+
+def ngram_advance(states, arc_keys, arc_w, arc_to, backoff_w, backoff_to, V: int, depth: int, default_score: float, start_state: int):
+    if _use_native(states) and depth <= 16:
+        return _nat().ngram_advance(states.contiguous(), arc_keys, arc_w, arc_to, backoff_w, backoff_to, V, depth, default_score,
+                                    start_state)
+    return reference.ngram_advance(states, arc_keys, arc_w, arc_to, backoff_w, backoff_to, V, depth, default_score, start_state)
+
+
 # ----------------------------------------------------------------------------- dense layers
 def linear(x, weight, bias=None, act: Optional[str] = None, residual=None, alpha: float = 1.0, dropout_p: float = 0.0):
     """``residual + alpha * dropout(act(x W^T + b))``; ``dropout_p`` > 0 means "apply dropout now" (callers pass 0 in eval)."""

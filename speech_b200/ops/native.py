@@ -337,6 +337,29 @@ def adamw_flat(master, grad, exp_avg, exp_avg_sq, lowp, lr, beta1, beta2, eps, w
 
 
 from .native_blocks import conv_module_core, mha_attention, relpos_attention  # noqa: E402,F401
+def specaugment_(x: torch.Tensor, f_start, f_width, t_start, t_width, mask_value: float = 0.0) -> torch.Tensor:
+    """Mask ``x`` [B, F, T] (fp32 / bf16, contiguous) in place; start / width tensors are int32 [B, n] or None."""
+    B, F, T = x.shape
+    nf = 0 if f_start is None else f_start.shape[1]
+    nt = 0 if t_start is None else t_start.shape[1]
+    _check(lib().sb_specaugment(_ptr(x), ctypes.c_int(int(x.dtype == torch.bfloat16)), ctypes.c_int(B), ctypes.c_int(F), ctypes.c_int(T),
+                                _ptr(f_start), _ptr(f_width), ctypes.c_int(nf), _ptr(t_start), _ptr(t_width), ctypes.c_int(nt),
+                                ctypes.c_void_p(0), ctypes.c_float(mask_value), _stream()), "sb_specaugment")
+    return x
+
+
+def ngram_advance(states, arc_keys, arc_w, arc_to, backoff_w, backoff_to, V: int, depth: int, default_score: float, start_state: int):
+    """One back-off automaton step for every (hypothesis, token): returns ``scores [B, V]`` fp32 and ``next_states [B, V]`` int64."""
+    B = states.shape[0]
+    scores = torch.empty((B, V), dtype=torch.float32, device=states.device)
+    nxt = torch.empty((B, V), dtype=torch.long, device=states.device)
+    _check(lib().sb_ngram_advance(_ptr(states), _ptr(arc_keys), _ptr(arc_w), _ptr(arc_to), _ptr(backoff_w), _ptr(backoff_to),
+                                  ctypes.c_int(arc_keys.shape[0]), ctypes.c_int(backoff_to.shape[0]), ctypes.c_int(B), ctypes.c_int(V),
+                                  ctypes.c_int(depth), ctypes.c_float(default_score), ctypes.c_longlong(start_state), _ptr(scores),
+                                  _ptr(nxt), _stream()), "sb_ngram_advance")
+    return scores, nxt
+
+
 from .native_transducer import transducer_joint_loss, transducer_loss_from_logits  # noqa: E402,F401
 from .native_lstm import lstm  # noqa: E402,F401
 from .native_ctc import ctc_loss  # noqa: E402,F401

@@ -357,3 +357,39 @@ def lstm(x, weights: List[torch.Tensor], h0=None, c0=None, num_layers: int = 1, 
         c0 = x.new_zeros(num_layers, B, H)
     out, h, c = torch._VF.lstm(x, (h0, c0), [w.to(x.dtype) for w in weights], True, num_layers, dropout, training, False, False)
     return out, (h, c)
+
+
+def specaugment(x, f_start, f_width, t_start, t_width, mask_value: float = 0.0):
+    B, F, T = x.shape
+    fill = torch.zeros(B, F, T, dtype=torch.bool, device=x.device)
+    if f_start is not None and f_start.shape[1] > 0:
+        f = torch.arange(F, device=x.device)[None, None, :]
+        fill |= ((f >= f_start[..., None]) & (f < (f_start + f_width)[..., None])).any(dim=1)[:, :, None]
+    if t_start is not None and t_start.shape[1] > 0:
+        t = torch.arange(T, device=x.device)[None, None, :]
+        fill |= ((t >= t_start[..., None]) & (t < (t_start + t_width)[..., None])).any(dim=1)[:, None, :]
+    return x.masked_fill(fill, mask_value)
+
+
+def ngram_advance(states, arc_keys, arc_w, arc_to, backoff_w, backoff_to, V: int, depth: int, default_score: float, start_state: int):
+    """Up to ``depth`` rounds of a vectorised binary search over the sorted arc keys, adding back-off weights for the
+    (state, token) pairs not yet resolved."""
+    B = states.shape[0]
+    tok = torch.arange(V, dtype=torch.long, device=states.device)
+    cur = states.view(B, 1).expand(B, V)
+    acc = torch.zeros((B, V), dtype=torch.float32, device=states.device)
+    done = torch.zeros((B, V), dtype=torch.bool, device=states.device)
+    scores = torch.zeros_like(acc)
+    nxt = torch.full((B, V), start_state, dtype=torch.long, device=states.device)
+    last = arc_keys.shape[0] - 1
+    for _ in range(depth):
+        key = cur * V + tok
+        idx = torch.searchsorted(arc_keys, key).clamp(max=last)
+        hit = (arc_keys[idx] == key) & ~done
+        scores = torch.where(hit, acc + arc_w[idx], scores)
+        nxt = torch.where(hit, arc_to[idx], nxt)
+        done = done | hit
+        acc = acc + backoff_w[cur]
+        cur = backoff_to[cur]
+    scores = torch.where(done, scores, acc + default_score)
+    return scores, nxt

@@ -225,6 +225,61 @@ class MagpieTTSModel(ModelPT):
         out = self.local_transformer(seq, mask)["output"]
         return torch.stack([self.local_transformer_out_projections[c](out[:, c]) for c in range(target_codes.shape[1])], dim=1).float()
 
+    @property
+    def local_mask_id(self) -> int:
+        """Token that stands for "not decided yet" in the MaskGit local transformer (the last special audio token)."""
+        return self.num_all_tokens_per_codebook - 1
+
+    def local_transformer_maskgit_logits(self, h: torch.Tensor, target_codes: torch.Tensor, masked: torch.Tensor) -> torch.Tensor:
+        """Bidirectional local transformer: position 0 = decoder state, position 1+c = embedding of codebook c's token, or of
+        the mask token where ``masked[:, c]``; logits [N, C, V] for every codebook (reference: ``magpietts.py:532-570``)."""
+        C = target_codes.shape[1]
+        x0 = self.local_transformer_in_projection(h).unsqueeze(1)
+        inp = torch.where(masked, torch.full_like(target_codes, self.local_mask_id), target_codes)
+        embs = [self.local_transformer_audio_embeddings[c](inp[:, c]).unsqueeze(1) for c in range(C)]
+        seq = torch.cat([x0] + embs, dim=1)
+        mask = torch.ones(seq.shape[:2], dtype=torch.bool, device=seq.device)
+        out = self.local_transformer(seq, mask)["output"]
+        return torch.stack([self.local_transformer_out_projections[c](out[:, 1 + c]) for c in range(C)], dim=1).float()
+
+    def _maskgit_loss(self, h: torch.Tensor, target_codes: torch.Tensor) -> torch.Tensor:
+        """Mask a cosine-scheduled random share of every frame's codebooks (at least one) and predict the masked ones."""
+        N, C = target_codes.shape
+        ratio = torch.cos(torch.rand(N, device=h.device) * math.pi / 2)                     # in (0, 1], more often high
+        n_mask = (ratio * C).ceil().clamp(1, C).long()
+        order = torch.rand(N, C, device=h.device).argsort(dim=1).argsort(dim=1)
+        masked = order < n_mask[:, None]
+        lg = self.local_transformer_maskgit_logits(h, target_codes, masked)
+        return F.cross_entropy(lg[masked], target_codes[masked])
+
+    @torch.no_grad()
+    def _local_maskgit(self, h, temperature, topk, n_steps: int = 3, uncond=None, cfg_scale: float = 1.0):
+        """Iterative parallel decoding of one frame: predict all undecided codebooks, keep the most confident ones, repeat."""
+        CS = len(self.audio_embeddings)
+        N = h.shape[0]
+        codes = torch.full((N, CS), self.local_mask_id, dtype=torch.long, device=h.device)
+        masked = torch.ones(N, CS, dtype=torch.bool, device=h.device)
+        for it in range(n_steps):
+            lg = self.local_transformer_maskgit_logits(h, codes, masked)
+            if uncond is not None:
+                ul = self.local_transformer_maskgit_logits(uncond, codes, masked)
+                lg = ul + cfg_scale * (lg - ul)
+            lg[..., self.audio_bos_id] = float("-inf")
+            lg[..., self.audio_eos_id + 1:] = float("-inf")
+            tok = self._sample(lg, temperature, topk)
+            conf = torch.softmax(lg, -1).gather(-1, tok.unsqueeze(-1)).squeeze(-1).masked_fill(~masked, float("inf"))
+            # number of codebooks still undecided after this round follows the cosine schedule; the last round decides all
+            keep_masked = 0 if it == n_steps - 1 else int(math.floor(CS * math.cos(math.pi / 2 * (it + 1) / n_steps)))
+            codes = torch.where(masked, tok, codes)
+            if keep_masked > 0:
+                redo = conf.argsort(dim=1)[:, :keep_masked]                                 # least confident stay undecided
+                newmask = torch.zeros_like(masked).scatter(1, redo, True) & masked
+            else:
+                newmask = torch.zeros_like(masked)
+            codes = torch.where(newmask, torch.full_like(codes, self.local_mask_id), codes)
+            masked = newmask
+        return codes
+
     def _loss(self, batch):
         text, text_len, audio, audio_len = batch[:4]
         codes, codes_len = self.audio_to_codes(audio, audio_len)
@@ -236,8 +291,11 @@ class MagpieTTSModel(ModelPT):
         logs = {"codebook_loss": ce.detach()}
         loss = ce
         if self.local_transformer_type != "none":
-            lt = self.local_transformer_logits(h[xmask].float(), tgt[xmask])
-            lt_loss = F.cross_entropy(lt.reshape(-1, lt.shape[-1]), tgt[xmask].reshape(-1))
+            if self.local_transformer_type == "maskgit":
+                lt_loss = self._maskgit_loss(h[xmask].float(), tgt[xmask])
+            else:
+                lt = self.local_transformer_logits(h[xmask].float(), tgt[xmask])
+                lt_loss = F.cross_entropy(lt.reshape(-1, lt.shape[-1]), tgt[xmask].reshape(-1))
             loss = loss + lt_loss
             logs["local_transformer_loss"] = lt_loss.detach()
         if self.alignment_loss_scale > 0 and not drop and self.alignment_layers:
@@ -302,6 +360,10 @@ class MagpieTTSModel(ModelPT):
                 logits = logits[B:] + cfg_scale * (logits[:B] - logits[B:])
             if self.local_transformer_type == "autoregressive":
                 nxt = self._local_ar(h[:B].float(), temperature, topk, uncond=h[B:].float() if use_cfg else None, cfg_scale=cfg_scale)
+            elif self.local_transformer_type == "maskgit":
+                nxt = self._local_maskgit(h[:B].float(), temperature, topk, uncond=h[B:].float() if use_cfg else None, cfg_scale=cfg_scale)
+                if step < min_generated_frames:
+                    nxt = torch.where(nxt == self.audio_eos_id, torch.zeros_like(nxt), nxt)
             else:
                 logits[..., self.audio_bos_id] = float("-inf")
                 logits[..., self.audio_eos_id + 1:] = float("-inf")

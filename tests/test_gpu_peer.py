@@ -77,7 +77,7 @@ PEER_SCRIPT = textwrap.dedent("""
         same = x.clone(); dist.broadcast(same, 0)
         assert torch.equal(same, x), "ranks disagree"
     native.check_status()
-    print("RESULT", json.dumps({{"rank": rank, "worst": worst}}))
+    sys.stdout.write("RESULT " + json.dumps({{"rank": rank, "worst": worst}}) + chr(10)); sys.stdout.flush()
     dist.destroy_process_group()
 """)
 
@@ -176,7 +176,7 @@ SYNC_BN_SCRIPT = textwrap.dedent("""
     rm = res[1][2].clone(); dist.broadcast(rm, 0)
     out["rm_same"] = bool(torch.allclose(rm, res[1][2], atol=1e-6))
     native.check_status()
-    print("RESULT", json.dumps(out))
+    sys.stdout.write("RESULT " + json.dumps(out) + chr(10)); sys.stdout.flush()
     dist.destroy_process_group()
 """)
 
@@ -252,8 +252,14 @@ GEMM_RS_SCRIPT = textwrap.dedent("""
         y = x @ w.t()
         dist.reduce_scatter_tensor(out, y)
     t_fused, t_base = timed(lambda: op(x, w)), timed(baseline)
+    xl = torch.randn(1024, 2048, device=dev).to(torch.bfloat16); w3 = torch.randn(4096, 2048, device=dev).to(torch.bfloat16)
+    gathered = torch.empty(1024 * world, 2048, device=dev, dtype=torch.bfloat16)
+    def ag_baseline():
+        dist.all_gather_into_tensor(gathered, xl)
+        return gathered @ w3.t()
+    t_ag, t_ag_base = timed(lambda: ag(xl, w3)), timed(ag_baseline)
     native.check_status()
-    print("RESULT", json.dumps({{"rank": rank, "worst": worst, "fused_ms": t_fused, "nccl_ms": t_base}}))
+    sys.stdout.write("RESULT " + json.dumps({{"rank": rank, "worst": worst, "fused_ms": t_fused, "nccl_ms": t_base, "ag_fused_ms": t_ag, "ag_nccl_ms": t_ag_base}}) + chr(10)); sys.stdout.flush()
     dist.destroy_process_group()
 """)
 
@@ -274,3 +280,4 @@ def test_gemm_reduce_scatter_fused_over_peer_memory(tmp_path):
     assert len(res) == n, (out.stdout[-1500:], out.stderr[-1500:])
     assert max(r["worst"] for r in res) < 2e-2
     print("gemm+reduce-scatter ms (fused / gemm+nccl):", max(r["fused_ms"] for r in res), max(r["nccl_ms"] for r in res))
+    print("all-gather+gemm ms (fused / nccl+gemm):", max(r["ag_fused_ms"] for r in res), max(r["ag_nccl_ms"] for r in res))

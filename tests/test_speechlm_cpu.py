@@ -214,3 +214,70 @@ def test_duplex_models_and_salm_variants():
     auto = SALMAutomodel(scfg, tokenizer=tok)
     auto.configure_model(None)
     assert auto.device_mesh is None
+
+
+def test_ear_tts_mog_rvq_duplex_speech_decoder_and_voice_chat():
+    from speech_b200.speechlm.duplex import DuplexSTTModel
+    from speech_b200.speechlm.ear_tts import (DuplexEARTTS, DuplexS2SSpeechDecoderModel, EARTTSModel, MoGHead, NemotronVoiceChat,
+                                              ResidualVQ)
+
+    torch.manual_seed(0)
+    rvq = ResidualVQ(3, 16, 8)
+    codes = torch.randint(0, 16, (2, 5, 3))
+    lat = rvq.embed(codes)
+    assert lat.shape == (2, 5, 8)
+    # a latent that is exactly a depth sum quantises to a tuple with the same sum (greedy residual search is consistent)
+    again = rvq.embed(rvq.encode(lat))
+    assert float((again - lat).norm()) <= float(lat.norm()) * 0.5
+    assert torch.allclose(rvq.embed(codes, torch.full((2, 5), 1)), rvq.codebooks[0][codes[..., 0]])
+    head = MoGHead(32, 64, 8, num_layers=1, num_predictions=4, low_rank=4)
+    x = torch.randn(6, 32)
+    logits, mus, logs = head(x)
+    assert logits.shape == (6, 4) and mus.shape == (6, 4, 8) and logs.shape == (6, 1)
+    # the mixture density integrates to one: NLL of a one-component head equals the Gaussian formula
+    one = MoGHead(32, 64, 8, num_layers=1, num_predictions=1, low_rank=None)
+    _, mu1, ls1 = one(x)
+    tgt = torch.randn(6, 8)
+    want = 0.5 * ((tgt - mu1[:, 0]) ** 2).sum(-1) * torch.exp(-2 * ls1[:, 0]) + 8 * ls1[:, 0] + 4 * math.log(2 * math.pi)
+    assert torch.allclose(one.nll(x, tgt), want, atol=1e-4)
+    g = torch.Generator().manual_seed(1)
+    s = head.infer(x, top_p_or_k=1, generator=g)              # top-1: the mean of the most likely component
+    best = logits.argmax(-1)
+    assert torch.allclose(s, mus[torch.arange(6), best], atol=1e-5)
+    cfg = OmegaConf.create({"tts": {"backbone": dict(TINY), "num_quantizers": 3, "codebook_size": 16, "latent_size": 8, "num_predictions": 4,
+                                    "low_rank": 4, "cfg_dropout": 0.5}, "optim": {"name": "adamw", "lr": 1e-3}})
+    tts = DuplexEARTTS(cfg)
+    batch = {"target_tokens": torch.randint(3, 50, (2, 12)), "target_codes": torch.randint(0, 16, (2, 12, 3)), "target_lens": torch.tensor([12, 9])}
+    loss = tts.training_step(batch, 0)["loss"]
+    loss.backward()
+    assert math.isfinite(float(loss)) and tts.tts.head.proj_logits.weight.grad is not None and tts.tts.rvq.codebooks.grad is None
+    gen = tts.offline_inference(batch["target_tokens"][:, :6], guidance_scale=1.5, top_p_or_k=2)
+    assert gen["codes"].shape == (2, 6, 3) and int(gen["codes"].max()) < 16
+    # incremental generation with caches equals the teacher-forced forward on its own outputs (top-1, no noise)
+    m: EARTTSModel = tts.tts.eval()
+    toks = batch["target_tokens"][:1, :5]
+    c = m.generate(toks, top_p_or_k=1)
+    hist = m.rvq.embed(c)
+    prev = torch.cat([m.bos_emb.expand(1, 1, -1), hist[:, :-1]], dim=1)
+    h = m.backbone(inputs_embeds=m._inputs(prev, toks), return_hidden=True)["hidden_states"]
+    lg, mu, _ = m.head(h)
+    full = m.rvq.encode(mu[0, torch.arange(5), lg[0].argmax(-1)])
+    assert torch.equal(full, c[0])
+    pc = {"preprocessor": {**preprocessor_cfg(32), "dither": 0.0}, "encoder": encoder_cfg("small", 32, 0.0, 0.0, n_layers=1),
+          "modality_adapter": {"_target_": "speech_b200.speechlm.perception.IdentityConnector", "d_model": 176}}
+    scfg = OmegaConf.create({"llm": dict(TINY), "perception": pc, "codebook_size": 10, "num_codebooks": 2,
+                             "speech_decoder": dict(TINY, num_hidden_layers=1), "optim": {"name": "adamw", "lr": 1e-3}})
+    audio, lens = torch.randn(2, 16000), torch.tensor([16000, 12000])
+    sd = DuplexS2SSpeechDecoderModel(scfg)
+    l = sd.training_step({"source_audio": audio, "source_audio_lens": lens, "target_tokens": torch.randint(3, 50, (2, 30)),
+                          "target_codes": torch.randint(0, 10, (2, 30, 2))}, 0)["loss"]
+    l.backward()
+    assert math.isfinite(float(l)) and sd.audio_head.weight.grad is not None and sd.hidden_proj.weight.grad is not None
+    out = sd.offline_inference(audio, lens)
+    assert out["codes"].shape == (2, out["tokens"].shape[1], 2) and len(out["text"]) == 2
+    chat = NemotronVoiceChat(DuplexSTTModel(scfg), tts)
+    res = chat.offline_inference(audio, lens, top_p_or_k=1)
+    assert res["codes"].shape[:2] == res["tokens"].shape and res["codes"].shape[2] == 3
+    # the speaking half lags the text channel by one frame: the first spoken frame is conditioned on PAD
+    st = chat.init_state(2, audio.device)
+    assert int(st["pending_text"][0]) == chat.stt.text_pad_id

@@ -102,6 +102,33 @@ def test_cache_aware_pipeline_matches_offline_limited_context(kind):
     assert pipe.rtfx() > 0
 
 
+def test_cache_aware_pipeline_full_batch_in_slot_order_skips_the_gather():
+    """A batch that holds every slot in order reads the resident caches directly; the tokens equal the offline ones."""
+    torch.manual_seed(0)
+    model = EncDecCTCModelBPE(_streaming_overrides(fastconformer_ctc_config(
+        "small", vocab_size=32, n_layers=2, causal=True, att_context_size=[8, 1], att_context_style="chunked_limited",
+        conv_norm_type="layer_norm")))
+    model.eval()
+    audios = [_audio(16000 * 2, 1), _audio(16000 * 2, 2), _audio(16000 * 2, 3)]
+    pipe = PipelineBuilder.build_pipeline({"pipeline_type": "cache_aware", "streaming": {"batch_size": 3, "num_slots": 3},
+                                           "endpointing": {"stop_history_eou": 100000}}, asr_model=model)
+    cm = pipe.context_manager
+    seen = []
+    orig = cm.get_context
+
+    def spy(ids):
+        ctx, mp = orig(ids)
+        seen.append(ctx.cache_last_channel.data_ptr() == cm.cache_last_channel.data_ptr())
+        return ctx, mp
+
+    cm.get_context = spy
+    out = pipe.run(audios)
+    assert any(seen)                                                   # the resident tensors were handed out as they are
+    off_text = [h.text if hasattr(h, "text") else h for h in model.transcribe(audios, batch_size=1)]
+    for i in range(3):
+        assert out[i].text.split() == off_text[i].split(), i
+
+
 def test_buffered_ctc_pipeline_runs_and_times_words():
     torch.manual_seed(0)
     model = EncDecCTCModelBPE(_streaming_overrides(fastconformer_ctc_config("small", vocab_size=32, n_layers=1)))

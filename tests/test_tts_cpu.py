@@ -181,3 +181,135 @@ def test_preference_losses_and_grpo_math():
     l = grpo_loss(new, new.detach(), torch.tensor([1.0, -1.0]), ref_logp=torch.tensor([-5.5, -6.0]), kl_beta=0.1, lengths=torch.tensor([5, 5]))
     l.backward()
     assert new.grad[0] < 0 < new.grad[1]          # raise the likelihood of the above-average sample, lower the other
+
+
+def test_mamba2_chunked_equals_recurrence_and_easy_magpie_trains_and_generates():
+    import math
+
+    from speech_b200.core.config import OmegaConf
+    from speech_b200.tts.easy_magpie import EasyMagpieTTSModel, Mamba2Block, NemotronHDecoder
+
+    torch.manual_seed(0)
+    blk = Mamba2Block(32, d_state=8, head_dim=8, n_groups=2, chunk_size=5).eval()
+    u = torch.randn(2, 13, 32)
+    full = blk(u)
+    cache = {}
+    first = blk(u[:, :4], cache)                                     # chunked prefill fills the cache ...
+    steps = [blk(u[:, t:t + 1], cache) for t in range(4, 13)]        # ... and the O(1) recurrence continues from it
+    inc = torch.cat([first] + steps, dim=1)
+    assert torch.allclose(full, inc, atol=1e-4), float((full - inc).abs().max())
+    one = Mamba2Block(32, d_state=8, head_dim=8, n_groups=2, chunk_size=64).eval()
+    one.load_state_dict(blk.state_dict())
+    assert torch.allclose(one(u), full, atol=1e-4)                   # the chunk length does not change the result
+    tiny = dict(vocab_size=40, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=8)
+    from speech_b200.speechlm.llm import LLMConfig
+
+    dec = NemotronHDecoder(LLMConfig(**tiny), "M-*-M", {"d_state": 8, "head_dim": 8}).eval()
+    x = torch.randn(2, 9, 32)
+    ref = dec(x)
+    c = dec.new_cache()
+    got = torch.cat([dec(x[:, :5], c)] + [dec(x[:, t:t + 1], c) for t in range(5, 9)], dim=1)
+    assert torch.allclose(ref, got, atol=1e-4)
+    for backbone in ("transformer", "nemotron_h"):
+        cfg = OmegaConf.create({"backbone_type": backbone, "backbone": tiny, "hybrid_pattern": "M*-", "mamba": {"d_state": 8, "head_dim": 8},
+                                "num_codebooks": 3, "codebook_size": 12, "optim": {"name": "adamw", "lr": 1e-3}})
+        m = EasyMagpieTTSModel(cfg)
+        batch = {"text": torch.randint(0, 40, (2, 7)), "text_len": torch.tensor([7, 5]), "codes": torch.randint(0, 12, (2, 3, 10)),
+                 "codes_len": torch.tensor([10, 6])}
+        loss = m.training_step(batch, 0)["loss"]
+        loss.backward()
+        assert math.isfinite(float(loss)) and m.heads[2].weight.grad is not None and m.text_emb.weight.grad is not None
+        # the EOS frame is the last target of every utterance
+        _, tgt, mask = m(batch["text"], batch["text_len"], batch["codes"], batch["codes_len"])
+        assert int(tgt[1, 6, 0]) == m.audio_eos_id and bool(mask[1, 6]) and not bool(mask[1, 7])
+        codes, lens = m.infer_batch(batch["text"], max_steps=6, generator=torch.Generator().manual_seed(0))
+        assert codes.shape[:2] == (2, 3) and codes.shape[2] <= 6 and (codes.numel() == 0 or int(codes.max()) < 12) and lens.shape == (2,)
+        # greedy decoding with caches equals teacher forcing on its own output
+        g, gl = m.infer_batch(batch["text"][:1], max_steps=4, temperature=0.0)
+        if g.shape[2] > 1:
+            lg, _, _ = m(batch["text"][:1], torch.tensor([7]), g, torch.tensor([g.shape[2]]))
+            lg = lg[0, : g.shape[2]].clone()
+            lg[..., m.audio_bos_id] = float("-inf")
+            lg[:, 1:, m.audio_eos_id] = float("-inf")
+            assert torch.equal(lg.argmax(-1).t(), g[0])
+
+
+def _magpie_cfg(local="none", **extra):
+    tf = dict(n_layers=1, d_model=32, d_ffn=64, sa_n_heads=2, kernel_size=1, p_dropout=0.0)
+    return OmegaConf.create({
+        "embedding_dim": 32, "frame_stacking_factor": 1, "num_special_audio_tokens": 4,
+        "encoder": dict(tf, is_causal=False), "decoder": dict(tf, has_xattn=True, xa_d_memory=32, xa_n_heads=1, is_causal=True,
+                                                             use_learnable_pos_emb=True, max_length_causal_mask=256),
+        "local_transformer_type": local, "local_transformer_n_layers": 1, "local_transformer_hidden_dim": 32,
+        "train_ds": {"synthetic": {"num_samples": 8}, "batch_size": 4}, "optim": {"name": "adamw", "lr": 2e-3, "weight_decay": 0.0}, **extra})
+
+
+def test_magpie_maskgit_local_transformer_and_cfg_distillation():
+    from speech_b200.tts.cfg_distillation import MagpieTTSModelOnlineCFGDistillation, distillation_kl, guided_logits
+
+    torch.manual_seed(0)
+    codec = AudioCodecModel(OmegaConf.create({**CODEC_CFG, "train_discriminator": False}))
+    tok = CharTokenizer(list("abcdefgh "))
+    m = MagpieTTSModel(_magpie_cfg("maskgit"), codec=codec, tokenizer=tok)
+    tr = Trainer(max_steps=2, accelerator="cpu", log_every_n_steps=1, enable_checkpointing=False, logger=False)
+    tr.fit(m)
+    assert math.isfinite(float(tr.callback_metrics["train_local_transformer_loss"]))
+    h = torch.randn(5, 32)
+    codes = m._local_maskgit(h, temperature=0.7, topk=10, n_steps=3)
+    C = len(m.audio_embeddings)
+    assert codes.shape == (5, C) and int(codes.max()) <= m.audio_eos_id          # every codebook decided, no mask / BOS left
+    audio, alen = m.do_tts("abc", max_decoder_steps=4)
+    assert audio.shape[0] == 1 and int(alen[0]) > 0
+    # guided logits and the KL objective
+    c, u = torch.randn(2, 3, 4, 7), torch.randn(2, 3, 4, 7)
+    assert torch.allclose(guided_logits(c, u, 1.0), c, atol=1e-5) and torch.allclose(guided_logits(c, u, 0.0), u)
+    mask = torch.ones(2, 3, dtype=torch.bool)
+    assert float(distillation_kl(c, c, mask)) < 1e-6 and float(distillation_kl(c, u, mask)) > 0
+    teacher = MagpieTTSModel(_magpie_cfg(), codec=codec, tokenizer=tok)
+    stu = MagpieTTSModelOnlineCFGDistillation(_magpie_cfg(cfg_scale_range=[1.0, 3.0], ce_weight=0.1), codec=codec, tokenizer=tok, teacher=teacher)
+    assert not any(n.startswith("_teacher") for n, _ in stu.named_parameters())
+    tr = Trainer(max_steps=2, accelerator="cpu", log_every_n_steps=1, enable_checkpointing=False, logger=False)
+    tr.fit(stu)
+    assert math.isfinite(float(tr.callback_metrics["train_distillation_loss"])) and 1.0 <= float(tr.callback_metrics["train_cfg_scale"]) <= 3.0
+    assert all(p.grad is None for p in teacher.parameters())
+    out = stu.infer_batch(torch.tensor([[1, 2, 3]]), torch.tensor([3]), cfg_scale=2.0, max_decoder_steps=3)
+    assert out[0].shape[0] == 1
+
+
+def test_tts_eval_metrics_frechet_similarity_rtf_harness():
+    from speech_b200.tts.eval_metrics import (FrechetCodecDistance, MosPredictorWrapper, RTFMetrics, evaluate_tts, frechet_distance,
+                                              intelligibility, speaker_similarity)
+
+    g = torch.Generator().manual_seed(0)
+    mu, cov = torch.zeros(3), torch.eye(3)
+    assert frechet_distance(mu, cov, mu, cov) < 1e-9
+    # closed form for axis-aligned Gaussians: |dmu|^2 + sum (s1 - s2)^2
+    d = frechet_distance(torch.tensor([1.0, 0, 0]), torch.diag(torch.tensor([4.0, 1, 1])), mu, cov)
+    assert abs(d - (1.0 + 1.0)) < 1e-6
+    fcd = FrechetCodecDistance()
+    real = torch.randn(4000, 6, generator=g)
+    fcd.update(real_latents=real[:2000], fake_latents=real[2000:])
+    near = fcd.compute()
+    far = FrechetCodecDistance()
+    far.update(real_latents=real[:2000], fake_latents=real[2000:] * 2 + 1)
+    assert near < 0.1 < far.compute()
+    emb = lambda a, l: torch.stack([a.mean(-1), a.std(-1)], dim=-1)  # noqa: E731
+    x = torch.randn(2, 100, generator=g) + 1
+    assert torch.allclose(speaker_similarity(emb, x, None, x, None), torch.ones(2), atol=1e-6)
+    sc = intelligibility(lambda auds: ["Hello, world", "good bye"], [None, None], ["hello world", "good day"])
+    assert abs(sc["wer"] - 0.25) < 1e-9 and sc["cer"] > 0
+    r = RTFMetrics(100)
+    r.timed(lambda: None)
+    r.add_audio(250)
+    assert r.compute()["audio_seconds"] == 2.5
+    mos = MosPredictorWrapper(lambda x, sr: x.abs().mean(-1), 100, batch_size=2)
+    assert len(mos([torch.ones(5), torch.ones(9), torch.zeros(3)])) == 3
+
+    class _Fake:
+        def do_tts(self, text, **kw):
+            n = 50 * len(text)
+            return torch.ones(1, n), torch.tensor([n])
+
+    res = evaluate_tts(_Fake(), [{"text": "ab", "audio": torch.ones(80)}, {"text": "abcd"}], 100, transcribe=lambda a: ["ab", "abcd"],
+                       speaker_embed=emb, mos=mos)
+    assert res["wer"] == 0.0 and res["utterances"] == 2 and abs(res["audio_seconds"] - 3.0) < 1e-9 and "speaker_similarity" in res and "mos" in res
