@@ -153,7 +153,7 @@ def save_wav(path: str, samples: np.ndarray, sr: int = 16000) -> None:
     pcm = np.clip(samples, -1.0, 1.0)
     pcm = (pcm * 32767.0).astype("<i2")
     with wave.open(path, "wb") as w:
-        w.setnchannels(1)
+        w.setnchannels(1 if pcm.ndim == 1 else pcm.shape[1])          # [n] mono or [n, channels] interleaved on write
         w.setsampwidth(2)
         w.setframerate(sr)
         w.writeframes(pcm.tobytes())

@@ -6,7 +6,7 @@ dynamic-programming Levenshtein distance over word or character lists.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+from typing import Sequence, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -36,14 +36,44 @@ def word_error_rate(hypotheses: List[str], references: List[str], use_cer: bool 
     return scores / words if words != 0 else float("inf")
 
 
+def edit_operations(hyp: Sequence, ref: Sequence) -> Tuple[int, int, int]:
+    """(insertions, deletions, substitutions) of one minimum-cost alignment of ``hyp`` against ``ref``."""
+    R, H = len(ref), len(hyp)
+    d = [[0] * (H + 1) for _ in range(R + 1)]
+    for i in range(R + 1):
+        d[i][0] = i
+    for j in range(H + 1):
+        d[0][j] = j
+    for i in range(1, R + 1):
+        ri, row, up = ref[i - 1], d[i], d[i - 1]
+        for j in range(1, H + 1):
+            row[j] = min(up[j - 1] + (ri != hyp[j - 1]), up[j] + 1, row[j - 1] + 1)
+    ins = dele = sub = 0
+    i, j = R, H
+    while i > 0 or j > 0:
+        if i > 0 and j > 0 and d[i][j] == d[i - 1][j - 1] + (ref[i - 1] != hyp[j - 1]):
+            sub += ref[i - 1] != hyp[j - 1]
+            i, j = i - 1, j - 1
+        elif i > 0 and d[i][j] == d[i - 1][j] + 1:
+            dele += 1
+            i -= 1
+        else:
+            ins += 1
+            j -= 1
+    return ins, dele, sub
+
+
 def word_error_rate_detail(hypotheses, references, use_cer=False) -> Tuple[float, int, float, float, float]:
-    scores = words = 0
+    """(WER, reference tokens, insertion rate, deletion rate, substitution rate)."""
+    words = ins = dele = sub = 0
     for h, r in zip(hypotheses, references):
         hl, rl = (list(h), list(r)) if use_cer else (h.split(), r.split())
         words += len(rl)
-        scores += edit_distance(hl, rl)
-    wer = scores / words if words else float("inf")
-    return wer, words, float("nan"), float("nan"), float("nan")
+        a, b, c = edit_operations(hl, rl)
+        ins, dele, sub = ins + a, dele + b, sub + c
+    if not words:
+        return float("inf"), 0, float("inf"), float("inf"), float("inf")
+    return (ins + dele + sub) / words, words, ins / words, dele / words, sub / words
 
 
 class WER:

@@ -281,3 +281,53 @@ def test_ear_tts_mog_rvq_duplex_speech_decoder_and_voice_chat():
     # the speaking half lags the text channel by one frame: the first spoken frame is conditioned on PAD
     st = chat.init_state(2, audio.device)
     assert int(st["pending_text"][0]) == chat.stt.text_pad_id
+
+
+def test_serving_plugin_token_estimator_lora_merge_export_and_splice(tmp_path):
+    from speech_b200.speechlm import vllm_plugin as vp
+    from speech_b200.speechlm.perception import AudioPerceptionModule
+
+    torch.manual_seed(0)
+    est = vp.AudioTokenEstimator()
+    pc = OmegaConf.create({"preprocessor": {**preprocessor_cfg(32), "dither": 0.0}, "encoder": encoder_cfg("small", 32, 0.0, 0.0, n_layers=1),
+                           "modality_adapter": {"_target_": "speech_b200.speechlm.perception.IdentityConnector", "d_model": 176}, "output_dim": 64})
+    perc = AudioPerceptionModule(pc).eval()
+    # the integer arithmetic predicts the encoder's real output length
+    for n in (1600, 4000, 15999, 16000, 23457, 48000):
+        _, ln = perc(input_signal=torch.randn(1, n), input_signal_length=torch.tensor([n]))
+        assert est.single_pass(n) == int(ln[0]), n
+    # chunking: a short tail is folded into the previous chunk; the total is the sum over chunks
+    assert est.spans(68000, 2.0) == [(0, 32000), (32000, 68000)]
+    assert est.spans(16000 * 5, 2.0)[-1] == (64000, 80000)
+    assert est.tokens(68000, 2.0) == est.single_pass(32000) + est.single_pass(36000)
+    for tgt in (7, 100, 333):
+        n = est.samples_for_tokens(tgt, 2.0)
+        assert est.tokens(n, 2.0) >= tgt and est.tokens(n - 1, 2.0) < tgt
+    # LoRA merge
+    w, a, b = torch.randn(6, 4), torch.randn(2, 4), torch.randn(6, 2)
+    merged = vp.merge_lora_into_base({"l.q.base.weight": w, "l.q.lora_A": a, "l.q.lora_B": b, "l.norm.weight": torch.ones(4)}, 0.5)
+    assert set(merged) == {"l.q.weight", "l.norm.weight"} and torch.allclose(merged["l.q.weight"], w + 0.5 * b @ a, atol=1e-6)
+    with pytest.raises(KeyError):
+        vp.merge_lora_into_base({"x.lora_A": a, "x.lora_B": b}, 1.0)
+    # splice
+    emb = torch.nn.Embedding(50, 64)
+    srv = vp.SpeechLMServingModel(perc, emb, placeholder_id=49, estimator=est, encoder_chunk_size_seconds=1.0)
+    audio, lens = torch.randn(2, 40000), torch.tensor([40000, 9000])
+    mm = srv.get_multimodal_embeddings(audio, lens)
+    assert [m.shape[0] for m in mm] == [est.tokens(40000, 1.0), est.tokens(9000, 1.0)] and mm[0].shape[1] == 64
+    ids = srv.expand_placeholders([3, 49, 5, 49, 7], [40000, 9000])
+    assert ids.count(49) == mm[0].shape[0] + mm[1].shape[0]
+    full = srv.get_input_embeddings(torch.tensor(ids), mm)
+    assert full.shape == (len(ids), 64) and torch.allclose(full[1], mm[0][0]) and torch.allclose(full[0], emb.weight[3])
+    with pytest.raises(ValueError):
+        srv.get_input_embeddings(torch.tensor(ids[:-3] + [1, 1, 1]), mm)
+    # registration hands the lazy class path to the engine's registry
+    seen = {}
+
+    class _Reg:
+        @staticmethod
+        def register_model(name, path):
+            seen[name] = path
+
+    vp.register(_Reg)
+    assert seen == {vp.ARCHITECTURE: "speech_b200.speechlm.vllm_plugin:" + vp.ARCHITECTURE}

@@ -199,3 +199,46 @@ def test_extra_tokenizers_and_chat_template():
     enc = tk.apply_chat_template(msgs, tokenize=True)
     assert len(enc["input_ids"]) == len(enc["assistant_mask"]) and 0 < sum(enc["assistant_mask"]) < len(enc["input_ids"])
     assert tk.apply_chat_template(msgs, template="llama3").startswith("<|begin_of_text|><|start_header_id|>user")
+
+
+def test_asr_evaluator_explorer_report_and_rir_generator(tmp_path):
+    import json
+
+    import numpy as np
+
+    from speech_b200.data.rir_generator import RIRCorpusGenerator, image_source_rir, measure_rt60, sabine_reflection
+    from speech_b200.utils.asr_evaluator import ASREvaluator, align_words, write_explorer_report
+    from speech_b200.utils.metrics import word_error_rate_detail
+
+    wer, n, ins, dele, sub = word_error_rate_detail(["a x c d e"], ["a b c d"])
+    assert n == 4 and abs(wer - 0.5) < 1e-9 and abs(ins - 0.25) < 1e-9 and dele == 0 and abs(sub - 0.25) < 1e-9
+    assert [op for op, _, _ in align_words("a b c d".split(), "a x c d e".split())] == ["ok", "sub", "ok", "ok", "ins"]
+    man = tmp_path / "m.json"
+    rows = [{"audio_filepath": f"/x/{i}.wav", "duration": 1.0 + 3 * i, "text": t, "gender": g}
+            for i, (t, g) in enumerate([("hello world", "f"), ("good morning all", "m"), ("one two three four", "f")])]
+    man.write_text("\n".join(json.dumps(r) for r in rows))
+    fake = {"/x/0.wav": "hello world", "/x/1.wav": "good morning", "/x/2.wav": "one too three four"}
+    ev = ASREvaluator(transcribe_fn=lambda paths: [fake[p] for p in paths])
+    res = ev.run(str(man), str(tmp_path / "out"), metadata_keys=["gender"], duration_buckets=[3.0, 6.0])
+    assert abs(res["wer"] - 2 / 9) < 1e-9 and abs(res["del_rate"] - 1 / 9) < 1e-9 and abs(res["sub_rate"] - 1 / 9) < 1e-9
+    assert res["breakdown"]["gender"]["m"]["wer"] == pytest.approx(1 / 3) and res["breakdown"]["gender"]["f"]["utterances"] == 2
+    assert set(res["breakdown"]["duration"]) == {"<3s", "3-6s", ">=6s"}
+    preds = [json.loads(l) for l in (tmp_path / "out" / "predictions.json").read_text().splitlines()]
+    assert preds[1]["pred_text"] == "good morning" and preds[1]["wer"] == pytest.approx(1 / 3)
+    stats = write_explorer_report(preds, str(tmp_path / "report.html"))
+    page = (tmp_path / "report.html").read_text()
+    assert stats["utterances"] == 3 and ("sub", "two", "too", 1) in stats["top_errors"] and "two→too" in page and "<svg" in page
+    # image-source room response: direct path first, at distance / c, and a decay close to the requested RT60
+    room, src, mic = [6.0, 5.0, 3.0], [2.0, 2.5, 1.5], [4.0, 2.5, 1.5]
+    h = image_source_rir(room, src, mic, rt60=0.4, sample_rate=16000, max_order=17)
+    first = int(np.argmax(np.abs(h) > 0.5 * np.abs(h).max()))
+    assert abs(first - 2.0 / 343.0 * 16000) <= 2
+    assert 0 < sabine_reflection(room, 0.4) < 1 and sabine_reflection(room, 0.8) > sabine_reflection(room, 0.2)
+    rt = measure_rt60(h, 16000, decay_db=20)
+    assert 0.2 < rt < 0.8, rt
+    with pytest.raises(ValueError):
+        image_source_rir(room, [7.0, 1, 1], mic, 0.3)
+    gen = RIRCorpusGenerator(num_mics=2, max_order=4, seed=1)
+    path = gen.generate(str(tmp_path / "rirs"), 2)
+    recs = [json.loads(l) for l in open(path)]
+    assert len(recs) == 2 and len(recs[0]["mic_positions"]) == 2 and (tmp_path / "rirs" / "rir_00001.wav").exists()
