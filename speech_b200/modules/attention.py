@@ -138,9 +138,16 @@ class MultiHeadAttention(nn.Module):
 
     def update_cache(self, key, value, query, cache):
         if cache is not None:
-            key = value = torch.cat([cache.to(key.dtype), key], dim=1)
+            n_cache = cache.shape[1]
             q_keep_size = query.shape[1] - self.cache_drop_size
-            cache = torch.cat([cache[:, q_keep_size:, :], query[:, :q_keep_size, :].to(cache.dtype)], dim=1)
+            self_attention = key is query
+            key = value = torch.cat([cache.to(key.dtype), key], dim=1)
+            if self_attention and q_keep_size > 0 and key.dtype == cache.dtype:
+                # the new cache is the window of `cache ++ query` that ends after the kept query frames: a view, not a copy
+                # (the caller stacks the per-layer caches into one tensor, which is the only copy that is needed)
+                cache = key[:, q_keep_size:q_keep_size + n_cache, :]
+            else:
+                cache = torch.cat([cache[:, q_keep_size:, :], query[:, :q_keep_size, :].to(cache.dtype)], dim=1)
         return key, value, query, cache
 
     def forward(self, query, key, value, mask=None, pos_emb=None, cache=None, residual=None, out_dropout: float = 0.0):

@@ -36,6 +36,17 @@ struct SbGemmArgs {
   int peer_a_rows;  // rows per shard (multiple of 128)
   int peer_world;
   int pair;         // 0 = default policy, 1 = use CTA pairs (cta_group::2) when the shape allows, -1 = never
+  // In-kernel rank synchronisation for the fused collectives (all null / 0 = none).  sig_flags is a DEVICE array [sig_world] of
+  // device pointers: entry r is rank r's flag array (16 x u32: slots 0..7 "shard of rank i is in place", slots 8..15
+  // "contributions of rank i have landed").  Flags carry a per-call epoch that only grows.
+  //   sig_head: block 0 publishes this rank's "in place" flag to every rank at kernel start, and the TMA producer waits (bounded)
+  //             for the owner's flag before its first load from that rank's memory (all-gather + GEMM);
+  //   sig_tail: the last block to finish publishes this rank's "landed" flag to every rank (GEMM + reduce-scatter).
+  unsigned int* const* sig_flags;
+  unsigned int* sig_counter;   // device word, zero between calls: blocks that have finished
+  int sig_world, sig_rank;
+  unsigned int sig_epoch;
+  int sig_head, sig_tail, pad3_;
 };
 
 

@@ -81,6 +81,11 @@ struct GemmParams {
   long long num_work;  // num_tiles * ksplit
   int a_peer_rows;     // > 0: all-gather + GEMM: rows [r * a_peer_rows, (r+1) * a_peer_rows) of A live in rank r's memory (peer_a.m[r])
   int debug;           // diagnostics only (wrong results): 1 = tensor core alone (operands loaded once), 2 = loads alone (no MMAs)
+  // rank synchronisation inside the kernel (see SbGemmArgs): flag arrays of all ranks, this rank, the call's epoch
+  unsigned int* const* sig_flags;
+  unsigned int* sig_counter;
+  int sig_world, sig_rank, sig_head, sig_tail;
+  unsigned int sig_epoch;
   EpilogueArgs ep;
   int* status;
 };
@@ -116,6 +121,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     // put that latency on the critical path of each producer / consumer hand-over.  Every 64th probe is plenty for a bound.
     if ((++probes & 63u) == 0 && (clock64() - t0 > SB_WAIT_CYCLES || sb_failed(status))) {
       sb_set_status(status, code, (int)parity);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void flag_store_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int flag_load_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait for a rank's flag to reach `epoch` (flags only grow; the comparison survives wrap-around).
+__device__ __forceinline__ bool flag_wait(const unsigned int* p, unsigned int epoch, int* status) {
+  if ((int)(flag_load_acquire_sys(p) - epoch) >= 0) return true;
+  const long long t0 = clock64();
+  unsigned int probes = 0;
+  while ((int)(flag_load_acquire_sys(p) - epoch) < 0) {
+    if ((++probes & 15u) == 0 && (clock64() - t0 > SB_WAIT_CYCLES || sb_failed(status))) {
+      sb_set_status(status, SB_TIMEOUT_PEER_FLAG, (int)epoch);
       return false;
     }
   }
@@ -310,11 +337,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (p.sig_head && blockIdx.x == 0 && threadIdx.x == 64) {
+    // this rank's shard was written by earlier work on this stream: tell every rank (this one included) that it is in place
+    __threadfence_system();
+    for (int r = 0; r < p.sig_world; ++r) flag_store_release_sys(p.sig_flags[r] + p.sig_rank, p.sig_epoch);
+  }
+
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       long long it = 0;
       bool ok = true;
+      unsigned int ready = p.sig_head ? 0u : 0xffffffffu;   // ranks whose "in place" flag this producer has seen
       for (long long w = worker; w < p.num_work && ok; w += num_workers) {
         const long long tile = p.ksplit > 1 ? w / p.ksplit : w;
         const int kb_begin = p.ksplit > 1 ? (int)(w % p.ksplit) * p.kb_per : 0;
@@ -360,6 +394,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               tma_load_4d(sa + TILE_BYTES / 2, &tmap_a, full_bar(s), a_row0 + 64, kb * BLOCK_K, b0, b1);
             } else if (p.a_peer_rows > 0) {
               const int owner = a_row0 / p.a_peer_rows;
+              if (!((ready >> owner) & 1u)) {
+                // the expectation is already posted: on a time-out the load is still issued (from a shard that may be stale; the
+                // status word tells the host), so that the barrier completes and the kernel ends in its normal way
+                flag_wait(p.sig_flags[p.sig_rank] + owner, p.sig_epoch, p.status);
+                ready |= 1u << owner;
+              }
               tma_load_4d(sa, &peer_a.m[owner], full_bar(s), kb * BLOCK_K, a_row0 - owner * p.a_peer_rows, b0, b1);
             } else {
               tma_load_4d(sa, &tmap_a, full_bar(s), kb * BLOCK_K, a_row0, b0, b1);
@@ -635,8 +675,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 
   // ------------------------------------------------------------------ common exit
+  if (p.sig_tail && warp >= 2) __threadfence_system();   // this thread's reductions into peer memory are performed before the block reports
   tc_fence_before();
   __syncthreads();
+  if (p.sig_tail && threadIdx.x == 0) {
+    unsigned int done;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(done) : "l"(p.sig_counter) : "memory");
+    if (done == gridDim.x - 1) {
+      // last block of this rank: every block's reductions are ordered before this point; publish "landed" to every rank
+      *((volatile unsigned int*)p.sig_counter) = 0u;
+      __threadfence_system();
+      for (int r = 0; r < p.sig_world; ++r) flag_store_release_sys(p.sig_flags[r] + 8 + p.sig_rank, p.sig_epoch);
+    }
+  }
   if (PAIR) cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while its partner may still reach into it
   tc_fence_after();
   if (warp == 1) {
@@ -758,6 +809,13 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
     }
     p.a_peer_rows = a->peer_a_rows;
   }
+  p.sig_flags = a->sig_flags; p.sig_counter = a->sig_counter;
+  p.sig_world = a->sig_world; p.sig_rank = a->sig_rank; p.sig_epoch = a->sig_epoch;
+  p.sig_head = (a->sig_flags && a->sig_head) ? 1 : 0;
+  p.sig_tail = (a->sig_flags && a->sig_tail) ? 1 : 0;
+  if ((p.sig_head || p.sig_tail) && (a->sig_world < 1 || a->sig_world > 8 || a->sig_rank < 0 || a->sig_rank >= a->sig_world)) return -8;
+  if (p.sig_tail && !a->sig_counter) return -8;
+  if (p.sig_head && !a->peer_A) return -8;
   p.status = sb_status_ptr();
   if (!p.status) return -2;
   static const int env_debug = [] { const char* e = getenv("SPEECH_B200_GEMM_DEBUG"); return e ? atoi(e) : 0; }();

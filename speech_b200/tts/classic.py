@@ -377,3 +377,72 @@ class AlignerModel(ModelPT):
     def durations(self, spec, spec_len, text, text_len) -> torch.Tensor:
         soft, _ = self.forward(spec, spec_len, text, text_len)
         return binarize_attention(soft.squeeze(1), text_len, spec_len).sum(1)
+
+
+class SSLDisentangler(ModelPT):
+    """Content / speaker disentanglement on a self-supervised speech encoder (features for voice conversion and zero-shot TTS).
+
+    One Conformer encoder, two heads: the *content* head maps every frame to an embedding and to phoneme logits trained with CTC;
+    the *speaker* head pools the frames (mean + standard deviation), maps to an embedding and classifies the speaker.  The
+    content embedding is normalised per utterance (instance norm over time) so that speaker-dependent offsets do not leak into it.
+    ``forward`` returns ``(content_logits, content_embedding [B, T, Dc], speaker_logits, speaker_embedding [B, Ds], lengths)``.
+    Reference: ``tts/models/ssl_tts.py`` (``SSLDisentangler``: downstream heads, per-task losses, ``forward_for_export``).
+    """
+
+    def __init__(self, cfg: DictConfig, trainer=None):
+        super().__init__(cfg=cfg, trainer=trainer)
+        from ..core.instantiate import instantiate
+        from ..modules.preprocessor import AudioToMelSpectrogramPreprocessor
+
+        cfg = self._cfg
+        self.preprocessor = AudioToMelSpectrogramPreprocessor(**{k: v for k, v in dict(cfg.preprocessor).items() if k != "_target_"})
+        self.encoder = instantiate(cfg.encoder)
+        d = int(cfg_get(cfg, "encoder_dim", getattr(self.encoder, "d_model", 256)))
+        self.content_dim, self.speaker_dim = int(cfg_get(cfg, "content_emb_dim", 128)), int(cfg_get(cfg, "speaker_emb_dim", 128))
+        self.num_phonemes, self.num_speakers = int(cfg_get(cfg, "num_phonemes", 64)), int(cfg_get(cfg, "num_speakers", 16))
+        self.content_proj = nn.Linear(d, self.content_dim)
+        self.content_out = nn.Linear(self.content_dim, self.num_phonemes + 1)           # + CTC blank (last index)
+        self.speaker_proj = nn.Linear(2 * d, self.speaker_dim)
+        self.speaker_out = nn.Linear(self.speaker_dim, self.num_speakers)
+        self.content_weight, self.speaker_weight = float(cfg_get(cfg, "content_loss_weight", 1.0)), float(cfg_get(cfg, "speaker_loss_weight", 1.0))
+
+    @classmethod
+    def list_available_models(cls):
+        return []
+
+    def setup_training_data(self, c):
+        self._train_dl = None
+
+    def setup_validation_data(self, c):
+        self._validation_dl = None
+
+    def forward(self, input_signal, input_signal_length):
+        feats, flen = self.preprocessor(input_signal=input_signal, length=input_signal_length)
+        enc, elen = self.encoder(audio_signal=feats, length=flen)                        # [B, D, T]
+        h = enc.transpose(1, 2).float()
+        mask = (torch.arange(h.shape[1], device=h.device)[None] < elen[:, None]).unsqueeze(-1)
+        n = elen.clamp(min=1).view(-1, 1).float()
+        mean = (h * mask).sum(1) / n
+        std = (((h - mean.unsqueeze(1)) ** 2 * mask).sum(1) / n).clamp(min=1e-5).sqrt()
+        spk_emb = F.normalize(self.speaker_proj(torch.cat([mean, std], dim=-1)), dim=-1)
+        c = self.content_proj(h)
+        cm = (c * mask).sum(1, keepdim=True) / n.unsqueeze(-1)
+        cs = (((c - cm) ** 2 * mask).sum(1, keepdim=True) / n.unsqueeze(-1)).clamp(min=1e-5).sqrt()
+        content = (c - cm) / cs * mask
+        return self.content_out(content), content, self.speaker_out(spk_emb), spk_emb, elen
+
+    def training_step(self, batch, batch_idx):
+        """batch: audio [B, S], audio_len [B], phonemes [B, U], phoneme_len [B], speaker [B]."""
+        audio, alen, ph, phl, spk = batch
+        logits, _, spk_logits, _, elen = self(audio, alen)
+        ctc = F.ctc_loss(logits.log_softmax(-1).transpose(0, 1), ph, elen, phl, blank=self.num_phonemes, zero_infinity=True)
+        ce = F.cross_entropy(spk_logits, spk)
+        loss = self.content_weight * ctc + self.speaker_weight * ce
+        self.log_dict({"train_loss": loss.detach(), "content_loss": ctc.detach(), "speaker_loss": ce.detach(),
+                       "speaker_acc": (spk_logits.argmax(-1) == spk).float().mean()})
+        return {"loss": loss}
+
+    @torch.no_grad()
+    def forward_for_export(self, input_signal, input_signal_length):
+        _, content, _, spk, elen = self(input_signal, input_signal_length)
+        return content, spk, elen

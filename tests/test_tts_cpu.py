@@ -313,3 +313,24 @@ def test_tts_eval_metrics_frechet_similarity_rtf_harness():
     res = evaluate_tts(_Fake(), [{"text": "ab", "audio": torch.ones(80)}, {"text": "abcd"}], 100, transcribe=lambda a: ["ab", "abcd"],
                        speaker_embed=emb, mos=mos)
     assert res["wer"] == 0.0 and res["utterances"] == 2 and abs(res["audio_seconds"] - 3.0) < 1e-9 and "speaker_similarity" in res and "mos" in res
+
+
+def test_ssl_disentangler_heads_and_losses():
+    from speech_b200.models.configs import encoder_cfg, preprocessor_cfg
+    from speech_b200.tts.classic import SSLDisentangler
+
+    torch.manual_seed(0)
+    cfg = OmegaConf.create({"preprocessor": {**preprocessor_cfg(32), "dither": 0.0}, "encoder": encoder_cfg("small", 32, 0.0, 0.0, n_layers=1),
+                            "encoder_dim": 176, "content_emb_dim": 24, "speaker_emb_dim": 16, "num_phonemes": 11, "num_speakers": 3,
+                            "optim": {"name": "adamw", "lr": 1e-3}})
+    m = SSLDisentangler(cfg)
+    audio, alen = torch.randn(2, 16000), torch.tensor([16000, 11000])
+    logits, content, spk_logits, spk, elen = m(audio, alen)
+    assert logits.shape[-1] == 12 and content.shape[-1] == 24 and spk_logits.shape == (2, 3) and spk.shape == (2, 16)
+    assert torch.allclose(spk.norm(dim=-1), torch.ones(2), atol=1e-5)
+    # per-utterance normalisation of the content embedding: zero mean over the valid frames, nothing beyond them
+    n1 = int(elen[1])
+    assert float(content[1, :n1].detach().mean(0).abs().max()) < 1e-4 and float(content[1, n1:].detach().abs().sum()) == 0
+    out = m.training_step((audio, alen, torch.randint(0, 11, (2, 5)), torch.tensor([5, 3]), torch.tensor([0, 2])), 0)
+    out["loss"].backward()
+    assert math.isfinite(float(out["loss"])) and m.speaker_out.weight.grad is not None and m.content_out.weight.grad is not None
