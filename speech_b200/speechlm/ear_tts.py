@@ -248,16 +248,28 @@ class DuplexEARTTS(ModelPT):
         cb = getattr(audio_codec, "rvq_codebooks", None)
         if cb is not None:
             self.tts.set_rvq_embs(cb)
+        if not self._is_model_being_restored and self._train_dl is None:
+            self._setup_dataloaders_from_cfg()
+
+    def _setup_dataloaders_from_cfg(self):
+        if hasattr(self, "tts"):                                                         # the base constructor calls this before the layers exist
+            super()._setup_dataloaders_from_cfg()
 
     @classmethod
     def list_available_models(cls):
         return []
 
+    def _loader(self, c):
+        from ..tts.code_datasets import build_code_dataloader
+
+        m = self.tts
+        return build_code_dataloader(c, num_codebooks=m.K, codebook_size=m.N, text_vocab=m.text_vocab, tokenizer=self.tokenizer, frame_aligned=True)
+
     def setup_training_data(self, c):
-        self._train_dl = None
+        self._train_dl = self._loader(c)
 
     def setup_validation_data(self, c):
-        self._validation_dl = None
+        self._validation_dl = self._loader(c)
 
     def forward(self, codes, tokens, lens=None):
         mask = None if lens is None else torch.arange(codes.shape[1], device=codes.device)[None] < lens[:, None]

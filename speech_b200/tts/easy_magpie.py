@@ -185,16 +185,32 @@ class EasyMagpieTTSModel(ModelPT):
         self.text_emb = nn.Embedding(text_vocab, hidden)
         self.audio_emb = nn.ModuleList(nn.Embedding(self.vocab, hidden) for _ in range(self.C))
         self.heads = nn.ModuleList(nn.Linear(hidden, self.vocab) for _ in range(self.C))
+        if not self._is_model_being_restored and self._train_dl is None:
+            self._setup_dataloaders_from_cfg()
+
+    def _setup_dataloaders_from_cfg(self):
+        if hasattr(self, "heads"):                                                       # the base constructor calls this before the layers exist
+            super()._setup_dataloaders_from_cfg()
 
     @classmethod
     def list_available_models(cls):
         return []
 
+    def _loader(self, c):
+        from .code_datasets import build_code_dataloader
+
+        return build_code_dataloader(c, num_codebooks=self.C, codebook_size=self.N, text_vocab=self.text_emb.num_embeddings, tokenizer=self.tokenizer)
+
     def setup_training_data(self, c):
-        self._train_dl = None
+        self._train_dl = self._loader(c)
 
     def setup_validation_data(self, c):
-        self._validation_dl = None
+        self._validation_dl = self._loader(c)
+
+    def validation_step(self, batch, batch_idx, dataloader_idx=0):
+        with torch.no_grad():
+            logits, tgt, mask = self(batch["text"], batch["text_len"], batch["codes"].long(), batch["codes_len"])
+        return {"val_loss": F.cross_entropy(logits[mask].reshape(-1, self.vocab), tgt[mask].reshape(-1))}
 
     # ------------------------------------------------------------------ pieces
     def _embed_frames(self, codes: torch.Tensor) -> torch.Tensor:

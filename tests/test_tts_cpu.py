@@ -334,3 +334,23 @@ def test_ssl_disentangler_heads_and_losses():
     out = m.training_step((audio, alen, torch.randint(0, 11, (2, 5)), torch.tensor([5, 3]), torch.tensor([0, 2])), 0)
     out["loss"].backward()
     assert math.isfinite(float(out["loss"])) and m.speaker_out.weight.grad is not None and m.content_out.weight.grad is not None
+
+
+def test_code_token_models_train_through_the_trainer_on_synthetic_codes():
+    from speech_b200.speechlm.ear_tts import DuplexEARTTS
+    from speech_b200.tts.easy_magpie import EasyMagpieTTSModel
+
+    torch.manual_seed(0)
+    tiny = dict(vocab_size=40, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2, head_dim=8)
+    ds = {"synthetic": {"num_samples": 8}, "batch_size": 4}
+    em = EasyMagpieTTSModel(OmegaConf.create({"backbone_type": "nemotron_h", "backbone": tiny, "hybrid_pattern": "M*-", "mamba": {"d_state": 8, "head_dim": 8},
+                                              "num_codebooks": 2, "codebook_size": 12, "train_ds": ds, "validation_ds": ds,
+                                              "optim": {"name": "adamw", "lr": 1e-3}}))
+    tr = Trainer(max_steps=3, accelerator="cpu", log_every_n_steps=1, enable_checkpointing=False, logger=False)
+    tr.fit(em)
+    assert math.isfinite(float(tr.callback_metrics["train_loss"]))
+    ear = DuplexEARTTS(OmegaConf.create({"tts": {"backbone": tiny, "num_quantizers": 3, "codebook_size": 16, "latent_size": 8, "num_predictions": 4,
+                                                 "low_rank": 4}, "train_ds": ds, "optim": {"name": "adamw", "lr": 1e-3}}))
+    tr = Trainer(max_steps=3, accelerator="cpu", log_every_n_steps=1, enable_checkpointing=False, logger=False)
+    tr.fit(ear)
+    assert math.isfinite(float(tr.callback_metrics["train_loss"]))
