@@ -192,3 +192,57 @@ def test_streaming_aed_waitk_and_alignatt_policies():
     st.pred_tokens_ids[0, 2:10] = torch.tensor([7, 8, 7, 8, 7, 8, 7, 8])
     st.current_context_lengths[0] = 10
     assert bool(loose.detect_hallucinations(st)[0])
+
+
+def test_lexicon_ctc_beam_decoder_with_word_lm_and_graph_roundtrip(tmp_path):
+    import math
+
+    import numpy as np
+
+    from speech_b200.decoding.lexicon_decoder import (LexiconCTCBeamDecoder, LexiconTrie, WordNGramLM, compile_lexicon_graph, read_openfst_text,
+                                                      write_openfst_text)
+    from speech_b200.decoding.ngram_lm import write_arpa
+
+    # tokens: 0 blank, 1 c, 2 a, 3 t, 4 r, 5 s
+    lex = {"cat": [[1, 2, 3]], "car": [[1, 2, 4]], "at": [[2, 3]], "cats": [[1, 2, 3, 5]], "a": [[2]], "tt": [[3, 3]]}
+    trie = LexiconTrie(lex)
+
+    def frames(seq, V=6, hi=0.9):
+        lp = np.full((len(seq), V), math.log((1 - hi) / (V - 1)))
+        for t, k in enumerate(seq):
+            lp[t, k] = math.log(hi)
+        return lp
+
+    dec = LexiconCTCBeamDecoder(trie, blank_id=0, beam_size=8)
+    # "c c _ a t _ c a r": repeats collapse, blank separates, two words come out
+    assert dec.decode(frames([1, 1, 0, 2, 3, 0, 1, 2, 4]))[0].words == ["cat", "car"]
+    # a doubled letter needs the blank between its two tokens
+    assert dec.decode(frames([3, 0, 3]))[0].words == ["tt"]
+    # the acoustic evidence says "c a x" with x undecided between t and r: the word LM decides
+    lp = frames([1, 2, 3])
+    lp[2, 3] = lp[2, 4] = math.log(0.45)
+    arpa = str(tmp_path / "w.arpa")
+    write_arpa(arpa, {("<s>",): (-99.0, 0.0), ("</s>",): (-1.0, 0.0), ("cat",): (-2.0, 0.0), ("car",): (-0.3, 0.0), ("at",): (-1.0, 0.0),
+                      ("cats",): (-2.0, 0.0), ("a",): (-1.0, 0.0), ("tt",): (-3.0, 0.0)})
+    lm = WordNGramLM.from_arpa(arpa)
+    assert abs(lm.score((), "car") - (-0.3 * math.log(10))) < 1e-9
+    with_lm = LexiconCTCBeamDecoder(trie, blank_id=0, lm=lm, beam_size=8, lm_weight=2.0)
+    assert with_lm.decode(lp)[0].words == ["car"]
+    lm2 = WordNGramLM(1, {**lm.ng, ("cat",): (-0.1, 0.0), ("car",): (-3.0, 0.0)})
+    assert LexiconCTCBeamDecoder(trie, blank_id=0, lm=lm2, beam_size=8, lm_weight=2.0).decode(lp)[0].words == ["cat"]
+    # token sequences outside the lexicon never come out; with an unk score they surface as <unk>
+    odd = frames([4, 0, 5])
+    assert dec.decode(odd) == [] or all(w in lex for w in dec.decode(odd)[0].words)
+    # the compiled token-to-word graph survives the OpenFst text format and decodes identically
+    arcs = compile_lexicon_graph(trie)
+    finals = [s for s, ws in enumerate(trie.words) if ws] + [0]
+    write_openfst_text(arcs, finals, str(tmp_path / "TL.fst.txt"))
+    arcs2, finals2 = read_openfst_text(str(tmp_path / "TL.fst.txt"))
+    assert sorted(arcs2, key=str) == sorted(arcs, key=str) and sorted(finals2) == sorted(set(finals))
+    dec2 = LexiconCTCBeamDecoder(trie, blank_id=0, beam_size=8, graph=arcs2)
+    x = frames([1, 2, 3, 5, 0, 2, 0, 2, 3])
+    r1, r2 = dec.decode(x, n_best=3), dec2.decode(x, n_best=3)
+    assert [r.words for r in r1] == [r.words for r in r2] and r1[0].words == ["cats", "a", "at"]
+    assert r1[0].word_frames[0] in (4, 5) and len(r1[0].word_frames) == 3
+    batch = dec.decode_batch(np.stack([x, x]), [9, 4])
+    assert batch[0].text == "cats a at" and batch[1].words == ["cats"]
