@@ -325,6 +325,74 @@ class BufferedRNNTPipeline(_BufferedPipeline):
             st.append_tokens(toks, times)
 
 
+def merge_by_word_overlap(committed: List[str], new: List[str], max_overlap: int = 12) -> List[str]:
+    """Join two word sequences whose end / start overlap: the longest suffix of ``committed`` that is a prefix of ``new`` is kept
+    once (windows of a sliding buffer re-transcribe the words of their shared audio)."""
+    for n in range(min(max_overlap, len(committed), len(new)), 0, -1):
+        if committed[-n:] == new[:n]:
+            return committed + new[n:]
+    return committed + new
+
+
+class BufferedSALMPipeline(BasePipeline):
+    """Speech-LLM transcription of live streams: every step the model is prompted with the stream's current audio window
+    (``left context | new chunk``) and asked for the transcript; the window's words are merged into the running transcript by
+    their overlap with what earlier windows already produced, and words become final once the audio they came from has left the
+    window (reference: ``inference/pipelines/buffered_salm_pipeline.py``).  ``salm`` needs ``generate(dialogs, audios,
+    audio_lens, max_new_tokens)`` and a tokenizer with ``ids_to_text``."""
+
+    def __init__(self, cfg, salm):
+        super().__init__()
+        cfg = cfg if isinstance(cfg, DictConfig) else OmegaConf.create(cfg or {})
+        self.cfg, self.salm = cfg, salm
+        self.sample_rate = int(_get(cfg, "streaming.sample_rate", 16000))
+        self.batch_size = int(_get(cfg, "streaming.batch_size", 8))
+        self.chunk_secs = float(_get(cfg, "streaming.chunk_size", 2.0))
+        self.left_secs = float(_get(cfg, "streaming.left_padding_size", 6.0))
+        self.chunk_samples = int(round(self.chunk_secs * self.sample_rate))
+        self.window_samples = int(round((self.chunk_secs + self.left_secs) * self.sample_rate))
+        self.prompt = str(_get(cfg, "salm.prompt", "Transcribe the following: " + getattr(salm, "audio_locator_tag", "<|audioplaceholder|>")))
+        self.max_new_tokens = int(_get(cfg, "salm.max_new_tokens", 64))
+        self.bufferer = AudioBufferer(self.sample_rate, self.chunk_secs + self.left_secs)
+
+    def open_session(self) -> None:
+        super().open_session()
+        self.bufferer.reset()
+
+    def get_request_generator(self) -> ContinuousBatchedRequestStreamer:
+        return ContinuousBatchedRequestStreamer(n_frames_per_stream=self.chunk_samples, batch_size=self.batch_size,
+                                                sample_rate=self.sample_rate, request_type=RequestType.FRAME)
+
+    def _ids_to_text(self, ids) -> str:
+        tok = self.salm.tokenizer
+        stop = {getattr(self.salm, "text_eos_id", -1), getattr(self.salm, "text_pad_id", -1)}
+        ids = [int(t) for t in ids if int(t) not in stop]
+        return tok.ids_to_text(ids) if ids else ""
+
+    def transcribe_step(self, requests: List[Frame]) -> None:
+        states = [self.get_state(r.stream_id, r.options) for r in requests]
+        windows, left_pad = self.bufferer.update(requests)
+        audios, lens = [], []
+        for b in range(windows.shape[0]):
+            tail = max(0, int(requests[b].size) - int(requests[b].length))   # zero padding of a short last chunk
+            a = windows[b, int(left_pad[b]): windows.shape[1] - tail]   # only the audio heard so far
+            audios.append(a)
+            lens.append(a.shape[0])
+        n = max(lens)
+        batch = torch.stack([torch.nn.functional.pad(a, (0, n - a.shape[0])) for a in audios])
+        dialogs = [[{"role": "user", "content": self.prompt}] for _ in requests]
+        out = self.salm.generate(dialogs, audios=batch, audio_lens=torch.tensor(lens), max_new_tokens=self.max_new_tokens)
+        for st, r, ids in zip(states, requests, out):
+            words = self._ids_to_text(ids.tolist()).split()
+            merged = merge_by_word_overlap(st.extra.get("salm_words", []), words)
+            st.extra["salm_words"] = merged
+            res = self._outputs.setdefault(st.stream_id, PipelineOutput(st.stream_id))
+            res.text = res.partial_text = " ".join(merged)
+            if r.is_last:
+                st.is_finished = True
+                self.delete_state(st.stream_id)
+
+
 # ====================================================================================== builder
 class PipelineBuilder:
     """``cfg.pipeline_type`` ∈ {cache_aware, buffered}; ``cfg.asr_decoding_type`` ∈ {rnnt, ctc} (auto from the model when
@@ -351,3 +419,7 @@ class PipelineBuilder:
             dec = _get(cfg, "asr_decoding_type", None) or w.decoder_type
             return (BufferedRNNTPipeline if dec == "rnnt" else BufferedCTCPipeline)(cfg, w)
         raise ValueError(f"unknown pipeline_type {kind}")
+
+    @staticmethod
+    def build_salm_pipeline(cfg, salm) -> BasePipeline:
+        return BufferedSALMPipeline(cfg, salm)

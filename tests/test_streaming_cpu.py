@@ -224,3 +224,39 @@ def test_chunked_aed_inference_merges_short_tail():
     f = FrameBatchMultiTaskAED(M(), chunk_len=1.0, batch_size=2, min_tail=0.5, sample_rate=100)
     f.read_audio_file(torch.zeros(330))
     assert f.transcribe() == "len100 len100 len130" and BatchedFrameASRTDT is BatchedFrameASRRNNT
+
+
+def test_buffered_salm_pipeline_merges_window_transcripts_by_overlap():
+    from speech_b200.inference.pipelines import BufferedSALMPipeline, merge_by_word_overlap
+
+    assert merge_by_word_overlap("a b c d".split(), "c d e f".split()) == "a b c d e f".split()
+    assert merge_by_word_overlap([], ["x"]) == ["x"] and merge_by_word_overlap(["a"], ["b"]) == ["a", "b"]
+
+    class _Tok:
+        words = ["zero", "one", "two", "three", "four", "five", "six", "seven"]
+
+        def ids_to_text(self, ids):
+            return " ".join(self.words[i] for i in ids)
+
+    class _FakeSALM:
+        """Speaks one word per half second of audio: the word index is the absolute half-second index, recovered from the
+        sample values (each stream's audio is a ramp of its half-second index)."""
+        tokenizer, text_eos_id, text_pad_id, audio_locator_tag = _Tok(), 98, 99, "<|audioplaceholder|>"
+        calls = []
+
+        def generate(self, dialogs, audios, audio_lens, max_new_tokens):
+            assert all("<|audioplaceholder|>" in d[0]["content"] for d in dialogs)
+            self.calls.append(tuple(int(n) for n in audio_lens))
+            rows = []
+            for a, n in zip(audios, audio_lens):
+                idx = [int(round(float(a[k * 8000 + 4000]))) for k in range(int(n) // 8000)]
+                rows.append(idx + [98] + [99] * (max_new_tokens - len(idx) - 1))
+            return torch.tensor(rows)
+
+    audio = torch.cat([torch.full((8000,), float(k)) for k in range(8)]).numpy()          # 4 s, half second k holds the value k
+    pipe = BufferedSALMPipeline({"streaming": {"batch_size": 2, "chunk_size": 1.0, "left_padding_size": 1.0}, "salm": {"max_new_tokens": 8}}, _FakeSALM())
+    out = pipe.run([audio, audio[: 8000 * 5]])
+    assert out[0].text == "zero one two three four five six seven"
+    assert out[1].text == "zero one two three four"
+    # the first step sees one second, later steps the two-second window
+    assert pipe.salm.calls[0] == (16000, 16000) and pipe.salm.calls[1] == (32000, 32000)
