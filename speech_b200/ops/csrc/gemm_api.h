@@ -47,6 +47,15 @@ struct SbGemmArgs {
   int sig_world, sig_rank;
   unsigned int sig_epoch;
   int sig_head, sig_tail, pad3_;
+  // Staging for all-gather + GEMM (with sig_head): instead of loading A tiles from the owner's memory for every column tile
+  // (the shard would cross NVLink once per column tile), the blocks first copy every remote shard ONCE into this rank's
+  // staging area with plain peer loads, while the tiles of this rank's own rows are already being multiplied; tiles of remote
+  // rows wait (bounded) until all blocks have finished copying.  peer_A[r] then names the LOCAL staging slot of rank r (and
+  // this rank's own shard for r == sig_rank).  stage_src is a DEVICE array [sig_world] of the ranks' shard addresses.
+  const void* const* stage_src;
+  void* stage_dst;              // staging area: sig_world slots of stage_bytes each
+  long long stage_bytes;        // bytes of one shard (multiple of 16); 0 = no staging
+  unsigned int* stage_counter;  // device words, zero between calls: [0] blocks that finished copying, [1] blocks that exited
 };
 
 

@@ -86,6 +86,11 @@ struct GemmParams {
   unsigned int* sig_counter;
   int sig_world, sig_rank, sig_head, sig_tail;
   unsigned int sig_epoch;
+  // staging of remote shards into local memory (all-gather + GEMM; see SbGemmArgs)
+  const void* const* stage_src;
+  void* stage_dst;
+  long long stage_bytes;
+  unsigned int* stage_counter;
   EpilogueArgs ep;
   int* status;
 };
@@ -276,6 +281,29 @@ struct PeerMaps {
   CUtensorMap m[8];
 };
 
+// Row tile / column tile of work item `rem` (index inside one batch entry).  Ordinary GEMMs walk the row tiles fastest.  With a
+// row-sharded A (all-gather + GEMM) the tiles of THIS rank's rows come first, for all column tiles, then the other ranks' rows
+// starting with the next rank: the multiplication starts on local data while remote shards are still on their way.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int rem, int tile_m_rows, int& tm, int& tn) {
+  if (p.a_peer_rows <= 0 || !p.sig_head) {
+    tm = rem % p.tiles_m;
+    tn = rem / p.tiles_m;
+    return;
+  }
+  const int own = p.a_peer_rows / tile_m_rows;            // row tiles per rank (shards are whole tiles)
+  const int own_items = own * p.tiles_n;
+  if (rem < own_items) {
+    tm = p.sig_rank * own + rem % own;
+    tn = rem / own;
+  } else {
+    const int r2 = rem - own_items;
+    const int others = p.tiles_m - own;                   // row tiles of the other ranks, walked in rotated order
+    const int k = r2 % others;
+    tm = (p.sig_rank * own + own + k) % p.tiles_m;
+    tn = r2 / others;
+  }
+}
+
 template <bool A_MN, bool B_MN, int BN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -355,7 +383,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int kb_end = p.ksplit > 1 ? min(num_kb, kb_begin + p.kb_per) : num_kb;
         const int batch = (int)(tile / ((long long)p.tiles_m * p.tiles_n));
         const int rem = (int)(tile % ((long long)p.tiles_m * p.tiles_n));
-        const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
+        int tm, tn;
+        tile_coords(p, rem, TILE_M, tm, tn);
         const int b0 = batch % p.batch0;
         const int a_row0 = tm * TILE_M + (int)cta_rank * BLOCK_M;      // first A row (output row) staged by this CTA
         const int b_row0 = tn * BLOCK_N + (int)cta_rank * B_ROWS;      // first B row (output column) staged by this CTA
@@ -397,8 +426,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               if (!((ready >> owner) & 1u)) {
                 // the expectation is already posted: on a time-out the load is still issued (from a shard that may be stale; the
                 // status word tells the host), so that the barrier completes and the kernel ends in its normal way
-                flag_wait(p.sig_flags[p.sig_rank] + owner, p.sig_epoch, p.status);
-                ready |= 1u << owner;
+                if (p.stage_bytes > 0 && owner != p.sig_rank) {
+                  // staged mode: every block has copied its slice of the remote shards into local memory
+                  const long long t0 = clock64();
+                  unsigned int probes = 0;
+                  while (*((volatile unsigned int*)p.stage_counter) < gridDim.x) {
+                    if ((++probes & 15u) == 0 && (clock64() - t0 > SB_WAIT_CYCLES || sb_failed(p.status))) {
+                      sb_set_status(p.status, SB_TIMEOUT_PEER_FLAG, 1000 + owner);
+                      break;
+                    }
+                  }
+                  __threadfence();
+                  asm volatile("fence.proxy.async;" ::: "memory");
+                  ready = 0xffffffffu;                              // all remote shards are staged at once
+                } else {
+                  flag_wait(p.sig_flags[p.sig_rank] + owner, p.sig_epoch, p.status);
+                  ready |= 1u << owner;
+                }
               }
               tma_load_4d(sa, &peer_a.m[owner], full_bar(s), kb * BLOCK_K, a_row0 - owner * p.a_peer_rows, b0, b1);
             } else {
@@ -474,6 +518,37 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int q = warp & 3;            // TMEM lane quarter owned by this warp
     const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
     const EpilogueArgs& e = p.ep;
+    if (p.stage_bytes > 0) {
+      // Remote shards -> local staging, each byte once: this block copies its slice of every other rank's shard with plain
+      // 16-byte peer loads, while the MMA pipeline already works on this rank's own rows.  The eight epilogue warps have
+      // nothing else to do until the first accumulator is complete.
+      const int te = (int)threadIdx.x - 64;                       // 0 .. 255
+      const long long n16 = p.stage_bytes >> 4;
+      const long long per = (n16 + gridDim.x - 1) / gridDim.x;
+      const long long lo = (long long)blockIdx.x * per;
+      const long long hi = lo + per < n16 ? lo + per : n16;
+      for (int r = 0; r < p.sig_world; ++r) {
+        if (r == p.sig_rank) continue;
+        if (te == 0) flag_wait(p.sig_flags[p.sig_rank] + r, p.sig_epoch, p.status);   // rank r's shard is in place
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const uint4* src = reinterpret_cast<const uint4*>(p.stage_src[r]);
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.stage_dst) + (long long)r * p.stage_bytes);
+        long long i = lo + te;
+        for (; i + 3 * 256 < hi; i += 4 * 256) {                   // four loads in flight per thread
+          const uint4 v0 = __ldcg(src + i), v1 = __ldcg(src + i + 256), v2 = __ldcg(src + i + 512), v3 = __ldcg(src + i + 768);
+          dst[i] = v0; dst[i + 256] = v1; dst[i + 512] = v2; dst[i + 768] = v3;
+        }
+        for (; i < hi; i += 256) dst[i] = __ldcg(src + i);
+      }
+      __threadfence();
+      asm volatile("fence.proxy.async;" ::: "memory");              // the staged bytes are read back through TMA (async proxy)
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (te == 0) {
+        unsigned int old;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.stage_counter) : "memory");
+        (void)old;
+      }
+    }
     uint8_t* stage = smem + NUM_STAGES * STAGE_BYTES + 256 + (warp - 2) * EPI_STAGE_BYTES;
     long long tcount = 0;
     bool ok = true;
@@ -481,7 +556,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const long long tile = p.ksplit > 1 ? w / p.ksplit : w;
       const int batch = (int)(tile / ((long long)p.tiles_m * p.tiles_n));
       const int rem = (int)(tile % ((long long)p.tiles_m * p.tiles_n));
-      const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
+      int tm, tn;
+      tile_coords(p, rem, TILE_M, tm, tn);
       const int b0 = batch % p.batch0, b1 = batch / p.batch0;
       const int tile_row0 = tm * TILE_M + (int)cta_rank * BLOCK_M;   // first output row held in this CTA's tensor memory
       const int acc = (int)(tcount % NUM_ACC);
@@ -678,6 +754,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (p.sig_tail && warp >= 2) __threadfence_system();   // this thread's reductions into peer memory are performed before the block reports
   tc_fence_before();
   __syncthreads();
+  if (p.stage_bytes > 0 && threadIdx.x == 0) {
+    // the last block out clears both staging counters for the next call
+    unsigned int gone;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(gone) : "l"(p.stage_counter + 1) : "memory");
+    if (gone == gridDim.x - 1) {
+      *((volatile unsigned int*)p.stage_counter) = 0u;
+      *((volatile unsigned int*)(p.stage_counter + 1)) = 0u;
+      __threadfence();
+    }
+  }
   if (p.sig_tail && threadIdx.x == 0) {
     unsigned int done;
     asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(done) : "l"(p.sig_counter) : "memory");
@@ -816,6 +902,9 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   if ((p.sig_head || p.sig_tail) && (a->sig_world < 1 || a->sig_world > 8 || a->sig_rank < 0 || a->sig_rank >= a->sig_world)) return -8;
   if (p.sig_tail && !a->sig_counter) return -8;
   if (p.sig_head && !a->peer_A) return -8;
+  p.stage_src = a->stage_src; p.stage_dst = a->stage_dst; p.stage_counter = a->stage_counter;
+  p.stage_bytes = (a->stage_src && a->stage_dst && a->stage_counter) ? a->stage_bytes : 0;
+  if (p.stage_bytes > 0 && (!p.sig_head || (p.stage_bytes & 15) != 0 || pair)) return -9;
   p.status = sb_status_ptr();
   if (!p.status) return -2;
   static const int env_debug = [] { const char* e = getenv("SPEECH_B200_GEMM_DEBUG"); return e ? atoi(e) : 0; }();

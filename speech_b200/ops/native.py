@@ -40,6 +40,7 @@ class SbGemmArgs(ctypes.Structure):
         ("drop_p", ctypes.c_float), ("drop_seed", ctypes.c_ulonglong), ("ksplit", ctypes.c_int), ("pad_", ctypes.c_int), ("peer_D", ctypes.c_void_p), ("peer_rows", ctypes.c_int), ("pad2_", ctypes.c_int), ("peer_A", ctypes.c_void_p), ("peer_a_rows", ctypes.c_int), ("peer_world", ctypes.c_int), ("pair", ctypes.c_int),
         ("sig_flags", ctypes.c_void_p), ("sig_counter", ctypes.c_void_p), ("sig_world", ctypes.c_int), ("sig_rank", ctypes.c_int),
         ("sig_epoch", ctypes.c_uint), ("sig_head", ctypes.c_int), ("sig_tail", ctypes.c_int), ("pad3_", ctypes.c_int),
+        ("stage_src", ctypes.c_void_p), ("stage_dst", ctypes.c_void_p), ("stage_bytes", ctypes.c_longlong), ("stage_counter", ctypes.c_void_p),
     ]
 
 
@@ -108,11 +109,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
          ldp: Optional[int] = None, p_bs: Tuple[int, int] = (0, 0), alpha: float = 1.0, beta: float = 0.0,
          max_ctas: int = 0, fold_batch1: bool = False, tile_n: int = 0, drop_p: float = 0.0, drop_seed: int = 0,
          ksplit: int = 0, pair: int = 0, peer_out: int = 0, peer_rows: int = 0, peer_a=None, peer_a_rows: int = 0,
-         sig: Optional[Tuple[int, int, int, int, int, int, int]] = None) -> torch.Tensor:
+         sig: Optional[Tuple[int, int, int, int, int, int, int]] = None,
+         stage: Optional[Tuple[int, int, int, int]] = None) -> torch.Tensor:
     """``out = epilogue(alpha * A @ B^T)`` on raw strided bf16 operands (see csrc/gemm_tcgen05.cu).
 
     ``sig`` = (flag table pointer, counter pointer, world, rank, epoch, head, tail): rank synchronisation inside the kernel for
-    the fused collectives (``parallel/fused.py``).
+    the fused collectives (``parallel/fused.py``); ``stage`` = (device table of the ranks' shard addresses, local staging area,
+    bytes per shard, counter words): remote shards are copied once into local memory by the kernel's own blocks.
 
     ``a_mn`` / ``b_mn``: the operand is stored transposed (A as [K, M], B as [K, N]).  ``lda`` / ``ldb`` are the row
     strides of the *stored* matrices, in elements (multiples of 8).
@@ -135,7 +138,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
         float(drop_p), int(drop_seed) if drop_p > 0.0 else 0, int(ksplit), 0, int(peer_out) or None, int(peer_rows), 0,
         ctypes.cast(peer_a, ctypes.c_void_p) if peer_a is not None else None, int(peer_a_rows), len(peer_a) if peer_a is not None else 0, int(pair),
         *((int(sig[0]) or None, int(sig[1]) or None, int(sig[2]), int(sig[3]), int(sig[4]) & 0xFFFFFFFF, int(sig[5]), int(sig[6]), 0)
-          if sig is not None else (None, None, 0, 0, 0, 0, 0, 0)))
+          if sig is not None else (None, None, 0, 0, 0, 0, 0, 0)),
+        *((int(stage[0]) or None, int(stage[1]) or None, int(stage[2]), int(stage[3]) or None) if stage is not None else (None, None, 0, None)))
     _check(lib().sb_gemm_bf16(ctypes.byref(g), _stream()), "sb_gemm_bf16")
     return out
 

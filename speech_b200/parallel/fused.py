@@ -95,7 +95,10 @@ class GemmReduceScatter:
 
 
 class AllGatherGemm:
-    def __init__(self, max_rows_per_rank: int, max_k: int, device: torch.device, group=None):
+    def __init__(self, max_rows_per_rank: int, max_k: int, device: torch.device, group=None, staged: bool = True):
+        """``staged``: the kernel's blocks first copy each remote shard once into local memory (plain peer loads) and the TMA
+        producer reads remote rows from there; without it every A tile is loaded from the owner's memory by every column tile
+        that needs it, which multiplies the NVLink traffic by the number of column tiles."""
         import ctypes
 
         from ..ops import native
@@ -110,6 +113,11 @@ class AllGatherGemm:
         self.buf = SymmetricBuffer(2 * self.half, device, self.group)
         self.peer_ptrs = [int(p) for p in self.buf.handle.buffer_ptrs]
         self.flags = _RankFlags(device, self.group)
+        self.staged = bool(staged) and self.world > 1
+        if self.staged:
+            self.staging = torch.empty(self.world * self.half, dtype=torch.uint8, device=device)
+            self.src_tables = [torch.tensor([p + h * self.half for p in self.peer_ptrs], dtype=torch.int64, device=device) for h in range(2)]
+            self.stage_counter = torch.zeros(4, dtype=torch.int32, device=device)
 
     def input_buffer(self, rows: int, K: int) -> torch.Tensor:
         """The shard buffer of the NEXT call as a [rows, K] bf16 view: a producer kernel can write its output there directly,
@@ -134,7 +142,14 @@ class AllGatherGemm:
         h = epoch & 1
         M, N = rows * self.world, w.shape[0]
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x_local.device)
+        sig = (self.flags.table, 0, self.world, self.rank, epoch, 1, 0)
+        if self.staged:
+            nbytes = rows * K * 2
+            base = self.staging.data_ptr()
+            arr = (self.ctypes.c_void_p * self.world)(*[mine.data_ptr() if r == self.rank else base + r * nbytes for r in range(self.world)])
+            self.native.gemm(mine, w, out, M=M, N=N, K=K, lda=K, ldb=w.stride(0), ldd=N, bias=bias, act=act, peer_a=arr, peer_a_rows=rows, pair=-1,
+                             sig=sig, stage=(self.src_tables[h].data_ptr(), base, nbytes, self.stage_counter.data_ptr()))
+            return out
         arr = (self.ctypes.c_void_p * self.world)(*[p + h * self.half for p in self.peer_ptrs])
-        self.native.gemm(mine, w, out, M=M, N=N, K=K, lda=K, ldb=w.stride(0), ldd=N, bias=bias, act=act, peer_a=arr, peer_a_rows=rows, pair=-1,
-                         sig=(self.flags.table, 0, self.world, self.rank, epoch, 1, 0))
+        self.native.gemm(mine, w, out, M=M, N=N, K=K, lda=K, ldb=w.stride(0), ldd=N, bias=bias, act=act, peer_a=arr, peer_a_rows=rows, pair=-1, sig=sig)
         return out

@@ -236,6 +236,18 @@ GEMM_RS_SCRIPT = textwrap.dedent("""
         ref = torch.relu(torch.cat(parts).float() @ w2.float().t() + b2)
         torch.cuda.synchronize()
         worst = max(worst, float((got - ref).abs().max() / ref.abs().max()) * 0.1)     # bf16 output: scaled into the fp32 budget below
+    # the un-staged variant (A tiles loaded from the owner's memory by every column tile) stays covered
+    ag_direct = AllGatherGemm(256, 512, dev, staged=False)
+    torch.manual_seed(500 + rank)
+    xl = torch.randn(256, 512, device=dev).to(torch.bfloat16)
+    torch.manual_seed(501)
+    w2 = (torch.randn(384, 512, device=dev) * 0.1).to(torch.bfloat16)
+    got = ag_direct(xl, w2).float()
+    parts = [torch.empty_like(xl) for _ in range(world)]
+    dist.all_gather(parts, xl)
+    ref = torch.cat(parts).float() @ w2.float().t()
+    torch.cuda.synchronize()
+    worst = max(worst, float((got - ref).abs().max() / ref.abs().max()) * 0.1)
     # timing against GEMM + NCCL reduce-scatter (device events, max over ranks is taken by the test)
     M, N, K = 1024 * world, 1024, 4096
     x = torch.randn(M, K, device=dev).to(torch.bfloat16); w = torch.randn(N, K, device=dev).to(torch.bfloat16)
