@@ -289,6 +289,15 @@ def main():
     run.trainer = Trainer(max_steps=total_steps, precision="bf16-mixed", gradient_clip_val=1.0, log_every_n_steps=10 ** 9,
                           accelerator="gpu", sync_batchnorm=True, enable_checkpointing=False, logger=False)
     run.started = False
+    # The 16 batches have 16 different shapes and only the first W of them are seen during warm-up: reserve the device memory
+    # pool once (one large block handed back to the caching allocator, which then carves every later request out of it), so that
+    # the first visit of a shape inside the timed region does not go to the driver for memory.
+    reserve_gb = float(os.environ.get("SPEECH_B200_BENCH_RESERVE_GB", "72"))
+    if reserve_gb > 0:
+        free_b, _ = torch.cuda.mem_get_info(dev)
+        n = int(min(reserve_gb * 2 ** 30, 0.6 * free_b))
+        block = torch.empty(n, dtype=torch.uint8, device=dev)
+        del block
 
     ms, audio, launches, clocks, losses = run(e2e=False)
     run.trainer.current_epoch = 0
