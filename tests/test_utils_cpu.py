@@ -242,3 +242,34 @@ def test_asr_evaluator_explorer_report_and_rir_generator(tmp_path):
     path = gen.generate(str(tmp_path / "rirs"), 2)
     recs = [json.loads(l) for l in open(path)]
     assert len(recs) == 2 and len(recs[0]["mic_positions"]) == 2 and (tmp_path / "rirs" / "rir_00001.wav").exists()
+
+
+def test_fp8_post_training_quantisation_calibrate_replace_report_roundtrip(tmp_path):
+    import torch
+
+    from speech_b200.utils.quantization import (QuantLinear, calibrate, load_quantized, quantization_report, quantize_model, save_quantized,
+                                                to_e4m3)
+
+    # e4m3 grid: exact values stay, 3 mantissa bits otherwise, saturation at 448
+    x = torch.tensor([0.0, 1.0, 1.0625, 1.125, 3.3, 447.0, 1000.0, -0.3])
+    q = to_e4m3(x)
+    assert q.tolist()[:2] == [0.0, 1.0] and float(q[3]) == 1.125 and float(q[6]) == 448.0 and abs(float(q[4]) - 3.25) < 1e-6
+    assert float((q[2] - 1.0).abs()) in (0.0, 0.125)
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 16))
+    batches = [(torch.randn(8, 32),) for _ in range(6)]
+    amax = calibrate(net, batches, percentile=100.0)
+    assert set(amax) == {"0", "2"} and amax["0"] > 2.0 and amax["2"] > 0
+    only = calibrate(net, batches, skip=[r"^2$"])
+    assert set(only) == {"0"}
+    rep = quantization_report(net, amax)
+    assert len(rep) == 2 and all(r["weight_sqnr_db"] > 25 for r in rep)          # about 6 dB per mantissa bit + the per-channel scale
+    ref = net(batches[0][0])
+    assert quantize_model(net, amax) == ["0", "2"] and isinstance(net[0], QuantLinear)
+    out = net(batches[0][0])
+    rel = float((out - ref).norm() / ref.norm())
+    assert 0 < rel < 0.08, rel
+    save_quantized(net, str(tmp_path / "q.pt"))
+    fresh = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 16))
+    load_quantized(fresh, str(tmp_path / "q.pt"))
+    assert torch.equal(fresh(batches[0][0]), out)
