@@ -56,6 +56,10 @@ struct SbGemmArgs {
   void* stage_dst;              // staging area: sig_world slots of stage_bytes each
   long long stage_bytes;        // bytes of one shard (multiple of 16); 0 = no staging
   unsigned int* stage_counter;  // device words, zero between calls: [0] blocks that finished copying, [1] blocks that exited
+  // Optional fp32 scratch of at least M * N * 4 bytes for small-M GEMMs with a bf16 output: when given (and the shape has few
+  // output tiles and a long K), K is split over more blocks through this scratch and a second small kernel applies the epilogue.
+  void* splitk_ws;
+  long long splitk_ws_bytes;
 };
 
 

@@ -821,9 +821,87 @@ bool g_attr_set[16] = {};
 
 }  // namespace
 
+// ---------------------------------------------------------------------------------------------------------------------------
+// Small-M GEMMs with a bf16 output (inference with a few hundred tokens: streaming steps, decoding): the output has a handful of
+// tiles, so a handful of blocks would each walk the whole K extent with at most NUM_STAGES loads in flight, and the kernel
+// time is (K blocks / stages) x memory latency.  Splitting K over more blocks keeps every block's slice inside its pipeline
+// depth; the partial sums meet in an fp32 workspace that the caller provides (vector reductions, L2-resident) and a small kernel
+// applies the epilogue.  Without a workspace the GEMM runs as one pass.
+__global__ void splitk_finish_kernel(const float* __restrict__ ws, int M, int N, __nv_bfloat16* __restrict__ D, long long ldd,
+                                     const float* __restrict__ bias_f32, const __nv_bfloat16* __restrict__ bias_bf16,
+                                     __nv_bfloat16* __restrict__ D_pre, long long ldp, const __nv_bfloat16* __restrict__ residual,
+                                     long long ldr, float alpha, int act) {
+  const int n4 = N >> 2;
+  const long long total = (long long)M * n4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int m = (int)(i / n4), c = (int)(i % n4) * 4;
+    const float4 w = __ldcg(reinterpret_cast<const float4*>(ws + (long long)m * N + c));
+    float v[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (bias_f32) v[j] += __ldg(bias_f32 + c + j);
+      else if (bias_bf16) v[j] += __bfloat162float(bias_bf16[c + j]);
+    }
+    if (D_pre) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) D_pre[(long long)m * ldp + c + j] = __float2bfloat16(v[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (act == 2) v[j] = sb_swish(v[j]);
+      else if (act == 1) v[j] = fmaxf(v[j], 0.f);
+      else if (act == 3) v[j] = sb_gelu(v[j]);
+      v[j] *= alpha;
+      if (residual) v[j] += __bfloat162float(residual[(long long)m * ldr + c + j]);
+      D[(long long)m * ldd + c + j] = __float2bfloat16(v[j]);
+    }
+  }
+}
+
+SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream);
+
+// 1 = handled (rc in *out_rc), 0 = not applicable
+static int small_m_splitk(const SbGemmArgs* a, cudaStream_t stream, int* out_rc) {
+  static const bool enabled = [] { const char* e = getenv("SPEECH_B200_SMALL_M_SPLITK"); return !(e && e[0] == '0'); }();
+  if (!enabled || a->d_is_f32 || a->beta != 0.f || a->batch0 != 1 || a->batch1 != 1 || a->fold_batch1 || a->aux || a->drop_p > 0.f ||
+      a->peer_D || a->peer_A || a->sig_flags || a->ksplit != 0 || a->a_mn_major || a->M > 1024 || (a->N & 3) || a->pair == 1)
+    return 0;
+  const int num_kb = (a->K + BLOCK_K - 1) / BLOCK_K;
+  const long long tiles = (long long)((a->M + BLOCK_M - 1) / BLOCK_M) * ((a->N + 127) / 128);
+  const int sms = sb_num_sms() - sb_reserved_sms();
+  if (num_kb < 12 || tiles * 4 > sms || !a->splitk_ws || (long long)a->M * a->N * 4 > a->splitk_ws_bytes) return 0;
+  int split = (int)(sms / tiles);
+  if (split > num_kb / 4) split = num_kb / 4;     // a slice keeps at least four K blocks
+  if (split > 16) split = 16;
+  if (split < 2) return 0;
+  float* ws = (float*)a->splitk_ws;   // the caller's scratch (stream-ordered allocation), M x N fp32
+  cudaError_t ce = cudaMemsetAsync(ws, 0, (size_t)a->M * a->N * 4, stream);
+  if (ce != cudaSuccess) { *out_rc = (int)ce; return 1; }
+  SbGemmArgs g = *a;
+  g.D = ws; g.d_is_f32 = 1; g.ldd = a->N; g.beta = 1.f;
+  g.bias = nullptr; g.residual = nullptr; g.D_pre = nullptr; g.act = 0; g.alpha = 1.f;
+  g.tile_n = 128; g.ksplit = split; g.pair = -1; g.splitk_ws = nullptr; g.splitk_ws_bytes = 0;
+  int rc = sb_gemm_bf16(&g, stream);
+  if (rc != 0) { *out_rc = rc; return 1; }
+  const long long total = (long long)a->M * (a->N >> 2);
+  long long blocks = (total + 255) / 256;
+  if (blocks > (long long)sms * 4) blocks = (long long)sms * 4;
+  splitk_finish_kernel<<<(int)blocks, 256, 0, stream>>>(ws, a->M, a->N, (__nv_bfloat16*)a->D, a->ldd,
+                                                       (a->bias && a->bias_is_f32) ? (const float*)a->bias : nullptr,
+                                                       (a->bias && !a->bias_is_f32) ? (const __nv_bfloat16*)a->bias : nullptr,
+                                                       (__nv_bfloat16*)a->D_pre, a->ldp, (const __nv_bfloat16*)a->residual, a->ldr, a->alpha,
+                                                       a->act);
+  *out_rc = (int)cudaGetLastError();
+  return 1;
+}
+
 // Returns 0 on success, a negative code for invalid arguments, or a positive cudaError_t.
 SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   if (a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batch0 <= 0 || a->batch1 <= 0) return -1;
+  {
+    int rc = 0;
+    if (small_m_splitk(a, stream, &rc)) return rc;
+  }
   // 256-wide tiles when the problem has enough of them to fill the machine, else 128-wide
   // split-K is possible when the epilogue is exactly D(fp32) += alpha * A B^T: weight gradients (long K, few output tiles)
   const bool can_split = a->d_is_f32 && a->beta == 1.f && !a->bias && !a->residual && !a->aux && !a->D_pre && a->act == 0 &&

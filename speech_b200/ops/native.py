@@ -21,6 +21,7 @@ import torch
 _LIB = None
 _LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libspeech_b200.so")
 launch_count = 0  # number of kernel-launching library calls (benchmarks report it)
+_SMALL_M_SPLITK = os.environ.get("SPEECH_B200_SMALL_M_SPLITK", "1") != "0"
 
 
 class SbGemmArgs(ctypes.Structure):
@@ -41,6 +42,7 @@ class SbGemmArgs(ctypes.Structure):
         ("sig_flags", ctypes.c_void_p), ("sig_counter", ctypes.c_void_p), ("sig_world", ctypes.c_int), ("sig_rank", ctypes.c_int),
         ("sig_epoch", ctypes.c_uint), ("sig_head", ctypes.c_int), ("sig_tail", ctypes.c_int), ("pad3_", ctypes.c_int),
         ("stage_src", ctypes.c_void_p), ("stage_dst", ctypes.c_void_p), ("stage_bytes", ctypes.c_longlong), ("stage_counter", ctypes.c_void_p),
+        ("splitk_ws", ctypes.c_void_p), ("splitk_ws_bytes", ctypes.c_longlong),
     ]
 
 
@@ -122,6 +124,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
     """
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "GEMM operands must be bf16"
     assert out.dtype in (torch.float32, torch.bfloat16)
+    # few output tiles and a long K (inference on a few hundred tokens): hand the kernel an fp32 scratch so that it can split K
+    ws = None
+    if (M <= 1024 and K >= 768 and ksplit == 0 and out.dtype == torch.bfloat16 and batch == (1, 1) and aux is None and drop_p <= 0.0
+            and beta == 0.0 and peer_a is None and not peer_out and M * N <= (4 << 20) and _SMALL_M_SPLITK):
+        ws = torch.empty(M * N, dtype=torch.float32, device=out.device)
     # one positional constructor call: field-by-field assignment through ctypes descriptors costs several microseconds
     g = SbGemmArgs(
         a.data_ptr(), b.data_ptr(), M, N, K, int(a_mn), int(b_mn),
@@ -139,7 +146,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int,
         ctypes.cast(peer_a, ctypes.c_void_p) if peer_a is not None else None, int(peer_a_rows), len(peer_a) if peer_a is not None else 0, int(pair),
         *((int(sig[0]) or None, int(sig[1]) or None, int(sig[2]), int(sig[3]), int(sig[4]) & 0xFFFFFFFF, int(sig[5]), int(sig[6]), 0)
           if sig is not None else (None, None, 0, 0, 0, 0, 0, 0)),
-        *((int(stage[0]) or None, int(stage[1]) or None, int(stage[2]), int(stage[3]) or None) if stage is not None else (None, None, 0, None)))
+        *((int(stage[0]) or None, int(stage[1]) or None, int(stage[2]), int(stage[3]) or None) if stage is not None else (None, None, 0, None)),
+        ws.data_ptr() if ws is not None else None, ws.numel() * 4 if ws is not None else 0)
     _check(lib().sb_gemm_bf16(ctypes.byref(g), _stream()), "sb_gemm_bf16")
     return out
 

@@ -220,3 +220,28 @@ def test_layernorm_forward_register_path_and_backward_residual():
         torch.nn.functional.layer_norm(x32, (D,), g32, b32, 1e-5).backward(dy.float())
         assert (dx.float() - (x32.grad + dres.float())).abs().max().item() < 0.08
         assert (dg - g32.grad).abs().max().item() < 0.02 * rows ** 0.5 and (db - b32.grad).abs().max().item() < 0.02 * rows ** 0.5
+
+
+@pytest.mark.parametrize("M,N,K,b_mn", [(256, 1024, 4096, False), (130, 520, 1024, False), (64, 2048, 1536, True), (512, 4096, 1024, False)])
+def test_gemm_small_m_split_k_through_scratch_matches_single_pass(M, N, K, b_mn):
+    """Few output tiles and a long K: the wrapper hands the kernel an fp32 scratch, K is split over more blocks and a second
+    kernel applies bias / activation / scale / residual and writes the pre-activation; same result as the one-pass kernel."""
+    nat = _native()
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn((K, N) if b_mn else (N, K), device="cuda") * 0.05).to(torch.bfloat16)
+    bias = torch.randn(N, device="cuda")
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    out, pre = torch.empty(M, N, device="cuda", dtype=torch.bfloat16), torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    launches = nat.launch_count
+    nat.gemm(a, b, out, M=M, N=N, K=K, b_mn=b_mn, bias=bias, act="swish", residual=res, out_pre=pre, alpha=0.5)
+    nat.check_status()
+    z = a.float() @ (b.float() if b_mn else b.float().t()) + bias
+    ref = 0.5 * torch.nn.functional.silu(z) + res.float()
+    assert (pre.float() - z).abs().max().item() <= 2e-2 * max(1.0, z.abs().max().item())
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    # ksplit=-1 forces the one-pass kernel: both paths agree to bf16 rounding
+    one = torch.empty_like(out)
+    nat.gemm(a, b, one, M=M, N=N, K=K, b_mn=b_mn, bias=bias, act="swish", residual=res, alpha=0.5, ksplit=-1)
+    assert (one.float() - out.float()).abs().max().item() <= 3e-2 * max(1.0, ref.abs().max().item())
+    assert nat.launch_count == launches + 2
