@@ -273,3 +273,56 @@ def test_fp8_post_training_quantisation_calibrate_replace_report_roundtrip(tmp_p
     fresh = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 16))
     load_quantized(fresh, str(tmp_path / "q.pt"))
     assert torch.equal(fresh(batches[0][0]), out)
+
+
+def test_sharded_checkpoint_io_precision_timing_launcher_telemetry_punctuation(tmp_path):
+    import sys
+
+    import torch
+
+    from speech_b200.utils.extras import (DeltaTimingCallback, DistributedCheckpointIO, FlashPrecision, ProcessLauncher, TelemetryCallback,
+                                          punctuation_error_rate)
+
+    # two "ranks" write one checkpoint: replicated tensors are spread over the ranks, the sharded one is stored piecewise
+    full = {"a.weight": torch.randn(4, 3), "b.bias": torch.randn(5), "emb": torch.arange(12.0).view(6, 2)}
+    path = str(tmp_path / "ckpt")
+    ios = [DistributedCheckpointIO(rank=r, world_size=2, async_save=True) for r in range(2)]
+    for r, io in enumerate(ios):
+        st = dict(full, emb=full["emb"][3 * r: 3 * r + 3])
+        io.save_checkpoint(st, path, sharded={"emb": 0}, extra={"step": 7})
+    assert not DistributedCheckpointIO.is_complete(path)               # the index appears only after the writes are joined
+    for io in reversed(ios):
+        io.finalize()
+    assert DistributedCheckpointIO.is_complete(path)
+    got, extra = DistributedCheckpointIO.load_checkpoint(path)
+    assert extra == {"step": 7} and all(torch.equal(got[k], full[k]) for k in full)
+    net = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.LayerNorm(4))
+    net[1].register_parameter("norm_scale", torch.nn.Parameter(torch.ones(4)))
+    FlashPrecision().convert_module(net)
+    assert net[0].weight.dtype == torch.bfloat16 and net[1].norm_scale.dtype == torch.float32
+    b = FlashPrecision().convert_input({"audio_signal": torch.zeros(2, 8), "features": torch.zeros(2, 8), "tokens": torch.zeros(2, 3, dtype=torch.long)})
+    assert b["audio_signal"].dtype == torch.float32 and b["features"].dtype == torch.bfloat16 and b["tokens"].dtype == torch.long
+    t = [0.0]
+
+    class Tr:
+        callback_metrics = {}
+
+    cb = DeltaTimingCallback(clock=lambda: t[0])
+    for dt in (1.0, 2.5):
+        cb.on_train_batch_end(Tr, None, None, None, 0)
+        t[0] += dt
+    cb.on_train_batch_end(Tr, None, None, None, 0)
+    assert Tr.callback_metrics["train_step_timing in s"] == 2.5
+    tel = TelemetryCallback(path=str(tmp_path / "tel.jsonl"), clock=lambda: t[0])
+    tel.on_model_init_start()
+    t[0] += 3.0
+    tel.on_model_init_end(params=10)
+    assert tel.durations() == {"model_init": 3.0} and len(open(tmp_path / "tel.jsonl").read().splitlines()) == 2
+    jobs = ProcessLauncher.expand_sweep({"lr": [1, 2], "bs": [8]})
+    assert jobs == [["lr=1", "bs=8"], ["lr=2", "bs=8"]]
+    code = "import sys, os; print(sys.argv[1:], os.environ.get('CUDA_VISIBLE_DEVICES')); sys.exit(3 if 'lr=2' in sys.argv else 0)"
+    res = ProcessLauncher([sys.executable, "-c", code], gpu_ids=[5, 6], log_dir=str(tmp_path / "mr")).launch(jobs)
+    assert [r[1] for r in res] == [0, 3] and "lr=1" in open(res[0][2]).read() and open(res[0][2]).read().strip()[-1] in "56"
+    per = punctuation_error_rate(["hello, world how are you."], ["hello world, how are you?"])
+    assert per[","]["insertions"] == 1 and per[","]["deletions"] == 1 and per["?"]["substitutions"] == 1 and per["overall"]["correct"] == 0
+    assert punctuation_error_rate(["yes, it is."], ["yes, it is."])["overall"]["per"] == 0.0
