@@ -148,6 +148,27 @@ class ConvSubsampling(nn.Module):
             x = self.conv(x.transpose(1, 2)).transpose(1, 2)
         return x, out_lengths
 
+    def prime_shapes(self, shapes, device, dtype=None) -> None:
+        """Run the convolution stack forward and backward once on zeros for every ``(batch, frames)`` in ``shapes``.  The
+        convolution library builds an execution plan per problem shape on first use (milliseconds each, three per layer with the
+        backward passes); with bucketed batches the shapes are known before training starts, so the plans can be built then
+        instead of inside the first step that meets a shape.  Parameter gradients produced here are discarded."""
+        if not self.conv2d_subsampling:
+            return
+        import contextlib
+
+        ctx = torch.autocast("cuda", dtype=dtype) if (dtype is not None and torch.device(device).type == "cuda") else contextlib.nullcontext()
+        was = self.training
+        self.train()
+        for b, t in shapes:
+            x = torch.zeros(int(b), int(t), self._feat_in, device=device, requires_grad=True)
+            with ctx:
+                y, _ = self.conv(x, torch.full((int(b),), int(t), device=device, dtype=torch.long))
+            y.float().sum().backward()
+        for p in self.parameters():
+            p.grad = None
+        self.train(was)
+
     def reset_parameters(self):
         if self._subsampling != "dw_striding":
             return

@@ -76,7 +76,7 @@ class PeerAllReduce:
         self.recv_off = self.flags_bytes + region
         self.buf = SymmetricBuffer(self.flags_bytes + 2 * region, device, group)
         self.rank, self.world = self.buf.rank, self.buf.world
-        self.ctas = int(ctas or os.environ.get("SPEECH_B200_PEER_CTAS", 8))
+        self.ctas = int(ctas or os.environ.get("SPEECH_B200_PEER_CTAS", 12))
         self.epoch = 0
 
     def __call__(self, flat: torch.Tensor, scale: float = 1.0) -> None:
