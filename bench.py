@@ -24,6 +24,10 @@ from __future__ import annotations
 import argparse
 import json
 import os
+
+# Load every kernel image when its module is loaded instead of on first launch: lazily loaded kernels are paged in from disk the
+# first time a shape selects them, which on a freshly started machine lands inside the timed steps.  Must be set before CUDA starts.
+os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
 import statistics
 import subprocess
 import sys
