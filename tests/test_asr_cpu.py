@@ -216,3 +216,15 @@ def test_normalised_lstm_variants_thread_state():
         y.sum().backward()
     with pytest.raises(ValueError):
         rnn(16, 24, 1, norm="instance")
+
+
+def test_subsampling_prime_shapes_leaves_no_gradients_and_keeps_mode():
+    import torch
+
+    from speech_b200.modules.subsampling import ConvSubsampling
+
+    sub = ConvSubsampling(subsampling="dw_striding", subsampling_factor=8, feat_in=16, feat_out=32, conv_channels=8).eval()
+    before = [p.detach().clone() for p in sub.parameters()]
+    sub.prime_shapes([(2, 40), (3, 57)], "cpu")
+    assert not sub.training and all(p.grad is None for p in sub.parameters())
+    assert all(torch.equal(a, b) for a, b in zip(before, sub.parameters()))
