@@ -85,6 +85,9 @@ __device__ __forceinline__ void add8(float* acc, const uint4& v) {
   }
 }
 
+// LOCAL = false leaves out the two local phases (cast into the send region, unpack from the receive region): they are then run
+// by the wide element-wise kernels below, so that the few blocks of this kernel only do what needs them, the peer traffic.
+template <bool LOCAL>
 __global__ void __launch_bounds__(512) peer_allreduce_kernel(SbPeerArgs a) {
   __shared__ int s_fail;
   const int b = blockIdx.x;
@@ -102,7 +105,7 @@ __global__ void __launch_bounds__(512) peer_allreduce_kernel(SbPeerArgs a) {
   constexpr int UNR = 4;
   const long long step = (long long)blockDim.x * 8;
   // ---- phase 0: local cast of sub-chunk b of every slice
-  for (int p = 0; p < a.world; ++p) {
+  for (int p = 0; LOCAL && p < a.world; ++p) {
     const long long base = (long long)p * a.slice;
     for (long long i0 = c0 + (long long)threadIdx.x * 8; i0 < c1; i0 += step * UNR) {
       float4 x[UNR], y[UNR];
@@ -190,7 +193,7 @@ __global__ void __launch_bounds__(512) peer_allreduce_kernel(SbPeerArgs a) {
   }
 
   // ---- phase B: unpack sub-chunk b of every slice into the fp32 arena
-  for (int p = 0; p < a.world; ++p) {
+  for (int p = 0; LOCAL && p < a.world; ++p) {
     const long long base = (long long)p * a.slice;
     for (long long i0 = c0 + (long long)threadIdx.x * 8; i0 < c1; i0 += step * UNR) {
       uint4 v[UNR];
@@ -216,6 +219,43 @@ __global__ void __launch_bounds__(512) peer_allreduce_kernel(SbPeerArgs a) {
   }
 }
 
+// fp32 gradients * scale -> bf16 send region (elements beyond n are zero), whole GPU wide and short
+__global__ void peer_pack_kernel(const float* __restrict__ grad, __nv_bfloat16* __restrict__ send, long long n, long long padded, float scale) {
+  const long long n8 = padded >> 3;
+  for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < n8; g += (long long)gridDim.x * blockDim.x) {
+    const long long e = g << 3;
+    float t[8];
+    if (e + 8 <= n) {
+      const float4 x = *reinterpret_cast<const float4*>(grad + e), y = *reinterpret_cast<const float4*>(grad + e + 4);
+      t[0] = x.x; t[1] = x.y; t[2] = x.z; t[3] = x.w; t[4] = y.x; t[5] = y.y; t[6] = y.z; t[7] = y.w;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) t[k] = e + k < n ? grad[e + k] : 0.f;
+    }
+    __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(t[2 * k] * scale, t[2 * k + 1] * scale);
+    *reinterpret_cast<uint4*>(send + e) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
+// bf16 receive region -> fp32 gradients
+__global__ void peer_unpack_kernel(const __nv_bfloat16* __restrict__ recv, float* __restrict__ grad, long long n) {
+  const long long n8 = (n + 7) >> 3;
+  for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < n8; g += (long long)gridDim.x * blockDim.x) {
+    const long long e = g << 3;
+    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(recv + e));     // written by other GPUs
+    float t[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    add8(t, v);
+    if (e + 8 <= n) {
+      *reinterpret_cast<float4*>(grad + e) = make_float4(t[0], t[1], t[2], t[3]);
+      *reinterpret_cast<float4*>(grad + e + 4) = make_float4(t[4], t[5], t[6], t[7]);
+    } else {
+      for (int k = 0; k < 8 && e + k < n; ++k) grad[e + k] = t[k];
+    }
+  }
+}
+
 }  // namespace
 
 // Bytes of the flag block at the start of a symmetric buffer.
@@ -235,7 +275,36 @@ SB_API int sb_peer_allreduce(SbPeerArgs* a, cudaStream_t stream) {
   if (a->status == nullptr) return -3;
   a->slice = slice;
   a->chunk = chunk;
-  peer_allreduce_kernel<<<a->ctas, 512, 0, stream>>>(*a);
+  peer_allreduce_kernel<true><<<a->ctas, 512, 0, stream>>>(*a);
+  return (int)cudaGetLastError();
+}
+
+// Same reduction as three launches on `stream`: a wide cast kernel, the peer kernel with its local phases left out, a wide unpack
+// kernel.  With the local phases inside the few-block kernel those blocks spend most of their time on local memory at the
+// bandwidth of a few SMs; as wide kernels the same bytes take a fraction of a millisecond, squeezed in between the GEMMs.
+// `my_base` is this rank's symmetric buffer (the entry of `buffers` for this rank).
+SB_API int sb_peer_allreduce_split(SbPeerArgs* a, void* my_base, cudaStream_t stream) {
+  if (a->world < 1 || a->world > SB_PEER_MAX_WORLD || a->rank < 0 || a->rank >= a->world || !my_base) return -1;
+  if (a->ctas < 1 || a->ctas > SB_PEER_MAX_CTAS || a->n <= 0 || a->epoch == 0) return -1;
+  if ((reinterpret_cast<unsigned long long>(a->grad) & 15ull) || (a->send_off & 15) || (a->recv_off & 15) || (a->flags_off & 3)) return -2;
+  long long slice = (a->n + a->world - 1) / a->world;
+  slice = (slice + 7) / 8 * 8;
+  long long chunk = (slice + a->ctas - 1) / a->ctas;
+  chunk = (chunk + 7) / 8 * 8;
+  a->status = sb_status_ptr();
+  if (a->status == nullptr) return -3;
+  a->slice = slice;
+  a->chunk = chunk;
+  const long long padded = slice * a->world;
+  __nv_bfloat16* send = reinterpret_cast<__nv_bfloat16*>((char*)my_base + a->send_off);
+  const __nv_bfloat16* recv = reinterpret_cast<const __nv_bfloat16*>((char*)my_base + a->recv_off);
+  long long blocks = ((padded >> 3) + 255) / 256;
+  const long long cap = (long long)sb_num_sms() * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  peer_pack_kernel<<<(int)blocks, 256, 0, stream>>>(a->grad, send, a->n, padded, a->scale);
+  peer_allreduce_kernel<false><<<a->ctas, 512, 0, stream>>>(*a);
+  peer_unpack_kernel<<<(int)blocks, 256, 0, stream>>>(recv, a->grad, a->n);
   return (int)cudaGetLastError();
 }
 

@@ -78,6 +78,10 @@ class PeerAllReduce:
         self.rank, self.world = self.buf.rank, self.buf.world
         self.ctas = int(ctas or os.environ.get("SPEECH_B200_PEER_CTAS", 12))
         self.epoch = 0
+        # the cast into the send region and the unpack from the receive region as wide kernels of their own (default), or inside
+        # the few-block peer kernel
+        self.split_local = os.environ.get("SPEECH_B200_PEER_SPLIT", "1") != "0"
+        self.lib.sb_peer_allreduce_split.restype = ctypes.c_int
 
     def __call__(self, flat: torch.Tensor, scale: float = 1.0) -> None:
         """In-place ``flat <- bf16_round(sum_over_ranks(bf16(flat * scale)))`` on the current stream."""
@@ -89,8 +93,12 @@ class PeerAllReduce:
         self.epoch += 1
         a = SbPeerArgs(flat.data_ptr(), self.buf.ptrs_dev, 0, self.send_off, self.recv_off, n, 0, 0, self.rank, self.world,
                        self.ctas, self.epoch, float(scale), None)
-        rc = self.lib.sb_peer_allreduce(ctypes.byref(a), self.native._stream())
-        self.native.launch_count += 1
+        if self.split_local:
+            rc = self.lib.sb_peer_allreduce_split(ctypes.byref(a), ctypes.c_void_p(self.buf.tensor.data_ptr()), self.native._stream())
+            self.native.launch_count += 3
+        else:
+            rc = self.lib.sb_peer_allreduce(ctypes.byref(a), self.native._stream())
+            self.native.launch_count += 1
         if rc != 0:
             raise RuntimeError(f"sb_peer_allreduce failed with code {rc}")
 
