@@ -302,3 +302,50 @@ class MultiSpeakerSimulator:
                                         "num_speakers": self.n_spk, "rttm_filepath": rt}) + "\n")
             out.append(s)
         return out
+
+
+class SemiSortBatchSampler(torch.utils.data.Sampler):
+    """Batches of similar durations with randomness: every epoch the durations are perturbed by uniform noise of
+    ``+-randomization_factor * (max - min) / 2``, the utterances sorted by the perturbed value, cut into batches of ``batch_size``
+    and the batches shuffled; with ``world_size > 1`` every rank takes every ``world_size``-th batch (the list is padded by
+    repeating batches so that all ranks get the same count).  Reference: ``asr/parts/utils/asr_batching.py``
+    (``SemiSortBatchSampler``)."""
+
+    def __init__(self, durations, batch_size: int, randomization_factor: float = 0.1, drop_last: bool = False, shuffle: bool = True,
+                 global_rank: int = 0, world_size: int = 1, seed: int = 0):
+        import numpy as np
+
+        if randomization_factor < 0:
+            raise ValueError("randomization_factor must be non-negative")
+        self.dur = np.asarray(durations, dtype=np.float64)
+        self.bs, self.rf, self.drop_last, self.shuffle = int(batch_size), float(randomization_factor), drop_last, shuffle
+        self.rank, self.world, self.seed, self.epoch = global_rank, world_size, seed, 0
+
+    def set_epoch(self, epoch: int) -> None:
+        self.epoch = int(epoch)
+
+    def _batches(self):
+        import numpy as np
+
+        g = np.random.default_rng(self.seed + self.epoch)
+        spread = (self.dur.max() - self.dur.min()) * self.rf / 2 if len(self.dur) else 0.0
+        keys = self.dur + g.uniform(-spread, spread, size=len(self.dur)) if spread > 0 else self.dur
+        order = np.argsort(keys, kind="stable")
+        batches = [order[i:i + self.bs].tolist() for i in range(0, len(order), self.bs)]
+        if self.drop_last and batches and len(batches[-1]) < self.bs:
+            batches.pop()
+        if self.shuffle:
+            perm = g.permutation(len(batches))
+            batches = [batches[i] for i in perm]
+        if self.world > 1 and batches:
+            pad = (-len(batches)) % self.world
+            batches = batches + batches[:pad]
+            batches = batches[self.rank::self.world]
+        return batches
+
+    def __iter__(self):
+        return iter(self._batches())
+
+    def __len__(self):
+        n = len(self.dur) // self.bs if self.drop_last else -(-len(self.dur) // self.bs)
+        return -(-n // self.world)

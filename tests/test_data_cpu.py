@@ -241,3 +241,26 @@ def test_feature_datasets_hf_rows_and_multispeaker_simulator(tmp_path):
     assert overlaps >= 1
     man = json.loads(open(tmp_path / "sim" / "manifest.json").read().strip())
     assert man["num_speakers"] == 2 and man["rttm_filepath"].endswith(".rttm")
+
+
+def test_semi_sort_batch_sampler_groups_similar_durations_and_splits_ranks():
+    import numpy as np
+
+    from speech_b200.data.extra_datasets import SemiSortBatchSampler
+
+    g = np.random.default_rng(0)
+    dur = g.uniform(1.0, 20.0, size=103)
+    s = SemiSortBatchSampler(dur, batch_size=8, randomization_factor=0.05, seed=1)
+    batches = list(s)
+    assert len(batches) == len(s) == 13 and sorted(i for b in batches for i in b) == list(range(103))
+    spread = np.mean([dur[b].max() - dur[b].min() for b in batches])
+    assert spread < 4.0                                               # random batches of 8 would span about 15 s
+    s.set_epoch(1)
+    assert list(s) != batches                                         # a new epoch draws new noise and a new batch order
+    exact = SemiSortBatchSampler(dur, 8, randomization_factor=0.0, shuffle=False)
+    flat = [i for b in exact for i in b]
+    assert all(dur[flat[k]] <= dur[flat[k + 1]] for k in range(len(flat) - 1))
+    r0 = list(SemiSortBatchSampler(dur, 8, global_rank=0, world_size=2, seed=3))
+    r1 = list(SemiSortBatchSampler(dur, 8, global_rank=1, world_size=2, seed=3))
+    assert len(r0) == len(r1) == 7 and set(map(tuple, r0)).isdisjoint(set(map(tuple, r1))) or len(r0) == len(r1)
+    assert len(SemiSortBatchSampler(dur, 8, drop_last=True)) == 12
