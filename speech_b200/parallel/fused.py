@@ -9,9 +9,11 @@ accumulators.  The ranks synchronise inside the kernels: the GEMM's last block p
 system-scope fences, and the consumer kernel that converts (and clears) the accumulator waits for all ranks' flags.
 
 ``AllGatherGemm`` — the column-parallel linear layer fed by sequence-parallel activations (all-gather, then QKV / up projection)
-as ONE GEMM launch: every rank keeps its row shard of the activations in a symmetric buffer, and the GEMM's TMA producer loads
-each A tile straight from the memory of the rank that owns those rows (one tensor map per rank, plain tiled loads, no multicast).
-The gathered activation matrix never exists in memory.
+as ONE GEMM launch: every rank keeps its row shard of the activations in a symmetric buffer.  By default the kernel's own
+blocks copy each remote shard once into local memory (the epilogue warps, with plain peer loads, while the tensor pipe multiplies
+this rank's own rows, which the tile order puts first); the TMA producer then reads remote rows from the local copy.  Without
+staging the producer loads each A tile straight from the memory of the rank that owns those rows (one tensor map per rank, plain
+tiled loads, no multicast), which sends a shard over NVLink once per column tile: only worthwhile for narrow outputs.
 
 The reference reaches the same results with a cuBLAS GEMM preceded by an NCCL all-gather / followed by an NCCL reduce-scatter
 (``speechlm2/parts/parallel.py`` tensor-parallel plans over ``torch.distributed.tensor``).
