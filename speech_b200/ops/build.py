@@ -31,25 +31,35 @@ def _nvcc() -> str:
     return cand
 
 
+def _variant():
+    """Optional diagnostic variant: ``SPEECH_B200_BUILD_DEFS="-DSB_GEMM_DIAG"`` builds ``libspeech_b200_diag.so`` in its own
+    object directory, next to the product library (which never carries diagnostic code)."""
+    defs = os.environ.get("SPEECH_B200_BUILD_DEFS", "").split()
+    if not defs:
+        return [], BUILD, LIB
+    return defs, BUILD + "_diag", os.path.join(HERE, "libspeech_b200_diag.so")
+
+
 def _digest(path: str) -> str:
     h = hashlib.sha1()
     for p in [path] + sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))):
         with open(p, "rb") as f:
             h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + _variant()[0]).encode())
     return h.hexdigest()
 
 
 def _compile(src: str, verbose: bool) -> str:
     name = os.path.splitext(os.path.basename(src))[0]
-    obj = os.path.join(BUILD, name + ".o")
+    defs, bdir, _ = _variant()
+    obj = os.path.join(bdir, name + ".o")
     stamp = obj + ".sha1"
     dg = _digest(src)
     if os.path.exists(obj) and os.path.exists(stamp) and open(stamp).read() == dg:
         return obj
-    cmd = [_nvcc()] + NVCC_FLAGS + ["-I", CSRC, "-c", src, "-o", obj]
+    cmd = [_nvcc()] + NVCC_FLAGS + defs + ["-I", CSRC, "-c", src, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
-    log = os.path.join(BUILD, name + ".log")
+    log = os.path.join(bdir, name + ".log")
     with open(log, "w") as f:
         f.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
     if r.returncode != 0:
@@ -64,20 +74,21 @@ def _compile(src: str, verbose: bool) -> str:
 
 
 def build(verbose: bool = False, force: bool = False) -> str:
-    os.makedirs(BUILD, exist_ok=True)
+    _, bdir, lib = _variant()
+    os.makedirs(bdir, exist_ok=True)
     if force:
-        for f in os.listdir(BUILD):
-            os.remove(os.path.join(BUILD, f))
+        for f in os.listdir(bdir):
+            os.remove(os.path.join(bdir, f))
     srcs: List[str] = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(lambda s: _compile(s, verbose), srcs))
     newest = max(os.path.getmtime(o) for o in objs)
-    if not os.path.exists(LIB) or os.path.getmtime(LIB) < newest:
-        cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-lcudart", "-Xlinker", "-z,noexecstack"]
+    if not os.path.exists(lib) or os.path.getmtime(lib) < newest:
+        cmd = [_nvcc(), "-shared", "-o", lib] + objs + ["-lcudart", "-Xlinker", "-z,noexecstack"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stderr[-4000:]}")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":

@@ -23,6 +23,13 @@ enum SbStatus : int {
 #define SB_WAIT_CYCLES 2000000000ll
 #endif
 
+// The wait limit can be changed at run time (sb_set_wait_cycles in status.cu): ints 4-5 of the status array hold it as one
+// 64-bit cycle count, 0 meaning the compile-time default.  Kernels read it only on the slow path of a wait.
+__device__ __forceinline__ long long sb_wait_cycles(const int* status) {
+  const long long v = *reinterpret_cast<const volatile long long*>(status + 4);
+  return v > 0 ? v : SB_WAIT_CYCLES;
+}
+
 // The status word lives in status.cu; host code fetches its device address once per device with
 // sb_status_ptr() and passes it to every kernel that can wait.
 SB_API int* sb_status_ptr();

@@ -24,7 +24,7 @@ __global__ void wait_reduce_out_kernel(float* __restrict__ acc, void* __restrict
     const long long t0 = clock64();
     unsigned int probes = 0;
     while ((int)(ld_acquire_sys(f) - epoch) < 0) {
-      if ((++probes & 15u) == 0 && (clock64() - t0 > SB_WAIT_CYCLES || sb_failed(status))) {
+      if ((++probes & 15u) == 0 && (clock64() - t0 > sb_wait_cycles(status) || sb_failed(status))) {
         sb_set_status(status, SB_TIMEOUT_PEER_FLAG, (int)threadIdx.x);
         break;
       }

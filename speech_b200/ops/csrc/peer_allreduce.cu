@@ -15,7 +15,7 @@
 // CTA b only ever waits for CTA b of the peers, so no CTA depends on another CTA of its own GPU and the grid needs no
 // co-residency.  Flags only grow (epoch = launch counter, identical on all ranks), so they are never reset; a rank that is
 // one bucket ahead cannot touch a buffer a slower rank still uses because each phase is gated by the slower rank's flag.
-// Every wait is bounded: after SB_WAIT_CYCLES the CTA records SB_TIMEOUT_PEER_FLAG in the status word and returns
+// Every wait is bounded: after the wait limit (common.cuh) the CTA records SB_TIMEOUT_PEER_FLAG in the status word and returns
 // without touching peer memory again.
 #include "common.cuh"
 
@@ -49,12 +49,12 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
 }
 
 // Thread q < world waits for peer q's flag; everyone gets the verdict.  Returns false after a timeout.
-__device__ bool wait_peers(const unsigned int* my_flags, int b, int world, int rank, unsigned int want, int* s_fail) {
+__device__ bool wait_peers(const unsigned int* my_flags, int b, int world, int rank, unsigned int want, int* s_fail, const int* status) {
   if (threadIdx.x < world && threadIdx.x != rank) {
     const unsigned int* f = my_flags + (long long)b * SB_PEER_MAX_WORLD + threadIdx.x;
     const long long t0 = clock64();
     while ((int)(ld_acquire_sys(f) - want) < 0) {
-      if (clock64() - t0 > SB_WAIT_CYCLES) {
+      if (clock64() - t0 > sb_wait_cycles(status)) {
         atomicExch(s_fail, 1);
         break;
       }
@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(512) peer_allreduce_kernel(SbPeerArgs a) {
     }
   }
   signal_peers(a, b, 2u * a.epoch + 1u);
-  if (!wait_peers(my_flags, b, a.world, a.rank, 2u * a.epoch + 1u, &s_fail)) {
+  if (!wait_peers(my_flags, b, a.world, a.rank, 2u * a.epoch + 1u, &s_fail, a.status)) {
     if (threadIdx.x == 0) sb_set_status(a.status, SB_TIMEOUT_PEER_FLAG, 1);
     return;
   }
@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(512) peer_allreduce_kernel(SbPeerArgs a) {
     }
   }
   signal_peers(a, b, 2u * a.epoch + 2u);
-  if (!wait_peers(my_flags, b, a.world, a.rank, 2u * a.epoch + 2u, &s_fail)) {
+  if (!wait_peers(my_flags, b, a.world, a.rank, 2u * a.epoch + 2u, &s_fail, a.status)) {
     if (threadIdx.x == 0) sb_set_status(a.status, SB_TIMEOUT_PEER_FLAG, 2);
     return;
   }

@@ -8,7 +8,7 @@
 // Call number `epoch` (1, 2, ... identical on all ranks) uses half `epoch & 1` of the flags and slots.  A rank can only start
 // call e+2 after it has seen every peer's flag of call e+1, and a peer raises that flag only after it finished reading the
 // slots of call e, so two halves are enough.  Plain P2P stores and loads only (no TMA, no multicast).  The wait is bounded:
-// after SB_WAIT_CYCLES the kernel records SB_TIMEOUT_PEER_FLAG in the status word and leaves `data` untouched.
+// after the wait limit (common.cuh) the kernel records SB_TIMEOUT_PEER_FLAG in the status word and leaves `data` untouched.
 #include "common.cuh"
 
 #include "peer_small.h"
@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(256) peer_small_allreduce_kernel(SbPeerSmallAr
                             threadIdx.x;
     const long long t0 = clock64();
     while ((int)(ld_acquire_sys_u32(f) - a.epoch) < 0) {
-      if (clock64() - t0 > SB_WAIT_CYCLES) {
+      if (clock64() - t0 > sb_wait_cycles(a.status)) {
         atomicExch(&s_fail, 1);
         break;
       }

@@ -3,7 +3,8 @@
 #include <stdio.h>
 
 #define SB_MAX_DEVICES 16
-static __device__ int g_sb_status[4];
+// ints 0-3: status word (code, block, detail, spare); ints 4-5: run-time wait limit in cycles (0 = SB_WAIT_CYCLES)
+static __device__ __align__(16) int g_sb_status[8];
 static int* g_status_ptr[SB_MAX_DEVICES] = {nullptr};
 
 SB_API int* sb_status_ptr() {
@@ -30,6 +31,17 @@ SB_API int sb_read_status(int* out4, int clear, cudaStream_t stream) {
     if (e != cudaSuccess) return (int)e;
   }
   return 0;
+}
+
+// Sets the limit of every bounded in-kernel wait on the current device, in SM clock cycles (0 restores the compile-time
+// default of about a second).  Training raises it so that ordinary skew between ranks (a rank that validates or logs longer)
+// does not trip it; tests lower it to make a wait run out quickly.  Synchronises the device.
+SB_API int sb_set_wait_cycles(long long cycles) {
+  int* p = sb_status_ptr();
+  if (!p) return -1;
+  if (cycles < 0) cycles = 0;
+  cudaError_t e = cudaMemcpy(p + 4, &cycles, sizeof(long long), cudaMemcpyHostToDevice);
+  return (int)e;
 }
 
 SB_API const char* sb_status_string(int code) {

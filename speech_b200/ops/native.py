@@ -19,7 +19,7 @@ from typing import Any, List, Optional, Sequence, Tuple
 import torch
 
 _LIB = None
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libspeech_b200.so")
+_LIB_PATH = os.environ.get("SPEECH_B200_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "libspeech_b200.so")
 launch_count = 0  # number of kernel-launching library calls (benchmarks report it)
 _SMALL_M_SPLITK = os.environ.get("SPEECH_B200_SMALL_M_SPLITK", "1") != "0"
 
