@@ -523,6 +523,39 @@ class ModelPT(nn.Module, Typing, Serialization):
     def get_test_dataloader_prefix(self, dataloader_idx: int = 0) -> str:
         return (self._test_names[dataloader_idx] + "_") if self._test_names else ""
 
+    @staticmethod
+    def reduce_sums(values, device=None):
+        """Sum a short list of python numbers over all ranks (identity without a process group).  Metrics that are ratios of
+        sums (WER = errors / words, mean loss = sum / count) are formed from the reduced numerators and denominators, as the
+        reference's torchmetrics-based WER does with ``dist_reduce_fx='sum'`` (``collections/asr/metrics/wer.py``)."""
+        import torch.distributed as dist
+
+        vals = [float(v) for v in values]
+        if not (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1):
+            return vals
+        on_gpu = dist.get_backend() == "nccl"
+        t = torch.tensor(vals, dtype=torch.float64, device=device if (on_gpu and device is not None) else ("cuda" if on_gpu else "cpu"))
+        dist.all_reduce(t)
+        return [float(x) for x in t.cpu()]
+
+    def _sync_logged(self, log: Dict[str, Any]) -> Dict[str, Any]:
+        """Mean over ranks of every scalar about to be logged at an epoch end (``sync_dist=True`` of the reference,
+        ``core/classes/modelPT.py:991``), so that ``trainer.callback_metrics``, and with it every checkpoint and early-stopping
+        decision, is identical on all ranks."""
+        import torch.distributed as dist
+
+        if not (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1):
+            return log
+        keys = sorted(k for k, v in log.items() if isinstance(v, (int, float)) or (torch.is_tensor(v) and v.numel() == 1))
+        if not keys:
+            return log
+        world = dist.get_world_size()
+        red = self.reduce_sums([float(log[k]) for k in keys], getattr(self, "device", None))
+        out = dict(log)
+        for k, v in zip(keys, red):
+            out[k] = torch.tensor(v / world, dtype=torch.float32)
+        return out
+
     def _epoch_end(self, outputs, multi_fn, prefix_fn, which: str):
         if not outputs:
             return {}
@@ -530,6 +563,8 @@ class ModelPT(nn.Module, Typing, Serialization):
         if single:
             out = multi_fn(outputs, 0) or {}
             log = out.pop("log", {}) if isinstance(out, dict) else {}
+            log = self._sync_logged(log)
+            out = self._sync_logged(out) if isinstance(out, dict) else out
             self.log_dict(log)
             for k, v in (out.items() if isinstance(out, dict) else []):
                 self.log(k, v)
@@ -546,6 +581,7 @@ class ModelPT(nn.Module, Typing, Serialization):
                 if idx == primary and k in (f"{which}_loss", f"{which}_wer"):
                     merged[k] = v
                 merged[prefix + k] = v
+        merged = self._sync_logged(merged)
         self.log_dict(merged)
         return merged
 

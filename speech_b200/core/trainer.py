@@ -381,11 +381,13 @@ class Trainer:
         ctx = self.grad_sync.no_sync() if (self.grad_sync is not None and not sync_now) else contextlib.nullcontext()
         with ctx:
             (loss / accum if accum > 1 else loss).backward()
+        if last_micro and self.grad_sync is not None:
+            # the bucket reductions launched during backward are joined BEFORE any hook looks at (or zeroes) the gradients
+            self.grad_sync.finish_step()
         model.on_after_backward()
         self._call("on_after_backward")
         if last_micro:
-            if self.grad_sync is not None:
-                self.grad_sync.finish_step()
+            self._check_kernel_status()
             for opt in self.optimizers:
                 self._clip_gradients(opt)
                 self._call("on_before_optimizer_step", opt)
@@ -401,6 +403,26 @@ class Trainer:
         self._call("on_train_batch_end", out, batch, batch_idx)
         if last_micro and (self.global_step % max(1, self.log_every_n_steps) == 0 or self.global_step == 1):
             self._flush_logs(self.global_step)
+
+    def _check_kernel_status(self):
+        """Fail the run when a kernel of an earlier step gave up a bounded wait (a peer rank that never arrived).
+
+        The kernels themselves keep such a step harmless: the update kernel and the gradient unpack return without writing once
+        the device status word is set.  Here the word of the PREVIOUS step is read (an asynchronous copy into pinned memory
+        made at that step, so this never waits for the GPU's current work) and turned into an exception on every rank that
+        sees it; ranks that did not time out themselves run into the missing rank at their next bucket and fail the same way."""
+        if self.device.type != "cuda" or self.grad_sync is None:
+            return
+        from ..ops import native
+
+        st = getattr(self, "_status_probe", None)
+        if st is None:
+            st = self._status_probe = native.StatusProbe(self.device)
+        code = st.poll()
+        if code:
+            raise RuntimeError(f"a device kernel gave up a bounded wait in an earlier step: {native.status_message(code)}; "
+                               "the optimizer update of that step was skipped on this rank")
+        st.record()
 
     def _clip_gradients(self, opt):
         if self.gradient_clip_val <= 0 or getattr(opt, "max_grad_norm", 0.0) > 0:

@@ -49,10 +49,13 @@ class ASRModel(ModelPT):
     def multi_validation_epoch_end(self, outputs, dataloader_idx: int = 0):
         if not outputs:
             return {}
-        val_loss_mean = torch.stack([x["val_loss"] for x in outputs if "val_loss" in x]).mean() \
-            if any("val_loss" in x for x in outputs) else None
+        # validation data is sharded over ranks: numerators and denominators are summed over all of them first
+        losses = [x["val_loss"] for x in outputs if "val_loss" in x]
+        loss_sum = float(torch.stack([l.detach().float() for l in losses]).sum()) if losses else 0.0
         num = sum(float(x["val_wer_num"]) for x in outputs if "val_wer_num" in x)
         den = sum(float(x["val_wer_denom"]) for x in outputs if "val_wer_denom" in x)
+        loss_sum, loss_cnt, num, den = self.reduce_sums([loss_sum, float(len(losses)), num, den], self.device)
+        val_loss_mean = torch.tensor(loss_sum / loss_cnt) if loss_cnt > 0 else None
         log = {}
         if val_loss_mean is not None:
             log["val_loss"] = val_loss_mean

@@ -43,19 +43,31 @@ __device__ __forceinline__ void sb_set_status(int* status, int code, int detail)
 }
 __device__ __forceinline__ bool sb_failed(const int* status) { return *((volatile const int*)status) != 0; }
 
-// Stateless dropout mask: element `idx` of the tensor drawn with `seed` is kept iff the hash is >= thresh
-// (thresh = p * 2^32).  Forward kernels and the backward kernels that rebuild the mask call this with the same
-// (seed, row * N + col), so no mask tensor is ever stored.
-__device__ __forceinline__ bool sb_dropout_keep(unsigned long long seed, unsigned long long idx, unsigned int thresh) {
-  unsigned int h = (unsigned int)idx * 0x9E3779B1u ^ (unsigned int)(idx >> 32) * 0x85EBCA77u ^ (unsigned int)seed;
+// Stateless dropout mask.  One 32-bit hash serves FOUR consecutive elements: element `idx` of the tensor drawn with `seed` takes
+// byte (idx & 3) of hash(seed, idx >> 2) and is kept iff that byte is >= thresh, an 8-bit threshold (p * 256, rounded; the
+// effective drop probability is thresh / 256 and the keep scale 256 / (256 - thresh)).  Forward kernels and the backward kernels
+// that rebuild the mask call these with the same (seed, row * N + col), so no mask tensor is ever stored; kernels that own four
+// aligned elements call sb_dropout_hash4 once and test the bytes.
+__device__ __forceinline__ unsigned int sb_dropout_hash4(unsigned long long seed, unsigned long long group) {
+  unsigned int h = (unsigned int)group * 0x9E3779B1u ^ (unsigned int)(group >> 32) * 0x85EBCA77u ^ (unsigned int)seed;
   h ^= h >> 16; h *= 0x7FEB352Du; h ^= h >> 15; h *= 0x846CA68Bu; h ^= h >> 16;
   h ^= (unsigned int)(seed >> 32); h *= 0x9E3779B1u; h ^= h >> 15; h *= 0x2C1B3C6Du; h ^= h >> 12;
-  return h >= thresh;
+  return h;
+}
+__device__ __forceinline__ bool sb_dropout_keep_in(unsigned int h, int k, unsigned int thresh) {
+  return ((h >> (8 * k)) & 255u) >= thresh;
+}
+__device__ __forceinline__ bool sb_dropout_keep(unsigned long long seed, unsigned long long idx, unsigned int thresh) {
+  return sb_dropout_keep_in(sb_dropout_hash4(seed, idx >> 2), (int)(idx & 3ull), thresh);
 }
 static inline unsigned int sb_dropout_threshold(float p) {
   if (p <= 0.f) return 0u;
-  double t = (double)p * 4294967296.0;
-  return t >= 4294967295.0 ? 4294967295u : (unsigned int)t;
+  const unsigned int t = (unsigned int)(p * 256.f + 0.5f);
+  return t > 255u ? 255u : t;
+}
+static inline float sb_dropout_scale(float p) {
+  const unsigned int t = sb_dropout_threshold(p);
+  return t ? 256.f / (256.f - (float)t) : 1.f;
 }
 
 // rcp.approx instead of an IEEE division: the full-precision divide costs more than the rest of an epilogue put together

@@ -273,7 +273,12 @@ __global__ void __launch_bounds__(256) layernorm_bwd_reg_kernel(
 // scalars[1] = gradient multiplier (clip coefficient x loss scale), read from device memory.
 __global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
                              float* __restrict__ v, __nv_bfloat16* __restrict__ lowp, long long n, float lr, float beta1,
-                             float beta2, float eps, float wd, float bc1, float rsqrt_bc2, const float* __restrict__ scalars) {
+                             float beta2, float eps, float wd, float bc1, float rsqrt_bc2, const float* __restrict__ scalars,
+                             const int* __restrict__ status) {
+  // The update is skipped as a whole when the gradient norm of this step was not finite (scalars[2], set by the clip kernel
+  // after the gradients were reduced over ranks, hence identical on all of them) or when a kernel of this step gave up a wait
+  // (status word): the gradients may then be incomplete.  The host learns of either through its own reads.
+  if ((scalars && scalars[2] != 0.f) || (status && *((volatile const int*)status) != 0)) return;
   const float gs = scalars ? scalars[1] : 1.f;
   const long long stride = (long long)gridDim.x * blockDim.x * 4;
   for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
@@ -339,7 +344,7 @@ __global__ void clip_coef_kernel(const float* __restrict__ partial, int nparts, 
     scalars[0] = norm;
     float c = max_norm / (norm + 1e-6f);
     scalars[1] = grad_scale * (c < 1.f ? c : 1.f);
-    if (!isfinite(norm)) scalars[2] = 1.f;
+    scalars[2] = isfinite(norm) ? 0.f : 1.f;
   }
 }
 
@@ -445,7 +450,7 @@ SB_API int sb_adamw(float* p, const float* g, float* m, float* v, void* lowp, lo
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   adamw_kernel<<<(int)blocks, threads, 0, stream>>>(p, g, m, v, (__nv_bfloat16*)lowp, n, lr, beta1, beta2, eps, wd, bc1,
-                                                   1.f / sqrtf(bc2), scalars);
+                                                   1.f / sqrtf(bc2), scalars, sb_status_ptr());
   return (int)cudaGetLastError();
 }
 
@@ -497,6 +502,9 @@ __global__ void scale_dact_kernel(const __nv_bfloat16* __restrict__ dy, long lon
     const __nv_bfloat162* hg = reinterpret_cast<const __nv_bfloat162*>(&rg);
     const __nv_bfloat162* hz = reinterpret_cast<const __nv_bfloat162*>(&rz);
     __align__(16) __nv_bfloat162 o[4];
+    // N is a multiple of 8 and c of 8: the eight elements are two aligned groups of four, one hash each
+    const unsigned long long grp = ((unsigned long long)r * N + c) >> 2;
+    const unsigned int h0 = thresh ? sb_dropout_hash4(seed, grp) : 0u, h1 = thresh ? sb_dropout_hash4(seed, grp + 1) : 0u;
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       float2 g = __bfloat1622float2(hg[u]), zz = __bfloat1622float2(hz[u]);
@@ -506,9 +514,9 @@ __global__ void scale_dact_kernel(const __nv_bfloat16* __restrict__ dy, long lon
       else if (act == 3) { d0 = sb_dgelu(zz.x); d1 = sb_dgelu(zz.y); }
       else { d0 = d1 = 1.f; }
       if (thresh) {
-        const unsigned long long idx = (unsigned long long)r * N + c + 2 * u;
-        d0 = sb_dropout_keep(seed, idx, thresh) ? d0 * drop_scale : 0.f;
-        d1 = sb_dropout_keep(seed, idx + 1, thresh) ? d1 * drop_scale : 0.f;
+        const unsigned int h = u < 2 ? h0 : h1;
+        d0 = sb_dropout_keep_in(h, (2 * u) & 3, thresh) ? d0 * drop_scale : 0.f;
+        d1 = sb_dropout_keep_in(h, (2 * u + 1) & 3, thresh) ? d1 * drop_scale : 0.f;
       }
       o[u] = __floats2bfloat162_rn(alpha * g.x * d0, alpha * g.y * d1);
     }
@@ -535,6 +543,6 @@ SB_API int sb_scale_dact_dropout(const void* dy, long long ld_dy, const void* z,
   if (blocks > cap) blocks = cap;
   scale_dact_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)dy, ld_dy, (const __nv_bfloat16*)z,
                                                     (__nv_bfloat16*)dz, rows, N, act, alpha, sb_dropout_threshold(drop_p),
-                                                    drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f, seed);
+                                                    sb_dropout_scale(drop_p), seed);
   return (int)cudaGetLastError();
 }

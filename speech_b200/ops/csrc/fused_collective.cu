@@ -31,6 +31,9 @@ __global__ void wait_reduce_out_kernel(float* __restrict__ acc, void* __restrict
     }
   }
   __syncthreads();
+  // After a give-up (here or in an earlier kernel of the step) the accumulator may still receive late contributions: it is
+  // neither converted nor cleared, the output keeps its old contents and the host reads the status word.
+  if (sb_failed(status)) return;
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     float4* src = reinterpret_cast<float4*>(acc) + i;

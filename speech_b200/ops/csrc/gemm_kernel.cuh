@@ -64,7 +64,7 @@ struct EpilogueArgs {
   int tma_p;     // D_pre is written through its tensor map
   int tma_ragged_d, tma_ragged_p;  // the last, partial column block may also go through the map: its valid part is whole 16-byte
                                    // units (the copy engine clips columns in units of 16 bytes, not of elements)
-  unsigned int drop_thresh;  // 0 = no dropout; otherwise keep iff sb_dropout_keep(seed, batch*M*N + m*N + n, thresh)
+  unsigned int drop_thresh;  // 0 = no dropout; otherwise the 8-bit threshold of sb_dropout_keep(seed, batch*M*N + m*N + n, thresh)
   float drop_scale;          // 1 / (1 - p)
   unsigned long long drop_seed;
   // GEMM + reduce-scatter: output row m belongs to rank m / peer_rows and is ADDED (fp32 reductions over NVLink peer stores)
@@ -399,6 +399,9 @@ __device__ __noinline__ float ld_bias_guard(const float* bf, const __nv_bfloat16
 }
 __device__ __noinline__ float ld_bf16_guard(const __nv_bfloat16* p, int j, int n) { return j < n ? __bfloat162float(p[j]) : 0.f; }
 __device__ __noinline__ float gelu_call(float x) { return sb_gelu(x); }
+__device__ __noinline__ float drop_call(float x, unsigned long long seed, unsigned long long idx, unsigned int thresh, float scale) {
+  return sb_dropout_keep(seed, idx, thresh) ? x * scale : 0.f;
+}
 __device__ __noinline__ float dact_call(float g, float z, int dact) { return apply_dact(g, z, dact); }
 
 // Epilogue classes: the kernel is compiled once per class and carries only that class's code.
@@ -579,6 +582,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
           ready = __shfl_sync(0xffffffffu, ready, 0);
+          // after a give-up no tile is loaded from a shard that may not be in place: the roles end through their bounded waits
+          if (__any_sync(0xffffffffu, sb_failed(p.status) ? 1 : 0)) { ok = false; break; }
         }
         for (int n = kb_end - kb_begin; n > 0; --n) {
 #ifdef SB_GEMM_DIAG
@@ -860,8 +865,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         if (EPI != EPI_LEAN && e.drop_thresh) {
           const unsigned long long base = ((unsigned long long)batch * p.M + row) * (unsigned long long)p.N + col0;
+          if ((p.N & 3) == 0) {
+            // rows start on a multiple of four elements: one hash per group of four columns
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = sb_dropout_keep(e.drop_seed, base + j, e.drop_thresh) ? v[j] * e.drop_scale : 0.f;
+            for (int g = 0; g < 8; ++g) {
+              const unsigned int h = sb_dropout_hash4(e.drop_seed, (base >> 2) + g);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) v[4 * g + u] = sb_dropout_keep_in(h, u, e.drop_thresh) ? v[4 * g + u] * e.drop_scale : 0.f;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = drop_call(v[j], e.drop_seed, base + j, e.drop_thresh, e.drop_scale);
+          }
         }
         if (e.alpha != 1.f) {
 #pragma unroll
@@ -1029,20 +1044,32 @@ int launch_gemm_variant(int variant, int grid, bool pair, cudaStream_t stream, c
     if (ae != cudaSuccess) return (int)ae;
     attr_set[variant] = true;
   }
-  if (pair) {
+  // Staged all-gather + GEMM: tiles of remote rows wait until EVERY block has copied its slice, a grid-wide dependency.  A
+  // cooperative launch starts the grid only when all of its blocks can be resident together, whatever else runs on the device.
+  const bool coop = p.stage_bytes > 0;
+  if (pair || coop) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(grid, 1, 1);
     cfg.blockDim = dim3(NUM_THREADS, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (pair) {
+      attr[na].id = cudaLaunchAttributeClusterDimension;
+      attr[na].val.clusterDim.x = 2;
+      attr[na].val.clusterDim.y = 1;
+      attr[na].val.clusterDim.z = 1;
+      ++na;
+    }
+    if (coop) {
+      attr[na].id = cudaLaunchAttributeCooperative;
+      attr[na].val.cooperative = 1;
+      ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = na;
     return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, p, pm, td, tp);
   }
   kern<<<grid, NUM_THREADS, smem, stream>>>(ta, tb, p, pm, td, tp);

@@ -286,7 +286,7 @@ SB_API int sb_gemm_bf16(const SbGemmArgs* a, cudaStream_t stream) {
   if (a->D_pre && !a->d_is_f32 && make_out_map(&tp, a->D_pre, false, a->N, a->M, a->ldp, a->batch0, ob1, a->p_bs0, a->p_bs1) == 0)
     e.tma_p = 1;
   e.drop_thresh = sb_dropout_threshold(a->drop_p);
-  e.drop_scale = a->drop_p > 0.f ? 1.f / (1.f - a->drop_p) : 1.f;
+  e.drop_scale = sb_dropout_scale(a->drop_p);
   e.drop_seed = a->drop_seed;
   int grid = sb_num_sms() - sb_reserved_sms();
   if (grid < 8) grid = 8;

@@ -240,7 +240,10 @@ __global__ void peer_pack_kernel(const float* __restrict__ grad, __nv_bfloat16* 
 }
 
 // bf16 receive region -> fp32 gradients
-__global__ void peer_unpack_kernel(const __nv_bfloat16* __restrict__ recv, float* __restrict__ grad, long long n) {
+__global__ void peer_unpack_kernel(const __nv_bfloat16* __restrict__ recv, float* __restrict__ grad, long long n,
+                                   const int* __restrict__ status) {
+  // after a give-up of the peer kernel the receive region holds an earlier bucket: leave the gradients alone
+  if (sb_failed(status)) return;
   const long long n8 = (n + 7) >> 3;
   for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < n8; g += (long long)gridDim.x * blockDim.x) {
     const long long e = g << 3;
@@ -304,7 +307,7 @@ SB_API int sb_peer_allreduce_split(SbPeerArgs* a, void* my_base, cudaStream_t st
   if (blocks < 1) blocks = 1;
   peer_pack_kernel<<<(int)blocks, 256, 0, stream>>>(a->grad, send, a->n, padded, a->scale);
   peer_allreduce_kernel<false><<<a->ctas, 512, 0, stream>>>(*a);
-  peer_unpack_kernel<<<(int)blocks, 256, 0, stream>>>(recv, a->grad, a->n);
+  peer_unpack_kernel<<<(int)blocks, 256, 0, stream>>>(recv, a->grad, a->n, a->status);
   return (int)cudaGetLastError();
 }
 

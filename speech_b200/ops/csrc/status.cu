@@ -44,6 +44,14 @@ SB_API int sb_set_wait_cycles(long long cycles) {
   return (int)e;
 }
 
+// Enqueues a copy of the 4-int status word into pinned host memory on `stream` (no synchronisation); the caller records an
+// event behind it and reads `host4` once the event has completed.
+SB_API int sb_status_copy_async(int* host4, cudaStream_t stream) {
+  int* p = sb_status_ptr();
+  if (!p || !host4) return -1;
+  return (int)cudaMemcpyAsync(host4, p, 4 * sizeof(int), cudaMemcpyDeviceToHost, stream);
+}
+
 SB_API const char* sb_status_string(int code) {
   switch (code) {
     case SB_OK: return "ok";

@@ -98,6 +98,44 @@ def check_status(clear: bool = True) -> None:
         raise RuntimeError(f"a speech_b200 kernel reported status {out[0]} ({msg}) in block {out[1]}, detail {out[2]}")
 
 
+def status_message(code: int) -> str:
+    return lib().sb_status_string(int(code)).decode()
+
+
+def set_wait_seconds(seconds: float, clock_hz: float = 2.0e9) -> None:
+    """Limit of every bounded in-kernel wait on the current device (0 restores the default of about a second)."""
+    lib().sb_set_wait_cycles.argtypes = [ctypes.c_longlong]
+    rc = lib().sb_set_wait_cycles(ctypes.c_longlong(int(max(0.0, seconds) * clock_hz)))
+    if rc != 0:
+        raise RuntimeError(f"sb_set_wait_cycles failed with code {rc}")
+
+
+class StatusProbe:
+    """Non-blocking view of the device status word: ``record()`` enqueues a copy of the word into pinned memory on the current
+    stream, ``poll()`` returns the code of the last completed copy (0 = ok) without waiting for the device."""
+
+    def __init__(self, device: torch.device):
+        self.host = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self.event: Optional[torch.cuda.Event] = None
+        self.device = device
+
+    def record(self) -> None:
+        rc = lib().sb_status_copy_async(ctypes.c_void_p(self.host.data_ptr()), _stream())
+        if rc != 0:
+            raise RuntimeError(f"sb_status_copy_async failed with code {rc}")
+        self.event = torch.cuda.Event()
+        self.event.record()
+
+    def poll(self, wait: bool = False) -> int:
+        if self.event is None:
+            return 0
+        if wait:
+            self.event.synchronize()
+        elif not self.event.query():
+            return 0
+        return int(self.host[0])
+
+
 ACT = {None: 0, "none": 0, "relu": 1, "swish": 2, "silu": 2, "gelu": 3}
 
 

@@ -150,6 +150,8 @@ class GradSync:
     def begin_step(self):
         self._pending = [{id(p) for p in b["params"]} for b in self.buckets]
         self._launched = [False] * len(self.buckets)
+        self._complete = [False] * len(self.buckets)
+        self._next = 0          # buckets are launched strictly in index order, the same order on every rank
         self._works = []
 
     @contextlib.contextmanager
@@ -170,7 +172,13 @@ class GradSync:
             return
         self._pending[bi].discard(id(param))
         if not self._pending[bi]:
-            self._launch(bi)
+            self._complete[bi] = True
+            # Launch only the consecutive prefix of complete buckets.  The order in which gradients become final may differ
+            # between ranks (a parameter unused on one rank, conditional heads); the collective of launch k must nevertheless
+            # pair the same bucket on every rank, as c10d's reducer guarantees with its fixed bucket order.
+            while self._next < len(self.buckets) and self._complete[self._next]:
+                self._launch(self._next)
+                self._next += 1
 
     def _launch(self, bi: int):
         self._launched[bi] = True
@@ -197,9 +205,10 @@ class GradSync:
 
     def finish_step(self):
         """Launch whatever has not been launched (unused parameters), wait for all buckets."""
-        for bi in range(len(self.buckets)):
+        for bi in range(self._next, len(self.buckets)):
             if not self._launched[bi]:
                 self._launch(bi)
+        self._next = len(self.buckets)
         for w in self._works:
             w.wait()
         if self.comm_stream is not None:
@@ -222,9 +231,11 @@ def build_grad_sync(model, optimizers, strategy_spec, world_size: int, device: t
     if kind in ("auto", "ddp", "ddp_find_unused_parameters_true", "nccl"):
         use_peer = device.type == "cuda" and os.environ.get("SPEECH_B200_PEER_ALLREDUCE", "1") == "1"
         if use_peer and kind != "nccl":
-            try:
-                from .symm import PeerGradSync
+            from .symm import PeerGradSync
 
+            if os.environ.get("SPEECH_B200_PEER_ALLREDUCE_STRICT", "0") == "1":
+                return PeerGradSync(model, optimizers, world_size, device, sync_batchnorm=sync_batchnorm)
+            try:
                 return PeerGradSync(model, optimizers, world_size, device, sync_batchnorm=sync_batchnorm)
             except Exception as e:  # noqa: BLE001
                 logging.warning(f"peer-memory gradient exchange unavailable ({e}); using NCCL all-reduce")

@@ -162,6 +162,10 @@ class PeerGradSync(GradSync):
         self.reducer = PeerAllReduce(biggest, device)
         # persistent GEMMs size their grids to the SMs that are left while a bucket kernel is resident on the other stream
         self.reducer.lib.sb_set_reserved_sms(ctypes.c_int(self.reducer.ctas))
+        # Ranks drift apart by far more than the kernels' default wait limit of about a second in ordinary training (module
+        # loading in the first step, a rank that validates or logs longer, a dataloader worker restarting): waits for a peer get
+        # a minute before they give up, which then means a lost rank and fails the run (Trainer._check_kernel_status).
+        self.reducer.native.set_wait_seconds(float(os.environ.get("SPEECH_B200_WAIT_SECONDS", "60")))
         logging.info(f"peer-memory gradient exchange: {len(self.buckets)} buckets, largest {biggest * 4 / 2**20:.1f} MB, "
                      f"{self.reducer.ctas} CTAs per bucket")
 

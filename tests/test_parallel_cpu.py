@@ -79,3 +79,79 @@ def test_mesh_layout_without_process_groups():
     assert m.coords == {"pp": 0, "dp_replicate": 1, "dp_shard": 0, "cp": 0, "tp": 1}
     assert m.ranks("tp") == [4, 5] and m.ranks("dp_shard") == [5, 7] and m.ranks("dp") == [1, 3, 5, 7]
     assert m.size("dp") == 4 and m.rank("dp") == 2 and not m.is_dp_source()
+
+
+ORDER_SCRIPT = textwrap.dedent("""
+    import os, sys, torch, torch.distributed as dist
+    sys.path.insert(0, {repo!r})
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from speech_b200.parallel.ddp import GradSync
+    from speech_b200.core.modelpt import ModelPT
+
+    # ---- (1) a parameter that is unused on one rank only: buckets must still pair up across ranks
+    torch.manual_seed(0)
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = torch.nn.Linear(8, 8); self.b = torch.nn.Linear(8, 8); self.c = torch.nn.Linear(8, 8)
+        def forward(self, x, use_b):
+            h = self.a(x)
+            if use_b:
+                h = h + self.b(x)
+            return self.c(h).pow(2).mean()
+    net = Net()
+    # tiny buckets: every parameter tensor is its own bucket, so a wrong launch order would pair different tensors
+    sync = GradSync(net, [], world, torch.device("cpu"), bucket_mb=1e-6)
+    assert len(sync.buckets) >= 5
+    launched = []
+    orig = sync._launch
+    def spy(bi):
+        launched.append(bi); orig(bi)
+    sync._launch = spy
+    x = torch.randn(4, 8, generator=torch.Generator().manual_seed(100 + rank))
+    for p in net.parameters():
+        p.grad = None
+    sync.begin_step()
+    loss = net(x, use_b=(rank == 0))
+    loss.backward()
+    for p in net.b.parameters():        # the rank that skipped b contributes zeros
+        if p.grad is None:
+            p.grad = torch.zeros_like(p)
+    sync.finish_step()
+    assert launched == sorted(launched) and len(launched) == len(sync.buckets), launched
+    # reference: plain average of the per-rank gradients
+    ref = Net(); ref.load_state_dict(net.state_dict())
+    ref(x, use_b=(rank == 0)).backward()
+    for (n_, p), q in zip(net.named_parameters(), ref.parameters()):
+        g = q.grad.clone() if q.grad is not None else torch.zeros_like(q)
+        dist.all_reduce(g); g /= world
+        assert torch.allclose(p.grad, g, atol=1e-6), n_
+
+    # ---- (2) epoch-end metrics differ per rank before the reduction and agree after it
+    from speech_b200.models.asr_model import ASRModel
+    class Dummy:
+        device = torch.device("cpu")
+    outs = [{{"val_loss": torch.tensor(1.0 + rank), "val_wer_num": 3.0 + 5 * rank, "val_wer_denom": 10.0}}]
+    res = ASRModel.multi_validation_epoch_end(type("M", (), {{"reduce_sums": staticmethod(ModelPT.reduce_sums), "device": torch.device("cpu")}})(), outs)
+    assert abs(float(res["log"]["val_wer"]) - (3.0 + 8.0) / 20.0) < 1e-6, res
+    assert abs(float(res["log"]["val_loss"]) - 1.5) < 1e-6, res
+    # the generic path: any logged scalar becomes the mean over ranks
+    m = type("M", (), {{"reduce_sums": staticmethod(ModelPT.reduce_sums), "device": torch.device("cpu")}})()
+    synced = ModelPT._sync_logged(m, {{"val_acc": torch.tensor(0.25 + 0.5 * rank), "n": 2}})
+    assert abs(float(synced["val_acc"]) - 0.5) < 1e-6
+    print("RESULT ok", rank)
+    dist.destroy_process_group()
+""")
+
+
+def test_bucket_order_and_metric_sync_two_ranks(tmp_path):
+    """Buckets launch in index order even when gradients become final in a different order on one rank, and validation
+    metrics are identical on all ranks after the epoch-end reduction."""
+    script = tmp_path / "order.py"
+    script.write_text(ORDER_SCRIPT.format(repo=REPO))
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29764", str(script)],
+                         capture_output=True, text=True, timeout=600, env=dict(os.environ, MASTER_ADDR="127.0.0.1"))
+    assert out.returncode == 0, out.stderr[-3000:]
+    assert out.stdout.count("RESULT ok") == 2
