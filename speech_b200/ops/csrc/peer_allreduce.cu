@@ -18,6 +18,7 @@
 // Every wait is bounded: after the wait limit (common.cuh) the CTA records SB_TIMEOUT_PEER_FLAG in the status word and returns
 // without touching peer memory again.
 #include "common.cuh"
+#include <stdlib.h>
 
 #define SB_PEER_MAX_WORLD 16
 #define SB_PEER_MAX_CTAS 128
@@ -259,6 +260,161 @@ __global__ void peer_unpack_kernel(const __nv_bfloat16* __restrict__ recv, float
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Peer phase with bulk copies (the default): a few CTAs keep hundreds of kilobytes in flight over NVLink.
+//
+// CTA b owns sub-chunk b of THIS rank's slice.  It walks the sub-chunk in tiles of `tile` bytes through a ring of STAGES
+// shared-memory stages; a stage holds the tile of every rank's send region (fetched with cp.async.bulk, an untiled bulk copy
+// from peer memory that completes on an mbarrier; no multicast) plus the reduced tile.  The 256 threads sum the `world` tiles
+// in fp32, round once to bf16, and thread 0 sends the result to every rank's receive region with bulk stores.  Loads of the
+// following STAGES - 1 tiles are in flight while a tile is summed, so a CTA has (STAGES - 1) * (world - 1) * tile bytes on
+// the links; four CTAs cover what a 12-CTA register-staged kernel could not.  Same flag protocol as above (CTA b only ever
+// waits for CTA b of its peers), same bounded waits.
+constexpr int BULK_THREADS = 256;
+constexpr int BULK_SMEM = 200 * 1024;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+__global__ void __launch_bounds__(BULK_THREADS) peer_allreduce_bulk_kernel(SbPeerArgs a, int tile_bytes, int stages) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ int s_fail;
+  __shared__ __align__(8) unsigned long long bars[16];
+  const int b = blockIdx.x;
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    s_fail = 0;
+    for (int s = 0; s < stages; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bars[s])));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  char* my_base = (char*)a.buffers[a.rank];
+  const unsigned int* my_flags = reinterpret_cast<const unsigned int*>(my_base + a.flags_off);
+  const long long c0 = (long long)b * a.chunk;                              // elements inside the slice
+  const long long c1 = min(a.slice, c0 + a.chunk);
+  const long long base = (long long)a.rank * a.slice;
+  const int tile_elems = tile_bytes / 2;
+  const long long ntiles = c1 > c0 ? (c1 - c0 + tile_elems - 1) / tile_elems : 0;
+  const int stage_bytes = tile_bytes * (a.world + 1);
+  const uint32_t smem0 = (smem_addr(smem_raw) + 127u) & ~127u;
+
+  // the send regions of all ranks are complete (their pack kernels ran before this kernel on their streams)
+  signal_peers(a, b, 2u * a.epoch + 1u);
+  if (!wait_peers(my_flags, b, a.world, a.rank, 2u * a.epoch + 1u, &s_fail, a.status)) {
+    if (tid == 0) sb_set_status(a.status, SB_TIMEOUT_PEER_FLAG, 1);
+    return;
+  }
+
+  auto issue_loads = [&](long long t) {       // thread 0: fetch tile t of every rank into stage t % stages
+    const int s = (int)(t % stages);
+    const long long e0 = c0 + t * tile_elems;
+    const uint32_t bytes = (uint32_t)(min((long long)tile_elems, c1 - e0) * 2);   // multiple of 16: chunk and slice are of 8
+    const uint32_t bar = smem_addr(&bars[s]);
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes * a.world)
+                 : "memory");
+    for (int q = 0; q < a.world; ++q) {
+      const int src_rank = (a.rank + q) % a.world;      // start with the local copy, then walk the ring
+      const char* src = (const char*)a.buffers[src_rank] + a.send_off + (base + e0) * 2;
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(smem0 + s * stage_bytes + q * tile_bytes), "l"(src), "r"(bytes), "r"(bar) : "memory");
+    }
+  };
+
+  long long issued = 0;                       // thread 0: tiles whose loads have been issued
+  if (tid == 0)
+    for (long long t = 0; t < ntiles && t < stages - 1; ++t, ++issued) issue_loads(t);
+  bool ok = true;
+  long long done = 0;
+  for (long long t = 0; t < ntiles; ++t) {
+    const int s = (int)(t % stages);
+    const uint32_t par = (uint32_t)((t / stages) & 1);
+    // (1) the stage that tile t + stages - 1 will use was consumed in iteration t - 1 (all threads passed its barrier below) and
+    //     its result tile has been read by the bulk stores issued then
+    if (tid == 0 && t + stages - 1 < ntiles) {
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      issue_loads(t + stages - 1);
+      ++issued;
+    }
+    // (2) wait for tile t (bounded)
+    {
+      const uint32_t bar = smem_addr(&bars[s]);
+      if (!mbar_try(bar, par)) {
+        const long long t0 = clock64();
+        unsigned int probes = 0;
+        while (!mbar_try(bar, par)) {
+          if ((++probes & 63u) == 0 && (clock64() - t0 > sb_wait_cycles(a.status) || sb_failed(a.status))) {
+            atomicExch(&s_fail, 1);
+            break;
+          }
+        }
+      }
+    }
+    if (__syncthreads_or(s_fail)) { ok = false; break; }
+    // (3) sum the world tiles: a thread owns 16 bytes at a time
+    const long long e0 = c0 + t * tile_elems;
+    const int n16 = (int)(min((long long)tile_elems, c1 - e0) / 8);
+    const unsigned char* st = smem_raw + (smem0 - smem_addr(smem_raw)) + (size_t)s * stage_bytes;
+    unsigned char* out = const_cast<unsigned char*>(st) + (size_t)a.world * tile_bytes;
+    for (int i = tid; i < n16; i += BULK_THREADS) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      // fixed summation order by RANK (not by ring position), so that every rank rounds identical sums
+      for (int r = 0; r < a.world; ++r) {
+        const int q = (r - a.rank + a.world) % a.world;
+        add8(acc, *reinterpret_cast<const uint4*>(st + (size_t)q * tile_bytes + (size_t)i * 16));
+      }
+      __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+      *reinterpret_cast<uint4*>(out + (size_t)i * 16) = *reinterpret_cast<const uint4*>(o);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    // (4) the reduced tile goes to every rank's receive region
+    if (tid == 0) {
+      const uint32_t bytes = (uint32_t)n16 * 16u;
+      for (int q = 0; q < a.world; ++q) {
+        const int dst_rank = (a.rank + q) % a.world;
+        char* dst = (char*)a.buffers[dst_rank] + a.recv_off + (base + e0) * 2;
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                     ::"l"(dst), "r"(smem0 + s * stage_bytes + a.world * tile_bytes), "r"(bytes) : "memory");
+      }
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+    done = t + 1;
+  }
+  if (tid == 0) {
+    if (!ok) {
+      // after a give-up: copies that are still on their way into this CTA's shared memory get one more (bounded) wait each
+      for (long long t = done; t < issued; ++t) {
+        const uint32_t bar = smem_addr(&bars[t % stages]);
+        const uint32_t par = (uint32_t)((t / stages) & 1);
+        const long long t0 = clock64();
+        while (!mbar_try(bar, par) && clock64() - t0 < sb_wait_cycles(a.status)) { }
+      }
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // every store of this CTA has been performed
+    asm volatile("fence.proxy.async;" ::: "memory");
+  }
+  __syncthreads();
+  if (!ok) {
+    if (tid == 0) sb_set_status(a.status, SB_TIMEOUT_PEER_FLAG, 3);
+    return;
+  }
+  signal_peers(a, b, 2u * a.epoch + 2u);
+  if (!wait_peers(my_flags, b, a.world, a.rank, 2u * a.epoch + 2u, &s_fail, a.status)) {
+    if (tid == 0) sb_set_status(a.status, SB_TIMEOUT_PEER_FLAG, 2);
+    return;
+  }
+}
+
 }  // namespace
 
 // Bytes of the flag block at the start of a symmetric buffer.
@@ -306,7 +462,24 @@ SB_API int sb_peer_allreduce_split(SbPeerArgs* a, void* my_base, cudaStream_t st
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   peer_pack_kernel<<<(int)blocks, 256, 0, stream>>>(a->grad, send, a->n, padded, a->scale);
-  peer_allreduce_kernel<false><<<a->ctas, 512, 0, stream>>>(*a);
+  static const bool use_bulk = [] { const char* e = getenv("SPEECH_B200_PEER_BULK"); return !(e && e[0] == '0'); }();
+  if (use_bulk) {
+    // stage = (world + 1) tiles; at least three stages in 200 KB, tiles of 1-16 KB
+    int tile = (BULK_SMEM - 256) / (4 * (a->world + 1));
+    tile = tile >= 16384 ? 16384 : (tile / 1024) * 1024;
+    if (tile < 1024) tile = 1024;
+    int stages = (BULK_SMEM - 256) / (tile * (a->world + 1));
+    if (stages > 8) stages = 8;
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t ae = cudaFuncSetAttribute(peer_allreduce_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BULK_SMEM);
+      if (ae != cudaSuccess) return (int)ae;
+      attr_set = true;
+    }
+    peer_allreduce_bulk_kernel<<<a->ctas, BULK_THREADS, BULK_SMEM, stream>>>(*a, tile, stages);
+  } else {
+    peer_allreduce_kernel<false><<<a->ctas, 512, 0, stream>>>(*a);
+  }
   peer_unpack_kernel<<<(int)blocks, 256, 0, stream>>>(recv, a->grad, a->n, a->status);
   return (int)cudaGetLastError();
 }

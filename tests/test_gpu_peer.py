@@ -38,6 +38,75 @@ def test_one_rank_world_rounds_through_bf16(n, ctas):
     native.check_status()
 
 
+@pytest.mark.parametrize("n,ctas", [(8, 1), (1000, 3), (1_000_003, 4), (40_000_000, 4)])
+def test_one_rank_world_bulk_copy_path(n, ctas):
+    """The three-launch form (wide cast, bulk-copy peer kernel, wide unpack) on a one-rank world: tiling, ring of stages,
+    tails that are not whole tiles."""
+    from speech_b200.ops import native
+    from speech_b200.parallel.symm import SbPeerArgs, padded_elems
+
+    lib = native.lib()
+    lib.sb_peer_flags_bytes.restype = ctypes.c_longlong
+    dev = torch.device("cuda:0")
+    torch.manual_seed(n)
+    g = torch.randn(n, device=dev)
+    want = (g * 0.25).to(torch.bfloat16).float()
+    flags = int(lib.sb_peer_flags_bytes())
+    region = -(-padded_elems(n, 1) * 2 // 256) * 256
+    buf = torch.zeros(flags + 2 * region, dtype=torch.uint8, device=dev)
+    ptrs = torch.tensor([buf.data_ptr()], dtype=torch.int64, device=dev)
+    for epoch in (1, 2, 3):
+        x = g.clone()
+        a = SbPeerArgs(x.data_ptr(), ptrs.data_ptr(), 0, flags, flags + region, n, 0, 0, 0, 1, ctas, epoch, 0.25, None)
+        assert lib.sb_peer_allreduce_split(ctypes.byref(a), ctypes.c_void_p(buf.data_ptr()), native._stream()) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(x, want)
+    native.check_status()
+
+
+def test_wait_for_an_absent_peer_runs_out_and_the_context_survives():
+    """A two-rank world in which the second rank never launches: the kernel's wait for its flag gives up after the (shortened)
+    limit, records SB_TIMEOUT_PEER_FLAG, leaves the gradients untouched (the unpack and the optimizer update return once the
+    status word is set), and the next launches on the same context work."""
+    from speech_b200.ops import native
+    from speech_b200.parallel.symm import SbPeerArgs, padded_elems
+
+    lib = native.lib()
+    lib.sb_peer_flags_bytes.restype = ctypes.c_longlong
+    dev = torch.device("cuda:0")
+    n = 100_000
+    flags = int(lib.sb_peer_flags_bytes())
+    region = -(-padded_elems(n, 2) * 2 // 256) * 256
+    mine = torch.zeros(flags + 2 * region, dtype=torch.uint8, device=dev)
+    absent = torch.zeros(flags + 2 * region, dtype=torch.uint8, device=dev)    # stands for the peer's buffer; nobody raises its flags
+    ptrs = torch.tensor([mine.data_ptr(), absent.data_ptr()], dtype=torch.int64, device=dev)
+    g = torch.randn(n, device=dev)
+    x = g.clone()
+    native.set_wait_seconds(0.05)
+    try:
+        a = SbPeerArgs(x.data_ptr(), ptrs.data_ptr(), 0, flags, flags + region, n, 0, 0, 0, 2, 2, 1, 0.5, None)
+        assert lib.sb_peer_allreduce_split(ctypes.byref(a), ctypes.c_void_p(mine.data_ptr()), native._stream()) == 0
+        torch.cuda.synchronize()
+        with pytest.raises(RuntimeError, match="peer"):
+            native.check_status()                      # reads and clears the status word
+        assert torch.equal(x, g), "gradients must be left alone after a give-up"
+    finally:
+        native.set_wait_seconds(0.0)
+    # the context is intact: an ordinary one-rank reduction and a GEMM still work
+    one = torch.tensor([mine.data_ptr()], dtype=torch.int64, device=dev)
+    mine.zero_()
+    y = g.clone()
+    b = SbPeerArgs(y.data_ptr(), one.data_ptr(), 0, flags, flags + region, n, 0, 0, 0, 1, 2, 1, 1.0, None)
+    assert lib.sb_peer_allreduce_split(ctypes.byref(b), ctypes.c_void_p(mine.data_ptr()), native._stream()) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(y, g.to(torch.bfloat16).float())
+    a_ = torch.randn(256, 128, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(256, 256, device=dev, dtype=torch.bfloat16)
+    native.gemm(a_, torch.randn(256, 128, device=dev, dtype=torch.bfloat16), out, M=256, N=256, K=128)
+    torch.cuda.synchronize()
+    native.check_status()
+
+
 def test_bad_arguments_are_rejected():
     from speech_b200.ops import native
     from speech_b200.parallel.symm import SbPeerArgs
