@@ -262,7 +262,7 @@ def eager_arm(args, rank, world, local, dev):
 
     # untimed pass over every batch shape (JIT compilation of the Numba kernels, cuDNN plans, allocator growth)
     saved = (args.warmup, args.steps)
-    args.warmup, args.steps = 0, len(batches)
+    args.warmup, args.steps = 0, 16          # the same count on every rank (the ranks' batch lists differ in length)
     run(False)
     args.warmup, args.steps = saved
     ms, audio, clocks, losses = run(False)
@@ -298,6 +298,11 @@ def eager_arm(args, rank, world, local, dev):
 
 def main():
     args = parse_args()
+    if os.environ.get("SPEECH_B200_BENCH_WATCHDOG"):
+        # dumps every thread's Python stack if the run is still going after that many seconds (where a hang sits)
+        import faulthandler
+
+        faulthandler.dump_traceback_later(float(os.environ["SPEECH_B200_BENCH_WATCHDOG"]), repeat=True)
     if args.impl == "reference":
         return reference_arm()
     import torch
@@ -399,8 +404,8 @@ def main():
 
     # untimed pass over every batch shape: neither timed pass is the one that meets a shape (or a kernel image) first
     saved = (args.warmup, args.steps)
-    args.warmup, args.steps = 0, len(batches)
-    total_steps = len(batches)
+    args.warmup, args.steps = 0, 16          # the same count on every rank (the ranks' batch lists differ in length)
+    total_steps = 16
     run(e2e=False)
     run.trainer.current_epoch = 0
     args.warmup, args.steps = saved
@@ -409,7 +414,10 @@ def main():
     if world > 1:
         gs = run.trainer.grad_sync
         if type(gs).__name__ != "PeerGradSync":
-            raise SystemExit(f"bench.py: gradient exchange is {type(gs).__name__}, not the peer-memory kernel")
+            if os.environ.get("SPEECH_B200_PEER_ALLREDUCE", "1") == "1":
+                raise SystemExit(f"bench.py: gradient exchange is {type(gs).__name__}, not the peer-memory kernel")
+            gs = None       # NCCL all-reduce requested explicitly (comparison runs): reported as such in config.grad_exchange
+    if world > 1 and gs is not None:
         # first bucket of the peer all-reduce against NCCL on the same data
         n = gs.buckets[0]["view"].numel()
         g = torch.Generator(device=dev).manual_seed(4321 + rank)
@@ -417,8 +425,8 @@ def main():
         want = x / world
         dist.all_reduce(want)
         got = x.clone()
+        gs.comm_stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(gs.comm_stream):
-            gs.comm_stream.wait_stream(torch.cuda.current_stream())
             gs.reducer(got, 1.0 / world)
         torch.cuda.current_stream().wait_stream(gs.comm_stream)
         torch.cuda.synchronize()
@@ -454,7 +462,10 @@ def main():
                        "parallelism": f"dp{world}", "dropout": args.dropout,
                        "prednet_dropout": float(cfg.decoder.prednet.get("dropout", 0.0)),
                        "joint_dropout": float(cfg.joint.jointnet.get("dropout", 0.0)),
-                       "grad_exchange": type(run.trainer.grad_sync).__name__ if world > 1 else "none",
+                       "grad_exchange": (f"{type(run.trainer.grad_sync).__name__}: {run.trainer.grad_sync.launched_in_backward} of "
+                                         f"{len(run.trainer.grad_sync.buckets)} buckets launched during backward"
+                                         + (f", {run.trainer.grad_sync.reducer.ctas} CTAs" if hasattr(run.trainer.grad_sync, "reducer") else ""))
+                       if world > 1 else "none",
                        "optimizer": "AdamW+Noam, clip 1.0",
                        "l2": "no flush: per-step activations are several GB, far larger than the 126 MB L2"},
             "clocks": clocks, "gpu_launches": launches,

@@ -19,6 +19,7 @@
 // without touching peer memory again.
 #include "common.cuh"
 #include <stdlib.h>
+#include <string.h>
 
 #define SB_PEER_MAX_WORLD 16
 #define SB_PEER_MAX_CTAS 128
@@ -54,8 +55,10 @@ __device__ bool wait_peers(const unsigned int* my_flags, int b, int world, int r
   if (threadIdx.x < world && threadIdx.x != rank) {
     const unsigned int* f = my_flags + (long long)b * SB_PEER_MAX_WORLD + threadIdx.x;
     const long long t0 = clock64();
+    unsigned int probes = 0;
     while ((int)(ld_acquire_sys(f) - want) < 0) {
-      if (clock64() - t0 > sb_wait_cycles(status)) {
+      // once any kernel has given up (status word set) later waits end at once: a lost rank costs one limit, not one per launch
+      if (clock64() - t0 > sb_wait_cycles(status) || ((++probes & 255u) == 0 && sb_failed(status))) {
         atomicExch(s_fail, 1);
         break;
       }
@@ -262,7 +265,7 @@ __global__ void peer_unpack_kernel(const __nv_bfloat16* __restrict__ recv, float
 
 
 // ---------------------------------------------------------------------------------------------------------------------------
-// Peer phase with bulk copies (the default): a few CTAs keep hundreds of kilobytes in flight over NVLink.
+// Peer phase with bulk copies (opt-in, see sb_peer_allreduce_split).
 //
 // CTA b owns sub-chunk b of THIS rank's slice.  It walks the sub-chunk in tiles of `tile` bytes through a ring of STAGES
 // shared-memory stages; a stage holds the tile of every rank's send region (fetched with cp.async.bulk, an untiled bulk copy
@@ -462,7 +465,9 @@ SB_API int sb_peer_allreduce_split(SbPeerArgs* a, void* my_base, cudaStream_t st
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   peer_pack_kernel<<<(int)blocks, 256, 0, stream>>>(a->grad, send, a->n, padded, a->scale);
-  static const bool use_bulk = [] { const char* e = getenv("SPEECH_B200_PEER_BULK"); return !(e && e[0] == '0'); }();
+  // The bulk-copy kernel is opt-in (SPEECH_B200_PEER_BULK=1): with its ring of 16 KB tiles a CTA keeps under 50 KB on the
+  // links at two ranks, and measured end to end (TDT-0.6B, 2 GPUs) it is slower than the register-staged kernel on 12 CTAs.
+  static const bool use_bulk = [] { const char* e = getenv("SPEECH_B200_PEER_BULK"); return e && e[0] == '1'; }();
   if (use_bulk) {
     // stage = (world + 1) tiles; at least three stages in 200 KB, tiles of 1-16 KB
     int tile = (BULK_SMEM - 256) / (4 * (a->world + 1));
@@ -476,7 +481,24 @@ SB_API int sb_peer_allreduce_split(SbPeerArgs* a, void* my_base, cudaStream_t st
       if (ae != cudaSuccess) return (int)ae;
       attr_set = true;
     }
-    peer_allreduce_bulk_kernel<<<a->ctas, BULK_THREADS, BULK_SMEM, stream>>>(*a, tile, stages);
+    // Launched as clusters of two CTAs when their number is even (the cluster is used for nothing else): a cluster of two
+    // occupies both SMs of one TPC, so that the persistent GEMMs running beside this kernel, which are themselves built from
+    // CTA pairs, lose whole pairs and not one SM out of several pairs.
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(a->ctas, 1, 1);
+    cfg.blockDim = dim3(BULK_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = BULK_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (a->ctas % 2 == 0) ? 2 : 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, peer_allreduce_bulk_kernel, *a, tile, stages);
+    if (le != cudaSuccess) return (int)le;
   } else {
     peer_allreduce_kernel<false><<<a->ctas, 512, 0, stream>>>(*a);
   }

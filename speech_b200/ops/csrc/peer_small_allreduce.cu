@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(256) peer_small_allreduce_kernel(SbPeerSmallAr
                             threadIdx.x;
     const long long t0 = clock64();
     while ((int)(ld_acquire_sys_u32(f) - a.epoch) < 0) {
-      if (clock64() - t0 > sb_wait_cycles(a.status)) {
+      if (clock64() - t0 > sb_wait_cycles(a.status) || sb_failed(a.status)) {
         atomicExch(&s_fail, 1);
         break;
       }

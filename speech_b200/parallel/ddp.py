@@ -153,6 +153,7 @@ class GradSync:
         self._complete = [False] * len(self.buckets)
         self._next = 0          # buckets are launched strictly in index order, the same order on every rank
         self._works = []
+        self.launched_in_backward = 0
 
     @contextlib.contextmanager
     def no_sync(self):
@@ -179,6 +180,7 @@ class GradSync:
             while self._next < len(self.buckets) and self._complete[self._next]:
                 self._launch(self._next)
                 self._next += 1
+                self.launched_in_backward += 1
 
     def _launch(self, bi: int):
         self._launched[bi] = True

@@ -76,7 +76,7 @@ class PeerAllReduce:
         self.recv_off = self.flags_bytes + region
         self.buf = SymmetricBuffer(self.flags_bytes + 2 * region, device, group)
         self.rank, self.world = self.buf.rank, self.buf.world
-        self.ctas = int(ctas or os.environ.get("SPEECH_B200_PEER_CTAS", 4))
+        self.ctas = int(ctas or os.environ.get("SPEECH_B200_PEER_CTAS", 12))
         self.epoch = 0
         # the cast into the send region and the unpack from the receive region as wide kernels of their own (default), or inside
         # the few-block peer kernel

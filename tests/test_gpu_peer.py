@@ -39,9 +39,20 @@ def test_one_rank_world_rounds_through_bf16(n, ctas):
 
 
 @pytest.mark.parametrize("n,ctas", [(8, 1), (1000, 3), (1_000_003, 4), (40_000_000, 4)])
-def test_one_rank_world_bulk_copy_path(n, ctas):
-    """The three-launch form (wide cast, bulk-copy peer kernel, wide unpack) on a one-rank world: tiling, ring of stages,
-    tails that are not whole tiles."""
+@pytest.mark.parametrize("bulk", ["0", "1"])
+def test_one_rank_world_three_launch_form(n, ctas, bulk):
+    """The three-launch form (wide cast, peer kernel, wide unpack) on a one-rank world, with the register-staged and with the
+    bulk-copy peer kernel (child process: the choice is read once per process): tiling, ring of stages, ragged tails."""
+    if bulk == "1":
+        code = f"import tests.test_gpu_peer as t; t._three_launch_body({n}, {ctas})"
+        env = dict(os.environ, SPEECH_B200_PEER_BULK="1", PYTHONPATH=REPO)
+        out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, env=env, cwd=REPO)
+        assert out.returncode == 0, out.stderr[-2000:]
+        return
+    _three_launch_body(n, ctas)
+
+
+def _three_launch_body(n, ctas):
     from speech_b200.ops import native
     from speech_b200.parallel.symm import SbPeerArgs, padded_elems
 
