@@ -137,6 +137,11 @@ class ConvSubsampling(nn.Module):
 
     def forward(self, x, lengths):
         """x: [B, T, F] features; returns ([B, T', d_model], lengths')."""
+        if self._native_front_end(x):
+            from ..ops import native_subsampling as ns
+
+            convs = [m for m in self.conv if isinstance(m, nn.Conv2d)]
+            return ns.dw_striding_forward(x, lengths, convs, self.out.weight, self.out.bias, self.is_causal)
         if self.conv2d_subsampling:
             x, out_lengths = self.conv(x, lengths)
             b, c, t, f = x.shape
@@ -148,6 +153,16 @@ class ConvSubsampling(nn.Module):
             x = self.conv(x.transpose(1, 2)).transpose(1, 2)
         return x, out_lengths
 
+    def _native_front_end(self, x) -> bool:
+        """The channels-last kernels of ``ops/csrc/subsampling.cu`` serve the depthwise-striding front end in bf16 on GPUs."""
+        if not (self.conv2d_subsampling and self._subsampling == "dw_striding" and x.is_cuda and x.dim() == 3):
+            return False
+        if ops.get_compute_dtype() != torch.bfloat16 or not ops._use_native(x):
+            return False
+        from ..ops import native_subsampling as ns
+
+        return ns.supported(self._conv_channels, self._sampling_num, self._feat_in) and self._feat_out % 8 == 0
+
     def prime_shapes(self, shapes, device, dtype=None) -> None:
         """Run the convolution stack forward and backward once on zeros for every ``(batch, frames)`` in ``shapes``.  The
         convolution library builds an execution plan per problem shape on first use (milliseconds each, three per layer with the
@@ -155,6 +170,8 @@ class ConvSubsampling(nn.Module):
         instead of inside the first step that meets a shape.  Parameter gradients produced here are discarded."""
         if not self.conv2d_subsampling:
             return
+        if dtype == torch.bfloat16 and torch.device(device).type == "cuda" and self._subsampling == "dw_striding" and ops.native_available():
+            return  # the native front end has no per-shape plans
         import contextlib
 
         ctx = torch.autocast("cuda", dtype=dtype) if (dtype is not None and torch.device(device).type == "cuda") else contextlib.nullcontext()
