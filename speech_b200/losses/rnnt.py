@@ -116,8 +116,14 @@ class RNNTLoss(Loss):
                 loss = ops.transducer_loss_from_logits(acts.contiguous(), labels, act_lens, label_lens, self._blank,
                                                        self.durations, self.sigma)
         elif self.kind == "multiblank":
-            loss = _ref.multiblank_loss_from_logits(acts, labels, act_lens, label_lens, self._blank,
-                                                    self.big_blank_durations, self.sigma)
+            if acts.is_cuda and ops._use_native(acts):
+                from ..ops import native_transducer as _nt
+
+                loss = _nt.multiblank_loss_from_logits(acts, labels, act_lens, label_lens, self._blank,
+                                                       self.big_blank_durations, self.sigma)
+            else:
+                loss = _ref.multiblank_loss_from_logits(acts, labels, act_lens, label_lens, self._blank,
+                                                        self.big_blank_durations, self.sigma)
         else:
             loss = ops.transducer_loss_from_logits(acts.contiguous(), labels, act_lens, label_lens, self._blank, [], 0.0)
         if self.fastemit_lambda:
@@ -131,8 +137,9 @@ class RNNTLoss(Loss):
 
     # ------------------------------------------------------------------ fused with the joint
     def forward_fused(self, f, g, weight, bias, transcripts, encoder_lengths, transcript_lengths, act: str = "relu",
-                      fused_batch_size: Optional[int] = None):
-        """f: [B,T,H] and g: [B,U+1,H] projected encoder / prediction outputs; returns per-utterance losses."""
+                      fused_batch_size: Optional[int] = None, dropout_p: float = 0.0):
+        """f: [B,T,H] and g: [B,U+1,H] projected encoder / prediction outputs; returns per-utterance losses.  ``dropout_p`` is
+        the joint network's dropout, applied inside the fused kernels on GPUs."""
         f_len, y_len = encoder_lengths.long(), transcript_lengths.long()
         transcripts = transcripts.long()
         if self.kind == "multiblank":
@@ -143,7 +150,7 @@ class RNNTLoss(Loss):
             nd = len(self.durations)
             durations, sigma, w, b = [], 0.0, weight[:-nd], (bias[:-nd] if bias is not None else None)
         return ops.transducer_joint_loss(f, g, w, b, transcripts, f_len, y_len, self._blank, durations, sigma, act,
-                                         self.fastemit_lambda, fused_batch_size or 0)
+                                         self.fastemit_lambda, fused_batch_size or 0, dropout_p=dropout_p)
 
     def forward_from_joint_fn(self, joint, f, g, transcripts, f_len, y_len, fused_batch_size, w=None, b=None, act="relu"):
         """Generic sub-batched path: build logits for ``fused_batch_size`` utterances at a time."""

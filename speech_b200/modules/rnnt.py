@@ -515,14 +515,17 @@ class RNNTJoint(NeuralModule, AdapterModuleMixin):
         if decoder_outputs is not None:
             f = self.project_encoder(encoder_outputs)
             g = self.project_prednet(decoder_outputs)
-            if self._joint_dropout and self.training:
-                # dropout sits between the activation and the output GEMM; fall back to the generic joint
+            drop = float(self._joint_dropout or 0.0) if self.training else 0.0
+            if drop > 0.0 and (not f.is_cuda or self.activation.lower() != "relu" or getattr(self._loss, "kind", "") == "multiblank"):
+                # dropout sits between the activation and the output GEMM; the fused kernels apply it for the ReLU joint on GPUs,
+                # everything else takes the generic joint
                 per_utt = self._loss.forward_from_joint_fn(self, f, g, transcripts, encoder_lengths, transcript_lengths,
                                                            self._fused_batch_size)
             else:
                 lin = self.joint_net[-1]
                 per_utt = self._loss.forward_fused(f, g, lin.weight, lin.bias, transcripts, encoder_lengths,
-                                                   transcript_lengths, self.activation.lower(), self._fused_batch_size)
+                                                   transcript_lengths, self.activation.lower(), self._fused_batch_size,
+                                                   dropout_p=drop)
             loss_value = self._loss.reduce(per_utt, transcript_lengths)
         wer = wer_num = wer_denom = None
         if compute_wer:

@@ -1,8 +1,9 @@
 """Config-facing wrappers of the transformer stack, the token classifier head and the AED sequence generators.
 
-``TransformerDecoderNM`` / ``TransformerEncoderNM`` hold ``embedding`` + ``decoder`` / ``encoder`` sub-modules exactly like
-the reference (``nemo/collections/asr/modules/transformer/transformer.py:159``), so Canary checkpoints' ``transf_decoder.*``
-keys load; ``TokenClassifier`` is ``mlp.layer0`` + log-softmax (``parts/submodules/token_classifier.py``).  Greedy and beam
+``TransformerDecoderNM`` / ``TransformerEncoderNM`` hold ``_embedding`` + ``_decoder`` / ``_encoder`` sub-modules under the
+reference's attribute names (``nemo/collections/asr/modules/transformer/transformer.py:97,106,190,199``; ``embedding`` /
+``decoder`` / ``encoder`` are read-only properties there as here), so Canary checkpoints' ``transf_decoder._embedding.*`` and
+``transf_decoder._decoder.*`` keys load; ``TokenClassifier`` is ``mlp.layer0`` + log-softmax (``parts/submodules/token_classifier.py``).  Greedy and beam
 generators with incremental decoding follow ``transformer_generators.py:36,400``.
 """
 from __future__ import annotations
@@ -24,14 +25,22 @@ class TransformerEncoderNM(NeuralModule):
                  pre_ln_final_layer_norm=True):
         super().__init__()
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
-        self.embedding = TransformerEmbedding(vocab_size, hidden_size, max_sequence_length, num_token_types, embedding_dropout,
-                                              learn_positional_encodings)
-        self.encoder = TransformerEncoder(num_layers, hidden_size, inner_size, mask_future, num_attention_heads,
+        self._embedding = TransformerEmbedding(vocab_size, hidden_size, max_sequence_length, num_token_types, embedding_dropout,
+                                               learn_positional_encodings)
+        self._encoder = TransformerEncoder(num_layers, hidden_size, inner_size, mask_future, num_attention_heads,
                                           attn_score_dropout, attn_layer_dropout, ffn_dropout, hidden_act, pre_ln,
                                           pre_ln_final_layer_norm)
 
+    @property
+    def embedding(self):
+        return self._embedding
+
+    @property
+    def encoder(self):
+        return self._encoder
+
     def forward(self, input_ids, encoder_mask):
-        return self.encoder(self.embedding(input_ids), encoder_mask)
+        return self._encoder(self._embedding(input_ids), encoder_mask)
 
 
 class TransformerDecoderNM(NeuralModule):
@@ -43,10 +52,18 @@ class TransformerDecoderNM(NeuralModule):
         self.vocab_size, self.hidden_size, self.max_sequence_length = vocab_size, hidden_size, max_sequence_length
         self.num_states = num_layers + 1
         self.return_mems = False
-        self.embedding = TransformerEmbedding(vocab_size, hidden_size, max_sequence_length, num_token_types, embedding_dropout,
-                                              learn_positional_encodings)
-        self.decoder = TransformerDecoder(num_layers, hidden_size, inner_size, num_attention_heads, attn_score_dropout,
+        self._embedding = TransformerEmbedding(vocab_size, hidden_size, max_sequence_length, num_token_types, embedding_dropout,
+                                               learn_positional_encodings)
+        self._decoder = TransformerDecoder(num_layers, hidden_size, inner_size, num_attention_heads, attn_score_dropout,
                                           attn_layer_dropout, ffn_dropout, hidden_act, pre_ln, pre_ln_final_layer_norm)
+
+    @property
+    def embedding(self):
+        return self._embedding
+
+    @property
+    def decoder(self):
+        return self._decoder
 
     def forward(self, input_ids, decoder_mask, encoder_embeddings, encoder_mask, decoder_mems=None):
         start_pos = 0

@@ -192,12 +192,12 @@ def lstm(x, weights, h0=None, c0=None, num_layers=1, dropout=0.0, training=False
 
 # ----------------------------------------------------------------------------- losses
 def transducer_joint_loss(f, g, w, b, targets, f_len, y_len, blank, durations, sigma, act="relu",
-                          fastemit_lambda=0.0, sub_batch=0):
+                          fastemit_lambda=0.0, sub_batch=0, dropout_p: float = 0.0):
     if _use_native(f) and f.dtype == torch.bfloat16 and act == "relu":
         return _nat().transducer_joint_loss(f, g, w, b, targets, f_len, y_len, blank, durations, sigma,
-                                              fastemit_lambda)
+                                              fastemit_lambda, dropout_p)
     return reference.transducer_joint_loss(f, g, w, b, targets, f_len, y_len, blank, durations, sigma, act,
-                                           fastemit_lambda, sub_batch)
+                                           fastemit_lambda, sub_batch, dropout_p=dropout_p)
 
 
 def transducer_loss_from_logits(logits, targets, f_len, y_len, blank, durations, sigma=0.0):

@@ -20,15 +20,24 @@ namespace {
 constexpr float NEG = -1.0e30f;
 constexpr int MAXD = 8;
 
+// Arc model of the lattice.  n == 0: plain RNNT.  n > 0, free_label == 0: TDT (every blank AND label arc carries a duration
+// d[i] with log-prob lpd[., i]; blank arcs need d > 0).  n > 0, free_label == 1: multi-blank RNNT (reference kernels
+// parts/numba/rnnt_loss/utils/cuda_utils/gpu_rnnt_kernel.py:411,570,720): blank symbol i advances d[i] > 0 frames with log-prob
+// lpd[., i] (lpb is then all zero), label arcs advance u only and cost lpl.
 struct Durations {
   int n;
+  int free_label;
   int d[MAXD];
 };
+constexpr int SB_DURATIONS_FREE_LABEL = 256;   // flag added to the duration count in the C interface
 
 __global__ void joint_build_h_kernel(const __nv_bfloat16* __restrict__ f, const __nv_bfloat16* __restrict__ g,
                                      __nv_bfloat16* __restrict__ h, int b0, int nb, int T, int U1, int Hj, long long f_bs,
-                                     long long g_bs) {
-  // rows of the chunk: (b - b0, t, u); f: [B,T,Hj] with batch stride f_bs, g: [B,U1,Hj] with batch stride g_bs
+                                     long long g_bs, unsigned int drop_thresh, float drop_scale, unsigned long long seed) {
+  // rows of the chunk: (b - b0, t, u); f: [B,T,Hj] with batch stride f_bs, g: [B,U1,Hj] with batch stride g_bs.
+  // Dropout of the joint network (after the activation, as in the reference's joint_net = [act, Dropout, Linear]): the mask is
+  // a hash of (seed, element index in the full [B, T, U1, Hj] lattice), so the backward pass rebuilds the same hidden units
+  // when it recomputes a chunk; dropped units are stored as zero, which also zeroes their ReLU derivative.
   const long long rows = (long long)nb * T * U1;
   const int h8 = Hj / 8;
   const long long total = rows * h8;
@@ -46,7 +55,15 @@ __global__ void joint_build_h_kernel(const __nv_bfloat16* __restrict__ f, const 
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       float2 a = __bfloat1622float2(hf[k]), bb = __bfloat1622float2(hg[k]);
-      o[k] = __floats2bfloat162_rn(fmaxf(a.x + bb.x, 0.f), fmaxf(a.y + bb.y, 0.f));
+      float v0 = fmaxf(a.x + bb.x, 0.f), v1 = fmaxf(a.y + bb.y, 0.f);
+      if (drop_thresh) {
+        // eight consecutive elements: groups (base >> 2) and (base >> 2) + 1 of the four-per-hash mask
+        const unsigned long long base = ((((unsigned long long)b * T + t) * U1 + u) * (unsigned long long)Hj + c);
+        const unsigned int hh = sb_dropout_hash4(seed, (base >> 2) + (k >> 1));
+        v0 = sb_dropout_keep_in(hh, (2 * k) & 3, drop_thresh) ? v0 * drop_scale : 0.f;
+        v1 = sb_dropout_keep_in(hh, (2 * k + 1) & 3, drop_thresh) ? v1 * drop_scale : 0.f;
+      }
+      o[k] = __floats2bfloat162_rn(v0, v1);
     }
     *reinterpret_cast<uint4*>(h + r * Hj + c) = *reinterpret_cast<uint4*>(o);
   }
@@ -97,10 +114,10 @@ __global__ void joint_lse_gather_kernel(const float* __restrict__ z, int ldz, co
 }
 
 // alpha(t,u): one CTA per utterance, thread per u, anti-diagonal wavefront.
-__global__ void transducer_alpha_kernel(const float* __restrict__ lpb, const float* __restrict__ lpl, const float* __restrict__ lpd,
-                                        const long long* __restrict__ f_len, const long long* __restrict__ y_len,
-                                        float* __restrict__ alpha, float* __restrict__ loglik, int T, int U1, Durations du) {
-  const int b = blockIdx.x;
+__device__ __forceinline__ void transducer_alpha_body(int b, const float* __restrict__ lpb, const float* __restrict__ lpl,
+                                                      const float* __restrict__ lpd, const long long* __restrict__ f_len,
+                                                      const long long* __restrict__ y_len, float* __restrict__ alpha,
+                                                      float* __restrict__ loglik, int T, int U1, const Durations& du) {
   const int u = threadIdx.x;
   const int Tb = (int)f_len[b], Ub = (int)y_len[b];  // valid t < Tb, u <= Ub
   const long long base = (long long)b * T * U1;
@@ -121,11 +138,12 @@ __global__ void transducer_alpha_kernel(const float* __restrict__ lpb, const flo
             const long long nd = base + (long long)tp * U1 + u;
             a = log_add(a, alpha[nd] + lpb[nd] + lpd[nd * D + i]);
           }
-          if (u > 0) {
+          if (u > 0 && !du.free_label) {
             const long long nd = base + (long long)tp * U1 + u - 1;
             a = log_add(a, alpha[nd] + lpl[nd] + lpd[nd * D + i]);
           }
         }
+        if (du.free_label && u > 0) a = log_add(a, alpha[base + (long long)t * U1 + u - 1] + lpl[base + (long long)t * U1 + u - 1]);
       }
       alpha[base + (long long)t * U1 + u] = a;
     }
@@ -149,10 +167,10 @@ __global__ void transducer_alpha_kernel(const float* __restrict__ lpb, const flo
 }
 
 // beta(t,u) = log-prob of finishing from node (t,u).
-__global__ void transducer_beta_kernel(const float* __restrict__ lpb, const float* __restrict__ lpl, const float* __restrict__ lpd,
-                                       const long long* __restrict__ f_len, const long long* __restrict__ y_len,
-                                       float* __restrict__ beta, int T, int U1, Durations du) {
-  const int b = blockIdx.x;
+__device__ __forceinline__ void transducer_beta_body(int b, const float* __restrict__ lpb, const float* __restrict__ lpl,
+                                                     const float* __restrict__ lpd, const long long* __restrict__ f_len,
+                                                     const long long* __restrict__ y_len, float* __restrict__ beta, int T, int U1,
+                                                     const Durations& du) {
   const int u = threadIdx.x;
   const int Tb = (int)f_len[b], Ub = (int)y_len[b];
   const long long base = (long long)b * T * U1;
@@ -174,13 +192,25 @@ __global__ void transducer_beta_kernel(const float* __restrict__ lpb, const floa
             if (t + d == Tb && u == Ub) bt = log_add(bt, lpb[nd] + ld);
             else if (t + d < Tb) bt = log_add(bt, lpb[nd] + ld + beta[nd + (long long)d * U1]);
           }
-          if (u < Ub && t + d < Tb) bt = log_add(bt, lpl[nd] + ld + beta[nd + (long long)d * U1 + 1]);
+          if (!du.free_label && u < Ub && t + d < Tb) bt = log_add(bt, lpl[nd] + ld + beta[nd + (long long)d * U1 + 1]);
         }
+        if (du.free_label && u < Ub) bt = log_add(bt, lpl[nd] + beta[nd + 1]);
       }
       beta[nd] = bt;
     }
     __syncthreads();
   }
+}
+
+// Both recursions in one launch: blocks [0, B) run the forward variables, blocks [B, 2B) the backward variables.  Each is a
+// chain of T + U dependent steps per utterance (latency-bound, one block per utterance), so running them side by side halves
+// the time of the pair.  beta == nullptr: forward variables only (grid B).
+__global__ void transducer_alpha_beta_kernel(const float* __restrict__ lpb, const float* __restrict__ lpl, const float* __restrict__ lpd,
+                                             const long long* __restrict__ f_len, const long long* __restrict__ y_len,
+                                             float* __restrict__ alpha, float* __restrict__ beta, float* __restrict__ loglik, int B,
+                                             int T, int U1, Durations du) {
+  if ((int)blockIdx.x < B) transducer_alpha_body(blockIdx.x, lpb, lpl, lpd, f_len, y_len, alpha, loglik, T, U1, du);
+  else transducer_beta_body(blockIdx.x - B, lpb, lpl, lpd, f_len, y_len, beta, T, U1, du);
 }
 
 // Per node: gradient of the loss (-loglik * upstream) w.r.t. lp_blank, lp_label, lp_dur[d]; thread per node.
@@ -220,11 +250,13 @@ __global__ void transducer_node_grads_kernel(const float* __restrict__ lpb, cons
             if (t + d == Tb && u == Ub) occ_b = __expf(a + lpb[nd] + ld - ll);
             else if (t + d < Tb) occ_b = __expf(a + lpb[nd] + ld + beta[nd + (long long)d * U1] - ll);
           }
-          if (u < Ub && t + d < Tb) occ_l = (1.f + fastemit) * __expf(a + lpl[nd] + ld + beta[nd + (long long)d * U1 + 1] - ll);
+          if (!du.free_label && u < Ub && t + d < Tb)
+            occ_l = (1.f + fastemit) * __expf(a + lpl[nd] + ld + beta[nd + (long long)d * U1 + 1] - ll);
           g_b += up * occ_b;
           g_l += up * occ_l;
           g_d[i] = up * (occ_b + occ_l);
         }
+        if (du.free_label && u < Ub) g_l = up * (1.f + fastemit) * __expf(a + lpl[nd] + beta[nd + 1] - ll);
       }
     }
     gb[nd] = g_b;
@@ -308,6 +340,8 @@ __global__ void joint_reduce_dh_kernel(const __nv_bfloat16* __restrict__ dh, flo
 // Same gather as joint_lse_gather but from already materialised logits of the whole batch (non-fused joint path).
 Durations make_durations(const int* d, int n) {
   Durations du;
+  du.free_label = (n & SB_DURATIONS_FREE_LABEL) ? 1 : 0;
+  n &= SB_DURATIONS_FREE_LABEL - 1;
   du.n = n;
   for (int i = 0; i < MAXD; ++i) du.d[i] = i < n ? d[i] : 0;
   return du;
@@ -316,14 +350,15 @@ Durations make_durations(const int* d, int n) {
 }  // namespace
 
 SB_API int sb_joint_build_h(const void* f, const void* g, void* h, int b0, int nb, int T, int U1, int Hj, long long f_bs,
-                            long long g_bs, cudaStream_t stream) {
+                            long long g_bs, float drop_p, unsigned long long seed, cudaStream_t stream) {
   if (Hj % 8 != 0 || nb <= 0) return -1;
   const long long total = (long long)nb * T * U1 * (Hj / 8);
   long long blocks = (total + 255) / 256;
   const long long cap = (long long)sb_num_sms() * 16;
   if (blocks > cap) blocks = cap;
   joint_build_h_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)f, (const __nv_bfloat16*)g, (__nv_bfloat16*)h, b0, nb,
-                                                       T, U1, Hj, f_bs, g_bs);
+                                                       T, U1, Hj, f_bs, g_bs, sb_dropout_threshold(drop_p), sb_dropout_scale(drop_p),
+                                                       seed);
   return (int)cudaGetLastError();
 }
 
@@ -340,11 +375,10 @@ SB_API int sb_joint_lse_gather(const float* z, int ldz, const long long* targets
 SB_API int sb_transducer_alpha_beta(const float* lpb, const float* lpl, const float* lpd, const long long* f_len,
                                     const long long* y_len, float* alpha, float* beta, float* loglik, int B, int T, int U1,
                                     const int* durations, int D, cudaStream_t stream) {
-  if (U1 > 1024 || D > MAXD || B <= 0) return -1;
+  if (U1 > 1024 || (D & (SB_DURATIONS_FREE_LABEL - 1)) > MAXD || B <= 0) return -1;
   const Durations du = make_durations(durations, D);
   const int threads = (U1 + 31) / 32 * 32;
-  transducer_alpha_kernel<<<B, threads, 0, stream>>>(lpb, lpl, lpd, f_len, y_len, alpha, loglik, T, U1, du);
-  if (beta) transducer_beta_kernel<<<B, threads, 0, stream>>>(lpb, lpl, lpd, f_len, y_len, beta, T, U1, du);
+  transducer_alpha_beta_kernel<<<beta ? 2 * B : B, threads, 0, stream>>>(lpb, lpl, lpd, f_len, y_len, alpha, beta, loglik, B, T, U1, du);
   return (int)cudaGetLastError();
 }
 
@@ -352,7 +386,7 @@ SB_API int sb_transducer_node_grads(const float* lpb, const float* lpl, const fl
                                     const float* loglik, const float* upstream, const long long* f_len, const long long* y_len,
                                     float* gb, float* gl, float* gd, int B, int T, int U1, const int* durations, int D,
                                     float fastemit, cudaStream_t stream) {
-  if (D > MAXD) return -1;
+  if ((D & (SB_DURATIONS_FREE_LABEL - 1)) > MAXD) return -1;
   const Durations du = make_durations(durations, D);
   const long long total = (long long)B * T * U1;
   long long blocks = (total + 255) / 256;

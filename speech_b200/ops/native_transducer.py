@@ -26,18 +26,21 @@ def _dur_array(durations: Sequence[int]):
     return arr
 
 
-def _lattice_forward(lpb, lpl, lpd, f_len, y_len, B, T, U1, durations, need_beta: bool):
+FREE_LABEL = 256     # flag on the duration count: multi-blank arc model (see csrc/transducer.cu, struct Durations)
+
+
+def _lattice_forward(lpb, lpl, lpd, f_len, y_len, B, T, U1, durations, need_beta: bool, flag: int = 0):
     dev = lpb.device
     alpha = torch.empty((B, T, U1), dtype=torch.float32, device=dev)
     beta = torch.empty((B, T, U1), dtype=torch.float32, device=dev) if need_beta else None
     ll = torch.empty(B, dtype=torch.float32, device=dev)
     N._check(N.lib().sb_transducer_alpha_beta(N._ptr(lpb), N._ptr(lpl), N._ptr(lpd), N._ptr(f_len), N._ptr(y_len), N._ptr(alpha),
                                               N._ptr(beta), N._ptr(ll), _i(B), _i(T), _i(U1), _dur_array(durations),
-                                              _i(len(durations)), N._stream()), "sb_transducer_alpha_beta")
+                                              _i(len(durations) + flag), N._stream()), "sb_transducer_alpha_beta")
     return alpha, beta, ll
 
 
-def _node_grads(lpb, lpl, lpd, alpha, beta, ll, upstream, f_len, y_len, B, T, U1, durations, fastemit):
+def _node_grads(lpb, lpl, lpd, alpha, beta, ll, upstream, f_len, y_len, B, T, U1, durations, fastemit, flag: int = 0):
     dev = lpb.device
     D = len(durations)
     gb = torch.empty((B, T, U1), dtype=torch.float32, device=dev)
@@ -45,14 +48,14 @@ def _node_grads(lpb, lpl, lpd, alpha, beta, ll, upstream, f_len, y_len, B, T, U1
     gd = torch.empty((B, T, U1, max(D, 1)), dtype=torch.float32, device=dev)
     N._check(N.lib().sb_transducer_node_grads(N._ptr(lpb), N._ptr(lpl), N._ptr(lpd), N._ptr(alpha), N._ptr(beta), N._ptr(ll),
                                               N._ptr(upstream), N._ptr(f_len), N._ptr(y_len), N._ptr(gb), N._ptr(gl), N._ptr(gd),
-                                              _i(B), _i(T), _i(U1), _dur_array(durations), _i(D), ctypes.c_float(fastemit),
+                                              _i(B), _i(T), _i(U1), _dur_array(durations), _i(D + flag), ctypes.c_float(fastemit),
                                               N._stream()), "sb_transducer_node_grads")
     return gb, gl, gd
 
 
 class _JointLossFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, f, g, weight, bias, targets, f_len, y_len, blank, durations, sigma, fastemit):
+    def forward(ctx, f, g, weight, bias, targets, f_len, y_len, blank, durations, sigma, fastemit, drop_p=0.0):
         B, T, Hj = f.shape
         U1 = g.shape[1]
         dev = f.device
@@ -76,11 +79,14 @@ class _JointLossFn(torch.autograd.Function):
         rows_max = min(B, nb_chunk) * T * U1
         h = torch.empty((rows_max, Hj), dtype=torch.bfloat16, device=dev)
         z = torch.empty((rows_max, ldz), dtype=torch.float32, device=dev)
+        drop_p = float(drop_p)
+        seed = N._next_dropout_seed() if drop_p > 0.0 else 0
         for b0 in range(0, B, nb_chunk):
             nb = min(nb_chunk, B - b0)
             rows = nb * T * U1
             N._check(N.lib().sb_joint_build_h(N._ptr(f), N._ptr(g), N._ptr(h), _i(b0), _i(nb), _i(T), _i(U1), _i(Hj),
-                                              ctypes.c_longlong(T * Hj), ctypes.c_longlong(U1 * Hj), N._stream()), "sb_joint_build_h")
+                                              ctypes.c_longlong(T * Hj), ctypes.c_longlong(U1 * Hj), ctypes.c_float(drop_p),
+                                              ctypes.c_ulonglong(seed), N._stream()), "sb_joint_build_h")
             N.gemm(h, wl, z, M=rows, N=V, K=Hj, ldd=ldz, bias=bias)
             N._check(N.lib().sb_joint_lse_gather(N._ptr(z), _i(ldz), N._ptr(targets), _i(targets.shape[1]), N._ptr(lse_tok),
                                                  N._ptr(lse_dur), N._ptr(lpb), N._ptr(lpl), N._ptr(lpd), _i(b0), _i(nb), _i(T),
@@ -91,6 +97,7 @@ class _JointLossFn(torch.autograd.Function):
         ctx.save_for_backward(f, g, targets, f_len, y_len, lse_tok, lse_dur, lpb, lpl, lpd, alpha, beta, ll)
         ctx.weight, ctx.bias = weight, bias
         ctx.cfg = (B, T, U1, Hj, V, V1, D, blank, list(durations), fastemit, nb_chunk, ldz)
+        ctx.drop = (drop_p, seed)
         loss = -ll
         return loss * (1.0 + fastemit) if fastemit else loss
 
@@ -99,6 +106,11 @@ class _JointLossFn(torch.autograd.Function):
         f, g, targets, f_len, y_len, lse_tok, lse_dur, lpb, lpl, lpd, alpha, beta, ll = ctx.saved_tensors
         weight, bias = ctx.weight, ctx.bias
         B, T, U1, Hj, V, V1, D, blank, durations, fastemit, nb_chunk, ldz = ctx.cfg
+        drop_p, seed = ctx.drop
+        drop_scale = 1.0
+        if drop_p > 0.0:
+            t8 = min(255, int(drop_p * 256.0 + 0.5))          # the kernels' 8-bit threshold (common.cuh, sb_dropout_threshold)
+            drop_scale = 256.0 / (256.0 - t8) if t8 else 1.0
         dev = f.device
         wl = N._lowp_weight(weight)
         up = dloss.float().contiguous()
@@ -121,14 +133,15 @@ class _JointLossFn(torch.autograd.Function):
             nb = min(nb_chunk, B - b0)
             rows = nb * T * U1
             N._check(N.lib().sb_joint_build_h(N._ptr(f), N._ptr(g), N._ptr(h), _i(b0), _i(nb), _i(T), _i(U1), _i(Hj),
-                                              ctypes.c_longlong(T * Hj), ctypes.c_longlong(U1 * Hj), N._stream()), "sb_joint_build_h")
+                                              ctypes.c_longlong(T * Hj), ctypes.c_longlong(U1 * Hj), ctypes.c_float(drop_p),
+                                              ctypes.c_ulonglong(seed), N._stream()), "sb_joint_build_h")
             N.gemm(h, wl, z, M=rows, N=V, K=Hj, ldd=ldz, bias=bias)
             N._check(N.lib().sb_joint_dlogits(N._ptr(z), _i(ldz), N._ptr(targets), _i(targets.shape[1]), N._ptr(lse_tok),
                                               N._ptr(lse_dur), N._ptr(gb), N._ptr(gl), N._ptr(gd), N._ptr(dz), _i(lddz), _i(b0),
                                               _i(nb), _i(T), _i(U1), _i(V1), _i(D), _i(blank), ctypes.c_float(-1.0), N._stream()),
                      "sb_joint_dlogits")
-            # dH = dZ W, masked by relu'(h)
-            N.gemm(dz, wl, dh, M=rows, N=Hj, K=V, lda=lddz, b_mn=True, ldb=Hj, aux=h, dact="relu", ldx=Hj)
+            # dH = scale * dZ W, masked by relu'(h): dropped units are zero in h, so the same mask removes them
+            N.gemm(dz, wl, dh, M=rows, N=Hj, K=V, lda=lddz, b_mn=True, ldb=Hj, aux=h, dact="relu", ldx=Hj, alpha=drop_scale)
             # dW += dZ^T H
             N.gemm(dz, h, dW, M=V, N=Hj, K=rows, a_mn=True, lda=lddz, b_mn=True, ldb=Hj, beta=1.0)
             if dB is not None:
@@ -143,11 +156,12 @@ class _JointLossFn(torch.autograd.Function):
             if direct_b:
                 cb(bias)
         return (df.to(torch.bfloat16), dg.to(torch.bfloat16), None if direct_w else dW.view(weight.shape),
-                None if (bias is None or direct_b) else dB, None, None, None, None, None, None, None)
+                None if (bias is None or direct_b) else dB, None, None, None, None, None, None, None, None)
 
 
-def transducer_joint_loss(f, g, w, b, targets, f_len, y_len, blank, durations, sigma, fastemit_lambda=0.0):
-    """Per-utterance negative log-likelihood; f: [B,T,H], g: [B,U+1,H] (bf16), w: [V+1+D, H], b: [V+1+D]."""
+def transducer_joint_loss(f, g, w, b, targets, f_len, y_len, blank, durations, sigma, fastemit_lambda=0.0, dropout_p=0.0):
+    """Per-utterance negative log-likelihood; f: [B,T,H], g: [B,U+1,H] (bf16), w: [V+1+D, H], b: [V+1+D].  ``dropout_p`` is the
+    joint network's dropout (applied to the hidden lattice after the activation)."""
     Hj = f.shape[-1]
     if Hj % 8 != 0 or g.shape[1] > 1024 or len(durations) > 8:
         from . import reference
@@ -156,7 +170,7 @@ def transducer_joint_loss(f, g, w, b, targets, f_len, y_len, blank, durations, s
                                                fastemit_lambda, 4)
     T_max = f.shape[1]
     return _JointLossFn.apply(f, g, w, b, targets, f_len.clamp(max=T_max), y_len, int(blank), tuple(durations), float(sigma),
-                              float(fastemit_lambda))
+                              float(fastemit_lambda), float(dropout_p))
 
 
 class _LatticeLossFn(torch.autograd.Function):
@@ -204,3 +218,44 @@ def transducer_loss_from_logits(logits, targets, f_len, y_len, blank, durations,
 
         return reference.tdt_loss_from_logits(logits, targets, f_len, y_len, blank, durations, sigma)
     return _LatticeLossFn.apply(logits, targets, f_len, y_len, int(blank), tuple(durations), float(sigma))
+
+
+class _MultiBlankLatticeFn(torch.autograd.Function):
+    """Multi-blank RNNT lattice on the native wavefront kernels: ``arcs`` [B, T, U1, n] are the log-probs of the blank symbols
+    (the standard blank first), ``label`` [B, T, U1] those of the next target token; returns the negative log-likelihood per
+    utterance and, in backward, the occupancy-weighted gradients of both."""
+
+    @staticmethod
+    def forward(ctx, arcs, label, f_len, y_len, durations):
+        B, T, U1, D = arcs.shape
+        arcs, label = arcs.float().contiguous(), label.float().contiguous()
+        f_len, y_len = f_len.long().contiguous(), y_len.long().contiguous()
+        zero = torch.zeros_like(label)
+        alpha, beta, ll = _lattice_forward(zero, label, arcs, f_len, y_len, B, T, U1, durations, True, FREE_LABEL)
+        ctx.save_for_backward(zero, label, arcs, alpha, beta, ll, f_len, y_len)
+        ctx.durations = list(durations)
+        return -ll
+
+    @staticmethod
+    def backward(ctx, dloss):
+        zero, label, arcs, alpha, beta, ll, f_len, y_len = ctx.saved_tensors
+        B, T, U1, D = arcs.shape
+        _, gl, gd = _node_grads(zero, label, arcs, alpha, beta, ll, dloss.float().contiguous(), f_len, y_len, B, T, U1, ctx.durations,
+                                0.0, FREE_LABEL)
+        return gd, gl, None, None, None
+
+
+def multiblank_loss_from_logits(logits, targets, f_len, y_len, blank: int, big_blank_durations: Sequence[int], sigma: float = 0.0):
+    """Multi-blank RNNT loss (reference ``losses/rnnt.py`` ``multiblank_rnnt`` on the Numba kernels ``gpu_rnnt_kernel.py:411,570,720``):
+    the big-blank symbols sit right before the standard blank in the vocabulary; one log-softmax over all symbols, minus sigma."""
+    B, T, U1, _ = logits.shape
+    nb = len(big_blank_durations)
+    if U1 > 1024 or nb + 1 > 8:
+        from . import reference
+
+        return reference.multiblank_loss_from_logits(logits, targets, f_len, y_len, blank, big_blank_durations, sigma)
+    tok = torch.log_softmax(logits.float(), dim=-1) - sigma
+    arcs = torch.stack([tok[..., blank]] + [tok[..., blank - nb + i] for i in range(nb)], dim=-1)
+    tgt = torch.cat([targets, targets.new_zeros(B, 1)], dim=1).clamp(min=0).long()
+    label = torch.gather(tok, 3, tgt[:, None, :, None].expand(B, T, U1, 1)).squeeze(-1)
+    return _MultiBlankLatticeFn.apply(arcs, label, f_len, y_len, (1,) + tuple(int(d) for d in big_blank_durations))

@@ -264,7 +264,7 @@ def joint_logits(f, g, w, b, act: str = "relu"):
 
 
 def transducer_joint_loss(f, g, w, b, targets, f_len, y_len, blank: int, durations: Sequence[int], sigma: float,
-                          act: str = "relu", fastemit_lambda: float = 0.0, sub_batch: int = 0):
+                          act: str = "relu", fastemit_lambda: float = 0.0, sub_batch: int = 0, dropout_p: float = 0.0):
     """Joint network + RNNT/TDT negative log-likelihood per utterance, computed sub-batch by sub-batch with the
     T and U axes trimmed to the sub-batch maximum (reference fused mode: ``modules/rnnt.py:1495-1641``)."""
     B = f.shape[0]
@@ -274,7 +274,11 @@ def transducer_joint_loss(f, g, w, b, targets, f_len, y_len, blank: int, duratio
         e = min(B, s + sub_batch)
         tl = int(f_len[s:e].max())
         ul = int(y_len[s:e].max())
-        logits = joint_logits(f[s:e, :tl].float(), g[s:e, : ul + 1].float(), w.float(), None if b is None else b.float(), act)
+        if dropout_p > 0.0:
+            hid = F.dropout(act_fn(act)(f[s:e, :tl].float().unsqueeze(2) + g[s:e, : ul + 1].float().unsqueeze(1)), dropout_p, True)
+            logits = F.linear(hid, w.float(), None if b is None else b.float())
+        else:
+            logits = joint_logits(f[s:e, :tl].float(), g[s:e, : ul + 1].float(), w.float(), None if b is None else b.float(), act)
         out.append(tdt_loss_from_logits(logits, targets[s:e, :ul], f_len[s:e], y_len[s:e], blank, durations, sigma))
     loss = torch.cat(out)
     return loss * (1.0 + fastemit_lambda) if fastemit_lambda else loss

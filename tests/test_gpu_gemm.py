@@ -32,8 +32,9 @@ def test_gemm_layouts(a_mn, b_mn, M, N, K):
     nat.gemm(a, b, out, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, lda=a.stride(0), ldb=b.stride(0), ldd=Np)
     nat.check_status()
     ref = _ref(av, bv, a_mn, b_mn)
-    err = (out[:, :N] - ref).abs().max().item()
-    assert err <= 2e-2 * (K ** 0.5), f"max abs err {err}"
+    # bf16 operands are exact in fp32 and the accumulation is fp32: only the summation order differs from the reference
+    err = (out[:, :N] - ref).abs().max().item() / ref.abs().max().item()
+    assert err <= 1e-3, f"max relative err {err}"
     assert torch.isnan(out[:, N:]).all()
 
 
@@ -245,3 +246,39 @@ def test_gemm_small_m_split_k_through_scratch_matches_single_pass(M, N, K, b_mn)
     nat.gemm(a, b, one, M=M, N=N, K=K, b_mn=b_mn, bias=bias, act="swish", residual=res, alpha=0.5, ksplit=-1)
     assert (one.float() - out.float()).abs().max().item() <= 3e-2 * max(1.0, ref.abs().max().item())
     assert nat.launch_count == launches + 2
+
+
+@pytest.mark.parametrize("M,N,K,epi", [(3750, 1024, 1024, "plain"), (1000, 4096, 512, "fwd"), (777, 520, 264, "bwd")])
+def test_gemm_is_bitwise_reproducible(M, N, K, epi):
+    """Without split-K every output element is produced by one CTA in a fixed order: two runs must agree bit for bit."""
+    nat = _native()
+    torch.manual_seed(3)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda")
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    aux = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    outs = []
+    for _ in range(3):
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        if epi == "plain":
+            nat.gemm(a, b, out, M=M, N=N, K=K, ksplit=-1)
+        elif epi == "fwd":
+            nat.gemm(a, b, out, M=M, N=N, K=K, bias=bias, act="swish", residual=res, alpha=0.5, drop_p=0.1, drop_seed=1234, ksplit=-1)
+        else:
+            nat.gemm(a, b, out, M=M, N=N, K=K, aux=aux, dact="swish", residual=res, ksplit=-1)
+        torch.cuda.synchronize()
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    nat.check_status()
+
+
+def test_layernorm_and_conv_module_are_bitwise_reproducible():
+    from speech_b200 import ops
+
+    torch.manual_seed(4)
+    x = torch.randn(3760, 1024, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(1024, device="cuda")
+    b = torch.randn(1024, device="cuda")
+    y = [ops.layer_norm(x, w, b, 1e-5) for _ in range(2)]
+    assert torch.equal(y[0], y[1])

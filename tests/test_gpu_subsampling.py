@@ -84,6 +84,8 @@ def test_front_end_rows_beyond_length_do_not_influence_results():
         y.float().pow(2).sum().backward()
         outs.append((y.float().detach().clone(), mod.conv[0].weight.grad.clone()))
     t_valid = int(L[1])
-    assert torch.equal(outs[0][0][0], outs[1][0][0])
-    assert torch.equal(outs[0][0][1, :t_valid], outs[1][0][1, :t_valid])
-    assert torch.allclose(outs[0][1], outs[1][1], rtol=1e-3, atol=1e-3)
+    assert torch.equal(outs[0][0][0], outs[1][0][0]), (outs[0][0][0] - outs[1][0][0]).abs().max()
+    assert torch.equal(outs[0][0][1, :t_valid], outs[1][0][1, :t_valid]), (outs[0][0][1, :t_valid] - outs[1][0][1, :t_valid]).abs().max()
+    # gradients are accumulated with atomics (order varies): equal up to fp32 summation order
+    rel = ((outs[0][1] - outs[1][1]).norm() / outs[0][1].norm()).item()
+    assert rel < 1e-4, rel
