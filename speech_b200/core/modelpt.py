@@ -455,6 +455,9 @@ class ModelPT(nn.Module, Typing, Serialization):
                 fusion = [fg for m in self.modules() if hasattr(m, "arena_fusion_groups") for fg in m.arena_fusion_groups()]
                 optimizer = _optim.get_optimizer("fused_adamw")(groups, lr=lr, max_grad_norm=clip or 0.0,
                                                                 fusion_groups=fusion, **kwargs)
+            elif name in ("fully_sharded_adamw", "fsdp2_adamw"):
+                clip = getattr(tr, "gradient_clip_val", 0.0) if tr is not None else 0.0
+                optimizer = _optim.get_optimizer(name)(groups, model=self, lr=lr, max_grad_norm=clip or 0.0, device=self.device, **kwargs)
             else:
                 optimizer = _optim.get_optimizer(name)(groups, lr=lr, **kwargs)
         self._optimizer = optimizer

@@ -235,6 +235,16 @@ def _fused_adamw(*args, **kwargs):
     return FusedAdamW(*args, **kwargs)
 
 
+def _fully_sharded_adamw(params, model=None, **kwargs):
+    """ZeRO-3 AdamW (``parallel/fsdp2.py``); needs the model (units are modules), which ``ModelPT.setup_optimization`` passes."""
+    from ...parallel.fsdp2 import FullyShardedAdamW
+
+    if model is None:
+        raise ValueError("fully_sharded_adamw needs `model=`: construct it through ModelPT.setup_optimization or pass the module")
+    kwargs.pop("amsgrad", None)
+    return FullyShardedAdamW(model, **kwargs)
+
+
 def _sharded_adamw(*args, **kwargs):
     from ...parallel.fsdp import ShardedFusedAdamW
 
@@ -257,6 +267,8 @@ AVAILABLE_OPTIMIZERS: Dict[str, Any] = {
     "fused_adamw": _fused_adamw,
     "distributed_fused_adam": _sharded_adamw,
     "sharded_adamw": _sharded_adamw,
+    "fully_sharded_adamw": _fully_sharded_adamw,
+    "fsdp2_adamw": _fully_sharded_adamw,
 }
 
 

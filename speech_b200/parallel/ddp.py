@@ -242,6 +242,10 @@ def build_grad_sync(model, optimizers, strategy_spec, world_size: int, device: t
             except Exception as e:  # noqa: BLE001
                 logging.warning(f"peer-memory gradient exchange unavailable ({e}); using NCCL all-reduce")
         return GradSync(model, optimizers, world_size, device, sync_batchnorm=sync_batchnorm)
+    if any(type(o).__name__ == "FullyShardedAdamW" for o in optimizers):
+        from .fsdp2 import FSDP2GradSync
+
+        return FSDP2GradSync(model, optimizers, world_size, device, sync_batchnorm=sync_batchnorm)
     if kind in ("fsdp", "fsdp2", "zero", "sharded"):
         from .fsdp import ShardedGradSync
 

@@ -373,3 +373,88 @@ def test_gemm_reduce_scatter_fused_over_peer_memory(tmp_path):
     assert max(r["worst"] for r in res) < 2e-2
     print("gemm+reduce-scatter ms (fused / gemm+nccl):", max(r["fused_ms"] for r in res), max(r["nccl_ms"] for r in res))
     print("all-gather+gemm ms (fused / nccl+gemm):", max(r["ag_fused_ms"] for r in res), max(r["ag_nccl_ms"] for r in res))
+
+
+FSDP2_GPU_SCRIPT = textwrap.dedent("""
+    import os, sys, copy, json, torch, torch.distributed as dist
+    sys.path.insert(0, {repo!r})
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from speech_b200.ops import native
+    from speech_b200.parallel.fsdp2 import FullyShardedAdamW, FSDP2GradSync
+
+    class Block(torch.nn.Module):
+        def __init__(self, d):
+            super().__init__()
+            self.a = torch.nn.Linear(d, 2 * d); self.b = torch.nn.Linear(2 * d, d); self.n = torch.nn.LayerNorm(d)
+        def forward(self, x):
+            return x + self.b(torch.relu(self.a(self.n(x))))
+    class Net(torch.nn.Module):
+        def __init__(self, d=256, L=4):
+            super().__init__()
+            self.inp = torch.nn.Linear(64, d)
+            self.layers = torch.nn.ModuleList(Block(d) for _ in range(L))
+            self.head = torch.nn.Linear(d, 8)
+        def forward(self, x):
+            x = self.inp(x)
+            for l in self.layers:
+                x = l(x)
+            return self.head(x)
+
+    worst = 0.0
+    for clip in (0.0, 1.0):
+        torch.manual_seed(0)
+        ref = Net().to(dev)
+        with torch.no_grad():
+            for p in ref.parameters():
+                p.copy_(p.to(torch.bfloat16).float())         # both sides start from bf16-representable weights
+        net = copy.deepcopy(ref)
+        ref_opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, weight_decay=1e-2)
+        opt = FullyShardedAdamW(net, lr=1e-3, weight_decay=1e-2, max_grad_norm=clip, device=dev)
+        sync = FSDP2GradSync(net, [opt], world, dev)
+        for it in range(3):
+            torch.manual_seed(100 * it + rank)
+            x = torch.randn(32, 64, device=dev); y = torch.randn(32, 8, device=dev)
+            ref_opt.zero_grad()
+            (ref(x) - y).pow(2).mean().backward()
+            for p in ref.parameters():
+                dist.all_reduce(p.grad); p.grad /= world
+            if clip > 0:
+                torch.nn.utils.clip_grad_norm_(ref.parameters(), clip)
+            ref_opt.step()
+            sync.begin_step()
+            (net(x) - y).pow(2).mean().backward()
+            sync.finish_step()
+            opt.step()
+            torch.cuda.synchronize()
+        full = opt.gather_full_state()
+        for pr, pn in zip(ref.parameters(), net.parameters()):
+            worst = max(worst, float((full[id(pn)] - pr.detach()).abs().max() / pr.detach().abs().max().clamp(min=1e-3)))
+        assert sync.launched_in_backward == 4
+    native.check_status()
+    rep = opt.memory_report()
+    sys.stdout.write("RESULT " + json.dumps({{"rank": rank, "worst": worst, "frac": rep["persistent_fraction_of_replicated"]}}) + chr(10))
+    sys.stdout.flush()
+    dist.destroy_process_group()
+""")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fully_sharded_adamw_on_peer_memory_follows_replicated_adamw(tmp_path):
+    """ZeRO-3 on the peer-memory kernels (gather + up-cast, pack + reduce-scatter + AdamW) against replicated AdamW.  The sharded
+    side computes with bf16-rounded weights and exchanges bf16 gradients, so the trajectories agree to bf16 accuracy."""
+    script = tmp_path / "fsdp2_gpu.py"
+    script.write_text(FSDP2_GPU_SCRIPT.format(repo=REPO))
+    n = 2
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                          "--master-addr", "127.0.0.1", "--master-port", "29747", str(script)],
+                         capture_output=True, text=True, timeout=300, env=env)
+    assert out.returncode == 0, (out.stdout[-2000:], out.stderr[-3000:])
+    import re
+
+    res = [json.loads(m) for m in re.findall(r"RESULT (\{[^{}]*\})", out.stdout)]
+    assert len(res) == n
+    assert max(r["worst"] for r in res) < 0.02, res
