@@ -52,22 +52,41 @@ class ReduceFromTP(torch.autograd.Function):
         return g, None
 
 
+def _all_gather_dim(x: torch.Tensor, group, dim: int) -> torch.Tensor:
+    ws = dist.get_world_size(group)
+    x = x.contiguous()
+    if dim == 0 and dist.get_backend(group) == "nccl":
+        out = torch.empty((ws * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x, group=group)
+        return out
+    parts = [torch.empty_like(x) for _ in range(ws)]
+    dist.all_gather(parts, x, group=group)
+    return torch.cat(parts, dim=dim)
+
+
+def _reduce_scatter_dim(x: torch.Tensor, group, dim: int) -> torch.Tensor:
+    """Sum over the group, keep this rank's chunk along ``dim``: a true reduce-scatter on NCCL (each rank receives 1/W of the
+    data); gloo has none, so CPU tests reduce everything and slice."""
+    ws, r = dist.get_world_size(group), dist.get_rank(group)
+    if dist.get_backend(group) == "nccl":
+        xs = x.movedim(dim, 0).contiguous()
+        out = torch.empty((xs.shape[0] // ws,) + tuple(xs.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, xs, group=group)
+        return out.movedim(0, dim).contiguous()
+    return _all_reduce(x.clone(), group).chunk(ws, dim=dim)[r].contiguous()
+
+
 class GatherFromSP(torch.autograd.Function):
     """All-gather along the sequence dim forward, reduce-scatter backward."""
 
     @staticmethod
     def forward(ctx, x, group, dim):
         ctx.group, ctx.dim = group, dim
-        ws = dist.get_world_size(group)
-        parts = [torch.empty_like(x) for _ in range(ws)]
-        dist.all_gather(parts, x.contiguous(), group=group)
-        return torch.cat(parts, dim=dim)
+        return _all_gather_dim(x, group, dim)
 
     @staticmethod
     def backward(ctx, g):
-        ws, r = dist.get_world_size(ctx.group), dist.get_rank(ctx.group)
-        g = _all_reduce(g.clone(), ctx.group)
-        return g.chunk(ws, dim=ctx.dim)[r].contiguous(), None, None
+        return _reduce_scatter_dim(g, ctx.group, ctx.dim), None, None
 
 
 class ReduceScatterToSP(torch.autograd.Function):
@@ -76,16 +95,109 @@ class ReduceScatterToSP(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group, dim):
         ctx.group, ctx.dim = group, dim
+        return _reduce_scatter_dim(x, group, dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _all_gather_dim(g, ctx.group, ctx.dim), None, None
+
+
+class ScatterToSP(torch.autograd.Function):
+    """Keep this rank's chunk of a replicated tensor along ``dim`` (entry of the sequence-parallel region); all-gather backward."""
+
+    @staticmethod
+    def forward(ctx, x, group, dim):
+        ctx.group, ctx.dim = group, dim
         ws, r = dist.get_world_size(group), dist.get_rank(group)
-        x = _all_reduce(x.clone(), group)
         return x.chunk(ws, dim=dim)[r].contiguous()
 
     @staticmethod
     def backward(ctx, g):
-        ws = dist.get_world_size(ctx.group)
-        parts = [torch.empty_like(g) for _ in range(ws)]
-        dist.all_gather(parts, g.contiguous(), group=ctx.group)
-        return torch.cat(parts, dim=ctx.dim), None, None
+        return _all_gather_dim(g, ctx.group, ctx.dim), None, None
+
+
+class GatherFromSPReplicated(torch.autograd.Function):
+    """All-gather forward; the gathered tensor is consumed identically on every rank (replicated loss), so the backward keeps
+    this rank's chunk of the (identical) gradient."""
+
+    @staticmethod
+    def forward(ctx, x, group, dim):
+        ctx.group, ctx.dim = group, dim
+        return _all_gather_dim(x, group, dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        ws, r = dist.get_world_size(ctx.group), dist.get_rank(ctx.group)
+        return g.chunk(ws, dim=ctx.dim)[r].contiguous(), None, None
+
+
+class FusedColumnParallelFn(torch.autograd.Function):
+    """``y = all_gather_rows(x_local) @ w_local^T`` as ONE kernel over peer memory (``parallel.fused.AllGatherGemm``: remote row
+    shards are copied once by the GEMM's own idle warps while the tensor pipe works on the local rows), and its backward
+    ``dx_local = reduce_scatter_rows(dy @ w_local)`` as ONE kernel too (``GemmReduceScatter``: the epilogue adds every tile into
+    the owner rank's accumulator over NVLink).  The weight gradient needs the gathered input once more (NCCL all-gather)."""
+
+    @staticmethod
+    def forward(ctx, x_local, weight, bias, ops_pair):
+        ag, rs = ops_pair
+        from ..ops import lowp
+
+        wl = lowp(weight, torch.bfloat16)
+        y = ag(x_local.contiguous(), wl.contiguous(), bias=bias)
+        ctx.save_for_backward(x_local)
+        ctx.weight, ctx.bias, ctx.pair = weight, bias, ops_pair
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x_local,) = ctx.saved_tensors
+        ag, rs = ctx.pair
+        weight, bias = ctx.weight, ctx.bias
+        from ..ops import lowp, native
+
+        wl = lowp(weight, torch.bfloat16).contiguous()        # [N_local, K]
+        dy = dy.contiguous()
+        # dx [rows, K] = dy [rows, N_local] @ w [N_local, K]: the "weight" of that GEMM is w^T, i.e. w read MN-major
+        dx_local = rs(dy, wl.t().contiguous(), out_dtype=torch.bfloat16)
+        x_full = _all_gather_dim(x_local, ag.group, 0)
+        N, K = wl.shape
+        dw = torch.zeros((N, K), dtype=torch.float32, device=dy.device)
+        native.gemm(dy, x_full, dw, M=N, N=K, K=dy.shape[0], a_mn=True, lda=dy.stride(0), b_mn=True, ldb=x_full.stride(0), beta=1.0)
+        db = dy.float().sum(0) if bias is not None else None
+        return dx_local, dw.to(weight.dtype), db, None
+
+
+class FusedRowParallelFn(torch.autograd.Function):
+    """``y_local = reduce_scatter_rows(x @ w_local^T)`` (one GEMM + reduce-scatter kernel) with backward
+    ``dx = all_gather_rows(dy_local) @ w_local`` (one all-gather + GEMM kernel)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, ops_pair):
+        ag, rs = ops_pair
+        from ..ops import lowp
+
+        wl = lowp(weight, torch.bfloat16).contiguous()        # [N, K_local]
+        y_local = rs(x.contiguous(), wl, out_dtype=torch.bfloat16)
+        ctx.save_for_backward(x)
+        ctx.weight, ctx.pair = weight, ops_pair
+        return y_local
+
+    @staticmethod
+    def backward(ctx, dy_local):
+        (x,) = ctx.saved_tensors
+        ag, rs = ctx.pair
+        weight = ctx.weight
+        from ..ops import lowp, native
+
+        wl = lowp(weight, torch.bfloat16).contiguous()        # [N, K_local]
+        dy_local = dy_local.contiguous()
+        # dx [rows, K_local] = gather(dy) [rows, N] @ w [N, K_local]: the GEMM's weight argument is w^T [K_local, N]
+        dx = ag(dy_local, wl.t().contiguous())
+        dy_full = _all_gather_dim(dy_local, ag.group, 0)
+        N, K = wl.shape
+        dw = torch.zeros((N, K), dtype=torch.float32, device=x.device)
+        native.gemm(dy_full, x, dw, M=N, N=K, K=x.shape[0], a_mn=True, lda=dy_full.stride(0), b_mn=True, ldb=x.stride(0), beta=1.0)
+        return dx, dw.to(weight.dtype), None
 
 
 def _shard_linear(lin: nn.Linear, dim: int, rank: int, ws: int) -> None:
@@ -105,7 +217,12 @@ def _shard_linear(lin: nn.Linear, dim: int, rank: int, ws: int) -> None:
 
 
 def apply_tensor_parallel_llm(llm, group, sequence_parallel: bool = False) -> None:
-    """Shard every decoder layer of ``speechlm.llm.CausalLM`` over ``group`` in place."""
+    """Shard every decoder layer of ``speechlm.llm.CausalLM`` over ``group`` in place.
+
+    ``sequence_parallel``: the residual stream between blocks is sharded along the sequence (dim 1): the embeddings are
+    scattered on entry, every norm works on its shard, the normalised shard is all-gathered in front of the column-parallel
+    projections, the row-parallel projections end in a reduce-scatter, and the final hidden states are gathered in front of the
+    output head (the reference's plan: ``salm.py:459-532``, ``SequenceParallel`` norms, ``Colwise`` / ``Rowwise`` linears)."""
     ws, r = dist.get_world_size(group), dist.get_rank(group)
     if ws == 1:
         return
@@ -119,8 +236,29 @@ def apply_tensor_parallel_llm(llm, group, sequence_parallel: bool = False) -> No
         for lin in (att.o_proj, mlp.down_proj):
             _shard_linear(getattr(lin, "base", lin), 1, r, ws)
         att.n_q, att.n_kv = cfg.num_attention_heads // ws, cfg.num_key_value_heads // ws
-        layer.tp_reduce = (lambda x, g=group: ReduceFromTP.apply(x, g))
-        _wrap_inputs(layer, group)
+        if sequence_parallel:
+            layer.tp_reduce = (lambda x, g=group: ReduceScatterToSP.apply(x, g, 1))
+            for norm in (layer.input_layernorm, layer.post_attention_layernorm):
+                fwd = norm.forward
+                norm.forward = (lambda x, f=fwd, g=group: GatherFromSP.apply(f(x), g, 1))
+                for p in norm.parameters():
+                    p._sequence_parallel = True       # gradients of shard-wise norms are partial: summed over the group
+        else:
+            layer.tp_reduce = (lambda x, g=group: ReduceFromTP.apply(x, g))
+            _wrap_inputs(layer, group)
+    if sequence_parallel:
+        llm.model.sp_scatter = (lambda x, g=group: ScatterToSP.apply(x, g, 1))
+        llm.model.sp_gather = (lambda x, g=group: GatherFromSPReplicated.apply(x, g, 1))
+        for p in llm.model.norm.parameters():
+            p._sequence_parallel = True
+
+
+def allreduce_sequence_parallel_grads(module: nn.Module, group) -> None:
+    """Sum the gradients of parameters that saw only a sequence shard (norm weights) over the tensor-parallel group; call after
+    backward, before the optimizer step."""
+    for p in module.parameters():
+        if getattr(p, "_sequence_parallel", False) and p.grad is not None:
+            dist.all_reduce(p.grad, group=group)
 
 
 def _wrap_inputs(layer, group) -> None:

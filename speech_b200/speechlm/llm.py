@@ -238,6 +238,11 @@ class CausalLM(nn.Module):
                 position_ids = torch.arange(past, past + T, device=x.device).unsqueeze(0).expand(B, T)
         cos, sin = rope_tables(position_ids, self.config.dh, self.config.rope_theta)
         mask = self.build_mask(attention_mask, T, past + T, x.dtype, x.device, seq_ids)
+        sp = getattr(self.model, "sp_scatter", None) is not None and cache is None
+        if sp:
+            # sequence parallelism: the residual stream lives as [B, T / W, H] between blocks (positions, mask and rotary tables
+            # above refer to the full sequence, which the blocks see after their all-gather)
+            x = self.model.sp_scatter(x)
         for li, layer in enumerate(self.model.layers):
             c = cache[li] if cache is not None else None
             if self.gradient_checkpointing and self.training and c is None:
@@ -245,6 +250,8 @@ class CausalLM(nn.Module):
             else:
                 x = layer(x, cos, sin, mask, c)
         x = self.model.norm(x)
+        if sp:
+            x = self.model.sp_gather(x)
         out = {"hidden_states": x, "cache": cache}
         if not return_hidden:
             out["logits"] = self.lm_head(x)

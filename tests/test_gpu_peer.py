@@ -458,3 +458,74 @@ def test_fully_sharded_adamw_on_peer_memory_follows_replicated_adamw(tmp_path):
     res = [json.loads(m) for m in re.findall(r"RESULT (\{[^{}]*\})", out.stdout)]
     assert len(res) == n
     assert max(r["worst"] for r in res) < 0.02, res
+
+
+TP_FUSED_SCRIPT = textwrap.dedent("""
+    import os, sys, json, torch, torch.distributed as dist
+    sys.path.insert(0, {repo!r})
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from speech_b200.ops import native
+    from speech_b200.parallel.fused import AllGatherGemm, GemmReduceScatter
+    from speech_b200.parallel.tp import FusedColumnParallelFn, FusedRowParallelFn
+    pair = (AllGatherGemm(512, 2048, dev), GemmReduceScatter(512, 2048, dev))
+    def rel(a, b): return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp(min=1e-6))
+    worst = 0.0
+    # column-parallel: y = gather(x_local) w^T
+    rows, K, Nl = 256, 512, 384
+    torch.manual_seed(10 + rank)
+    x_local = torch.randn(rows, K, device=dev).to(torch.bfloat16).requires_grad_(True)
+    w = torch.nn.Parameter((torch.randn(Nl, K, device=dev) * 0.05))
+    b = torch.nn.Parameter(torch.randn(Nl, device=dev))
+    dy = torch.randn(rows * world, Nl, device=dev).to(torch.bfloat16)
+    y = FusedColumnParallelFn.apply(x_local, w, b, pair)
+    y.backward(dy)
+    parts = [torch.empty_like(x_local) for _ in range(world)]
+    dist.all_gather(parts, x_local.detach())
+    x_full = torch.cat(parts).float()
+    wq = w.detach().to(torch.bfloat16).float()
+    y_ref = x_full @ wq.t() + b.detach()
+    dx_full = dy.float() @ wq
+    dx_ref = torch.empty(rows, K, device=dev)
+    dist.reduce_scatter_tensor(dx_ref, dx_full)
+    worst = max(worst, rel(y, y_ref), rel(x_local.grad, dx_ref), rel(w.grad, dy.float().t() @ x_full), rel(b.grad, dy.float().sum(0)))
+    # row-parallel: y_local = reduce_scatter(x w_local^T)
+    M, Kl, N = 256 * world, 256, 384
+    torch.manual_seed(20 + rank)
+    x = torch.randn(M, Kl, device=dev).to(torch.bfloat16).requires_grad_(True)
+    w2 = torch.nn.Parameter((torch.randn(N, Kl, device=dev) * 0.05))
+    dyl = torch.randn(M // world, N, device=dev).to(torch.bfloat16)
+    yl = FusedRowParallelFn.apply(x, w2, pair)
+    yl.backward(dyl)
+    w2q = w2.detach().to(torch.bfloat16).float()
+    full = x.detach().float() @ w2q.t()
+    y2_ref = torch.empty(M // world, N, device=dev)
+    dist.reduce_scatter_tensor(y2_ref, full)
+    dparts = [torch.empty_like(dyl) for _ in range(world)]
+    dist.all_gather(dparts, dyl)
+    dy_full = torch.cat(dparts).float()
+    worst = max(worst, rel(yl, y2_ref), rel(x.grad, dy_full @ w2q), rel(w2.grad, dy_full.t() @ x.detach().float()))
+    torch.cuda.synchronize()
+    native.check_status()
+    sys.stdout.write("RESULT " + json.dumps({{"rank": rank, "worst": worst}}) + chr(10)); sys.stdout.flush()
+    dist.destroy_process_group()
+""")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_tensor_parallel_linears_forward_and_backward(tmp_path):
+    """Column- and row-parallel linears on the fused all-gather + GEMM / GEMM + reduce-scatter kernels, forward and backward,
+    against NCCL collectives around fp32 matmuls."""
+    script = tmp_path / "tp_fused.py"
+    script.write_text(TP_FUSED_SCRIPT.format(repo=REPO))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29749", str(script)],
+                         capture_output=True, text=True, timeout=300, env=env)
+    assert out.returncode == 0, (out.stdout[-2000:], out.stderr[-3000:])
+    import re
+
+    res = [json.loads(m) for m in re.findall(r"RESULT (\{[^{}]*\})", out.stdout)]
+    assert len(res) == 2 and max(r["worst"] for r in res) < 0.02, res

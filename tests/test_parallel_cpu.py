@@ -30,6 +30,21 @@ SCRIPT = textwrap.dedent("""
     g_ref = ref.model.layers[0].self_attn.q_proj.weight.grad.chunk(2, 0)[mesh.rank("tp")]
     assert torch.allclose(g_ref, tp.model.layers[0].self_attn.q_proj.weight.grad, atol=1e-6)
     assert torch.allclose(ref.model.embed_tokens.weight.grad, tp.model.embed_tokens.weight.grad, atol=1e-6)
+    # sequence parallelism on top: residual stream sharded over the sequence, same logits and gradients
+    from speech_b200.parallel.tp import allreduce_sequence_parallel_grads
+    sp = CausalLM(cfg); sp.load_state_dict(ref.state_dict())
+    apply_tensor_parallel_llm(sp, mesh.group("tp"), sequence_parallel=True)
+    ids8 = torch.randint(0, 64, (2, 8))
+    ref.zero_grad()
+    a8 = ref(input_ids=ids8)["logits"]; c8 = sp(input_ids=ids8)["logits"]
+    assert torch.allclose(a8, c8, atol=1e-5), (a8 - c8).abs().max()
+    a8.pow(2).mean().backward(); c8.pow(2).mean().backward()
+    allreduce_sequence_parallel_grads(sp, mesh.group("tp"))
+    g_ref = ref.model.layers[1].mlp.down_proj.weight.grad.chunk(2, 1)[mesh.rank("tp")]
+    assert torch.allclose(g_ref, sp.model.layers[1].mlp.down_proj.weight.grad, atol=1e-6)
+    assert torch.allclose(ref.model.layers[0].input_layernorm.weight.grad, sp.model.layers[0].input_layernorm.weight.grad, atol=1e-6)
+    assert torch.allclose(ref.model.norm.weight.grad, sp.model.norm.weight.grad, atol=1e-6)
+    assert torch.allclose(ref.model.embed_tokens.weight.grad, sp.model.embed_tokens.weight.grad, atol=1e-6)
     # vocab-parallel CE
     lg = torch.randn(3, 5, 64); tg = torch.randint(0, 64, (3, 5)); tg[0, 0] = -100
     full = torch.nn.functional.cross_entropy(lg.view(-1, 64), tg.view(-1), ignore_index=-100, reduction="none").view(3, 5)
