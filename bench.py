@@ -51,6 +51,9 @@ def parse_args():
     ap.add_argument("--batch-seconds", type=float, default=300.0)
     ap.add_argument("--dropout", type=float, default=0.1)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--config", default="tdt", choices=["tdt", "canary_fsdp"],
+                    help="tdt: Parakeet-TDT-0.6B-shape, data parallel (the headline); canary_fsdp: Canary-1B-v2-shape AED, fully sharded "
+                         "(ZeRO-3) at N > 1, ~600 s of 5-40 s audio per GPU")
     return ap.parse_args()
 
 
@@ -106,16 +109,18 @@ def make_batches(args, rank: int, world: int, vocab: int):
     import torch
 
     g = np.random.default_rng(1234 + rank)
+    canary = getattr(args, "config", "tdt") == "canary_fsdp"
     n_utts = 400
-    durs = g.uniform(10.0, 20.0, size=n_utts)
-    edges = np.arange(11.0, 20.0 + 1e-6, 1.0)
+    lo, hi = (5.0, 40.0) if canary else (10.0, 20.0)
+    durs = g.uniform(lo, hi, size=n_utts)
+    edges = np.arange(lo + (5.0 if canary else 1.0), hi + 1e-6, 5.0 if canary else 1.0)
     bucket = np.searchsorted(edges, durs, side="right")
     batches = []
     for b in range(len(edges) + 1):
         idx = np.nonzero(bucket == b)[0]
         if len(idx) == 0:
             continue
-        top = float(edges[b]) if b < len(edges) else 20.0
+        top = float(edges[b]) if b < len(edges) else hi
         per = max(1, int(args.batch_seconds // top))
         for s in range(0, len(idx) - per + 1, per):
             batches.append(idx[s:s + per])
@@ -126,11 +131,15 @@ def make_batches(args, rank: int, world: int, vocab: int):
         lens = (durs[ids] * 16000).astype(np.int64)
         L = int(lens.max())
         audio = torch.zeros(len(ids), L, dtype=torch.float32)
-        ntok = np.maximum(1, np.round(durs[ids] * 3.0)).astype(np.int64)
+        ntok = np.maximum(1, np.round(durs[ids] * 3.0)).astype(np.int64) + (6 if canary else 0)
         toks = torch.zeros(len(ids), int(ntok.max()), dtype=torch.long)
         for i, (n, u) in enumerate(zip(lens, ntok)):
             audio[i, :n] = torch.from_numpy((g.standard_normal(n) * 0.1).astype(np.float32))
-            toks[i, :u] = torch.from_numpy(g.integers(0, vocab, size=u))
+            if canary:    # six task / language tokens out of 32 special ids, then the transcript
+                toks[i, :6] = torch.from_numpy(g.integers(1, 33, size=6))
+                toks[i, 6:u] = torch.from_numpy(g.integers(33, vocab, size=u - 6))
+            else:
+                toks[i, :u] = torch.from_numpy(g.integers(0, vocab, size=u))
         batch = (audio, torch.from_numpy(lens), toks, torch.from_numpy(ntok))
         if torch.cuda.is_available():
             batch = tuple(t.pin_memory() for t in batch)
@@ -331,10 +340,22 @@ def main():
     if args.impl == "native":
         ops.native.load()
     torch.manual_seed(0)
-    vocab = 1024
-    cfg = fastconformer_transducer_config(args.size, vocab_size=vocab, dropout=args.dropout, loss="tdt", durations=(0, 1, 2, 3, 4),
-                                          sigma=0.02, n_layers=args.layers, lr=5.0, sched="noam")
-    model = EncDecRNNTBPEModel(cfg)
+    canary = args.config == "canary_fsdp"
+    if canary:
+        from speech_b200.models.aed_models import EncDecMultiTaskModel
+        from speech_b200.models.configs import canary_aed_config
+
+        vocab = 16384
+        if args.batch_seconds == 300.0:
+            args.batch_seconds = 600.0
+        cfg = canary_aed_config("xlarge", enc_layers=args.layers or 32, vocab_size=vocab, dropout=args.dropout,
+                                optim_name="fully_sharded_adamw" if world > 1 else "adamw")
+        model = EncDecMultiTaskModel(cfg)
+    else:
+        vocab = 1024
+        cfg = fastconformer_transducer_config(args.size, vocab_size=vocab, dropout=args.dropout, loss="tdt", durations=(0, 1, 2, 3, 4),
+                                              sigma=0.02, n_layers=args.layers, lr=5.0, sched="noam")
+        model = EncDecRNNTBPEModel(cfg)
     data = make_batches(args, rank, world, vocab)
     batches = [b for b, _ in data]
     durations = [d for _, d in data]
@@ -413,7 +434,11 @@ def main():
     args.warmup, args.steps = saved
     total_steps = args.warmup + args.steps
     allreduce_check = None
-    if world > 1:
+    if world > 1 and canary:
+        gs = None
+        if type(run.trainer.grad_sync).__name__ != "FSDP2GradSync":
+            raise SystemExit(f"bench.py: strategy is {type(run.trainer.grad_sync).__name__}, not the fully-sharded engine")
+    elif world > 1:
         gs = run.trainer.grad_sync
         if type(gs).__name__ != "PeerGradSync":
             if os.environ.get("SPEECH_B200_PEER_ALLREDUCE", "1") == "1":
@@ -454,16 +479,19 @@ def main():
         ops.native.check_status()
     if rank == 0:
         out = {
-            "metric": "TDT-0.6B train audio-sec/s", "value": round(value, 2), "unit": "audio-seconds/s", "n_gpus": world,
+            "metric": "Canary-1B AED train audio-sec/s" if canary else "TDT-0.6B train audio-sec/s", "value": round(value, 2),
+            "unit": "audio-seconds/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": args.impl,
-            "config": {"model": f"FastConformer-{args.size}-TDT (24L d1024 8h ffn4096 k9, 2xLSTM640, joint640, vocab1024, "
-                                f"durations 0-4, sigma 0.02)" if args.layers is None else f"DEBUG layers={args.layers}",
-                       "global_batch": f"~{args.batch_seconds:.0f} s audio per GPU (15-27 utterances of 10-20 s)",
-                       "seq_len": "10-20 s audio = 125-250 encoder frames, 30-60 tokens",
-                       "parallelism": f"dp{world}", "dropout": args.dropout,
-                       "prednet_dropout": float(cfg.decoder.prednet.get("dropout", 0.0)),
-                       "joint_dropout": float(cfg.joint.jointnet.get("dropout", 0.0)),
+            "config": {"model": (("Canary-1B-v2 shape: FastConformer 32L d1024 8h ffn4096 k9 + Transformer decoder 8L d1024 16h ffn4096, vocab 16384, "
+                                  "label smoothing 0.1") if canary else
+                                 (f"FastConformer-{args.size}-TDT (24L d1024 8h ffn4096 k9, 2xLSTM640, joint640, vocab1024, "
+                                  f"durations 0-4, sigma 0.02)")) if args.layers is None else f"DEBUG layers={args.layers}",
+                       "global_batch": f"~{args.batch_seconds:.0f} s audio per GPU" + ("" if canary else " (15-27 utterances of 10-20 s)"),
+                       "seq_len": "5-40 s audio, 6 prompt + ~3 tokens/s" if canary else "10-20 s audio = 125-250 encoder frames, 30-60 tokens",
+                       "parallelism": (f"fsdp2 (ZeRO-3) over {world}" if (canary and world > 1) else f"dp{world}"), "dropout": args.dropout,
+                       "prednet_dropout": None if canary else float(cfg.decoder.prednet.get("dropout", 0.0)),
+                       "joint_dropout": None if canary else float(cfg.joint.jointnet.get("dropout", 0.0)),
                        "grad_exchange": (f"{type(run.trainer.grad_sync).__name__}: {run.trainer.grad_sync.launched_in_backward} of "
                                          f"{len(run.trainer.grad_sync.buckets)} buckets launched during backward"
                                          + (f", {run.trainer.grad_sync.reducer.ctas} CTAs" if hasattr(run.trainer.grad_sync, "reducer") else ""))
@@ -475,6 +503,8 @@ def main():
         }
         if allreduce_check is not None:
             out["allreduce_check"] = allreduce_check
+        if canary and world > 1:
+            out["fsdp_memory"] = run.trainer.optimizers[0].memory_report()
         if not args.no_e2e:
             out["e2e"] = {"value": round(audio2 / (ms2 / 1e3), 2), "unit": "audio-seconds/s", "h2d_bytes_per_step": int(h2d),
                           "d2h_bytes_per_step": 4, "ms_per_step": round(ms2 / args.steps, 3)}

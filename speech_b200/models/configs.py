@@ -106,3 +106,35 @@ def fastconformer_transducer_config(size: str = "xlarge", vocab_size: int = 1024
                                       "num_classes": -1, "vocabulary": []},
                           "decoding": {"strategy": "greedy_batch"}}
     return OmegaConf.create(cfg)
+
+
+def canary_aed_config(size: str = "xlarge", enc_layers: int = 32, dec_layers: int = 8, dec_hidden: int = 1024, dec_heads: int = 16,
+                      dec_inner: int = 4096, vocab_size: int = 16384, features: int = 80, dropout: float = 0.1,
+                      label_smoothing: float = 0.1, lr: float = 3e-4, optim_name: str = "adamw",
+                      tokenizer: Optional[Dict[str, Any]] = None, max_sequence_length: int = 1024, **enc_over) -> DictConfig:
+    """Canary-1B-v2-shape attention encoder-decoder (reference ``examples/asr/conf/speech_multitask/fast-conformer_aed.yaml``):
+    FastConformer encoder, Transformer decoder with cross-attention and learned positions, tied output head, label-smoothed
+    cross entropy."""
+    s = FASTCONFORMER_SIZES[size]
+    tok = tokenizer or {"type": "synthetic", "vocab_size": vocab_size}
+    optim = optim_cfg(lr, None, s["d_model"])
+    optim["name"] = optim_name
+    return OmegaConf.create({
+        "sample_rate": 16000, "log_prediction": False, "prompt_format": "canary2", "use_loss_mask_for_prompt": False,
+        "model_defaults": {"asr_enc_hidden": s["d_model"], "lm_dec_hidden": dec_hidden},
+        "tokenizer": tok,
+        "preprocessor": preprocessor_cfg(features),
+        "spec_augment": None,
+        "encoder": encoder_cfg(size, features, dropout, dropout, n_layers=enc_layers, **enc_over),
+        "transf_decoder": {"_target_": "speech_b200.modules.transformer_nm.get_transformer", "library": "nemo", "encoder": False,
+                           "pre_ln_final_layer_norm": True,
+                           "config_dict": {"max_sequence_length": max_sequence_length, "num_token_types": 0, "embedding_dropout": dropout,
+                                           "learn_positional_encodings": True, "hidden_size": dec_hidden, "inner_size": dec_inner,
+                                           "num_layers": dec_layers, "num_attention_heads": dec_heads, "ffn_dropout": dropout,
+                                           "attn_score_dropout": dropout, "attn_layer_dropout": dropout, "hidden_act": "relu",
+                                           "pre_ln": True, "vocab_size": vocab_size}},
+        "head": {"num_layers": 1, "activation": "relu", "log_softmax": True, "dropout": 0.0},
+        "loss": {"label_smoothing": label_smoothing},
+        "decoding": {"strategy": "greedy", "greedy": {"max_generation_delta": 50}},
+        "optim": optim,
+    })

@@ -230,6 +230,11 @@ def build_grad_sync(model, optimizers, strategy_spec, world_size: int, device: t
     if world_size <= 1 or not dist.is_initialized():
         return None
     kind = strategy_spec if isinstance(strategy_spec, str) else getattr(strategy_spec, "kind", "auto")
+    if any(type(o).__name__ == "FullyShardedAdamW" for o in optimizers):
+        # a fully-sharded optimizer brings its own gradient path (reduce-scatter per unit), whatever the strategy string says
+        from .fsdp2 import FSDP2GradSync
+
+        return FSDP2GradSync(model, optimizers, world_size, device, sync_batchnorm=sync_batchnorm)
     if kind in ("auto", "ddp", "ddp_find_unused_parameters_true", "nccl"):
         use_peer = device.type == "cuda" and os.environ.get("SPEECH_B200_PEER_ALLREDUCE", "1") == "1"
         if use_peer and kind != "nccl":
@@ -242,10 +247,6 @@ def build_grad_sync(model, optimizers, strategy_spec, world_size: int, device: t
             except Exception as e:  # noqa: BLE001
                 logging.warning(f"peer-memory gradient exchange unavailable ({e}); using NCCL all-reduce")
         return GradSync(model, optimizers, world_size, device, sync_batchnorm=sync_batchnorm)
-    if any(type(o).__name__ == "FullyShardedAdamW" for o in optimizers):
-        from .fsdp2 import FSDP2GradSync
-
-        return FSDP2GradSync(model, optimizers, world_size, device, sync_batchnorm=sync_batchnorm)
     if kind in ("fsdp", "fsdp2", "zero", "sharded"):
         from .fsdp import ShardedGradSync
 

@@ -193,7 +193,10 @@ class FullyShardedAdamW(Optimizer):
             self.param_buf.barrier()          # every rank's slices are in place before anybody gathers them
 
     # ------------------------------------------------------------------ gather / free
-    def _views(self, u: _Unit, f32: torch.Tensor, lowp: Optional[torch.Tensor], grad: Optional[torch.Tensor]) -> None:
+    def _views(self, u: _Unit, f32: torch.Tensor, lowp: Optional[torch.Tensor], grad: Optional[torch.Tensor], attach: bool = True) -> None:
+        """Point the unit's parameters at their gathered images.  ``grad``: the unit's gradient slot; with ``attach`` it also
+        becomes ``parameter.grad`` (autograd accumulates into it), otherwise only the kernels' ``_grad_view`` is set (its address
+        is fixed per unit, and the whole-layer executor records it when it first meets the layer, in forward)."""
         for p in u.params:
             o, n = u.offsets[id(p)]
             shape = self._shape_of(p)
@@ -202,7 +205,8 @@ class FullyShardedAdamW(Optimizer):
                 p._lowp = lowp[o:o + n].view(shape)
             if grad is not None:
                 p._grad_view = grad[o:o + n].view(shape)
-                p.grad = p._grad_view
+                if attach:
+                    p.grad = p._grad_view
             p._arena = self
 
     def _shape_of(self, p) -> Tuple[int, ...]:
@@ -241,7 +245,7 @@ class FullyShardedAdamW(Optimizer):
                 lowp[:n].copy_(f32[:n])
             u.ready_event = None
         u.gathered = True
-        self._views(u, f32, lowp, None)
+        self._views(u, f32, lowp, self.root_grad if u is self.root else self.pool_grad[u.index % 2], attach=False)
 
     def _wait_gathered(self, u: _Unit) -> None:
         ev = getattr(u, "ready_event", None)
@@ -461,6 +465,12 @@ class FSDP2GradSync:
         for p in (q for b in self.buckets for q in b["params"]):
             p.register_post_accumulate_grad_hook(lambda param: self.mark_ready(param))
         self.launched_in_backward = 0
+        if sync_batchnorm:
+            from .ddp import small_allreduce
+
+            for m in model.modules():
+                if hasattr(m, "bn_stats_reduce"):
+                    m.bn_stats_reduce = small_allreduce
 
     def begin_step(self):
         self.opt.begin_step()

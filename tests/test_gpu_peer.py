@@ -430,8 +430,14 @@ FSDP2_GPU_SCRIPT = textwrap.dedent("""
             opt.step()
             torch.cuda.synchronize()
         full = opt.gather_full_state()
-        for pr, pn in zip(ref.parameters(), net.parameters()):
-            worst = max(worst, float((full[id(pn)] - pr.detach()).abs().max() / pr.detach().abs().max().clamp(min=1e-3)))
+        # Adam's first steps move every element by about lr whatever the gradient's size, so elements whose gradient is within
+        # bf16 noise of zero may step the other way: compare all parameters together (relative L2) and bound single elements by
+        # the distance two opposite trajectories can reach
+        num = sum(float((full[id(pn)] - pr.detach()).pow(2).sum()) for pr, pn in zip(ref.parameters(), net.parameters()))
+        den = sum(float(pr.detach().pow(2).sum()) for pr in ref.parameters())
+        worst = max(worst, (num / den) ** 0.5)
+        worst_abs = max(float((full[id(pn)] - pr.detach()).abs().max()) for pr, pn in zip(ref.parameters(), net.parameters()))
+        assert worst_abs < 2.5 * 1e-3 * 3, worst_abs
         assert sync.launched_in_backward == 4
     native.check_status()
     rep = opt.memory_report()
@@ -457,7 +463,7 @@ def test_fully_sharded_adamw_on_peer_memory_follows_replicated_adamw(tmp_path):
 
     res = [json.loads(m) for m in re.findall(r"RESULT (\{[^{}]*\})", out.stdout)]
     assert len(res) == n
-    assert max(r["worst"] for r in res) < 0.02, res
+    assert max(r["worst"] for r in res) < 5e-3, res
 
 
 TP_FUSED_SCRIPT = textwrap.dedent("""
