@@ -44,6 +44,8 @@ SB_API int sb_dwconv_glu_bwd(const void* ds, const void* y, const void* g, const
 SB_API int sb_scale_dact_dropout(const void* dy, long long ld_dy, const void* z, void* dz, int rows, int N, int act, float alpha,
                                  float drop_p, unsigned long long seed, cudaStream_t stream);
 SB_API int sb_colsum_bf16(const void* x, long long ld, int rows, int N, float* out, cudaStream_t stream);
+SB_API int sb_scale_dact_dropout_bias(const void* dy, long long ld_dy, const void* z, void* dz, int rows, int N, int act, float alpha,
+                                      float drop_p, unsigned long long seed, float* gb, cudaStream_t stream);
 
 // One linear layer: bf16 weight [out, in], fp32 bias [out] (may be null), fp32 gradient accumulators (null in inference).
 struct SbLinearParams {
@@ -296,7 +298,8 @@ struct Exec {
   // The input gradient can leave its GEMM already multiplied by the previous activation's derivative and dropout mask:
   // dx = dropout(dz @ w) * act'(dx_pre)  (dx_pre = that activation's saved input, dx_seed = its forward dropout seed).
   bool linear_bwd(const bf16* dz, long long ld_dz, const bf16* x, long long ldx, const SbLinearParams& p, bf16* dx, int M, int N,
-                  int K, const bf16* dx_pre = nullptr, int dx_dact = 0, float dx_drop = 0.f, unsigned long long dx_seed = 0) {
+                  int K, const bf16* dx_pre = nullptr, int dx_dact = 0, float dx_drop = 0.f, unsigned long long dx_seed = 0,
+                  bool bias_grad_done = false) {
     char label[32];
     if (dx) {
       SbGemmArgs g = gemm_defaults();
@@ -318,7 +321,7 @@ struct Exec {
       sub = label;
       if (!run(sb_gemm_bf16(&g, stream))) return false;
     }
-    if (p.gb) {
+    if (p.gb && !bias_grad_done) {   // otherwise the kernel that produced dz has already added its column sums to p.gb
       sub = ".bgrad";
       if (!run(sb_colsum_bf16(dz, ld_dz, M, N, p.gb, stream))) return false;
     }
@@ -477,15 +480,21 @@ SB_API int sb_conformer_layer_bwd(SbConformerLayerArgs* a, cudaStream_t stream) 
 
   // One macaron feed-forward half: y = res_in + fc * drop(lin_b(drop(swish(lin_a(LN res_in))))).
   // G_in = gradient of y; writes the gradient of res_in into G_out.
+  // dz = alpha * dropout-mask * dy * act'(z), with the bias gradient of the linear layer that consumes dz folded into the same pass
+  auto dact_bias = [&](const bf16* dy_, long long ld, const bf16* z_, bf16* dz_, int N_, int act_, float alpha_, float p_, unsigned long long sd,
+                       float* gb_) {
+    if (gb_) return e.named(".scale_dact_dropout_bias", sb_scale_dact_dropout_bias(dy_, ld, z_, dz_, R, N_, act_, alpha_, p_, sd, gb_, stream));
+    return e.named(".scale_dact_dropout", sb_scale_dact_dropout(dy_, ld, z_, dz_, R, N_, act_, alpha_, p_, sd, stream));
+  };
   auto ff_bwd = [&](const bf16* G_in, bf16* G_out, const bf16* res_in, const bf16* h, const bf16* pre, const bf16* act_out,
                     const SbNormParams& norm, const SbLinearParams& la, const SbLinearParams& lb, const float* mean,
                     const float* rstd, unsigned long long seed_inner, unsigned long long seed_out) {
-    bool k = e.named(".scale_dact_dropout", sb_scale_dact_dropout(G_in, d, nullptr, w.dzd, R, d, 0, a->fc_factor, p_ff, seed_out, stream));
+    bool k = dact_bias(G_in, d, nullptr, w.dzd, d, 0, a->fc_factor, p_ff, seed_out, lb.gb);
     // (folding swish'(pre) and the inner dropout into this dgrad GEMM's epilogue was measured slower: with K = d the GEMM is
     // epilogue-bound and the per-row loads of `pre` more than double it; the separate pass below runs at HBM speed)
-    k = k && e.linear_bwd(w.dzd, d, act_out, F, lb, w.big, R, d, F);
-    k = k && e.named(".scale_dact_dropout", sb_scale_dact_dropout(w.big, F, pre, w.big, R, F, 2, 1.f, p_ff, seed_inner, stream));
-    k = k && e.linear_bwd(w.big, F, h, d, la, w.dh, R, F, d);
+    k = k && e.linear_bwd(w.dzd, d, act_out, F, lb, w.big, R, d, F, nullptr, 0, 0.f, 0, true);
+    k = k && dact_bias(w.big, F, pre, w.big, F, 2, 1.f, p_ff, seed_inner, la.gb);
+    k = k && e.linear_bwd(w.big, F, h, d, la, w.dh, R, F, d, nullptr, 0, 0.f, 0, true);
     k = k && e.ln_bwd(w.dh, res_in, norm, mean, rstd, G_out, G_in, R, d);
     return k;
   };
@@ -500,12 +509,14 @@ SB_API int sb_conformer_layer_bwd(SbConformerLayerArgs* a, cudaStream_t stream) 
   e.tag = "conv";
   {
     const bf16* dz = w.GB;
+    bool bias_done = false;
     if (p_out > 0.f) {
-      ok = ok && e.named(".scale_dact_dropout", sb_scale_dact_dropout(w.GB, d, nullptr, w.dzd, R, d, 0, 1.f, p_out, a->seeds[4], stream));
+      ok = ok && dact_bias(w.GB, d, nullptr, w.dzd, d, 0, 1.f, p_out, a->seeds[4], a->pw2.gb);
       dz = w.dzd;
+      bias_done = a->pw2.gb != nullptr;
     }
     bf16* ds = w.dh;
-    ok = ok && e.linear_bwd(dz, d, s.s, d, a->pw2, ds, R, d, d);
+    ok = ok && e.linear_bwd(dz, d, s.s, d, a->pw2, ds, R, d, d, nullptr, 0, 0.f, 0, bias_done);
     ok = ok && e.zero(w.sums, 2 * d * sizeof(float));
     ok = ok && e.named(".bn_silu_bwd_stats", sb_bn_silu_bwd_stats(ds, s.y, s.mean_rstd, a->bn_w, a->bn_b, w.sums, R, d, stream));
     bf16* dg = w.big;
@@ -531,12 +542,14 @@ SB_API int sb_conformer_layer_bwd(SbConformerLayerArgs* a, cudaStream_t stream) 
   e.tag = "att";
   {
     const bf16* dz = w.GA;
+    bool bias_done = false;
     if (p_out > 0.f) {
-      ok = ok && e.named(".scale_dact_dropout", sb_scale_dact_dropout(w.GA, d, nullptr, w.dzd, R, d, 0, 1.f, p_out, a->seeds[3], stream));
+      ok = ok && dact_bias(w.GA, d, nullptr, w.dzd, d, 0, 1.f, p_out, a->seeds[3], a->out_proj.gb);
       dz = w.dzd;
+      bias_done = a->out_proj.gb != nullptr;
     }
     bf16* dctx = w.dh;
-    ok = ok && e.linear_bwd(dz, d, s.ctx, d, a->out_proj, dctx, R, d, d);
+    ok = ok && e.linear_bwd(dz, d, s.ctx, d, a->out_proj, dctx, R, d, d, nullptr, 0, 0.f, 0, bias_done);
     const bf16* Pu = (p_att > 0.f) ? s.Pd : s.Pm;
     bf16 *dQ = w.dqkv, *dK = w.dqkv + d, *dV = w.dqkv + 2 * d;
     const bf16 *kk = s.qkv + d, *vv = s.qkv + 2 * d;

@@ -525,6 +525,85 @@ __global__ void scale_dact_kernel(const __nv_bfloat16* __restrict__ dy, long lon
 }
 }  // namespace
 
+namespace {
+// The same element-wise work with the bias gradient folded in: a thread keeps ONE group of eight columns and walks down the rows,
+// so that it can also accumulate the column sums of dz (= the gradient of the linear layer's bias, which the caller would
+// otherwise compute with a second pass over dz).  Block = 256 threads = CG column groups x RL row lanes; the block's row lanes
+// meet in shared memory and one atomic per column and block reaches gb (which is accumulated into).
+__global__ void __launch_bounds__(256) scale_dact_colsum_kernel(const __nv_bfloat16* __restrict__ dy, long long ld_dy,
+                                                               const __nv_bfloat16* __restrict__ z, __nv_bfloat16* __restrict__ dz, int rows,
+                                                               int N, int act, float alpha, unsigned int thresh, float drop_scale,
+                                                               unsigned long long seed, float* __restrict__ gb, int cgs, int rows_per_block) {
+  __shared__ float red[256 * 8];
+  const int rl_n = 256 / cgs;                               // row lanes of the block
+  const int cg = blockIdx.x * cgs + (threadIdx.x % cgs);    // this thread's column group
+  const int rl = threadIdx.x / cgs;
+  const int c = cg * 8;
+  const int r0 = blockIdx.y * rows_per_block, r1 = min(rows, r0 + rows_per_block);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (c < N) {
+    for (int r = r0 + rl; r < r1; r += rl_n) {
+      const uint4 rg = *reinterpret_cast<const uint4*>(dy + (long long)r * ld_dy + c);
+      const uint4 rz = z ? *reinterpret_cast<const uint4*>(z + (long long)r * N + c) : make_uint4(0, 0, 0, 0);
+      const __nv_bfloat162* hg = reinterpret_cast<const __nv_bfloat162*>(&rg);
+      const __nv_bfloat162* hz = reinterpret_cast<const __nv_bfloat162*>(&rz);
+      const unsigned long long grp = ((unsigned long long)r * N + c) >> 2;
+      const unsigned int h0 = thresh ? sb_dropout_hash4(seed, grp) : 0u, h1 = thresh ? sb_dropout_hash4(seed, grp + 1) : 0u;
+      __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 g = __bfloat1622float2(hg[u]), zz = __bfloat1622float2(hz[u]);
+        float d0, d1;
+        if (act == 1) { d0 = zz.x > 0.f ? 1.f : 0.f; d1 = zz.y > 0.f ? 1.f : 0.f; }
+        else if (act == 2) { d0 = sb_dswish(zz.x); d1 = sb_dswish(zz.y); }
+        else if (act == 3) { d0 = sb_dgelu(zz.x); d1 = sb_dgelu(zz.y); }
+        else { d0 = d1 = 1.f; }
+        if (thresh) {
+          const unsigned int h = u < 2 ? h0 : h1;
+          d0 = sb_dropout_keep_in(h, (2 * u) & 3, thresh) ? d0 * drop_scale : 0.f;
+          d1 = sb_dropout_keep_in(h, (2 * u + 1) & 3, thresh) ? d1 * drop_scale : 0.f;
+        }
+        o[u] = __floats2bfloat162_rn(alpha * g.x * d0, alpha * g.y * d1);
+        const float2 w = __bfloat1622float2(o[u]);          // the sums see the rounded values, as a separate pass over dz would
+        acc[2 * u] += w.x;
+        acc[2 * u + 1] += w.y;
+      }
+      *reinterpret_cast<uint4*>(dz + (long long)r * N + c) = *reinterpret_cast<uint4*>(o);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) red[threadIdx.x * 8 + k] = acc[k];
+  __syncthreads();
+  if (rl == 0 && c < N) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float sum = 0.f;
+      for (int q = 0; q < rl_n; ++q) sum += red[(q * cgs + (threadIdx.x % cgs)) * 8 + k];
+      atomicAdd(gb + c + k, sum);
+    }
+  }
+}
+}  // namespace
+
+// dz = alpha * mask * dy * act'(z) and gb[N] += column sums of dz, in one pass.
+SB_API int sb_scale_dact_dropout_bias(const void* dy, long long ld_dy, const void* z, void* dz, int rows, int N, int act, float alpha,
+                                      float drop_p, unsigned long long seed, float* gb, cudaStream_t stream) {
+  if (N % 8 != 0 || rows <= 0 || !gb) return -1;
+  if (z == nullptr) act = 0;
+  const int ngroups = N / 8;
+  int cgs = ngroups >= 128 ? 128 : (ngroups >= 64 ? 64 : (ngroups >= 32 ? 32 : 16));   // column groups per block (divides 256)
+  const int col_blocks = (ngroups + cgs - 1) / cgs;
+  int row_blocks = (4 * sb_num_sms() + col_blocks - 1) / col_blocks;
+  const int rl_n = 256 / cgs;
+  if (row_blocks > (rows + 8 * rl_n - 1) / (8 * rl_n)) row_blocks = (rows + 8 * rl_n - 1) / (8 * rl_n);
+  if (row_blocks < 1) row_blocks = 1;
+  const int rpb = (rows + row_blocks - 1) / row_blocks;
+  dim3 grid(col_blocks, (rows + rpb - 1) / rpb);
+  scale_dact_colsum_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)dy, ld_dy, (const __nv_bfloat16*)z, (__nv_bfloat16*)dz, rows, N,
+                                                    act, alpha, sb_dropout_threshold(drop_p), sb_dropout_scale(drop_p), seed, gb, cgs, rpb);
+  return (int)cudaGetLastError();
+}
+
 SB_API int sb_scale_dact_dropout(const void* dy, long long ld_dy, const void* z, void* dz, int rows, int N, int act, float alpha,
                                  float drop_p, unsigned long long seed, cudaStream_t stream);
 
