@@ -332,7 +332,7 @@ class StatelessNet(nn.Module):
             appended = torch.cat([state[0], y], dim=1)
             ctx_len = appended.shape[1]
             if ctx_len > self.context_size:
-                appended = appended[:, ctx_len - self.context_size - U + 1 if False else -(self.context_size + U - 1):]
+                appended = appended[:, -(self.context_size + U - 1):]
             state = [appended[:, -self.context_size:] if appended.shape[1] >= self.context_size else appended]
         else:
             state = [y[:, -self.context_size:]] if U >= self.context_size else [

@@ -74,7 +74,10 @@ SB_API int sb_grad_norm_static_max_parts() { return SB_GRAD_NORM_STATIC_MAX_PART
 SB_API int sb_grad_norm_clip_static(const float* g, long long n, float* scalars, float max_norm, float grad_scale, int nparts,
                                     cudaStream_t stream) {
   if (g == nullptr || scalars == nullptr || n < 0 || nparts < 0) return SB_GRAD_NORM_STATIC_E_BAD_ARG;
-  if (nparts == 0) nparts = sb_num_sms() * 8;
+  if (nparts == 0) {   // default: eight blocks per SM, clamped to what the static array holds
+    nparts = sb_num_sms() * 8;
+    if (nparts > SB_GRAD_NORM_STATIC_MAX_PARTS) nparts = SB_GRAD_NORM_STATIC_MAX_PARTS;
+  }
   if (nparts > SB_GRAD_NORM_STATIC_MAX_PARTS) {
     fprintf(stderr,
             "sb_grad_norm_clip_static: %d partial sums requested but the static scratch holds %d; "

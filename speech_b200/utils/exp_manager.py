@@ -214,6 +214,52 @@ class MLFlowLogger(BaseLogger):
         self.mlflow.end_run()
 
 
+class ClearMLLogger(BaseLogger):
+    """ClearML task logger (reference ``nemo/utils/loggers/clearml_logger.py``): scalars go to the task's logger, one series
+    per metric name; the optional package is imported on construction."""
+
+    def __init__(self, save_dir, name="", version="", **kwargs):
+        super().__init__(save_dir, name, version)
+        from clearml import Task
+
+        self.task = Task.init(project_name=kwargs.get("project", name) or "speech_b200", task_name=kwargs.get("task", version) or name,
+                              output_uri=kwargs.get("output_uri", None), reuse_last_task_id=False)
+        self.log_cfg = bool(kwargs.get("log_cfg", False))
+
+    def log_metrics(self, metrics, step):
+        lg = self.task.get_logger()
+        for k, v in metrics.items():
+            lg.report_scalar(title=k, series=k, value=float(v), iteration=int(step))
+
+    def log_hyperparams(self, params):
+        self.task.connect(dict(params) if isinstance(params, dict) else {"config": str(params)})
+
+    def finalize(self, status="success"):
+        self.task.close()
+
+
+class NeptuneLogger(BaseLogger):
+    """Neptune run logger (the reference hands ``neptune_logger_kwargs`` to Lightning's NeptuneLogger)."""
+
+    def __init__(self, save_dir, name="", version="", **kwargs):
+        super().__init__(save_dir, name, version)
+        import neptune
+
+        kwargs.setdefault("name", name)
+        self.run = neptune.init_run(**kwargs)
+        self.prefix = kwargs.get("prefix", "training")
+
+    def log_metrics(self, metrics, step):
+        for k, v in metrics.items():
+            self.run[f"{self.prefix}/{k}"].append(float(v), step=int(step))
+
+    def log_hyperparams(self, params):
+        self.run["hyperparams"] = dict(params) if isinstance(params, dict) else str(params)
+
+    def finalize(self, status="success"):
+        self.run.stop()
+
+
 class DLLogger(JSONLLogger):
     """DLLogger-style JSON stream (``DLLL`` prefix per line)."""
 
@@ -242,9 +288,14 @@ def configure_loggers(trainer, exp_dir, log_dir, name, version, cfg: DictConfig)
                 loggers.append(cls(str(log_dir), name, version, **kw))
             except ImportError as e:
                 raise LoggerMisconfigurationError(f"{cls.__name__} requested but its package is missing: {e}")
-    for flag in ("create_clearml_logger", "create_neptune_logger"):
+    for flag, kwname, cls in (("create_clearml_logger", "clearml_logger_kwargs", ClearMLLogger),
+                              ("create_neptune_logger", "neptune_logger_kwargs", NeptuneLogger)):
         if cfg.get(flag, False):
-            raise LoggerMisconfigurationError(f"{flag}: the backing package is not available in this environment")
+            kw = to_container(cfg.get(kwname)) if cfg.get(kwname) else {}
+            try:
+                loggers.append(cls(str(log_dir), name, version, **kw))
+            except ImportError as e:
+                raise LoggerMisconfigurationError(f"{cls.__name__} requested but its package is missing: {e}")
     trainer.loggers = loggers if is_global_rank_zero() else []
 
 
