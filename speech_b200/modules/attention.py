@@ -215,48 +215,89 @@ class RelPositionMultiHeadAttention(MultiHeadAttention):
 
 
 class RelPositionMultiHeadAttentionLongformer(RelPositionMultiHeadAttention):
-    """Local (sliding window) relative-position attention with optional global tokens.
+    """Local (sliding window) relative-position attention with optional global tokens, in O(T * window) memory.
 
-    Attention of frame i is restricted to [i-left, i+right]; the first ``global_tokens`` frames attend to and are
-    attended by everything.  Relative terms use the window positional table of
-    :class:`LocalAttRelPositionalEncoding`.
+    Attention of frame i is restricted to [i-left, i+right]; the ``global_tokens`` frames (every ``global_tokens_spacing``-th
+    frame from the start) attend to and are attended by everything.  Relative terms use the window positional table of
+    :class:`LocalAttRelPositionalEncoding` and apply inside the band only.  The reference gets the same memory behaviour from
+    overlapping-chunk matmuls (``multi_head_attention.py:364-997``, ``sliding_chunks_matmul_qk / _pv``); here the query axis
+    is walked in blocks of ``query_block`` frames and each block sees only its ``query_block + left + right`` keys (plus the
+    global ones), so no ``[T, T]`` tensor is ever formed and hour-long inputs fit.
     """
 
     def __init__(self, n_head, n_feat, dropout_rate, pos_bias_u=None, pos_bias_v=None, att_context_size=(128, 128),
-                 max_cache_len=0, global_tokens=0, global_tokens_spacing=1, global_attn_separate=False, use_bias=True):
+                 max_cache_len=0, global_tokens=0, global_tokens_spacing=1, global_attn_separate=False, use_bias=True,
+                 query_block: int = 512):
         super().__init__(n_head, n_feat, dropout_rate, pos_bias_u, pos_bias_v, max_cache_len, use_bias)
         self.att_context_size = tuple(att_context_size)
         self.global_tokens, self.global_tokens_spacing = global_tokens, global_tokens_spacing
+        self.query_block = int(query_block)
 
     def forward(self, query, key, value, pad_mask=None, pos_emb=None, cache=None, residual=None, mask=None, out_dropout: float = 0.0):
         B, T, _ = query.shape
+        dev = query.device
         q, k, v = self._qkv(query, key, value)
         left, right = self.att_context_size
         p = ops.linear(pos_emb.to(q.dtype), self.linear_pos.weight, None).view(1, -1, self.h, self.d_k)  # window table
         qf = q.float()
-        q_u = (qf + self.pos_bias_u.float()).transpose(1, 2)
+        q_u = (qf + self.pos_bias_u.float()).transpose(1, 2)            # [B, H, T, d]
         q_v = (qf + self.pos_bias_v.float()).transpose(1, 2)
-        ac = torch.matmul(q_u, k.float().transpose(1, 2).transpose(-2, -1))  # B,H,T,T
-        bd_win = torch.matmul(q_v, p.float().transpose(1, 2).transpose(-2, -1))  # B,H,T,W ; col c <-> offset left-c
-        idx_i = torch.arange(T, device=query.device)[:, None]
-        idx_j = torch.arange(T, device=query.device)[None, :]
-        rel = idx_i - idx_j  # i-j in [-right, left] inside the band
-        band = (rel <= left) & (rel >= -right)
-        col = (left - rel).clamp(0, left + right)
-        bd = torch.gather(bd_win, 3, col[None, None].expand(B, self.h, T, T))
-        scores = (ac + bd) / self.s_d_k
-        visible = band.clone()
+        kT = k.float().transpose(1, 2)                                   # [B, H, T, d]
+        vT = v.float().transpose(1, 2)
+        pT = p.float().transpose(1, 2)                                   # [1, H, W, d]; column c <-> offset i - j = left - c
+        g = None
         if self.global_tokens > 0:
-            g = torch.arange(0, self.global_tokens * self.global_tokens_spacing, self.global_tokens_spacing,
-                             device=query.device)
-            visible[g, :] = True
-            visible[:, g] = True
-        hidden = ~visible[None].expand(B, T, T)
-        if pad_mask is not None:
-            hidden = hidden | pad_mask[:, None, :] | pad_mask[:, :, None]
-        scores = scores.masked_fill(hidden[:, None], -INF_VAL)
-        attn = torch.softmax(scores, dim=-1).masked_fill(hidden[:, None], 0.0)
-        attn = torch.nn.functional.dropout(attn, self.dropout_rate, self.training)
-        ctx = torch.matmul(attn, v.float().transpose(1, 2)).transpose(1, 2).reshape(B, T, -1).to(query.dtype)
+            g = torch.arange(0, self.global_tokens * self.global_tokens_spacing, self.global_tokens_spacing, device=dev)
+            g = g[g < T]
+            kg, vg = kT[:, :, g], vT[:, :, g]
+            is_g = torch.zeros(T, dtype=torch.bool, device=dev)
+            is_g[g] = True
+        ctx = torch.empty(B, self.h, T, self.d_k, dtype=torch.float32, device=dev)
+        bq = max(1, self.query_block)
+        for i0 in range(0, T, bq):
+            i1 = min(T, i0 + bq)
+            k0, k1 = max(0, i0 - left), min(T, i1 + right)
+            qi = torch.arange(i0, i1, device=dev)[:, None]
+            kj = torch.arange(k0, k1, device=dev)[None, :]
+            rel = qi - kj
+            band = (rel <= left) & (rel >= -right)
+            ac = torch.matmul(q_u[:, :, i0:i1], kT[:, :, k0:k1].transpose(-2, -1))                 # [B, H, bq, wk]
+            bd_win = torch.matmul(q_v[:, :, i0:i1], pT.transpose(-2, -1))                          # [B, H, bq, W]
+            col = (left - rel).clamp(0, left + right)
+            bd = torch.gather(bd_win, 3, col[None, None].expand(B, self.h, i1 - i0, k1 - k0))
+            scores = (ac + bd) / self.s_d_k
+            hidden = (~band)[None].expand(B, i1 - i0, k1 - k0)
+            if g is not None:
+                hidden = hidden | is_g[k0:k1][None, None, :]          # global keys are counted once, in the global block below
+            if pad_mask is not None:
+                hidden = hidden | pad_mask[:, None, k0:k1] | pad_mask[:, i0:i1, None]
+            scores = scores.masked_fill(hidden[:, None], -INF_VAL)
+            if g is not None:
+                sg = torch.matmul(q_u[:, :, i0:i1], kg.transpose(-2, -1)) / self.s_d_k             # [B, H, bq, G]
+                hg = torch.zeros(B, i1 - i0, g.numel(), dtype=torch.bool, device=dev)
+                if pad_mask is not None:
+                    hg = hg | pad_mask[:, g][:, None, :] | pad_mask[:, i0:i1, None]
+                sg = sg.masked_fill(hg[:, None], -INF_VAL)
+                allp = torch.softmax(torch.cat([scores, sg], dim=-1), dim=-1)
+                allp = allp.masked_fill(torch.cat([hidden, hg], dim=-1)[:, None], 0.0)
+                allp = torch.nn.functional.dropout(allp, self.dropout_rate, self.training)
+                wk = k1 - k0
+                ctx[:, :, i0:i1] = torch.matmul(allp[..., :wk], vT[:, :, k0:k1]) + torch.matmul(allp[..., wk:], vg)
+            else:
+                attn = torch.softmax(scores, dim=-1).masked_fill(hidden[:, None], 0.0)
+                attn = torch.nn.functional.dropout(attn, self.dropout_rate, self.training)
+                ctx[:, :, i0:i1] = torch.matmul(attn, vT[:, :, k0:k1])
+        if g is not None and g.numel() > 0:
+            # rows of the global frames: full attention over every key ([G, T] scores), content term only
+            sg = torch.matmul(q_u[:, :, g], kT.transpose(-2, -1)) / self.s_d_k
+            if pad_mask is not None:
+                hgr = pad_mask[:, None, :] | pad_mask[:, g][:, :, None]
+                sg = sg.masked_fill(hgr[:, None], -INF_VAL)
+            ag = torch.softmax(sg, dim=-1)
+            if pad_mask is not None:
+                ag = ag.masked_fill(hgr[:, None], 0.0)
+            ag = torch.nn.functional.dropout(ag, self.dropout_rate, self.training)
+            ctx[:, :, g] = torch.matmul(ag, vT)
+        ctx = ctx.transpose(1, 2).reshape(B, T, -1).to(query.dtype)
         out = ops.linear(ctx, self.linear_out.weight, self.linear_out.bias, residual=residual, dropout_p=out_dropout)
         return out if cache is None else (out, cache)

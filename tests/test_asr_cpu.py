@@ -228,3 +228,52 @@ def test_subsampling_prime_shapes_leaves_no_gradients_and_keeps_mode():
     sub.prime_shapes([(2, 40), (3, 57)], "cpu")
     assert not sub.training and all(p.grad is None for p in sub.parameters())
     assert all(torch.equal(a, b) for a, b in zip(before, sub.parameters()))
+
+
+def test_longformer_attention_is_banded_and_matches_dense_masked_attention():
+    """Sliding-window relative-position attention computed block by block (no [T, T] tensor) equals dense attention with a
+    band mask, for several block sizes, with padding; and it runs on a sequence whose dense score matrix would not fit a test."""
+    import torch
+    from speech_b200.modules.attention import LocalAttRelPositionalEncoding, RelPositionMultiHeadAttentionLongformer
+
+    torch.manual_seed(0)
+    B, T, D, H, left, right = 2, 75, 32, 4, 6, 4
+    att = RelPositionMultiHeadAttentionLongformer(H, D, 0.0, att_context_size=(left, right), query_block=16).eval()
+    torch.nn.init.normal_(att.pos_bias_u, std=0.3); torch.nn.init.normal_(att.pos_bias_v, std=0.3)
+    pe = LocalAttRelPositionalEncoding(att_context_size=[left, right], d_model=D, dropout_rate=0.0)
+    pe.extend_pe(T, torch.device("cpu"), torch.float32)
+    x = torch.randn(B, T, D)
+    _, pos = pe(x)
+    pad = torch.zeros(B, T, dtype=torch.bool); pad[1, 60:] = True
+    out = att(x, x, x, pad_mask=pad, pos_emb=pos)
+    # dense reference
+    q, k, v = att._qkv(x, x, x)
+    p = torch.nn.functional.linear(pos, att.linear_pos.weight).view(1, -1, H, D // H)
+    qu = (q + att.pos_bias_u).transpose(1, 2); qv = (q + att.pos_bias_v).transpose(1, 2)
+    ac = qu @ k.transpose(1, 2).transpose(-2, -1)
+    bdw = qv @ p.transpose(1, 2).transpose(-2, -1)
+    i = torch.arange(T)[:, None]; j = torch.arange(T)[None, :]
+    rel = i - j
+    band = (rel <= left) & (rel >= -right)
+    bd = torch.gather(bdw, 3, (left - rel).clamp(0, left + right)[None, None].expand(B, H, T, T))
+    hidden = (~band)[None] | pad[:, None, :] | pad[:, :, None]
+    sc = ((ac + bd) / att.s_d_k).masked_fill(hidden[:, None], -10000.0)
+    a = torch.softmax(sc, -1).masked_fill(hidden[:, None], 0.0)
+    ref = torch.nn.functional.linear((a @ v.transpose(1, 2)).transpose(1, 2).reshape(B, T, D), att.linear_out.weight, att.linear_out.bias)
+    assert torch.allclose(out[~pad], ref[~pad], atol=1e-5), (out - ref).abs().max()
+    for qb in (1, 7, 200):
+        att.query_block = qb
+        assert torch.allclose(att(x, x, x, pad_mask=pad, pos_emb=pos)[~pad], ref[~pad], atol=1e-5)
+    # global tokens: every frame additionally sees frames 0 and 8; those two see everything
+    att2 = RelPositionMultiHeadAttentionLongformer(H, D, 0.0, att_context_size=(left, right), global_tokens=2, global_tokens_spacing=8,
+                                                   query_block=16).eval()
+    att2.load_state_dict(att.state_dict())
+    o2 = att2(x, x, x, pad_mask=pad, pos_emb=pos)
+    assert torch.isfinite(o2).all() and not torch.allclose(o2[0, 40], out[0, 40])
+    # a long input: 20 000 frames would need 4 x 20000^2 x 4 B = 6.4 GB per batch element as dense scores
+    Tl = 20000
+    pe.extend_pe(Tl, torch.device("cpu"), torch.float32)
+    xl = torch.randn(1, Tl, D)
+    _, posl = pe(xl)
+    att.query_block = 1024
+    assert att(xl, xl, xl, pos_emb=posl).shape == (1, Tl, D)
