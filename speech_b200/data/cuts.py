@@ -2,10 +2,13 @@
 
 ``get_dataloader_from_cuts_config(config, ...)`` understands the keys of ``LhotseDataLoadingConfig``
 (``common/data/lhotse/dataloader.py:71-256``): inputs (``manifest_filepath``, ``tarred_audio_filepaths``, ``cuts_path``,
-``input_cfg`` trees with ``type`` / ``weight`` / ``tags`` and nested ``group``), sampling (``batch_size``,
+``shar_path``, ``input_cfg`` trees with ``type`` / ``weight`` / ``tags`` and nested ``group``; the source types are listed
+in :mod:`speech_b200.data.sources`), sampling (``batch_size``,
 ``batch_duration``, ``quadratic_duration``, ``num_buckets``, ``bucket_duration_bins`` 1-D or 2-D,
 ``bucket_batch_size``, ``batch_tokens`` + ``token_equivalent_duration``, ``max_open_streams`` ignored), filters
-(``min_duration`` / ``max_duration``, ``min_tps`` / ``max_tps``, ``max_cer`` ignored without hypotheses), ordering
+(``min_duration`` / ``max_duration``, ``min_tps`` / ``max_tps``, ``min_tokens`` / ``max_tokens``, ``min_tpt`` / ``max_tpt``,
+``max_cer``, ``keep_validation_status``, ``min_context_speaker_similarity``), multimodal sampling
+(``use_multimodal_sampling`` + ``batch_tokens`` + ``quadratic_factor`` + ``measure_total_length``), ordering
 (``shuffle``, ``seed``, ``shard_seed`` "trng" / "randomized" / int), augmentation (``noise_path`` + ``noise_snr`` +
 ``noise_mix_prob``, ``perturb_speed``, ``rir_enabled`` + ``rir_path`` + ``rir_prob``, ``truncate_duration``,
 ``cut_into_windows_duration``), and ``multi_config`` (several sub-configs fused round-robin / zipped / by weight).
@@ -181,17 +184,17 @@ def read_nemo_tarred(manifest_paths, tar_paths, tags: Optional[Dict[str, Any]] =
 
 
 def read_txt(paths, language: Optional[str] = None, tags: Optional[Dict[str, Any]] = None) -> CutSet:
-    def gen():
-        for p in expand_sharded_filepaths(paths):
-            with open(p, encoding="utf-8") as f:
-                for k, line in enumerate(f):
-                    if line.strip():
-                        yield Cut(f"{os.path.basename(p)}-{k}", None, 0.0, text=line.strip(), lang=language, custom=dict(tags or {}))
-    return CutSet(gen)
+    from .sources import get_parser
+
+    return get_parser("txt")({"paths": paths, "language": language, "tags": tags}, {})
 
 
 def parse_input_cfg(input_cfg, seed: int = 0, rank: int = 0, world: int = 1) -> CutSet:
-    """``input_cfg``: list of ``{type, weight, tags, ...}`` entries; ``type: group`` nests another ``input_cfg``."""
+    """``input_cfg``: list of ``{type, weight, tags, ...}`` entries (or the path of a YAML file holding one); ``type: group``
+    nests another ``input_cfg``.  Each type is read by the parser registered for it in :mod:`speech_b200.data.sources`;
+    entries are interleaved at random in proportion to their ``weight``."""
+    from .sources import get_parser
+
     if isinstance(input_cfg, str):
         import yaml
 
@@ -201,28 +204,24 @@ def parse_input_cfg(input_cfg, seed: int = 0, rank: int = 0, world: int = 1) -> 
     for i, e in enumerate(input_cfg):
         e = dict(e)
         t = e.get("type", "nemo")
-        tags = e.get("tags")
         if t == "group":
             cs = parse_input_cfg(e["input_cfg"], seed + i + 1, rank, world)
-        elif t == "nemo":
-            cs = read_nemo_manifest(e["manifest_filepath"], tags=tags)
-        elif t == "nemo_tarred":
-            cs = read_nemo_tarred(e["manifest_filepath"], e["tarred_audio_filepaths"], tags, rank, world)
-        elif t in ("txt", "txt_pair"):
-            cs = read_txt(e.get("paths", e.get("source_paths")), e.get("language"), tags)
-        elif t in ("multimodal_conversation", "lhotse_as_conversation"):
-            from ..speechlm.data import read_conversations
-
-            convs = read_conversations(e["manifest_filepath"])
-            cs = CutSet([Cut(c.get("id", str(k)), None, sum(float(t_.get("duration", 0)) for t_ in c["conversations"]),
-                             custom={"conversation": c, **(tags or {})}) for k, c in enumerate(convs)])
+            if e.get("tags"):
+                tags = dict(e["tags"])
+                cs = cs.map(lambda c, tags=tags: _with_tags(c, tags))
         else:
-            raise ValueError(f"unsupported input_cfg type '{t}'")
+            cs = get_parser(t)(e, {"seed": seed + i, "rank": rank, "world": world})
         sets.append(cs)
         weights.append(float(e.get("weight", 1.0)))
     if len(sets) == 1:
         return sets[0]
     return CutSet.mux(sets, weights, seed=seed)
+
+
+def _with_tags(c: Cut, tags: Dict[str, Any]) -> Cut:
+    for k, v in tags.items():
+        c.custom.setdefault(k, v)
+    return c
 
 
 def reweight_by_temperature(weights: Sequence[float], temperature: float) -> List[float]:
@@ -349,8 +348,20 @@ def build_cutset_from_config(c: Dict[str, Any], rank: int = 0, world: int = 1) -
         cuts = read_nemo_tarred(c["manifest_filepath"], c["tarred_audio_filepaths"], None, rank, world)
     elif c.get("manifest_filepath") is not None:
         cuts = read_nemo_manifest(c["manifest_filepath"], c.get("lang_field", "lang"), c.get("text_field", "text"))
+    elif c.get("shar_path") is not None or c.get("cuts_path") is not None:
+        from .sources import get_parser
+
+        cuts = get_parser("lhotse")(c, {"seed": seed, "rank": rank, "world": world})
     else:
-        raise ValueError("the data config needs input_cfg, manifest_filepath or tarred_audio_filepaths")
+        raise ValueError("the data config needs input_cfg, manifest_filepath, tarred_audio_filepaths, cuts_path or shar_path")
+    from .sampling import CERFilter, ContextSpeakerSimilarityFilter, ValidationStatusFilter
+
+    if c.get("keep_validation_status") is not None:
+        cuts = cuts.filter(ValidationStatusFilter(c["keep_validation_status"]))
+    if c.get("max_cer") is not None:
+        cuts = cuts.filter(CERFilter(c["max_cer"]))
+    if c.get("min_context_speaker_similarity") is not None:
+        cuts = cuts.filter(ContextSpeakerSimilarityFilter(c["min_context_speaker_similarity"]))
     if c.get("cut_into_windows_duration"):
         cuts = cuts.cut_into_windows(float(c["cut_into_windows_duration"]))
     if c.get("truncate_duration"):
@@ -358,7 +369,9 @@ def build_cutset_from_config(c: Dict[str, Any], rank: int = 0, world: int = 1) -
         cuts = cuts.truncate(float(c["truncate_duration"]), rng)
     lo, hi = c.get("min_duration"), c.get("max_duration")
     if lo is not None or hi is not None:
-        cuts = cuts.filter(lambda k: (lo is None or k.duration >= lo) and (hi is None or k.duration <= hi))
+        from .sampling import DurationFilter
+
+        cuts = cuts.filter(DurationFilter(lo, hi))
     ps = c.get("perturb_speed")
     if ps:
         factors = [0.9, 1.1] if ps is True else list(ps)
@@ -374,7 +387,7 @@ def get_dataloader_from_cuts_config(config, global_rank: int = 0, world_size: in
         subs = [get_dataloader_from_cuts_config({**v, "multi_config": False}, global_rank, world_size, tokenizer, labels, dataset_cls)
                 for k, v in c.items() if isinstance(v, dict) and k not in ("sampler_fusion",)]
         return FusedLoader(subs, mode=c.get("sampler_fusion", "round_robin"), weights=c.get("sampler_weights"), seed=c.get("seed", 0))
-    tarred = c.get("tarred_audio_filepaths") is not None
+    tarred = c.get("tarred_audio_filepaths") is not None or c.get("shar_path") is not None
     cuts = build_cutset_from_config(c, global_rank if tarred else 0, world_size if tarred else 1).to_eager()
     aug: List[Callable] = []
     sr = c.get("sample_rate", 16000)
@@ -390,8 +403,25 @@ def get_dataloader_from_cuts_config(config, global_rank: int = 0, world_size: in
         keep = [i for i, k in enumerate(ds.cuts) if k.duration <= 0 or
                 ((min_tps is None or ds.num_tokens(i) / k.duration >= min_tps) and (max_tps is None or ds.num_tokens(i) / k.duration <= max_tps))]
         ds.cuts = [ds.cuts[i] for i in keep]
+    if any(c.get(k) is not None for k in ("min_tokens", "max_tokens", "min_tpt", "max_tpt")):
+        from .sampling import TokenCountFilter, TokenPerTokenFilter
+
+        ted_f = c.get("token_equivalent_duration")
+        f1 = TokenCountFilter(c.get("min_tokens"), c.get("max_tokens"), bool(c.get("measure_total_length", False)), tokenizer, ted_f)
+        f2 = TokenPerTokenFilter(c.get("min_tpt"), c.get("max_tpt"), tokenizer)
+        ds.cuts = [k for k in ds.cuts if f1(k) and f2(k)]
     durs = ds.durations()
-    if c.get("batch_tokens"):
+    if c.get("use_multimodal_sampling"):
+        # every example is measured in tokens (audio converted with token_equivalent_duration); the bucketing sampler then
+        # works on those lengths and "batch_duration" is the token budget of a mini-batch
+        from .sampling import MultimodalSamplingConstraint
+
+        msc = MultimodalSamplingConstraint(c.get("token_equivalent_duration"), measure_total_length=bool(c.get("measure_total_length", False)),
+                                           tokenizer=tokenizer)
+        durs = [msc.measure_length(k) for k in ds.cuts]
+        c = {**c, "batch_duration": float(c["batch_tokens"]) if c.get("batch_tokens") else None,
+             "quadratic_duration": c.get("quadratic_factor")}
+    elif c.get("batch_tokens"):
         ted = float(c.get("token_equivalent_duration", 0.08))
         durs = [d + ds.num_tokens(i) * ted for i, d in enumerate(durs)]        # audio + text measured in seconds
         c = {**c, "batch_duration": float(c["batch_tokens"]) * ted}

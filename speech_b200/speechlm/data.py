@@ -30,6 +30,39 @@ def read_conversations(path: str) -> List[Dict[str, Any]]:
     return out
 
 
+def conversations_from_input_cfg(input_cfg, seed: int = 0, rank: int = 0, world: int = 1, max_examples: Optional[int] = None):
+    """Any mixture of the cut pipeline's sources (``multimodal_conversation``, ``share_gpt``, ``lhotse_as_conversation``,
+    ``nemo_sft_jsonl``, ``txt_pair``, plain audio manifests ...) as conversation records.  Audio cuts become
+    (audio, transcript) turns, text pairs (question + source, target) turns.  ``max_examples`` bounds sources that repeat."""
+    from ..core.config import DictConfig, to_container
+    from ..data.cuts import parse_input_cfg
+
+    if isinstance(input_cfg, DictConfig) or not isinstance(input_cfg, (list, str)):
+        input_cfg = to_container(input_cfg, resolve=True)
+    out = []
+    for k, c in enumerate(parse_input_cfg(input_cfg, seed, rank, world)):
+        if max_examples is not None and k >= max_examples:
+            break
+        kind = c.custom.get("kind")
+        if kind == "conversation":
+            out.append(c.custom["conversation"])
+        elif kind == "sft":
+            pre = [{"from": "System", "type": "text", "value": c.custom["system"]}] if c.custom.get("system") else []
+            out.append({"id": c.id, "conversations": pre + [{"from": t["role"].title(), "type": "text", "value": t["value"]} for t in c.custom["turns"]]})
+        elif kind == "text_pair":
+            q = c.custom.get("question")
+            out.append({"id": c.id, "conversations": [{"from": "User", "type": "text", "value": (q + " " if q else "") + c.custom["source"]},
+                                                      {"from": "Assistant", "type": "text", "value": c.custom["target"]}]})
+        elif kind == "text":
+            out.append({"id": c.id, "conversations": [{"from": "Assistant", "type": "text", "value": c.text}]})
+        else:
+            a = {"from": "User", "type": "audio", "value": c.audio if isinstance(c.audio, str) else c.id, "duration": c.duration, "offset": c.offset}
+            if not isinstance(c.audio, str):
+                a["audio"] = c.load_audio()
+            out.append({"id": c.id, "conversations": [a, {"from": "Assistant", "type": "text", "value": c.text}]})
+    return out
+
+
 class SALMDataset(Dataset):
     def __init__(self, conversations: Sequence[Dict[str, Any]], tokenizer, prompt_formatter, audio_locator_tag: str,
                  pad_id: int, sample_rate: int = 16000, token_equivalent_duration: float = 0.08):
@@ -58,7 +91,7 @@ class SALMDataset(Dataset):
             role = "assistant" if t["from"].lower() in ("assistant", "agent", "gpt") else \
                 ("system" if t["from"].lower() == "system" else "user")
             if t.get("type", "text") == "audio":
-                v = t["value"]
+                v = t["audio"] if t.get("audio") is not None else t["value"]
                 x = load_audio(v, target_sr=self.sr, offset=float(t.get("offset", 0.0) or 0.0), duration=t.get("duration")) \
                     if isinstance(v, str) else np.asarray(v, dtype=np.float32)
                 audios.append(torch.as_tensor(x, dtype=torch.float32))
@@ -146,7 +179,13 @@ class TokenBudgetLoader:
 def build_salm_dataloader(config, tokenizer, prompt_formatter, audio_locator_tag: str, pad_id: int, rank: int = 0, world_size: int = 1):
     get = config.get if hasattr(config, "get") else (lambda k, d=None: getattr(config, k, d))
     syn = get("synthetic", None)
-    convs = synthetic_conversations(**dict(syn)) if syn is not None else read_conversations(get("manifest_filepath"))
+    if syn is not None:
+        convs = synthetic_conversations(**dict(syn))
+    elif get("input_cfg", None) is not None:
+        convs = conversations_from_input_cfg(get("input_cfg"), seed=get("seed", 0), rank=rank, world=world_size,
+                                             max_examples=get("max_examples", None))
+    else:
+        convs = read_conversations(get("manifest_filepath"))
     ds = SALMDataset(convs, tokenizer, prompt_formatter, audio_locator_tag, pad_id, sample_rate=get("sample_rate", 16000),
                      token_equivalent_duration=get("token_equivalent_duration", 0.08))
     return TokenBudgetLoader(ds, batch_size=get("batch_size", None) or (None if get("batch_tokens", None) else 4),
