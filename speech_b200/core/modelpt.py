@@ -479,7 +479,8 @@ class ModelPT(nn.Module, Typing, Serialization):
         pass
 
     def on_train_end(self):
-        pass
+        if getattr(self, "_step_hooks", None) is not None:
+            self._step_hooks.close()
 
     def on_train_epoch_start(self):
         pass
@@ -487,11 +488,26 @@ class ModelPT(nn.Module, Typing, Serialization):
     def on_train_epoch_end(self):
         pass
 
+    def _hooks(self):
+        """Profiling windows and scheduled freezing read from ``cfg`` on first use (see :mod:`speech_b200.core.profiling`)."""
+        h = getattr(self, "_step_hooks", None)
+        if h is None:
+            from .profiling import StepHooks
+
+            rank = torch.distributed.get_rank() if torch.distributed.is_available() and torch.distributed.is_initialized() else 0
+            h = StepHooks(getattr(self, "cfg", None), rank=rank)
+            object.__setattr__(self, "_step_hooks", h)
+        return h
+
     def on_train_batch_start(self, batch, batch_idx: int):
-        pass
+        h = self._hooks()
+        if h.active:
+            h.batch_start(self, batch_idx, self.trainer.global_step if self.trainer is not None else batch_idx)
 
     def on_train_batch_end(self, outputs, batch, batch_idx: int):
-        pass
+        h = self._hooks()
+        if h.active:
+            h.batch_end(self, batch_idx, self.trainer.global_step if self.trainer is not None else batch_idx + 1)
 
     def on_after_backward(self):
         pass

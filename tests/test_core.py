@@ -231,3 +231,61 @@ def test_ema_optimizer_and_main_params_wrapper():
         naive(torch.ones(1, 8, dtype=torch.bfloat16)).sum().backward()
         o.step()
     assert float(naive.weight[0, 0]) == 1.0               # every update rounds away in bf16
+
+
+def test_step_hooks_profiling_windows_and_scheduled_freezing(tmp_path):
+    """nsys / memory windows call the profiler API on the configured steps and ranks only; freeze_updates freezes a
+    sub-module for its scheduled updates and keeps it in train mode."""
+    import torch
+    from speech_b200.core.config import OmegaConf
+    from speech_b200.core.profiling import StepHooks
+
+    class Api:
+        def __init__(self):
+            self.calls = []
+        def profiler_start(self): self.calls.append("start")
+        def profiler_stop(self): self.calls.append("stop")
+        def nvtx_push(self, n): self.calls.append("push")
+        def nvtx_pop(self): self.calls.append("pop")
+        def record_memory(self, on): self.calls.append(f"mem{int(on)}")
+        def dump_memory(self, path): self.calls.append("dump"); open(path, "wb").write(b"x")
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.encoder = torch.nn.Sequential(torch.nn.Linear(2, 2), torch.nn.Dropout(0.5))
+            self.decoder = torch.nn.Linear(2, 2)
+
+    cfg = OmegaConf.create({"nsys_profile": {"enabled": True, "start_step": 2, "end_step": 3, "ranks": [0]},
+                            "memory_profile": {"enabled": True, "start_step": 1, "end_step": 1, "rank": 0, "output_path": str(tmp_path)},
+                            "freeze_updates": {"enabled": True, "modules": {"encoder": 2, "decoder": [3, 4]}}})
+    api, m = Api(), M().train()
+    h = StepHooks(cfg, rank=0, cuda_api=api)
+    frozen = []
+    for step in range(6):
+        h.batch_start(m, step, step)
+        frozen.append((not m.encoder[0].weight.requires_grad, not m.decoder.weight.requires_grad))
+        assert m.encoder.training
+        h.batch_end(m, step, step + 1)
+    assert frozen == [(True, False), (True, False), (False, True), (False, True), (False, False), (False, False)]
+    assert api.calls == ["mem1", "dump", "mem0", "start", "push", "pop", "push", "pop", "stop"]
+    assert (tmp_path / "memory_profile_rank0.pickle").exists()
+    other = Api()
+    h1 = StepHooks(cfg, rank=1, cuda_api=other)
+    for step in range(5):
+        h1.batch_start(m, step, step); h1.batch_end(m, step, step + 1)
+    assert other.calls == []
+    import pytest
+    with pytest.raises(ValueError, match="end_step"):
+        StepHooks(OmegaConf.create({"nsys_profile": {"enabled": True, "start_step": 5, "end_step": 1}}))
+    with pytest.raises(ValueError, match="output_path"):
+        StepHooks(OmegaConf.create({"memory_profile": {"enabled": True, "start_step": 0, "end_step": 1, "output_path": None}}))
+    # execution-trace capture on CPU
+    ch = StepHooks(OmegaConf.create({"chakra_profile": {"enabled": True, "start_step": 1, "end_step": 2, "warmup_steps": 0, "active_steps": 2,
+                                                        "trace_dir": str(tmp_path)}}), rank=0, cuda_api=Api())
+    for step in range(4):
+        ch.batch_start(m, step, step)
+        m.decoder(torch.randn(3, 2)).sum().backward()
+        ch.batch_end(m, step, step + 1)
+    import glob
+    assert glob.glob(str(tmp_path / "*_chakra" / "rank-0.json"))
