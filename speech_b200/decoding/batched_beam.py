@@ -31,6 +31,7 @@ class BatchedBeamHyps:
         self.scores = torch.full((B, K), NEG, dtype=torch.float32, device=device)
         self.scores[:, 0] = 0.0
         self.hash = torch.zeros((B, K), dtype=torch.long, device=device)
+        self.prev_hash = torch.full((B, K), -1, dtype=torch.long, device=device)   # hash of the transcript without its last token
         self.last_label = torch.full((B, K), blank, dtype=torch.long, device=device)
 
     def _grow(self):
@@ -48,12 +49,14 @@ class BatchedBeamHyps:
         self.frames = self.frames.gather(1, idx)
         self.lengths = self.lengths.gather(1, src)
         self.hash = self.hash.gather(1, src)
+        self.prev_hash = self.prev_hash.gather(1, src)
         self.last_label = self.last_label.gather(1, src)
         add = (labels >= 0) & (labels != self.blank)
         pos = self.lengths.clamp(max=self.max_len - 1).unsqueeze(-1)
         self.tokens.scatter_(2, pos, torch.where(add, labels, self.tokens.gather(2, pos).squeeze(-1)).unsqueeze(-1))
         self.frames.scatter_(2, pos, torch.where(add, frames, self.frames.gather(2, pos).squeeze(-1)).unsqueeze(-1))
         self.lengths = self.lengths + add.long()
+        self.prev_hash = torch.where(add, self.hash, self.prev_hash)
         self.hash = torch.where(add, (self.hash * _HASH_MUL + labels + 1) % 2305843009213693951, self.hash)
         self.last_label = torch.where(add, labels, self.last_label)
         self.scores = scores
@@ -204,6 +207,132 @@ class ModifiedALSDBatchedComputer:
                 fstates[i] = torch.where(emitted, adv, st_src)
             hyps.recombine(extra_key=t_idx)
         self.final_t = t_idx
+        return hyps
+
+
+class ModifiedAESBatchedComputer:
+    """Batched modified adaptive expansion search (mAES) for plain RNNT (reference ``rnnt_maes_batched_computer.py:30-370``,
+    after Kim et al., "Accelerating RNN transducer inference via adaptive expansion search").
+
+    The search is time synchronous: every beam entry of an utterance sits on the same frame.  On each frame the beam is
+    expanded ``maes_num_steps`` times.  One expansion takes the ``beam_size + maes_expansion_beta`` best tokens (blank
+    included) of every entry that has not taken blank on this frame yet, drops the candidates more than
+    ``maes_expansion_gamma`` below that entry's best candidate, removes candidates that spell the same transcript, and
+    keeps the best ``beam_size`` of the candidates and of the entries already closed on this frame.  Entries still open
+    after the last expansion are closed with a forced blank.  Before the expansions a *prefix search* adds to an entry
+    the probability of reaching it from another beam entry that is its prefix by one token.
+    """
+
+    def __init__(self, decoder, joint, blank_index: int, beam_size: int = 4, maes_num_steps: int = 2, maes_expansion_beta: int = 2,
+                 maes_expansion_gamma: float = 2.3, fusion_models=None, fusion_models_alpha=None, score_norm: bool = True,
+                 durations=None, **_):
+        if durations:
+            raise ValueError("maes_batch decodes plain RNNT only; use malsd_batch for TDT models")
+        if maes_num_steps < 1:
+            raise ValueError("maes_num_steps must be at least 1")
+        self.decoder, self.joint = decoder, joint
+        self.blank, self.K = blank_index, beam_size
+        self.steps, self.gamma = int(maes_num_steps), float(maes_expansion_gamma)
+        self.E = beam_size + int(maes_expansion_beta)
+        self.fusion_models = list(fusion_models or [])
+        self.fusion_alphas = list(fusion_models_alpha or [])
+        self.score_norm = score_norm
+
+    @torch.no_grad()
+    def __call__(self, x: torch.Tensor, out_len: torch.Tensor) -> BatchedBeamHyps:
+        B, T, _ = x.shape
+        K, dev, dt = self.K, x.device, torch.float32
+        enc = self.joint.project_encoder(x.to(dt))
+        lin, act = self.joint.joint_net[-1], self.joint.joint_net[0]
+        V1 = lin.out_features
+        E = min(self.E, V1)
+        hyps = BatchedBeamHyps(B, K, init_length=T, device=dev, blank=self.blank)
+        dec_out, state = self.decoder.predict(None, state=None, add_sos=False, batch_size=B * K)
+        state = [s for s in state] if state is not None else None
+        dec_proj = self.joint.project_prednet(dec_out.to(dt))[:, 0]              # [B*K, H]
+        out_len = out_len.to(dev)
+        fstates = [m.get_init_states(B * K, bos=True).view(B, K) for m in self.fusion_models]
+        brange = torch.arange(B, device=dev).view(B, 1)
+
+        def logps_at(t):
+            f = enc[:, min(t, T - 1)].unsqueeze(1)                                 # [B,1,H]
+            logits = torch.nn.functional.linear(act(f + dec_proj.view(B, K, -1)), lin.weight.to(dt), lin.bias.to(dt))
+            lp = torch.log_softmax(logits, dim=-1)
+            nxt = []
+            for m, a, st in zip(self.fusion_models, self.fusion_alphas, fstates):
+                sc, nx = m.advance(st.reshape(-1))
+                lp[..., : self.blank] += a * sc.view(B, K, -1).to(dt)
+                nxt.append(nx.view(B, K, -1))
+            return lp, nxt
+
+        for t in range(int(T)):
+            frame_on = (out_len > t).view(B, 1)
+            alive = hyps.scores > NEG / 2
+            open_ = frame_on & alive                                                # entries that may still emit on this frame
+            if not bool(open_.any()):
+                break
+            lp, fnext = logps_at(t)
+            # prefix search: entry j = entry i + [v]  =>  score_j (+)= score_i + log p_i(v)
+            ext = (hyps.prev_hash.unsqueeze(1) == hyps.hash.unsqueeze(2)) & (hyps.lengths.unsqueeze(1) == hyps.lengths.unsqueeze(2) + 1)
+            ext = ext & open_.unsqueeze(2) & open_.unsqueeze(1)                     # [b, i, j]
+            via = hyps.scores.unsqueeze(2) + lp.gather(2, hyps.last_label.clamp(max=V1 - 1).unsqueeze(1).expand(B, K, K))
+            via = via.masked_fill(~ext, NEG)
+            hyps.scores = torch.where(open_, torch.logsumexp(torch.cat([hyps.scores.unsqueeze(1), via], dim=1), dim=1), hyps.scores)
+            tvec = torch.full((B, K), t, device=dev, dtype=torch.long)
+            for _ in range(self.steps):
+                if not bool(open_.any()):
+                    break
+                top_s, top_v = lp.topk(E, dim=-1)                                   # [B,K,E]
+                cand = hyps.scores.unsqueeze(-1) + top_s
+                cand = cand.masked_fill(cand <= cand.max(dim=-1, keepdim=True).values - self.gamma, NEG)
+                cand = cand.masked_fill(~open_.unsqueeze(-1), NEG)
+                cand_lab = top_v
+                # a closed entry competes unchanged through the last slot of its row
+                closed = alive & ~open_
+                cand[..., -1] = torch.where(closed, hyps.scores, cand[..., -1])
+                cand_lab = cand_lab.clone()
+                cand_lab[..., -1] = torch.where(closed, torch.full_like(top_v[..., -1], -1), cand_lab[..., -1])
+                # duplicates: same transcript after the step and same open / closed status
+                is_tok = (cand_lab >= 0) & (cand_lab != self.blank)
+                new_hash = torch.where(is_tok, (hyps.hash.unsqueeze(-1) * _HASH_MUL + cand_lab + 1) % 2305843009213693951,
+                                       hyps.hash.unsqueeze(-1).expand(B, K, E))
+                key_h, key_o, sc = new_hash.reshape(B, K * E), is_tok.reshape(B, K * E), cand.reshape(B, K * E)
+                same = (key_h.unsqueeze(2) == key_h.unsqueeze(1)) & (key_o.unsqueeze(2) == key_o.unsqueeze(1))
+                live = sc > NEG / 2
+                same = same & live.unsqueeze(1) & live.unsqueeze(2)
+                better = same & ((sc.unsqueeze(1) > sc.unsqueeze(2)) |
+                                 ((sc.unsqueeze(1) == sc.unsqueeze(2)) &
+                                  (torch.arange(K * E, device=dev).view(1, 1, -1) < torch.arange(K * E, device=dev).view(1, -1, 1))))
+                sc = sc.masked_fill(better.any(dim=2), NEG)                          # someone equal and better exists
+                best_s, best_i = sc.topk(K, dim=1)
+                src = best_i // E
+                lab = cand_lab.reshape(B, K * E).gather(1, best_i)
+                lab = torch.where(best_s > NEG / 2, lab, torch.full_like(lab, -1))
+                emitted = (lab >= 0) & (lab != self.blank)
+                was_open = open_.gather(1, src)
+                hyps.reorder_and_extend(src, lab, tvec, best_s)
+                flat_src = (brange * K + src).reshape(-1)
+                if state is not None:
+                    state = [s.index_select(1, flat_src) for s in state]
+                dec_proj = dec_proj.index_select(0, flat_src)
+                emb_in = torch.where(emitted, lab, torch.full_like(lab, self.blank)).reshape(-1, 1)
+                new_out, new_state = self.decoder.predict(emb_in, state=state, add_sos=False, batch_size=B * K)
+                new_proj = self.joint.project_prednet(new_out.to(dt))[:, 0]
+                em = emitted.reshape(-1)
+                dec_proj = torch.where(em.unsqueeze(-1), new_proj, dec_proj)
+                if state is not None:
+                    state = [torch.where(em.view(1, -1, 1), ns, s) for ns, s in zip(new_state, state)]
+                for i in range(len(fstates)):
+                    st_src = fstates[i].gather(1, src)
+                    nx = fnext[i].gather(1, src.unsqueeze(-1).expand(-1, -1, fnext[i].shape[-1]))
+                    adv = nx.gather(2, lab.clamp(min=0, max=self.blank - 1).unsqueeze(-1)).squeeze(-1)
+                    fstates[i] = torch.where(emitted, adv, st_src)
+                alive = hyps.scores > NEG / 2
+                open_ = was_open & emitted & alive
+                lp, fnext = logps_at(t)
+            if bool(open_.any()):
+                hyps.scores = torch.where(open_, hyps.scores + lp[..., self.blank], hyps.scores)
+            hyps.recombine()
         return hyps
 
 

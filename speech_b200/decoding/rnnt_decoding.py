@@ -274,6 +274,11 @@ class GreedyBatchedRNNTInfer:
                  use_cuda_graph_decoder=True, include_duration=False, fusion_models=None, fusion_models_alpha=None, **_):
         self.decoder, self.joint = decoder_model, joint_model
         self._blank_index = blank_index
+        self.frame_looping = None
+        if not loop_labels and not durations and not fusion_models and not preserve_alignments:
+            from .rnnt_greedy import FrameLoopingBatchedComputer
+
+            self.frame_looping = FrameLoopingBatchedComputer(decoder_model, joint_model, blank_index, max_symbols_per_step)
         self.decoding_computer = GreedyBatchedLabelLoopingComputer(
             decoder_model, joint_model, blank_index, durations, max_symbols_per_step, preserve_alignments,
             preserve_frame_confidence, include_duration, fusion_models, fusion_models_alpha,
@@ -291,6 +296,12 @@ class GreedyBatchedRNNTInfer:
         """encoder_output: [B, D, T].  ``partial_hypotheses`` carry the decoder state for streaming continuation."""
         x = encoder_output.transpose(1, 2)
         prev = None
+        if self.frame_looping is not None and partial_hypotheses is None:
+            hyps = self.frame_looping(x, encoded_lengths.to(x.device))
+            out = batched_hyps_to_hypotheses(hyps, None, batch_size=x.shape[0])
+            for h, n in zip(out, encoded_lengths.tolist()):
+                h.last_frame = int(n)
+            return (out,)
         if partial_hypotheses is not None and any(h is not None and h.dec_state is not None for h in partial_hypotheses):
             # streams that join a running batch start from the prediction net's start-symbol state
             fresh = None
@@ -327,14 +338,20 @@ class BeamBatchedRNNTInfer:
 
     def __init__(self, decoder_model, joint_model, blank_index: int, beam_size: int = 4, durations=None,
                  max_symbols_per_step=10, score_norm: bool = True, return_best_hypothesis: bool = True,
-                 fusion_models=None, fusion_models_alpha=None, **_):
-        from .batched_beam import ModifiedALSDBatchedComputer
+                 fusion_models=None, fusion_models_alpha=None, search_type: str = "malsd_batch", maes_num_steps: int = 2,
+                 maes_expansion_beta: int = 2, maes_expansion_gamma: float = 2.3, **_):
+        from .batched_beam import ModifiedAESBatchedComputer, ModifiedALSDBatchedComputer
 
         self.return_best_hypothesis = return_best_hypothesis
         self.score_norm = score_norm
-        self.decoding_computer = ModifiedALSDBatchedComputer(
-            decoder_model, joint_model, blank_index, beam_size, durations, max_symbols_per_step, fusion_models,
-            fusion_models_alpha, score_norm=score_norm)
+        if search_type == "maes_batch":
+            self.decoding_computer = ModifiedAESBatchedComputer(
+                decoder_model, joint_model, blank_index, beam_size, maes_num_steps, maes_expansion_beta, maes_expansion_gamma,
+                fusion_models, fusion_models_alpha, score_norm=score_norm, durations=durations)
+        else:
+            self.decoding_computer = ModifiedALSDBatchedComputer(
+                decoder_model, joint_model, blank_index, beam_size, durations, max_symbols_per_step, fusion_models,
+                fusion_models_alpha, score_norm=score_norm)
 
     @torch.no_grad()
     def __call__(self, encoder_output: torch.Tensor, encoded_lengths: torch.Tensor, partial_hypotheses=None):
@@ -409,7 +426,16 @@ class AbstractRNNTDecoding:
         self.strategy = strategy
         g = cfg_get(self.cfg, "greedy", None) or {}
         bm = cfg_get(self.cfg, "beam", None) or {}
-        if strategy in ("greedy", "greedy_batch"):
+        if strategy == "greedy" and not cfg_get(g, "ngram_lm_model", None) and not cfg_get(g, "boosting_tree", None):
+            from .rnnt_greedy import GreedyRNNTInfer
+
+            self.decoding = GreedyRNNTInfer(
+                decoder, joint, blank_id, durations=self.durations,
+                max_symbols_per_step=cfg_get(g, "max_symbols", None) or cfg_get(g, "max_symbols_per_step", 10),
+                preserve_alignments=bool(self.preserve_alignments),
+                preserve_frame_confidence=bool(cfg_get(self.cfg, "preserve_frame_confidence", False)),
+                include_duration=bool(self.tdt_include_token_duration))
+        elif strategy in ("greedy", "greedy_batch"):
             fusion_models, alphas = [], []
             if cfg_get(g, "ngram_lm_model", None):
                 from .ngram_lm import NGramGPULanguageModel
@@ -445,7 +471,9 @@ class AbstractRNNTDecoding:
                 decoder, joint, blank_id, beam_size=cfg_get(bm, "beam_size", 4), durations=self.durations,
                 max_symbols_per_step=cfg_get(bm, "max_symbols_per_step", None) or cfg_get(bm, "max_symbols", 10),
                 score_norm=cfg_get(bm, "score_norm", True), return_best_hypothesis=cfg_get(bm, "return_best_hypothesis", True),
-                fusion_models=fusion_models, fusion_models_alpha=alphas)
+                fusion_models=fusion_models, fusion_models_alpha=alphas, search_type=strategy,
+                maes_num_steps=cfg_get(bm, "maes_num_steps", 2), maes_expansion_beta=cfg_get(bm, "maes_expansion_beta", 2),
+                maes_expansion_gamma=cfg_get(bm, "maes_expansion_gamma", 2.3))
         else:
             st = {"beam": "default"}.get(strategy, strategy)
             self.decoding = BeamRNNTInfer(

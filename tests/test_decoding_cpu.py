@@ -246,3 +246,101 @@ def test_lexicon_ctc_beam_decoder_with_word_lm_and_graph_roundtrip(tmp_path):
     assert r1[0].word_frames[0] in (4, 5) and len(r1[0].word_frames) == 3
     batch = dec.decode_batch(np.stack([x, x]), [9, 4])
     assert batch[0].text == "cats a at" and batch[1].words == ["cats"]
+
+
+def _tiny_transducer(loss="rnnt", seed=1):
+    from speech_b200.models import EncDecRNNTBPEModel
+    from speech_b200.models.configs import fastconformer_transducer_config
+
+    torch.manual_seed(seed)
+    m = EncDecRNNTBPEModel(fastconformer_transducer_config("small", vocab_size=16, loss=loss, dropout=0.0, n_layers=1, sched=None, lr=1e-3))
+    # a bias towards labels so that the random model emits several tokens per utterance
+    with torch.no_grad():
+        m.joint.joint_net[-1].bias[:16] += 1.0
+    return m.eval()
+
+
+def _exact_log_prob(m, enc_b, tokens):
+    """log p(tokens | frames) of an RNNT by the forward recursion over the full lattice (plain loops, one utterance)."""
+    blank = m.decoding.blank_id
+    T, U = enc_b.shape[0], len(tokens)
+    dec_out, state = m.decoder.predict(None, state=None, add_sos=False, batch_size=1)
+    outs = [dec_out]
+    for tok in tokens:
+        o, state = m.decoder.predict(torch.tensor([[tok]]), state=state, add_sos=False, batch_size=1)
+        outs.append(o)
+    g = m.joint.project_prednet(torch.cat(outs, dim=1).float())[0]           # [U+1, H]
+    f = m.joint.project_encoder(enc_b.float().unsqueeze(0))[0]                # [T, H]
+    lin, act = m.joint.joint_net[-1], m.joint.joint_net[0]
+    lp = torch.log_softmax(torch.nn.functional.linear(act(f[:, None] + g[None]), lin.weight.float(), lin.bias.float()), dim=-1)
+    alpha = torch.full((T, U + 1), -1e30)
+    alpha[0, 0] = 0.0
+    for t in range(T):
+        for u in range(U + 1):
+            c = []
+            if t > 0:
+                c.append(alpha[t - 1, u] + lp[t - 1, u, blank])
+            if u > 0:
+                c.append(alpha[t, u - 1] + lp[t, u - 1, tokens[u - 1]])
+            if c:
+                alpha[t, u] = torch.logsumexp(torch.stack(c), dim=0)
+    return float((alpha[T - 1, U] + lp[T - 1, U, blank]).detach())
+
+
+def test_maes_batched_is_batch_invariant_and_scores_are_path_sums_below_the_exact_probability():
+    from speech_b200.decoding.batched_beam import ModifiedAESBatchedComputer
+
+    m = _tiny_transducer()
+    blank = m.decoding.blank_id
+    enc = torch.randn(3, 6, 176)
+    lens = torch.tensor([6, 4, 5])
+    comp = ModifiedAESBatchedComputer(m.decoder, m.joint, blank, beam_size=3, maes_num_steps=2, maes_expansion_beta=1, maes_expansion_gamma=4.0)
+    full = comp(enc, lens).to_hyps_list(score_norm=False)
+    for b in range(3):
+        single = comp(enc[b:b + 1, : int(lens[b])], lens[b:b + 1]).to_hyps_list(score_norm=False)[0]
+        assert [h[0] for h in single] == [h[0] for h in full[b]]
+        assert all(abs(x[2] - y[2]) < 1e-3 for x, y in zip(single, full[b]))
+        # every beam entry is a distinct transcript whose score sums some of its alignments: it cannot exceed the exact value
+        assert len({tuple(h[0]) for h in full[b]}) == len(full[b])
+        for tok, frames, s in full[b]:
+            assert len(frames) == len(tok) and all(0 <= f < int(lens[b]) for f in frames)
+            exact = _exact_log_prob(m, enc[b, : int(lens[b])], tok)
+            assert s <= exact + 1e-3
+    # the best beam entry is at least as probable as the greedy transcript
+    greedy = m.decoding.rnnt_decoder_predictions_tensor(enc.transpose(1, 2), lens, return_hypotheses=True)
+    for b in range(3):
+        g_exact = _exact_log_prob(m, enc[b, : int(lens[b])], greedy[b].y_sequence.tolist())
+        best_exact = max(_exact_log_prob(m, enc[b, : int(lens[b])], h[0]) for h in full[b])
+        assert best_exact >= g_exact - 1e-3
+    with pytest.raises(ValueError, match="plain RNNT"):
+        ModifiedAESBatchedComputer(m.decoder, m.joint, blank, durations=[0, 1, 2])
+
+
+def test_greedy_variants_agree_and_strategies_dispatch():
+    from speech_b200.decoding.rnnt_decoding import RNNTBPEDecoding
+    from speech_b200.decoding.rnnt_greedy import FrameLoopingBatchedComputer, GreedyRNNTInfer
+
+    m = _tiny_transducer()
+    enc = torch.randn(3, 9, 176)
+    lens = torch.tensor([9, 5, 7])
+    ref = m.decoding.rnnt_decoder_predictions_tensor(enc.transpose(1, 2), lens, return_hypotheses=True)
+    assert sum(len(h.y_sequence) for h in ref) > 3
+    fl = FrameLoopingBatchedComputer(m.decoder, m.joint, m.decoding.blank_id, 10)(enc, lens)
+    per = GreedyRNNTInfer(m.decoder, m.joint, m.decoding.blank_id, max_symbols_per_step=10, preserve_alignments=True)(enc.transpose(1, 2), lens)[0]
+    for b in range(3):
+        n = int(fl.current_lengths[b])
+        assert fl.transcript[b, :n].tolist() == ref[b].y_sequence.tolist() == per[b].y_sequence.tolist()
+        assert fl.timestamps[b, :n].tolist() == ref[b].timestamp.tolist() == per[b].timestamp.tolist()
+        assert len(per[b].alignments) <= int(lens[b])
+    for strategy, extra in (("greedy", {}), ("greedy_batch", {"greedy": {"loop_labels": False}}), ("maes_batch", {"beam": {"beam_size": 2}})):
+        d = RNNTBPEDecoding({"strategy": strategy, **extra}, m.decoder, m.joint, m.tokenizer)
+        out = d.rnnt_decoder_predictions_tensor(enc.transpose(1, 2), lens, return_hypotheses=True)
+        if strategy != "maes_batch":
+            assert [h.y_sequence.tolist() for h in out] == [h.y_sequence.tolist() for h in ref]
+        assert all(isinstance(h.text, str) for h in out)
+    # per-sample greedy on a TDT model equals the label-looping decoder
+    mt = _tiny_transducer(loss="tdt", seed=3)
+    ref_t = mt.decoding.rnnt_decoder_predictions_tensor(enc.transpose(1, 2), lens, return_hypotheses=True)
+    per_t = GreedyRNNTInfer(mt.decoder, mt.joint, mt.decoding.blank_id, durations=mt.decoding.durations, max_symbols_per_step=10)(enc.transpose(1, 2), lens)[0]
+    for b in range(3):
+        assert per_t[b].y_sequence.tolist() == ref_t[b].y_sequence.tolist() and per_t[b].timestamp.tolist() == ref_t[b].timestamp.tolist()
