@@ -457,13 +457,19 @@ class ModelPT(nn.Module, Typing, Serialization):
                                                                 fusion_groups=fusion, **kwargs)
             elif name in ("fully_sharded_adamw", "fsdp2_adamw"):
                 clip = getattr(tr, "gradient_clip_val", 0.0) if tr is not None else 0.0
-                optimizer = _optim.get_optimizer(name)(groups, model=self, lr=lr, max_grad_norm=clip or 0.0, device=self.device, **kwargs)
+                optimizer = _optim.get_optimizer(name)(groups, model=self, lr=lr, max_grad_norm=clip or 0.0, device=self.device,
+                                                       **{**kwargs, **self._sharded_optimizer_kwargs()})
             else:
                 optimizer = _optim.get_optimizer(name)(groups, lr=lr, **kwargs)
         self._optimizer = optimizer
         self._scheduler = _sched.prepare_lr_scheduler(optimizer, sched_cfg and optim_config, self._train_dl) \
             if sched_cfg is not None else None
         return self._optimizer, self._scheduler
+
+    def _sharded_optimizer_kwargs(self) -> Dict[str, Any]:
+        """Extra arguments of the fully-sharded optimizer (``group``, ``replicate_group``, ``units``); models that live on a
+        device mesh override this."""
+        return {}
 
     def configure_optimizers(self):
         self.setup_optimization()

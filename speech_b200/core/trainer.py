@@ -427,6 +427,10 @@ class Trainer:
     def _clip_gradients(self, opt):
         if self.gradient_clip_val <= 0 or getattr(opt, "max_grad_norm", 0.0) > 0:
             return  # fused optimizers clip inside their update kernel
+        custom = getattr(self.model, "configure_gradient_clipping", None)
+        if custom is not None:
+            custom(opt, self.gradient_clip_val)       # models on a device mesh compute the norm over the right groups
+            return
         params = [p for g in opt.param_groups for p in g["params"] if p.grad is not None]
         if params:
             torch.nn.utils.clip_grad_norm_(params, self.gradient_clip_val)

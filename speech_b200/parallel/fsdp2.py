@@ -151,7 +151,7 @@ class FullyShardedAdamW(Optimizer):
                     o, n = u.offsets[id(p)]
                     flat[o:o + n].copy_(p.data.reshape(-1).to(dev))
                 if self.world > 1:
-                    dist.broadcast(flat, 0, group=group)           # all ranks start from rank 0's values
+                    dist.broadcast(flat, dist.get_global_rank(group, 0) if group is not None else 0, group=group)   # start from the group's first rank
                 self.master[u.shard_base:u.shard_base + u.slice].copy_(flat[self.rank * u.slice:(self.rank + 1) * u.slice])
                 for p in u.params:
                     p.data = torch.empty(0, dtype=torch.float32, device=dev)   # nothing is replicated while a unit is not gathered
@@ -395,7 +395,15 @@ class FullyShardedAdamW(Optimizer):
             self.grad_shard.div_(self.replicas)
             dist.all_reduce(self.grad_shard, group=self.replicate_group)
         if self.max_grad_norm > 0:
-            if self.cuda and self.world > 1 and self.replicas == 1:
+            if getattr(self, "_tp_mask", None) is not None:
+                # tensor-parallel model: slices of tensor-parallel parameters differ over the tp group and are summed there;
+                # everything else is replicated over it and counted once
+                g2 = self.grad_shard.double().pow(2)
+                sq_tp = (g2 * self._tp_mask).sum().float().view(1)
+                sq_rep = g2.sum().float().view(1) - sq_tp
+                dist.all_reduce(sq_tp, group=self._tp_group)
+                sq = sq_tp + sq_rep
+            elif self.cuda and self.world > 1 and self.replicas == 1:
                 sq = self._scalars[3:4].clone()
             else:
                 sq = self.grad_shard.double().pow(2).sum().float().view(1)
@@ -417,6 +425,22 @@ class FullyShardedAdamW(Optimizer):
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         pass           # gradient slots are zeroed when a unit's backward starts
+
+    def set_tensor_parallel(self, tp_group, is_tp_param) -> None:
+        """Make the clipping norm exact on a (data-parallel x tensor-parallel) mesh.  ``is_tp_param(p)`` says whether ``p``
+        holds one tensor-parallel slice of a larger weight (its squared gradient norm is then summed over ``tp_group``);
+        other parameters are replicas over that group and enter the norm once."""
+        mask = torch.zeros(self.shard_numel, dtype=torch.bool, device=self.device)
+        for u in self.all_units:
+            lo, hi = self.rank * u.slice, (self.rank + 1) * u.slice
+            for q in u.params:
+                if not is_tp_param(q):
+                    continue
+                o, n = u.offsets[id(q)]
+                a, b = max(o, lo), min(o + n, hi)
+                if a < b:
+                    mask[u.shard_base + a - lo:u.shard_base + b - lo] = True
+        self._tp_mask, self._tp_group = mask, tp_group
 
     @property
     def last_grad_norm(self) -> torch.Tensor:

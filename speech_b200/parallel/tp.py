@@ -206,10 +206,12 @@ def _shard_linear(lin: nn.Linear, dim: int, rank: int, ws: int) -> None:
     if w.shape[dim] % ws:
         raise ValueError(f"cannot split dimension of size {w.shape[dim]} over {ws} ranks")
     lin.weight = nn.Parameter(w.chunk(ws, dim=dim)[rank].clone(), requires_grad=lin.weight.requires_grad)
+    lin.weight._tensor_parallel = True          # one slice of a larger weight: norms and checkpoints treat it as such
     if dim == 0:
         lin.out_features = lin.weight.shape[0]
         if lin.bias is not None:
             lin.bias = nn.Parameter(lin.bias.data.chunk(ws, dim=0)[rank].clone(), requires_grad=lin.bias.requires_grad)
+            lin.bias._tensor_parallel = True
     else:
         lin.in_features = lin.weight.shape[1]
         if lin.bias is not None and rank != 0:
@@ -242,22 +244,74 @@ def apply_tensor_parallel_llm(llm, group, sequence_parallel: bool = False) -> No
                 fwd = norm.forward
                 norm.forward = (lambda x, f=fwd, g=group: GatherFromSP.apply(f(x), g, 1))
                 for p in norm.parameters():
-                    p._sequence_parallel = True       # gradients of shard-wise norms are partial: summed over the group
+                    _sum_grad_over_group(p, group)    # gradients of shard-wise norms are partial: summed over the group
         else:
             layer.tp_reduce = (lambda x, g=group: ReduceFromTP.apply(x, g))
             _wrap_inputs(layer, group)
+        # per-head norms of queries / keys are replicated weights that see only this rank's heads
+        for name in ("q_norm", "k_norm"):
+            nm = getattr(att, name, None)
+            if isinstance(nm, nn.Module):
+                for p in nm.parameters():
+                    _sum_grad_over_group(p, group)
     if sequence_parallel:
         llm.model.sp_scatter = (lambda x, g=group: ScatterToSP.apply(x, g, 1))
         llm.model.sp_gather = (lambda x, g=group: GatherFromSPReplicated.apply(x, g, 1))
         for p in llm.model.norm.parameters():
-            p._sequence_parallel = True
+            _sum_grad_over_group(p, group)
+
+
+def clip_grad_norm_mesh(params, max_norm: float, tp_group=None, dp_shard_group=None, sharded=lambda p: False) -> torch.Tensor:
+    """Global-norm clipping on a mesh.  A parameter tagged ``_tensor_parallel`` is one slice of a weight split over
+    ``tp_group``: its squared norm is summed over that group.  A parameter for which ``sharded(p)`` holds is a slice over
+    ``dp_shard_group`` and is summed there.  All other parameters are replicas and count once, so that every rank arrives at
+    the same norm (the reference groups DTensor gradients by mesh and placement to the same end, ``salm_automodel.py:551-567``)."""
+    params = [p for p in params if p.grad is not None]
+    if not params:
+        return torch.zeros(())
+    dev = params[0].grad.device
+    sq = {"rep": torch.zeros((), device=dev, dtype=torch.float32), "tp": torch.zeros((), device=dev, dtype=torch.float32),
+          "dp": torch.zeros((), device=dev, dtype=torch.float32), "tpdp": torch.zeros((), device=dev, dtype=torch.float32)}
+    for p in params:
+        key = ("tp" if getattr(p, "_tensor_parallel", False) else "") + ("dp" if sharded(p) else "") or "rep"
+        sq[key] += p.grad.detach().float().pow(2).sum()
+    if tp_group is not None:
+        buf = torch.stack([sq["tp"], sq["tpdp"]])
+        dist.all_reduce(buf, group=tp_group)
+        sq["tp"], sq["tpdp"] = buf[0], buf[1]
+    if dp_shard_group is not None:
+        buf = torch.stack([sq["dp"], sq["tpdp"]])
+        dist.all_reduce(buf, group=dp_shard_group)
+        sq["dp"], sq["tpdp"] = buf[0], buf[1]
+    norm = (sq["rep"] + sq["tp"] + sq["dp"] + sq["tpdp"]).sqrt()
+    coef = torch.clamp(max_norm / (norm + 1e-6), max=1.0)
+    for p in params:
+        p.grad.mul_(coef.to(p.grad.dtype))
+    return norm
+
+
+def _sum_grad_over_group(p: nn.Parameter, group) -> None:
+    """A replicated parameter whose gradient on each rank covers only part of the work (a sequence shard, this rank's heads):
+    the incoming gradient of every backward pass is summed over ``group`` before it is accumulated, so gradient accumulation
+    and sharded optimizers that consume gradients inside backward both see the full gradient."""
+    if getattr(p, "_partial_grad_group", None) is not None:
+        return
+    p._partial_grad_group = group
+    p._sequence_parallel = True
+
+    def hook(g, group=group):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=group)
+        return g
+    p.register_hook(hook)
 
 
 def allreduce_sequence_parallel_grads(module: nn.Module, group) -> None:
-    """Sum the gradients of parameters that saw only a sequence shard (norm weights) over the tensor-parallel group; call after
-    backward, before the optimizer step."""
+    """Sum partial gradients of replicated parameters over the tensor-parallel group after backward.  Parameters prepared by
+    :func:`apply_tensor_parallel_llm` do this themselves in a gradient hook and are skipped; the call remains for modules
+    whose parameters were tagged ``_sequence_parallel`` by hand."""
     for p in module.parameters():
-        if getattr(p, "_sequence_parallel", False) and p.grad is not None:
+        if getattr(p, "_sequence_parallel", False) and getattr(p, "_partial_grad_group", None) is None and p.grad is not None:
             dist.all_reduce(p.grad, group=group)
 
 

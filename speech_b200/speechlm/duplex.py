@@ -7,11 +7,9 @@
   codes (one table per codebook) and an audio head predicts the next codes of all codebooks; generated codes are turned into a
   waveform by the codec.  Codebook vocabulary = codec size + 3 control codes (speech BOS / EOS / delay).
 * ``SALMWithAsrDecoder`` — SALM plus an auxiliary CTC head on the perception output (loss = LLM loss + ``asr_weight`` · CTC).
-* ``SALMAutomodel`` — SALM constructed under a device mesh: tensor-parallel plan applied to the LLM blocks and the sharded
-  optimizer chosen from the mesh's data-parallel size.
 
 Reference: ``speechlm2/models/duplex_s2s_model.py:48-400`` (channels, control codes, ``forward`` with ``text_logits`` /
-``audio_logits``, ``offline_inference``), ``duplex_stt_model.py``, ``salm_asr_decoder.py``, ``salm_automodel.py:373-390``.
+``audio_logits``, ``offline_inference``), ``duplex_stt_model.py``, ``salm_asr_decoder.py``.
 """
 from __future__ import annotations
 
@@ -245,17 +243,3 @@ class SALMWithAsrDecoder(SALM):
         return out
 
 
-class SALMAutomodel(SALM):
-    """SALM set up for a device mesh: ``configure_model(mesh)`` applies the tensor-parallel plan to the LLM blocks (column /
-    row parallel projections, vocabulary-parallel head) and records the data-parallel group used for loss normalisation."""
-
-    def configure_model(self, mesh=None) -> None:
-        self.device_mesh = mesh
-        if mesh is None:
-            return
-        from ..parallel.tp import apply_tensor_parallel_llm
-
-        tp = mesh.group("tp") if mesh.size("tp") > 1 else None
-        if tp is not None:
-            apply_tensor_parallel_llm(self.llm, tp)
-        self.dp_group = mesh.group("dp") if mesh.size("dp") > 1 else None

@@ -1,0 +1,240 @@
+"""SALM trained on a device mesh: fully-sharded / hybrid-sharded data parallelism, tensor + sequence parallelism, packed
+batches and losses normalised by the global number of labelled tokens.
+
+The reference gets these from ``nemo_automodel`` (``speechlm2/models/salm_automodel.py``: FSDP2 / HSDP / TP / SP plans,
+packed THD batches ``parts/packed_sequences.py``, global-token normalisation ``:353-423``, validation sums ``:433-475``,
+mesh-aware clipping ``:551-567``).  Here the pieces are this package's own:
+
+* ``configure_model(mesh)`` applies the tensor-parallel plan (optionally sequence parallel) to the LLM over the mesh's ``tp``
+  group and remembers the data-parallel groups;
+* with ``optim.name: fully_sharded_adamw`` the parameters, gradients and AdamW state are sharded over ``dp_shard`` by
+  :class:`speech_b200.parallel.fsdp2.FullyShardedAdamW` (units: every LLM block and every audio-encoder block; embeddings,
+  output head and modality adapter form the root unit) and replicated over ``dp_replicate`` (hybrid sharding);
+* ``pack_sequences`` turns a padded batch into rows without padding (several sequences per row, block-diagonal causal
+  attention, positions restarting at every sequence);
+* the training loss is ``sum of token losses on this rank x dp_size / labelled tokens of the whole data-parallel group``, so
+  that the gradient average over data-parallel ranks is the gradient of the global per-token mean no matter how unevenly
+  the labelled tokens are spread.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from .salm import IGNORE_INDEX, SALM
+
+
+def pack_sequences(input_embeds: torch.Tensor, attention_mask: torch.Tensor, target_ids: torch.Tensor,
+                   row_len: Optional[int] = None) -> Dict[str, torch.Tensor]:
+    """Padded ``[B, T, H]`` batch -> packed ``[R, L, H]`` rows.
+
+    Sequences (the unpadded part of every row, wherever the padding sits) are placed first-fit in decreasing order of
+    length into rows of capacity ``row_len`` (default: the total number of tokens, i.e. one row).  Returns
+    ``input_embeds``, ``target_ids`` (``IGNORE_INDEX`` on padding), ``seq_ids`` (1-based sequence number per position, 0 on
+    padding: attention is allowed only between equal ids), ``position_ids`` (restart at 0 in every sequence),
+    ``attention_mask`` and ``cu_seqlens`` (``[R][n_r + 1]`` boundaries as a list of tensors)."""
+    B, T, H = input_embeds.shape
+    mask = attention_mask.bool()
+    lens = mask.sum(dim=1).tolist()
+    total = int(sum(lens))
+    L = int(row_len or total)
+    if max(lens) > L:
+        raise ValueError(f"a sequence of {max(lens)} tokens does not fit rows of {L}")
+    rows: List[List[int]] = []
+    free: List[int] = []
+    for b in sorted(range(B), key=lambda i: -lens[i]):
+        if lens[b] == 0:
+            continue
+        for r in range(len(rows)):
+            if free[r] >= lens[b]:
+                rows[r].append(b)
+                free[r] -= lens[b]
+                break
+        else:
+            rows.append([b])
+            free.append(L - lens[b])
+    R = max(1, len(rows))
+    emb = input_embeds.new_zeros((R, L, H))
+    tgt = target_ids.new_full((R, L), IGNORE_INDEX)
+    seq = torch.zeros((R, L), dtype=torch.long, device=input_embeds.device)
+    pos = torch.zeros((R, L), dtype=torch.long, device=input_embeds.device)
+    cu = []
+    for r, members in enumerate(rows):
+        o, bounds = 0, [0]
+        for k, b in enumerate(members):
+            n = lens[b]
+            emb[r, o:o + n] = input_embeds[b][mask[b]]
+            tgt[r, o:o + n] = target_ids[b][mask[b]]
+            seq[r, o:o + n] = k + 1
+            pos[r, o:o + n] = torch.arange(n, device=pos.device)
+            o += n
+            bounds.append(o)
+        cu.append(torch.tensor(bounds, dtype=torch.int32, device=input_embeds.device))
+    return {"input_embeds": emb, "target_ids": tgt, "seq_ids": seq, "position_ids": pos, "attention_mask": seq > 0, "cu_seqlens": cu}
+
+
+class SALMAutomodel(SALM):
+    """``cfg`` keys on top of SALM's: ``sequence_parallel`` (bool), ``packed_sequences: {enabled, row_len}``,
+    ``fsdp_units`` ("auto": LLM blocks + audio-encoder blocks)."""
+
+    def __init__(self, cfg, trainer=None, llm=None, tokenizer=None):
+        super().__init__(cfg, trainer=trainer, llm=llm, tokenizer=tokenizer)
+        self._device_mesh = None
+        self._dp_group = None
+        self._dp_size = 1
+        self._val_sums: Dict[str, List[torch.Tensor]] = {}
+
+    # ------------------------------------------------------------------ mesh
+    @property
+    def device_mesh(self):
+        return self._device_mesh
+
+    def configure_model(self, device_mesh=None) -> None:
+        self._device_mesh = device_mesh
+        if device_mesh is None:
+            return
+        from ..parallel.tp import apply_tensor_parallel_llm
+
+        for dim in ("pp", "cp"):
+            if device_mesh.size(dim) > 1:
+                raise ValueError(f"{dim} > 1 is not available for SALMAutomodel; use dp_replicate / dp_shard / tp")
+        if device_mesh.size("tp") > 1:
+            apply_tensor_parallel_llm(self.llm, device_mesh.group("tp"), sequence_parallel=bool(self.cfg.get("sequence_parallel", False)))
+        self._dp_size = device_mesh.size("dp")
+        self._dp_group = device_mesh.group("dp") if self._dp_size > 1 else None
+
+    def _sharded_optimizer_kwargs(self) -> Dict[str, Any]:
+        m = self._device_mesh
+        kw: Dict[str, Any] = {"units": self.fsdp_units()}
+        if m is not None:
+            if m.size("dp_shard") > 1:
+                kw["group"] = m.group("dp_shard")
+            if m.size("dp_replicate") > 1:
+                kw["replicate_group"] = m.group("dp_replicate")
+        return kw
+
+    def fsdp_units(self) -> List[torch.nn.Module]:
+        """Modules gathered / resharded as one: each LLM block and each audio-encoder block.  What is left (embeddings, final
+        norm, output head, modality adapter, pre-encoder) stays gathered for the whole step as the root unit."""
+        units: List[torch.nn.Module] = []
+        enc = getattr(self.perception, "encoder", None)
+        if enc is not None and hasattr(enc, "layers"):
+            units += list(enc.layers)
+        units += list(self.llm.model.layers)          # forward order: backward meets (and reduces) them in reverse
+        return [u for u in units if any(p.requires_grad for p in u.parameters())]
+
+    def setup_optimization(self, optim_config=None, optim_kwargs=None):
+        out = super().setup_optimization(optim_config, optim_kwargs)
+        m = self._device_mesh
+        opt = self._optimizer
+        if m is not None and m.size("tp") > 1 and hasattr(opt, "set_tensor_parallel"):
+            opt.set_tensor_parallel(m.group("tp"), lambda p: getattr(p, "_tensor_parallel", False))
+        return out
+
+    def configure_gradient_clipping(self, optimizer, gradient_clip_val: float) -> None:
+        """Called by the trainer for optimizers that do not clip inside their own update."""
+        from ..parallel.tp import clip_grad_norm_mesh
+
+        m = self._device_mesh
+        tp = m.group("tp") if m is not None and m.size("tp") > 1 else None
+        params = [p for g in optimizer.param_groups for p in g["params"]]
+        self._last_grad_norm = clip_grad_norm_mesh(params, gradient_clip_val, tp_group=tp)
+
+    def on_after_backward(self):
+        m = self._device_mesh
+        if m is not None and m.size("tp") > 1 and bool(self.cfg.get("sequence_parallel", False)):
+            from ..parallel.tp import allreduce_sequence_parallel_grads
+
+            allreduce_sequence_parallel_grads(self.llm, m.group("tp"))
+
+    def _sequence_multiple(self) -> int:
+        m = self._device_mesh
+        if m is not None and m.size("tp") > 1 and bool(self.cfg.get("sequence_parallel", False)):
+            return m.size("tp")
+        return 1
+
+    # ------------------------------------------------------------------ loss
+    def _token_loss_sums(self, batch) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, Dict[str, torch.Tensor]]:
+        """(sum of token losses, number of labelled tokens, number predicted correctly, the model inputs)."""
+        inp = self.prepare_inputs(batch)
+        pk = self.cfg.get("packed_sequences", None)
+        if pk is not None and pk.get("enabled", False):
+            row_len = pk.get("row_len", None)
+            mult = self._sequence_multiple()
+            if row_len is None and mult > 1:
+                total = int(inp["attention_mask"].sum())
+                row_len = (total + mult - 1) // mult * mult
+            packed = pack_sequences(inp["input_embeds"], inp["attention_mask"], inp["target_ids"], row_len)
+            out = self.llm(inputs_embeds=packed["input_embeds"], attention_mask=packed["attention_mask"],
+                           position_ids=packed["position_ids"], seq_ids=packed["seq_ids"])
+            tgt = packed["target_ids"]
+            inp = {**inp, "packed": packed}
+        else:
+            emb, am, tgt = inp["input_embeds"], inp["attention_mask"], inp["target_ids"]
+            mult = self._sequence_multiple()
+            if emb.shape[1] % mult:
+                # sequence parallelism splits the time axis evenly over the tensor-parallel ranks: right-pad to a multiple
+                extra = mult - emb.shape[1] % mult
+                emb = F.pad(emb, (0, 0, 0, extra))
+                am = F.pad(am, (0, extra), value=0)
+                tgt = F.pad(tgt, (0, extra), value=IGNORE_INDEX)
+            out = self.forward(emb, am)
+        logits = out["logits"].float()
+        loss_sum = F.cross_entropy(logits.reshape(-1, logits.shape[-1]), tgt.reshape(-1), ignore_index=IGNORE_INDEX, reduction="sum")
+        labelled = tgt != IGNORE_INDEX
+        n = labelled.sum()
+        correct = ((logits.argmax(dim=-1) == tgt) & labelled).sum()
+        return loss_sum, n, correct, inp
+
+    def training_step(self, batch, batch_idx):
+        loss_sum, n, _, inp = self._token_loss_sums(batch)
+        n_global = n.clone()
+        if self._dp_group is not None:
+            dist.all_reduce(n_global, group=self._dp_group)
+        n_global = n_global.clamp(min=1)
+        # gradients are averaged over the dp ranks afterwards: dp_size x local sum / global count makes that average the
+        # gradient of (sum over all ranks) / (labelled tokens on all ranks)
+        loss = loss_sum * self._dp_size / n_global
+        emb = inp["packed"]["input_embeds"] if "packed" in inp else inp["input_embeds"]
+        B, T = emb.shape[:2]
+        self.log_dict({"train_loss": (loss_sum.detach() / n.clamp(min=1)), "learning_rate": 0.0, "batch_size": float(B),
+                       "sequence_length": float(T), "num_frames": float(n), "num_frames_global": float(n_global),
+                       "target_to_input_ratio": float(n) / max(1, B * T)})
+        return {"loss": loss}
+
+    def on_validation_epoch_start(self):
+        self._val_sums = {}
+
+    def validation_step(self, batch, batch_idx, dataloader_idx=0):
+        loss_sum, n, correct, _ = self._token_loss_sums(batch)
+        sums = torch.stack([loss_sum.detach().double(), correct.double(), n.double()])
+        self._val_sums.setdefault(str(dataloader_idx), []).append(sums)
+        return {"val_loss": loss_sum.detach() / n.clamp(min=1)}
+
+    def on_validation_epoch_end(self):
+        """Token-weighted loss and accuracy over every rank's validation batches (sums are reduced, not means)."""
+        names = sorted(self._val_sums)
+        if self._dp_group is not None:
+            # ranks may hold different subsets of loaders: agree on the list first
+            gathered: List[Any] = [None] * self._dp_size
+            dist.all_gather_object(gathered, names, group=self._dp_group)
+            names = sorted({n for g in gathered for n in g})
+        losses = []
+        for name in names:
+            parts = self._val_sums.get(name)
+            dev = self.device
+            s = torch.stack(parts).sum(dim=0) if parts else torch.zeros(3, dtype=torch.float64, device=dev)
+            if self._dp_group is not None:
+                s = s.to(dev)
+                dist.all_reduce(s, group=self._dp_group)
+            nf = s[2].clamp(min=1)
+            tag = "" if len(names) == 1 else f"_{name}"
+            self.log(f"val_loss{tag}", (s[0] / nf).float())
+            self.log(f"val_acc{tag}", (s[1] / nf).float())
+            losses.append(s[0] / nf)
+        if len(names) > 1:
+            self.log("val_loss", torch.stack(losses).mean().float())
+        self._val_sums = {}

@@ -5,6 +5,8 @@ import subprocess
 import sys
 import textwrap
 
+import pytest
+
 REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 SCRIPT = textwrap.dedent("""
@@ -243,3 +245,90 @@ def test_fully_sharded_adamw_matches_replicated_adamw_two_ranks(tmp_path):
                          capture_output=True, text=True, timeout=600, env=dict(os.environ, MASTER_ADDR="127.0.0.1"))
     assert out.returncode == 0, out.stderr[-3000:]
     assert out.stdout.count("RESULT ok") == 2
+
+
+SALM_MESH_SCRIPT = textwrap.dedent("""
+    import os, sys, copy, torch, torch.distributed as dist
+    sys.path.insert(0, {repo!r})
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from speech_b200.core.config import OmegaConf
+    from speech_b200.models.configs import encoder_cfg, preprocessor_cfg
+    from speech_b200.parallel.fsdp2 import FullyShardedAdamW, FSDP2GradSync
+    from speech_b200.parallel.mesh import DeviceMesh
+    from speech_b200.speechlm.data import SALMDataset, synthetic_conversations
+    from speech_b200.speechlm.salm_automodel import SALMAutomodel
+    from speech_b200.tokenizers import ByteLevelTokenizer
+
+    TINY = dict(vocab_size=300, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                head_dim=8, tie_word_embeddings=False, qk_norm=True, model_type="qwen3")
+    pc = {{"preprocessor": {{**preprocessor_cfg(32), "dither": 0.0}}, "encoder": encoder_cfg("small", 32, 0.0, 0.0, n_layers=1),
+          "modality_adapter": {{"_target_": "speech_b200.speechlm.perception.IdentityConnector", "d_model": 176}}, "output_dim": 32}}
+    tok = ByteLevelTokenizer(special_tokens=["<pad>", "<s>", "</s>", "<|im_start|>", "<|im_end|>"])
+    cfg = OmegaConf.create({{"audio_locator_tag": "<|audioplaceholder|>", "prompt_format": "qwen", "llm": TINY, "perception": pc,
+                            "freeze_params": [], "prevent_freeze_params": [], "sequence_parallel": {sp}, "optim": {{"name": "adamw", "lr": 1e-3}}}})
+    torch.manual_seed(0)
+    ref = SALMAutomodel(cfg, tokenizer=tok).train()
+    model = copy.deepcopy(ref)
+    mesh = DeviceMesh({{"dp_shard": 2, "tp": 2}})
+    model.configure_model(mesh)
+    dp_rank, tp_rank = mesh.rank("dp_shard"), mesh.rank("tp")
+    assert model._dp_size == 2 and sum(getattr(p, "_tensor_parallel", False) for p in model.parameters()) > 0
+    kw = model._sharded_optimizer_kwargs()
+    assert len(kw["units"]) == 3 and "replicate_group" not in kw
+    opt = FullyShardedAdamW(model, lr=1e-2, weight_decay=0.0, max_grad_norm=0.3, device="cpu", **kw)
+    opt.set_tensor_parallel(mesh.group("tp"), lambda p: getattr(p, "_tensor_parallel", False))
+    sync = FSDP2GradSync(model, [opt], 2, torch.device("cpu"))
+    ref_opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.0)
+    ds = SALMDataset(synthetic_conversations(8, seed=3, min_duration=0.3, max_duration=0.6), tok, ref.prompt_formatter(), cfg.audio_locator_tag, ref.text_pad_id)
+    for it in range(2):
+        # data-parallel rank 0 gets one conversation, rank 1 gets three: very different numbers of labelled tokens
+        parts = [[4 * it], [4 * it + 1, 4 * it + 2, 4 * it + 3]]
+        batches = [ds.collate([ds[i] for i in p]) for p in parts]
+        ref_opt.zero_grad()
+        sums = [ref._token_loss_sums(b) for b in batches]
+        n_total = sum(int(s[1]) for s in sums)
+        (sum(s[0] for s in sums) / n_total).backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.3)
+        ref_opt.step()
+        sync.begin_step()
+        out = model.training_step(batches[dp_rank], it)
+        out["loss"].backward()
+        model.on_after_backward()
+        sync.finish_step()
+        opt.step()
+    full = opt.gather_full_state()
+    worst = 0.0
+    for (name, pr), pn in zip(ref.named_parameters(), model.parameters()):
+        got, want = full[id(pn)], pr.detach()
+        if getattr(pn, "_tensor_parallel", False):
+            dim = [i for i, (a, b) in enumerate(zip(got.shape, want.shape)) if a != b][0]
+            want = want.chunk(2, dim=dim)[tp_rank]
+        err = float((got - want).abs().max())
+        worst = max(worst, err)
+        if name.endswith("depthwise_conv.bias"):
+            continue          # a bias in front of batch norm has a zero gradient: Adam turns its rounding noise into steps
+        assert err < 3e-4, (name, err)
+    # validation sums are token weighted over the data-parallel group
+    model.eval(); ref.eval()
+    model.on_validation_epoch_start()
+    with torch.no_grad():
+        model.validation_step(batches[dp_rank], 0)
+        model.on_validation_epoch_end()
+    print("RESULT ok", rank, worst)
+    dist.destroy_process_group()
+""")
+
+
+@pytest.mark.parametrize("sp", [False, True])
+def test_salm_automodel_on_a_dp_shard_by_tp_mesh_matches_single_process_four_ranks(tmp_path, sp):
+    """2 (fully sharded data parallel) x 2 (tensor [+ sequence] parallel): after two steps with uneven labelled-token counts
+    per data-parallel rank and global-norm clipping, every parameter slice equals the single-process model trained on the
+    union of the batches with the per-token mean loss."""
+    script = tmp_path / "salm_mesh.py"
+    script.write_text(SALM_MESH_SCRIPT.format(repo=REPO, sp=sp))
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+                          "--master-addr", "127.0.0.1", "--master-port", "29768" if sp else "29767", str(script)],
+                         capture_output=True, text=True, timeout=900, env=dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2"))
+    assert out.returncode == 0, out.stderr[-4000:]
+    assert out.stdout.count("RESULT ok") == 4

@@ -174,7 +174,8 @@ def test_packed_sequences_cp_partition_chunking_and_metrics():
 
 
 def test_duplex_models_and_salm_variants():
-    from speech_b200.speechlm.duplex import DuplexS2SModel, DuplexSTTModel, SALMAutomodel, SALMWithAsrDecoder
+    from speech_b200.speechlm.duplex import DuplexS2SModel, DuplexSTTModel, SALMWithAsrDecoder
+    from speech_b200.speechlm.salm_automodel import SALMAutomodel, pack_sequences
 
     torch.manual_seed(0)
     pc = {"preprocessor": {**preprocessor_cfg(32), "dither": 0.0}, "encoder": encoder_cfg("small", 32, 0.0, 0.0, n_layers=1),
@@ -214,6 +215,22 @@ def test_duplex_models_and_salm_variants():
     auto = SALMAutomodel(scfg, tokenizer=tok)
     auto.configure_model(None)
     assert auto.device_mesh is None
+    # packed rows give the same loss as the padded batch
+    from speech_b200.speechlm.data import SALMDataset, synthetic_conversations
+    ds = SALMDataset(synthetic_conversations(3, seed=1), tok, auto.prompt_formatter(), scfg.audio_locator_tag, auto.text_pad_id)
+    batch = ds.collate([ds[i] for i in range(3)])
+    auto.eval()
+    ls, n, correct, inp = auto._token_loss_sums(batch)
+    pk = pack_sequences(inp["input_embeds"], inp["attention_mask"], inp["target_ids"])
+    assert pk["input_embeds"].shape[0] == 1 and int(pk["seq_ids"].max()) == 3 and int((pk["target_ids"] != -100).sum()) == int(n)
+    assert int(pk["position_ids"].max()) == int(inp["attention_mask"].sum(1).max()) - 1
+    from speech_b200.core.config import open_dict
+    with open_dict(auto.cfg):
+        auto.cfg.packed_sequences = {"enabled": True, "row_len": None}
+    ls2, n2, correct2, _ = auto._token_loss_sums(batch)
+    assert int(n2) == int(n) and abs(float(ls2) - float(ls)) < 1e-3 * abs(float(ls)) and int(correct2) == int(correct)
+    rows = pack_sequences(inp["input_embeds"], inp["attention_mask"], inp["target_ids"], row_len=int(inp["attention_mask"].sum(1).max()) + 2)
+    assert rows["input_embeds"].shape[0] >= 2 and len(rows["cu_seqlens"]) == rows["input_embeds"].shape[0]
 
 
 def test_ear_tts_mog_rvq_duplex_speech_decoder_and_voice_chat():
