@@ -85,14 +85,14 @@ def _install_default_aliases() -> None:
     a("nemo.collections.asr.models.EncDecMultiTaskModel", MD + "aed_models.EncDecMultiTaskModel")
     a("nemo.collections.asr.models.aed_multitask_models.EncDecMultiTaskModel", MD + "aed_models.EncDecMultiTaskModel")
     a("nemo.collections.asr.models.SortformerEncLabelModel", MD + "sortformer_models.SortformerEncLabelModel")
-    a("nemo.collections.asr.models.EncDecSpeakerLabelModel", MD + "label_models.EncDecSpeakerLabelModel")
+    a("nemo.collections.asr.models.EncDecSpeakerLabelModel", MD + "classification_models.EncDecSpeakerLabelModel")
     a("nemo.collections.asr.models.EncDecClassificationModel", MD + "classification_models.EncDecClassificationModel")
     for name, mod in (("EncDecFrameClassificationModel", "classification_models"), ("EncDecRegressionModel", "classification_models"),
                       ("SpeechEncDecSelfSupervisedModel", "ssl_models"), ("EncDecMaskedTokenPredModel", "ssl_models"),
                       ("EncDecDenoiseMaskedTokenPredModel", "ssl_models"), ("EncDecRNNTBPEModelWithPrompt", "asr_variants"),
                       ("EncDecHybridRNNTCTCBPEModelWithPrompt", "asr_variants"), ("EncDecRNNTBPEEOUModel", "asr_variants"),
                       ("EncDecHybridRNNTCTCBPEEOUModel", "asr_variants"), ("EncDecMultiTalkerRNNTBPEModel", "asr_variants"),
-                      ("EncDecTransfModelBPE", "asr_variants"), ("ConfidenceEnsembleModel", "asr_variants"),
+                      ("EncDecTransfModelBPE", "transformer_bpe_models"), ("ConfidenceEnsembleModel", "asr_variants"),
                       ("ClusteringDiarizer", "diarizers"), ("OnlineDiarizer", "diarizers")):
         a("nemo.collections.asr.models." + name, MD + mod + "." + name)
     for name in ("ConvASRDecoderReconstruction", "ECAPAEncoder", "ParallelConvASREncoder"):

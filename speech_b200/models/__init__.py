@@ -7,7 +7,6 @@ from .asr_variants import (  # noqa: F401
     EncDecMultiTalkerRNNTBPEModel,
     EncDecRNNTBPEEOUModel,
     EncDecRNNTBPEModelWithPrompt,
-    EncDecTransfModelBPE,
 )
 from .classification_models import (  # noqa: F401
     EncDecClassificationModel,
@@ -20,6 +19,7 @@ from .diarizers import ClusteringDiarizer, OnlineDiarizer  # noqa: F401
 from .hybrid_models import EncDecHybridRNNTCTCBPEModel, EncDecHybridRNNTCTCModel  # noqa: F401
 from .rnnt_models import EncDecRNNTBPEModel, EncDecRNNTModel  # noqa: F401
 from .sortformer_models import SortformerEncLabelModel  # noqa: F401
+from .transformer_bpe_models import EncDecTransfModelBPE  # noqa: F401
 from .ssl_models import (  # noqa: F401
     EncDecDenoiseMaskedTokenPredModel,
     EncDecMaskedTokenPredModel,

@@ -251,11 +251,6 @@ class EncDecMultiTalkerRNNTBPEModel(EncDecRNNTBPEModel):
             self.set_speaker_targets(None)
 
 
-# ---------------------------------------------------------------------------------------------- speech translation
-class EncDecTransfModelBPE(EncDecMultiTaskModel):
-    """Same computation as the multitask AED model without a prompt: ``<bos> text <eos>`` targets."""
-
-
 # ---------------------------------------------------------------------------------------------- confidence ensemble
 def entropy_confidence(log_probs: torch.Tensor, alpha: float = 0.33, kind: str = "tsallis") -> torch.Tensor:
     """Per-frame confidence in [0, 1] from a distribution (``parts/utils/asr_confidence_utils.py``): normalised

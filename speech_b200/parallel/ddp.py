@@ -62,7 +62,11 @@ class GradSync:
                  bucket_mb: float = DEFAULT_BUCKET_MB, sync_batchnorm: bool = False, grad_dtype: Optional[torch.dtype] = None):
         self.model, self.world_size, self.device = model, world_size, device
         self.arena = next((o.arena for o in optimizers if hasattr(o, "arena")), None)
-        self.params = [p for p in model.parameters() if p.requires_grad]
+        # parameters tagged ``_no_dp_sync`` (expert-parallel experts: every rank owns different ones) stay out of the exchange
+        self.params = [p for p in model.parameters() if p.requires_grad and not getattr(p, "_no_dp_sync", False)]
+        if self.arena is not None and any(getattr(p, "_no_dp_sync", False) and id(p) in self.arena.offsets for p in model.parameters()):
+            raise ValueError("expert-parallel parameters cannot live in the flat optimizer arena, which is exchanged as a whole: "
+                             "set `fused_optimizer: false` (or another optim.name) for models with expert parallelism")
         self.bucket_bytes = int(bucket_mb * 1024 * 1024)
         self._sync_enabled = True
         self._works: List[Any] = []
@@ -81,6 +85,7 @@ class GradSync:
                 rest = [p for p in self.model.parameters() if id(p) not in self.arena.offsets]
             else:
                 rest = list(self.model.parameters())
+            rest = [p for p in rest if not getattr(p, "_no_dp_sync", False)]
             for t in rest + list(self.model.buffers()):
                 if t.is_floating_point() or t.dtype in (torch.long, torch.int):
                     dist.broadcast(t.data, 0)

@@ -233,10 +233,13 @@ def apply_tensor_parallel_llm(llm, group, sequence_parallel: bool = False) -> No
         raise ValueError(f"heads ({cfg.num_attention_heads} / {cfg.num_key_value_heads}) are not divisible by tp={ws}")
     for layer in llm.model.layers:
         att, mlp = layer.self_attn, layer.mlp
-        for lin in (att.q_proj, att.k_proj, att.v_proj, mlp.gate_proj, mlp.up_proj):
+        dense = hasattr(mlp, "gate_proj")
+        for lin in (att.q_proj, att.k_proj, att.v_proj) + ((mlp.gate_proj, mlp.up_proj) if dense else ()):
             _shard_linear(getattr(lin, "base", lin), 0, r, ws)
-        for lin in (att.o_proj, mlp.down_proj):
+        for lin in (att.o_proj,) + ((mlp.down_proj,) if dense else ()):
             _shard_linear(getattr(lin, "base", lin), 1, r, ws)
+        if not dense:
+            _shard_experts_inner(mlp, r, ws, group)
         att.n_q, att.n_kv = cfg.num_attention_heads // ws, cfg.num_key_value_heads // ws
         if sequence_parallel:
             layer.tp_reduce = (lambda x, g=group: ReduceScatterToSP.apply(x, g, 1))
@@ -259,6 +262,23 @@ def apply_tensor_parallel_llm(llm, group, sequence_parallel: bool = False) -> No
         llm.model.sp_gather = (lambda x, g=group: GatherFromSPReplicated.apply(x, g, 1))
         for p in llm.model.norm.parameters():
             _sum_grad_over_group(p, group)
+
+
+def _shard_experts_inner(blk, rank: int, ws: int, group) -> None:
+    """Mixture-of-experts block under tensor parallelism: every expert's inner dimension is split (gate and up halves alike),
+    so each rank produces a partial sum of every expert's output and the usual reduction after the block completes it.  The
+    router is replicated and routes identically on all ranks; its gradient arrives through the partial outputs and is summed."""
+    E, I, H = blk.E, blk.inner, blk.hidden
+    if I % ws:
+        raise ValueError(f"expert inner size {I} is not divisible by tp={ws}")
+    gu = blk.gate_up.data.view(E, 2, I, H).chunk(ws, dim=2)[rank].reshape(E, 2 * (I // ws), H).clone()
+    dn = blk.down.data.chunk(ws, dim=2)[rank].clone()
+    blk.gate_up = nn.Parameter(gu, requires_grad=blk.gate_up.requires_grad)
+    blk.down = nn.Parameter(dn, requires_grad=blk.down.requires_grad)
+    blk.gate_up._tensor_parallel = blk.down._tensor_parallel = True
+    blk.inner = I // ws
+    blk.tp_size = ws              # the auxiliary loss is the same on every rank: scaled so that the summed router gradient counts it once
+    _sum_grad_over_group(blk.gate.weight, group)
 
 
 def clip_grad_norm_mesh(params, max_norm: float, tp_group=None, dp_shard_group=None, sharded=lambda p: False) -> torch.Tensor:

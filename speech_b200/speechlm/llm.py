@@ -46,6 +46,14 @@ class LLMConfig:
     bos_token_id: Optional[int] = None
     eos_token_id: Optional[int] = None
     pad_token_id: Optional[int] = None
+    # mixture of experts (Qwen3-MoE): 0 experts = dense model
+    num_experts: int = 0
+    num_experts_per_tok: int = 2
+    moe_intermediate_size: Optional[int] = None
+    norm_topk_prob: bool = True
+    router_aux_loss_coef: float = 0.0
+    decoder_sparse_step: int = 1              # every n-th layer is sparse ...
+    mlp_only_layers: tuple = ()               # ... except these, which stay dense
 
     @classmethod
     def from_hf(cls, d: Dict[str, Any]) -> "LLMConfig":
@@ -57,7 +65,14 @@ class LLMConfig:
         kw.setdefault("num_key_value_heads", d.get("num_attention_heads"))
         if isinstance(kw.get("eos_token_id"), list):
             kw["eos_token_id"] = kw["eos_token_id"][0]
+        if "num_local_experts" in d and "num_experts" not in d:         # Mixtral spelling
+            kw["num_experts"] = d["num_local_experts"]
+        if "mlp_only_layers" in kw:
+            kw["mlp_only_layers"] = tuple(kw["mlp_only_layers"] or ())
         return cls(**kw)
+
+    def is_sparse_layer(self, i: int) -> bool:
+        return self.num_experts > 0 and i not in self.mlp_only_layers and (i + 1) % max(1, self.decoder_sparse_step) == 0
 
     @property
     def dh(self) -> int:
@@ -149,10 +164,16 @@ class MLP(nn.Module):
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: LLMConfig, tp_size: int = 1):
+    def __init__(self, cfg: LLMConfig, tp_size: int = 1, layer_idx: int = 0):
         super().__init__()
         self.self_attn = Attention(cfg, tp_size)
-        self.mlp = MLP(cfg, tp_size)
+        if cfg.is_sparse_layer(layer_idx):
+            from .moe import SparseMoEBlock
+
+            self.mlp = SparseMoEBlock(cfg.hidden_size, cfg.moe_intermediate_size or cfg.intermediate_size, cfg.num_experts,
+                                      cfg.num_experts_per_tok, cfg.norm_topk_prob, cfg.router_aux_loss_coef)
+        else:
+            self.mlp = MLP(cfg, tp_size)
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
         self.tp_reduce = None          # set by the tensor-parallel plan: all-reduce (or reduce-scatter) of partial sums
@@ -173,7 +194,7 @@ class DecoderModel(nn.Module):
         super().__init__()
         self.cfg = cfg
         self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
-        self.layers = nn.ModuleList([DecoderLayer(cfg, tp_size) for _ in range(cfg.num_hidden_layers)])
+        self.layers = nn.ModuleList([DecoderLayer(cfg, tp_size, i) for i in range(cfg.num_hidden_layers)])
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
 
 
@@ -335,6 +356,16 @@ class CausalLM(nn.Module):
                 raise FileNotFoundError(f"no weight files (*.safetensors / pytorch_model*.bin) under {path}")
             if model.config.tie_word_embeddings:
                 sd.pop("lm_head.weight", None)
+            if model.config.num_experts > 0:
+                from .moe import SparseMoEBlock
+
+                for name, blk in model.named_modules():
+                    if isinstance(blk, SparseMoEBlock) and f"{name}.experts.0.gate_proj.weight" in sd:
+                        blk.load_per_expert(sd, prefix=name + ".")
+                        for k in [k for k in sd if k.startswith(name + ".experts.") or k == name + ".gate.weight"]:
+                            sd.pop(k)
+                        sd[name + ".gate.weight"] = blk.gate.weight.detach()
+                        sd[name + ".gate_up"], sd[name + ".down"] = blk.gate_up.detach(), blk.down.detach()
             missing, unexpected = model.load_state_dict(sd, strict=False)
             missing = [m for m in missing if not (m == "lm_head.weight" and model.config.tie_word_embeddings)]
             if missing:

@@ -10,6 +10,9 @@ mesh-aware clipping ``:551-567``).  Here the pieces are this package's own:
 * with ``optim.name: fully_sharded_adamw`` the parameters, gradients and AdamW state are sharded over ``dp_shard`` by
   :class:`speech_b200.parallel.fsdp2.FullyShardedAdamW` (units: every LLM block and every audio-encoder block; embeddings,
   output head and modality adapter form the root unit) and replicated over ``dp_replicate`` (hybrid sharding);
+* mixture-of-experts LLMs (``speechlm/moe.py``) run expert parallel over the data-parallel group (``expert_parallel: true``)
+  or with experts split along their inner dimension under ``tp``; the auxiliary load-balancing loss joins the training loss
+  and ``moe_metrics`` logs expert loads;
 * ``pack_sequences`` turns a padded batch into rows without padding (several sequences per row, block-diagonal causal
   attention, positions restarting at every sequence);
 * the training loss is ``sum of token losses on this rank x dp_size / labelled tokens of the whole data-parallel group``, so
@@ -78,7 +81,7 @@ def pack_sequences(input_embeds: torch.Tensor, attention_mask: torch.Tensor, tar
 
 class SALMAutomodel(SALM):
     """``cfg`` keys on top of SALM's: ``sequence_parallel`` (bool), ``packed_sequences: {enabled, row_len}``,
-    ``fsdp_units`` ("auto": LLM blocks + audio-encoder blocks)."""
+    ``expert_parallel`` (bool), ``moe_metrics: {enabled, mode, top_k_experts, every_n_steps}``."""
 
     def __init__(self, cfg, trainer=None, llm=None, tokenizer=None):
         super().__init__(cfg, trainer=trainer, llm=llm, tokenizer=tokenizer)
@@ -105,9 +108,42 @@ class SALMAutomodel(SALM):
             apply_tensor_parallel_llm(self.llm, device_mesh.group("tp"), sequence_parallel=bool(self.cfg.get("sequence_parallel", False)))
         self._dp_size = device_mesh.size("dp")
         self._dp_group = device_mesh.group("dp") if self._dp_size > 1 else None
+        if bool(self.cfg.get("expert_parallel", False)) and self._dp_group is not None:
+            # experts are split over the data-parallel ranks; their gradients stay local, so the optimizer must keep
+            # parameters per rank (no fully-sharded / arena optimizer for this model)
+            from .moe import apply_expert_parallel
+
+            if apply_expert_parallel(self.llm, self._dp_group) == 0:
+                raise ValueError("expert_parallel is set but the LLM has no mixture-of-experts layers")
+        self.setup_moe_options()
+
+    def setup_moe_options(self) -> None:
+        """``moe_metrics: {enabled, mode: brief | detailed, top_k_experts, every_n_steps}`` switches expert-load tracking on."""
+        mm = self.cfg.get("moe_metrics", None)
+        if mm is not None and mm.get("enabled", False):
+            from .moe import enable_load_tracking
+
+            enable_load_tracking(self.llm, True)
+
+    def maybe_log_moe_metrics(self, step: int) -> None:
+        mm = self.cfg.get("moe_metrics", None)
+        if mm is None or not mm.get("enabled", False) or step % int(mm.get("every_n_steps", 1)):
+            return
+        from .moe import collect_expert_loads, load_balance_summary
+
+        loads = collect_expert_loads(self.llm, dp_group=self._dp_group)
+        self.log_dict(load_balance_summary(loads))
+        if mm.get("mode", "brief") == "detailed":
+            k = int(mm.get("top_k_experts", 5))
+            for name, v in loads.items():
+                top = v.topk(min(k, v.numel()))
+                self.log_dict({f"moe/{name}/expert_{int(i)}_load": float(x) for x, i in zip(top.values, top.indices)})
 
     def _sharded_optimizer_kwargs(self) -> Dict[str, Any]:
         m = self._device_mesh
+        if any(getattr(p, "_expert_parallel", False) for p in self.parameters()):
+            raise ValueError("expert-parallel experts differ per rank and cannot be sharded as replicas: use a per-rank optimizer "
+                             "(for example optim.name: adamw with fused_optimizer: false)")
         kw: Dict[str, Any] = {"units": self.fsdp_units()}
         if m is not None:
             if m.size("dp_shard") > 1:
@@ -198,6 +234,12 @@ class SALMAutomodel(SALM):
         # gradients are averaged over the dp ranks afterwards: dp_size x local sum / global count makes that average the
         # gradient of (sum over all ranks) / (labelled tokens on all ranks)
         loss = loss_sum * self._dp_size / n_global
+        from .moe import moe_aux_loss
+
+        aux = moe_aux_loss(self.llm)
+        if aux is not None:
+            loss = loss + aux
+        self.maybe_log_moe_metrics(batch_idx)
         emb = inp["packed"]["input_embeds"] if "packed" in inp else inp["input_embeds"]
         B, T = emb.shape[:2]
         self.log_dict({"train_loss": (loss_sum.detach() / n.clamp(min=1)), "learning_rate": 0.0, "batch_size": float(B),

@@ -520,6 +520,7 @@ class SyntheticTokenizer(TokenizerSpec):
 
     def __init__(self, vocab_size: int):
         self.vocab = [f"▁w{i}" for i in range(vocab_size)]
+        self.pad_id, self.bos_id, self.eos_id = 0, 1, 2          # the first three ids double as control tokens for decoders that need them
 
     def text_to_ids(self, text):
         return [int(w[1:]) for w in text.split() if w.startswith("w") and w[1:].isdigit()]

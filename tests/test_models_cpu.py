@@ -233,3 +233,58 @@ def test_extra_encoders_rnn_transformer_wav2vec_parallel_expert():
     assert fused.shape == base.shape and not torch.allclose(fused, base)
     expect = pe.asr_norm(base.transpose(1, 2)) + pe.diar_norm(spk) @ pe.diar_kernel
     assert torch.allclose(fused.transpose(1, 2), expect, atol=1e-5)
+
+
+def test_transformer_decoder_translation_model_trains_decodes_and_scores_bleu(tmp_path):
+    """EncDecTransfModelBPE: encoder -> adapter -> Transformer encoder -> Transformer decoder; the loss falls on a fixed batch,
+    beam search returns token strings, and the epoch-end hook reports a position-weighted loss and corpus BLEU."""
+    import torch
+    from speech_b200.core.config import OmegaConf
+    from speech_b200.models import EncDecTransfModelBPE
+    from speech_b200.models.configs import encoder_cfg, preprocessor_cfg
+    from speech_b200.models.transformer_bpe_models import corpus_bleu
+    from speech_b200.tokenizers import ByteLevelTokenizer
+
+    assert corpus_bleu(["the cat sat on the mat ."], ["the cat sat on the mat ."]) > 99.9
+    assert corpus_bleu(["a b c d e f"], ["u v w x y z"]) == 0.0
+    mid = corpus_bleu(["the cat sat on a mat today"], ["the cat sat on the mat today"])
+    assert 20.0 < mid < 80.0
+    assert corpus_bleu(["Hello, world!"], ["Hello , world !"]) > 99.9          # 13a tokenisation splits punctuation
+
+    torch.manual_seed(0)
+    tr = {"hidden_size": 48, "inner_size": 96, "num_layers": 1, "num_attention_heads": 4, "ffn_dropout": 0.0, "attn_score_dropout": 0.0,
+          "attn_layer_dropout": 0.0, "pre_ln": True, "max_sequence_length": 64}
+    cfg = OmegaConf.create({
+        "sample_rate": 16000, "tokenizer": {"type": "synthetic", "vocab_size": 32},
+        "preprocessor": {**preprocessor_cfg(32), "dither": 0.0}, "encoder": encoder_cfg("small", 32, 0.0, 0.0, n_layers=1), "spec_augment": None,
+        "transf_encoder": dict(tr), "transf_decoder": dict(tr, learn_positional_encodings=True),
+        "head": {"num_layers": 1, "activation": "relu", "log_softmax": True, "dropout": 0.0},
+        "beam_search": {"beam_size": 2, "len_pen": 0.6, "max_generation_delta": 5}, "label_smoothing": 0.1,
+        "optim": {"name": "adamw", "lr": 3e-3}})
+    m = EncDecTransfModelBPE(cfg)
+    assert isinstance(m.adapter, torch.nn.Linear) and m.use_transf_encoder
+    assert m.log_softmax.mlp.layer0.weight is m.transf_decoder.embedding.token_embedding.weight
+    t = m.tokenizer
+    audio, lens = torch.randn(2, 8000), torch.tensor([8000, 6400])
+    body = torch.randint(3, 30, (2, 5))
+    tokens = torch.cat([torch.full((2, 1), t.bos_id), body, torch.full((2, 1), t.eos_id)], dim=1)
+    tokens[1, 5:] = torch.tensor([t.eos_id, t.pad_id])
+    batch = (audio, lens, tokens, torch.tensor([7, 6]))
+    opt = torch.optim.AdamW(m.parameters(), lr=3e-3)
+    losses = []
+    for _ in range(12):
+        opt.zero_grad()
+        loss = m.training_step(batch, 0)["loss"]
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    assert losses[-1] < 0.8 * losses[0]
+    m.eval()
+    out = m.validation_step(batch, 0)
+    assert len(out["translations"]) == 2 and out["loss_weight"] == 2 * 6
+    res = m.multi_validation_epoch_end([out, out], 0)
+    assert "val_sacreBLEU" in "".join(res["log"]) and float(res["val_loss"]) == pytest.approx(float(out["val_loss"]), rel=1e-5)
+    hyps = m._transcribe_forward_and_decode(audio, lens, None)
+    assert len(hyps) == 2 and all(isinstance(h.text, str) for h in hyps)
+    with pytest.raises(ValueError, match="either input_signal"):
+        m.forward()

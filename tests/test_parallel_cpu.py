@@ -332,3 +332,87 @@ def test_salm_automodel_on_a_dp_shard_by_tp_mesh_matches_single_process_four_ran
                          capture_output=True, text=True, timeout=900, env=dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2"))
     assert out.returncode == 0, out.stderr[-4000:]
     assert out.stdout.count("RESULT ok") == 4
+
+
+MOE_EP_SCRIPT = textwrap.dedent("""
+    import os, sys, copy, torch, torch.distributed as dist
+    sys.path.insert(0, {repo!r})
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from speech_b200.speechlm.llm import CausalLM, LLMConfig
+    from speech_b200.speechlm.moe import SparseMoEBlock, apply_expert_parallel, moe_aux_loss
+    from speech_b200.parallel.ddp import GradSync
+    from speech_b200.parallel.tp import apply_tensor_parallel_llm
+
+    cfg = LLMConfig(vocab_size=48, hidden_size=16, intermediate_size=32, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=4,
+                    num_experts=4, num_experts_per_tok=2, moe_intermediate_size=8, router_aux_loss_coef=0.01, model_type="qwen3_moe",
+                    tie_word_embeddings=False)
+    torch.manual_seed(0)
+    ref = CausalLM(cfg).train()
+    ids_all = torch.randint(0, 48, (world, 3, 6))
+    tgt_all = torch.randint(0, 48, (world, 3, 6))
+
+    def loss_of(model, ids, tgt):
+        lg = model(input_ids=ids)["logits"].float()
+        l = torch.nn.functional.cross_entropy(lg.reshape(-1, 48), tgt.reshape(-1))
+        aux = moe_aux_loss(model)
+        return l + aux if aux is not None else l
+
+    # ---- expert parallel x data parallel: rank r trains on batch r, experts are split
+    ep = copy.deepcopy(ref)
+    assert apply_expert_parallel(ep, dist.group.WORLD) == 2
+    assert ep.model.layers[0].mlp.gate_up.shape[0] == 2
+    sync = GradSync(ep, [], world, torch.device("cpu"))
+    assert all(not getattr(p, "_no_dp_sync", False) for p in sync.params) and len(sync.params) < len(list(ep.parameters()))
+    sync.begin_step() if hasattr(sync, "begin_step") else None
+    loss_of(ep, ids_all[rank], tgt_all[rank]).backward()
+    sync.finish_step()
+    # single process: mean over the ranks' batches.  The auxiliary loss of the parallel model uses group-wide routing statistics,
+    # so the reference computes it on the concatenated batch.
+    ref.zero_grad()
+    lg = ref(input_ids=ids_all.reshape(-1, 6))["logits"].float()
+    ce = torch.nn.functional.cross_entropy(lg.reshape(-1, 48), tgt_all.reshape(-1))
+    (ce + moe_aux_loss(ref)).backward()
+    worst = 0.0
+    for (n, pr), (_, pe) in zip(ref.named_parameters(), ep.named_parameters()):
+        want = pr.grad
+        if getattr(pe, "_expert_parallel", False):
+            want = want[rank * 2:(rank + 1) * 2]
+        err = float((pe.grad - want).abs().max()) / (float(want.abs().max()) + 1e-12)
+        worst = max(worst, err)
+        assert err < 2e-4, (n, err)
+    # ---- tensor parallel over the experts' inner dimension: same batch on both ranks
+    tp = copy.deepcopy(ref)
+    tp.zero_grad()
+    apply_tensor_parallel_llm(tp, dist.group.WORLD)
+    assert tp.model.layers[0].mlp.gate_up.shape == (4, 8, 16)
+    ids, tgt = ids_all[0], tgt_all[0]
+    ref.zero_grad()
+    l_ref = loss_of(ref, ids, tgt); l_ref.backward()
+    l_tp = loss_of(tp, ids, tgt); l_tp.backward()
+    assert abs(float(l_ref) - float(l_tp)) < 1e-5 + 0.01 * 0.5 * 2.5       # the parallel model reports aux / tp_size
+    for (n, pr), (_, pt) in zip(ref.named_parameters(), tp.named_parameters()):
+        want = pr.grad
+        if getattr(pt, "_tensor_parallel", False):
+            if n.endswith("gate_up"):
+                want = want.view(4, 2, 8, 16).chunk(2, dim=2)[rank].reshape(4, 8, 16)
+            else:
+                dim = [i for i, (a, b) in enumerate(zip(pt.shape, want.shape)) if a != b][0]
+                want = want.chunk(2, dim=dim)[rank]
+        err = float((pt.grad - want).abs().max()) / (float(want.abs().max()) + 1e-12)
+        assert err < 2e-4, ("tp", n, err)
+    print("RESULT ok", rank, worst)
+    dist.destroy_process_group()
+""")
+
+
+def test_moe_expert_parallel_and_expert_tensor_parallel_gradients_two_ranks(tmp_path):
+    """Experts split over two ranks (dispatch / combine all-to-all) with data-parallel averaging of the dense parameters, and
+    experts split along their inner dimension under tensor parallelism: every gradient equals the single-process one."""
+    script = tmp_path / "moe_ep.py"
+    script.write_text(MOE_EP_SCRIPT.format(repo=REPO))
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29771", str(script)],
+                         capture_output=True, text=True, timeout=600, env=dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2"))
+    assert out.returncode == 0, out.stderr[-4000:]
+    assert out.stdout.count("RESULT ok") == 2

@@ -348,3 +348,64 @@ def test_serving_plugin_token_estimator_lora_merge_export_and_splice(tmp_path):
 
     vp.register(_Reg)
     assert seen == {vp.ARCHITECTURE: "speech_b200.speechlm.vllm_plugin:" + vp.ARCHITECTURE}
+
+
+def test_sparse_moe_block_matches_per_token_reference_and_per_expert_checkpoints(tmp_path):
+    from speech_b200.speechlm.llm import CausalLM, LLMConfig
+    from speech_b200.speechlm.moe import SparseMoEBlock, collect_expert_loads, enable_load_tracking, load_balance_summary, moe_aux_loss
+
+    torch.manual_seed(0)
+    blk = SparseMoEBlock(16, 24, num_experts=6, top_k=2, norm_topk_prob=True, aux_loss_coef=0.01).train()
+    x = torch.randn(3, 5, 16, requires_grad=True)
+    y = blk(x)
+    # reference: token by token, expert by expert
+    xf = x.detach().reshape(-1, 16)
+    probs = torch.softmax(xf @ blk.gate.weight.T, -1)
+    w, idx = probs.topk(2, -1)
+    w = w / w.sum(-1, keepdim=True)
+    ref = torch.zeros_like(xf)
+    for n in range(xf.shape[0]):
+        for j in range(2):
+            e = int(idx[n, j])
+            g, u = (blk.gate_up[e] @ xf[n]).chunk(2)
+            ref[n] += w[n, j] * (blk.down[e] @ (torch.nn.functional.silu(g) * u))
+    assert torch.allclose(y.reshape(-1, 16), ref, atol=1e-5)
+    aux = moe_aux_loss(blk)
+    assert aux is not None and 0.005 < float(aux) < 0.05 and moe_aux_loss(blk) is None
+    (y.sum() + aux).backward()
+    assert blk.gate.weight.grad is not None and blk.gate_up.grad is not None and x.grad is not None
+    # uniform router -> auxiliary loss of exactly coef
+    with torch.no_grad():
+        blk.gate.weight.zero_()
+    p = torch.full((12, 6), 1 / 6)
+    assert abs(float(blk.load_balancing_loss(p, torch.arange(24).view(12, 2) % 6)) - 1.0) < 1e-6
+    # an LLM with sparse layers; per-expert checkpoint layout round trip
+    cfg = LLMConfig(vocab_size=64, hidden_size=16, intermediate_size=32, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=4,
+                    num_experts=4, num_experts_per_tok=2, moe_intermediate_size=8, router_aux_loss_coef=0.001, mlp_only_layers=(0,),
+                    model_type="qwen3_moe", tie_word_embeddings=False)
+    lm = CausalLM(cfg).eval()
+    kinds = [type(l.mlp).__name__ for l in lm.model.layers]
+    assert kinds == ["MLP", "SparseMoEBlock", "SparseMoEBlock"]
+    ids = torch.randint(0, 64, (2, 7))
+    out = lm(input_ids=ids)["logits"]
+    sd = {k: v for k, v in lm.state_dict().items() if ".mlp.gate_up" not in k and ".mlp.down" not in k or "layers.0." in k}
+    for i in (1, 2):
+        sd.pop(f"model.layers.{i}.mlp.gate.weight")
+        sd.update(lm.model.layers[i].mlp.per_expert_state(prefix=f"model.layers.{i}.mlp."))
+    assert "model.layers.1.mlp.experts.3.up_proj.weight" in sd
+    import json, os
+    from safetensors.torch import save_file
+    d = tmp_path / "moe"
+    os.makedirs(d)
+    save_file({k: v.contiguous() for k, v in sd.items()}, str(d / "model.safetensors"))
+    hf = {k: getattr(cfg, k) for k in cfg.__dataclass_fields__}
+    hf["mlp_only_layers"] = list(cfg.mlp_only_layers)
+    json.dump(hf, open(d / "config.json", "w"))
+    lm2 = CausalLM.from_pretrained(str(d)).eval()
+    assert torch.allclose(lm2(input_ids=ids)["logits"], out, atol=1e-5)
+    enable_load_tracking(lm2)
+    lm2(input_ids=ids)
+    loads = collect_expert_loads(lm2)
+    assert len(loads) == 2 and all(float(v.sum()) == 2 * 7 * 2 for v in loads.values())
+    s = load_balance_summary(loads)
+    assert s["moe/max_over_mean_load"] >= 1.0 and 0.0 <= s["moe/idle_expert_fraction"] <= 1.0
