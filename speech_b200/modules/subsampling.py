@@ -136,7 +136,56 @@ class ConvSubsampling(nn.Module):
         return [0, self.subsampling_factor + 1]
 
     def forward(self, x, lengths):
-        """x: [B, T, F] features; returns ([B, T', d_model], lengths')."""
+        """x: [B, T, F] features; returns ([B, T', d_model], lengths').
+
+        ``subsampling_conv_chunking_factor``: -1 never splits; 1 splits only when the widest activation of the stack
+        (``B x conv_channels x T/2 x F/2``) would pass 2**31 elements, the limit of 32-bit indexing in convolution kernels;
+        ``n > 1`` always splits into pieces of at most ``1/n`` of that activation (the reference has the same switch,
+        ``subsampling.py:427-466``, and splits by batch, then by channel).  Here pieces are taken along the batch first and,
+        for single long recordings, along time: chunks start on a multiple of the subsampling factor and carry one output
+        frame of context on either side, which makes the chunked result equal to the unsplit one, masks included."""
+        f = self.subsampling_conv_chunking_factor
+        if self.conv2d_subsampling and f != -1 and x.dim() == 3:
+            B, T, F_ = x.shape
+            widest = self._conv_channels * ((T + 1) // 2) * ((F_ + 1) // 2)          # per batch element, after the first layer
+            budget = 2 ** 31 if f == 1 else max(1, (B * widest) // f)
+            if B * widest > budget:
+                return self._forward_chunked(x, lengths, widest, budget)
+        return self._forward_once(x, lengths)
+
+    def _forward_chunked(self, x, lengths, widest: int, budget: int):
+        B, T, _ = x.shape
+        sf = self.subsampling_factor
+        if widest <= budget or self.is_causal or self._subsampling not in ("dw_striding", "striding"):
+            # whole recordings fit (or time splitting is not exact for this variant): groups of batch elements
+            per = max(1, budget // max(1, widest))
+            outs, lens = [], []
+            for b0 in range(0, B, per):
+                y, l = self._forward_once(x[b0:b0 + per], lengths[b0:b0 + per])
+                outs.append(y)
+                lens.append(l)
+            return torch.cat(outs, dim=0), torch.cat(lens, dim=0)
+        # one recording is too long: time chunks of `step` input frames (a multiple of the subsampling factor) with a halo of
+        # one output frame (sf input frames) on both sides; the halo's outputs are dropped
+        frames_budget = max(4 * sf, int(T * budget / widest))
+        step = max(sf, (frames_budget - 2 * sf) // sf * sf)
+        outs, out_len = [], None
+        for b in range(B):
+            pieces = []
+            for t0 in range(0, T, step):
+                lo, hi = max(0, t0 - sf), min(T, t0 + step + sf)
+                y, _ = self._forward_once(x[b:b + 1, lo:hi], (lengths[b:b + 1] - lo).clamp(min=0, max=hi - lo))
+                drop = (t0 - lo) // sf
+                keep = -(-min(step, T - t0) // sf) if t0 + step < T else y.shape[1] - drop
+                pieces.append(y[:, drop:drop + keep])
+            outs.append(torch.cat(pieces, dim=1))
+        n = max(o.shape[1] for o in outs)
+        out = torch.cat([torch.nn.functional.pad(o, (0, 0, 0, n - o.shape[1])) for o in outs], dim=0)
+        out_len = calc_length(lengths, self._left_padding + self._right_padding, self._kernel_size, self._stride, self._ceil_mode,
+                              self._sampling_num)
+        return out, out_len.to(lengths.dtype) if torch.is_tensor(out_len) else out_len
+
+    def _forward_once(self, x, lengths):
         if self._native_front_end(x):
             from ..ops import native_subsampling as ns
 

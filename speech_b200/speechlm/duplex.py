@@ -45,10 +45,26 @@ class DuplexSTTModel(ModelPT):
         self.text_bos_id = int(cfg_get(cfg, "text_bos_id", getattr(tokenizer, "bos_id", 1) or 1))
         self.text_eos_id = int(cfg_get(cfg, "text_eos_id", getattr(tokenizer, "eos_id", 2) or 2))
         self.text_loss_weight = float(cfg_get(cfg, "text_loss_weight", 1.0))
+        # optional second output channel: the recognised text of the user, frame aligned like the agent channel
+        self.predict_user_text = bool(cfg_get(cfg, "predict_user_text", False))
+        if self.predict_user_text and type(self) is DuplexSTTModel:
+            H, V = self.llm.config.hidden_size, self.llm.config.vocab_size
+            self.embed_asr_tokens = nn.Embedding(V, H)
+            self.asr_head = nn.Linear(H, V, bias=False)
+            self.asr_loss_weight = float(cfg_get(cfg, "asr_loss_weight", 1.0))
+        else:
+            self.predict_user_text = False
 
     @classmethod
     def list_available_models(cls):
         return []
+
+    @property
+    def streaming_inference(self):
+        """The frame-synchronous engine (prompts, forced turn taking, chunk-by-chunk feeding)."""
+        from .duplex_streaming import DuplexSTTStreamingInference
+
+        return DuplexSTTStreamingInference(self)
 
     def setup_training_data(self, c):
         self._train_dl = None
@@ -57,11 +73,18 @@ class DuplexSTTModel(ModelPT):
         self._validation_dl = None
 
     # ------------------------------------------------------------------ channels
-    def _frame_inputs(self, source_emb: torch.Tensor, prev_text: torch.Tensor, prev_codes: Optional[torch.Tensor] = None) -> torch.Tensor:
-        return source_emb + self.embed_tokens(prev_text).to(source_emb.dtype)
+    def _frame_inputs(self, source_emb: torch.Tensor, prev_text: torch.Tensor, prev_codes: Optional[torch.Tensor] = None,
+                      prev_asr: Optional[torch.Tensor] = None) -> torch.Tensor:
+        x = source_emb + self.embed_tokens(prev_text).to(source_emb.dtype)
+        if self.predict_user_text and prev_asr is not None:
+            x = x + self.embed_asr_tokens(prev_asr).to(source_emb.dtype)
+        return x
 
     def _heads(self, hidden: torch.Tensor) -> Dict[str, torch.Tensor]:
-        return {"text_logits": self.llm.lm_head(hidden)}
+        out = {"text_logits": self.llm.lm_head(hidden)}
+        if self.predict_user_text:
+            out["asr_logits"] = self.asr_head(hidden)
+        return out
 
     def forward(self, input_embeds: torch.Tensor, cache=None) -> Dict[str, Any]:
         out = self.llm(inputs_embeds=input_embeds, cache=cache, return_hidden=True)
@@ -78,14 +101,27 @@ class DuplexSTTModel(ModelPT):
         emb, tgt = emb[:, :T], batch["target_tokens"][:, :T].long()
         prev = torch.cat([torch.full_like(tgt[:, :1], self.text_pad_id), tgt[:, :-1]], dim=1)
         mask = torch.arange(T, device=emb.device)[None, :] < emb_len.clamp(max=T)[:, None]
-        return {"emb": emb, "prev_text": prev, "text_labels": tgt, "mask": mask, "T": T}
+        out = {"emb": emb, "prev_text": prev, "text_labels": tgt, "mask": mask, "T": T}
+        if self.predict_user_text and "source_tokens" in batch:
+            src = batch["source_tokens"][:, :T].long()
+            out["asr_labels"] = src
+            out["prev_asr"] = torch.cat([torch.full_like(src[:, :1], self.text_pad_id), src[:, :-1]], dim=1)
+        return out
 
     def _losses(self, batch) -> Dict[str, torch.Tensor]:
         inp = self.prepare_inputs(batch)
-        out = self(self._frame_inputs(inp["emb"], inp["prev_text"], inp.get("prev_codes")))
+        if self.predict_user_text:
+            out = self(self._frame_inputs(inp["emb"], inp["prev_text"], inp.get("prev_codes"), inp.get("prev_asr")))
+        else:
+            out = self(self._frame_inputs(inp["emb"], inp["prev_text"], inp.get("prev_codes")))
         m = inp["mask"]
         text = F.cross_entropy(out["text_logits"][m].float(), inp["text_labels"][m])
-        return {"text_loss": text, "loss": self.text_loss_weight * text, "_out": out, "_inp": inp}
+        res = {"text_loss": text, "loss": self.text_loss_weight * text, "_out": out, "_inp": inp}
+        if self.predict_user_text and "asr_labels" in inp:
+            asr = F.cross_entropy(out["asr_logits"][m].float(), inp["asr_labels"][m])
+            res["asr_loss"] = asr
+            res["loss"] = res["loss"] + self.asr_loss_weight * asr
+        return res
 
     def training_step(self, batch, batch_idx):
         l = self._losses(batch)

@@ -277,3 +277,32 @@ def test_longformer_attention_is_banded_and_matches_dense_masked_attention():
     _, posl = pe(xl)
     att.query_block = 1024
     assert att(xl, xl, xl, pos_emb=posl).shape == (1, Tl, D)
+
+
+def test_subsampling_conv_chunking_by_batch_and_by_time_equals_unsplit():
+    import torch
+    from speech_b200.modules.subsampling import ConvSubsampling
+
+    torch.manual_seed(0)
+    for kind in ("dw_striding", "striding"):
+        sub = ConvSubsampling(kind, 8, 80, 32, 16, subsampling_conv_chunking_factor=-1).eval()
+        x = torch.randn(3, 203, 80)
+        lens = torch.tensor([203, 150, 77])
+        with torch.no_grad():
+            ref, ref_len = sub(x, lens)
+            sub.subsampling_conv_chunking_factor = 1
+            same, _ = sub(x, lens)                       # far below the 2**31 limit: one piece
+            assert torch.equal(same, ref)
+            sub.subsampling_conv_chunking_factor = 3     # by batch
+            by_batch, l1 = sub(x, lens)
+            assert torch.allclose(by_batch, ref, atol=1e-6) and torch.equal(l1, ref_len)
+            sub.subsampling_conv_chunking_factor = 16    # a single recording no longer fits: time chunks with halos
+            calls = []
+            orig = sub._forward_once
+            sub._forward_once = lambda a, b: (calls.append(a.shape), orig(a, b))[1]
+            by_time, l2 = sub(x, lens)
+            assert len(calls) > 3 and max(c[1] for c in calls) < 120
+        assert by_time.shape == ref.shape and torch.equal(l2, ref_len)
+        for b in range(3):
+            n = int(ref_len[b])
+            assert torch.allclose(by_time[b, :n], ref[b, :n], atol=1e-5), (kind, b, (by_time[b, :n] - ref[b, :n]).abs().max())

@@ -409,3 +409,53 @@ def test_sparse_moe_block_matches_per_token_reference_and_per_expert_checkpoints
     assert len(loads) == 2 and all(float(v.sum()) == 2 * 7 * 2 for v in loads.values())
     s = load_balance_summary(loads)
     assert s["moe/max_over_mean_load"] >= 1.0 and 0.0 <= s["moe/idle_expert_fraction"] <= 1.0
+
+
+def test_duplex_stt_streaming_engine_prompts_turn_taking_and_chunked_feeding():
+    from speech_b200.speechlm.duplex import DuplexSTTModel
+    from speech_b200.speechlm.duplex_streaming import DuplexState, DuplexSTTStreamingInference
+
+    torch.manual_seed(0)
+    pc = {"preprocessor": {**preprocessor_cfg(32), "dither": 0.0}, "encoder": encoder_cfg("small", 32, 0.0, 0.0, n_layers=1),
+          "modality_adapter": {"_target_": "speech_b200.speechlm.perception.IdentityConnector", "d_model": 176}}
+    cfg = OmegaConf.create({"llm": dict(TINY), "perception": pc, "predict_user_text": True, "optim": {"name": "adamw", "lr": 1e-3}})
+    m = DuplexSTTModel(cfg).eval()
+    assert m.predict_user_text
+    audio, lens = torch.randn(2, 16000), torch.tensor([16000, 12000])
+    # training with both channels
+    T = 12
+    loss = m.training_step({"source_audio": audio, "source_audio_lens": lens, "target_tokens": torch.randint(3, 50, (2, T)),
+                            "source_tokens": torch.randint(3, 50, (2, T))}, 0)["loss"]
+    loss.backward()
+    assert m.asr_head.weight.grad is not None and m.embed_asr_tokens.weight.grad is not None
+    eng = m.streaming_inference
+    plain = eng.offline_inference(audio, lens)
+    assert plain["tokens"].shape == plain["asr_tokens"].shape and plain["tokens"].shape[1] == int(plain["lengths"].max())
+    # the cached frame loop equals teacher forcing on its own outputs
+    emb, _ = m.perception(input_signal=audio, input_signal_length=lens)
+    prev_t = torch.cat([torch.full((2, 1), m.text_pad_id), plain["tokens"][:, :-1]], 1)
+    prev_a = torch.cat([torch.full((2, 1), m.text_pad_id), plain["asr_tokens"][:, :-1]], 1)
+    full = m(m._frame_inputs(emb, prev_t, None, prev_a))
+    assert torch.equal(full["text_logits"].argmax(-1), plain["tokens"]) and torch.equal(full["asr_logits"].argmax(-1), plain["asr_tokens"])
+    # prompts of different lengths are right aligned; trailing padding adds frames
+    prompts = torch.tensor([[5, 6, 7], [9, 0, 0]])
+    withp = eng.offline_inference(audio, lens, prompt_tokens=prompts, prompt_token_lens=torch.tensor([3, 1]), input_pad_len=3200)
+    assert withp["tokens"].shape[1] > plain["tokens"].shape[1]
+    # forced turn taking: silence after speech on the user channel forces the agent to start
+    st = DuplexState(cache=[dict() for _ in m.llm.model.layers])
+    force = DuplexSTTStreamingInference(m, force_turn_taking=True, threshold=6, pad_window=3)
+    st.gen_text = [torch.full((1,), m.text_pad_id) for _ in range(5)]
+    st.gen_asr = [torch.tensor([11]), torch.tensor([12])] + [torch.full((1,), m.text_pad_id) for _ in range(3)]
+    st.t = 5
+    out = force._force_turn_taking(st, torch.tensor([33]), torch.tensor([m.text_pad_id]), torch.zeros(1, dtype=torch.bool))
+    assert int(out) == m.text_bos_id
+    st.gen_text[3] = torch.tensor([m.text_bos_id])         # the agent already started: nothing is forced
+    assert int(force._force_turn_taking(st, torch.tensor([33]), torch.tensor([m.text_pad_id]), torch.zeros(1, dtype=torch.bool))) == 33
+    st.gen_asr[2:] = [torch.tensor([13]) for _ in range(3)]  # user barges in while the agent talks: agent EOS
+    assert int(force._force_turn_taking(st, torch.tensor([33]), torch.tensor([force.user_bos]), torch.zeros(1, dtype=torch.bool))) == m.text_eos_id
+    # chunk-by-chunk feeding covers every frame exactly once
+    s2 = eng.start(2)
+    n = 0
+    for k in range(0, 16000, 4000):
+        n += eng.feed(s2, audio[:, k:k + 4000])["tokens"].shape[1]
+    assert n == s2.t == s2.frames_done and abs(n - plain["tokens"].shape[1]) <= 1
