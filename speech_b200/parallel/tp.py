@@ -264,6 +264,18 @@ def apply_tensor_parallel_llm(llm, group, sequence_parallel: bool = False) -> No
             _sum_grad_over_group(p, group)
 
 
+def apply_context_parallel_llm(llm, group) -> None:
+    """Context parallelism for ``speechlm.llm.CausalLM``: every rank of ``group`` carries a contiguous ``T / W`` slice of the
+    sequence through the blocks; each attention module all-gathers keys and values along time (backward: reduce-scatter of their
+    gradients) and attends with its local queries under the causal / packed-sequence mask of the full sequence.  Parameter
+    gradients cover the local tokens only, so the group is part of the gradient-averaging group, like data parallelism."""
+    if dist.get_world_size(group) == 1:
+        return
+    for layer in llm.model.layers:
+        layer.self_attn.cp_gather = (lambda t, g=group: GatherFromSP.apply(t.contiguous(), g, 2))
+    llm.model.cp_group = group
+
+
 def _shard_experts_inner(blk, rank: int, ws: int, group) -> None:
     """Mixture-of-experts block under tensor parallelism: every expert's inner dimension is split (gate and up halves alike),
     so each rank produces a partial sum of every expert's output and the usual reduction after the block completes it.  The

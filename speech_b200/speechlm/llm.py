@@ -137,6 +137,9 @@ class Attention(nn.Module):
             q, k = self.q_norm(q), self.k_norm(k)
         q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
         q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        cp_gather = getattr(self, "cp_gather", None)
+        if cp_gather is not None and cache is None:
+            k, v = cp_gather(k), cp_gather(v)        # context parallelism: queries stay local, keys / values of all ranks
         if cache is not None:
             if "k" in cache:
                 k = torch.cat([cache["k"], k], dim=2)
@@ -227,17 +230,20 @@ class CausalLM(nn.Module):
         self.model.embed_tokens = emb
 
     @staticmethod
-    def build_mask(attention_mask: Optional[torch.Tensor], T_q: int, T_k: int, dtype, device, seq_ids: Optional[torch.Tensor] = None):
-        """Additive mask [B, 1, T_q, T_k]: causal, key padding, and block-diagonal over ``seq_ids`` for packed batches."""
-        if attention_mask is None and seq_ids is None:
+    def build_mask(attention_mask: Optional[torch.Tensor], T_q: int, T_k: int, dtype, device, seq_ids: Optional[torch.Tensor] = None,
+                   q_offset: Optional[int] = None):
+        """Additive mask [B, 1, T_q, T_k]: causal, key padding, and block-diagonal over ``seq_ids`` for packed batches.  The
+        queries are positions ``q_offset .. q_offset + T_q`` of the key axis (default: the last ``T_q``)."""
+        if attention_mask is None and seq_ids is None and q_offset is None:
             return None
-        i = torch.arange(T_k - T_q, T_k, device=device).view(1, 1, T_q, 1)
+        q0 = T_k - T_q if q_offset is None else q_offset
+        i = torch.arange(q0, q0 + T_q, device=device).view(1, 1, T_q, 1)
         j = torch.arange(T_k, device=device).view(1, 1, 1, T_k)
         ok = j <= i
         if attention_mask is not None:
             ok = ok & attention_mask.bool().view(attention_mask.shape[0], 1, 1, T_k)
         if seq_ids is not None:
-            ok = ok & (seq_ids.view(seq_ids.shape[0], 1, T_k, 1)[:, :, -T_q:] == seq_ids.view(seq_ids.shape[0], 1, 1, T_k))
+            ok = ok & (seq_ids.view(seq_ids.shape[0], 1, T_k, 1)[:, :, q0:q0 + T_q] == seq_ids.view(seq_ids.shape[0], 1, 1, T_k))
         # rows that can see nothing (left padding) attend to themselves to keep softmax finite
         ok = ok | (~ok.any(dim=-1, keepdim=True) & (j == i))
         return torch.zeros(ok.shape, dtype=dtype, device=device).masked_fill(~ok, float("-inf"))
@@ -257,8 +263,25 @@ class CausalLM(nn.Module):
                 position_ids = (attention_mask.long().cumsum(-1) - 1).clamp(min=0)[:, -T:]
             else:
                 position_ids = torch.arange(past, past + T, device=x.device).unsqueeze(0).expand(B, T)
+        cp = getattr(self.model, "cp_group", None) if cache is None else None
+        cp_slice = None
+        if cp is not None:
+            # context parallelism: this rank keeps a contiguous T / W slice of the sequence through every block; attention sees
+            # the keys and values of all ranks (gathered inside each attention module)
+            import torch.distributed as dist
+
+            W, r = dist.get_world_size(cp), dist.get_rank(cp)
+            if T % W:
+                raise ValueError(f"sequence length {T} is not divisible by the context-parallel size {W}: pad the batch")
+            Tl = T // W
+            cp_slice = (r * Tl, (r + 1) * Tl)
+            x = x[:, cp_slice[0]:cp_slice[1]]
+            position_ids = position_ids[:, cp_slice[0]:cp_slice[1]]
         cos, sin = rope_tables(position_ids, self.config.dh, self.config.rope_theta)
-        mask = self.build_mask(attention_mask, T, past + T, x.dtype, x.device, seq_ids)
+        if cp_slice is not None:
+            mask = self.build_mask(attention_mask, cp_slice[1] - cp_slice[0], T, x.dtype, x.device, seq_ids, q_offset=cp_slice[0])
+        else:
+            mask = self.build_mask(attention_mask, T, past + T, x.dtype, x.device, seq_ids)
         sp = getattr(self.model, "sp_scatter", None) is not None and cache is None
         if sp:
             # sequence parallelism: the residual stream lives as [B, T / W, H] between blocks (positions, mask and rotary tables
@@ -274,6 +297,8 @@ class CausalLM(nn.Module):
         if sp:
             x = self.model.sp_gather(x)
         out = {"hidden_states": x, "cache": cache}
+        if cp_slice is not None:
+            out["cp_slice"] = cp_slice          # hidden states / logits cover these positions only
         if not return_hidden:
             out["logits"] = self.lm_head(x)
         return out

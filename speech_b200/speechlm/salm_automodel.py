@@ -13,6 +13,8 @@ mesh-aware clipping ``:551-567``).  Here the pieces are this package's own:
 * mixture-of-experts LLMs (``speechlm/moe.py``) run expert parallel over the data-parallel group (``expert_parallel: true``)
   or with experts split along their inner dimension under ``tp``; the auxiliary load-balancing loss joins the training loss
   and ``moe_metrics`` logs expert loads;
+* context parallelism (``cp``): each rank carries a slice of the (packed) sequence, attention gathers keys / values, and the
+  ``cp`` ranks join the data-parallel ranks for loss normalisation and gradient averaging;
 * ``pack_sequences`` turns a padded batch into rows without padding (several sequences per row, block-diagonal causal
   attention, positions restarting at every sequence);
 * the training loss is ``sum of token losses on this rank x dp_size / labelled tokens of the whole data-parallel group``, so
@@ -101,13 +103,17 @@ class SALMAutomodel(SALM):
             return
         from ..parallel.tp import apply_tensor_parallel_llm
 
-        for dim in ("pp", "cp"):
-            if device_mesh.size(dim) > 1:
-                raise ValueError(f"{dim} > 1 is not available for SALMAutomodel; use dp_replicate / dp_shard / tp")
+        if device_mesh.size("pp") > 1:
+            raise ValueError("pp > 1 is not available for SALMAutomodel; use dp_replicate / dp_shard / cp / tp")
         if device_mesh.size("tp") > 1:
             apply_tensor_parallel_llm(self.llm, device_mesh.group("tp"), sequence_parallel=bool(self.cfg.get("sequence_parallel", False)))
-        self._dp_size = device_mesh.size("dp")
-        self._dp_group = device_mesh.group("dp") if self._dp_size > 1 else None
+        if device_mesh.size("cp") > 1:
+            from ..parallel.tp import apply_context_parallel_llm
+
+            apply_context_parallel_llm(self.llm, device_mesh.group("cp"))
+        # ranks that see different tokens: data parallel and context parallel alike (loss normalisation, gradient averaging)
+        self._dp_size = device_mesh.size("dp_cp")
+        self._dp_group = device_mesh.group("dp_cp") if self._dp_size > 1 else None
         if bool(self.cfg.get("expert_parallel", False)) and self._dp_group is not None:
             # experts are split over the data-parallel ranks; their gradients stay local, so the optimizer must keep
             # parameters per rank (no fully-sharded / arena optimizer for this model)
@@ -146,8 +152,8 @@ class SALMAutomodel(SALM):
                              "(for example optim.name: adamw with fused_optimizer: false)")
         kw: Dict[str, Any] = {"units": self.fsdp_units()}
         if m is not None:
-            if m.size("dp_shard") > 1:
-                kw["group"] = m.group("dp_shard")
+            if m.size("dp_shard_cp") > 1:
+                kw["group"] = m.group("dp_shard_cp")
             if m.size("dp_replicate") > 1:
                 kw["replicate_group"] = m.group("dp_replicate")
         return kw
@@ -188,9 +194,12 @@ class SALMAutomodel(SALM):
 
     def _sequence_multiple(self) -> int:
         m = self._device_mesh
-        if m is not None and m.size("tp") > 1 and bool(self.cfg.get("sequence_parallel", False)):
-            return m.size("tp")
-        return 1
+        if m is None:
+            return 1
+        mult = m.size("cp")
+        if m.size("tp") > 1 and bool(self.cfg.get("sequence_parallel", False)):
+            mult *= m.size("tp")
+        return mult
 
     # ------------------------------------------------------------------ loss
     def _token_loss_sums(self, batch) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, Dict[str, torch.Tensor]]:
@@ -219,6 +228,8 @@ class SALMAutomodel(SALM):
                 tgt = F.pad(tgt, (0, extra), value=IGNORE_INDEX)
             out = self.forward(emb, am)
         logits = out["logits"].float()
+        if "cp_slice" in out:
+            tgt = tgt[:, out["cp_slice"][0]:out["cp_slice"][1]]        # this rank scores its slice of the sequence
         loss_sum = F.cross_entropy(logits.reshape(-1, logits.shape[-1]), tgt.reshape(-1), ignore_index=IGNORE_INDEX, reduction="sum")
         labelled = tgt != IGNORE_INDEX
         n = labelled.sum()

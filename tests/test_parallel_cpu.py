@@ -270,15 +270,23 @@ SALM_MESH_SCRIPT = textwrap.dedent("""
     torch.manual_seed(0)
     ref = SALMAutomodel(cfg, tokenizer=tok).train()
     model = copy.deepcopy(ref)
-    mesh = DeviceMesh({{"dp_shard": 2, "tp": 2}})
+    second = {second!r}
+    mesh = DeviceMesh({{"dp_shard": 2, second: 2}})
+    if second == "cp":
+        from speech_b200.core.config import open_dict
+        for mdl in (ref, model):
+            with open_dict(mdl.cfg):
+                mdl.cfg.packed_sequences = {{"enabled": True, "row_len": None}}
     model.configure_model(mesh)
     dp_rank, tp_rank = mesh.rank("dp_shard"), mesh.rank("tp")
-    assert model._dp_size == 2 and sum(getattr(p, "_tensor_parallel", False) for p in model.parameters()) > 0
+    n_tp = sum(getattr(p, "_tensor_parallel", False) for p in model.parameters())
+    assert (model._dp_size, n_tp > 0) == ((2, True) if second == "tp" else (4, False))
     kw = model._sharded_optimizer_kwargs()
     assert len(kw["units"]) == 3 and "replicate_group" not in kw
     opt = FullyShardedAdamW(model, lr=1e-2, weight_decay=0.0, max_grad_norm=0.3, device="cpu", **kw)
-    opt.set_tensor_parallel(mesh.group("tp"), lambda p: getattr(p, "_tensor_parallel", False))
-    sync = FSDP2GradSync(model, [opt], 2, torch.device("cpu"))
+    if second == "tp":
+        opt.set_tensor_parallel(mesh.group("tp"), lambda p: getattr(p, "_tensor_parallel", False))
+    sync = FSDP2GradSync(model, [opt], opt.world, torch.device("cpu"))
     ref_opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.0)
     ds = SALMDataset(synthetic_conversations(8, seed=3, min_duration=0.3, max_duration=0.6), tok, ref.prompt_formatter(), cfg.audio_locator_tag, ref.text_pad_id)
     for it in range(2):
@@ -320,15 +328,15 @@ SALM_MESH_SCRIPT = textwrap.dedent("""
 """)
 
 
-@pytest.mark.parametrize("sp", [False, True])
-def test_salm_automodel_on_a_dp_shard_by_tp_mesh_matches_single_process_four_ranks(tmp_path, sp):
-    """2 (fully sharded data parallel) x 2 (tensor [+ sequence] parallel): after two steps with uneven labelled-token counts
-    per data-parallel rank and global-norm clipping, every parameter slice equals the single-process model trained on the
-    union of the batches with the per-token mean loss."""
+@pytest.mark.parametrize("sp,second", [(False, "tp"), (True, "tp"), (False, "cp")])
+def test_salm_automodel_on_a_dp_shard_by_tp_or_cp_mesh_matches_single_process_four_ranks(tmp_path, sp, second):
+    """2 (fully sharded data parallel) x 2 (tensor [+ sequence] parallel, or context parallel over packed sequences): after two
+    steps with uneven labelled-token counts per data-parallel rank and global-norm clipping, every parameter slice equals the
+    single-process model trained on the union of the batches with the per-token mean loss."""
     script = tmp_path / "salm_mesh.py"
-    script.write_text(SALM_MESH_SCRIPT.format(repo=REPO, sp=sp))
+    script.write_text(SALM_MESH_SCRIPT.format(repo=REPO, sp=sp, second=second))
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
-                          "--master-addr", "127.0.0.1", "--master-port", "29768" if sp else "29767", str(script)],
+                          "--master-addr", "127.0.0.1", "--master-port", str(29767 + int(sp) + 2 * (second == "cp")), str(script)],
                          capture_output=True, text=True, timeout=900, env=dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2"))
     assert out.returncode == 0, out.stderr[-4000:]
     assert out.stdout.count("RESULT ok") == 4
