@@ -92,3 +92,130 @@ def test_generative_models_train_and_sample(cls, est):
     m.eval()
     y, _ = m(input_signal=torch.randn(1, 1, 900) * 0.1, input_length=torch.tensor([900]))
     assert y.shape == (1, 1, 900) and torch.isfinite(y).all()
+
+
+def test_multichannel_features_blocks_and_flex_channel_mask_estimator():
+    import random
+    from speech_b200.audio.multichannel import (ChannelAttentionPool, ChannelAugment, ChannelAveragePool, MaskEstimatorFlexChannels,
+                                                MixtureConsistencyProjection, SpectrogramToMultichannelFeatures, SSLPretrainWithMaskedPatch,
+                                                TransformAttendConcatenate, TransformAverageConcatenate)
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 17, 20, dtype=torch.cfloat)
+    lens = torch.tensor([20, 14])
+    f = SpectrogramToMultichannelFeatures(17, 3, mag_reduction="rms", use_ipd=True, mag_normalization="mean_var", ipd_normalization="mean")
+    feats, _ = f(x, lens)
+    assert feats.shape == (2, 3, 34, 20) and f.num_features == 34 and f.num_channels == 3
+    assert float(feats[1, :, :, 14:].abs().max()) == 0.0
+    assert float(feats[0, 0, :17].mean(-1).abs().max()) < 1e-5                      # mean-variance normalised magnitude
+    raw, _ = SpectrogramToMultichannelFeatures(17, 3, mag_reduction=None, use_ipd=True)(x, lens)
+    assert float(raw[:, :, 17:].abs().max()) <= math.pi + 1e-5 and torch.allclose(raw[:, :, :17], x.abs())
+    for blk in (TransformAverageConcatenate(34, 16), TransformAttendConcatenate(34, 16, n_head=2)):
+        blk.eval()
+        y = blk(feats)
+        assert y.shape == (2, 3, 16, 20)
+        perm = [2, 0, 1]
+        assert torch.allclose(blk(feats[:, perm]), y[:, perm], atol=1e-5)            # permutation equivariant
+    assert ChannelAveragePool()(feats).shape == (2, 1, 34, 20)
+    pool = ChannelAttentionPool(34).eval()
+    assert torch.allclose(pool(feats[:, [1, 2, 0]]), pool(feats), atol=1e-5)         # permutation invariant
+    aug = ChannelAugment(num_channels_min=2, rng=random.Random(0))
+    assert aug(x).shape[1] in (2, 3)
+    est = MaskEstimatorFlexChannels(num_outputs=2, num_subbands=17, num_blocks=2, channel_reduction_position=1, temporal_block_num_layers=1,
+                                    temporal_block_num_heads=2, temporal_block_dimension=16, num_input_channels=3).eval()
+    m, _ = est(x, lens)
+    assert m.shape == (2, 2, 17, 20) and float(m.min()) >= 0 and float(m.max()) <= 1 and float(m[1, :, :, 14:].abs().max()) == 0
+    m4, _ = est(torch.randn(2, 4, 17, 20, dtype=torch.cfloat), lens)                  # another number of channels, same weights
+    assert m4.shape == (2, 2, 17, 20)
+    end = MaskEstimatorFlexChannels(1, 17, 1, -1, "average", "transform_average_concatenate", temporal_block_num_layers=1,
+                                    temporal_block_num_heads=2, temporal_block_dimension=16).eval()
+    assert end(x, lens)[0].shape == (2, 1, 17, 20)
+    mix = torch.randn(2, 1, 5, 7, dtype=torch.cfloat)
+    est_src = torch.randn(2, 3, 5, 7, dtype=torch.cfloat)
+    for w in (None, "power"):
+        proj = MixtureConsistencyProjection(w)(mix, est_src)
+        assert torch.allclose(proj.sum(1, keepdim=True), mix, atol=1e-4)
+    masked = SSLPretrainWithMaskedPatch(patch_size=4, mask_fraction=0.5, rng=random.Random(1))(torch.ones(2, 8, 20), lens)
+    zero_frames = (masked[0].abs().sum(0) == 0).sum()
+    assert int(zero_frames) == 12 and set((masked[0].abs().sum(0) == 0).view(5, 4).all(1).tolist()) == {True, False}
+
+
+def test_gss_wpe_and_parametric_wiener_filter_on_synthetic_scenes():
+    from speech_b200.audio.multichannel import MaskBasedDereverbWPE, MaskEstimatorGSS, ParametricMultichannelWienerFilter, WPEFilter
+
+    torch.manual_seed(0)
+    B, C, F, N = 1, 4, 6, 400
+    # two sources with distinct steering vectors, active in different halves (plus an overlap), weak noise
+    steer = torch.randn(2, F, C, dtype=torch.cdouble)
+    act = torch.zeros(B, 2, N)
+    act[0, 0, :250] = 1
+    act[0, 1, 150:] = 1
+    s = torch.randn(2, F, N, dtype=torch.cdouble) * act[0].unsqueeze(1)
+    x = torch.einsum("sfc,sfn->cfn", steer, s).unsqueeze(0) + 0.01 * torch.randn(B, C, F, N, dtype=torch.cdouble)
+    gamma = MaskEstimatorGSS(num_iterations=8)(x, act)
+    assert gamma.shape == (B, 2, F, N) and torch.allclose(gamma.sum(1), torch.ones(B, F, N, dtype=gamma.dtype), atol=1e-5)
+    assert float(gamma[0, 0, :, :150].min()) > 0.99 and float(gamma[0, 1, :, 250:].min()) > 0.99
+    # in the overlap the posterior follows the dominant source
+    dom0 = (s[0].abs() > 3 * s[1].abs())[:, 150:250]
+    dom1 = (s[1].abs() > 3 * s[0].abs())[:, 150:250]
+    g0 = gamma[0, 0, :, 150:250]
+    assert float(g0[dom0].mean()) > float(g0[dom1].mean()) + 0.3
+    # PMWF with oracle covariances recovers source 0 at the reference microphone far better than the unprocessed mixture
+    ps = torch.einsum("fc,fd->fcd", steer[0], steer[0].conj()).unsqueeze(0)
+    pn = torch.einsum("fc,fd->fcd", steer[1], steer[1].conj()).unsqueeze(0) + 1e-4 * torch.eye(C, dtype=torch.cdouble)
+    target = (steer[0, :, 0].unsqueeze(-1) * s[0]).unsqueeze(0).unsqueeze(0)
+    for beta, rank in ((0.0, "one"), (1.0, "full")):
+        y = ParametricMultichannelWienerFilter(beta=beta, rank=rank, ref_channel=0)(x, ps, pn)
+        err, base = (y - target).abs().pow(2).mean(), (x[:, :1] - target).abs().pow(2).mean()
+        assert float(err) < 0.05 * float(base), (beta, rank, float(err), float(base))
+    y = ParametricMultichannelWienerFilter(beta=0.0, rank="one", ref_channel="max_snr")(x, ps, pn)
+    assert y.shape == (B, 1, F, N)
+    # WPE: reverberation that is an exact linear prediction from delayed frames (wet[t] = dry[t] + 0.5 wet[t-2] - 0.3 wet[t-3])
+    # is removed almost completely when the filter covers those taps
+    N2 = 800
+    dry = torch.randn(1, 1, 3, N2, dtype=torch.cdouble)
+    wet = dry.clone()
+    for t in range(3, N2):
+        wet[..., t] = dry[..., t] + 0.5 * wet[..., t - 2] - 0.3 * wet[..., t - 3]
+    filt = WPEFilter(filter_length=4, prediction_delay=2)
+    assert filt.convtensor(wet).shape == (1, 1, 3, N2, 4) and torch.equal(filt.convtensor(wet)[0, 0, 0, 10], wet[0, 0, 0, [8, 7, 6, 5]])
+    before = (wet - dry).abs().pow(2).mean()
+    exact, _ = filt(wet, torch.ones(1, 3, N2, dtype=torch.double))                       # flat power: plain least squares
+    assert float((exact - dry).abs().pow(2).mean()) < 0.02 * float(before)
+    # with the power re-estimated from the signal itself (a white source is the worst case for that weighting) it still helps
+    out, _ = MaskBasedDereverbWPE(filter_length=4, prediction_delay=2, num_iterations=2)(wet)
+    after = (out - dry).abs().pow(2).mean()
+    assert float(after) < 0.7 * float(before), (float(after), float(before))
+    lens = torch.tensor([500])
+    out_l, _ = MaskBasedDereverbWPE(filter_length=4, prediction_delay=2)(wet, lens)
+    assert float(out_l[..., 500:].abs().max()) == 0.0
+
+
+def test_transformer_unet_shapes_padding_and_time_conditioning():
+    from speech_b200.audio.transformer_unet import ConvPositionEmbed, LearnedSinusoidalPosEmb, SpectrogramTransformerUNet, TransformerUNet
+
+    torch.manual_seed(0)
+    assert LearnedSinusoidalPosEmb(8)(torch.tensor([0.1, 0.5])).shape == (2, 9)
+    with pytest.raises(ValueError):
+        ConvPositionEmbed(8, 4)
+    with pytest.raises(ValueError):
+        TransformerUNet(16, 3)
+    net = SpectrogramTransformerUNet(in_channels=2, out_channels=1, freq_dim=9, dim=32, depth=4, heads=4, conv_pos_embed_kernel_size=5).eval()
+    x = torch.randn(2, 1, 9, 12, dtype=torch.cfloat)
+    cond = torch.randn(2, 1, 9, 12, dtype=torch.cfloat)
+    lens = torch.tensor([12, 8])
+    y, _ = net(x, lens, condition=cond, time=torch.tensor([0.2, 0.9]))
+    assert y.shape == (2, 1, 9, 12) and y.is_complex() and float(y[1, :, :, 8:].abs().max()) == 0
+    # outputs of the valid part do not depend on what sits in the padding
+    x2 = x.clone(); x2[1, :, :, 8:] = 100.0
+    y2, _ = net(x2, lens, condition=cond, time=torch.tensor([0.2, 0.9]))
+    assert torch.allclose(y2[1, :, :, :8], y[1, :, :, :8], atol=1e-4)
+    # the time condition matters once the (zero-initialised) adaptive norms are trained
+    for m in net.modules():
+        if hasattr(m, "to_gamma"):
+            torch.nn.init.normal_(m.to_gamma.weight, std=0.5)
+    y3, _ = net(x, lens, condition=cond, time=torch.tensor([0.8, 0.1]))
+    y4, _ = net(x, lens, condition=cond, time=torch.tensor([0.2, 0.9]))
+    assert not torch.allclose(y3, y4, atol=1e-4)
+    y4.abs().sum().backward()
+    assert net.proj_in.weight.grad is not None
