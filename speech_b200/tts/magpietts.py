@@ -6,11 +6,14 @@ selected cross-attention heads); audio frames enter as the sum of one embedding 
 stacked frames) and leave through ``final_proj: d_model → codebooks · stack · tokens`` (``:524-530``); an optional *local
 transformer* refines the codebooks of one step autoregressively (``:532-570``); classifier-free guidance by dropping the
 text condition during training and mixing conditional / unconditional logits at inference; KV-cache autoregressive
-``infer_batch`` (``:2856``) and ``do_tts`` (``:3711``).
+``infer_batch`` (``:2856``) and ``do_tts`` (``:3711``).  Voice context (``model_type``: extra cross-attention memory through a
+context encoder, or a decoder prefix), an attention prior that keeps inference monotonic, and chunked long-form synthesis with
+state carried between chunks (``:4380``) are part of the model.
 """
 from __future__ import annotations
 
 import math
+from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Tuple
 
 import torch
@@ -58,6 +61,47 @@ class ForwardSumLoss(nn.Module):
         return total / B
 
 
+@dataclass
+class LongFormState:
+    """What a long-form synthesis run carries from one text chunk to the next."""
+
+    context_codes: Optional[torch.Tensor] = None          # stacked codes of the voice context [1, C·S, Tc]
+    context_len: Optional[torch.Tensor] = None
+    chunks_done: int = 0
+    text_history: List[str] = field(default_factory=list)
+
+
+def split_text_for_tts(transcript: str, max_chars: int = 200) -> List[str]:
+    """Sentences are kept whole where possible and merged up to ``max_chars``; a single sentence longer than that is split at
+    commas / semicolons, then at spaces."""
+    import re
+
+    def pieces(s: str) -> List[str]:
+        if len(s) <= max_chars:
+            return [s]
+        parts = [p.strip() for p in re.split(r"(?<=[,;:])\s+", s) if p.strip()]
+        if len(parts) == 1:
+            words, cur, out = s.split(), "", []
+            for w in words:
+                if cur and len(cur) + len(w) + 1 > max_chars:
+                    out.append(cur)
+                    cur = w
+                else:
+                    cur = (cur + " " + w).strip()
+            return out + ([cur] if cur else [])
+        return [q for p in parts for q in pieces(p)]
+
+    sents = [q for s in re.split(r"(?<=[.!?])\s+", transcript) if s.strip() for q in pieces(s.strip())]
+    chunks, cur = [], ""
+    for s in sents:
+        if cur and len(cur) + len(s) + 1 > max_chars:
+            chunks.append(cur)
+            cur = s
+        else:
+            cur = (cur + " " + s).strip()
+    return chunks + ([cur] if cur else [])
+
+
 class MagpieTTSModel(ModelPT):
     def __init__(self, cfg: DictConfig, trainer=None, codec: Optional[AudioCodecModel] = None, tokenizer=None):
         super().__init__(cfg=cfg, trainer=trainer)
@@ -93,6 +137,19 @@ class MagpieTTSModel(ModelPT):
         C = self.num_audio_codebooks * self.frame_stacking_factor
         self.audio_embeddings = nn.ModuleList([nn.Embedding(self.num_all_tokens_per_codebook, d) for _ in range(C)])
         self.final_proj = nn.Linear(d, C * self.num_all_tokens_per_codebook)
+        # ---- conditioning on a context recording (voice cloning).  ``model_type``:
+        #   "text_only"                 no context;
+        #   "multi_encoder_context_tts" context codes -> context encoder -> extra cross-attention memory next to the text;
+        #   "decoder_context_tts"       context code embeddings are a prefix of the decoder input;
+        #   "decoder_ce"                as above, but the prefix first goes through the context encoder.
+        # (reference ``tts/models/magpietts.py``: ``prepare_context_tensors`` and the ``model_type`` switch)
+        self.model_type = str(cfg_get(cfg, "model_type", "text_only"))
+        if self.model_type not in ("text_only", "multi_encoder_context_tts", "decoder_context_tts", "decoder_ce"):
+            raise ValueError(f"unknown model_type '{self.model_type}'")
+        if self.model_type in ("multi_encoder_context_tts", "decoder_ce"):
+            self.context_encoder = Transformer(**dict(cfg.context_encoder))
+        self.context_duration_min = float(cfg_get(cfg, "context_duration_min", 3.0))
+        self.context_duration_max = float(cfg_get(cfg, "context_duration_max", 10.0))
         # ---- optional local transformer over the codebooks of one step
         self.local_transformer_type = str(cfg_get(cfg, "local_transformer_type", "none")).lower()
         if self.local_transformer_type != "none":
@@ -199,19 +256,45 @@ class MagpieTTSModel(ModelPT):
             pri[b, :al, :tl] = beta_binomial_prior(tl, al, self.prior_scaling_factor).to(device)
         return pri
 
-    def forward(self, text, text_len, codes, codes_len, drop_condition: bool = False):
+    def prepare_context(self, context_codes: Optional[torch.Tensor], context_codes_len: Optional[torch.Tensor]):
+        """Context codes ``[B, C·S, Tc]`` (stacked like the targets) -> ``(embeddings [B, Tc, d], mask [B, Tc])`` after the
+        context encoder where the model has one; ``(None, None)`` for text-only models or when no context is given."""
+        if self.model_type == "text_only" or context_codes is None:
+            return None, None
+        emb = self.embed_audio_tokens(context_codes)
+        mask = torch.arange(emb.shape[1], device=emb.device)[None] < context_codes_len[:, None]
+        if hasattr(self, "context_encoder"):
+            emb = self.context_encoder(emb, mask)["output"]
+        return emb, mask
+
+    def forward(self, text, text_len, codes, codes_len, drop_condition: bool = False, context_codes=None, context_codes_len=None):
         """Teacher forcing.  codes [B, C·S, T] (stacked, with BOS / EOS).  Returns logits [B, T-1, C·S, N] and the
-        cross-attention probabilities of the decoder layers."""
+        cross-attention probabilities of the decoder layers (over the text positions only)."""
         cond, cond_mask = self.encode_text(text, text_len)
+        ctx, ctx_mask = self.prepare_context(context_codes, context_codes_len)
         if drop_condition:
             cond = torch.zeros_like(cond)
+            ctx = torch.zeros_like(ctx) if ctx is not None else None
         inp, tgt_len = codes[:, :, :-1], codes_len - 1
         x = self.embed_audio_tokens(inp)
         xmask = torch.arange(x.shape[1], device=x.device)[None] < tgt_len[:, None]
         prior = self._priors(text_len, tgt_len, x.shape[1], cond.shape[1], x.device) if self.training else None
+        n_prefix = n_mem = 0
+        if ctx is not None and self.model_type == "multi_encoder_context_tts":
+            n_mem = ctx.shape[1]
+            cond, cond_mask = torch.cat([ctx.to(cond.dtype), cond], 1), torch.cat([ctx_mask, cond_mask], 1)
+            if prior is not None:                                   # the prior constrains text positions only
+                prior = torch.cat([torch.ones(prior.shape[0], prior.shape[1], n_mem, device=prior.device), prior], 2)
+        elif ctx is not None:
+            n_prefix = ctx.shape[1]
+            x, xmask = torch.cat([ctx.to(x.dtype), x], 1), torch.cat([ctx_mask, xmask], 1)
+            if prior is not None:
+                prior = torch.cat([torch.ones(prior.shape[0], n_prefix, prior.shape[2], device=prior.device), prior], 1)
         priors = [prior if i in self.alignment_layers else None for i in range(len(self.decoder.layers))] if prior is not None else None
         out = self.decoder(x, xmask, cond=cond, cond_mask=cond_mask, attn_prior=priors)
-        h = out["output"]
+        h = out["output"][:, n_prefix:]
+        xmask = xmask[:, n_prefix:]
+        out["attn_probabilities"] = [None if a is None else a[:, :, n_prefix:, n_mem:] for a in out["attn_probabilities"]]
         B, T, _ = h.shape
         logits = ops.linear(h, self.final_proj.weight, self.final_proj.bias).float().view(B, T, len(self.audio_embeddings), -1)
         return logits, out["attn_probabilities"], h, xmask
@@ -285,7 +368,12 @@ class MagpieTTSModel(ModelPT):
         codes, codes_len = self.audio_to_codes(audio, audio_len)
         codes, codes_len = self.stack_codes(codes, codes_len)
         drop = self.training and self.cfg_unconditional_prob > 0 and float(torch.rand(())) < self.cfg_unconditional_prob
-        logits, attn, h, xmask = self.forward(text, text_len, codes, codes_len, drop_condition=drop)
+        ctx_codes = ctx_len = None
+        if self.model_type != "text_only" and len(batch) >= 6 and batch[4] is not None:
+            ctx_codes, ctx_len = self.audio_to_codes(batch[4], batch[5])           # (context_audio, context_audio_len)
+            ctx_codes, ctx_len = self.stack_codes(ctx_codes, ctx_len)
+        logits, attn, h, xmask = self.forward(text, text_len, codes, codes_len, drop_condition=drop, context_codes=ctx_codes,
+                                              context_codes_len=ctx_len)
         tgt = codes[:, :, 1:].permute(0, 2, 1)                         # [B, T-1, C·S]
         ce = F.cross_entropy(logits[xmask].reshape(-1, logits.shape[-1]), tgt[xmask].reshape(-1))
         logs = {"codebook_loss": ce.detach()}
@@ -335,17 +423,46 @@ class MagpieTTSModel(ModelPT):
 
     @torch.no_grad()
     def infer_batch(self, text, text_len, max_decoder_steps: int = 500, temperature: float = 0.7, topk: int = 80,
-                    use_cfg: bool = False, cfg_scale: float = 2.5, min_generated_frames: int = 4):
-        """Autoregressive decoding with KV caches.  Returns (audio [B, n], audio_len, codes [B, C, T], codes_len)."""
+                    use_cfg: bool = False, cfg_scale: float = 2.5, min_generated_frames: int = 4, context_codes=None,
+                    context_codes_len=None, attention_prior_strength: float = 0.0, attention_prior_window: int = 4,
+                    return_attention: bool = False):
+        """Autoregressive decoding with KV caches.  Returns (audio [B, n], audio_len, codes [B, C, T], codes_len).
+
+        ``context_codes`` [B, C·S, Tc] condition the voice (see ``model_type``).  For decoder-prefix models the contexts of a batch
+        are cut to the shortest one so that the prefix is dense in the cache.  ``attention_prior_strength`` > 0 keeps the
+        cross-attention monotonic at inference: at every step text positions further than ``attention_prior_window`` from the
+        position attended at the previous step are down-weighted by that factor (in log space), which prevents skipped or
+        repeated words on long inputs; generation of a row also ends once its attention has sat on the last text token for
+        ``2 * attention_prior_window`` steps without an end token."""
         self.eval()
         B, dev = text.shape[0], text.device
         cond, cond_mask = self.encode_text(text, text_len)
+        n_mem = 0
+        prefix = None
+        if context_codes is not None and self.model_type != "text_only":
+            if self.model_type != "multi_encoder_context_tts":
+                keep = int(context_codes_len.min())
+                context_codes, context_codes_len = context_codes[:, :, :keep], context_codes_len.clamp(max=keep)
+            ctx, ctx_mask = self.prepare_context(context_codes, context_codes_len)
+            if self.model_type == "multi_encoder_context_tts":
+                n_mem = ctx.shape[1]
+                cond, cond_mask = torch.cat([ctx.to(cond.dtype), cond], 1), torch.cat([ctx_mask, cond_mask], 1)
+            else:
+                prefix = ctx
         if use_cfg:
             cond = torch.cat([cond, torch.zeros_like(cond)], 0)
             cond_mask = torch.cat([cond_mask, cond_mask], 0)
         CS = len(self.audio_embeddings)
         cur = torch.full((B, CS, 1), self.audio_bos_id, dtype=torch.long, device=dev)
         cache = self.decoder.new_cache()
+        offset = 0
+        if prefix is not None:
+            px = torch.cat([prefix, torch.zeros_like(prefix)], 0) if use_cfg else prefix
+            self.decoder(px, torch.ones(px.shape[:2], dtype=torch.bool, device=dev), cond=cond, cond_mask=cond_mask, cache=cache)
+            offset = prefix.shape[1]
+        attended = torch.zeros(B, dtype=torch.long, device=dev)          # text position the alignment currently sits on
+        at_end = torch.zeros(B, dtype=torch.long, device=dev)
+        attn_trace = []
         done = torch.zeros(B, dtype=torch.bool, device=dev)
         end_step = torch.full((B,), max_decoder_steps, dtype=torch.long, device=dev)
         frames = []
@@ -354,7 +471,26 @@ class MagpieTTSModel(ModelPT):
             if use_cfg:
                 x = torch.cat([x, x], 0)
             xmask = torch.ones(x.shape[:2], dtype=torch.bool, device=dev)
-            h = self.decoder(x, xmask, cond=cond, cond_mask=cond_mask, cache=cache, position_offset=step)["output"][:, -1]
+            prior = None
+            if attention_prior_strength > 0:
+                pos = torch.arange(cond.shape[1] - n_mem, device=dev)[None, :]
+                near = (pos >= attended[:, None] - 1) & (pos <= attended[:, None] + attention_prior_window)
+                pr = torch.where(near, torch.ones((), device=dev), torch.full((), math.exp(-attention_prior_strength), device=dev))
+                pr = torch.cat([torch.ones(B, n_mem, device=dev), pr], 1).unsqueeze(1)          # [B, 1, T_cond]
+                prior = torch.cat([pr, torch.ones_like(pr)], 0) if use_cfg else pr
+                prior = [prior if (not self.alignment_layers or i in self.alignment_layers) else None for i in range(len(self.decoder.layers))]
+            dec = self.decoder(x, xmask, cond=cond, cond_mask=cond_mask, cache=cache, position_offset=offset + step, attn_prior=prior)
+            h = dec["output"][:, -1]
+            probs = [a for i, a in enumerate(dec["attn_probabilities"]) if a is not None and (not self.alignment_layers or i in self.alignment_layers)]
+            if probs:
+                a = torch.stack([p[:B, :, -1, n_mem:].float().mean(1) for p in probs]).mean(0)   # [B, T_text]
+                a = a.masked_fill(~cond_mask[:B, n_mem:], 0.0)
+                peak = a.argmax(-1)
+                attended = torch.where(peak > attended, torch.minimum(peak, attended + attention_prior_window), attended) \
+                    if attention_prior_strength > 0 else peak
+                at_end = torch.where(attended >= text_len.to(dev) - 1, at_end + 1, torch.zeros_like(at_end))
+                if return_attention:
+                    attn_trace.append(a)
             logits = ops.linear(h, self.final_proj.weight, self.final_proj.bias).float().view(h.shape[0], CS, -1)
             if use_cfg:
                 logits = logits[B:] + cfg_scale * (logits[:B] - logits[B:])
@@ -371,6 +507,8 @@ class MagpieTTSModel(ModelPT):
                     logits[..., self.audio_eos_id] = float("-inf")
                 nxt = self._sample(logits, temperature, topk)
             is_eos = (nxt == self.audio_eos_id).any(dim=1)
+            if attention_prior_strength > 0:
+                is_eos = is_eos | ((at_end >= 2 * attention_prior_window) & (step >= min_generated_frames))
             newly = is_eos & ~done
             end_step = torch.where(newly, torch.full_like(end_step, step), end_step)
             done = done | is_eos
@@ -383,6 +521,8 @@ class MagpieTTSModel(ModelPT):
         codes, lens = self.unstack_codes(codes, lens)
         lens = lens.clamp(min=1)
         audio, audio_len = self.codes_to_audio(codes, lens)
+        if return_attention:
+            return audio, audio_len, codes, lens, (torch.stack(attn_trace, 1) if attn_trace else None)
         return audio, audio_len, codes, lens
 
     def _local_ar(self, h, temperature, topk, uncond=None, cfg_scale=1.0):
@@ -406,6 +546,35 @@ class MagpieTTSModel(ModelPT):
                 useq = torch.cat([useq, e], 1)
         return torch.stack(out, dim=1)
 
+    def _generate_speech_with_state(self, transcript, max_chars_per_chunk, context_audio, carry_voice, crossfade_ms, **kw):
+        state = LongFormState()
+        if context_audio is not None:
+            a = context_audio.view(1, -1).to(self.device)
+            codes, n = self.audio_to_codes(a, torch.tensor([a.shape[1]], device=self.device))
+            state.context_codes, state.context_len = self.stack_codes(codes, n)
+        sr = int(getattr(self._codec, "sample_rate", 22050))
+        fade = int(sr * crossfade_ms / 1000)
+        out = torch.zeros(0, device=self.device)
+        for chunk in split_text_for_tts(transcript, max_chars_per_chunk):
+            ids = self.tokenize(chunk).unsqueeze(0).to(self.device)
+            audio, alen, codes, clen = self.infer_batch(ids, torch.tensor([ids.shape[1]], device=self.device),
+                                                        context_codes=state.context_codes, context_codes_len=state.context_len, **kw)
+            piece = audio[0, : int(alen[0])]
+            if state.context_codes is None and carry_voice:
+                # the first chunk fixes the voice of the rest (bounded by the longest context the model was trained with)
+                max_frames = max(1, int(self.context_duration_max * sr / max(1, getattr(self._codec, "samples_per_frame", 1024))))
+                st, sl = self.stack_codes(codes[:, :, :max_frames], clen.clamp(max=max_frames))
+                state.context_codes, state.context_len = st, sl
+            state.chunks_done += 1
+            state.text_history.append(chunk)
+            if out.numel() and fade > 0 and piece.numel() > fade and out.numel() > fade:
+                ramp = torch.linspace(0, 1, fade, device=piece.device)
+                out = torch.cat([out[:-fade], out[-fade:] * (1 - ramp) + piece[:fade] * ramp, piece[fade:]])
+            else:
+                out = torch.cat([out, piece])
+        self.last_long_form_state = state
+        return out
+
     def tokenize(self, transcript: str) -> torch.Tensor:
         ids = [self.text_bos_id] + list(self.tokenizer.text_to_ids(transcript)) + [self.text_eos_id]
         return torch.tensor(ids, dtype=torch.long)
@@ -417,9 +586,16 @@ class MagpieTTSModel(ModelPT):
         return audio, alen
 
     @torch.no_grad()
-    def generate_speech(self, transcript: str, max_chars_per_chunk: int = 200, **kw) -> torch.Tensor:
-        """Long-form synthesis: split at sentence boundaries, synthesise chunk by chunk, concatenate."""
+    def generate_speech(self, transcript: str, max_chars_per_chunk: int = 200, context_audio: Optional[torch.Tensor] = None,
+                        carry_voice: bool = True, crossfade_ms: float = 20.0, **kw) -> torch.Tensor:
+        """Long-form synthesis: the text is split at sentence boundaries into chunks that the decoder handles comfortably and
+        synthesised chunk by chunk; the state that crosses chunks (:class:`LongFormState`) is the voice context: the caller's
+        ``context_audio`` where given, otherwise (``carry_voice``) the codes of the first generated chunk, so that every chunk
+        is spoken by the same voice.  Chunks are joined with a short cross-fade."""
         import re
+
+        if self.model_type != "text_only":
+            return self._generate_speech_with_state(transcript, max_chars_per_chunk, context_audio, carry_voice, crossfade_ms, **kw)
 
         sents = [s.strip() for s in re.split(r"(?<=[.!?])\s+", transcript) if s.strip()]
         chunks, cur = [], ""

@@ -354,3 +354,51 @@ def test_code_token_models_train_through_the_trainer_on_synthetic_codes():
     tr = Trainer(max_steps=3, accelerator="cpu", log_every_n_steps=1, enable_checkpointing=False, logger=False)
     tr.fit(ear)
     assert math.isfinite(float(tr.callback_metrics["train_loss"]))
+
+
+@pytest.mark.parametrize("model_type", ["multi_encoder_context_tts", "decoder_context_tts", "decoder_ce"])
+def test_magpie_voice_context_attention_prior_and_long_form_state(model_type):
+    from speech_b200.tts.magpietts import LongFormState, split_text_for_tts
+
+    torch.manual_seed(0)
+    codec = AudioCodecModel(OmegaConf.create({**CODEC_CFG, "train_discriminator": False}))
+    tok = CharTokenizer(list("abcdefgh .,"))
+    tf = dict(n_layers=1, d_model=32, d_ffn=64, sa_n_heads=2, kernel_size=1, p_dropout=0.0)
+    m = MagpieTTSModel(_magpie_cfg(model_type=model_type, context_encoder=dict(tf, is_causal=False), alignment_decoder_loss_layers=[0],
+                                   prior_scaling_factor=0.5, alignment_loss_scale=0.1, context_duration_max=0.1), codec=codec, tokenizer=tok)
+    assert hasattr(m, "context_encoder") == (model_type != "decoder_context_tts")
+    text = torch.randint(0, 8, (2, 6))
+    tl = torch.tensor([6, 4])
+    audio, al = torch.randn(2, 1600) * 0.1, torch.tensor([1600, 1280])
+    ctx_audio, cl = torch.randn(2, 960) * 0.1, torch.tensor([960, 640])
+    m.train()
+    loss, logs = m._loss((text, tl, audio, al, ctx_audio, cl))
+    loss.backward()
+    assert math.isfinite(float(loss)) and "alignment_loss" in logs
+    if model_type != "decoder_context_tts":
+        assert next(m.context_encoder.parameters()).grad is not None
+    # the context changes the prediction; cross-attention returned to the caller covers text positions only
+    m.eval()
+    codes, n = m.stack_codes(*m.audio_to_codes(audio, al))
+    cc, cn = m.stack_codes(*m.audio_to_codes(ctx_audio, cl))
+    with torch.no_grad():
+        lg_a, attn, _, _ = m(text, tl, codes, n, context_codes=cc, context_codes_len=cn)
+        lg_b, _, _, _ = m(text, tl, codes, n, context_codes=cc.flip(-1), context_codes_len=cn)
+        lg_0, _, _, _ = m(text, tl, codes, n)
+    assert lg_a.shape == lg_0.shape and not torch.allclose(lg_a, lg_b)
+    m.train()
+    with torch.no_grad():
+        attn = m(text, tl, codes, n, context_codes=cc, context_codes_len=cn)[1]
+    m.eval()
+    assert attn[0].shape[-2:] == (codes.shape[-1] - 1, 6)
+    out = m.infer_batch(text, tl, max_decoder_steps=6, context_codes=cc, context_codes_len=cn, attention_prior_strength=4.0,
+                        attention_prior_window=2, return_attention=True)
+    assert out[2].shape[0] == 2 and out[4].shape[0] == 2 and out[4].shape[2] == 6
+    # long-form: chunks share the voice context, state is kept on the model
+    chunks = split_text_for_tts("abc def. gh ab, cd ef gh ab cd. a b.", 12)
+    assert all(len(c) <= 12 for c in chunks) and " ".join(chunks).replace(" ", "") == "abcdef.ghab,cdefghabcd.ab."
+    wav = m.generate_speech("abc def. gh ab. cd ef.", max_chars_per_chunk=8, max_decoder_steps=3, crossfade_ms=1.0)
+    st = m.last_long_form_state
+    assert isinstance(st, LongFormState) and st.chunks_done == 3 and st.context_codes is not None and wav.numel() > 0
+    wav2 = m.generate_speech("abc. def.", max_chars_per_chunk=5, max_decoder_steps=3, context_audio=ctx_audio[0])
+    assert m.last_long_form_state.context_codes.shape[-1] == int(cn[0]) and wav2.numel() > 0
