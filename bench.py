@@ -496,7 +496,8 @@ def main():
                                          f"{len(run.trainer.grad_sync.buckets)} buckets launched during backward"
                                          + (f", {run.trainer.grad_sync.reducer.ctas} CTAs" if hasattr(run.trainer.grad_sync, "reducer") else ""))
                        if world > 1 else "none",
-                       "optimizer": "AdamW+Noam, clip 1.0",
+                       "optimizer": (("fully sharded AdamW (ZeRO-3), constant lr 3e-4, clip 1.0" if world > 1 else "AdamW, constant lr 3e-4, clip 1.0")
+                                     if canary else "AdamW+Noam, clip 1.0"),
                        "l2": "no flush: per-step activations are several GB, far larger than the 126 MB L2"},
             "clocks": clocks, "gpu_launches": launches,
             "loss_first_last": [round(losses[0], 3), round(losses[-1], 3)],
