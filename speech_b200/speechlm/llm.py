@@ -86,10 +86,9 @@ class RMSNorm(nn.Module):
         self.variance_epsilon = eps
 
     def forward(self, x):
-        dt = x.dtype
-        xf = x.float()
-        xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.variance_epsilon)
-        return (self.weight.float() * xf).to(dt)
+        from ..ops.native_llm import rmsnorm
+
+        return rmsnorm(x, self.weight, self.variance_epsilon)       # one kernel each way for bf16 on GPUs, fp32 PyTorch otherwise
 
 
 def rope_tables(positions: torch.Tensor, dim: int, theta: float) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -135,8 +134,11 @@ class Attention(nn.Module):
         v = self.v_proj(x).view(B, T, self.n_kv, dh)
         if self.cfg.qk_norm:
             q, k = self.q_norm(q), self.k_norm(k)
+        from ..ops.native_llm import rope
+
+        cos_c, sin_c = (cos if cos.shape[0] == B else cos.expand(B, -1, -1)).contiguous(), (sin if sin.shape[0] == B else sin.expand(B, -1, -1)).contiguous()
+        q, k = rope(q, cos_c, sin_c), rope(k, cos_c, sin_c)        # on the [B, T, H, D] layout, before the head transpose
         q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
-        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
         cp_gather = getattr(self, "cp_gather", None)
         if cp_gather is not None and cache is None:
             k, v = cp_gather(k), cp_gather(v)        # context parallelism: queries stay local, keys / values of all ranks
@@ -163,7 +165,9 @@ class MLP(nn.Module):
         self.down_proj = _Linear(inner, cfg.hidden_size, bias=cfg.mlp_bias)
 
     def forward(self, x):
-        return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
+        from ..ops.native_llm import swiglu
+
+        return self.down_proj(swiglu(self.gate_proj(x), self.up_proj(x)))
 
 
 class DecoderLayer(nn.Module):
