@@ -33,6 +33,7 @@ def main():
     ap.add_argument("--enc-layers", type=int, default=32)
     ap.add_argument("--sequence-parallel", action="store_true")
     ap.add_argument("--packed", action="store_true")
+    ap.add_argument("--profile", default="", help="after the timed steps, run two more under torch.profiler and write the top kernels by device time to this file")
     ap.add_argument("--smoke-cpu", action="store_true", help="tiny model on the CPU, host clock: checks the script, measures nothing")
     args = ap.parse_args()
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
@@ -200,6 +201,18 @@ def main():
             "clocks": clocks, "gpu_launches": 0 if cpu else int(ops.native.launch_count - launches0), "loss_first_last": [losses[0], losses[-1]],
             "e2e": {"value": round(float(toks) / (float(ms) / 1e3), 1), "unit": "LLM input tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4,
                     "note": "the timed region itself copies inputs from pinned memory and reads the loss back every step"}}))
+    if args.profile and not cpu and rank == 0:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for i in range(2):
+                step(args.warmup + args.steps + i, False)
+            torch.cuda.synchronize()
+        with open(args.profile, "w") as f:
+            f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=90))
+    elif args.profile and not cpu:
+        for i in range(2):
+            step(args.warmup + args.steps + i, False)
     if world > 1:
         dist.destroy_process_group()
 

@@ -52,8 +52,10 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const fl
 }
 
 // dx = rstd * (g*dy - xhat * mean(g*dy*xhat)), xhat = x * rstd;  dgamma += sum_rows dy * xhat.
-// dgamma is accumulated per block in shared memory (fp32 [D]) and added to global memory once per block.
-template <bool SMALL>
+// A lane touches the same columns (lane*8 + k*256 ...) in every row, so for D <= NCH*256 its share of dgamma lives in NCH*8
+// registers across all rows of the block and reaches shared memory once; NCH = 0 is the generic form with one shared-memory
+// atomic per element.  Shared memory (fp32 [D]) is added to global memory once per block.
+template <int NCH>
 __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
                                    const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma,
                                    long long rows, int D) {
@@ -61,7 +63,12 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const _
   for (int i = threadIdx.x; i < D; i += blockDim.x) sdg[i] = 0.f;
   __syncthreads();
   const int wpb = blockDim.x >> 5, lane = threadIdx.x & 31;
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};      // SMALL (D <= 256): a lane owns the same 8 columns in every row
+  constexpr int NA = NCH > 0 ? NCH : 1;
+  float acc[NA][8];
+#pragma unroll
+  for (int k = 0; k < NA; ++k)
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc[k][u] = 0.f;
   for (long long row = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); row < rows; row += (long long)gridDim.x * wpb) {
     const __nv_bfloat16 *xr = x + row * D, *dyr = dy + row * D;
     const float rstd = rstd_in[row];
@@ -77,25 +84,51 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const _
     }
     dot = warp_sum(dot) / D;
     __nv_bfloat16* dxr = dx + row * D;
-    for (int i = lane * 8; i < D; i += 256) {
-      float fx[8], fd[8], o[8];
-      unpack8(*reinterpret_cast<const uint4*>(xr + i), fx);
-      unpack8(*reinterpret_cast<const uint4*>(dyr + i), fd);
-      const float4 g0 = *reinterpret_cast<const float4*>(gamma + i), g1 = *reinterpret_cast<const float4*>(gamma + i + 4);
-      const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    if (NCH > 0) {
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const float xh = fx[u] * rstd;
-        o[u] = rstd * (g[u] * fd[u] - xh * dot);
-        if (SMALL) acc[u] += fd[u] * xh;
-        else if (dgamma) atomicAdd(&sdg[i + u], fd[u] * xh);
+      for (int k = 0; k < NA; ++k) {
+        const int i = lane * 8 + k * 256;
+        if (i < D) {
+          float fx[8], fd[8], o[8];
+          unpack8(*reinterpret_cast<const uint4*>(xr + i), fx);
+          unpack8(*reinterpret_cast<const uint4*>(dyr + i), fd);
+          const float4 g0 = *reinterpret_cast<const float4*>(gamma + i), g1 = *reinterpret_cast<const float4*>(gamma + i + 4);
+          const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const float xh = fx[u] * rstd;
+            o[u] = rstd * (g[u] * fd[u] - xh * dot);
+            acc[k][u] += fd[u] * xh;
+          }
+          *reinterpret_cast<uint4*>(dxr + i) = pack8(o);
+        }
       }
-      *reinterpret_cast<uint4*>(dxr + i) = pack8(o);
+    } else {
+      for (int i = lane * 8; i < D; i += 256) {
+        float fx[8], fd[8], o[8];
+        unpack8(*reinterpret_cast<const uint4*>(xr + i), fx);
+        unpack8(*reinterpret_cast<const uint4*>(dyr + i), fd);
+        const float4 g0 = *reinterpret_cast<const float4*>(gamma + i), g1 = *reinterpret_cast<const float4*>(gamma + i + 4);
+        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float xh = fx[u] * rstd;
+          o[u] = rstd * (g[u] * fd[u] - xh * dot);
+          if (dgamma) atomicAdd(&sdg[i + u], fd[u] * xh);
+        }
+        *reinterpret_cast<uint4*>(dxr + i) = pack8(o);
+      }
     }
   }
-  if (SMALL && dgamma && lane * 8 < D) {
+  if (NCH > 0 && dgamma) {
 #pragma unroll
-    for (int u = 0; u < 8; ++u) atomicAdd(&sdg[lane * 8 + u], acc[u]);
+    for (int k = 0; k < NA; ++k) {
+      const int i = lane * 8 + k * 256;
+      if (i < D) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) atomicAdd(&sdg[i + u], acc[k][u]);
+      }
+    }
   }
   __syncthreads();
   if (dgamma)
@@ -184,12 +217,14 @@ SB_API int sb_rmsnorm_bwd(const void* dy, const void* x, const float* gamma, con
   // few blocks for short rows (many rows per block amortise the per-block flush of dgamma), at most two waves
   const long long cap = 148ll * 2;
   const int grid = (int)(nb > cap ? cap : nb);
-  if (D <= 256)
-    rmsnorm_bwd_kernel<true><<<grid, warps * 32, D * sizeof(float), stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, rstd,
-                                                                               (__nv_bfloat16*)dx, dgamma, rows, D);
-  else
-    rmsnorm_bwd_kernel<false><<<grid, warps * 32, D * sizeof(float), stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, rstd,
-                                                                                (__nv_bfloat16*)dx, dgamma, rows, D);
+  const __nv_bfloat16 *pdy = (const __nv_bfloat16*)dy, *px = (const __nv_bfloat16*)x;
+  __nv_bfloat16* pdx = (__nv_bfloat16*)dx;
+  const size_t smem = D * sizeof(float);
+  if (D <= 256) rmsnorm_bwd_kernel<1><<<grid, warps * 32, smem, stream>>>(pdy, px, gamma, rstd, pdx, dgamma, rows, D);
+  else if (D <= 512) rmsnorm_bwd_kernel<2><<<grid, warps * 32, smem, stream>>>(pdy, px, gamma, rstd, pdx, dgamma, rows, D);
+  else if (D <= 1024) rmsnorm_bwd_kernel<4><<<grid, warps * 32, smem, stream>>>(pdy, px, gamma, rstd, pdx, dgamma, rows, D);
+  else if (D <= 2048) rmsnorm_bwd_kernel<8><<<grid, warps * 32, smem, stream>>>(pdy, px, gamma, rstd, pdx, dgamma, rows, D);
+  else rmsnorm_bwd_kernel<0><<<grid, warps * 32, smem, stream>>>(pdy, px, gamma, rstd, pdx, dgamma, rows, D);
   return (int)cudaGetLastError();
 }
 

@@ -214,7 +214,7 @@ class SALMAutomodel(SALM):
                 row_len = (total + mult - 1) // mult * mult
             packed = pack_sequences(inp["input_embeds"], inp["attention_mask"], inp["target_ids"], row_len)
             out = self.llm(inputs_embeds=packed["input_embeds"], attention_mask=packed["attention_mask"],
-                           position_ids=packed["position_ids"], seq_ids=packed["seq_ids"])
+                           position_ids=packed["position_ids"], seq_ids=packed["seq_ids"], return_hidden=True)
             tgt = packed["target_ids"]
             inp = {**inp, "packed": packed}
         else:
@@ -226,14 +226,21 @@ class SALMAutomodel(SALM):
                 emb = F.pad(emb, (0, 0, 0, extra))
                 am = F.pad(am, (0, extra), value=0)
                 tgt = F.pad(tgt, (0, extra), value=IGNORE_INDEX)
-            out = self.forward(emb, am)
-        logits = out["logits"].float()
+            out = self.llm(inputs_embeds=emb, attention_mask=am, return_hidden=True)
         if "cp_slice" in out:
             tgt = tgt[:, out["cp_slice"][0]:out["cp_slice"][1]]        # this rank scores its slice of the sequence
-        loss_sum = F.cross_entropy(logits.reshape(-1, logits.shape[-1]), tgt.reshape(-1), ignore_index=IGNORE_INDEX, reduction="sum")
+        # the output head runs on the labelled positions only (prompt and audio positions carry no target): with a 150 k-entry
+        # vocabulary the head and the soft-max are a sizeable part of the step when computed for every position
+        h = out["hidden_states"]
         labelled = tgt != IGNORE_INDEX
         n = labelled.sum()
-        correct = ((logits.argmax(dim=-1) == tgt) & labelled).sum()
+        hs, ts = h[labelled], tgt[labelled]
+        if hs.shape[0] == 0:
+            zero = h.sum() * 0.0
+            return zero, n, n.clone(), inp
+        logits = self.llm.lm_head(hs).float()
+        loss_sum = F.cross_entropy(logits, ts, reduction="sum")
+        correct = (logits.argmax(dim=-1) == ts).sum()
         return loss_sum, n, correct, inp
 
     def training_step(self, batch, batch_idx):
