@@ -118,7 +118,8 @@ class SALMDataset(Dataset):
         audio = torch.zeros((len(auds), int(alen.max()) if len(auds) else 1))
         for i, a in enumerate(auds):
             audio[i, : a.numel()] = a
-        return {"audios": audio, "audio_lens": alen, "input_ids": ids, "loss_mask": mask}
+        # the number of positions with a target, counted here on the host: models use it to size per-target work without a device read
+        return {"audios": audio, "audio_lens": alen, "input_ids": ids, "loss_mask": mask, "num_loss_tokens": int(mask.sum())}
 
 
 def synthetic_conversations(num_samples: int, seed: int = 0, min_duration: float = 0.5, max_duration: float = 1.5,

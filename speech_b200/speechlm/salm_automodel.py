@@ -229,18 +229,24 @@ class SALMAutomodel(SALM):
             out = self.llm(inputs_embeds=emb, attention_mask=am, return_hidden=True)
         if "cp_slice" in out:
             tgt = tgt[:, out["cp_slice"][0]:out["cp_slice"][1]]        # this rank scores its slice of the sequence
-        # the output head runs on the labelled positions only (prompt and audio positions carry no target): with a 150 k-entry
-        # vocabulary the head and the soft-max are a sizeable part of the step when computed for every position
         h = out["hidden_states"]
         labelled = tgt != IGNORE_INDEX
         n = labelled.sum()
-        hs, ts = h[labelled], tgt[labelled]
-        if hs.shape[0] == 0:
-            zero = h.sum() * 0.0
-            return zero, n, n.clone(), inp
-        logits = self.llm.lm_head(hs).float()
-        loss_sum = F.cross_entropy(logits, ts, reduction="sum")
-        correct = (logits.argmax(dim=-1) == ts).sum()
+        cap = batch.get("num_loss_tokens", None) if isinstance(batch, dict) else None
+        if isinstance(cap, int) and 0 < cap < labelled.numel() // 2:
+            # The output head runs on the labelled positions only (prompt and audio positions carry no target; with a 150 k-entry
+            # vocabulary the head and the soft-max over every position are a sizeable part of the step).  ``num_loss_tokens`` is
+            # an upper bound counted on the host when the batch was collated, so the selection needs no device-to-host read:
+            # the first ``cap`` entries of a stable sort by the label flag; surplus entries are unlabelled and ignored by the loss.
+            order = torch.argsort(labelled.reshape(-1).to(torch.uint8), descending=True, stable=True)[:cap]
+            hs = h.reshape(-1, h.shape[-1]).index_select(0, order)
+            ts = tgt.reshape(-1).index_select(0, order)
+            logits = self.llm.lm_head(hs).float()
+        else:
+            logits = self.llm.lm_head(h).float()
+            logits, ts = logits.reshape(-1, logits.shape[-1]), tgt.reshape(-1)
+        loss_sum = F.cross_entropy(logits, ts, ignore_index=IGNORE_INDEX, reduction="sum")
+        correct = ((logits.argmax(dim=-1) == ts) & (ts != IGNORE_INDEX)).sum()
         return loss_sum, n, correct, inp
 
     def training_step(self, batch, batch_idx):
