@@ -391,3 +391,60 @@ def build(device, world: int, local_rank: int, n_layers: Optional[int], dropout:
         return loss.detach()
 
     return model, step
+
+
+# ----------------------------------------------------------------------------------------------------------- speech-LLM
+class RefEqSALM(nn.Module):
+    """Speech-LLM the way the reference assembles it from libraries: mel features -> Conformer encoder (above) -> linear
+    projection to the LLM width; text embedded by the LLM's table; audio embeddings spliced over the placeholder token of every
+    row (left padded); Hugging Face ``Qwen3ForCausalLM`` on ``inputs_embeds`` with ``labels`` (logits and cross entropy at every
+    position, as ``transformers`` computes them)."""
+
+    def __init__(self, llm_cfg: dict, enc_layers: int = 32, d_model: int = 1024, n_mels: int = 128, dropout: float = 0.1,
+                 placeholder_id: int = 0, pad_id: int = 0):
+        super().__init__()
+        from transformers import Qwen3Config, Qwen3ForCausalLM
+
+        self.features = MelFeatures(n_mels=n_mels)
+        self.encoder = ConformerEncoder(enc_layers, d_model, 8, 4 * d_model, 9, dropout, feat_in=n_mels)
+        cfg = Qwen3Config(**{k: v for k, v in llm_cfg.items() if k not in ("qk_norm", "model_type")})
+        self.llm = Qwen3ForCausalLM(cfg)
+        self.proj = nn.Linear(d_model, cfg.hidden_size)
+        self.placeholder_id, self.pad_id = placeholder_id, pad_id
+
+    def forward(self, audios, audio_lens, input_ids, loss_mask):
+        feats, flen = self.features(audios, audio_lens)
+        enc, elen = self.encoder(feats, flen)
+        aud = self.proj(enc)
+        emb_table = self.llm.get_input_embeddings()
+        rows, tgts = [], []
+        a = 0
+        elen_l = elen.tolist()
+        for b in range(input_ids.shape[0]):
+            ids = input_ids[b]
+            keep = ids != self.pad_id
+            ids, lm = ids[keep], loss_mask[b][keep]
+            pos = (ids == self.placeholder_id).nonzero().flatten().tolist()
+            text = emb_table(ids)
+            tgt = torch.where(lm.bool(), ids, torch.full_like(ids, -100))
+            parts, tparts, prev = [], [], 0
+            for p in pos:
+                n = int(elen_l[a])
+                parts += [text[prev:p], aud[a, :n].to(text.dtype)]
+                tparts += [tgt[prev:p], torch.full((n,), -100, dtype=tgt.dtype, device=tgt.device)]
+                prev, a = p + 1, a + 1
+            parts.append(text[prev:])
+            tparts.append(tgt[prev:])
+            rows.append(torch.cat(parts))
+            tgts.append(torch.cat(tparts))
+        L = max(r.shape[0] for r in rows)
+        H = rows[0].shape[1]
+        emb = rows[0].new_zeros((len(rows), L, H))
+        labels = torch.full((len(rows), L), -100, dtype=torch.long, device=emb.device)
+        mask = torch.zeros((len(rows), L), dtype=torch.long, device=emb.device)
+        for b, (r, t) in enumerate(zip(rows, tgts)):
+            emb[b, L - r.shape[0]:] = r
+            labels[b, L - r.shape[0]:] = t
+            mask[b, L - r.shape[0]:] = 1
+        out = self.llm(inputs_embeds=emb, attention_mask=mask, labels=labels)
+        return out.loss, emb.shape[0] * emb.shape[1]

@@ -33,6 +33,8 @@ def main():
     ap.add_argument("--enc-layers", type=int, default=32)
     ap.add_argument("--sequence-parallel", action="store_true")
     ap.add_argument("--packed", action="store_true")
+    ap.add_argument("--impl", default="native", choices=["native", "eager"],
+                    help="eager: the reference-equivalent arm (eager PyTorch Conformer + Hugging Face Qwen3 + torch AdamW), one GPU")
     ap.add_argument("--profile", default="", help="after the timed steps, run two more under torch.profiler and write the top kernels by device time to this file")
     ap.add_argument("--smoke-cpu", action="store_true", help="tiny model on the CPU, host clock: checks the script, measures nothing")
     args = ap.parse_args()
@@ -71,6 +73,18 @@ def main():
                             "optim": {"name": "fully_sharded_adamw" if sharded else "adamw", "lr": 1e-4, "weight_decay": 0.01}})
     tok = ByteLevelTokenizer(special_tokens=["<pad>", "<s>", "</s>", "<|im_start|>", "<|im_end|>"])
     model = SALMAutomodel(cfg, tokenizer=tok)
+    eager = None
+    if args.impl == "eager":
+        if world > 1:
+            raise SystemExit("the reference-equivalent arm of this benchmark runs on one GPU")
+        import sys
+
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+        from reference_equivalent import RefEqSALM
+
+        # the native model above is kept only for its tokenizer / prompt formatter / batch assembly; it never runs
+        eager = RefEqSALM(llm, enc_layers=(1 if cpu else args.enc_layers), d_model=(176 if cpu else 1024), n_mels=(32 if cpu else 128),
+                          dropout=0.1, placeholder_id=model.audio_locator_tag_id, pad_id=model.text_pad_id)
     mesh = None
     if world > 1:
         mesh = DeviceMesh({"dp_shard": world // args.tp, "tp": args.tp})
@@ -105,13 +119,19 @@ def main():
     batches = [{k: (v.pin_memory() if (torch.is_tensor(v) and not cpu) else v) for k, v in b.items()} for b in batches[:8]]
     h2d = sum(sum(v.numel() * v.element_size() for v in b.values() if torch.is_tensor(v)) for b in batches) / len(batches)
 
-    model.to(dev)
+    if eager is not None:
+        n_params = sum(p.numel() for p in eager.parameters())
+        eager.to(dev).train()
+        eopt = torch.optim.AdamW(eager.parameters(), lr=1e-4, weight_decay=0.01)
+    else:
+        model.to(dev)
     model.train()
     import types
 
     object.__setattr__(model, "_trainer", types.SimpleNamespace(gradient_clip_val=1.0, global_step=0))    # clip value for the optimizer
-    model.setup_optimization()
-    opt = model._optimizer
+    if eager is None:
+        model.setup_optimization()
+    opt = model._optimizer if eager is None else None
     sync = None
     if world > 1:
         from speech_b200.parallel.ddp import build_grad_sync
@@ -121,7 +141,24 @@ def main():
     tokens_done = torch.zeros((), dtype=torch.float64, device=dev)
     host_loss = torch.zeros(1) if cpu else torch.zeros(1).pin_memory()
 
+    def eager_step(i: int, count: bool):
+        import contextlib
+
+        b = {k: (v.to(dev, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batches[i % len(batches)].items()}
+        with (contextlib.nullcontext() if cpu else torch.autocast("cuda", dtype=cdt)):
+            loss, positions = eager(b["audios"], b["audio_lens"], b["input_ids"], b["loss_mask"])
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(eager.parameters(), 1.0)
+        eopt.step()
+        eopt.zero_grad(set_to_none=True)
+        host_loss.copy_(loss.detach().float().view(1), non_blocking=True)
+        if count:
+            tokens_done.add_(float(positions))
+        return {"loss": loss}
+
     def step(i: int, count: bool):
+        if eager is not None:
+            return eager_step(i, count)
         b = {k: (v.to(dev, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batches[i % len(batches)].items()}
         if sync is not None:
             sync.begin_step()
@@ -193,10 +230,11 @@ def main():
             "metric": "SALM (Canary-Qwen-2.5B shape) train tokens/s", "value": round(float(toks) / (float(ms) / 1e3), 1), "unit": "LLM input tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(float(ms) / args.steps, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "native" if eager is None else "reference-equivalent (eager PyTorch Conformer + Hugging Face Qwen3 + torch.optim.AdamW)",
             "config": {"model": f"FastConformer-xlarge {args.enc_layers}L encoder + Qwen3-1.7B-shape LLM {args.llm_layers}L, {n_params / 1e9:.2f} B parameters on rank 0",
                        "global_batch": f"<= {args.batch_tokens} padded LLM positions per data-parallel rank", "seq_len": "5-20 s audio (63-250 audio tokens) + prompt + ~1.5 answer words/s",
                        "parallelism": f"dp_shard{world // args.tp} x tp{args.tp}" + (" + sp" if args.sequence_parallel else ""),
-                       "optimizer": "fully sharded AdamW (ZeRO-3)" if sharded else "AdamW", "packed": bool(args.packed),
+                       "optimizer": "torch.optim.AdamW" if eager is not None else ("fully sharded AdamW (ZeRO-3)" if sharded else "AdamW"), "packed": bool(args.packed),
                        "l2": "no flush: weights alone are several GB"},
             "clocks": clocks, "gpu_launches": 0 if cpu else int(ops.native.launch_count - launches0), "loss_first_last": [losses[0], losses[-1]],
             "e2e": {"value": round(float(toks) / (float(ms) / 1e3), 1), "unit": "LLM input tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4,
