@@ -248,6 +248,8 @@ def main():
             torch.cuda.synchronize()
         with open(args.profile, "w") as f:
             f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=90))
+        if os.environ.get("SPEECH_B200_BENCH_TRACE"):
+            prof.export_chrome_trace(os.environ["SPEECH_B200_BENCH_TRACE"])      # kernel timeline per stream (.json or .json.gz)
     elif args.profile and not cpu:
         for i in range(2):
             step(args.warmup + args.steps + i, False)

@@ -65,17 +65,32 @@ __global__ void __launch_bounds__(512) peer_gather_kernel(void* const* __restric
                                                          __nv_bfloat16* __restrict__ dst, float* __restrict__ dst_f32) {
   const long long n8 = slice >> 3;
   const long long total = n8 * world;
-  for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(g / n8);
-    const long long i = (g - (long long)r * n8) << 3;
-    const uint4 v = __ldcg(reinterpret_cast<const uint4*>((const char*)bufs[r] + src_off + i * 2));
-    const long long o = (long long)r * slice + i;
-    *reinterpret_cast<uint4*>(dst + o) = v;
-    if (dst_f32) {
-      float t[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      add8(t, v);
-      *reinterpret_cast<float4*>(dst_f32 + o) = make_float4(t[0], t[1], t[2], t[3]);
-      *reinterpret_cast<float4*>(dst_f32 + o + 4) = make_float4(t[4], t[5], t[6], t[7]);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  // four peer loads in flight per thread: the copy is bound by NVLink latency, not by the few blocks' arithmetic
+  for (long long g0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; g0 < total; g0 += 4 * stride) {
+    uint4 v[4];
+    long long o[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long g = g0 + u * stride;
+      o[u] = -1;
+      if (g < total) {
+        const int r = (int)(g / n8);
+        const long long i = (g - (long long)r * n8) << 3;
+        v[u] = __ldcg(reinterpret_cast<const uint4*>((const char*)bufs[r] + src_off + i * 2));
+        o[u] = (long long)r * slice + i;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (o[u] < 0) continue;
+      *reinterpret_cast<uint4*>(dst + o[u]) = v[u];
+      if (dst_f32) {
+        float t[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        add8(t, v[u]);
+        *reinterpret_cast<float4*>(dst_f32 + o[u]) = make_float4(t[0], t[1], t[2], t[3]);
+        *reinterpret_cast<float4*>(dst_f32 + o[u] + 4) = make_float4(t[4], t[5], t[6], t[7]);
+      }
     }
   }
 }
@@ -135,7 +150,31 @@ __global__ void __launch_bounds__(512) peer_rs_adamw_kernel(SbFsdpArgs a) {
   const long long base = (long long)a.rank * a.slice;
   float sq = 0.f;
   const long long step = (long long)blockDim.x * 8;
-  for (long long i = c0 + (long long)threadIdx.x * 8; i < c1; i += step) {
+  long long i_begin = c0 + (long long)threadIdx.x * 8;
+  if (a.mode == 1 && a.world <= 2) {
+    // store-only form with few ranks: four positions (x world loads) in flight per thread; rank order of the sums is unchanged
+    for (; i_begin + 3 * step < c1; i_begin += 4 * step) {
+      uint4 v[4][2];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+          if (q < a.world) v[u][q] = __ldcg(reinterpret_cast<const uint4*>((const char*)a.grad_bufs[q] + a.buf_off + (base + i_begin + u * step) * 2));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+          if (q < a.world) add8(acc, v[u][q]);
+        const long long i = i_begin + u * step;
+        *reinterpret_cast<float4*>(a.grad_shard + i) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        *reinterpret_cast<float4*>(a.grad_shard + i + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sq += acc[k] * acc[k];
+      }
+    }
+  }
+  for (long long i = i_begin; i < c1; i += step) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     // fixed order by rank: every run (and every world layout) sums in the same order; four peer loads in flight
     for (int q0 = 0; q0 < a.world; q0 += 4) {

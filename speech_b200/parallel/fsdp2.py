@@ -79,7 +79,7 @@ class FullyShardedAdamW(Optimizer):
     """AdamW over 1/W slices; owns the sharded storage and drives gather / reduce-scatter for ``FSDP2GradSync``."""
 
     def __init__(self, model: torch.nn.Module, units: Optional[Sequence[torch.nn.Module]] = None, lr: float = 1e-3, betas=(0.9, 0.999),
-                 eps: float = 1e-8, weight_decay: float = 1e-2, max_grad_norm: float = 0.0, group=None, device=None, ctas: int = 8,
+                 eps: float = 1e-8, weight_decay: float = 1e-2, max_grad_norm: float = 0.0, group=None, device=None, ctas: int = 12,
                  gather_blocks: int = 32, replicate_group=None):
         """``group``: the ranks a unit is sharded over (default: all).  ``replicate_group``: hybrid sharding (HSDP) — ranks that
         hold the SAME slice in different shard groups; their reduced gradient slices are averaged before the update, which
@@ -197,6 +197,15 @@ class FullyShardedAdamW(Optimizer):
         """Point the unit's parameters at their gathered images.  ``grad``: the unit's gradient slot; with ``attach`` it also
         becomes ``parameter.grad`` (autograd accumulates into it), otherwise only the kernels' ``_grad_view`` is set (its address
         is fixed per unit, and the whole-layer executor records it when it first meets the layer, in forward)."""
+        # A unit always lands in the same pool slot and the same gradient slot, so the views are built once per (unit, buffers);
+        # later calls only re-attach ``.grad`` (begin_step clears it).  Building ~6 tensor views for each of a block's ~40
+        # parameters on every visit costs about a millisecond of host time per unit, more than a Conformer block computes.
+        key = (f32.data_ptr(), 0 if lowp is None else lowp.data_ptr(), 0 if grad is None else grad.data_ptr())
+        if getattr(u, "_view_key", None) == key:
+            if attach and grad is not None:
+                for p in u.params:
+                    p.grad = p._grad_view
+            return
         for p in u.params:
             o, n = u.offsets[id(p)]
             shape = self._shape_of(p)
@@ -208,6 +217,7 @@ class FullyShardedAdamW(Optimizer):
                 if attach:
                     p.grad = p._grad_view
             p._arena = self
+        u._view_key = key if grad is not None else None
 
     def _shape_of(self, p) -> Tuple[int, ...]:
         return self._shapes[id(p)]
