@@ -76,6 +76,10 @@ class SaveRestoreConnector:
     def save_to(self, model, save_path: str) -> str:
         from ..utils.logging import is_global_rank_zero
 
+        # a fully-sharded model keeps its parameters as slices inside the optimizer: every rank takes part in assembling the
+        # full values (a collective), then only rank 0 writes the archive
+        opt = getattr(model, "_optimizer", None)
+        full_sd = opt.full_model_state_dict() if hasattr(opt, "full_model_state_dict") else None
         if not is_global_rank_zero():
             return save_path
         save_path = os.path.abspath(os.path.expanduser(save_path))
@@ -89,7 +93,7 @@ class SaveRestoreConnector:
             if getattr(model, "artifacts", None):
                 self._handle_artifacts(model, nemo_file_folder=tmpdir)
                 self._update_artifact_paths(model, path2yaml_file=cfg_path)
-            self._save_state_dict_to_disk(model.state_dict(), weights_path)
+            self._save_state_dict_to_disk(full_sd if full_sd is not None else model.state_dict(), weights_path)
             self._make_nemo_file_from_folder(save_path, tmpdir)
         return save_path
 

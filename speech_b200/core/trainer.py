@@ -520,7 +520,7 @@ class Trainer:
             "epoch": self.current_epoch,
             "global_step": self.global_step,
             "batch_idx": self.batch_idx,
-            "state_dict": {k: v.detach().cpu() for k, v in model.state_dict().items()},
+            "state_dict": self._model_state_dict(),
             "hyper_parameters": {"cfg": to_container(model.cfg, resolve=True)},
             "pytorch-lightning_version": "speech_b200",
         }
@@ -530,6 +530,14 @@ class Trainer:
             ckpt["callbacks"] = {type(cb).__name__: cb.state_dict() for cb in self.callbacks if hasattr(cb, "state_dict")}
         self._call("on_save_checkpoint", ckpt)
         return ckpt
+
+    def _model_state_dict(self) -> Dict[str, Any]:
+        """Parameters of a fully-sharded model live as slices inside the optimizer: it assembles the full values (a collective,
+        which is why every rank builds the checkpoint dictionary although only rank 0 writes it)."""
+        for o in getattr(self, "optimizers", []) or []:
+            if hasattr(o, "full_model_state_dict"):
+                return o.full_model_state_dict()
+        return {k: v.detach().cpu() for k, v in self.model.state_dict().items()}
 
     def save_checkpoint(self, filepath: str, weights_only: bool = False):
         ckpt = self.dump_checkpoint(weights_only)
@@ -543,7 +551,18 @@ class Trainer:
 
     def _restore_checkpoint(self, path: str, weights_only: bool = False):
         ckpt = torch.load(path, map_location="cpu", weights_only=False)
-        self.model.load_state_dict(ckpt["state_dict"], strict=True)
+        sharded = [o for o in (getattr(self, "optimizers", []) or []) if hasattr(o, "load_full_params")]
+        if sharded:
+            # sharded parameters are taken slice-wise by their optimizer; the module only loads what the optimizer does not own
+            owned = set(sharded[0]._names().values())
+            rest = {k: v for k, v in ckpt["state_dict"].items() if k not in owned}
+            missing, unexpected = self.model.load_state_dict(rest, strict=False)
+            bad = [k for k in missing if k not in owned] + list(unexpected)
+            if bad:
+                raise KeyError(f"checkpoint does not match the model: {bad[:8]}")
+            sharded[0].load_full_params(ckpt["state_dict"])
+        else:
+            self.model.load_state_dict(ckpt["state_dict"], strict=True)
         if weights_only:
             return
         self.global_step = int(ckpt.get("global_step", 0))

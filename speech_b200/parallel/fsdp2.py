@@ -471,6 +471,92 @@ class FullyShardedAdamW(Optimizer):
                 out[id(p)] = full[o:o + n].view(self._shape_of(p)).clone()
         return out
 
+    # ------------------------------------------------------------------ checkpoints (independent of the number of ranks)
+    def _gather_flat(self, u: _Unit, shard: torch.Tensor) -> torch.Tensor:
+        full = torch.zeros(u.numel, dtype=torch.float32, device=self.device)
+        mine = shard[u.shard_base:u.shard_base + u.slice].contiguous()
+        if self.world > 1:
+            dist.all_gather(list(full.chunk(self.world)), mine, group=self.group)
+        else:
+            full.copy_(mine)
+        return full
+
+    def _names(self) -> Dict[int, str]:
+        return {id(p): n for n, p in self.model.named_parameters()}
+
+    def full_model_state_dict(self) -> Dict[str, torch.Tensor]:
+        """``model.state_dict()`` with every sharded parameter replaced by its full fp32 value (CPU tensors).  Parameters of
+        units that are not gathered hold no data, so the plain ``state_dict`` must not be saved.  A collective."""
+        names = self._names()
+        full = self.gather_full_state()
+        sd = {}
+        for k, v in self.model.state_dict().items():
+            sd[k] = v.detach().cpu() if torch.is_tensor(v) else v
+        prefix_free = {n: full[i].cpu() for i, n in names.items() if i in full}
+        for k in list(sd):
+            if k in prefix_free:
+                sd[k] = prefix_free[k]
+        return sd
+
+    def load_full_params(self, state_dict: Dict[str, torch.Tensor]) -> None:
+        """Take this rank's slices of the full parameter values in ``state_dict`` (names as in ``model.named_parameters()``);
+        entries that are missing keep their current value.  Every rank calls it with the same dictionary."""
+        names = self._names()
+        with torch.no_grad():
+            for u in self.all_units:
+                flat = self._gather_flat(u, self.master) if any(names[id(q)] not in state_dict for q in u.params) else \
+                    torch.zeros(u.numel, dtype=torch.float32, device=self.device)
+                for q in u.params:
+                    t = state_dict.get(names[id(q)])
+                    if t is not None:
+                        o, n = u.offsets[id(q)]
+                        if tuple(t.shape) != self._shape_of(q):
+                            raise ValueError(f"{names[id(q)]}: checkpoint shape {tuple(t.shape)} != {self._shape_of(q)}")
+                        flat[o:o + n].copy_(t.reshape(-1).to(self.device, torch.float32))
+                self.master[u.shard_base:u.shard_base + u.slice].copy_(flat[self.rank * u.slice:(self.rank + 1) * u.slice])
+                u.gathered = False
+        self._refresh_lowp_shards()
+        if self.root is not None:
+            self._gather(self.root)
+
+    def state_dict(self) -> Dict[str, Any]:
+        """Moments as full tensors in the parameters' own shapes, keyed by parameter name: no padding and no slice boundaries
+        enter the file, so the checkpoint loads at any number of ranks (and into a replicated AdamW of the same model).  The
+        reference needs a patch of its sharded optimizer for the same property (``core/optim/flash_optim.py:22``: uneven
+        FSDP2 shards in the saved optimizer state).  A collective."""
+        names = self._names()
+        state = {}
+        for u in self.all_units:
+            m, v = self._gather_flat(u, self.exp_avg), self._gather_flat(u, self.exp_avg_sq)
+            for q in u.params:
+                o, n = u.offsets[id(q)]
+                shape = self._shape_of(q)
+                state[names[id(q)]] = {"exp_avg": m[o:o + n].view(shape).cpu().clone(), "exp_avg_sq": v[o:o + n].view(shape).cpu().clone()}
+        groups = [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups]
+        return {"format": "fully_sharded_adamw/full-by-name", "step": self._step, "state": state, "param_groups": groups}
+
+    def load_state_dict(self, sd: Dict[str, Any]) -> None:
+        if sd.get("format") != "fully_sharded_adamw/full-by-name":
+            raise ValueError("not a FullyShardedAdamW state dict (expected the full-by-name format)")
+        names = self._names()
+        self._step = int(sd.get("step", 0))
+        for g, saved in zip(self.param_groups, sd.get("param_groups", [])):
+            g.update({k: v for k, v in saved.items() if k != "params"})
+        with torch.no_grad():
+            for u in self.all_units:
+                m = torch.zeros(u.numel, dtype=torch.float32, device=self.device)
+                v = torch.zeros(u.numel, dtype=torch.float32, device=self.device)
+                for q in u.params:
+                    st = sd["state"].get(names[id(q)])
+                    if st is None:
+                        continue
+                    o, n = u.offsets[id(q)]
+                    m[o:o + n].copy_(st["exp_avg"].reshape(-1).to(self.device, torch.float32))
+                    v[o:o + n].copy_(st["exp_avg_sq"].reshape(-1).to(self.device, torch.float32))
+                lo, hi = self.rank * u.slice, (self.rank + 1) * u.slice
+                self.exp_avg[u.shard_base:u.shard_base + u.slice].copy_(m[lo:hi])
+                self.exp_avg_sq[u.shard_base:u.shard_base + u.slice].copy_(v[lo:hi])
+
     def memory_report(self) -> Dict[str, float]:
         per = 4 + 8 + (2 if self.cuda else 0) + (4 if self.grad_shard is not None else 0)
         persistent = self.shard_numel * per
