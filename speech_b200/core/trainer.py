@@ -232,6 +232,9 @@ class Trainer:
         if self.device.type == "cuda":
             torch.cuda.set_device(self.device)
         model.to(self.device)
+        if hasattr(self.strategy_spec, "setup_model") and getattr(self.strategy_spec, "_model_set_up", None) is not model:
+            self.strategy_spec.setup_model(model)            # device mesh: the model shards itself before optimizers exist
+            self.strategy_spec._model_set_up = model
         for cb in self.callbacks:
             if hasattr(cb, "setup"):
                 cb.setup(self, model, stage)
@@ -258,6 +261,9 @@ class Trainer:
     def _setup_grad_sync(self):
         from ..parallel.ddp import build_grad_sync
 
+        if hasattr(self.strategy_spec, "build_grad_sync"):
+            self.grad_sync = self.strategy_spec.build_grad_sync(self.model, self.optimizers, self.device, sync_batchnorm=self.sync_batchnorm)
+            return
         self.grad_sync = build_grad_sync(self.model, self.optimizers, self.strategy_spec, self.world_size, self.device,
                                          sync_batchnorm=self.sync_batchnorm)
 

@@ -59,8 +59,13 @@ class _AllReduceSum(torch.autograd.Function):
 
 class GradSync:
     def __init__(self, model: torch.nn.Module, optimizers, world_size: int, device: torch.device,
-                 bucket_mb: float = DEFAULT_BUCKET_MB, sync_batchnorm: bool = False, grad_dtype: Optional[torch.dtype] = None):
+                 bucket_mb: float = DEFAULT_BUCKET_MB, sync_batchnorm: bool = False, grad_dtype: Optional[torch.dtype] = None,
+                 group=None):
+        """``group``: the process group gradients are averaged over (default: all ranks).  On a device mesh it is the
+        data-parallel group; ``world_size`` is then that group's size."""
         self.model, self.world_size, self.device = model, world_size, device
+        self.group = group
+        self._src = dist.get_global_rank(group, 0) if group is not None else 0
         self.arena = next((o.arena for o in optimizers if hasattr(o, "arena")), None)
         # parameters tagged ``_no_dp_sync`` (expert-parallel experts: every rank owns different ones) stay out of the exchange
         self.params = [p for p in model.parameters() if p.requires_grad and not getattr(p, "_no_dp_sync", False)]
@@ -80,7 +85,7 @@ class GradSync:
     def _broadcast_parameters(self):
         with torch.no_grad():
             if self.arena is not None:
-                dist.broadcast(self.arena.master, 0)
+                dist.broadcast(self.arena.master, self._src, group=self.group)
                 self.arena.refresh_lowp()
                 rest = [p for p in self.model.parameters() if id(p) not in self.arena.offsets]
             else:
@@ -88,7 +93,7 @@ class GradSync:
             rest = [p for p in rest if not getattr(p, "_no_dp_sync", False)]
             for t in rest + list(self.model.buffers()):
                 if t.is_floating_point() or t.dtype in (torch.long, torch.int):
-                    dist.broadcast(t.data, 0)
+                    dist.broadcast(t.data, self._src, group=self.group)
 
     def enable_sync_batchnorm(self):
         """Conformer conv modules reduce their BatchNorm sums over all ranks (one small all-reduce per layer)."""
@@ -204,10 +209,10 @@ class GradSync:
             self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(self.comm_stream):
                 flat.div_(self.world_size)
-                w = dist.all_reduce(flat, async_op=True)
+                w = dist.all_reduce(flat, async_op=True, group=self.group)
         else:
             flat.div_(self.world_size)
-            w = dist.all_reduce(flat, async_op=True)
+            w = dist.all_reduce(flat, async_op=True, group=self.group)
         self._works.append(w)
 
     def finish_step(self):

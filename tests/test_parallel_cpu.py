@@ -443,3 +443,27 @@ def test_moe_expert_parallel_and_expert_tensor_parallel_gradients_two_ranks(tmp_
                          capture_output=True, text=True, timeout=600, env=dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2"))
     assert out.returncode == 0, out.stderr[-4000:]
     assert out.stdout.count("RESULT ok") == 2
+
+
+def test_parallel_strategy_sizes_validation_and_sampler_arguments():
+    from speech_b200.parallel.strategy import ParallelStrategy
+    from speech_b200.speechlm.llm import LLMConfig
+
+    st = ParallelStrategy(dp_replicate_size=2, dp_shard_size=-1, tp_size=2, sequence_parallel=True)
+    mesh = st.setup(world_size=16, rank=5, create_groups=False)
+    assert mesh.sizes == {"pp": 1, "dp_replicate": 2, "dp_shard": 4, "cp": 1, "tp": 2} and mesh.size("dp") == 8
+    assert st.distributed_sampler_kwargs == {"num_replicas": 8, "rank": 2}            # rank 5 = (dp 2, tp 1)
+    ok = LLMConfig(num_attention_heads=16, num_key_value_heads=8, intermediate_size=6144)
+    assert st.validate(ok) == [] and st.validate(ok, max_sequence_multiple=8) == []
+    bad = st.validate(LLMConfig(num_attention_heads=6, num_key_value_heads=3, intermediate_size=1001), max_sequence_multiple=3)
+    assert len(bad) == 3 and "heads" in bad[0] and "feed-forward" in bad[1] and "multiples of 2" in bad[2]
+    assert "sequence_parallel needs" in ParallelStrategy(tp_size=1, sequence_parallel=True).validate()[0]
+    ep = ParallelStrategy(dp_shard_size=4, expert_parallel=True)
+    ep.setup(world_size=4, rank=0, create_groups=False)
+    assert "no experts" in ep.validate(ok)[0]
+    assert "6 experts" in ep.validate(LLMConfig(num_attention_heads=4, num_key_value_heads=4, num_experts=6, moe_intermediate_size=64))[0]
+    with pytest.raises(ValueError, match="pipeline"):
+        ParallelStrategy(pp_size=2).setup(world_size=4, rank=0, create_groups=False)
+    tp_only = ParallelStrategy(dp_shard_size=1, tp_size=4)
+    tp_only.setup(world_size=4, rank=1, create_groups=False)
+    assert tp_only.build_grad_sync(None, [], None) is None               # no rank sees different tokens: nothing to exchange
