@@ -142,6 +142,7 @@ class Trainer:
         self.sanity_checking = False
         self.interrupted = False
         self._resume_skip_batches = 0
+        self._batches_in_epoch = 0           # batches of the current epoch already trained on (saved in checkpoints)
         self.checkpoint_callback = next((c for c in self.callbacks if hasattr(c, "best_model_path")), None)
 
     # ------------------------------------------------------------------ properties
@@ -337,14 +338,16 @@ class Trainer:
             val_every = self.val_check_interval
             if isinstance(val_every, float):
                 val_every = max(1, int(n_batches * val_every)) if n_batches != float("inf") else None
+            epoch_complete = True
             for batch_idx, batch in enumerate(dl):
                 if batch_idx >= n_batches:
                     break
                 if self._resume_skip_batches > 0:
-                    self._resume_skip_batches -= 1
+                    self._resume_skip_batches -= 1      # resumed inside an epoch: these batches were trained on before the checkpoint
                     continue
                 self.batch_idx = batch_idx
                 self._train_batch(batch, batch_idx)
+                self._batches_in_epoch = batch_idx + 1
                 stepped = (batch_idx + 1) % self.accumulate_grad_batches == 0
                 if stepped and val_every and isinstance(self.val_check_interval, int) and \
                         self.global_step % val_every == 0 and model.val_dataloader() is not None:
@@ -354,10 +357,15 @@ class Trainer:
                         and model.val_dataloader() is not None:
                     self._validate_in_fit()
                 if self.should_stop or self._should_stop_steps():
+                    epoch_complete = n_batches != float("inf") and batch_idx + 1 >= n_batches
                     break
             model.on_train_epoch_end()
             self._call("on_train_epoch_end")
-            self.current_epoch += 1
+            if epoch_complete:
+                # a run that stops inside an epoch (max_steps, early stop) stays in that epoch: a checkpoint taken now resumes
+                # with the remaining batches of the same epoch and the same shuffling order
+                self.current_epoch += 1
+                self._batches_in_epoch = 0
 
     def _validate_in_fit(self):
         self._run_eval("val")
@@ -526,6 +534,7 @@ class Trainer:
             "epoch": self.current_epoch,
             "global_step": self.global_step,
             "batch_idx": self.batch_idx,
+            "batches_in_epoch": self._batches_in_epoch,
             "state_dict": self._model_state_dict(),
             "hyper_parameters": {"cfg": to_container(model.cfg, resolve=True)},
             "pytorch-lightning_version": "speech_b200",
@@ -543,7 +552,12 @@ class Trainer:
         for o in getattr(self, "optimizers", []) or []:
             if hasattr(o, "full_model_state_dict"):
                 return o.full_model_state_dict()
-        return {k: v.detach().cpu() for k, v in self.model.state_dict().items()}
+        sd = {k: v.detach() for k, v in self.model.state_dict().items()}
+        mp = {n: p for n, p in self.model.named_parameters() if getattr(p, "_mp_gather", None) is not None}
+        for n, p in mp.items():                      # tensor- / expert-parallel slices are written as whole tensors
+            if n in sd:
+                sd[n] = p._mp_gather(sd[n])
+        return {k: v.cpu() for k, v in sd.items()}
 
     def save_checkpoint(self, filepath: str, weights_only: bool = False):
         ckpt = self.dump_checkpoint(weights_only)
@@ -568,11 +582,21 @@ class Trainer:
                 raise KeyError(f"checkpoint does not match the model: {bad[:8]}")
             sharded[0].load_full_params(ckpt["state_dict"])
         else:
-            self.model.load_state_dict(ckpt["state_dict"], strict=True)
+            sd = ckpt["state_dict"]
+            mp = {n: p for n, p in self.model.named_parameters() if getattr(p, "_mp_slice", None) is not None}
+            if mp:
+                from ..parallel.tp import mp_local
+
+                sd = dict(sd)
+                for n, p in mp.items():
+                    if n in sd:
+                        sd[n] = mp_local(p, sd[n], p.shape)
+            self.model.load_state_dict(sd, strict=True)
         if weights_only:
             return
         self.global_step = int(ckpt.get("global_step", 0))
         self.current_epoch = int(ckpt.get("epoch", 0))
+        self._resume_skip_batches = self._batches_in_epoch = int(ckpt.get("batches_in_epoch", 0))
         for o, s in zip(self.optimizers, ckpt.get("optimizer_states", [])):
             o.load_state_dict(s)
         for o in self.optimizers:

@@ -492,7 +492,10 @@ class FullyShardedAdamW(Optimizer):
         sd = {}
         for k, v in self.model.state_dict().items():
             sd[k] = v.detach().cpu() if torch.is_tensor(v) else v
-        prefix_free = {n: full[i].cpu() for i, n in names.items() if i in full}
+        from .tp import mp_full
+
+        by_id = {id(q): q for q in self.model.parameters()}
+        prefix_free = {n: mp_full(by_id[i], full[i]).cpu() for i, n in names.items() if i in full}     # tensor-parallel slices -> whole
         for k in list(sd):
             if k in prefix_free:
                 sd[k] = prefix_free[k]
@@ -509,9 +512,10 @@ class FullyShardedAdamW(Optimizer):
                 for q in u.params:
                     t = state_dict.get(names[id(q)])
                     if t is not None:
+                        from .tp import mp_local
+
                         o, n = u.offsets[id(q)]
-                        if tuple(t.shape) != self._shape_of(q):
-                            raise ValueError(f"{names[id(q)]}: checkpoint shape {tuple(t.shape)} != {self._shape_of(q)}")
+                        t = mp_local(q, t, self._shape_of(q))            # this rank's tensor-parallel slice of a full tensor
                         flat[o:o + n].copy_(t.reshape(-1).to(self.device, torch.float32))
                 self.master[u.shard_base:u.shard_base + u.slice].copy_(flat[self.rank * u.slice:(self.rank + 1) * u.slice])
                 u.gathered = False
@@ -531,7 +535,10 @@ class FullyShardedAdamW(Optimizer):
             for q in u.params:
                 o, n = u.offsets[id(q)]
                 shape = self._shape_of(q)
-                state[names[id(q)]] = {"exp_avg": m[o:o + n].view(shape).cpu().clone(), "exp_avg_sq": v[o:o + n].view(shape).cpu().clone()}
+                from .tp import mp_full
+
+                state[names[id(q)]] = {"exp_avg": mp_full(q, m[o:o + n].view(shape)).cpu().clone(),
+                                       "exp_avg_sq": mp_full(q, v[o:o + n].view(shape)).cpu().clone()}
         groups = [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups]
         return {"format": "fully_sharded_adamw/full-by-name", "step": self._step, "state": state, "param_groups": groups}
 
@@ -550,9 +557,12 @@ class FullyShardedAdamW(Optimizer):
                     st = sd["state"].get(names[id(q)])
                     if st is None:
                         continue
+                    from .tp import mp_local
+
                     o, n = u.offsets[id(q)]
-                    m[o:o + n].copy_(st["exp_avg"].reshape(-1).to(self.device, torch.float32))
-                    v[o:o + n].copy_(st["exp_avg_sq"].reshape(-1).to(self.device, torch.float32))
+                    shape = self._shape_of(q)
+                    m[o:o + n].copy_(mp_local(q, st["exp_avg"], shape).reshape(-1).to(self.device, torch.float32))
+                    v[o:o + n].copy_(mp_local(q, st["exp_avg_sq"], shape).reshape(-1).to(self.device, torch.float32))
                 lo, hi = self.rank * u.slice, (self.rank + 1) * u.slice
                 self.exp_avg[u.shard_base:u.shard_base + u.slice].copy_(m[lo:hi])
                 self.exp_avg_sq[u.shard_base:u.shard_base + u.slice].copy_(v[lo:hi])

@@ -200,18 +200,55 @@ class FusedRowParallelFn(torch.autograd.Function):
         return dx, dw.to(weight.dtype), None
 
 
-def _shard_linear(lin: nn.Linear, dim: int, rank: int, ws: int) -> None:
+def mark_model_parallel(p: torch.Tensor, group, dim: int, rank: int, ws: int, gather=None, take=None) -> None:
+    """Record how a parameter that holds one slice of a larger tensor relates to the whole: ``p._mp_gather(local) -> full``
+    (a collective over ``group``) and ``p._mp_slice(full) -> local``.  Checkpoint code uses the pair to write full tensors and
+    to cut this rank's slice out of them again, so files do not depend on the parallel layout."""
+    def _gather(local: torch.Tensor) -> torch.Tensor:
+        parts = [torch.empty_like(local) for _ in range(ws)]
+        dist.all_gather(parts, local.contiguous(), group=group)
+        return torch.cat(parts, dim=dim)
+
+    def _take(full: torch.Tensor) -> torch.Tensor:
+        return full.chunk(ws, dim=dim)[rank].clone()
+
+    p._mp_gather = gather or _gather
+    p._mp_slice = take or _take
+
+
+def mp_full(p: torch.Tensor, local: torch.Tensor) -> torch.Tensor:
+    g = getattr(p, "_mp_gather", None)
+    return g(local) if g is not None else local
+
+
+def mp_local(p: torch.Tensor, full: torch.Tensor, local_shape) -> torch.Tensor:
+    if tuple(full.shape) == tuple(local_shape):
+        return full
+    t = getattr(p, "_mp_slice", None)
+    if t is None:
+        raise ValueError(f"checkpoint tensor of shape {tuple(full.shape)} does not fit a parameter of shape {tuple(local_shape)}")
+    out = t(full)
+    if tuple(out.shape) != tuple(local_shape):
+        raise ValueError(f"slice of shape {tuple(out.shape)} does not fit a parameter of shape {tuple(local_shape)}")
+    return out
+
+
+def _shard_linear(lin: nn.Linear, dim: int, rank: int, ws: int, group=None) -> None:
     """Keep this rank's slice of the weight (dim 0 = output features / column-parallel, 1 = input features / row-parallel)."""
     w = lin.weight.data
     if w.shape[dim] % ws:
         raise ValueError(f"cannot split dimension of size {w.shape[dim]} over {ws} ranks")
     lin.weight = nn.Parameter(w.chunk(ws, dim=dim)[rank].clone(), requires_grad=lin.weight.requires_grad)
     lin.weight._tensor_parallel = True          # one slice of a larger weight: norms and checkpoints treat it as such
+    if group is not None:
+        mark_model_parallel(lin.weight, group, dim, rank, ws)
     if dim == 0:
         lin.out_features = lin.weight.shape[0]
         if lin.bias is not None:
             lin.bias = nn.Parameter(lin.bias.data.chunk(ws, dim=0)[rank].clone(), requires_grad=lin.bias.requires_grad)
             lin.bias._tensor_parallel = True
+            if group is not None:
+                mark_model_parallel(lin.bias, group, 0, rank, ws)
     else:
         lin.in_features = lin.weight.shape[1]
         if lin.bias is not None and rank != 0:
@@ -235,9 +272,9 @@ def apply_tensor_parallel_llm(llm, group, sequence_parallel: bool = False) -> No
         att, mlp = layer.self_attn, layer.mlp
         dense = hasattr(mlp, "gate_proj")
         for lin in (att.q_proj, att.k_proj, att.v_proj) + ((mlp.gate_proj, mlp.up_proj) if dense else ()):
-            _shard_linear(getattr(lin, "base", lin), 0, r, ws)
+            _shard_linear(getattr(lin, "base", lin), 0, r, ws, group)
         for lin in (att.o_proj,) + ((mlp.down_proj,) if dense else ()):
-            _shard_linear(getattr(lin, "base", lin), 1, r, ws)
+            _shard_linear(getattr(lin, "base", lin), 1, r, ws, group)
         if not dense:
             _shard_experts_inner(mlp, r, ws, group)
         att.n_q, att.n_kv = cfg.num_attention_heads // ws, cfg.num_key_value_heads // ws
@@ -288,6 +325,15 @@ def _shard_experts_inner(blk, rank: int, ws: int, group) -> None:
     blk.gate_up = nn.Parameter(gu, requires_grad=blk.gate_up.requires_grad)
     blk.down = nn.Parameter(dn, requires_grad=blk.down.requires_grad)
     blk.gate_up._tensor_parallel = blk.down._tensor_parallel = True
+
+    def gather_gu(local):            # [E, 2 I/W, H] slices -> [E, 2 I, H] with the gate and up halves kept apart
+        parts = [torch.empty_like(local) for _ in range(ws)]
+        dist.all_gather(parts, local.contiguous(), group=group)
+        return torch.cat([q.view(E, 2, I // ws, H) for q in parts], dim=2).reshape(E, 2 * I, H)
+
+    mark_model_parallel(blk.gate_up, group, 1, rank, ws, gather=gather_gu,
+                        take=lambda full: full.view(E, 2, I, H).chunk(ws, dim=2)[rank].reshape(E, 2 * (I // ws), H).clone())
+    mark_model_parallel(blk.down, group, 2, rank, ws)
     blk.inner = I // ws
     blk.tp_size = ws              # the auxiliary loss is the same on every rank: scaled so that the summed router gradient counts it once
     _sum_grad_over_group(blk.gate.weight, group)

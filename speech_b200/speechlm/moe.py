@@ -185,6 +185,9 @@ def apply_expert_parallel(module: nn.Module, group) -> int:
             p = nn.Parameter(full.data[r * L:(r + 1) * L].clone(), requires_grad=full.requires_grad)
             p._expert_parallel = True
             p._no_dp_sync = True
+            from ..parallel.tp import mark_model_parallel
+
+            mark_model_parallel(p, group, 0, r, W)
             p.register_hook(lambda g, W=W: g / W)
             setattr(blk, name, p)
         blk.ep_group, blk.ep_rank, blk.ep_size, blk.local_first, blk.local_n = group, r, W, r * L, L

@@ -122,6 +122,10 @@ class SALMAutomodel(SALM):
             if apply_expert_parallel(self.llm, self._dp_group) == 0:
                 raise ValueError("expert_parallel is set but the LLM has no mixture-of-experts layers")
         self.setup_moe_options()
+        # loaders built before the mesh existed were sharded over all ranks: rebuild them over the data-parallel group
+        for attr, key in (("_train_dl", "train_ds"), ("_validation_dl", "validation_ds"), ("_test_dl", "test_ds")):
+            if getattr(self, attr, None) is not None and self.cfg.get(key, None) is not None:
+                setattr(self, attr, self._loader(self.cfg.get(key)))
 
     def setup_moe_options(self) -> None:
         """``moe_metrics: {enabled, mode: brief | detailed, top_k_experts, every_n_steps}`` switches expert-load tracking on."""
@@ -191,6 +195,18 @@ class SALMAutomodel(SALM):
             from ..parallel.tp import allreduce_sequence_parallel_grads
 
             allreduce_sequence_parallel_grads(self.llm, m.group("tp"))
+
+    def _loader(self, config):
+        """Data is sharded over the ranks that must see different samples (the mesh's ``dp`` group); tensor- and
+        context-parallel peers of a rank build the same batches from the same shard."""
+        m = getattr(self, "_device_mesh", None)          # loaders are first built inside the base constructor
+        if config is None or m is None:
+            return super()._loader(config)
+        from .data import build_salm_dataloader
+
+        dp = m.size("dp")
+        return build_salm_dataloader(config, self.tokenizer, self.prompt_formatter(), self.audio_locator_tag, self.text_pad_id,
+                                     m.rank("dp") if dp > 1 else 0, dp)
 
     def _sequence_multiple(self) -> int:
         m = self._device_mesh

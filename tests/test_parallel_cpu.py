@@ -467,3 +467,58 @@ def test_parallel_strategy_sizes_validation_and_sampler_arguments():
     tp_only = ParallelStrategy(dp_shard_size=1, tp_size=4)
     tp_only.setup(world_size=4, rank=1, create_groups=False)
     assert tp_only.build_grad_sync(None, [], None) is None               # no rank sees different tokens: nothing to exchange
+
+
+SALM_TRAINER_SCRIPT = textwrap.dedent("""
+    import os, sys, torch, torch.distributed as dist
+    sys.path.insert(0, {repo!r})
+    from speech_b200.core.config import OmegaConf
+    from speech_b200.core.trainer import Trainer
+    from speech_b200.models.configs import encoder_cfg, preprocessor_cfg
+    from speech_b200.parallel.strategy import ParallelStrategy
+    from speech_b200.speechlm.salm_automodel import SALMAutomodel
+    from speech_b200.tokenizers import ByteLevelTokenizer
+
+    TINY = dict(vocab_size=300, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                head_dim=8, tie_word_embeddings=False, qk_norm=True, model_type="qwen3")
+    pc = {{"preprocessor": {{**preprocessor_cfg(32), "dither": 0.0}}, "encoder": encoder_cfg("small", 32, 0.0, 0.0, n_layers=1),
+          "modality_adapter": {{"_target_": "speech_b200.speechlm.perception.IdentityConnector", "d_model": 176}}}}
+    tok = ByteLevelTokenizer(special_tokens=["<pad>", "<s>", "</s>", "<|im_start|>", "<|im_end|>"])
+    def make():
+        cfg = OmegaConf.create({{"audio_locator_tag": "<|audioplaceholder|>", "prompt_format": "qwen", "llm": TINY, "perception": pc,
+                                "freeze_params": [], "prevent_freeze_params": [],
+                                "train_ds": {{"synthetic": {{"num_samples": 16, "seed": 5, "min_duration": 0.3, "max_duration": 0.6}}, "batch_size": 2}},
+                                "optim": {{"name": "fully_sharded_adamw", "lr": 1e-2, "weight_decay": 0.0}}}})
+        torch.manual_seed(0)
+        return SALMAutomodel(cfg, tokenizer=tok)
+    ckpt = {ckpt!r}
+    # run A: 4 steps in one go.  run B: 2 steps, checkpoint, fresh objects, 2 more steps from the checkpoint.
+    def trainer(steps):
+        return Trainer(max_steps=steps, accelerator="cpu", strategy=ParallelStrategy(dp_shard_size=2, tp_size=2), gradient_clip_val=0.5,
+                       log_every_n_steps=1, enable_checkpointing=False, logger=False)
+    ta = trainer(4); ma = make(); ta.fit(ma)
+    rank = dist.get_rank()
+    assert type(ta.grad_sync).__name__ == "FSDP2GradSync" and ma._dp_size == 2 and ta.global_step == 4
+    assert len(ma._train_dl.ds) == 16 and ma._train_dl.world == 2                       # sharded over dp, not over all 4 ranks
+    tb = trainer(2); mb = make(); tb.fit(mb)
+    tb.save_checkpoint(ckpt)
+    tc = trainer(4); mc = make(); tc.fit(mc, ckpt_path=ckpt)
+    assert tc.global_step == 4
+    fa, fc = ma._optimizer.gather_full_state(), mc._optimizer.gather_full_state()
+    worst = max(float((fa[id(pa)] - fc[id(pc_)]).abs().max()) for pa, pc_ in zip(ma.parameters(), mc.parameters()))
+    assert worst < 1e-5, worst
+    print("RESULT ok", rank, worst)
+    dist.destroy_process_group()
+""")
+
+
+def test_trainer_with_parallel_strategy_trains_salm_on_a_mesh_and_resumes_four_ranks(tmp_path):
+    """Trainer(strategy=ParallelStrategy(dp_shard 2 x tp 2)) drives SALMAutomodel with the fully-sharded optimizer; a run that is
+    check-pointed after two steps and resumed in fresh objects ends with the same parameters as the uninterrupted run."""
+    script = tmp_path / "salm_trainer.py"
+    script.write_text(SALM_TRAINER_SCRIPT.format(repo=REPO, ckpt=str(tmp_path / "step2.ckpt")))
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+                          "--master-addr", "127.0.0.1", "--master-port", "29773", str(script)],
+                         capture_output=True, text=True, timeout=900, env=dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2"))
+    assert out.returncode == 0, out.stderr[-4000:]
+    assert out.stdout.count("RESULT ok") == 4
