@@ -459,3 +459,47 @@ def test_duplex_stt_streaming_engine_prompts_turn_taking_and_chunked_feeding():
     for k in range(0, 16000, 4000):
         n += eng.feed(s2, audio[:, k:k + 4000])["tokens"].shape[1]
     assert n == s2.t == s2.frames_done and abs(n - plain["tokens"].shape[1]) <= 1
+
+
+def test_speechlm_metrics_turn_taking_mcq_empty_text_and_results_logger(tmp_path):
+    import json
+    from speech_b200.speechlm.metrics import (EmptyTextMetric, MCQEvaluator, ResultsLogger, TurnTakingMetrics, compute_turn_taking_metrics,
+                                              extract_answer)
+
+    EOS, BOS, PAD = 2, 1, 0
+    src = torch.full((4, 40), PAD); prd = torch.full((4, 40), PAD)
+    src[0, 10] = EOS; prd[0, 15] = BOS           # 5 frames late: success, 0.4 s
+    src[1, 10] = EOS; prd[1, 30] = BOS           # 20 frames late: failure
+    src[2, 10] = EOS                             # agent never starts: failure
+    prd[3, 5] = BOS                              # user never ends: not counted
+    acc, lat = compute_turn_taking_metrics(src, prd, EOS, BOS, tolerance=13, latency_multiplier=0.08)
+    assert abs(acc - 1 / 3) < 1e-9 and abs(lat - 0.4) < 1e-9
+    tt = TurnTakingMetrics(EOS, BOS)
+    tt.update("dev", src, prd); tt.update("dev", src[:1], prd[:1])
+    out = tt.compute()
+    assert abs(float(out["turn_taking_acc_dev"]) - (1 / 3 + 1) / 2) < 1e-6 and tt.compute() == {}
+    cases = {"The answer is B.": "B", "I would choose option (c) because ...": "C", "**D** since the speaker says so": "D", "a": "A",
+             "<2> The correct answer is: **A) cats**": "A", "B) the second one": "B", "答案是C": "C", "(d)": "D", "Hard to say, none fits": None, "": None,
+             "Looking at the options, (b) is the best answer": "B"}
+    for text, want in cases.items():
+        assert extract_answer(text) == want, (text, extract_answer(text))
+    (tmp_path / "man").mkdir()
+    with open(tmp_path / "man" / "quiz.jsonl", "w") as f:
+        for i, a in enumerate("ABCD"):
+            f.write(json.dumps({"id": f"q{i}", "answer": a}) + "\n")
+    ev = MCQEvaluator(str(tmp_path / "man"))
+    res = ev.evaluate("quiz", [{"id": "q0", "pred_text": "The answer is A"}, {"id": "q1", "pred_text": "I would pick c"},
+                               {"id": "q2", "pred_text": "no idea"}, {"id": "zz", "pred_text": "A"}])
+    assert res == {"mcq_acc": 1 / 3, "mcq_answered": 2 / 3, "mcq_total": 3.0}
+    em = EmptyTextMetric(); em.update("dev", ["hi", " ", ""]); assert abs(float(em.compute()["empty_text_rate_dev"]) - 2 / 3) < 1e-6
+    # two "ranks" write, rank 0 merges (duplicate id from sampler padding is dropped)
+    r1 = ResultsLogger(str(tmp_path / "res"), rank=1, world_size=2)
+    r1.update("quiz", ["q2", "q0"], ["no idea", "The answer is A"], ["c", "a"])
+    r1.reset()
+    r0 = ResultsLogger(str(tmp_path / "res"), rank=0, world_size=1, mcq_evaluator=ev)
+    r0.world = 2
+    r0.update("quiz", ["q0", "q1"], ["The answer is A", "i would pick c"], ["a", "b"])
+    m = r0.compute_and_save(["quiz"])
+    merged = [json.loads(l) for l in open(tmp_path / "res" / "quiz.jsonl")]
+    assert [r["id"] for r in merged] == ["q0", "q1", "q2"] and m["quiz/num_samples"] == 3.0 and m["quiz/mcq_acc"] == 1 / 3
+    assert m["quiz/wer"] > 1.0 and m["quiz/empty_text_rate"] == 0.0 and (tmp_path / "res" / "metrics.json").exists()
