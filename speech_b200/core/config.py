@@ -687,6 +687,13 @@ def hydra_runner(config_path: Optional[str] = ".", config_name: Optional[str] = 
     named by ``--config-path`` / ``--config-name`` (or the decorator defaults) is loaded,
     ``key=value`` overrides from ``sys.argv`` are applied, the working directory is left
     unchanged and no ``.hydra`` output directory is written.
+
+    ``-m`` / ``--multirun`` turns comma-separated override values into a sweep (``lr=1e-3,1e-4 model.size=small,large`` is four
+    jobs, Cartesian product, first key slowest).  Jobs run one after the other in this process by default; with
+    ``hydra.launcher.n_jobs=N`` (or ``hydra/launcher=processes``) each job is a child process running the same script with
+    its own overrides, at most N at a time, each pinned to one GPU of ``hydra.launcher.gpus=[0,1,...]`` when given
+    (the reference's process launcher, ``core/utils/process_launcher/launcher.py``).  The wrapper then returns the list of
+    results (task return values, or ``(overrides, return code, log path)`` for child processes).
     """
 
     def decorator(task_function: Callable[[DictConfig], Any]):
@@ -696,10 +703,14 @@ def hydra_runner(config_path: Optional[str] = ".", config_name: Optional[str] = 
                 return task_function(cfg_passthrough)
             args = list(sys.argv[1:] if argv is None else argv)
             cpath, cname, overrides = config_path, config_name, []
+            multirun = False
             i = 0
             while i < len(args):
                 a = args[i]
-                if a in ("--config-path", "-cp"):
+                if a in ("-m", "--multirun"):
+                    multirun = True
+                    i += 1
+                elif a in ("--config-path", "-cp"):
                     cpath = args[i + 1]
                     i += 2
                 elif a.startswith("--config-path="):
@@ -726,12 +737,69 @@ def hydra_runner(config_path: Optional[str] = ".", config_name: Optional[str] = 
                     base = cand if os.path.isdir(cand) else base
                 fname = cname if cname.endswith((".yaml", ".yml")) else cname + ".yaml"
                 cfg = OmegaConf.merge(cfg, OmegaConf.load(os.path.join(base, fname)))
+            if multirun:
+                launcher = {o.split("=", 1)[0]: o.split("=", 1)[1] for o in overrides if o.startswith(("hydra.launcher.", "hydra/launcher="))}
+                overrides = [o for o in overrides if not o.startswith(("hydra.launcher.", "hydra/launcher="))]
+                jobs = expand_multirun_overrides(overrides)
+                n_jobs = int(launcher.get("hydra.launcher.n_jobs", 0) or 0)
+                if n_jobs > 0 or launcher.get("hydra/launcher") == "processes":
+                    from ..utils.extras import ProcessLauncher
+
+                    gpus = launcher.get("hydra.launcher.gpus")
+                    gpu_ids = [int(g) for g in gpus.strip("[]").split(",") if g.strip()] if gpus else None
+                    mod = sys.modules.get(task_function.__module__)
+                    script = os.path.abspath(getattr(mod, "__file__", sys.argv[0]))
+                    base_cmd = [sys.executable, script] + ([f"--config-path={cpath}"] if cpath else []) + ([f"--config-name={cname}"] if cname else [])
+                    pl = ProcessLauncher(base_cmd, gpu_ids=gpu_ids, max_parallel=n_jobs or None,
+                                         log_dir=launcher.get("hydra.launcher.log_dir", "multirun"))
+                    return pl.launch(jobs)
+                results = []
+                for job in jobs:
+                    c = OmegaConf.create(to_container(cfg, resolve=False))
+                    apply_overrides(c, job)
+                    results.append(task_function(c))
+                return results
             apply_overrides(cfg, overrides)
             return task_function(cfg)
 
         return wrapper
 
     return decorator
+
+
+def expand_multirun_overrides(overrides: Sequence[str]) -> List[List[str]]:
+    """``["lr=1e-3,1e-4", "size=small", "aug=[a,b],[c]"]`` -> one override list per job.  Commas inside brackets, braces,
+    parentheses or quotes do not split; the first swept key varies slowest."""
+    def split_top(v: str) -> List[str]:
+        parts, depth, cur, quote = [], 0, "", None
+        for ch in v:
+            if quote:
+                cur += ch
+                if ch == quote:
+                    quote = None
+                continue
+            if ch in "\"'":
+                quote = ch
+            elif ch in "[{(":
+                depth += 1
+            elif ch in "]})":
+                depth -= 1
+            if ch == "," and depth == 0:
+                parts.append(cur)
+                cur = ""
+            else:
+                cur += ch
+        return parts + [cur]
+
+    jobs: List[List[str]] = [[]]
+    for o in overrides:
+        if "=" not in o:
+            jobs = [j + [o] for j in jobs]
+            continue
+        k, v = o.split("=", 1)
+        vals = split_top(v)
+        jobs = [j + [f"{k}={x}"] for j in jobs for x in vals]
+    return jobs
 
 
 def cfg_get(cfg: Any, key: str, default: Any = None) -> Any:

@@ -390,3 +390,100 @@ class ShardedCheckpointIO:
             idx = json.load(f)
         return [torch.load(os.path.join(directory, f"shard_{r}.pt"), map_location="cpu", weights_only=False)
                 for r in range(idx["world_size"])]
+
+
+# ------------------------------------------------------------------------------------------------ model utilities
+def wrap_training_step(fn):
+    """Decorator for ``training_step``: a ``'log'`` entry in the returned dictionary (the older way of reporting step metrics)
+    is taken out and sent through ``self.log_dict`` (reference ``utils/model_utils.py:470-478``)."""
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(self, *args, **kwargs):
+        out = fn(self, *args, **kwargs)
+        if isinstance(out, dict) and "log" in out:
+            self.log_dict(out.pop("log"))
+        return out
+    return wrapper
+
+
+def uninject_model_parallel_rank(filepath: str) -> str:
+    """Inverse of :func:`inject_model_parallel_rank`: ``dir/mp_rank_01/x.ckpt`` -> ``dir/x.ckpt``."""
+    filepath = str(filepath)
+    parent = os.path.basename(os.path.dirname(filepath))
+    if any(tag in parent for tag in ("mp_rank", "tp_rank", "fsdp_shard")):
+        return os.path.join(os.path.dirname(os.path.dirname(filepath)), os.path.basename(filepath))
+    return filepath
+
+
+def ckpt_to_dir(filepath: str) -> str:
+    """Directory that holds a sharded checkpoint named like the file: ``a/b/step=10.ckpt`` -> ``a/b/step=10``."""
+    filepath = str(filepath)
+    return filepath[: -len(".ckpt")] if filepath.endswith(".ckpt") else filepath
+
+
+def import_class_by_path(path: str):
+    """``"package.module.Class"`` -> the class object."""
+    import importlib
+
+    mod, _, name = path.rpartition(".")
+    return getattr(importlib.import_module(mod), name)
+
+
+def resolve_subclass_pretrained_model_info(base_class) -> List[Any]:
+    """Pretrained-model records of ``base_class`` and of every subclass that has been imported, each tagged with its class,
+    sorted and without duplicates."""
+    seen, out = set(), []
+
+    def walk(cls):
+        for sub in cls.__subclasses__():
+            walk(sub)
+        lst = getattr(cls, "list_available_models", None)
+        for info in (lst() or []) if lst is not None else []:
+            if getattr(info, "class_", None) is None:
+                info.class_ = cls
+            key = (getattr(info, "pretrained_model_name", repr(info)), info.class_.__name__)
+            if key not in seen:
+                seen.add(key)
+                out.append(info)
+    walk(base_class)
+    return sorted(out, key=lambda i: (getattr(i, "pretrained_model_name", ""), i.class_.__name__))
+
+
+def param_is_not_shared(param) -> bool:
+    return not getattr(param, "shared", False)
+
+
+def unwrap_model(model, module_instances: Optional[Tuple[type, ...]] = None):
+    """Strip wrapper modules (anything with a ``.module`` attribute of the given types, or any wrapper when no types are given);
+    lists are unwrapped element-wise."""
+    if isinstance(model, (list, tuple)):
+        return type(model)(unwrap_model(m, module_instances) for m in model)
+    while hasattr(model, "module") and (module_instances is None or isinstance(model, module_instances)):
+        model = model.module
+    return model
+
+
+def parse_dataset_as_name(name: str) -> str:
+    """Log prefix of a validation / test set from its manifest path: base name without extension, ``manifest`` and separators
+    stripped (``/data/dev_other_manifest.json`` -> ``dev_other``)."""
+    base = os.path.splitext(os.path.basename(str(name).rstrip("/")))[0] if os.path.splitext(str(name))[1] else os.path.basename(str(name).rstrip("/"))
+    base = base.replace("-", "_")
+    for junk in ("manifest", "dataset"):
+        base = base.replace(junk, "")
+    base = "_".join(p for p in base.split("_") if p)
+    return base or "dataset"
+
+
+def unique_names_check(name_list: Optional[List[str]]) -> None:
+    """Warn when two validation / test sets would log under the same prefix (their metrics would overwrite each other)."""
+    if not name_list:
+        return
+    seen: Dict[str, int] = {}
+    for n in name_list:
+        seen[n] = seen.get(n, 0) + 1
+    dup = [n for n, c in seen.items() if c > 1]
+    if dup:
+        from .logging import logging
+
+        logging.warning(f"dataset names are not unique, metrics will collide: {dup}")

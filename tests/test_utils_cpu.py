@@ -326,3 +326,53 @@ def test_sharded_checkpoint_io_precision_timing_launcher_telemetry_punctuation(t
     per = punctuation_error_rate(["hello, world how are you."], ["hello world, how are you?"])
     assert per[","]["insertions"] == 1 and per[","]["deletions"] == 1 and per["?"]["substitutions"] == 1 and per["overall"]["correct"] == 0
     assert punctuation_error_rate(["yes, it is."], ["yes, it is."])["overall"]["per"] == 0.0
+
+
+def test_multirun_sweeps_and_model_utilities(tmp_path):
+    import sys
+    from speech_b200.core.config import OmegaConf, expand_multirun_overrides, hydra_runner
+    from speech_b200.utils import misc
+
+    assert expand_multirun_overrides(["lr=1e-3,1e-4", "size=small", "aug=[a,b],[c]"]) == [
+        ["lr=1e-3", "size=small", "aug=[a,b]"], ["lr=1e-3", "size=small", "aug=[c]"],
+        ["lr=1e-4", "size=small", "aug=[a,b]"], ["lr=1e-4", "size=small", "aug=[c]"]]
+    (tmp_path / "c.yaml").write_text("lr: 0.1\nsize: tiny\nnested: {k: 1}\n")
+
+    @hydra_runner(config_path=str(tmp_path), config_name="c")
+    def main(cfg):
+        return (cfg.lr, cfg.size, cfg.nested.k)
+
+    assert main(argv=["lr=0.5"]) == (0.5, "tiny", 1)
+    assert main(argv=["-m", "lr=0.5,0.25", "nested.k=7,8"]) == [(0.5, "tiny", 7), (0.5, "tiny", 8), (0.25, "tiny", 7), (0.25, "tiny", 8)]
+    # child-process launcher: the same script is started once per job
+    script = tmp_path / "job.py"
+    script.write_text(
+        "import sys\nsys.path.insert(0, %r)\nfrom speech_b200.core.config import hydra_runner\n"
+        "@hydra_runner(config_path=%r, config_name='c')\ndef main(cfg):\n    print('JOB', cfg.lr, cfg.size)\n"
+        "if __name__ == '__main__':\n    r = main()\n    print('RESULTS', r)\n" % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))), str(tmp_path)))
+    import subprocess
+    out = subprocess.run([sys.executable, str(script), "-m", "lr=1,2", "size=a", "hydra.launcher.n_jobs=2", f"hydra.launcher.log_dir={tmp_path / 'mr'}"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    logs = sorted((tmp_path / "mr").glob("job_*.log"))
+    assert len(logs) == 2 and "JOB 1 a" in logs[0].read_text() and "JOB 2 a" in logs[1].read_text()
+
+    class M:
+        logged = None
+        def log_dict(self, d): self.logged = d
+        @misc.wrap_training_step
+        def training_step(self, batch): return {"loss": 1.0, "log": {"lr": 0.1}}
+    m = M()
+    assert m.training_step(None) == {"loss": 1.0} and m.logged == {"lr": 0.1}
+    assert misc.uninject_model_parallel_rank("/a/mp_rank_01/x.ckpt") == "/a/x.ckpt" and misc.uninject_model_parallel_rank("/a/b/x.ckpt") == "/a/b/x.ckpt"
+    assert misc.ckpt_to_dir("a/step=10.ckpt") == "a/step=10"
+    assert misc.import_class_by_path("collections.OrderedDict").__name__ == "OrderedDict"
+    assert misc.parse_dataset_as_name("/data/dev-other_manifest.json") == "dev_other" and misc.parse_dataset_as_name("manifest.json") == "dataset"
+    class W:
+        def __init__(self, m): self.module = m
+    core = object()
+    assert misc.unwrap_model(W(W(core))) is core and misc.unwrap_model([W(core)]) == [core]
+    from speech_b200.core.modelpt import ModelPT
+    from speech_b200 import models  # noqa: F401  (imports the model classes)
+    infos = misc.resolve_subclass_pretrained_model_info(ModelPT)
+    assert isinstance(infos, list)
