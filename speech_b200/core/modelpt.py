@@ -466,6 +466,13 @@ class ModelPT(nn.Module, Typing, Serialization):
             if sched_cfg is not None else None
         return self._optimizer, self._scheduler
 
+    def load_state_dict(self, state_dict, strict: bool = True, **kw):
+        """Adapters listed in ``cfg.adapters`` are rebuilt before the weights are loaded, so a check-point written with adapters
+        restores into a freshly constructed model."""
+        if hasattr(self, "restore_adapters_from_cfg"):
+            self.restore_adapters_from_cfg()
+        return super().load_state_dict(state_dict, strict=strict, **kw)
+
     def _sharded_optimizer_kwargs(self) -> Dict[str, Any]:
         """Extra arguments of the fully-sharded optimizer (``group``, ``replicate_group``, ``units``); models that live on a
         device mesh override this."""

@@ -209,8 +209,14 @@ class AdapterModuleMixin:
         if name in self.adapter_layer:
             raise ValueError(f"Adapter with name `{name}` already exists")
         plain = to_container(cfg, resolve=True) if isinstance(cfg, DictConfig) else dict(cfg)
-        plain.pop("adapter_strategy", None)
-        if "_target_" in plain:
+        from .adapters import ADAPTER_CLASSES, build_strategy
+
+        strategy_cfg = plain.pop("adapter_strategy", None)
+        short = str(plain.get("_target_", "")).rsplit(".", 1)[-1]
+        if short in ADAPTER_CLASSES:
+            kw = {k: v for k, v in plain.items() if k != "_target_"}
+            module = ADAPTER_CLASSES[short](adapter_strategy=strategy_cfg, **kw)
+        elif "_target_" in plain:
             from .instantiate import TARGET_ALIASES
 
             TARGET_ALIASES.setdefault("nemo.collections.common.parts.adapter_modules.LinearAdapter",
@@ -218,6 +224,9 @@ class AdapterModuleMixin:
             module = _from_config_dict(plain)
         else:
             module = LinearAdapter(**plain)
+        if not hasattr(module, "adapter_strategy"):
+            module.adapter_strategy = build_strategy(strategy_cfg)
+        plain = {**plain, **({"adapter_strategy": strategy_cfg} if strategy_cfg is not None else {})}
         dev = next((p.device for p in self.parameters()), None) if isinstance(self, nn.Module) else None
         if dev is not None:
             module = module.to(dev)
@@ -246,6 +255,9 @@ class AdapterModuleMixin:
             self.adapter_layer[k].train()
 
     def forward_enabled_adapters(self, x: torch.Tensor) -> torch.Tensor:
+        """Apply the enabled adapters in the order they were added, each merged by its strategy (residual add by default)."""
         for k in self.get_enabled_adapters():
-            x = x + self.adapter_layer[k](x)
+            ad = self.adapter_layer[k]
+            strategy = getattr(ad, "adapter_strategy", None)
+            x = strategy(x, ad, module=self) if strategy is not None else x + ad(x)
         return x

@@ -279,7 +279,10 @@ class InterCTCMixin:
         return total, metrics
 
 
-class ASRModuleMixin:
+from ..core.adapters import ASRAdapterModelMixin  # noqa: E402
+
+
+class ASRModuleMixin(ASRAdapterModelMixin):
     def change_attention_model(self, self_attention_model: str = None, att_context_size: List[int] = None,
                                update_config: bool = True):
         if not hasattr(self, "encoder") or not hasattr(self.encoder, "change_attention_model"):

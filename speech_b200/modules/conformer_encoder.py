@@ -287,6 +287,36 @@ class ConformerEncoder(NeuralModule, AccessMixin):
             encoded_len = torch.clamp(encoded_len, max=self.streaming_cfg.valid_out_len)
         return encoded, encoded_len, clc, clt, clcl
 
+    # ------------------------------------------------------------------ adapters (every layer hosts a copy)
+    def add_adapter(self, name: str, cfg) -> None:
+        for layer in self.layers:
+            layer.add_adapter(name, cfg)
+
+    def is_adapter_available(self) -> bool:
+        return any(layer.is_adapter_available() for layer in self.layers)
+
+    def set_enabled_adapters(self, name=None, enabled: bool = True) -> None:
+        for layer in self.layers:
+            if layer.is_adapter_available():
+                layer.set_enabled_adapters(name, enabled)
+
+    def get_enabled_adapters(self):
+        names = []
+        for layer in self.layers:
+            for n in layer.get_enabled_adapters():
+                if n not in names:
+                    names.append(n)
+        return names
+
+    def unfreeze_enabled_adapters(self, freeze_batchnorm: bool = True) -> None:
+        for layer in self.layers:
+            if layer.is_adapter_available():
+                layer.unfreeze_enabled_adapters(freeze_batchnorm)
+
+    @property
+    def adapter_cfg(self):
+        return getattr(self.layers[0], "adapter_cfg", {}) if len(self.layers) else {}
+
     @typecheck()
     def forward(self, audio_signal, length, cache_last_channel=None, cache_last_time=None, cache_last_channel_len=None,
                 bypass_pre_encode=False):

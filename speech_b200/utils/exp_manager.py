@@ -411,6 +411,12 @@ def exp_manager(trainer, cfg: Optional[Union[DictConfig, Dict]] = None) -> Optio
     schema = OmegaConf.structured(ExpManagerConfig)
     if isinstance(cfg, dict):
         cfg = OmegaConf.create(cfg)
+    else:
+        # interpolations such as ``name: ${name}`` point into the tree this block came from: resolve them there, before the
+        # block becomes a tree of its own
+        from ..core.config import to_container
+
+        cfg = OmegaConf.create(to_container(cfg, resolve=True))
     unknown = [k for k in cfg.keys() if k not in schema]
     if unknown:
         raise ValueError(f"Unknown exp_manager config keys: {unknown}")

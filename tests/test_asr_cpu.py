@@ -306,3 +306,74 @@ def test_subsampling_conv_chunking_by_batch_and_by_time_equals_unsplit():
         for b in range(3):
             n = int(ref_len[b])
             assert torch.allclose(by_time[b, :n], ref[b, :n], atol=1e-5), (kind, b, (by_time[b, :n] - ref[b, :n]).abs().max())
+
+
+def test_model_level_adapters_strategies_save_load_and_restore(tmp_path):
+    import torch
+    from speech_b200.core.adapters import (MultiHeadAttentionAdapter, PositionalEncodingAdapter, RelPositionMultiHeadAttentionAdapter,
+                                          ResidualAddAdapterStrategy, adapter_auxiliary_loss)
+    from speech_b200.models import EncDecCTCModelBPE
+    from speech_b200.models.configs import fastconformer_ctc_config
+
+    torch.manual_seed(0)
+    m = EncDecCTCModelBPE(fastconformer_ctc_config("small", vocab_size=16, dropout=0.0, n_layers=2, lr=1e-3))
+    audio, lens = torch.randn(2, 8000), torch.tensor([8000, 6000])
+    m.eval()
+    base = m.forward(input_signal=audio, input_signal_length=lens)[0]
+    m.add_adapter("lin", {"in_features": 176, "dim": 8, "adapter_strategy": {"_target_": "ResidualAddAdapterStrategy", "l2_lambda": 0.1}})
+    m.add_adapter("encoder:att", {"_target_": "speech_b200.core.adapters.RelPositionMultiHeadAttentionAdapter", "n_head": 4, "n_feat": 176})
+    m.add_adapter("decoder:dec", {"in_features": 176, "dim": 4})
+    assert m.get_enabled_adapters() == ["encoder:lin", "encoder:att", "decoder:dec"] and set(m.cfg.adapters.keys()) == {"encoder:lin", "encoder:att", "decoder:dec"}
+    # zero-initialised outputs: adding adapters does not change the model
+    assert torch.allclose(m.forward(input_signal=audio, input_signal_length=lens)[0], base, atol=1e-5)
+    n_train = m.freeze_base_and_train_adapters()
+    assert 0 < n_train < 0.3 * sum(p.numel() for p in m.parameters())
+    assert all(("adapter_layer" in n) == p.requires_grad for n, p in m.named_parameters())
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "adapter_layer" in n:
+                p.add_(0.05 * torch.randn_like(p))
+    m.train()
+    out = m.forward(input_signal=audio, input_signal_length=lens)[0]
+    aux = adapter_auxiliary_loss(m)
+    assert aux is not None and float(aux) > 0 and adapter_auxiliary_loss(m) is None
+    (out.float().pow(2).mean() + aux).backward()
+    assert m.encoder.layers[0].adapter_layer["lin"].module[1].weight.grad is not None
+    m.eval()
+    with_ad = m.forward(input_signal=audio, input_signal_length=lens)[0]
+    m.set_enabled_adapters(enabled=False)
+    base = m.forward(input_signal=audio, input_signal_length=lens)[0]        # the training pass above moved the BatchNorm statistics
+    assert m.get_enabled_adapters() == [] and not torch.allclose(with_ad, base, atol=1e-4)
+    m.set_enabled_adapters("encoder:lin", True)
+    only_lin = m.forward(input_signal=audio, input_signal_length=lens)[0]
+    m.set_enabled_adapters(enabled=True)
+    # adapters alone: save, load into a fresh base model
+    m.save_adapters(str(tmp_path / "ad.pt"))
+    m.save_adapters(str(tmp_path / "lin.pt"), name="lin")
+    assert (tmp_path / "ad.pt").stat().st_size < 0.5 * sum(p.numel() * 4 for p in m.parameters())
+    torch.manual_seed(0)
+    fresh = EncDecCTCModelBPE(fastconformer_ctc_config("small", vocab_size=16, dropout=0.0, n_layers=2, lr=1e-3)).eval()
+    base_sd = {k: v for k, v in m.state_dict().items() if "adapter_layer" not in k}     # same base model (BatchNorm statistics included)
+    fresh.load_state_dict(base_sd, strict=False)
+    fresh.load_adapters(str(tmp_path / "ad.pt"))
+    assert torch.allclose(fresh.forward(input_signal=audio, input_signal_length=lens)[0], with_ad, atol=1e-5)
+    torch.manual_seed(0)
+    fresh2 = EncDecCTCModelBPE(fastconformer_ctc_config("small", vocab_size=16, dropout=0.0, n_layers=2, lr=1e-3)).eval()
+    fresh2.load_state_dict(base_sd, strict=False)
+    fresh2.load_adapters(str(tmp_path / "lin.pt"), name="lin")
+    assert fresh2.get_enabled_adapters() == ["encoder:lin"] and torch.allclose(fresh2.forward(input_signal=audio, input_signal_length=lens)[0], only_lin, atol=1e-5)
+    # whole model with adapters through .nemo
+    m.save_to(str(tmp_path / "m.nemo"))
+    back = EncDecCTCModelBPE.restore_from(str(tmp_path / "m.nemo")).eval()
+    assert back.get_enabled_adapters() == m.get_enabled_adapters()
+    assert torch.allclose(back.forward(input_signal=audio, input_signal_length=lens)[0], with_ad, atol=1e-5)
+    # stand-alone modules and the stochastic-depth strategy
+    x = torch.randn(2, 9, 32)
+    for ad in (MultiHeadAttentionAdapter(4, 32), RelPositionMultiHeadAttentionAdapter(4, 32, max_rel=3)):
+        assert float(ad(x).abs().max()) == 0.0          # zero-initialised output projection
+    assert torch.equal(PositionalEncodingAdapter(32, max_len=16)(x), x)
+    host = torch.nn.Linear(1, 1).train()
+    st = ResidualAddAdapterStrategy(stochastic_depth=1.0)
+    assert torch.equal(st(x, torch.nn.Linear(32, 32), module=host), x)
+    with pytest.raises(ValueError, match="not one of"):
+        m.add_adapter("vocoder:x", {"in_features": 176, "dim": 4})

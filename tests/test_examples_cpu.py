@@ -48,3 +48,42 @@ def test_train_transcribe_and_stream_examples(tmp_path):
         f"output_filename={tmp_path / 'stream.json'}", "streaming.batch_size=2", "streaming.chunk_size=0.4",
         "streaming.left_padding_size=0.4", "streaming.right_padding_size=0.2"], str(tmp_path))
     assert "RTFx" in log and len(open(tmp_path / "stream.json").read().splitlines()) == 3
+
+
+def test_adapter_training_and_evaluation_examples(tmp_path):
+    """Base model from the CTC example, then the adapter recipe: only the adapter trains, it is saved alone and with the model, and
+    the evaluation script reports WER with and without it."""
+    import torch
+    from speech_b200.data.audio_to_text import save_wav
+
+    g = np.random.default_rng(0)
+    man = tmp_path / "train.json"
+    with open(man, "w") as f:
+        for i in range(4):
+            p = str(tmp_path / f"a{i}.wav")
+            save_wav(p, (0.1 * g.standard_normal(16000)).astype(np.float32))
+            f.write(json.dumps({"audio_filepath": p, "duration": 1.0, "text": "w1 w2 w3"}) + "\n")
+    exp = tmp_path / "exp"
+    _run("examples/asr/asr_ctc/speech_to_text_ctc_bpe.py", [
+        "model.tokenizer.type=synthetic", "+model.tokenizer.vocab_size=32", "model.tokenizer.dir=null",
+        "+model.train_ds.synthetic={num_samples: 4, vocab_size: 32, min_duration: 1.0, max_duration: 1.2}",
+        "model.train_ds.manifest_filepath=null", "model.validation_ds.manifest_filepath=null", "model.train_ds.batch_size=4",
+        "model.train_ds.num_workers=0", "model.encoder.n_layers=1", "model.encoder.d_model=64", "model.encoder.n_heads=4",
+        "trainer.max_steps=1", "trainer.max_epochs=null", "trainer.accelerator=cpu", "trainer.devices=1", "trainer.precision=32",
+        "trainer.strategy=auto", f"exp_manager.exp_dir={exp}", "exp_manager.create_tensorboard_logger=false"], str(tmp_path))
+    base = glob.glob(str(exp / "**" / "*.nemo"), recursive=True)[0]
+    out = tmp_path / "adapt"
+    _run("examples/asr/asr_adapters/train_asr_adapter.py", [
+        f"model.nemo_model={base}", f"model.train_ds.manifest_filepath={man}", "model.train_ds.batch_size=2", "model.train_ds.max_duration=5.0",
+        "model.adapter.adapter_name=encoder:domain", "model.adapter.d_model=64", "model.adapter.linear.dim=4", "model.optim.sched=null",
+        "trainer.max_steps=2", "trainer.accelerator=cpu", "trainer.precision=32", f"exp_manager.exp_dir={out}",
+        "+exp_manager.create_tensorboard_logger=false"], str(tmp_path))
+    ad = glob.glob(str(out / "**" / "adapters.pt"), recursive=True)
+    adapted = glob.glob(str(out / "**" / "ASR-Adapter.nemo"), recursive=True)
+    assert ad and adapted
+    blob = torch.load(ad[0], weights_only=False)
+    assert list(blob["__cfg__"]) == ["encoder:domain"] and all("adapter_layer.domain" in k for k in blob["state_dict"])
+    log = _run("examples/asr/asr_adapters/eval_asr_adapter.py", [f"model_path={adapted[0]}", f"manifest={man}", "adapter_name=encoder:domain", "batch_size=2"],
+               str(tmp_path))
+    res = json.loads([l for l in log.splitlines() if l.startswith("{")][-1])
+    assert res["enabled_adapters"] == ["encoder:domain"] and "wer_with_adapter" in res and "wer_without_adapters" in res
