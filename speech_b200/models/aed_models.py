@@ -145,6 +145,32 @@ class EncDecMultiTaskModel(ASRModel, ASRBPEMixin, ASRModuleMixin, TranscriptionM
         self.use_loss_mask_for_prompt = cfg.get("use_loss_mask_for_prompt", False)
         self._setup_decoding()
         self.wer = WER(decoding=self.decoding, log_prediction=cfg.get("log_prediction", False))
+        if self.__dict__.pop("_loaders_deferred", False):
+            self._setup_dataloaders_from_cfg()
+
+    def _setup_dataloader_from_config(self, config):
+        """Manifests / cut sources go through the prompted dataset: every utterance becomes ``prompt tokens + transcript + end
+        token`` under this model's prompt format, with the slot values (languages, task, punctuation ...) taken from the
+        manifest fields (``data/cuts_datasets.py``).  Synthetic data keeps the plain token dataset."""
+        if config is None:
+            return None
+        if cfg_get(config, "synthetic", None) is not None:
+            return super()._setup_dataloader_from_config(config)
+        if "prompt" not in self.__dict__:
+            self._loaders_deferred = True          # called from the base constructor, before the prompt formatter exists
+            return None
+        import os
+        from functools import partial
+
+        from ..data.cuts import get_dataloader_from_cuts_config
+        from ..data.cuts_datasets import PromptedAudioToTextCutsDataset
+
+        rank = self.global_rank if self._trainer is not None else int(os.environ.get("RANK", 0))
+        ws = self.world_size if self._trainer is not None else int(os.environ.get("WORLD_SIZE", 1))
+        defaults = cfg_get(config, "prompt_defaults", None)
+        defaults = to_container(defaults, resolve=True) if isinstance(defaults, DictConfig) else (defaults if isinstance(defaults, dict) else None)
+        ds_cls = partial(PromptedAudioToTextCutsDataset, prompt=self.prompt, prompt_defaults=defaults)
+        return get_dataloader_from_cuts_config(config, rank, ws, tokenizer=self.tokenizer, dataset_cls=ds_cls)
 
     def _setup_decoding(self):
         dcfg = self._cfg.get("decoding", None) or OmegaConf.structured(MultiTaskDecodingConfig)

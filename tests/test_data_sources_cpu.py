@@ -7,6 +7,7 @@ import tarfile
 
 import numpy as np
 import pytest
+import torch
 
 from speech_b200.data.audio_to_text import save_wav
 from speech_b200.data.cuts import get_dataloader_from_cuts_config, parse_input_cfg
@@ -208,3 +209,66 @@ def test_salm_loader_reads_a_mixture_of_sources(tmp_path):
     convs = conversations_from_input_cfg(cfg, seed=1)
     kinds = sorted(tuple(t["type"] for t in c["conversations"]) for c in convs)
     assert kinds == [("audio", "text"), ("text", "text")]
+
+
+def _canary_tokenizer():
+    from speech_b200.tokenizers import CANARY_SPECIAL_TOKENIZER, CanaryTokenizer, CharTokenizer
+
+    specials = ["<|nospeech|>", "<pad>", "<|endoftext|>", "<|startoftranscript|>", "<|pnc|>", "<|nopnc|>", "<|transcribe|>", "<|translate|>",
+                "<|en|>", "<|de|>"]
+    return CanaryTokenizer({CANARY_SPECIAL_TOKENIZER: CharTokenizer(specials), "en": CharTokenizer(list("abcdefghijklmnopqrstuvwxyz ")),
+                            "de": CharTokenizer(list("abcdefghijklmnopqrstuvwxyzäöü "))})
+
+
+def test_task_datasets_over_cuts_prompted_prompt_index_speaker_eou_diarization():
+    from functools import partial
+
+    from speech_b200.data.cuts import Cut
+    from speech_b200.data.cuts_datasets import (DiarLabelCutsDataset, EOUCutsDataset, PromptedAudioToTextCutsDataset, PromptedAudioToTextMiniBatch,
+                                                PromptIndexCutsDataset, SpeakerCutsDataset)
+    from speech_b200.prompts import PromptFormatter
+
+    tok = _canary_tokenizer()
+    rng = np.random.default_rng(0)
+    def wav(sec):
+        return (0.1 * rng.standard_normal(int(16000 * sec))).astype(np.float32)
+    cuts = [Cut("a", wav(0.5), 0.5, text="hallo welt", lang="de", custom={"source_lang": "en", "target_lang": "de", "pnc": "no"}),
+            Cut("b", wav(0.8), 0.8, text="good day", lang="en", custom={"speaker": "s2"})]
+    prompt = PromptFormatter.resolve("canary")(tokenizer=tok)
+    ds = PromptedAudioToTextCutsDataset(cuts, tokenizer=tok, prompt=prompt, return_minibatch=True)
+    mb = ds.collate_fn([ds[0], ds[1]])
+    assert isinstance(mb, PromptedAudioToTextMiniBatch) and mb.audio.shape == (2, 12800) and mb.audio_lens.tolist() == [8000, 12800]
+    sid = tok.spl_token_to_id
+    assert mb.prompt[0, : mb.prompt_lens[0]].tolist() == [sid("startoftranscript"), sid("en"), sid("translate"), sid("de"), sid("nopnc")]
+    assert mb.prompt[1, : mb.prompt_lens[1]].tolist() == [sid("startoftranscript"), sid("en"), sid("transcribe"), sid("en"), sid("pnc")]
+    n0 = int(mb.prompted_transcript_lens[0])
+    assert mb.prompted_transcript[0, n0 - 1] == sid("endoftext") and n0 == 5 + len("hallo welt") + 1
+    assert torch.equal(mb.prompted_transcript[0, :5], mb.prompt[0, :5]) and mb.transcript_lens.tolist() == [len("hallo welt") + 1, len("good day") + 1]
+    inp, out = mb.get_decoder_inputs_outputs()
+    assert torch.equal(inp[:, 1:], out[:, :-1]) and ds.num_tokens(1) == 5 + len("good day") + 1
+    tup = PromptedAudioToTextCutsDataset(cuts, tokenizer=tok, prompt=prompt).collate_fn([ds[0], ds[1]])
+    assert len(tup) == 6 and torch.equal(tup[2], mb.prompted_transcript) and torch.equal(tup[5], mb.prompt_lens)
+    # prompt index
+    pi = PromptIndexCutsDataset(cuts, tokenizer=tok, prompt_dictionary={"en": 0, "de": 1, "fr": 2}, prompt_field="target_lang")
+    b = pi.collate_fn([pi[0], pi[1]])
+    assert b[4].tolist() == [[0.0, 1.0, 0.0], [1.0, 0.0, 0.0]]
+    # speakers and activity
+    multi = Cut("m", wav(1.0), 1.0, text="x", lang="en", custom={"speaker": "s1", "supervisions": [
+        {"start": 0.0, "duration": 0.4, "speaker": "s1", "text": "x"}, {"start": 0.32, "duration": 0.4, "speaker": "s2", "text": "y"}]})
+    sp = SpeakerCutsDataset([multi, cuts[1]], tokenizer=tok, frame_shift=0.08, max_speakers=3)
+    b = sp.collate_fn([sp[0], sp[1]])
+    assert b[4].tolist() == [0, 1] and b[5].shape == (2, 13, 3)
+    assert b[5][0, :5, 0].tolist() == [1.0] * 5 and b[5][0, 4:9, 1].tolist() == [1.0] * 5 and float(b[5][0, :, 2].sum()) == 0.0
+    dd = DiarLabelCutsDataset([multi], tokenizer=None, frame_shift=0.08, max_speakers=2)
+    a, al, act, tl = dd.collate_fn([dd[0]])
+    assert act.shape == (1, 13, 2) and tl.tolist() == [13] and float(act[0, 4, :].sum()) == 2.0        # overlap frame
+    # end of utterance
+    eo = EOUCutsDataset([Cut("e", wav(1.0), 1.0, text="ab", lang="en", custom={"sou_time": 0.16, "eou_time": 0.8}),
+                         Cut("f", wav(1.0), 1.0, text="ab", lang="en", custom={"eou_time": 1.5, "is_backchannel": False})],
+                        tokenizer=tok, eou_id=999, frame_shift=0.08)
+    b = eo.collate_fn([eo[0], eo[1]])
+    assert b[2][0, : b[3][0]].tolist()[-1] == 999 and 999 not in b[2][1].tolist()                      # the second utterance is cut short
+    assert b[4][0].tolist() == [0, 0] + [1] * 8 + [2] * 3 and b[4][1].tolist() == [1] * 13
+    padded = EOUCutsDataset([Cut("e", wav(1.0), 1.0, text="ab", lang="en")], tokenizer=tok, eou_id=999, pad_min=0.2, pad_max=0.4, seed=1)
+    a, al, t, tl, lab = padded[0]
+    assert int(al) > 16000 and lab[0] == 0 and lab[-1] == 2 and int((lab == 1).sum()) in (12, 13)

@@ -87,3 +87,52 @@ def test_adapter_training_and_evaluation_examples(tmp_path):
                str(tmp_path))
     res = json.loads([l for l in log.splitlines() if l.startswith("{")][-1])
     assert res["enabled_adapters"] == ["encoder:domain"] and "wer_with_adapter" in res and "wer_without_adapters" in res
+
+
+def test_aed_trains_from_a_manifest_with_prompts_and_the_chunked_and_streaming_scripts_run(tmp_path):
+    import torch
+    from speech_b200.core.trainer import Trainer
+    from speech_b200.data.audio_to_text import save_wav
+    from speech_b200.models import EncDecMultiTaskModel
+    from speech_b200.models.configs import canary_aed_config
+
+    g = np.random.default_rng(0)
+    man = tmp_path / "train.json"
+    with open(man, "w") as f:
+        for i in range(4):
+            p = str(tmp_path / f"a{i}.wav")
+            save_wav(p, (0.1 * g.standard_normal(16000 + 4000 * i)).astype(np.float32))
+            f.write(json.dumps({"audio_filepath": p, "duration": 1.0 + 0.25 * i, "text": "ab cd", "lang": "en", "source_lang": "en",
+                                "target_lang": "de" if i % 2 else "en", "pnc": "no"}) + "\n")
+    specials = ["<|nospeech|>", "<pad>", "<|endoftext|>", "<|startoftranscript|>", "<|pnc|>", "<|nopnc|>", "<|transcribe|>", "<|translate|>",
+                "<|en|>", "<|de|>"]
+    letters = list("abcdefghijklmnopqrstuvwxyz ")
+    tok = {"type": "agg", "langs": {"spl_tokens": {"type": "char", "vocab": specials}, "en": {"type": "char", "vocab": letters},
+                                    "de": {"type": "char", "vocab": letters}}}
+    cfg = canary_aed_config("small", enc_layers=1, dec_layers=1, dec_hidden=64, dec_heads=4, dec_inner=128, vocab_size=64, features=32,
+                            dropout=0.0, max_sequence_length=128, tokenizer=tok)
+    from speech_b200.core.config import open_dict
+    with open_dict(cfg):
+        cfg.prompt_format = "canary"
+        cfg.train_ds = {"manifest_filepath": str(man), "batch_size": 2, "shuffle": False, "sample_rate": 16000}
+    m = EncDecMultiTaskModel(cfg)
+    batch = next(iter(m._train_dl))
+    assert len(batch) == 6 and batch[2].shape[0] == 2 and batch[5].tolist() == [5, 5]           # five prompt tokens per utterance
+    sid = m.tokenizer.spl_token_to_id
+    assert batch[4][1].tolist() == [sid("startoftranscript"), sid("en"), sid("translate"), sid("de"), sid("nopnc")]
+    tr = Trainer(max_steps=2, accelerator="cpu", enable_checkpointing=False, logger=False, log_every_n_steps=1)
+    tr.fit(m)
+    assert np.isfinite(float(tr.callback_metrics["train_loss"]))
+    nemo = str(tmp_path / "aed.nemo")
+    m.save_to(nemo)
+    out = tmp_path / "chunked.json"
+    _run("examples/asr/asr_chunked_inference/aed/speech_to_text_aed_chunked_infer.py",
+         [f"model_path={nemo}", f"dataset_manifest={man}", f"output_filename={out}", "chunk_len_in_secs=0.6", "batch_size=2"], str(tmp_path))
+    recs = [json.loads(l) for l in open(out)]
+    assert len(recs) == 4 and all("pred_text" in r for r in recs)
+    out2 = tmp_path / "stream.json"
+    _run("examples/asr/asr_chunked_inference/aed/speech_to_text_aed_streaming_infer.py",
+         [f"model_path={nemo}", f"dataset_manifest={man}", f"output_filename={out2}", "chunk_secs=0.4", "decoding.streaming_policy=alignatt",
+          "decoding.alignatt_thr=2"], str(tmp_path))
+    recs = [json.loads(l) for l in open(out2)]
+    assert len(recs) == 4 and all("average_lagging_s" in r for r in recs)
