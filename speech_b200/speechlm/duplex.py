@@ -243,13 +243,60 @@ class DuplexS2SModel(DuplexSTTModel):
 
 
 class SALMWithAsrDecoder(SALM):
-    """SALM with an auxiliary CTC head on the perception embeddings; the head's vocabulary is the LLM tokenizer's."""
+    """SALM that also reads the hypothesis of an ASR decoder.  With ``perception._target_`` =
+    ``AudioTranscriptionPerceptionModule`` (a complete ASR model inside the perception module) every audio placeholder is replaced
+    by ``audio embeddings + embeddings of ">> <hypothesis> <<"`` tokenised with the LLM's tokenizer, so the LLM can copy, correct
+    or ignore the recogniser's words; ``asr_transcript_drop_prob`` blanks the hypothesis of a training example now and then so the
+    model keeps listening (reference ``speechlm2/models/salm_asr_decoder.py:169-215``).  Independently of that, ``asr_weight`` > 0
+    with ``asr_tokens`` in the batch trains an auxiliary CTC head on the perception embeddings."""
 
     def __init__(self, cfg: DictConfig, trainer=None, llm=None, tokenizer=None):
         super().__init__(cfg, trainer=trainer, llm=llm, tokenizer=tokenizer)
         self.asr_weight = float(cfg_get(self._cfg, "asr_weight", 0.3))
         self.asr_vocab = int(cfg_get(self._cfg, "asr_vocab_size", self.embed_tokens.num_embeddings))
         self.asr_head = nn.Linear(self.llm.config.hidden_size, self.asr_vocab + 1)
+        self.asr_transcript_drop_prob = float(cfg_get(self._cfg, "asr_transcript_drop_prob", 0.0))
+        self.transcript_template = str(cfg_get(self._cfg, "asr_transcript_template", ">> {} <<"))
+
+    @property
+    def reads_asr_hypotheses(self) -> bool:
+        return hasattr(self.perception, "transcribe_encoded")
+
+    def transcript_embeddings(self, encoded: torch.Tensor, encoded_len: torch.Tensor) -> Tuple[List[torch.Tensor], List[str]]:
+        import random
+
+        hyps = self.perception.transcribe_encoded(encoded, encoded_len)
+        texts = []
+        for h in hyps:
+            t = (h.text if hasattr(h, "text") else str(h)) or ""
+            if self.training and self.asr_transcript_drop_prob > 0 and random.random() < self.asr_transcript_drop_prob:
+                t = ""
+            texts.append(t)
+        ids = [torch.as_tensor(self.tokenizer.text_to_ids(self.transcript_template.format(t) if t else self.transcript_template.format("").replace("  ", " ")),
+                               dtype=torch.long, device=encoded.device) for t in texts]
+        embs = [self.embed_tokens(i) for i in ids]
+        return embs, texts
+
+    def prepare_inputs(self, batch):
+        if not self.reads_asr_hypotheses:
+            return super().prepare_inputs(batch)
+        from .. import ops
+        from .salm import IGNORE_INDEX, replace_placeholders_and_build_targets
+
+        encoded, encoded_len = self.perception.forward_encoder(batch["audios"], batch["audio_lens"])
+        t_embs, texts = self.transcript_embeddings(encoded, encoded_len)
+        audio_embs, audio_lens = self.perception(encoded=encoded, encoded_len=encoded_len)
+        repl = [torch.cat([e[: int(n)], t.to(e.dtype)], dim=0) for e, n, t in zip(audio_embs, audio_lens, t_embs)]
+        ids = batch["input_ids"]
+        text = self.embed_tokens(torch.where(ids == self.audio_locator_tag_id, torch.zeros_like(ids), ids))
+        cdt = ops.get_compute_dtype()
+        if cdt is not None:
+            text = text.to(cdt)
+        repl = [r.to(text.dtype) for r in repl]
+        tgt = torch.where(batch["loss_mask"].bool(), ids, torch.full_like(ids, IGNORE_INDEX))
+        emb, tgt, mask = replace_placeholders_and_build_targets(ids, text, self.text_pad_id, self.audio_locator_tag_id, repl, tgt)
+        self.last_asr_hypotheses = texts
+        return {"input_embeds": emb[:, :-1], "attention_mask": mask[:, :-1], "target_ids": tgt[:, 1:]}
 
     def asr_loss(self, audio_emb: torch.Tensor, audio_emb_lens: torch.Tensor, transcripts: torch.Tensor, transcript_lens: torch.Tensor) -> torch.Tensor:
         lp = F.log_softmax(self.asr_head(audio_emb.float()), dim=-1).transpose(0, 1)
@@ -257,7 +304,7 @@ class SALMWithAsrDecoder(SALM):
 
     def training_step(self, batch, batch_idx):
         out = super().training_step(batch, batch_idx)
-        if "asr_tokens" in batch:
+        if "asr_tokens" in batch and self.asr_weight > 0:
             emb, emb_len = self.perception(input_signal=batch["audios"], input_signal_length=batch["audio_lens"])
             aux = self.asr_loss(emb, emb_len, batch["asr_tokens"], batch["asr_token_lens"])
             out["loss"] = out["loss"] + self.asr_weight * aux

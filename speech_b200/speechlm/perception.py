@@ -159,3 +159,81 @@ class AudioPerceptionModule(NeuralModule):
         x = enc.transpose(1, 2)
         x = ops.linear(x, self.proj.weight, self.proj.bias)
         return x, enc_len
+
+
+class AudioTranscriptionPerceptionModule(AudioPerceptionModule):
+    """Perception built around a complete ASR model (CTC, transducer or hybrid): its encoder feeds the modality adapter as usual,
+    and its decoder transcribes the same encoder output, so that a speech-LLM can read the recogniser's hypothesis next to the
+    audio embeddings (reference ``speechlm2/modules/perception.py`` ``AudioTranscriptionPerceptionModule``).
+
+    ``asr``: an ASR model instance, a ``.nemo`` path, or a config dictionary ``{"_target_": <model class>, ...model cfg}``."""
+
+    def __init__(self, cfg=None, asr=None, modality_adapter=None, output_dim: Optional[int] = None, freeze_asr_decoder: bool = True, **kw):
+        if cfg is not None:
+            asr = asr if asr is not None else cfg_get(cfg, "asr", None) or cfg_get(cfg, "pretrained_asr", None)
+            modality_adapter = modality_adapter or cfg_get(cfg, "modality_adapter", None)
+            output_dim = output_dim or cfg_get(cfg, "output_dim", None)
+        if asr is None:
+            raise ValueError("an ASR model (instance, .nemo path or config with _target_) is required")
+        if isinstance(asr, str):
+            from ..models.asr_model import ASRModel
+
+            asr = ASRModel.restore_from(asr)
+        elif not isinstance(asr, nn.Module):
+            from ..core.config import to_container
+            from ..core.instantiate import locate
+
+            c = to_container(asr, resolve=True) if not isinstance(asr, dict) else dict(asr)
+            asr = locate(c.pop("_target_"))(OmegaConfCreate(c))
+        super().__init__(preprocessor=asr.preprocessor, encoder=asr.encoder, modality_adapter=modality_adapter, output_dim=output_dim,
+                         spec_augment=getattr(asr, "spec_augmentation", None))
+        self.asr = asr
+        if freeze_asr_decoder:
+            for name in ("decoder", "joint", "ctc_decoder"):
+                m = getattr(asr, name, None)
+                if isinstance(m, nn.Module):
+                    for p in m.parameters():
+                        p.requires_grad = False
+
+    def forward_encoder(self, input_signal, input_signal_length):
+        with torch.no_grad():
+            feats, flen = self.preprocessor(input_signal=input_signal, length=input_signal_length)
+        if self.spec_augmentation is not None and self.training:
+            feats = self.spec_augmentation(input_spec=feats, length=flen)
+        enc, enc_len = self.encoder(audio_signal=feats, length=flen)[:2]
+        return enc, enc_len
+
+    @torch.no_grad()
+    def transcribe_encoded(self, encoded: torch.Tensor, encoded_len: torch.Tensor):
+        """Hypotheses of the ASR model's own decoder for encoder output ``[B, D, T]`` (objects with ``.text``)."""
+        asr = self.asr
+        was = asr.training
+        asr.eval()
+        try:
+            if hasattr(asr, "joint") and hasattr(asr, "decoding") and hasattr(asr.decoding, "rnnt_decoder_predictions_tensor"):
+                hyps = asr.decoding.rnnt_decoder_predictions_tensor(encoded.detach(), encoded_len, return_hypotheses=True)
+            else:
+                dec = getattr(asr, "decoder", None) or getattr(asr, "ctc_decoder")
+                logp = dec(encoder_output=encoded.detach())
+                hyps = asr.decoding.ctc_decoder_predictions_tensor(logp, decoder_lengths=encoded_len, return_hypotheses=True)
+            hyps = hyps[0] if isinstance(hyps, tuple) else hyps
+        finally:
+            asr.train(was)
+        return hyps
+
+    def forward(self, input_signal=None, input_signal_length=None, processed_signal=None, processed_signal_length=None, encoded=None,
+                encoded_len=None):
+        if encoded is None:
+            return super().forward(input_signal, input_signal_length, processed_signal, processed_signal_length)
+        enc = encoded
+        if self.rote is not None:
+            enc = self.rote(enc.transpose(1, 2)).transpose(1, 2)
+        out = self.modality_adapter(audio_signal=enc, length=encoded_len)
+        x = ops.linear(out[0].transpose(1, 2), self.proj.weight, self.proj.bias)
+        return x, out[1]
+
+
+def OmegaConfCreate(d):
+    from ..core.config import OmegaConf
+
+    return OmegaConf.create(d)

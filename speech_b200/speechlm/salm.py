@@ -133,6 +133,11 @@ class SALM(ModelPT):
 
             asr = ASRModel.restore_from(cfg.pretrained_asr)
             self.perception = AudioPerceptionModule(pcfg, preprocessor=asr.preprocessor, encoder=asr.encoder)
+        elif cfg_get(pcfg, "asr", None) is not None or "Transcription" in str(cfg_get(pcfg, "_target_", "")):
+            from .perception import AudioTranscriptionPerceptionModule
+
+            # a complete ASR model inside the perception module: its decoder's hypotheses can be read by the LLM
+            self.perception = AudioTranscriptionPerceptionModule(pcfg, asr=cfg_get(pcfg, "asr", None) or cfg_get(cfg, "pretrained_asr", None))
         else:
             self.perception = AudioPerceptionModule(pcfg)
         if cfg_get(cfg, "lora", None) is not None:

@@ -503,3 +503,42 @@ def test_speechlm_metrics_turn_taking_mcq_empty_text_and_results_logger(tmp_path
     merged = [json.loads(l) for l in open(tmp_path / "res" / "quiz.jsonl")]
     assert [r["id"] for r in merged] == ["q0", "q1", "q2"] and m["quiz/num_samples"] == 3.0 and m["quiz/mcq_acc"] == 1 / 3
     assert m["quiz/wer"] > 1.0 and m["quiz/empty_text_rate"] == 0.0 and (tmp_path / "res" / "metrics.json").exists()
+
+
+def test_salm_with_asr_decoder_reads_the_recognisers_hypotheses():
+    from speech_b200.models.configs import fastconformer_ctc_config
+    from speech_b200.speechlm.data import SALMDataset, synthetic_conversations
+    from speech_b200.speechlm.duplex import SALMWithAsrDecoder
+    from speech_b200.speechlm.perception import AudioTranscriptionPerceptionModule
+
+    torch.manual_seed(0)
+    asr_cfg = OmegaConf.to_container(fastconformer_ctc_config("small", vocab_size=16, dropout=0.0, n_layers=1, features=32, lr=1e-3))
+    asr_cfg["preprocessor"]["dither"] = 0.0
+    tok = ByteLevelTokenizer(special_tokens=["<pad>", "<s>", "</s>", "<|im_start|>", "<|im_end|>"])
+    cfg = OmegaConf.create({"audio_locator_tag": "<|audioplaceholder|>", "prompt_format": "qwen", "llm": dict(TINY, tie_word_embeddings=True),
+                            "perception": {"asr": {"_target_": "speech_b200.models.EncDecCTCModelBPE", **asr_cfg},
+                                           "modality_adapter": {"_target_": "speech_b200.speechlm.perception.IdentityConnector", "d_model": 176}},
+                            "freeze_params": [], "prevent_freeze_params": [], "asr_weight": 0.0, "asr_transcript_drop_prob": 0.0,
+                            "optim": {"name": "adamw", "lr": 1e-3}})
+    m = SALMWithAsrDecoder(cfg, tokenizer=tok)
+    assert isinstance(m.perception, AudioTranscriptionPerceptionModule) and m.reads_asr_hypotheses
+    assert all(not p.requires_grad for p in m.perception.asr.decoder.parameters()) and any(p.requires_grad for p in m.perception.encoder.parameters())
+    ds = SALMDataset(synthetic_conversations(2, seed=1), tok, m.prompt_formatter(), cfg.audio_locator_tag, m.text_pad_id)
+    batch = ds.collate([ds[0], ds[1]])
+    m.eval()
+    inp = m.prepare_inputs(batch)
+    hyps = m.last_asr_hypotheses
+    assert len(hyps) == 2 and all(isinstance(h, str) for h in hyps)
+    # sequence length = text tokens - placeholder + audio frames + tokens of ">> hyp <<", per row (left padded to the longest)
+    enc, enc_len = m.perception.forward_encoder(batch["audios"], batch["audio_lens"])
+    n_text = (batch["input_ids"] != m.text_pad_id).sum(1)
+    want = [int(n_text[b]) - 1 + int(enc_len[b]) + len(tok.text_to_ids(m.transcript_template.format(hyps[b]) if hyps[b] else ">> <<")) for b in range(2)]
+    assert inp["input_embeds"].shape[1] == max(want) - 1 and inp["attention_mask"].sum(1).tolist() == [w - 1 for w in want]       # left padded; the last position is cut off
+    m.train()
+    loss = m.training_step(batch, 0)["loss"]
+    loss.backward()
+    assert math.isfinite(float(loss)) and next(m.perception.encoder.parameters()).grad is not None
+    # dropping every hypothesis shortens the inputs
+    m.asr_transcript_drop_prob = 1.0
+    short = m.prepare_inputs(batch)
+    assert short["input_embeds"].shape[1] <= inp["input_embeds"].shape[1] and m.last_asr_hypotheses == ["", ""]
