@@ -94,3 +94,70 @@ def test_tokenizer_builder(tmp_path):
     main(["--manifest", man, "--data_root", str(tmp_path / "tok"), "--vocab_size", "30", "--tokenizer", "wpe"])
     wp = WordPieceVocabTokenizer(str(tmp_path / "tok" / "tokenizer_wpe_v30" / "vocab.txt"))
     assert wp.ids_to_text(wp.text_to_ids("hello world")) == "hello world"
+
+
+def test_voice_agent_websocket_transport_and_server_app():
+    """The transport re-frames client audio, forwards pipeline events as JSON and the bot's speech as PCM; the example server's app
+    answers a whole conversation through a fake websocket (no network)."""
+    import asyncio
+    import importlib.util
+    import json
+    import os
+
+    import numpy as np
+
+    from speech_b200.agents.transport import WebsocketAudioTransport, float_to_pcm16, pcm16_to_float
+    from speech_b200.agents.voice_agent import build_voice_agent
+
+    x = np.linspace(-1, 1, 9, dtype=np.float32)
+    assert np.abs(pcm16_to_float(float_to_pcm16(x)) - x).max() < 1e-4
+
+    class FakeWS:
+        def __init__(self, incoming):
+            self.incoming, self.sent_text, self.sent_bytes = list(incoming), [], []
+        async def receive(self):
+            return self.incoming.pop(0) if self.incoming else {"type": "websocket.disconnect"}
+        async def send_text(self, t): self.sent_text.append(json.loads(t))
+        async def send_bytes(self, b): self.sent_bytes.append(b)
+
+    sr = 16000
+    rng = np.random.default_rng(0)
+    speech = (0.2 * rng.standard_normal(int(0.8 * sr))).astype(np.float32)
+    silence = np.zeros(int(1.0 * sr), np.float32)
+    audio = np.concatenate([speech, silence])
+    msgs = [{"type": "message", "text": json.dumps({"type": "config", "sample_rate": sr})}]
+    for i in range(0, len(audio), 1000):                       # odd chunking on purpose: the transport re-frames to 80 ms
+        msgs.append({"type": "message", "bytes": float_to_pcm16(audio[i:i + 1000])})
+    msgs.append({"type": "message", "text": "not json"})
+    msgs.append({"type": "message", "text": json.dumps({"type": "end"})})
+    seen = []
+    def stt(chunk):
+        seen.append(len(chunk))
+        return ("hello there" if float(np.sqrt((chunk ** 2).mean())) > 0.01 else None), False
+    agent = build_voice_agent(stt, lambda hist: "hi " + hist[-1]["content"], lambda text: (np.full(4410, 0.1, np.float32), 22050),
+                              speech_threshold=0.01, max_silence=0.4)
+    ws = FakeWS(msgs)
+    asyncio.run(WebsocketAudioTransport(agent, sr, frame_ms=80.0, tts_chunk_ms=50.0).serve(ws))
+    assert set(seen) == {1280}                                    # every pipeline frame is 80 ms
+    kinds = [e["type"] for e in ws.sent_text]
+    assert "user_started" in kinds and "user_stopped" in kinds and "error" in kinds and kinds[-1] == "end"
+    finals = [e for e in ws.sent_text if e["type"] == "transcript" and e["final"]]
+    assert finals and finals[0]["text"] == "hello there"
+    assert any(e["type"] == "bot_text" and e["text"] == "hi hello there" for e in ws.sent_text)
+    assert {"type": "audio_format", "sample_rate": 22050} in ws.sent_text
+    pcm = b"".join(ws.sent_bytes)
+    assert len(pcm) == 4410 * 2 and len(ws.sent_bytes) == 5        # 200 ms of speech in packets of 1102 samples (50 ms)
+    # the example server builds its FastAPI app with fallbacks for absent models
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "voice_agent", "server.py")
+    spec = importlib.util.spec_from_file_location("va_server", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    from speech_b200.core.config import OmegaConf
+    cfg = OmegaConf.create(mod.DEFAULTS)
+    app = mod.build_app(cfg)
+    assert any(getattr(r, "path", "") == "/ws" for r in app.routes) and any(getattr(r, "path", "") == "/health" for r in app.routes)
+    step = mod.make_stt(cfg)
+    assert step(speech[:1280]) == ("(speech)", False) and step(silence[:1280]) == (None, False)
+    assert mod.make_llm(cfg)([{"role": "user", "content": "ping"}]) == "You said: ping"
+    wav, rate = mod.make_tts(cfg)("two words")
+    assert rate == 22050 and len(wav) == 2 * (int(0.12 * 22050) + int(0.05 * 22050))
