@@ -17,6 +17,14 @@ from .logging import logging
 
 def build_trainer(cfg: DictConfig) -> Trainer:
     kw = to_container(cfg.trainer, resolve=True) if cfg.get("trainer") is not None else {}
+    st = kw.get("strategy")
+    if isinstance(st, dict):
+        # ``strategy: {dp_shard_size: 4, tp_size: 2, sequence_parallel: true}`` (optionally with a ``_target_``) builds the device-mesh
+        # strategy object; plain strings ("auto", "ddp", "fsdp") pass through
+        from ..parallel.strategy import ParallelStrategy
+
+        st = {k: v for k, v in st.items() if k != "_target_"}
+        kw["strategy"] = ParallelStrategy(**st)
     return Trainer(**kw)
 
 

@@ -136,3 +136,39 @@ def test_aed_trains_from_a_manifest_with_prompts_and_the_chunked_and_streaming_s
           "decoding.alignatt_thr=2"], str(tmp_path))
     recs = [json.loads(l) for l in open(out2)]
     assert len(recs) == 4 and all("average_lagging_s" in r for r in recs)
+
+
+def test_duplex_infer_example_and_mesh_strategy_from_yaml(tmp_path):
+    import torch
+    from speech_b200.core.config import OmegaConf
+    from speech_b200.data.audio_to_text import save_wav
+    from speech_b200.models.configs import encoder_cfg, preprocessor_cfg
+    from speech_b200.parallel.strategy import ParallelStrategy
+    from speech_b200.speechlm.duplex import DuplexSTTModel
+    from speech_b200.utils.launch import build_trainer
+
+    tr = build_trainer(OmegaConf.create({"trainer": {"accelerator": "cpu", "max_steps": 1, "strategy": {"dp_shard_size": -1, "tp_size": 1,
+                                                                                                    "sequence_parallel": False}}}))
+    assert isinstance(tr.strategy_spec, ParallelStrategy) and tr.strategy_spec.dp_shard_size == -1
+    for name in ("salm_automodel", "duplex_stt", "salm"):
+        assert OmegaConf.load(os.path.join(REPO, "examples", "speechlm2", "conf", name + ".yaml")).model is not None
+    torch.manual_seed(0)
+    tiny = dict(vocab_size=300, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2,
+                head_dim=8, tie_word_embeddings=True, qk_norm=True, model_type="qwen3")
+    pc = {"preprocessor": {**preprocessor_cfg(32), "dither": 0.0}, "encoder": encoder_cfg("small", 32, 0.0, 0.0, n_layers=1),
+          "modality_adapter": {"_target_": "speech_b200.speechlm.perception.IdentityConnector", "d_model": 176}}
+    m = DuplexSTTModel(OmegaConf.create({"llm": tiny, "perception": pc, "predict_user_text": True, "optim": {"name": "adamw", "lr": 1e-3}}))
+    nemo = str(tmp_path / "duplex.nemo")
+    m.save_to(nemo)
+    g = np.random.default_rng(0)
+    man = tmp_path / "in.json"
+    with open(man, "w") as f:
+        for i in range(2):
+            p = str(tmp_path / f"d{i}.wav")
+            save_wav(p, (0.1 * g.standard_normal(16000)).astype(np.float32))
+            f.write(json.dumps({"audio_filepath": p, "duration": 1.0, "user_end_time": 0.8}) + "\n")
+    out = tmp_path / "gen.jsonl"
+    log = _run("examples/speechlm2/stt_duplex_infer.py", [f"pretrained_name={nemo}", f"inputs={man}", f"output_manifest={out}", "pad_seconds=0.5",
+                                                          "device=cpu", "batch_size=2"], str(tmp_path))
+    recs = [json.loads(l) for l in open(out)]
+    assert len(recs) == 2 and all("pred_text" in r and "pred_user_text" in r for r in recs) and "turn taking" in log
