@@ -250,13 +250,31 @@ class STFTDiscriminator(nn.Module):
 
 
 class Discriminator(nn.Module):
-    def __init__(self, periods=(2, 3, 5, 7, 11), stft_resolutions=((512, 128, 512), (1024, 256, 1024))):
+    """Period + STFT sub-discriminators; ``multiband_stft_resolutions`` adds banded STFT discriminators, and ``add_slm`` one on the
+    features of a frozen speech foundation model."""
+
+    def __init__(self, periods=(2, 3, 5, 7, 11), stft_resolutions=((512, 128, 512), (1024, 256, 1024)), multiband_stft_resolutions=(),
+                 stft_bands=((0.0, 0.1), (0.1, 0.25), (0.25, 0.5), (0.5, 0.75), (0.75, 1.0))):
         super().__init__()
-        self.discs = nn.ModuleList([PeriodDiscriminator(p) for p in periods] + [STFTDiscriminator(r) for r in stft_resolutions])
+        from .audio_codec_extra import MultiBandDiscriminatorSTFT
+
+        self.discs = nn.ModuleList([PeriodDiscriminator(p) for p in periods] + [STFTDiscriminator(tuple(r)) for r in stft_resolutions]
+                                   + [MultiBandDiscriminatorSTFT(tuple(r), stft_bands) for r in multiband_stft_resolutions])
+        self.slm = None
+
+    def add_slm(self, feature_extractor, **kw):
+        from .audio_codec_extra import SLMDiscriminator
+
+        self.slm = SLMDiscriminator(feature_extractor, **kw)
+        return self.slm
 
     def forward(self, audio_real, audio_gen):
         outs = [(d(audio_real), d(audio_gen)) for d in self.discs]
-        return ([o[0][0] for o in outs], [o[1][0] for o in outs], [o[0][1] for o in outs], [o[1][1] for o in outs])
+        res = ([o[0][0] for o in outs], [o[1][0] for o in outs], [o[0][1] for o in outs], [o[1][1] for o in outs])
+        if self.slm is not None:
+            for acc, extra in zip(res, self.slm(audio_real, audio_gen)):
+                acc.extend(extra)
+        return res
 
 
 def generator_adv_loss(scores_gen):
@@ -288,7 +306,12 @@ class AudioCodecModel(ModelPT):
             d.pop("_target_", None)
         self.audio_encoder = HiFiGANEncoder(**enc)
         self.vector_quantizer = GroupFiniteScalarQuantizer(**vq) if vq else None
-        self.audio_decoder = HiFiGANDecoder(**dec)
+        if dec.pop("causal", False):
+            from .audio_codec_extra import CausalHiFiGANDecoder
+
+            self.audio_decoder = CausalHiFiGANDecoder(**dec)
+        else:
+            self.audio_decoder = HiFiGANDecoder(**dec)
         self.samples_per_frame = self.audio_encoder.total_stride
         self.num_codebooks = self.vector_quantizer.num_groups if self.vector_quantizer is not None else 0
         self.codebook_size = self.vector_quantizer.codebook_size if self.vector_quantizer is not None else 0
@@ -297,6 +320,17 @@ class AudioCodecModel(ModelPT):
         self.stft_loss = MultiResolutionSTFTLoss()
         self.w = {"mel": cfg_get(cfg, "mel_loss_l1_scale", 15.0), "stft": cfg_get(cfg, "stft_loss_scale", 1.0),
                   "gen": cfg_get(cfg, "gen_loss_scale", 1.0), "fm": cfg_get(cfg, "feature_loss_scale", 1.0)}
+        from . import audio_codec_extra as X
+
+        kind = cfg_get(cfg, "gan_loss", "squared")
+        if kind not in ("squared", "hinged"):
+            raise ValueError(f"gan_loss must be 'squared' or 'hinged', got {kind!r}")
+        self.gen_loss = X.GeneratorHingedLoss() if kind == "hinged" else X.GeneratorSquaredLoss()
+        self.disc_loss = X.DiscriminatorHingedLoss() if kind == "hinged" else X.DiscriminatorSquaredLoss()
+        self.feature_loss = X.RelativeFeatureMatchingLoss() if cfg_get(cfg, "feature_loss_type", "absolute") == "relative" else None
+        self.w["time"] = cfg_get(cfg, "time_domain_loss_scale", 0.0)
+        self.w["sisdr"] = cfg_get(cfg, "si_sdr_loss_scale", 0.0)
+        self.time_loss, self.sisdr_loss = X.TimeDomainLoss(), X.SISDRLoss()
         self.automatic_optimization = False
         if not self._is_model_being_restored and self._train_dl is None:
             self._setup_dataloaders_from_cfg()
@@ -356,6 +390,23 @@ class AudioCodecModel(ModelPT):
     def decode(self, tokens, tokens_len):
         return self.audio_decoder(self.dequantize(tokens, tokens_len).to(next(self.audio_decoder.parameters()).dtype), tokens_len)
 
+    @torch.no_grad()
+    def decode_stream(self, tokens, state=None):
+        """Chunk of tokens ``[B, C, t]`` -> the next ``t * samples_per_frame`` samples; needs ``audio_decoder.causal: true``."""
+        if not hasattr(self.audio_decoder, "decode_stream"):
+            raise RuntimeError("streaming decode needs a causal decoder (audio_decoder.causal: true)")
+        lens = torch.full((tokens.shape[0],), tokens.shape[-1], device=tokens.device, dtype=torch.long)
+        z = self.dequantize(tokens, lens).to(next(self.audio_decoder.parameters()).dtype)
+        return self.audio_decoder.decode_stream(z, state)
+
+    def add_slm_discriminator(self, feature_extractor, **kw):
+        """Adds a discriminator over the features of a frozen speech foundation model (``feature_extractor(audio) -> [B, L, T, D]``);
+        call before ``configure_optimizers``."""
+        if self.discriminator is None:
+            raise RuntimeError("train_discriminator is off")
+        kw.setdefault("input_sr", self.sample_rate)
+        return self.discriminator.add_slm(feature_extractor, **kw)
+
     def forward(self, audio, audio_len):
         enc, enc_len = self.encode_audio(audio, audio_len)
         if self.vector_quantizer is not None:
@@ -384,15 +435,20 @@ class AudioCodecModel(ModelPT):
         manual = opts is not None and len(opts) == 2 and self.discriminator is not None
         if manual:
             sr, sg, _, _ = self.discriminator(audio, gen.detach())
-            d_loss = discriminator_loss(sr, sg)
+            d_loss = self.disc_loss(sr, sg)
             opts[1].zero_grad()
             d_loss.backward()
             opts[1].step()
             logs["d_loss"] = d_loss.detach()
         loss = self.w["mel"] * self.mel_loss(audio, gen, audio_len) + self.w["stft"] * self.stft_loss(audio, gen, audio_len)
+        if self.w["time"]:
+            loss = loss + self.w["time"] * self.time_loss(audio, gen, audio_len)
+        if self.w["sisdr"]:
+            loss = loss + self.w["sisdr"] * self.sisdr_loss(audio, gen, audio_len)
         if self.discriminator is not None:
             sr, sg, fr, fg = self.discriminator(audio, gen)
-            loss = loss + self.w["gen"] * generator_adv_loss(sg) + self.w["fm"] * feature_matching_loss(fr, fg)
+            fm = self.feature_loss(fr, fg) if self.feature_loss is not None else feature_matching_loss(fr, fg)
+            loss = loss + self.w["gen"] * self.gen_loss(sg) + self.w["fm"] * fm
         logs["train_loss"] = loss.detach()
         self.log_dict(logs)
         return {"loss": loss}

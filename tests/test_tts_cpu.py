@@ -402,3 +402,106 @@ def test_magpie_voice_context_attention_prior_and_long_form_state(model_type):
     assert isinstance(st, LongFormState) and st.chunks_done == 3 and st.context_codes is not None and wav.numel() > 0
     wav2 = m.generate_speech("abc. def.", max_chars_per_chunk=5, max_decoder_steps=3, context_audio=ctx_audio[0])
     assert m.last_long_form_state.context_codes.shape[-1] == int(cn[0]) and wav2.numel() > 0
+
+
+def test_causal_codec_decoder_streams_chunk_by_chunk_to_the_same_audio():
+    from speech_b200.tts.audio_codec_extra import CausalHiFiGANDecoder
+
+    torch.manual_seed(0)
+    dec = CausalHiFiGANDecoder(input_dim=8, up_sample_rates=(4, 2), base_channels=16, resblock_kernel_sizes=(3,), resblock_dilation_sizes=(1, 3)).eval()
+    z = torch.randn(2, 8, 12)
+    with torch.no_grad():
+        full, lens = dec(z, torch.tensor([12, 12]))
+        state, chunks = None, []
+        for a, b in ((0, 5), (5, 6), (6, 12)):
+            y, state = dec.decode_stream(z[:, :, a:b], state)
+            chunks.append(y)
+        # causality: changing a later latent frame leaves earlier samples alone
+        z2 = z.clone()
+        z2[:, :, 8:] += 1.0
+        full2, _ = dec(z2, torch.tensor([12, 12]))
+    assert full.shape == (2, 96) and lens.tolist() == [96, 96]
+    assert torch.allclose(torch.cat(chunks, dim=-1), full, atol=1e-5)
+    assert torch.allclose(full2[:, : 8 * 8], full[:, : 8 * 8], atol=1e-6) and not torch.allclose(full2[:, 64:], full[:, 64:])
+
+
+def test_codec_discriminators_and_losses():
+    from speech_b200.tts.audio_codec_extra import (
+        DiscriminatorHingedLoss, DiscriminatorSquaredLoss, GeneratorHingedLoss, GeneratorSquaredLoss, MMDLoss, MultiBandDiscriminatorSTFT,
+        MultiResolutionDiscriminatorSTFT, MultiResolutionMelLoss, RelativeFeatureMatchingLoss, ResNetSpeakerEncoder, SISDRLoss, SLMDiscriminator,
+        TimeDomainLoss,
+    )
+
+    torch.manual_seed(0)
+    real, gen = torch.randn(2, 4000), torch.randn(2, 4000)
+    mrd = MultiResolutionDiscriminatorSTFT(resolutions=((128, 32, 128), (256, 64, 256)), ch=4)
+    sr, sg, fr, fg = mrd(real, gen)
+    assert len(sr) == 2 and sr[0].dim() == 2 and len(fr[0]) == 5 * 4 + 1
+    assert MultiBandDiscriminatorSTFT((128, 32, 128), ch=4)(real)[0].shape[0] == 2
+    # a stand-in foundation model: 3 "layers" of framed audio
+    extract = lambda a: torch.stack([a.unfold(-1, 16, 160)] * 3, dim=1)  # noqa: E731
+    slm = SLMDiscriminator(extract, slm_hidden=16, slm_layers=3, initial_channel=4, input_sr=22050, slm_sr=16000)
+    s_r, s_g, f_r, f_g = slm(real, gen)
+    assert s_r[0].shape == s_g[0].shape and len(f_r[0]) == 3
+    for gl, dl, fake in ((GeneratorHingedLoss(), DiscriminatorHingedLoss(), -1.0), (GeneratorSquaredLoss(), DiscriminatorSquaredLoss(), 0.0)):
+        assert float(dl([torch.full((2, 3), 1.0)], [torch.full((2, 3), fake)])) == 0.0             # a perfect discriminator
+        assert float(dl([torch.full((2, 3), 0.0)], [torch.full((2, 3), 0.5)])) > 0.0
+        assert float(gl([torch.full((2, 3), 1.0)])) == 0.0 and float(gl([torch.full((2, 3), 0.0)])) == 1.0
+    assert float(RelativeFeatureMatchingLoss()(fr, fr)) == 0.0 and float(RelativeFeatureMatchingLoss()(fr, fg)) > 0
+    lens = torch.tensor([4000, 3000])
+    assert float(TimeDomainLoss()(real, real, lens)) == 0.0
+    mel = MultiResolutionMelLoss(16000, resolutions=((64, 16), (256, 64)), mel_dims=(10, 40))
+    assert float(mel(real, real, lens)) == 0.0 and float(mel(real, gen, lens)) > 0
+    # SI-SDR ignores scale and is clipped; noise lowers it
+    sd = SISDRLoss(clip_max=30.0)
+    assert float(sd(real, 3.0 * real)) == pytest.approx(-30.0, abs=1e-3)
+    assert float(sd(real, real + 0.1 * gen, lens)) == pytest.approx(-20.0, abs=1.5)
+    mmd = MMDLoss()
+    a, b = torch.randn(200, 6), torch.randn(200, 6)
+    assert abs(float(mmd(a, b))) < 0.02 < float(mmd(a, b + 2.0))
+    emb = ResNetSpeakerEncoder(n_mels=16, channels=(4, 8), proj_dim=12).eval()(torch.randn(2, 8000))
+    assert emb.shape == (2, 12) and torch.allclose(emb.norm(dim=-1), torch.ones(2), atol=1e-5)
+
+
+def test_codec_index_converter_round_trips_between_group_layouts():
+    from speech_b200.tts.audio_codec import GroupFiniteScalarQuantizer
+    from speech_b200.tts.audio_codec_extra import VectorQuantizerIndexConverter
+
+    old, new = GroupFiniteScalarQuantizer(4, [4, 4]), GroupFiniteScalarQuantizer(2, [4, 4, 4, 4])
+    conv = VectorQuantizerIndexConverter(old, new)
+    lens = torch.tensor([7, 5])
+    z = torch.randn(2, 8, 7)
+    deq_old, idx_old = old(z, lens)
+    idx_new = conv.convert_original_to_new(idx_old)
+    assert idx_new.shape == (2, 2, 7) and int(idx_new.max()) < 256
+    # the new layout decodes to the very same latent values, and the way back restores the indices
+    assert torch.allclose(new.decode(idx_new, lens), deq_old, atol=1e-6)
+    assert torch.equal(conv.convert_new_to_original(idx_new), idx_old)
+    with pytest.raises(ValueError):
+        VectorQuantizerIndexConverter(old, GroupFiniteScalarQuantizer(2, [8, 4, 4, 2]))
+
+
+def test_audio_codec_model_with_causal_decoder_slm_discriminator_and_hinged_losses():
+    torch.manual_seed(0)
+    cfg = OmegaConf.create({
+        "sample_rate": 16000, "mel_loss": {"n_mels": 20, "n_fft": 256, "hop": 64, "win": 256}, "gan_loss": "hinged", "feature_loss_type": "relative", "time_domain_loss_scale": 1.0, "si_sdr_loss_scale": 0.1,
+        "audio_encoder": {"down_sample_rates": [4, 2], "base_channels": 8, "encoded_dim": 8},
+        "vector_quantizer": {"num_groups": 2, "num_levels_per_group": [4, 4, 4, 4]},
+        "audio_decoder": {"causal": True, "input_dim": 8, "up_sample_rates": [2, 4], "base_channels": 16, "resblock_kernel_sizes": [3], "resblock_dilation_sizes": [1, 3]},
+        "discriminator": {"periods": [2], "stft_resolutions": [], "multiband_stft_resolutions": [[128, 32, 128]]},
+    })
+    m = AudioCodecModel(cfg)
+    m.add_slm_discriminator(lambda a: torch.stack([a.unfold(-1, 16, 160)] * 2, dim=1), slm_hidden=16, slm_layers=2, initial_channel=4, slm_sr=16000)
+    m.configure_optimizers()
+    assert any(n.startswith("discriminator.slm.") for n, _ in m.named_parameters())
+    audio, lens = torch.randn(2, 3200), torch.tensor([3200, 2400])
+    out = m.training_step((audio, lens), 0)
+    out["loss"].backward()
+    assert torch.isfinite(out["loss"])
+    # tokens -> audio in two chunks equals the one-shot decode
+    m.eval()
+    toks, tl = m.encode(audio, torch.tensor([3200, 3200]))
+    full, _ = m.decode(toks, tl)
+    a, st = m.decode_stream(toks[..., :150])
+    b, st = m.decode_stream(toks[..., 150:], st)
+    assert torch.allclose(torch.cat([a, b], -1), full, atol=1e-5)
