@@ -282,3 +282,26 @@ def test_layernorm_and_conv_module_are_bitwise_reproducible():
     b = torch.randn(1024, device="cuda")
     y = [ops.layer_norm(x, w, b, 1e-5) for _ in range(2)]
     assert torch.equal(y[0], y[1])
+
+
+def test_gemm_is_bitwise_repeatable_and_stays_inside_its_output():
+    """Two launches on the same operands give the same bits (each output tile has one writer and a fixed K order), and the bytes
+    around a ragged output (M, N not multiples of the tile) keep their sentinel."""
+    from speech_b200.utils.race_check import guarded_empty, run_twice
+
+    nat = _native()
+    torch.manual_seed(0)
+    M, N, K = 250, 1032, 640
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    g = guarded_empty((M, N), torch.bfloat16, device="cuda", guard_bytes=1 << 16)
+
+    def step():
+        nat.gemm(a, b, g.tensor, M=M, N=N, K=K, lda=K, ldb=K, ldd=N)
+        nat.check_status()
+        return g.tensor
+
+    run_twice(step).raise_if_different()
+    g.check("gemm output")
+    err = (g.tensor.float() - a.float() @ b.float().t()).abs().max().item()
+    assert err <= 0.5

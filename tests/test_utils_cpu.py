@@ -376,3 +376,40 @@ def test_multirun_sweeps_and_model_utilities(tmp_path):
     from speech_b200 import models  # noqa: F401  (imports the model classes)
     infos = misc.resolve_subclass_pretrained_model_info(ModelPT)
     assert isinstance(infos, list)
+
+
+def test_run_twice_reports_bitwise_differences_and_guard_bands_catch_overruns():
+    from speech_b200.utils.race_check import guarded_empty, run_twice
+
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(8, 4)
+    x = torch.randn(5, 8)
+
+    def step():
+        y = torch.nn.functional.dropout(lin(x), 0.5)          # random, but seeded alike in both runs
+        y.sum().backward()
+        return {"y": y}
+
+    assert run_twice(step, parameters=list(lin.parameters())).identical
+    counter = {"n": 0}
+
+    def racy():
+        counter["n"] += 1
+        y = lin(x).detach().clone()
+        if counter["n"] == 2:
+            y[3, 1] += 1e-6                                   # what an unordered accumulation looks like
+        return [y]
+
+    rep = run_twice(racy)
+    assert not rep.identical and rep.mismatches[0]["name"] == "out[0]" and rep.mismatches[0]["first"] == (3, 1) and rep.mismatches[0]["count"] == 1
+    with pytest.raises(AssertionError, match="differ"):
+        rep.raise_if_different()
+
+    g = guarded_empty((3, 5), torch.float32, guard_bytes=64, fill=0.0)
+    g.tensor.copy_(torch.randn(3, 5))
+    g.check()
+    flat = g._raw                                             # an out-of-bounds store two floats past the end
+    flat[g._guard + 60 + 8] = 0
+    assert g.violations() == [("after", 8)]
+    with pytest.raises(AssertionError, match="after the payload at byte offset 8"):
+        g.check("gemm output")
