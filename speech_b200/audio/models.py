@@ -43,10 +43,6 @@ class AudioToAudioModel(ModelPT):
             return
         super()._setup_dataloaders_from_cfg()
 
-    @classmethod
-    def list_available_models(cls):
-        return []
-
     # ------------------------------------------------------------------ data
     def _loader(self, config):
         if config is None:

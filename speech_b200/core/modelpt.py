@@ -234,7 +234,10 @@ class ModelPT(nn.Module, Typing, Serialization):
 
     @classmethod
     def list_available_models(cls) -> List[PretrainedModelInfo]:
-        return []
+        """Published checkpoints of this class (``core/model_catalog.py``); a subclass that overrides this with ``[]`` has none."""
+        from .model_catalog import entries_for_class
+
+        return [PretrainedModelInfo(pretrained_model_name=e.name, description=e.description, location=e.location, class_=cls) for e in entries_for_class(cls)]
 
     @classmethod
     def from_pretrained(cls, model_name: str, refresh_cache: bool = False, override_config_path=None,
@@ -242,9 +245,13 @@ class ModelPT(nn.Module, Typing, Serialization):
                         save_restore_connector=None):
         """Load by name.  A path to a ``.nemo`` file or an extracted directory is used directly; a
         ``org/name`` id is looked up in the local Hugging Face cache (this build has no network)."""
+        from .model_catalog import resolve_local
+
         path = None
         if os.path.exists(model_name):
             path = model_name
+        elif resolve_local(model_name) is not None:
+            path = resolve_local(model_name)
         elif "/" in model_name:
             try:
                 from huggingface_hub import snapshot_download

@@ -322,6 +322,3 @@ class ConfidenceEnsembleModel(ModelPT):
     def setup_training_data(self, c): ...
     def setup_validation_data(self, c): ...
 
-    @classmethod
-    def list_available_models(cls):
-        return []

@@ -127,10 +127,6 @@ class _EncDecLabelBase(ModelPT):
         acc = sum(int(o["test_correct"]) for o in outputs) / max(1, sum(int(o["test_total"]) for o in outputs))
         return {"test_loss": loss, "log": {"test_loss": loss, "test_epoch_top@1": acc}}
 
-    @classmethod
-    def list_available_models(cls):
-        return []
-
 
 class EncDecClassificationModel(_EncDecLabelBase):
     """Utterance-level classification (``classification_models.py`` ``EncDecClassificationModel``)."""

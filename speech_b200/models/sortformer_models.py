@@ -179,10 +179,6 @@ class SortformerEncLabelModel(ModelPT):
             return
         super()._setup_dataloaders_from_cfg()
 
-    @classmethod
-    def list_available_models(cls):
-        return []
-
     # ------------------------------------------------------------------ data: (audio, audio_len, targets [B, T', S], target_len)
     def _loader(self, config):
         if config is None:

@@ -116,10 +116,6 @@ class _SSLBase(ASRModel, ASRModuleMixin):
             return
         super()._setup_dataloaders_from_cfg()
 
-    @classmethod
-    def list_available_models(cls):
-        return []
-
 
 class SpeechEncDecSelfSupervisedModel(_SSLBase):
     def __init__(self, cfg: DictConfig, trainer=None):

@@ -209,6 +209,3 @@ class EncDecTransfModelBPE(ASRModel, ASRBPEMixin, ASRModuleMixin, TranscriptionM
             out.append(Hypothesis(score=0.0, y_sequence=torch.tensor(ids, dtype=torch.long), text=self.tokenizer.ids_to_text(ids)))
         return out
 
-    @classmethod
-    def list_available_models(cls):
-        return []

@@ -55,10 +55,6 @@ class DuplexSTTModel(ModelPT):
         else:
             self.predict_user_text = False
 
-    @classmethod
-    def list_available_models(cls):
-        return []
-
     @property
     def streaming_inference(self):
         """The frame-synchronous engine (prompts, forced turn taking, chunk-by-chunk feeding)."""

@@ -255,10 +255,6 @@ class DuplexEARTTS(ModelPT):
         if hasattr(self, "tts"):                                                         # the base constructor calls this before the layers exist
             super()._setup_dataloaders_from_cfg()
 
-    @classmethod
-    def list_available_models(cls):
-        return []
-
     def _loader(self, c):
         from ..tts.code_datasets import build_code_dataloader
 
@@ -318,10 +314,6 @@ class DuplexS2SSpeechDecoderModel(ModelPT):
         self.code_emb = nn.ModuleList(nn.Embedding(self.speech_vocab_size, hd) for _ in range(self.K))
         self.audio_head = nn.Linear(hd, self.K * self.speech_vocab_size)
         self.audio_loss_weight = float(cfg_get(cfg, "audio_loss_weight", 1.0))
-
-    @classmethod
-    def list_available_models(cls):
-        return []
 
     def setup_training_data(self, c):
         self._train_dl = None

@@ -155,10 +155,6 @@ class SALM(ModelPT):
             return
         super()._setup_dataloaders_from_cfg()
 
-    @classmethod
-    def list_available_models(cls):
-        return []
-
     # ------------------------------------------------------------------ ids
     @property
     def audio_locator_tag_id(self) -> int:

@@ -340,10 +340,6 @@ class AudioCodecModel(ModelPT):
             return
         super()._setup_dataloaders_from_cfg()
 
-    @classmethod
-    def list_available_models(cls):
-        return []
-
     # ------------------------------------------------------------------ data: batches of (audio, audio_len)
     def _loader(self, config):
         if config is None:

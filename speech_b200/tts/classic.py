@@ -189,10 +189,6 @@ class FastPitchModel(ModelPT):
         self.w = {"dur": cfg_get(cfg, "dur_loss_scale", 0.1), "pitch": cfg_get(cfg, "pitch_loss_scale", 0.1), "align": cfg_get(cfg, "align_loss_scale", 1.0)}
         self.bin_loss_start = cfg_get(cfg, "bin_loss_warmup_epochs", 100)
 
-    @classmethod
-    def list_available_models(cls):
-        return []
-
     def setup_training_data(self, c):
         from .data import build_tts_dataloader
 
@@ -292,10 +288,6 @@ class HifiGanModel(ModelPT):
         self.mel = MelLoss(self.sample_rate, self.n_mel, **dict(cfg_get(cfg, "mel", {}) or {}))
         self.l1_factor = cfg_get(cfg, "l1_loss_factor", 45.0)
 
-    @classmethod
-    def list_available_models(cls):
-        return []
-
     def setup_training_data(self, c):
         self._train_dl = None
 
@@ -347,10 +339,6 @@ class AlignerModel(ModelPT):
         self.alignment_encoder = ConvAttention(self.n_mel, d)
         self.forward_sum = ForwardSumLoss()
         self.mel = MelLoss(cfg_get(cfg, "sample_rate", 22050), self.n_mel)
-
-    @classmethod
-    def list_available_models(cls):
-        return []
 
     def setup_training_data(self, c):
         self._train_dl = None
@@ -405,10 +393,6 @@ class SSLDisentangler(ModelPT):
         self.speaker_proj = nn.Linear(2 * d, self.speaker_dim)
         self.speaker_out = nn.Linear(self.speaker_dim, self.num_speakers)
         self.content_weight, self.speaker_weight = float(cfg_get(cfg, "content_loss_weight", 1.0)), float(cfg_get(cfg, "speaker_loss_weight", 1.0))
-
-    @classmethod
-    def list_available_models(cls):
-        return []
 
     def setup_training_data(self, c):
         self._train_dl = None

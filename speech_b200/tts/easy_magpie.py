@@ -192,10 +192,6 @@ class EasyMagpieTTSModel(ModelPT):
         if hasattr(self, "heads"):                                                       # the base constructor calls this before the layers exist
             super()._setup_dataloaders_from_cfg()
 
-    @classmethod
-    def list_available_models(cls):
-        return []
-
     def _loader(self, c):
         from .code_datasets import build_code_dataloader
 

@@ -177,10 +177,6 @@ class MagpieTTSModel(ModelPT):
             return
         super()._setup_dataloaders_from_cfg()
 
-    @classmethod
-    def list_available_models(cls):
-        return []
-
     # ------------------------------------------------------------------ data: (text ids, text len, audio, audio len)
     def _loader(self, config):
         if config is None:

@@ -289,3 +289,27 @@ def test_step_hooks_profiling_windows_and_scheduled_freezing(tmp_path):
         ch.batch_end(m, step, step + 1)
     import glob
     assert glob.glob(str(tmp_path / "*_chakra" / "rank-0.json"))
+
+
+def test_model_catalogue_lists_by_class_and_resolves_names_from_the_local_cache(tmp_path, monkeypatch):
+    from speech_b200.core import model_catalog as mc
+    from speech_b200.models.ctc_models import EncDecCTCModel
+    from speech_b200.models.rnnt_models import EncDecRNNTBPEModel
+
+    names = [i.pretrained_model_name for i in EncDecRNNTBPEModel.list_available_models()]
+    assert "parakeet-tdt-0.6b-v2" in names and "canary-1b" not in names
+    assert all(i.location.startswith("https://") and i.class_ is EncDecRNNTBPEModel for i in EncDecRNNTBPEModel.list_available_models())
+    assert [e.name for e in mc.search("sortformer")] == ["diar_sortformer_4spk-v1", "diar_streaming_sortformer_4spk-v2"]
+    monkeypatch.setenv("NEMO_CACHE_DIR", str(tmp_path))
+    assert mc.resolve_local("QuartzNet15x5Base-En") is None
+    with pytest.raises(FileNotFoundError):
+        EncDecCTCModel.from_pretrained("QuartzNet15x5Base-En")
+    calls = []
+
+    def downloader(url, dest):
+        calls.append(url)
+        open(dest, "wb").write(b"x")
+
+    path = mc.fetch("QuartzNet15x5Base-En", downloader)
+    assert mc.fetch("QuartzNet15x5Base-En", downloader) == path and len(calls) == 1 and "QuartzNet15x5Base-En" in calls[0]
+    assert mc.resolve_local("QuartzNet15x5Base-En") == path
