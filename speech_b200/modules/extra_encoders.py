@@ -26,7 +26,7 @@ from .subsampling import ConvSubsampling, StackingSubsampling
 
 def _pre_encoder(subsampling: Optional[str], factor: int, feat_in: int, feat_out: int, conv_channels: int):
     if subsampling and factor > 1:
-        if subsampling in ("stacking", "stacking_norm"):
+        if subsampling in ("stacking", "stacking_norm", "feature_stacking"):
             return StackingSubsampling(factor, feat_in, feat_out, norm="norm" in subsampling)
         return ConvSubsampling(subsampling, factor, feat_in, feat_out, conv_channels if conv_channels > 0 else feat_out, activation=nn.ReLU())
     return nn.Linear(feat_in, feat_out)
@@ -163,16 +163,24 @@ class TransformerEncoder(NeuralModule):
                  qkv_bias: bool = False, qk_norm: bool = False, ff_expansion: float = 4.0, pre_block_norm: bool = True,
                  subsampling: str = "dw_striding", subsampling_factor: int = 4, subsampling_conv_channels: int = 256,
                  attn_mode: str = "full", self_attention_model: Optional[str] = "rel_pos", xscaling: bool = False, pos_emb_max_len: int = 5000,
-                 dropout_pre_encoder: float = 0.1, dropout_emb: float = 0.0):
+                 dropout_pre_encoder: Optional[float] = None, dropout_emb: float = 0.0, feat_out: int = -1, sync_max_audio_length: bool = True):
         super().__init__()
         self_attention_model = self_attention_model or "no_pos"
+        dropout_pre_encoder = drop_rate if dropout_pre_encoder is None else dropout_pre_encoder
+        if d_model % n_heads:
+            raise ValueError(f"d_model ({d_model}) must be divisible by n_heads ({n_heads})")
+        if d_model // n_heads < 16:
+            raise ValueError(f"head dimension d_model / n_heads = {d_model // n_heads} is below 16, the smallest the attention kernels tile")
         if attn_mode not in ("full", "causal"):
             raise ValueError(f"attn_mode must be one of ('full', 'causal'), got {attn_mode!r}")
         if self_attention_model not in ("abs_pos", "rel_pos", "no_pos"):
             raise ValueError(f"self_attention_model must be one of ('abs_pos', 'rel_pos', 'no_pos'), got {self_attention_model!r}")
         self.cfg = TransformerEncoderConfig(feat_in, d_model, n_heads, n_layers, drop_rate, qkv_bias, qk_norm, ff_expansion, pre_block_norm,
                                             subsampling_factor, attn_mode, self_attention_model)
-        self.d_model, self._feat_in, self._feat_out, self.subsampling_factor = d_model, feat_in, d_model, subsampling_factor
+        self.d_model, self._feat_in, self.subsampling_factor = d_model, feat_in, subsampling_factor
+        self._feat_out = feat_out if feat_out and feat_out > 0 else d_model
+        self.out_proj = nn.Linear(d_model, self._feat_out) if self._feat_out != d_model else None
+        self.sync_max_audio_length, self.max_audio_length = sync_max_audio_length, pos_emb_max_len
         self.pre_encode = _pre_encoder(subsampling, subsampling_factor, feat_in, d_model, subsampling_conv_channels)
         xs = math.sqrt(d_model) if xscaling else None
         if self_attention_model == "rel_pos":
@@ -210,7 +218,26 @@ class TransformerEncoder(NeuralModule):
         for blk in self.layers:
             x = blk(x, hidden, pos_emb)
         x = ops.layer_norm(x, self.final_norm.weight, self.final_norm.bias, self.final_norm.eps)
+        if self.out_proj is not None:
+            x = ops.linear(x, self.out_proj.weight, self.out_proj.bias)
         return x.transpose(1, 2), length
+
+    def set_max_audio_length(self, max_audio_length: int):
+        """Grows the positional table to ``max_audio_length`` frames (after sub-sampling)."""
+        self.max_audio_length = max(self.max_audio_length, int(max_audio_length))
+        if self.pos_enc is not None:
+            self.pos_enc.extend_pe(self.max_audio_length, next(self.parameters()).device)
+
+    def update_max_seq_length(self, seq_length: int, device=None):
+        """Before a forward on ``seq_length`` input frames: with ``sync_max_audio_length`` every rank grows its positional table to
+        the longest length among ranks, so that no rank re-allocates inside a step the others have passed."""
+        if self.sync_max_audio_length and torch.distributed.is_available() and torch.distributed.is_initialized():
+            t = torch.tensor([seq_length], dtype=torch.float32, device=device if torch.distributed.get_backend() == "nccl" else "cpu")
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            seq_length = int(t.item())
+        need = -(-int(seq_length) // max(1, self.subsampling_factor))
+        if need > self.max_audio_length:
+            self.set_max_audio_length(need)
 
 
 # ---------------------------------------------------------------------------------------------- wav2vec

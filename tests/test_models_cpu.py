@@ -217,6 +217,19 @@ def test_extra_encoders_rnn_transformer_wav2vec_parallel_expert():
             f2[0, :, 48:] += 1.0
             o3, _ = enc(audio_signal=f2, length=lens)
             assert torch.allclose(o3[0, :, :8], out[0, :, :8], atol=1e-4) and not torch.allclose(o3[0, :, 12:], out[0, :, 12:], atol=1e-4)
+    with pytest.raises(ValueError, match="below 16"):
+        TransformerEncoder(feat_in=32, d_model=64, n_heads=8, n_layers=1)
+    enc = TransformerEncoder(feat_in=32, d_model=64, n_heads=4, n_layers=1, subsampling="feature_stacking", subsampling_factor=4, feat_out=24,
+                             pos_emb_max_len=8).eval()
+    out, ol = enc(audio_signal=feats, length=lens)
+    assert out.shape == (2, 24, 16) and enc._feat_out == 24
+    enc.update_max_seq_length(400)
+    assert enc.max_audio_length == 100
+    enc.pos_bias_frozen = None
+    enc.layers[0].attn.pos_bias_u.requires_grad = False
+    enc.freeze()
+    enc.unfreeze(partial=True)
+    assert not enc.layers[0].attn.pos_bias_u.requires_grad and enc.layers[0].fc1.weight.requires_grad
     conv = ConvFeatureEncoder([{"emb_dim": 16, "kernel_size": 10, "stride": 5}, {"emb_dim": 16, "kernel_size": 3, "stride": 2}], embedding_dim=32)
     wav, wl = torch.randn(2, 1600), torch.tensor([1600, 1000])
     f, fl = conv(input_signal=wav, length=wl)
