@@ -95,8 +95,51 @@ class BatchedBeamHyps:
         return out
 
 
+class MALSDCarry:
+    """What MALSD keeps between two chunks of a stream: the beam, the prediction-network state and output of every entry, how far
+    an entry's time index ran past the end of the chunk (TDT durations may jump over it), language-model states, and the number of
+    encoder frames consumed so far (so that token frame indices stay global).  ``merge`` stacks the carries of several streams into
+    one batch and ``split`` undoes it, which lets a server batch whichever streams have a chunk ready."""
+
+    def __init__(self, hyps: BatchedBeamHyps, state, dec_proj: torch.Tensor, t_over: torch.Tensor, fstates: list, frame_offset: torch.Tensor):
+        self.hyps, self.state, self.dec_proj, self.t_over, self.fstates, self.frame_offset = hyps, state, dec_proj, t_over, fstates, frame_offset
+
+    @staticmethod
+    def merge(carries: "List[MALSDCarry]") -> "MALSDCarry":
+        h0 = carries[0].hyps
+        L = max(c.hyps.max_len for c in carries)
+        B = sum(c.hyps.B for c in carries)
+        hy = BatchedBeamHyps(B, h0.K, L, h0.tokens.device, h0.blank)
+        hy.max_len = L
+        pad = lambda t: torch.nn.functional.pad(t, (0, L - t.shape[-1]))  # noqa: E731
+        hy.tokens = torch.cat([pad(c.hyps.tokens) for c in carries], 0)
+        hy.frames = torch.cat([pad(c.hyps.frames) for c in carries], 0)
+        for name in ("lengths", "scores", "hash", "prev_hash", "last_label"):
+            setattr(hy, name, torch.cat([getattr(c.hyps, name) for c in carries], 0))
+        state = None
+        if carries[0].state is not None:
+            state = [torch.cat([c.state[i] for c in carries], dim=1) for i in range(len(carries[0].state))]
+        fst = [torch.cat([c.fstates[i] for c in carries], 0) for i in range(len(carries[0].fstates))]
+        return MALSDCarry(hy, state, torch.cat([c.dec_proj for c in carries], 0), torch.cat([c.t_over for c in carries], 0), fst,
+                          torch.cat([c.frame_offset for c in carries], 0))
+
+    def split(self) -> "List[MALSDCarry]":
+        out, K = [], self.hyps.K
+        for b in range(self.hyps.B):
+            hy = BatchedBeamHyps(1, K, self.hyps.max_len, self.hyps.tokens.device, self.hyps.blank)
+            hy.max_len = self.hyps.max_len
+            for name in ("tokens", "frames", "lengths", "scores", "hash", "prev_hash", "last_label"):
+                setattr(hy, name, getattr(self.hyps, name)[b:b + 1].clone())
+            state = None if self.state is None else [s[:, b * K:(b + 1) * K].clone() for s in self.state]
+            out.append(MALSDCarry(hy, state, self.dec_proj[b * K:(b + 1) * K].clone(), self.t_over[b:b + 1].clone(),
+                                  [f[b:b + 1].clone() for f in self.fstates], self.frame_offset[b:b + 1].clone()))
+        return out
+
+
 class ModifiedALSDBatchedComputer:
-    """MALSD beam search for RNNT (``durations`` empty) and TDT."""
+    """MALSD beam search for RNNT (``durations`` empty) and TDT.  Called with ``carry`` it continues a stream on its next chunk of
+    encoder frames and leaves the new carry in ``self.carry`` (``rnnt_malsd_batched_computer.py`` ``ModifiedALSDBatchedRNNTComputer``
+    called with a ``prev_batched_state``)."""
 
     def __init__(self, decoder, joint, blank_index: int, beam_size: int = 4, durations: Optional[List[int]] = None,
                  max_symbols_per_step: Optional[int] = 10, fusion_models=None, fusion_models_alpha=None,
@@ -112,8 +155,8 @@ class ModifiedALSDBatchedComputer:
         self.max_exp = max_expansions or beam_size
 
     @torch.no_grad()
-    def __call__(self, x: torch.Tensor, out_len: torch.Tensor) -> BatchedBeamHyps:
-        """x: [B, T, D_enc]; returns the final beam."""
+    def __call__(self, x: torch.Tensor, out_len: torch.Tensor, carry: Optional[MALSDCarry] = None) -> BatchedBeamHyps:
+        """x: [B, T, D_enc]; returns the final beam (of the whole stream so far when ``carry`` is given)."""
         B, T, _ = x.shape
         K, dev, dt = self.K, x.device, torch.float32
         enc = self.joint.project_encoder(x.to(dt))
@@ -121,16 +164,21 @@ class ModifiedALSDBatchedComputer:
         nd = len(self.durations)
         dur_t = torch.tensor(self.durations, device=dev, dtype=torch.long) if nd else None
         V1 = lin.out_features - nd
-        hyps = BatchedBeamHyps(B, K, init_length=T, device=dev, blank=self.blank)
-        dec_out, state = self.decoder.predict(None, state=None, add_sos=False, batch_size=B * K)
-        state = [s for s in state] if state is not None else None
-        dec_proj = self.joint.project_prednet(dec_out.to(dt))[:, 0]          # [B*K, H]
-        t_idx = torch.zeros((B, K), dtype=torch.long, device=dev)
-        sym = torch.zeros((B, K), dtype=torch.long, device=dev)              # labels emitted on the current frame
         out_len = out_len.to(dev)
+        if carry is None:
+            hyps = BatchedBeamHyps(B, K, init_length=T, device=dev, blank=self.blank)
+            dec_out, state = self.decoder.predict(None, state=None, add_sos=False, batch_size=B * K)
+            state = [s for s in state] if state is not None else None
+            dec_proj = self.joint.project_prednet(dec_out.to(dt))[:, 0]          # [B*K, H]
+            t_idx = torch.zeros((B, K), dtype=torch.long, device=dev)
+            fstates = [m.get_init_states(B * K, bos=True).view(B, K) for m in self.fusion_models]
+            frame_offset = torch.zeros(B, dtype=torch.long, device=dev)
+        else:
+            hyps, state, dec_proj, t_idx = carry.hyps, carry.state, carry.dec_proj, carry.t_over.clone()
+            fstates, frame_offset = list(carry.fstates), carry.frame_offset
+        sym = torch.zeros((B, K), dtype=torch.long, device=dev)              # labels emitted on the current frame
         last_t = (out_len - 1).clamp(min=0).view(B, 1)
         bidx = torch.arange(B, device=dev).view(B, 1).expand(B, K)
-        fstates = [m.get_init_states(B * K, bos=True).view(B, K) for m in self.fusion_models]
         E = min(self.max_exp, V1 - 1)
         for _ in range(int(T) * (self.max_symbols + 1) + 1):
             active = (t_idx < out_len.view(B, 1)) & (hyps.scores > NEG / 2)
@@ -185,7 +233,7 @@ class ModifiedALSDBatchedComputer:
             dur = torch.where(is_stay, torch.zeros_like(src), pick(cand_d.reshape(B, K * C)))
             emitted = (lab >= 0) & (lab != self.blank)
             old_t = t_idx.gather(1, src)
-            hyps.reorder_and_extend(src, lab, old_t, best_s)
+            hyps.reorder_and_extend(src, lab, old_t + frame_offset.view(B, 1), best_s)
             t_idx = old_t + dur
             sym = torch.where(dur > 0, torch.zeros_like(sym), sym.gather(1, src) + emitted.long())
             # prediction network: entries that emitted a label advance, the others keep the state of their source
@@ -207,6 +255,7 @@ class ModifiedALSDBatchedComputer:
                 fstates[i] = torch.where(emitted, adv, st_src)
             hyps.recombine(extra_key=t_idx)
         self.final_t = t_idx
+        self.carry = MALSDCarry(hyps, state, dec_proj, (t_idx - out_len.view(B, 1)).clamp(min=0), fstates, frame_offset + out_len)
         return hyps
 
 

@@ -201,7 +201,33 @@ class _CacheAwarePipeline(BasePipeline):
 
 
 class CacheAwareRNNTPipeline(_CacheAwarePipeline):
+    """Greedy by default; ``asr.decoding.strategy: malsd_batch`` (with ``asr.decoding.beam.beam_size``) keeps a beam per stream
+    between chunks, and the stream's running transcript is the beam's best entry."""
+
+    def __init__(self, cfg, asr_model):
+        super().__init__(cfg, asr_model)
+        self.malsd = None
+        if str(_get(self.cfg, "asr.decoding.strategy", "greedy_batch")) == "malsd_batch":
+            self.malsd = asr_model.build_malsd_computer(beam_size=int(_get(self.cfg, "asr.decoding.beam.beam_size", 4)),
+                                                        max_symbols_per_step=int(_get(self.cfg, "asr.decoding.beam.max_symbols_per_step", 10)))
+
+    def _decode_group_beam(self, feats, lens, ctx, states, drop_extra):
+        carries = [s.hypothesis for s in states]
+        for st in states:
+            if st.hypothesis is None:
+                st.extra["utt_base"] = st.frame_offset          # utterance-local frame indices are shifted to the stream's clock
+        best, new_ctx, enc_lens, new = self.asr_model.malsd_stream_step(self.malsd, feats, lens, ctx, carries, drop_extra_pre_encoded=drop_extra)
+        for st, (toks, frames, _), c in zip(states, best, new):
+            base = int(st.extra.get("utt_base", 0))
+            st.tokens, st.timesteps = [int(t) for t in toks], [int(f) + base for f in frames]
+            st.confidences = [1.0] * len(toks)
+            st.last_emit_frame = st.timesteps[-1] if toks else -1
+            st.hypothesis = c
+        return new_ctx, enc_lens
+
     def _decode_group(self, feats, lens, ctx, states, drop_extra):
+        if self.malsd is not None:
+            return self._decode_group_beam(feats, lens, ctx, states, drop_extra)
         prev = [s.hypothesis for s in states]
         prev = prev if any(p is not None for p in prev) else None
         hyps, new_ctx, enc_lens, _ = self.asr_model.stream_step(feats, lens, ctx, previous_hypotheses=prev,
@@ -410,9 +436,16 @@ class PipelineBuilder:
             _get(cfg, "asr.compute_dtype", None) if _get(cfg, "asr.compute_dtype", None) in ("bfloat16", "float16") else None]
         device = _get(cfg, "asr.device", None)
         if kind == "cache_aware":
-            w = CacheAwareASRInferenceWrapper(asr_model, device, dtype, _get(cfg, "asr.decoding", None),
-                                              _get(cfg, "streaming.att_context_size", None))
-            dec = _get(cfg, "asr_decoding_type", None) or w.decoder_type
+            from ..models.ctc_models import EncDecCTCModel
+            from .wrappers import CacheAwareCTCInferenceWrapper, CacheAwareRNNTInferenceWrapper
+
+            dec = (_get(cfg, "asr_decoding_type", None) or getattr(asr_model, "cur_decoder", None)
+                   or ("ctc" if isinstance(asr_model, EncDecCTCModel) else "rnnt"))
+            dcfg = _get(cfg, "asr.decoding", None)
+            if dec == "rnnt" and dcfg is not None and str(_get(cfg, "asr.decoding.strategy", "")) == "malsd_batch":
+                dcfg = None                        # the pipeline owns the beam search; the model's own decoding stays greedy
+            w = (CacheAwareRNNTInferenceWrapper if dec == "rnnt" else CacheAwareCTCInferenceWrapper)(
+                asr_model, device, dtype, dcfg, _get(cfg, "streaming.att_context_size", None))
             return (CacheAwareRNNTPipeline if dec == "rnnt" else CacheAwareCTCPipeline)(cfg, w)
         if kind == "buffered":
             w = ASRInferenceWrapper(asr_model, device, dtype, _get(cfg, "asr.decoding", None))

@@ -146,7 +146,46 @@ class CacheAwareASRInferenceWrapper(ASRInferenceWrapper):
 
 
 class CacheAwareRNNTInferenceWrapper(CacheAwareASRInferenceWrapper):
-    pass
+    def build_malsd_computer(self, beam_size: int = 4, max_symbols_per_step: int = 10, fusion_models=None, fusion_models_alpha=None):
+        """A batched beam-search computer over this model's prediction and joint networks (TDT durations picked up from the
+        model's decoding config)."""
+        from ..decoding.batched_beam import ModifiedALSDBatchedComputer
+
+        m = self.asr_model
+        durations = list(getattr(m.decoding, "durations", None) or [])
+        return ModifiedALSDBatchedComputer(m.decoder, m.joint, self.blank_id, beam_size=beam_size, durations=durations,
+                                           max_symbols_per_step=max_symbols_per_step, fusion_models=fusion_models,
+                                           fusion_models_alpha=fusion_models_alpha)
+
+    @torch.no_grad()
+    def malsd_stream_step(self, malsd_computer, features: torch.Tensor, lengths: torch.Tensor, context: CacheAwareContext, carries: list,
+                          drop_extra_pre_encoded: Optional[int] = None):
+        """One chunk for a batch of streams under beam search.  ``carries[i]`` is stream i's beam state from its previous chunk
+        (``None`` at the start of an utterance).  Returns ``(best, new_context, encoded_len, new_carries)`` with
+        ``best[i] = (tokens, frame indices within the utterance, score)`` of the currently best entry of stream i's beam — the
+        whole utterance so far, not only this chunk, because the best entry may change.
+        Reference: ``inference/model_wrappers/cache_aware_rnnt_inference_wrapper.py`` ``malsd_stream_step``."""
+        from ..decoding.batched_beam import MALSDCarry
+
+        m = self.asr_model
+        with self.autocast(), ops.compute_dtype(ops.get_compute_dtype()):
+            encoded, encoded_len, clc, clt, clcl = m.encoder.cache_aware_stream_step(
+                processed_signal=features.to(self.device), processed_signal_length=lengths.to(self.device),
+                cache_last_channel=context.cache_last_channel, cache_last_time=context.cache_last_time,
+                cache_last_channel_len=context.cache_last_channel_len, keep_all_outputs=False, drop_extra_pre_encoded=drop_extra_pre_encoded)
+        enc = encoded.transpose(1, 2).float()
+        fresh = [i for i, c in enumerate(carries) if c is None]
+        if fresh:                                  # open a beam for the streams that start an utterance: zero frames decode nothing
+            sub = torch.tensor(fresh, device=enc.device)
+            malsd_computer(enc[sub, :0], torch.zeros(len(fresh), dtype=torch.long, device=enc.device))
+            opened = malsd_computer.carry.split()
+            carries = list(carries)
+            for i, c in zip(fresh, opened):
+                carries[i] = c
+        hyps = malsd_computer(enc, encoded_len, MALSDCarry.merge(carries))
+        new_carries = malsd_computer.carry.split()
+        best = [h[0] if h else ([], [], 0.0) for h in hyps.to_hyps_list(score_norm=malsd_computer.score_norm)]
+        return best, CacheAwareContext(clc, clt, clcl), encoded_len, new_carries
 
 
 class CacheAwareCTCInferenceWrapper(CacheAwareASRInferenceWrapper):

@@ -124,6 +124,45 @@ def test_malsd_beam_one_equals_greedy_and_wider_beam_is_not_worse():
         assert max(s for _, _, s in h4[b]) >= h1[b][0][2] - 1e-4
 
 
+@pytest.mark.parametrize("loss", ["rnnt", "tdt"])
+def test_malsd_continues_a_stream_chunk_by_chunk_with_a_carry(loss):
+    from speech_b200.decoding.batched_beam import MALSDCarry
+    from speech_b200.models import EncDecRNNTBPEModel
+    from speech_b200.models.configs import fastconformer_transducer_config
+
+    torch.manual_seed(2)
+    m = EncDecRNNTBPEModel(fastconformer_transducer_config("small", vocab_size=16, loss=loss, dropout=0.0, n_layers=1, sched=None, lr=1e-3)).eval()
+    durations = [0, 1, 2, 3, 4] if loss == "tdt" else []
+    blank = m.decoding.blank_id
+    enc = torch.randn(2, 12, 176)
+    lens = torch.tensor([12, 12])
+    mk = lambda k: ModifiedALSDBatchedComputer(m.decoder, m.joint, blank, beam_size=k, durations=durations, max_symbols_per_step=5)  # noqa: E731
+    # beam 1 follows one path, so cutting the stream into chunks cannot change it
+    whole = mk(1)(enc, lens).to_hyps_list(score_norm=False)
+    comp, carry = mk(1), None
+    for a, b in ((0, 5), (5, 6), (6, 12)):
+        hy = comp(enc[:, a:b], torch.tensor([b - a, b - a]), carry)
+        carry = comp.carry
+    chunked = hy.to_hyps_list(score_norm=False)
+    for b in range(2):
+        assert chunked[b][0][0] == whole[b][0][0] and chunked[b][0][1] == whole[b][0][1]        # tokens and global frame indices
+        assert chunked[b][0][2] == pytest.approx(whole[b][0][2], abs=1e-4)
+    assert carry.frame_offset.tolist() == [12, 12]
+    # streams decoded in one merged batch give what each gives alone; split returns their own carries
+    comp4 = mk(3)
+    comp4(enc[:, :6], torch.tensor([6, 6]))
+    c0, c1 = comp4.carry.split()
+    alone = []
+    for c, row in ((c0, 0), (c1, 1)):
+        alone.append(comp4(enc[row:row + 1, 6:], torch.tensor([6]), c).to_hyps_list(score_norm=False)[0])
+    comp4(enc[:, :6], torch.tensor([6, 6]))
+    both = comp4(enc[:, 6:], torch.tensor([6, 6]), MALSDCarry.merge(comp4.carry.split())).to_hyps_list(score_norm=False)
+    for row in range(2):
+        assert [h[0] for h in both[row]] == [h[0] for h in alone[row]]
+        frames = both[row][0][1]
+        assert frames == sorted(frames) and all(0 <= f < 12 for f in frames)
+
+
 def test_lcs_merge_and_word_spotter():
     i, j, n, _ = longest_common_subsequence_merge([5, 6, 7, 8, 9], [8, 9, 10, 11])
     assert (i, j, n) == (3, 0, 2)

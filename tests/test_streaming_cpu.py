@@ -102,6 +102,30 @@ def test_cache_aware_pipeline_matches_offline_limited_context(kind):
     assert pipe.rtfx() > 0
 
 
+def test_cache_aware_rnnt_pipeline_with_a_beam_carried_between_chunks():
+    torch.manual_seed(0)
+    enc_over = dict(n_layers=2, causal=True, att_context_size=[8, 1], att_context_style="chunked_limited", conv_norm_type="layer_norm")
+    model = EncDecRNNTBPEModel(_streaming_overrides(fastconformer_transducer_config(
+        "small", vocab_size=32, loss="rnnt", dropout=0.0, sched=None, lr=1e-3, **enc_over))).eval()
+    audios = [_audio(16000 * 2 + 320, 1), _audio(16000 + 4000, 2), _audio(16000 * 3, 3)]
+
+    def run(beam):
+        pipe = PipelineBuilder.build_pipeline({"pipeline_type": "cache_aware", "streaming": {"batch_size": 2, "num_slots": 4},
+                                               "endpointing": {"stop_history_eou": 100000},
+                                               "asr": {"decoding": {"strategy": "malsd_batch", "beam": {"beam_size": beam}}}}, asr_model=model)
+        assert pipe.malsd is not None and pipe.malsd.K == beam
+        return pipe.run(audios)
+
+    greedy = PipelineBuilder.build_pipeline({"pipeline_type": "cache_aware", "streaming": {"batch_size": 2, "num_slots": 4},
+                                             "endpointing": {"stop_history_eou": 100000}}, asr_model=model).run(audios)
+    one, four = run(1), run(4)
+    for i in range(3):
+        assert one[i].text == greedy[i].text, i                # a beam of one is the greedy path, chunk boundaries included
+        assert isinstance(four[i].text, str)
+        times = [w.start for w in four[i].words]
+        assert times == sorted(times)
+
+
 def test_cache_aware_pipeline_full_batch_in_slot_order_skips_the_gather():
     """A batch that holds every slot in order reads the resident caches directly; the tokens equal the offline ones."""
     torch.manual_seed(0)
