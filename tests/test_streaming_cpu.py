@@ -284,3 +284,54 @@ def test_buffered_salm_pipeline_merges_window_transcripts_by_overlap():
     assert out[1].text == "zero one two three four"
     # the first step sees one second, later steps the two-second window
     assert pipe.salm.calls[0] == (16000, 16000) and pipe.salm.calls[1] == (32000, 32000)
+
+
+def test_alignment_preserving_itn_keeps_word_times_and_merges_punctuation():
+    from speech_b200.inference.state import Word
+    from speech_b200.inference.text_postprocess import (AlignmentPreservingInverseNormalizer, BatchAlignmentPreservingInverseNormalizer,
+                                                        merge_punctuation_and_itn)
+
+    itn = AlignmentPreservingInverseNormalizer()
+    words = "it costs twenty five dollars and the third one is fifty percent off".split()
+    src, out, spans = itn.get_word_alignment(words)
+    assert out == "it costs $25 and the 3rd one is 50% off".split()
+    assert (2, 5, 2, 3) in spans and (7, 8, 5, 6) in spans and (10, 12, 8, 9) in spans
+    assert sorted(i for a, b, _, _ in spans for i in range(a, b)) == list(range(len(words)))       # a partition of the input
+    assert sorted(o for _, _, a, b in spans for o in range(a, b)) == list(range(len(out)))         # and of the output
+    ws = [Word(text=w, start=0.5 * i, end=0.5 * i + 0.4, conf=0.9 if w != "five" else 0.5) for i, w in enumerate(words)]
+    new = itn.apply_to_words(ws)
+    price = next(w for w in new if w.text == "$25")
+    assert price.start == 1.0 and price.end == pytest.approx(2.4) and price.conf == 0.5
+    pnc = "It costs twenty five dollars, and the third one is fifty percent off.".split()
+    assert merge_punctuation_and_itn(pnc, out, spans) == "It costs $25, and the 3rd one is 50% off.".split()
+    batch = BatchAlignmentPreservingInverseNormalizer(itn, n_jobs=2)([ws, ws[:2]], [pnc, None])
+    assert [w.text for w in batch[0]] == "It costs $25, and the 3rd one is 50% off.".split() and [w.text for w in batch[1]] == ["it", "costs"]
+
+
+def test_llm_translator_continues_a_stable_prefix():
+    from speech_b200.inference.text_postprocess import LLMTranslator, TranslationPrompt
+
+    seen = []
+
+    def engine(prompts):
+        seen.extend(prompts)
+        # a toy "model": continues the prefix with upper-cased source words it has not produced yet
+        outs = []
+        for p in prompts:
+            src = p.split("English: ")[1].split("\n")[0].split()
+            prefix = p.split("assistant\n")[1]
+            done = len(prefix.split())
+            outs.append((" " if prefix else "") + " ".join(w.upper() for w in src[done:]) + "<|im_end|> ignored")
+        return outs
+
+    tr = LLMTranslator(engine, waitk=2, batch_size=1)
+    t1 = tr.translate(["hello my"], [""], ["en"], ["de"])
+    assert t1 == ["HELLO MY"] and "Translate the following English source text to German" in seen[0] and seen[0].endswith("assistant\n")
+    assert TranslationPrompt.extract("abc\ndef") == "abc"
+    # the next step agrees with the previous one on "HELLO M": cut back to the word boundary
+    assert tr.get_prefixes(["hello my dear"], ["HELLO MX DEAR"], ["HELLO MY"]) == ["HELLO"]
+    # the translations disagree from the start while the transcript has 6 words: the prefix is forced to 6 - waitk words
+    assert tr.get_prefixes(["a b c d e f"], ["U V W X Y Z"], ["K L"]) == ["U V W X"]
+    assert tr.get_prefixes([""], ["HALLUCINATION"], ["HALLUCINATION"]) == [""]
+    t2 = tr.translate(["hello my dear friend"], ["HELLO"], ["en"], ["de"])
+    assert t2 == ["HELLO MY DEAR FRIEND"]
