@@ -219,3 +219,48 @@ def test_transformer_unet_shapes_padding_and_time_conditioning():
     assert not torch.allclose(y3, y4, atol=1e-4)
     y4.abs().sum().backward()
     assert net.proj_in.weight.grad is not None
+
+
+def test_audio_metrics_wrapper_stoi_and_reference_free_estimates():
+    from speech_b200.audio.metrics import AudioMetricWrapper, QualityEstimator, SquimMOSMetric, SquimObjectiveMetric, stoi
+    from speech_b200.audio.modules import si_sdr
+
+    torch.manual_seed(0)
+    t = torch.arange(32000) / 16000.0
+    # speech-like: a carrier with a slow envelope, so that band envelopes carry information
+    clean = torch.sin(2 * math.pi * 220 * t) * (0.6 + 0.4 * torch.sin(2 * math.pi * 3 * t)) + 0.5 * torch.sin(2 * math.pi * 1300 * t) * (0.5 + 0.5 * torch.sin(2 * math.pi * 5 * t + 1))
+    noise = torch.randn_like(clean)
+    s_clean, s_mild, s_bad = float(stoi(clean, clean)), float(stoi(clean + 0.05 * noise, clean)), float(stoi(clean + 2.0 * noise, clean))
+    assert s_clean > 0.999 and s_clean > s_mild > s_bad and s_bad < 0.8
+    assert float(stoi(clean + 0.05 * noise, clean, extended=True)) > float(stoi(clean + 2.0 * noise, clean, extended=True))
+    # wrapper: channel selection and per-example trimming
+    tgt = torch.randn(2, 2, 4000)
+    est = tgt + 0.1 * torch.randn(2, 2, 4000)
+    est[1, :, 3000:] = 100.0                                          # garbage beyond the valid length of example 1
+    lens = torch.tensor([4000, 3000])
+    m = AudioMetricWrapper(lambda p, t_: si_sdr(p.unsqueeze(1), t_.unsqueeze(1)).squeeze(1), channel=1)
+    m.update(est, tgt, lens)
+    assert 15.0 < float(m.compute()) < 25.0
+    with pytest.raises(RuntimeError):
+        AudioMetricWrapper(lambda p, t_: p.sum(), channel=3).update(est, tgt)
+    # reference-free: the estimator learns to rank a clean and a noisy signal by SI-SDR and STOI
+    qe = QualityEstimator(d_model=32, n_layers=1, n_heads=2)
+    x = torch.stack([clean[:8000], clean[:8000] + 1.0 * noise[:8000]])
+    labels = {"si_sdr": torch.tensor([30.0, 0.0]), "stoi": torch.tensor([1.0, 0.5])}
+    opt = torch.optim.Adam(qe.parameters(), 3e-3)
+    for _ in range(60):
+        opt.zero_grad()
+        qe.training_loss(x, labels).backward()
+        opt.step()
+    qe.eval()
+    obj = SquimObjectiveMetric(16000, "si_sdr", estimator=qe)
+    obj.update(x[:1])
+    hi = float(obj.compute())
+    obj.reset()
+    obj.update(x[1:])
+    assert hi > float(obj.compute()) + 5.0
+    mos = SquimMOSMetric(8000, estimator=qe)
+    mos.update(x[:, ::2], x[:, ::2])
+    assert 1.0 <= float(mos.compute()) <= 5.0 and mos.state_dict() == {}
+    with pytest.raises(ValueError):
+        SquimObjectiveMetric(16000, "mos")
