@@ -505,3 +505,61 @@ def test_audio_codec_model_with_causal_decoder_slm_discriminator_and_hinged_loss
     a, st = m.decode_stream(toks[..., :150])
     b, st = m.decode_stream(toks[..., 150:], st)
     assert torch.allclose(torch.cat([a, b], -1), full, atol=1e-5)
+
+
+def test_ipa_pinyin_and_kana_g2p(tmp_path):
+    from speech_b200.tts.g2p import ChineseG2p, IpaG2p, JapaneseG2p, phoneme_error_rate
+
+    p = tmp_path / "ipa.txt"
+    p.write_text("HELLO\thəˈloʊ\nWORLD\tˈwɝld\nREAD\tˈɹid, ˈɹɛd\nCAT\tˈkæt\nWELL\tˈwɛl\nKNOWN\tˈnoʊn\nT͡ʃIP\tt͡ʃɪp\n", encoding="utf-8")
+    g = IpaG2p(str(p), heteronyms=["read"], grapheme_prefix="#")
+    assert g("hello world") == ["h", "ə", "ˈ", "l", "o", "ʊ", " ", "ˈ", "w", "ɝ", "l", "d"]
+    assert g("read")[:2] == ["#R", "#E"]                               # heteronym: left as (prefixed) graphemes
+    assert g("cat's cats")[:5] == ["ˈ", "k", "æ", "t", "s"] and g("cat's cats")[-1] == "s"
+    assert g("well-known") == ["ˈ", "w", "ɛ", "l", "-", "ˈ", "n", "o", "ʊ", "n"]
+    assert g("xyzzy!") == ["#X", "#Y", "#Z", "#Z", "#Y", "!"]          # unknown word spelled, punctuation kept
+    assert IpaG2p.split_ipa("t͡ʃɪːp") == ["t͡ʃ", "ɪː", "p"]
+    nostress = IpaG2p(str(p), use_stresses=False)
+    assert "ˈ" not in nostress("hello")
+    amb = IpaG2p({"read": ["ɹid", "ɹɛd"]}, ignore_ambiguous_words=False, grapheme_case="lower")
+    assert amb("read") == ["ɹ", "i", "d"]
+    amb.replace_symbols(["ɹ", "ɛ", "d"])
+    assert amb("read") == ["ɹ", "ɛ", "d"]
+    zh = ChineseG2p({"你好": "ni3 hao3", "世": "shi4", "界": "jie4"})
+    assert zh("你好世界 OK") == ["n", "i", "#3", "h", "ao", "#3", "sh", "i", "#4", "j", "ie", "#4", " ", "O", "K"]
+    ja = JapaneseG2p()
+    assert ja("きょう") == ["k", "j", "o", "ɯ"] and ja("ガッコー") == ["g", "a", "k", "k", "oː"] and ja("シャ") == ["ɕ", "a"]
+    with pytest.raises(ValueError):
+        ja("今日")
+    assert JapaneseG2p(kana_reader=lambda s: "キョウ")("今日") == ["k", "j", "o", "ɯ"]
+    assert phoneme_error_rate([["a", "b"]], [["a", "c", "d"]]) == pytest.approx(2 / 3)
+
+
+@pytest.mark.parametrize("kind", ["ctc", "seq2seq"])
+def test_neural_g2p_models_learn_a_toy_lexicon(kind, tmp_path):
+    import json
+
+    from speech_b200.tts.g2p import CTCG2PModel, Seq2SeqG2PModel
+
+    torch.manual_seed(0)
+    lex = [("cat", "k æ t"), ("tack", "t æ k"), ("act", "æ k t"), ("box", "b ɑ k s"), ("tax", "t æ k s"), ("cab", "k æ b")]
+    phon = sorted({p for _, s in lex for p in s.split()})
+    cfg = OmegaConf.create({"phonemes": phon, "d_model": 32, "n_layers": 1, "n_heads": 2, "upsample": 2,
+                            "train_ds": {"examples": [[g, p] for g, p in lex], "batch_size": 6, "shuffle": False}})
+    m = (CTCG2PModel if kind == "ctc" else Seq2SeqG2PModel)(cfg)
+    opt = torch.optim.Adam(m.parameters(), 5e-3)
+    batch = next(iter(m._train_dl))
+    first = None
+    for _ in range(150):
+        opt.zero_grad()
+        loss = m.training_step(batch, 0)["loss"]
+        loss.backward()
+        opt.step()
+        first = first if first is not None else float(loss)
+    assert float(loss) < 0.2 * first
+    assert m.predict(["cat", "box"]) == [["k", "æ", "t"], ["b", "ɑ", "k", "s"]]       # "box": more phonemes than letters
+    assert float(m.validation_step(batch, 0)["val_per"]) == 0.0
+    src, dst = tmp_path / "in.json", tmp_path / "out.json"
+    src.write_text("\n".join(json.dumps({"text_graphemes": g}) for g, _ in lex[:3]), encoding="utf-8")
+    preds = m.convert_graphemes_to_phonemes(str(src), str(dst))
+    assert preds == [s for _, s in lex[:3]] and json.loads(dst.read_text(encoding="utf-8").splitlines()[1])["pred_text"] == "t æ k"
