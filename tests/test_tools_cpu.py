@@ -161,3 +161,66 @@ def test_voice_agent_websocket_transport_and_server_app():
     assert mod.make_llm(cfg)([{"role": "user", "content": "ping"}]) == "You said: ping"
     wav, rate = mod.make_tts(cfg)("two words")
     assert rate == 22050 and len(wav) == 2 * (int(0.12 * 22050) + int(0.05 * 22050))
+
+
+def test_ctc_segmentation_finds_utterances_inside_a_long_recording(tmp_path):
+    import json
+
+    import numpy as np
+
+    from speech_b200.data.audio_to_text import save_wav
+    from speech_b200.decoding.ctc_segmentation import add_metrics, ctc_segment, cut_audio, filter_manifest, read_segments, split_text, write_segments
+
+    orig, norm = split_text("Mr. Smith (laughs) paid 3 dollars.  Then he left!  A very long sentence that goes on, and on and on without end, yes.",
+                            list("abcdefghijklmnopqrstuvwxyz' "), max_length=8, number_to_words=lambda d: {"3": "three"}[d])
+    assert norm[0] == "mister smith paid three dollars" and norm[1] == "then he left" and len(norm) == 4 and orig[1] == "Then he left!"
+    assert norm[2].endswith("goes on") and all(len(n.split()) <= 8 for n in norm)
+
+    # synthetic posteriors: 40 frames of noise, utterance A, 30 frames of noise, utterance B (poorly matching), 25 frames of noise
+    V, blank = 6, 5
+    rng = np.random.default_rng(0)
+    utt = [[0, 1, 2, 1], [3, 4, 3]]
+
+    def render(tokens, conf):
+        rows = []
+        for t in tokens:
+            for _ in range(3):
+                r = np.full(V, (1 - conf) / (V - 1))
+                r[t] = conf
+                rows.append(r)
+            r = np.full(V, 0.02)
+            r[blank] = 0.9
+            rows.append(r)
+        return rows
+
+    def noise(n):
+        r = np.full((n, V), 0.02)
+        r[:, blank] = 0.9
+        return list(r)
+
+    probs = np.array(noise(40) + render(utt[0], 0.9) + noise(30) + render(utt[1], 0.3) + noise(25))
+    probs = probs / probs.sum(-1, keepdims=True)
+    segs = ctc_segment(torch.tensor(np.log(probs)), utt, blank, frame_duration=0.04, score_window=6, texts=["a b c b", "d e d"])
+    assert abs(segs[0].start - 40 * 0.04) <= 0.04 and abs(segs[0].end - 55 * 0.04) <= 0.08
+    assert abs(segs[1].start - 86 * 0.04) <= 0.04 and segs[1].end <= (86 + 12) * 0.04 + 1e-6
+    assert segs[0].score > -0.5 and segs[1].score < segs[0].score - 0.5          # the badly matching utterance scores low
+
+    wav = tmp_path / "long.wav"
+    save_wav(str(wav), (0.1 * rng.standard_normal(int(123 * 0.04 * 16000))).astype(np.float32), 16000)
+    seg_file = tmp_path / "long_segments.txt"
+    write_segments(str(seg_file), str(wav), segs, ["A b c b.", "D e d!"])
+    path, back, orig2 = read_segments(str(seg_file))
+    assert path == str(wav) and orig2 == ["A b c b.", "D e d!"] and back[0].text == "a b c b"
+    manifests = cut_audio(str(seg_file), str(tmp_path / "out"), threshold=-0.8)
+    rows = {k: [json.loads(l) for l in open(p)] for k, p in manifests.items()}
+    assert len(rows["clips"]) == 1 and len(rows["low_score_clips"]) == 1 and len(rows["deleted_clips"]) == 3
+    assert abs(rows["clips"][0]["duration"] - (segs[0].end - segs[0].start)) < 0.01 and os.path.exists(rows["clips"][0]["audio_filepath"])
+    total = sum(r["duration"] for rs in rows.values() for r in rs)
+    assert abs(total - 123 * 0.04) < 0.05                                          # nothing of the recording is lost
+    m2, m3 = str(tmp_path / "m2.json"), str(tmp_path / "m3.json")
+    both = tmp_path / "both.json"
+    both.write_text(open(manifests["clips"]).read() + open(manifests["low_score_clips"]).read())
+    got = add_metrics(str(both), m2, transcribe=lambda paths: ["a b c b", "x y z"])
+    assert got[0]["WER"] == 0.0 and got[1]["WER"] == 100.0 and got[1]["start_CER"] > 0
+    kept, dropped = filter_manifest(m2, m3, min_duration=0.1)
+    assert kept > 0 and dropped > 0 and len(open(m3).read().splitlines()) == 1
