@@ -250,6 +250,24 @@ class EncDecMultiTalkerRNNTBPEModel(EncDecRNNTBPEModel):
         finally:
             self.set_speaker_targets(None)
 
+    def validation_pass(self, batch, batch_idx, dataloader_idx=0):
+        if len(batch) > 4:
+            self.set_speaker_targets(batch[4], batch[5] if len(batch) > 5 else None)
+        try:
+            return super().validation_pass(batch[:4], batch_idx, dataloader_idx)
+        finally:
+            self.set_speaker_targets(None)
+
+    @torch.no_grad()
+    def transcribe_with_speaker_targets(self, audio: torch.Tensor, lens: torch.Tensor, spk_targets: torch.Tensor,
+                                        bg_spk_targets: Optional[torch.Tensor] = None):
+        """Hypotheses of the speaker whose activity is ``spk_targets`` [B, T'] (``multitalker_asr_models.py`` ``_transcribe_forward``)."""
+        self.set_speaker_targets(spk_targets, bg_spk_targets)
+        try:
+            return self._transcribe_forward_and_decode(audio, lens, None)
+        finally:
+            self.set_speaker_targets(None)
+
 
 # ---------------------------------------------------------------------------------------------- confidence ensemble
 def entropy_confidence(log_probs: torch.Tensor, alpha: float = 0.33, kind: str = "tsallis") -> torch.Tensor:

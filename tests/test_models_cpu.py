@@ -301,3 +301,62 @@ def test_transformer_decoder_translation_model_trains_decodes_and_scores_bleu(tm
     assert len(hyps) == 2 and all(isinstance(h.text, str) for h in hyps)
     with pytest.raises(ValueError, match="either input_signal"):
         m.forward()
+
+
+def test_speaker_tagged_asr_offline_streaming_and_speaker_target_data(tmp_path):
+    import json
+
+    from speech_b200.core.config import open_dict
+    from speech_b200.models.multitalker import (SpeakerTaggedASR, SpeakerTargetDataset, find_active_speakers, get_simulated_softmax, mask_features,
+                                                sentences_from_words, write_seglst)
+
+    torch.manual_seed(0)
+    cfg = fastconformer_transducer_config("small", vocab_size=16, loss="rnnt", dropout=0.0, n_layers=2, sched=None, lr=1e-3, causal=True,
+                                          att_context_size=[8, 1], att_context_style="chunked_limited", conv_norm_type="layer_norm")
+    with open_dict(cfg):
+        cfg.preprocessor.normalize, cfg.preprocessor.dither, cfg.preprocessor.pad_to = "NA", 0.0, 0
+    asr = EncDecMultiTalkerRNNTBPEModel(cfg).eval()
+    audio = torch.randn(1, 32000) * 0.1
+    lens = torch.tensor([32000])
+    Tp = 26
+    diar = torch.zeros(1, Tp, 4)
+    diar[0, :14, 0] = 0.9                  # speaker 0 talks first
+    diar[0, 10:, 2] = 0.8                  # speaker 2 joins later, overlapping
+    assert find_active_speakers(diar, 0.5, 3) == [[2, 0]] and find_active_speakers(diar, 0.5, 15) == [[2]]
+    p = get_simulated_softmax(torch.tensor([0.9, 0.001, 0.6, 0.3]), limit_max_spks=3)
+    assert float(p.sum()) == pytest.approx(1.0) and float(p[3]) == 0.0 and float(p[1]) > 0
+    feats = torch.randn(1, 80, 200)
+    masked = mask_features(feats, diar[:, :, 0], subsampling=8)
+    assert torch.equal(masked[0, :, :112], feats[0, :, :112]) and bool((masked[0, :, 112:] == feats.min()).all())
+    tagger = SpeakerTaggedASR(asr, lambda a, l: diar, max_gap=0.5)
+    seglst = tagger.transcribe_offline(audio, lens, ["meeting"])
+    assert {d["speaker"] for d in seglst} <= {"speaker_0", "speaker_2"} and all(d["session_id"] == "meeting" and d["end_time"] >= d["start_time"] for d in seglst)
+    # the target mask matters: another speaker's mask changes the encoder output
+    asr.set_speaker_targets(diar[:, :, 0], diar[:, :, 2])
+    e0, _ = asr.forward(input_signal=audio, input_signal_length=lens)
+    asr.set_speaker_targets(diar[:, :, 2], diar[:, :, 0])
+    e2, _ = asr.forward(input_signal=audio, input_signal_length=lens)
+    asr.set_speaker_targets(None)
+    assert not torch.allclose(e0, e2)
+    hyps = asr.transcribe_with_speaker_targets(audio, lens, diar[:, :, 0], diar[:, :, 2])
+    assert len(hyps) == 1 and asr._spk_targets is None
+    streamed = tagger.stream(audio[0], diar[0])
+    assert tagger.manager.get_speakers() == [0, 2] and tagger.manager.instances[2].start_offset > 0
+    for d in streamed:
+        assert d["speaker"] in ("speaker_0", "speaker_2") and 0.0 <= d["start_time"] <= d["end_time"] <= 2.3
+    words = [{"word": "hi", "start_time": 0.0, "end_time": 0.2}, {"word": "there.", "start_time": 0.3, "end_time": 0.6},
+             {"word": "so", "start_time": 0.7, "end_time": 0.8}, {"word": "late", "start_time": 3.0, "end_time": 3.3}]
+    sents = sentences_from_words(words, "s", "speaker_1", max_gap=1.0)
+    assert [x["words"] for x in sents] == ["hi there.", "so", "late"] and sents[0]["end_time"] == 0.6
+    write_seglst(str(tmp_path / "out.seglst.json"), sents)
+    assert json.load(open(tmp_path / "out.seglst.json"))[2]["words"] == "late"
+    ds = SpeakerTargetDataset([{"audio": np.zeros(16000, dtype=np.float32),
+                                "segments": [{"speaker": "A", "start": 0.0, "end": 0.4, "text": "ab"}, {"speaker": "B", "start": 0.32, "end": 0.8, "text": "cd"},
+                                             {"speaker": "A", "start": 0.8, "end": 1.0, "text": "ef"}]}], asr.tokenizer, deterministic=True)
+    batch = SpeakerTargetDataset.collate([ds[0], ds[0]])
+    assert batch[4].shape == (2, 13) and batch[4][0].tolist() == [1.0] * 5 + [0.0] * 5 + [1.0] * 2 + [0.0] and batch[5][0].tolist() == [0.0] * 4 + [1.0] * 6 + [0.0] * 3
+    asr.train()
+    out = asr.training_step(batch, 0)
+    assert torch.isfinite(out["loss"])
+    asr.eval()
+    assert "val_wer" in asr.validation_pass(batch, 0)
