@@ -542,3 +542,51 @@ def test_salm_with_asr_decoder_reads_the_recognisers_hypotheses():
     m.asr_transcript_drop_prob = 1.0
     short = m.prepare_inputs(batch)
     assert short["input_embeds"].shape[1] <= inp["input_embeds"].shape[1] and m.last_asr_hypotheses == ["", ""]
+
+
+def test_rvq_vae_codec_round_trip_streaming_decode_and_training():
+    from speech_b200.speechlm.vae_codec import ProbabilisticRVQ, RVQVAEModel
+
+    torch.manual_seed(0)
+    cfg = dict(latent_size=16, n_fft=16, hop_length=4, base_hidden_size=8, channel_mult=(1, 2), rates=(2, 2), num_blocks=1, kernel_size=3,
+               codebook_size=32, num_quantizers=3)
+    m = RVQVAEModel(cfg).eval()
+    assert m.wav_to_token_ratio == 16 and not any(p.requires_grad for p in m.parameters())
+    wav = torch.randn(2, 1, 16 * 20) * 0.1
+    with pytest.raises(ValueError, match="multiple"):
+        m.ae_encode(wav[..., :-3])
+    assert m.pad_to_ratio(wav[..., :-3]).shape[-1] == 320
+    ids = m.encode(wav)
+    assert len(ids) == 3 and ids[0].shape == (2, 20) and int(ids[0].max()) < 32
+    full = m.decode(ids)
+    assert full.shape == (2, 1, 320) and float(full.abs().max()) <= 1.0
+    # residual quantisation: every level lowers the error
+    z = m.ae_encode(wav)
+    errs = [float((z - m.prvq.decode(ids[: k + 1])).pow(2).mean()) for k in range(3)]
+    assert errs[0] >= errs[1] >= errs[2]
+    # causal: decode in chunks of latents equals the one-shot decode; later latents do not change earlier samples
+    zq = m.prvq.decode(ids)
+    state, outs = None, []
+    for a, b in ((0, 7), (7, 8), (8, 20)):
+        y, state = m.decode_stream(zq[:, a:b], state)
+        outs.append(y)
+    assert torch.allclose(torch.cat(outs, -1), full, atol=1e-5)
+    z2 = zq.clone()
+    z2[:, 12:] += 1.0
+    assert torch.allclose(m.ae_decode(z2)[..., : 12 * 16], full[..., : 12 * 16], atol=1e-6)
+    # training: reconstruction improves, codebooks move toward the latents, variance tracks the residual
+    t = RVQVAEModel(cfg, trainable=True).train()
+    sig = torch.sin(torch.arange(320) * 0.2)[None, None].repeat(2, 1, 1) * 0.5
+    opt = torch.optim.Adam([p for p in t.parameters() if p.requires_grad], 3e-3)
+    v0 = t.prvq.variance.clone()
+    first = None
+    for _ in range(40):
+        opt.zero_grad()
+        out = t.training_loss(sig)
+        out["loss"].backward()
+        opt.step()
+        first = first if first is not None else float(out["loss"])
+    assert float(out["loss"]) < 0.7 * first and not torch.equal(t.prvq.variance, v0)
+    assert float(ProbabilisticRVQ(8, 4, 2).log_std) == 0.0
+    audio, alen = m.decode(tokens=torch.stack(ids, dim=1), tokens_len=torch.tensor([20, 10]))
+    assert torch.allclose(audio, full[:, 0]) and alen.tolist() == [320, 160] and m.rvq_codebooks.shape == (3, 32, 16)
