@@ -335,3 +335,91 @@ def test_llm_translator_continues_a_stable_prefix():
     assert tr.get_prefixes([""], ["HALLUCINATION"], ["HALLUCINATION"]) == [""]
     t2 = tr.translate(["hello my dear friend"], ["HELLO"], ["en"], ["de"])
     assert t2 == ["HELLO MY DEAR FRIEND"]
+
+
+def test_left_chunk_right_buffer_accounting_and_chunked_inference():
+    from speech_b200.utils.streaming_buffers import (AudioBatch, AudioFeatureIterator, BatchedFeatureFrameBufferer, ContextSize, FrameBatchChunkedCTC,
+                                                     FrameBatchChunkedRNNT, LongestCommonSubsequenceBatchedFrameASRRNNT, SimpleAudioDataset,
+                                                     StreamingBatchedAudioBuffer, StreamingFeatureBufferer, inplace_buffer_merge)
+
+    exp = ContextSize(left=6, chunk=4, right=2)
+    buf = StreamingBatchedAudioBuffer(2, exp)
+    stream = torch.arange(1, 21, dtype=torch.float32)[None].repeat(2, 1)
+    lens_total = torch.tensor([20, 13])                                  # the second stream is shorter
+    pos, seen = 0, []
+    first = True
+    while pos < 20:
+        n = exp.chunk + exp.right if first else exp.chunk
+        n = min(n, 20 - pos)
+        last = pos + n >= 20
+        lens = (lens_total - pos).clamp(min=0, max=n)
+        buf.add_audio_batch_(stream[:, pos:pos + n], lens, last, lens_total <= pos + n)
+        c = buf.context_size
+        assert buf.samples.shape[1] == c.total() <= exp.total()
+        chunk = buf.samples[0, c.left: c.left + c.chunk]
+        seen += chunk.tolist()
+        if not last:
+            assert c.chunk == exp.chunk and c.right == exp.right
+        pos, first = pos + n, False
+    assert seen == list(range(1, 21))                                    # every sample is the "chunk" exactly once, in order
+    assert buf.context_size.left == 8 and buf.context_size.right == 0          # no look-ahead is left, so the left context may use its room
+    b = buf.context_size_batch
+    assert int(b.right[1]) == 0 and int(b.total()[1]) <= exp.total()
+    assert inplace_buffer_merge([1, 2, 3, 4], [9, 8, 7], 2) == [1, 2, 9, 8, 7]
+
+    torch.manual_seed(0)
+    ctc = EncDecCTCModelBPE(_streaming_overrides(fastconformer_ctc_config("small", vocab_size=32, n_layers=1))).eval()
+    audio = _audio(16000 * 3, 5)
+    # incremental features equal whole-signal features
+    sfb = StreamingFeatureBufferer(ctc, chunk_size=0.5, buffer_size=4.0)
+    for k in range(0, 48000, 8000):
+        out = sfb.append(audio[k:k + 8000])
+    assert sfb.frames_seen == 299                                        # the newest half window waits for more samples
+    out = sfb.flush()
+    whole, _ = ctc.preprocessor(input_signal=torch.tensor(audio)[None], length=torch.tensor([48000]))
+    assert sfb.frames_seen == whole.shape[2] == 301 and torch.allclose(out[:, -301:], whole[0], atol=1e-4)
+    it = AudioFeatureIterator(audio, 1.0, ctc.preprocessor)
+    frames = list(it)
+    assert len(frames) == 3 and frames[0].shape == (80, 100)              # 300 valid frames
+    bb = BatchedFeatureFrameBufferer(ctc, frame_len=1.0, total_buffer=2.0)
+    bb.set_frame_reader(AudioFeatureIterator(audio, 1.0, ctc.preprocessor), 0)
+    bb.set_frame_reader(AudioFeatureIterator(audio[:16000], 1.0, ctc.preprocessor), 1)
+    steps = []
+    while True:
+        bufs, ids = bb.get_buffers_batch()
+        if not bufs:
+            break
+        steps.append(ids)
+        assert all(x.shape == (80, 200) for x in bufs)
+    assert steps[0] == [0, 1] and steps[-1] == [0]
+    chunked = FrameBatchChunkedCTC(ctc, frame_len=1.0, batch_size=2)
+    chunked.read_audio_file(audio)
+    assert isinstance(chunked.transcribe(), str) and len(chunked.all_preds) == 3
+    rnnt = EncDecRNNTBPEModel(_streaming_overrides(fastconformer_transducer_config("small", vocab_size=32, loss="rnnt", dropout=0.0, sched=None, lr=1e-3,
+                                                                                   n_layers=1))).eval()
+    for cls, kw in ((FrameBatchChunkedRNNT, dict(frame_len=1.0)), (LongestCommonSubsequenceBatchedFrameASRRNNT, dict(frame_len=0.8, total_buffer=2.4))):
+        d = cls(rnnt, batch_size=2, **kw)
+        d.read_audio_file(audio)
+        assert isinstance(d.transcribe(), str)
+    ds = SimpleAudioDataset([audio, audio[:1000]])
+    batch = AudioBatch.collate_fn([ds[0], ds[1]])
+    assert batch.audio_signals.shape == (2, 48000) and batch.audio_signal_lengths.tolist() == [48000, 1000] and batch.ids.tolist() == [0, 1]
+
+
+def test_streaming_transducer_inference_with_left_and_right_context():
+    from speech_b200.utils.streaming_buffers import streaming_transcribe_rnnt
+
+    torch.manual_seed(0)
+    rnnt = EncDecRNNTBPEModel(_streaming_overrides(fastconformer_transducer_config("small", vocab_size=32, loss="rnnt", dropout=0.0, sched=None, lr=1e-3,
+                                                                                   n_layers=1))).eval()
+    audio = torch.tensor(np.stack([_audio(32000, 1), _audio(32000, 2)]))
+    lens = torch.tensor([32000, 20000])
+    audio[1, 20000:] = 0
+    offline = rnnt.transcribe([audio[0].numpy(), audio[1, :20000].numpy()], batch_size=2, return_hypotheses=True)
+    # one chunk that holds everything is the offline pass
+    one = streaming_transcribe_rnnt(rnnt, audio[:1], lens[:1], chunk_secs=4.0, left_context_secs=0.0, right_context_secs=0.0)
+    assert [int(t) for t in one[0].y_sequence] == [int(t) for t in offline[0].y_sequence]
+    hyps = streaming_transcribe_rnnt(rnnt, audio, lens, chunk_secs=0.48, left_context_secs=0.96, right_context_secs=0.24)
+    assert len(hyps) == 2 and all(h is not None for h in hyps)
+    ts = [int(t) for t in (hyps[0].timestamp.tolist() if torch.is_tensor(hyps[0].timestamp) else hyps[0].timestamp)]
+    assert ts == sorted(ts)
