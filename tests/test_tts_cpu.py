@@ -563,3 +563,83 @@ def test_neural_g2p_models_learn_a_toy_lexicon(kind, tmp_path):
     src.write_text("\n".join(json.dumps({"text_graphemes": g}) for g, _ in lex[:3]), encoding="utf-8")
     preds = m.convert_graphemes_to_phonemes(str(src), str(dst))
     assert preds == [s for _, s in lex[:3]] and json.loads(dst.read_text(encoding="utf-8").splitlines()[1])["pred_text"] == "t æ k"
+
+
+def test_tts_data_stack_vocoder_magpie_featurizers_processors_trimming(tmp_path):
+    import json
+
+    import numpy as np
+
+    from speech_b200.data.audio_to_text import save_wav
+    from speech_b200.tts.data_extra import (BetaBinomialInterpolator, ChunkedTTSInferenceDataset, EnergyAudioTrimmer, EnergyFeaturizer, FeatureScaler,
+                                            LanguageThresholds, LogCompression, MagpieTTSDataset, MagpieTTSDatasetDPO, MeanVarianceNormalization,
+                                            MeanVarianceSpeakerNormalization, MelSpectrogramFeaturizer, PitchFeaturizer, VadAudioTrimmer, VocoderDataset,
+                                            normalize_volume)
+
+    sr = 16000
+    t = np.arange(sr) / sr
+    rows = {"a": [], "b": []}
+    for name, n, f0 in (("a", 4, 200.0), ("b", 1, 330.0)):
+        for k in range(n):
+            p = tmp_path / f"{name}{k}.wav"
+            save_wav(str(p), (0.3 * np.sin(2 * np.pi * f0 * t)).astype(np.float32), sr)
+            rows[name].append({"audio_filepath": p.name, "duration": 1.0, "text": f"hello {name} {k}. " * 2, "speaker": name, "language": "en",
+                               "reward": float(k % 2 == 0)})
+        (tmp_path / f"{name}.json").write_text("\n".join(json.dumps(r) for r in rows[name]))
+    meta = {n: {"manifest_path": str(tmp_path / f"{n}.json"), "audio_dir": str(tmp_path), "sample_weight": w} for n, w in (("a", 1.0), ("b", 1.0))}
+    voc = VocoderDataset(meta, sr, weighted_sampling_steps_per_epoch=50, n_samples=4000, resample_rates=[8000], volume_norm=True,
+                         feature_processors={"scale": FeatureScaler("audio", div_value=2.0)})
+    sampler = voc.get_sampler(batch_size=4)
+    drawn = [voc.samples[i]["dataset_name"] for i in sampler]
+    assert len(drawn) == 200 and 0.35 < drawn.count("b") / 200 < 0.65                  # one file of "b" is drawn as often as four of "a"
+    batch = voc.collate_fn([voc[0], voc[4]])
+    assert batch["audio"].shape == (2, 4000) and batch["audio_8000"].shape == (2, 2000) and float(batch["audio"].abs().max()) == pytest.approx(0.475, abs=1e-3)
+
+    tok = CharTokenizer(list("abcdefghijklmnopqrstuvwxyz .0123456789"))
+    ds = MagpieTTSDataset(meta, sr, {"en": tok}, codec_frame_rate=25.0, context_duration_min=0.2, context_duration_max=0.4, prior_scaling_factor=0.5)
+    b = ds.collate_fn([ds[0], ds[4]])
+    assert b["text"].shape[0] == 2 and b["audio"].shape == (2, sr) and 0.2 * sr - 2 <= b["context_audio"].shape[1] <= 0.4 * sr + 2
+    assert b["align_prior_matrix"].shape == (2, 25, int(b["text_lens"].max())) and torch.allclose(b["align_prior_matrix"][0].sum(-1), torch.ones(25), atol=1e-4)
+    assert len(MagpieTTSDataset.as_model_batch(b)) == 6 and int(b["text"][0, 0]) == tok.vocab_size
+    dpo = MagpieTTSDatasetDPO({"a": meta["a"]}, sr, {"en": tok})
+    pair = dpo.collate_fn([dpo[0], dpo[1]])
+    assert len(dpo) == 2 and pair["rewards"].tolist() == [[1.0, 0.0], [1.0, 0.0]] and pair["chosen"]["audio"].shape == pair["rejected"]["audio"].shape
+    long_manifest = tmp_path / "long.json"
+    long_manifest.write_text(json.dumps({"text": "one two three. " * 30, "context_audio_filepath": "a0.wav", "language": "en"}))
+    inf = ChunkedTTSInferenceDataset({"x": {"manifest_path": str(long_manifest), "audio_dir": str(tmp_path)}}, sr, {"en": tok}, max_chunk_chars=120)
+    item = inf.collate_fn([inf[0]])
+    assert len(item["chunked_tokens"][0]) >= 3 and all(len(c) <= 123 for c in item["chunked_tokens"][0]) and "context_audio" in item
+    assert LanguageThresholds().exceeds_threshold("字" * 101, "zh") and not LanguageThresholds().exceeds_threshold("short text", "en")
+
+    mel = MelSpectrogramFeaturizer(sample_rate=sr, mel_dim=20, win_length=512, hop_length=128)
+    entry = {"audio_filepath": "a0.wav"}
+    feat_dir = tmp_path / "feats"
+    for fz in (mel, EnergyFeaturizer(mel), PitchFeaturizer(sample_rate=sr, win_length=1024, hop_length=128)):
+        fz.save(entry, str(tmp_path), str(feat_dir))
+    ex = {**mel.load(entry, str(tmp_path), str(feat_dir)), **EnergyFeaturizer(mel).load(entry, str(tmp_path), str(feat_dir)),
+          **PitchFeaturizer(sample_rate=sr, win_length=1024, hop_length=128).load(entry, str(tmp_path), str(feat_dir)), "speaker": "a"}
+    assert ex["mel_spec"].shape == (20, 126) and ex["energy"].shape == (126,)
+    voiced = ex["voiced_mask"][8:-8]
+    assert bool(voiced.all()) and float((ex["pitch"][8:-8] - 200.0).abs().max()) < 2.0               # the 200 Hz tone is found
+    noise_pitch = PitchFeaturizer(sample_rate=sr, win_length=1024, hop_length=128).compute_pitch(torch.randn(8000) * 0.1)
+    assert float(noise_pitch[1].float().mean()) < 0.2                                                 # noise is unvoiced
+    stats = tmp_path / "stats.json"
+    stats.write_text(json.dumps({"default": {"pitch_mean": 100.0, "pitch_std": 50.0}, "a": {"pitch_mean": 200.0, "pitch_std": 10.0}}))
+    e1, e2 = dict(ex), dict(ex)
+    MeanVarianceNormalization("pitch", str(stats)).process(e1)
+    MeanVarianceSpeakerNormalization("pitch", str(stats)).process(e2)
+    assert float(e1["pitch"][20]) == pytest.approx(2.0, abs=0.05) and abs(float(e2["pitch"][20])) < 0.2
+    e3 = {"energy": ex["energy"].clone()}
+    LogCompression("energy").process(e3)
+    assert torch.allclose(e3["energy"], torch.log(ex["energy"] + 1.0))
+    assert torch.allclose(mel.collate_fn([{"mel_spec": ex["mel_spec"]}, {"mel_spec": ex["mel_spec"][:, :100]}])["mel_spec"][1, :, 100:], torch.zeros(20, 26))
+
+    sig = np.concatenate([np.zeros(8000), 0.5 * np.sin(2 * np.pi * 200 * t[:8000]), np.zeros(8000)]).astype(np.float32)
+    trimmed, s, e = EnergyAudioTrimmer(db_threshold=30.0, pad_seconds=0.05, trim_win_length=512, trim_hop_length=128).trim_audio(sig, sr)
+    assert 6500 <= s <= 8000 and 16000 <= e <= 17500 and len(trimmed) == e - s
+    vad = lambda frames: (frames.abs().amax(dim=1) > 0.1).float()  # noqa: E731
+    _, s2, e2_ = VadAudioTrimmer(vad, vad_sample_rate=8000, trim_win_length=256, trim_hop_length=64, pad_seconds=0.0).trim_audio(sig, sr)
+    assert 7000 <= s2 <= 8100 and 15900 <= e2_ <= 17000
+    assert float(np.abs(normalize_volume(sig, 0.5)).max()) == pytest.approx(0.5)
+    p = BetaBinomialInterpolator()(37, 12)
+    assert p.shape == (37, 12) and int(p[0].argmax()) == 0 and int(p[-1].argmax()) == 11
