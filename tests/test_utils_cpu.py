@@ -413,3 +413,65 @@ def test_run_twice_reports_bitwise_differences_and_guard_bands_catch_overruns():
     assert g.violations() == [("after", 8)]
     with pytest.raises(AssertionError, match="after the payload at byte offset 8"):
         g.check("gemm output")
+
+
+def test_vad_postprocessing_scoring_and_threshold_tuning(tmp_path):
+    import json
+
+    from speech_b200.utils import vad_utils as V
+
+    # window scores -> frame posteriors: a frame covered by three windows gets their mean / median
+    w = torch.tensor([0.0, 0.0, 1.0, 1.0, 0.0])
+    mean = V.generate_overlap_vad_seq(w, 0.03, 0.01, 0.01, "mean")
+    med = V.generate_overlap_vad_seq(w, 0.03, 0.01, 0.01, "median")
+    assert mean.shape == (7,) and mean[2] == pytest.approx(1 / 3) and mean[3] == pytest.approx(2 / 3) and float(med[2]) == 0.0 and float(med[3]) == 1.0
+    probs = torch.zeros(1000)
+    probs[100:300] = 0.9          # 1.0 - 3.0 s
+    probs[300:320] = 0.45         # a dip that hysteresis rides through (above offset 0.3)
+    probs[320:400] = 0.9          # - 4.0 s
+    probs[420:425] = 0.9          # a 50 ms burst
+    probs[700:900] = 0.8          # 7.0 - 9.0 s
+    seg = V.binarization(probs, {"onset": 0.6, "offset": 0.3, "pad_onset": 0.1, "pad_offset": 0.05})
+    assert seg.shape == (3, 2) and seg[0].tolist() == pytest.approx([0.9, 4.05]) and seg[1].tolist() == pytest.approx([4.1, 4.3])
+    clean = V.filtering(seg, {"min_duration_on": 0.3, "min_duration_off": 0.2, "filter_speech_first": 1.0})
+    assert clean.shape == (2, 2) and clean[1].tolist() == pytest.approx([6.9, 9.05])
+    merged = V.filtering(seg, {"min_duration_on": 0.3, "min_duration_off": 0.2, "filter_speech_first": 0.0})
+    assert merged[0].tolist() == pytest.approx([0.9, 4.3])                  # gaps filled first: the burst is absorbed
+    ref = torch.tensor([[1.0, 4.0], [7.0, 9.0]])
+    sc = V.detection_error_rate(ref, torch.tensor([[1.0, 3.0], [7.0, 9.5]]))
+    assert sc["miss"] == pytest.approx(20.0) and sc["FA"] == pytest.approx(10.0) and sc["DetER"] == pytest.approx(30.0)
+    best, score, trials = V.vad_tune_threshold_on_dev({"onset": [0.3, 0.6, 0.95], "pad_onset": [0.0, 0.5], "min_duration_on": [0.0, 0.2]},
+                                                      {"rec": probs}, {"rec": ref})
+    assert len(trials) == 12 and best["onset"] in (0.3, 0.6) and best["pad_onset"] == 0.0 and best["min_duration_on"] == 0.2 and score["DetER"] < 1.0
+    with pytest.raises(ValueError):
+        V.vad_tune_threshold_on_dev({"bogus": [1]}, {"rec": probs}, {"rec": ref})
+    labels = torch.zeros(1000)
+    labels[100:400] = 1
+    labels[700:900] = 1
+    assert V.frame_auroc(probs, labels) > 0.98 and V.frame_auroc(torch.rand(1000), labels) == pytest.approx(0.5, abs=0.08)
+    rttm = tmp_path / "a.rttm"
+    V.write_rttm(str(rttm), ref, "a")
+    assert torch.allclose(V.read_rttm_as_segments(str(rttm)), ref)
+    assert V.extract_labels(str(rttm), [0.5, 1.5, 5.0, 8.0]) == [0, 1, 0, 1] and V.extract_labels("0 1 1", []) == [0, 1, 1]
+    assert V.align_labels_to_frames([0.0] * 6, [0, 1, 1]) == [0, 0, 1, 1, 1, 1] and V.align_labels_to_frames([0.0] * 3, [0, 0, 1, 1, 1, 1]) == [0, 1, 1]
+    assert V.convert_labels_to_speech_segments([0, 1, 1, 0, 1], 0.5) == [(0.5, 1.5), (2.0, 2.5)]
+    man, out = tmp_path / "m.json", tmp_path / "o.json"
+    man.write_text(json.dumps({"audio_filepath": "x.wav", "duration": 950.0}) + "\n" + json.dumps({"audio_filepath": "y.wav", "duration": 30.0}))
+    assert V.write_long_audio_manifest(str(man), str(out), split_duration=400.0, window_length_in_sec=0.6) == 4
+    rows = [json.loads(l) for l in open(out)]
+    assert [r.get("stream_status") for r in rows] == ["start", "next", "end", None] and rows[1]["offset"] == 400.0 and rows[0]["duration"] == 400.6
+
+    class Toy(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.p = torch.nn.Parameter(torch.zeros(1))
+
+        def forward(self, input_signal, input_signal_length):
+            e = input_signal.pow(2).mean(dim=1)
+            return torch.stack([-(e * 400), e * 400], dim=1) + self.p
+
+    audio = torch.zeros(16000)
+    audio[4000:12000] = 0.3 * torch.randn(8000)
+    fp = V.generate_vad_frame_pred(Toy(), audio, window_length_in_sec=0.1, shift_length_in_sec=0.02)
+    seg = V.generate_vad_segment_table(fp, {"onset": 0.7, "offset": 0.7})
+    assert seg.shape == (1, 2) and abs(float(seg[0, 0]) - 0.25) < 0.08 and abs(float(seg[0, 1]) - 0.75) < 0.12
