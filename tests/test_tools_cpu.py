@@ -224,3 +224,99 @@ def test_ctc_segmentation_finds_utterances_inside_a_long_recording(tmp_path):
     assert got[0]["WER"] == 0.0 and got[1]["WER"] == 100.0 and got[1]["start_CER"] > 0
     kept, dropped = filter_manifest(m2, m3, min_duration=0.1)
     assert kept > 0 and dropped > 0 and len(open(m3).read().splitlines()) == 1
+
+
+def test_extra_data_tools(tmp_path):
+    import json
+    import tarfile
+
+    import numpy as np
+
+    from speech_b200.data import tools_extra as T
+    from speech_b200.data.audio_to_text import load_audio, read_manifest, save_wav, write_manifest
+
+    sr = 16000
+    rng = np.random.default_rng(0)
+    for spk in ("s1", "s2"):
+        os.makedirs(tmp_path / "corpus" / spk / "wav", exist_ok=True)
+    files = []
+    for spk, n in (("s1", 4), ("s2", 2)):
+        for k in range(n):
+            p = tmp_path / "corpus" / spk / f"{spk}_{k}.wav"
+            save_wav(str(p), (0.1 * rng.standard_normal(sr // 2 * (k + 1))).astype(np.float32), sr)
+            files.append(str(p))
+    # Kaldi directory with segments
+    kd = tmp_path / "kaldi"
+    os.makedirs(kd)
+    (kd / "wav.scp").write_text(f"rec1 {files[3]}\nrec2 {files[5]}\n")
+    (kd / "text").write_text("u1 hello world\nu2 good bye\nu3 again\n")
+    (kd / "segments").write_text("u1 rec1 0.0 0.8\nu2 rec1 1.0 1.9\nu3 rec2 0.1 0.6\n")
+    (kd / "utt2spk").write_text("u1 alice\nu2 alice\nu3 bob\n")
+    assert T.kaldi2json(str(kd), str(tmp_path / "k.json")) == 3
+    rows = read_manifest(str(tmp_path / "k.json"))
+    assert rows[1]["offset"] == 1.0 and rows[1]["duration"] == 0.9 and rows[2]["speaker"] == "bob" and rows[0]["text"] == "hello world"
+    (kd / "wav.scp").write_text("rec1 sox x.sph -t wav - |\n")
+    with pytest.raises(ValueError):
+        T.kaldi2json(str(kd), str(tmp_path / "k2.json"))
+    # speaker manifests
+    ntr, ndev = T.filelist_to_manifest(files, str(tmp_path / "spk.json"), id_index=-2, split_fraction=0.5)
+    assert (ntr, ndev) == (3, 3) and {r["label"] for r in read_manifest(str(tmp_path / "spk_dev.json"))} == {"s1", "s2"}
+    assert T.filelist_to_manifest(files, str(tmp_path / "spk3.json"), min_spkrs_count=3) == (4, 0)
+    rttm = tmp_path / "s1_0.rttm"
+    rttm.write_text("SPEAKER s1_0 1 0.0 0.2 <NA> <NA> A <NA> <NA>\nSPEAKER s1_0 1 0.2 0.2 <NA> <NA> B <NA> <NA>\n")
+    assert T.pathfiles_to_diarize_manifest(files[:2], str(tmp_path / "diar.json"), rttm_paths=[str(rttm)], add_duration=True) == 2
+    d = read_manifest(str(tmp_path / "diar.json"))
+    assert d[0]["num_speakers"] == 2 and d[0]["rttm_filepath"] == str(rttm) and d[1]["rttm_filepath"] is None and d[0]["duration"] == 0.5
+    # noise at a given SNR
+    write_manifest(str(tmp_path / "clean.json"), [{"audio_filepath": files[1], "duration": 1.0, "text": "a"}])
+    noise = tmp_path / "noise.wav"
+    save_wav(str(noise), (0.05 * rng.standard_normal(3000)).astype(np.float32), sr)
+    write_manifest(str(tmp_path / "noise.json"), [{"audio_filepath": str(noise), "duration": 3000 / sr}])
+    outs = T.add_noise(str(tmp_path / "clean.json"), str(tmp_path / "noise.json"), str(tmp_path / "noisy"), snrs=[0, 20])
+    x = load_audio(files[1])
+    for mp, snr in zip(outs, (0, 20)):
+        y = load_audio(read_manifest(mp)[0]["audio_filepath"])
+        got = 10 * np.log10(np.mean(x ** 2) / np.mean((y - x) ** 2))
+        assert abs(got - snr) < 0.7
+    # code switching
+    write_manifest(str(tmp_path / "en.json"), [{"audio_filepath": f, "duration": 0.5 * (k + 1), "text": f"en {k}"} for k, f in enumerate(files[:4])])
+    write_manifest(str(tmp_path / "es.json"), [{"audio_filepath": f, "duration": 0.5 * (k + 1), "text": f"es {k}"} for k, f in enumerate(files[4:])])
+    n = T.code_switching_manifest(str(tmp_path / "en.json"), str(tmp_path / "es.json"), str(tmp_path / "cs.json"), "en", "es", max_sample_duration=4.0,
+                                  min_sample_duration=2.0, dataset_size_hours=20 / 3600)
+    cs = [json.loads(l) for l in open(tmp_path / "cs.json")]
+    assert n == len(cs) >= 5 and all(2.0 <= c["duration"] <= 4.0 for c in cs) and {l for c in cs for l in c["lang_ids"]} == {"en", "es"}
+    m = T.code_switching_audio(str(tmp_path / "cs.json"), str(tmp_path / "cs_audio"), str(tmp_path / "cs_out.json"))
+    r0 = read_manifest(str(tmp_path / "cs_out.json"))[0]
+    assert m == n and r0["duration"] > cs[0]["duration"] and len(r0["word_lang_ids"]) == len(r0["text"].split())
+    # end of utterance labels, keyword scores, confidence metrics
+    write_manifest(str(tmp_path / "eou.json"), [{"audio_filepath": files[0], "duration": 1, "text": "Uh-huh"}, {"audio_filepath": files[0], "duration": 1, "text": "I'll go now!"},
+                                                {"audio_filepath": files[0], "duration": 1, "text": "??"}])
+    assert T.clean_eou_manifest(str(tmp_path / "eou.json"), str(tmp_path / "eou_clean.json")) == 2
+    assert T.add_eob_labels(str(tmp_path / "eou_clean.json"), str(tmp_path / "eou_lab.json")) == (1, 1)
+    assert [r["eou_label"] for r in read_manifest(str(tmp_path / "eou_lab.json"))] == ["<EOB>", "<EOU>"]
+    ks = T.keyword_fscore([{"text": "call nvidia and then call nvidia", "pred_text": "call in video and then call nvidia"},
+                           {"text": "no key here", "pred_text": "nvidia here"}], ["nvidia", "call"])
+    assert (ks["tp"], ks["fn"], ks["fp"]) == (3, 1, 1) and ks["precision"] == 0.75 and ks["recall"] == 0.75
+    good = T.confidence_benchmark([0.9, 0.8, 0.95, 0.2, 0.1, 0.85], [True, True, True, False, False, True])
+    bad = T.confidence_benchmark([0.5] * 6, [True, True, True, False, False, True])
+    assert good["auc_roc"] == 1.0 and good["auc_nt"] == pytest.approx(1.0) and good["nce"] > 0.5 > bad["nce"] and good["ece"] < bad["ece"] + 0.2
+    # token bins: equal token mass per bucket, 2-D sub-buckets
+    counts = [10] * 90 + [100] * 9 + [1000]
+    assert T.estimate_token_bins(counts, 3) == [100, 1000] and T.estimate_token_bins(counts, 2, max_tokens=100) == [10, 100]
+    two = T.estimate_token_bins([10, 10, 10, 10, 20, 20], 2, num_subbuckets=2, second_dim=[1, 3, 5, 7, 9, 11])
+    assert two == [(10, 3), (10, 7), (20, 9), (20, 11)]
+    convs = [{"id": f"c{k}", "conversations": [{"from": "User", "type": "audio", "value": files[k], "duration": 0.5}, {"from": "Assistant", "type": "text", "value": "ok"}]}
+             for k in range(3)]
+    shards = T.export_conversations_to_tar(convs, str(tmp_path / "tars"), shard_size=2)
+    assert len(shards) == 2
+    with tarfile.open(shards[0]) as tf:
+        names = tf.getnames()
+        assert names == ["c0_0.wav", "c0.json", "c1_0.wav", "c1.json"]
+        assert json.load(tf.extractfile("c0.json"))["conversations"][0]["value"] == "c0_0.wav"
+    # pseudo-label merge
+    write_manifest(str(tmp_path / "pred_rank0.json"), [{"audio_filepath": files[0], "pred_text": "new zero"}])
+    write_manifest(str(tmp_path / "pred_rank1.json"), [{"audio_filepath": files[1], "pred_text": "new one"}])
+    write_manifest(str(tmp_path / "src.json"), [{"audio_filepath": files[0], "duration": 1, "text": "old"}, {"audio_filepath": files[2], "duration": 1, "text": "untouched"}])
+    out = T.write_transcribed_files(str(tmp_path / "pred_rank*.json"), [str(tmp_path / "src.json")])
+    merged = read_manifest(out[0])
+    assert len(merged) == 1 and merged[0]["text"] == "new zero" and merged[0]["orig_text"] == "old"
