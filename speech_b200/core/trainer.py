@@ -262,6 +262,10 @@ class Trainer:
     def _setup_grad_sync(self):
         from ..parallel.ddp import build_grad_sync
 
+        if not getattr(self.model, "automatic_optimization", True):
+            self.grad_sync = None                       # manual_step averages the gradients of the optimizer it updates
+            return
+
         if hasattr(self.strategy_spec, "build_grad_sync"):
             self.grad_sync = self.strategy_spec.build_grad_sync(self.model, self.optimizers, self.device, sync_batchnorm=self.sync_batchnorm)
             return
@@ -379,6 +383,26 @@ class Trainer:
         batch = move_to_device(batch, self.device, None)
         model.on_train_batch_start(batch, batch_idx)
         self._call("on_train_batch_start", batch, batch_idx)
+        if not getattr(model, "automatic_optimization", True):
+            # the model drives its optimizers itself (several optimizers updated in turn, as in adversarial training): its
+            # training_step calls ``trainer.manual_step(loss, optimizer)`` for every update
+            self._in_manual_step = True
+            try:
+                with self.precision_context():
+                    out = model.training_step(batch, batch_idx)
+            finally:
+                self._in_manual_step = False
+            for sc in self.lr_scheduler_configs:
+                if sc.get("interval", "step") == "step" and (self.global_step + 1) % sc.get("frequency", 1) == 0 and not sc.get("reduce_on_plateau", False):
+                    sc["scheduler"].step()
+            self.global_step += 1
+            if self.optimizers:
+                self._collect_log("lr", self.optimizers[0].param_groups[0]["lr"])
+            model.on_train_batch_end(out, batch, batch_idx)
+            self._call("on_train_batch_end", out, batch, batch_idx)
+            if self.global_step % max(1, self.log_every_n_steps) == 0 or self.global_step == 1:
+                self._flush_logs(self.global_step)
+            return
         if first_micro:
             for opt in self.optimizers:
                 self._call("on_before_zero_grad", opt)
@@ -417,6 +441,27 @@ class Trainer:
         self._call("on_train_batch_end", out, batch, batch_idx)
         if last_micro and (self.global_step % max(1, self.log_every_n_steps) == 0 or self.global_step == 1):
             self._flush_logs(self.global_step)
+
+    @property
+    def in_manual_step(self) -> bool:
+        """True while a model with ``automatic_optimization = False`` runs its ``training_step`` under ``fit``."""
+        return bool(getattr(self, "_in_manual_step", False))
+
+    def manual_step(self, loss: torch.Tensor, optimizer, retain_graph: bool = False) -> None:
+        """One update of ``optimizer`` from ``loss`` for models that optimise manually: clears that optimizer's gradients, runs
+        backward, averages the gradients over data-parallel ranks, clips and steps."""
+        optimizer.zero_grad(set_to_none=True)
+        self._call("on_before_backward", loss)
+        loss.backward(retain_graph=retain_graph)
+        if self.world_size > 1 and torch.distributed.is_available() and torch.distributed.is_initialized():
+            for g in optimizer.param_groups:
+                for p in g["params"]:
+                    if p.grad is not None:
+                        torch.distributed.all_reduce(p.grad)
+                        p.grad.div_(self.world_size)
+        self._clip_gradients(optimizer)
+        self._call("on_before_optimizer_step", optimizer)
+        optimizer.step()
 
     def _check_kernel_status(self):
         """Fail the run when a kernel of an earlier step gave up a bounded wait (a peer rank that never arrived).

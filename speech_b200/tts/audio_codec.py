@@ -277,6 +277,19 @@ class Discriminator(nn.Module):
         return res
 
 
+def gan_update(model, loss: torch.Tensor, optimizer, standalone_step: bool) -> None:
+    """Applies ``loss`` to ``optimizer``: through the trainer when the model runs under ``fit`` (gradient averaging over ranks,
+    clipping, callbacks); directly when ``standalone_step`` (the discriminator update of a hand-driven loop).  A hand-driven
+    generator update is left to the caller, who gets the loss back from ``training_step``."""
+    tr = getattr(model, "_trainer", None)
+    if tr is not None and getattr(tr, "in_manual_step", False):
+        tr.manual_step(loss, optimizer)
+    elif standalone_step:
+        optimizer.zero_grad()
+        loss.backward()
+        optimizer.step()
+
+
 def generator_adv_loss(scores_gen):
     return sum(((1 - s) ** 2).mean() for s in scores_gen) / len(scores_gen)
 
@@ -432,9 +445,7 @@ class AudioCodecModel(ModelPT):
         if manual:
             sr, sg, _, _ = self.discriminator(audio, gen.detach())
             d_loss = self.disc_loss(sr, sg)
-            opts[1].zero_grad()
-            d_loss.backward()
-            opts[1].step()
+            gan_update(self, d_loss, opts[1], standalone_step=True)
             logs["d_loss"] = d_loss.detach()
         loss = self.w["mel"] * self.mel_loss(audio, gen, audio_len) + self.w["stft"] * self.stft_loss(audio, gen, audio_len)
         if self.w["time"]:
@@ -447,6 +458,8 @@ class AudioCodecModel(ModelPT):
             loss = loss + self.w["gen"] * self.gen_loss(sg) + self.w["fm"] * fm
         logs["train_loss"] = loss.detach()
         self.log_dict(logs)
+        if opts:
+            gan_update(self, loss, opts[0], standalone_step=False)
         return {"loss": loss}
 
     def validation_step(self, batch, batch_idx, dataloader_idx=0):

@@ -18,7 +18,7 @@ import torch.nn.functional as F
 
 from ..core.config import DictConfig, cfg_get
 from ..core.modelpt import ModelPT
-from .audio_codec import Discriminator, HiFiGANDecoder, MelLoss, discriminator_loss, feature_matching_loss, generator_adv_loss
+from .audio_codec import Discriminator, HiFiGANDecoder, MelLoss, discriminator_loss, feature_matching_loss, gan_update, generator_adv_loss
 from .magpietts import ForwardSumLoss, beta_binomial_prior
 from .transformer_2501 import Transformer
 
@@ -86,6 +86,53 @@ class PhonemeTokenizer:
 
     def ids_to_tokens(self, ids):
         return [self.tokens[int(i)] for i in ids]
+
+
+def build_text_tokenizer(cfg):
+    """``text_tokenizer`` block of a TTS model config -> tokenizer.  ``type``: ``char`` (``chars``: the alphabet), ``phoneme``
+    (CMUdict-style ``phoneme_dict`` path or mapping, optional ``phoneme_probability``) or ``ipa`` (``phoneme_dict`` of IPA
+    strings, ``locale``, ``heteronyms``); ids 0..2 are pad / blank / oov for the phoneme kinds."""
+    if cfg is None:
+        return None
+    get = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: getattr(cfg, k, d))
+    kind = get("type", "char")
+    if kind == "char":
+        from ..tokenizers import CharTokenizer
+
+        return CharTokenizer(list(get("chars", "abcdefghijklmnopqrstuvwxyz' .,?!-")))
+    if kind == "phoneme":
+        d = get("phoneme_dict")
+        return PhonemeTokenizer(DictG2p(dict(d) if not isinstance(d, str) else d, phoneme_probability=get("phoneme_probability", None)))
+    if kind == "ipa":
+        from .g2p import IpaG2p
+
+        d = get("phoneme_dict")
+        g2p = IpaG2p(dict(d) if not isinstance(d, str) else d, locale=get("locale", "en-US"), heteronyms=get("heteronyms", None),
+                     phoneme_probability=get("phoneme_probability", None), grapheme_prefix=get("grapheme_prefix", ""), use_chars=True)
+        tok = PhonemeTokenizer.__new__(PhonemeTokenizer)
+        chars = sorted({g2p.prefix + c for c in (get("chars", None) or "ABCDEFGHIJKLMNOPQRSTUVWXYZ'")}) + [" "] + list(DictG2p.PUNCT)
+        tok.tokens = ["<pad>", "<blank>", "<oov>"] + list(dict.fromkeys(sorted(g2p.symbols) + chars))
+        tok._t2i = {t: i for i, t in enumerate(tok.tokens)}
+        tok.g2p, tok.pad, tok.blank, tok.oov = g2p, 0, 1, 2
+        return tok
+    raise ValueError(f"unknown text tokenizer type {kind!r}")
+
+
+def _tts_loader(model, c, audio_only: bool = False):
+    """Text + audio batches for the acoustic models; ``audio_only`` drops the text (vocoder)."""
+    if c is None or (c.get("manifest_filepath", None) is None and c.get("synthetic", None) is None):
+        return None
+    from .data import build_tts_dataloader
+
+    return build_tts_dataloader(c, model.tokenizer if not audio_only else (model.tokenizer or _NoText()), cfg_get(model._cfg, "sample_rate", 22050),
+                                audio_only=audio_only)
+
+
+class _NoText:
+    vocab_size = 0
+
+    def text_to_ids(self, text):
+        return []
 
 
 # ---------------------------------------------------------------------------------------------- alignment utilities
@@ -167,8 +214,9 @@ class FastPitchModel(ModelPT):
     def __init__(self, cfg: DictConfig, trainer=None, tokenizer=None):
         super().__init__(cfg=cfg, trainer=trainer)
         cfg = self._cfg
-        self.tokenizer = tokenizer
-        n_sym = cfg_get(cfg, "n_symbols", tokenizer.vocab_size if tokenizer is not None else 128)
+        self.tokenizer = tokenizer if tokenizer is not None else build_text_tokenizer(cfg_get(cfg, "text_tokenizer", None))
+        # the datasets append <bos> / <eos> as vocab_size and vocab_size + 1
+        n_sym = cfg_get(cfg, "n_symbols", None) or (self.tokenizer.vocab_size + 2 if self.tokenizer is not None else 128)
         d = cfg_get(cfg, "symbols_embedding_dim", 384)
         self.n_mel = cfg_get(cfg, "n_mel_channels", 80)
         self.embedding = nn.Embedding(n_sym, d, padding_idx=0)
@@ -188,14 +236,22 @@ class FastPitchModel(ModelPT):
                            cfg_get(cfg, "win_length", 1024))
         self.w = {"dur": cfg_get(cfg, "dur_loss_scale", 0.1), "pitch": cfg_get(cfg, "pitch_loss_scale", 0.1), "align": cfg_get(cfg, "align_loss_scale", 1.0)}
         self.bin_loss_start = cfg_get(cfg, "bin_loss_warmup_epochs", 100)
+        if not self._is_model_being_restored and self._train_dl is None:
+            self._setup_dataloaders_from_cfg()
+
+    def _setup_dataloaders_from_cfg(self):
+        if hasattr(self, "forward_sum"):                             # the base constructor calls this before the layers exist
+            super()._setup_dataloaders_from_cfg()
 
     def setup_training_data(self, c):
-        from .data import build_tts_dataloader
-
-        self._train_dl = build_tts_dataloader(c, self.tokenizer, cfg_get(self._cfg, "sample_rate", 22050)) if c is not None else None
+        self._train_dl = _tts_loader(self, c)
 
     def setup_validation_data(self, c):
-        self._validation_dl = None
+        self._validation_dl = _tts_loader(self, c)
+
+    def validation_step(self, batch, batch_idx, dataloader_idx=0):
+        with torch.no_grad():
+            return {"val_loss": self.training_step(batch, batch_idx)["loss"]}
 
     @staticmethod
     def estimate_pitch(audio: torch.Tensor, hop: int, sr: int, fmin: float = 60.0, fmax: float = 400.0) -> torch.Tensor:
@@ -287,12 +343,27 @@ class HifiGanModel(ModelPT):
         self.discriminator = Discriminator(**dict(cfg_get(cfg, "discriminator", {}) or {}))
         self.mel = MelLoss(self.sample_rate, self.n_mel, **dict(cfg_get(cfg, "mel", {}) or {}))
         self.l1_factor = cfg_get(cfg, "l1_loss_factor", 45.0)
+        self.tokenizer = None
+        self.automatic_optimization = False
+        if not self._is_model_being_restored and self._train_dl is None:
+            self._setup_dataloaders_from_cfg()
+
+    def _setup_dataloaders_from_cfg(self):
+        if hasattr(self, "l1_factor"):
+            super()._setup_dataloaders_from_cfg()
 
     def setup_training_data(self, c):
-        self._train_dl = None
+        self._train_dl = _tts_loader(self, c, audio_only=True)
 
     def setup_validation_data(self, c):
-        self._validation_dl = None
+        self._validation_dl = _tts_loader(self, c, audio_only=True)
+
+    def validation_step(self, batch, batch_idx, dataloader_idx=0):
+        audio, audio_len = batch[0], batch[1]
+        with torch.no_grad():
+            gen = self.forward(self.mel.mel(audio))
+            n = min(gen.shape[-1], audio.shape[-1])
+            return {"val_loss": self.mel(audio[..., :n], gen[..., :n], audio_len)}
 
     def forward(self, spec: torch.Tensor) -> torch.Tensor:
         lens = torch.full((spec.shape[0],), spec.shape[2], device=spec.device, dtype=torch.long)
@@ -317,12 +388,12 @@ class HifiGanModel(ModelPT):
         if opts is not None:
             sr, sg, _, _ = self.discriminator(audio, gen.detach())
             d = discriminator_loss(sr, sg)
-            opts[1].zero_grad()
-            d.backward()
-            opts[1].step()
+            gan_update(self, d, opts[1], standalone_step=True)
         sr, sg, fr, fg = self.discriminator(audio, gen)
         loss = self.l1_factor * self.mel(audio, gen, audio_len) + generator_adv_loss(sg) + 2.0 * feature_matching_loss(fr, fg)
         self.log_dict({"train_loss": loss.detach()})
+        if opts is not None:
+            gan_update(self, loss, opts[0], standalone_step=False)
         return {"loss": loss}
 
 
@@ -332,16 +403,22 @@ class AlignerModel(ModelPT):
     def __init__(self, cfg: DictConfig, trainer=None, tokenizer=None):
         super().__init__(cfg=cfg, trainer=trainer)
         cfg = self._cfg
-        self.tokenizer = tokenizer
+        self.tokenizer = tokenizer if tokenizer is not None else build_text_tokenizer(cfg_get(cfg, "text_tokenizer", None))
         d = cfg_get(cfg, "symbols_embedding_dim", 256)
         self.n_mel = cfg_get(cfg, "n_mel_channels", 80)
-        self.embed = nn.Embedding(cfg_get(cfg, "n_symbols", tokenizer.vocab_size if tokenizer is not None else 128), d)
+        self.embed = nn.Embedding(cfg_get(cfg, "n_symbols", None) or (self.tokenizer.vocab_size + 2 if self.tokenizer is not None else 128), d)
         self.alignment_encoder = ConvAttention(self.n_mel, d)
         self.forward_sum = ForwardSumLoss()
-        self.mel = MelLoss(cfg_get(cfg, "sample_rate", 22050), self.n_mel)
+        self.mel = MelLoss(cfg_get(cfg, "sample_rate", 22050), self.n_mel, **dict(cfg_get(cfg, "mel", {}) or {}))
+        if not self._is_model_being_restored and self._train_dl is None:
+            self._setup_dataloaders_from_cfg()
+
+    def _setup_dataloaders_from_cfg(self):
+        if hasattr(self, "mel"):
+            super()._setup_dataloaders_from_cfg()
 
     def setup_training_data(self, c):
-        self._train_dl = None
+        self._train_dl = _tts_loader(self, c)
 
     def setup_validation_data(self, c):
         self._validation_dl = None

@@ -76,9 +76,17 @@ class SyntheticTTSDataset(Dataset):
     collate_fn = staticmethod(_collate)
 
 
-def build_tts_dataloader(config, tokenizer, sample_rate: int = 22050):
+def _collate_audio_only(batch):
+    _, _, audio, al = _collate(batch)
+    return audio, al
+
+
+def build_tts_dataloader(config, tokenizer, sample_rate: int = 22050, audio_only: bool = False):
+    """``audio_only``: batches are ``(audio, audio_len)`` (vocoder / codec training) instead of ``(text, text_len, audio, audio_len)``."""
     get = config.get if hasattr(config, "get") else (lambda k, d=None: getattr(config, k, d))
     syn = get("synthetic", None)
     ds = SyntheticTTSDataset(tokenizer=tokenizer, sample_rate=sample_rate, **dict(syn)) if syn is not None else \
         TextToSpeechDataset(get("manifest_filepath"), tokenizer, sample_rate, get("min_duration", 0.1), get("max_duration", None))
+    if audio_only:
+        ds.collate_fn = _collate_audio_only
     return get_dataloader_from_config(config, ds, 0, 1)

@@ -313,3 +313,45 @@ def test_model_catalogue_lists_by_class_and_resolves_names_from_the_local_cache(
     path = mc.fetch("QuartzNet15x5Base-En", downloader)
     assert mc.fetch("QuartzNet15x5Base-En", downloader) == path and len(calls) == 1 and "QuartzNet15x5Base-En" in calls[0]
     assert mc.resolve_local("QuartzNet15x5Base-En") == path
+
+
+def test_trainer_manual_optimization_updates_each_optimizer_from_its_own_loss():
+    import torch
+    from speech_b200.core.config import OmegaConf
+    from speech_b200.core.modelpt import ModelPT
+    from speech_b200.core.trainer import Trainer
+
+    class TwoPlayers(ModelPT):
+        def __init__(self, cfg, trainer=None):
+            super().__init__(cfg=cfg, trainer=trainer)
+            self.a = torch.nn.Parameter(torch.tensor(1.0))
+            self.b = torch.nn.Parameter(torch.tensor(1.0))
+            self.automatic_optimization = False
+            self.seen = []
+
+        def setup_training_data(self, c):
+            self._train_dl = torch.utils.data.DataLoader(torch.arange(4.0), batch_size=1)
+
+        def setup_validation_data(self, c):
+            self._validation_dl = None
+
+        def configure_optimizers(self):
+            self._optimizers = [torch.optim.SGD([self.a], lr=0.1), torch.optim.SGD([self.b], lr=0.1)]
+            return self._optimizers
+
+        def training_step(self, batch, batch_idx):
+            tr = self._trainer
+            assert tr.in_manual_step
+            # player b minimises (a * b) with a held fixed; player a then minimises -(a * b) and its loss also reaches b
+            tr.manual_step(self.a.detach() * self.b, self._optimizers[1])
+            loss_a = -(self.a * self.b)
+            tr.manual_step(loss_a, self._optimizers[0])
+            self.seen.append((float(self.a), float(self.b)))
+            return {"loss": loss_a.detach()}
+
+    m = TwoPlayers(OmegaConf.create({"train_ds": {}}))
+    m.setup_training_data(None)
+    tr = Trainer(max_steps=1, accelerator="cpu", devices=1, enable_checkpointing=False, logger=False, gradient_clip_val=0.0)
+    tr.fit(m)
+    # b moved by -lr * a = 0.9 (its own loss only: the gradient that a's loss left on b was never applied); a moved by +lr * b
+    assert tr.global_step == 1 and m.seen[0][1] == pytest.approx(0.9) and m.seen[0][0] == pytest.approx(1.0 + 0.1 * 0.9)

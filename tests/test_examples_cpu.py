@@ -172,3 +172,21 @@ def test_duplex_infer_example_and_mesh_strategy_from_yaml(tmp_path):
                                                           "device=cpu", "batch_size=2"], str(tmp_path))
     recs = [json.loads(l) for l in open(out)]
     assert len(recs) == 2 and all("pred_text" in r and "pred_user_text" in r for r in recs) and "turn taking" in log
+
+
+def test_tts_training_examples_run_through_the_trainer(tmp_path):
+    """FastPitch, the aligner, HiFi-GAN and the codec train from their shipped YAML on synthetic tone data; the adversarial
+    models go through the trainer's manual optimisation (generator and discriminator updated in turn)."""
+    common = ["trainer.max_steps=2", "trainer.max_epochs=null", "trainer.accelerator=cpu", "trainer.devices=1", "trainer.strategy=auto",
+              "exp_manager.create_tensorboard_logger=false", "exp_manager.create_checkpoint_callback=false", "model.train_ds.manifest_filepath=null",
+              "model.sample_rate=8000"]
+    syn = "+model.train_ds.synthetic={num_samples: 4, min_chars: 3, max_chars: 5}"
+    small_tf = ["model.symbols_embedding_dim=32", "model.d_inner=64", "model.encoder_layers=1", "model.decoder_layers=1", "model.n_mel_channels=20",
+                "model.n_fft=256", "model.hop_length=64", "model.win_length=256", "model.train_ds.batch_size=2", "model.train_ds.num_workers=0"]
+    _run("examples/tts/fastpitch.py", common + small_tf + [syn, f"exp_manager.exp_dir={tmp_path / 'fp'}", "model.optim.sched.warmup_steps=1"], str(tmp_path))
+    assert os.path.isdir(tmp_path / "fp" / "FastPitch")
+    _run("examples/tts/aligner.py", common + [syn, "model.symbols_embedding_dim=16", "model.n_mel_channels=20", "model.mel={n_fft: 256, hop: 64, win: 256}",
+                                              "model.train_ds.batch_size=2", "model.train_ds.num_workers=0", f"exp_manager.exp_dir={tmp_path / 'al'}"], str(tmp_path))
+    _run("examples/tts/hifigan.py", common + [syn, "model.generator={input_dim: 20, up_sample_rates: [4, 4, 4], base_channels: 16, resblock_kernel_sizes: [3]}",
+                                              "model.discriminator={periods: [2], stft_resolutions: [[256, 64, 256]]}", "model.mel={n_fft: 256, hop: 64, win: 256}",
+                                              "model.train_ds.batch_size=2", "model.train_ds.num_workers=0", f"exp_manager.exp_dir={tmp_path / 'hg'}"], str(tmp_path))
