@@ -23,21 +23,21 @@ def main(cfg):
     dev = "cpu" if (cfg.cuda is not None and int(cfg.cuda) < 0) or not torch.cuda.is_available() else f"cuda:{cfg.cuda or 0}"
     model = ASRModel.restore_from(cfg.model_path, map_location=dev).to(dev).eval()
     items = read_manifest(cfg.dataset_manifest)
-    hyps = model.transcribe([it["audio_filepath"] for it in items], batch_size=cfg.batch_size, return_hypotheses=True, timestamps=True)
-    spf = float(model.cfg.preprocessor.get("window_stride", 0.01)) * int(model.encoder.subsampling_factor)
-    eou_id = getattr(model, "eou_token_id", None)
-    preds, refs = [], []
+    hyps = model.transcribe([it["audio_filepath"] for it in items], batch_size=cfg.batch_size, return_hypotheses=True)
+    if not hasattr(model, "eou_predictions_from_hypothesis"):
+        raise ValueError(f"{type(model).__name__} has no end-of-utterance tokens")
+    tp = fp = fn = n = 0
+    latency, early = [], []
     for it, h in zip(items, hyps):
-        ys = [int(t) for t in (h.y_sequence.tolist() if torch.is_tensor(h.y_sequence) else h.y_sequence)]
-        ts = h.timestamp.tolist() if torch.is_tensor(h.timestamp) else list(h.timestamp if not isinstance(h.timestamp, dict) else h.timestamp.get("timestep", []))
-        hit = [t for y, t in zip(ys, ts) if eou_id is not None and y == eou_id]
-        end = (hit[-1] + 1) * spf if hit else (ts[-1] + 1) * spf if ts else 0.0
-        preds.append({"start_time": 0.0, "end_time": float(end), "eou_pred": bool(hit) or eou_id is None})
-        refs.append({"start_time": 0.0, "end_time": float(it.get("eou_time", it["duration"]))})
-    r = evaluate_eou(preds, refs, collar=float(cfg.collar))
-    lat = np.asarray(r.latency or [0.0])
-    summary = {"precision": r.true_positives / max(1, r.true_positives + r.false_positives), "recall": r.true_positives / max(1, r.num_utterances),
-               "early_cutoffs": len(r.early_cutoff), "missing": r.false_negatives, "latency_p50": float(np.percentile(lat, 50)), "latency_p90": float(np.percentile(lat, 90))}
+        r = evaluate_eou(model.eou_predictions_from_hypothesis(h), [{"start_time": 0.0, "end_time": float(it.get("eou_time", it["duration"]))}],
+                         collar=float(cfg.collar))
+        tp, fp, fn, n = tp + r.true_positives, fp + r.false_positives, fn + r.false_negatives, n + r.num_utterances
+        latency += r.latency
+        early += r.early_cutoff
+
+    lat = np.asarray(latency or [0.0])
+    summary = {"precision": tp / max(1, tp + fp), "recall": tp / max(1, n), "early_cutoffs": len(early), "missing": fn,
+               "latency_p50": float(np.percentile(lat, 50)), "latency_p90": float(np.percentile(lat, 90))}
     with open(cfg.output_filename, "w") as f:
         json.dump(summary, f, indent=2)
     logging.info(json.dumps(summary))

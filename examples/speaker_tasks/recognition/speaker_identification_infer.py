@@ -32,6 +32,8 @@ def main(cfg):
     speakers = sorted({it["label"] for it in enroll})
     ids = np.asarray([speakers.index(it["label"]) for it in enroll])
     if cfg.backend.backend_model == "cosine_similarity":
+        center = e_emb.mean(0, keepdims=True)                     # the part all speakers share carries no identity
+        e_emb, t_emb = norm(e_emb - center), norm(t_emb - center)
         cents = norm(np.stack([e_emb[ids == k].mean(0) for k in range(len(speakers))]))
         sim = t_emb @ cents.T
         pred, score = sim.argmax(1), sim.max(1)
@@ -41,6 +43,8 @@ def main(cfg):
         nc = cfg.backend.neural_classifier
         clf = torch.nn.Linear(e_emb.shape[1], len(speakers))
         opt = torch.optim.Adam(clf.parameters(), lr=nc.lr, weight_decay=nc.weight_decay)
+        mu, sd = e_emb.mean(0, keepdims=True), e_emb.std(0, keepdims=True) + 1e-6        # embeddings of one model share a large common part
+        e_emb, t_emb = (e_emb - mu) / sd, (t_emb - mu) / sd
         X, Y = torch.tensor(e_emb, dtype=torch.float32), torch.tensor(ids)
         for _ in range(int(nc.epochs)):
             opt.zero_grad()

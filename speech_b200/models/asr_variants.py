@@ -216,9 +216,9 @@ class EncDecMultiTalkerRNNTBPEModel(EncDecRNNTBPEModel):
         self.bg_spk_kernels = nn.ModuleDict({str(i): SpeakerKernel(d) for i in layers}) if self.add_bg_spk_kernel else None
         self._spk_targets: Optional[torch.Tensor] = None
         self._bg_targets: Optional[torch.Tensor] = None
-        self._hooks = []
+        self._spk_hook_handles = []
         for i in layers:
-            self._hooks.append(self.encoder.layers[i].register_forward_pre_hook(self._make_hook(str(i)), with_kwargs=True))
+            self._spk_hook_handles.append(self.encoder.layers[i].register_forward_pre_hook(self._make_hook(str(i)), with_kwargs=True))
 
     def set_speaker_targets(self, spk_targets: Optional[torch.Tensor], bg_spk_targets: Optional[torch.Tensor] = None):
         """``spk_targets`` [B, T'] activity (0..1) of the speaker to transcribe; ``bg_spk_targets`` everyone else."""

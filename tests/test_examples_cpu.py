@@ -190,3 +190,84 @@ def test_tts_training_examples_run_through_the_trainer(tmp_path):
     _run("examples/tts/hifigan.py", common + [syn, "model.generator={input_dim: 20, up_sample_rates: [4, 4, 4], base_channels: 16, resblock_kernel_sizes: [3]}",
                                               "model.discriminator={periods: [2], stft_resolutions: [[256, 64, 256]]}", "model.mel={n_fft: 256, hop: 64, win: 256}",
                                               "model.train_ds.batch_size=2", "model.train_ds.num_workers=0", f"exp_manager.exp_dir={tmp_path / 'hg'}"], str(tmp_path))
+
+
+def test_hybrid_conversion_evaluation_finetune_and_speaker_examples(tmp_path):
+    from speech_b200.data.audio_to_text import save_wav
+
+    g = np.random.default_rng(0)
+    man = tmp_path / "test.json"
+    with open(man, "w") as f:
+        for i in range(3):
+            p = str(tmp_path / f"a{i}.wav")
+            save_wav(p, (0.1 * g.standard_normal(16000 + 3000 * i)).astype(np.float32))
+            f.write(json.dumps({"audio_filepath": p, "duration": 1.0 + 0.1875 * i, "text": "w1 w2"}) + "\n")
+    small = ["model.tokenizer.type=synthetic", "+model.tokenizer.vocab_size=32", "model.tokenizer.dir=null",
+             "+model.train_ds.synthetic={num_samples: 4, vocab_size: 32, min_duration: 1.0, max_duration: 1.2}", "model.train_ds.manifest_filepath=null",
+             "model.validation_ds.manifest_filepath=null", "model.train_ds.batch_size=4", "model.train_ds.num_workers=0", "model.encoder.n_layers=1",
+             "model.encoder.d_model=64", "model.encoder.n_heads=4", "model.model_defaults.enc_hidden=64", "trainer.max_steps=1", "trainer.max_epochs=null",
+             "trainer.accelerator=cpu", "trainer.devices=1", "trainer.precision=32", "trainer.strategy=auto", "exp_manager.create_tensorboard_logger=false"]
+    _run("examples/asr/asr_hybrid_transducer_ctc/speech_to_text_hybrid_rnnt_ctc_bpe.py", small + [f"exp_manager.exp_dir={tmp_path / 'exp'}"], str(tmp_path))
+    hybrid = glob.glob(str(tmp_path / "exp" / "**" / "*.nemo"), recursive=True)[0]
+    ctc = str(tmp_path / "ctc.nemo")
+    _run("examples/asr/asr_hybrid_transducer_ctc/helpers/convert_nemo_asr_hybrid_to_ctc.py", ["-i", hybrid, "-o", ctc, "-t", "ctc"], str(tmp_path))
+    assert os.path.getsize(ctc) < os.path.getsize(hybrid)                      # the prediction and joint networks are gone
+    log = _run("examples/asr/speech_to_text_eval.py", [f"model_path={ctc}", f"dataset_manifest={man}", f"output_filename={tmp_path / 'eval.json'}", "cuda=-1",
+                                                       "scores_per_sample=true", "text_processing.do_lowercase=true"], str(tmp_path))
+    rows = [json.loads(l) for l in open(tmp_path / "eval.json")]
+    assert "WER:" in log and len(rows) == 3 and all("pred_text" in r and "wer" in r for r in rows)
+    log = _run("examples/asr/speech_to_text_eval.py", [f"dataset_manifest={tmp_path / 'eval.json'}", "only_score_manifest=true", "tolerance=1000",
+                                                       f"output_filename={tmp_path / 'eval2.json'}"], str(tmp_path))
+    assert "WER:" in log
+    _run("examples/asr/speech_to_text_finetune.py", [f"init_from_nemo_model={ctc}", "model.train_ds={manifest_filepath: " + str(man) + ", batch_size: 2, shuffle: true, "
+                                                     "num_workers: 0, max_duration: 5.0}", "trainer.max_steps=2", "trainer.accelerator=cpu",
+                                                     f"exp_manager.exp_dir={tmp_path / 'ft'}"], str(tmp_path))
+    _run("examples/asr/asr_vad/speech_to_text_with_vad.py", [f"asr_model={ctc}", "use_energy_vad=true", f"manifest_filepath={man}",
+                                                             f"output_filename={tmp_path / 'vadasr.json'}", "cuda=-1"], str(tmp_path))
+    assert len(open(tmp_path / "vadasr.json").read().splitlines()) == 3
+
+    # speaker pipeline: train -> embeddings -> trial scoring -> identification
+    t = np.arange(16000) / 16000
+    rows = []
+    for spk, f0 in (("A", 150), ("B", 300)):
+        os.makedirs(tmp_path / "spk" / spk / "s")
+        for i in range(3):
+            p = str(tmp_path / "spk" / spk / "s" / f"u{i}.wav")
+            save_wav(p, (0.3 * np.sin(2 * np.pi * f0 * t) + 0.02 * g.standard_normal(16000)).astype(np.float32))
+            rows.append({"audio_filepath": p, "duration": 1.0, "label": spk})
+    dump = lambda name, rs: open(tmp_path / name, "w").write("\n".join(json.dumps(r) for r in rs))  # noqa: E731
+    dump("spk_train.json", rows)
+    dump("enroll.json", [r for r in rows if not r["audio_filepath"].endswith("u2.wav")])
+    dump("spk_test.json", [r for r in rows if r["audio_filepath"].endswith("u2.wav")])
+    tr = [r["audio_filepath"] for r in rows]
+    open(tmp_path / "trials.txt", "w").write(f"1 {tr[0]} {tr[1]}\n0 {tr[0]} {tr[3]}\n1 {tr[3]} {tr[4]}\n0 {tr[2]} {tr[5]}\n")
+    _run("examples/speaker_tasks/recognition/speaker_reco.py", [
+        f"model.train_ds.manifest_filepath={tmp_path / 'spk_train.json'}", f"model.validation_ds.manifest_filepath={tmp_path / 'spk_train.json'}",
+        "model.train_ds.batch_size=6", "model.validation_ds.batch_size=6", "model.train_ds.num_workers=0", "model.validation_ds.num_workers=0",
+        "model.decoder.num_classes=2", "trainer.max_steps=10", "trainer.max_epochs=null", "trainer.accelerator=cpu", "trainer.devices=1", "trainer.strategy=auto",
+        "trainer.precision=32", f"exp_manager.exp_dir={tmp_path / 'spkexp'}", "exp_manager.create_tensorboard_logger=false"], str(tmp_path))
+    spk = glob.glob(str(tmp_path / "spkexp" / "**" / "*.nemo"), recursive=True)[0]
+    out = _run("examples/speaker_tasks/recognition/extract_speaker_embeddings.py", [f"--manifest={tmp_path / 'spk_train.json'}", f"--model_path={spk}",
+                                                                                      f"--embedding_dir={tmp_path / 'emb'}"], str(tmp_path))
+    pkl = str(tmp_path / "emb" / "embeddings" / "spk_train_embeddings.pkl")
+    assert pkl in out
+    out = _run("examples/speaker_tasks/recognition/voxceleb_eval.py", [f"--trial_file={tmp_path / 'trials.txt'}", f"--emb={pkl}"], str(tmp_path))
+    assert "EER:" in out and "minDCF:" in out                # the 10-step model's quality is not the subject here
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("voxceleb_eval", os.path.join(REPO, "examples/speaker_tasks/recognition/voxceleb_eval.py"))
+    sys.path.insert(0, os.path.join(REPO, "examples/speaker_tasks/recognition"))
+    try:
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+    finally:
+        sys.path.pop(0)
+    eer, dcf = mod.eer_and_min_dcf(np.array([0.9, 0.8, 0.7, 0.3, 0.2, 0.1]), np.array([1, 1, 1, 0, 0, 0]))
+    assert eer == 0.0 and dcf == 0.0
+    eer, _ = mod.eer_and_min_dcf(np.array([0.9, 0.8, 0.3, 0.7, 0.2, 0.1]), np.array([1, 1, 1, 0, 0, 0]))
+    assert abs(eer - 1 / 3) < 1e-9
+    for backend in ("cosine_similarity", "neural_classifier"):
+        out = _run("examples/speaker_tasks/recognition/speaker_identification_infer.py", [
+            f"model_path={spk}", f"data.enrollment_manifest={tmp_path / 'enroll.json'}", f"data.test_manifest={tmp_path / 'spk_test.json'}",
+            f"data.out_manifest={tmp_path / ('id_' + backend + '.json')}", f"backend.backend_model={backend}", "cuda=-1"], str(tmp_path))
+        assert "accuracy:" in out and len(open(tmp_path / ("id_" + backend + ".json")).read().splitlines()) == 2
