@@ -470,12 +470,61 @@ class SSLDisentangler(ModelPT):
         self.speaker_proj = nn.Linear(2 * d, self.speaker_dim)
         self.speaker_out = nn.Linear(self.speaker_dim, self.num_speakers)
         self.content_weight, self.speaker_weight = float(cfg_get(cfg, "content_loss_weight", 1.0)), float(cfg_get(cfg, "speaker_loss_weight", 1.0))
+        self._ssl_ready = True
+        if not self._is_model_being_restored and self._train_dl is None:
+            self._setup_dataloaders_from_cfg()
+
+    def _setup_dataloaders_from_cfg(self):
+        if getattr(self, "_ssl_ready", False):
+            super()._setup_dataloaders_from_cfg()
+
+    def _loader(self, c):
+        """Manifest lines ``{"audio_filepath", "duration", "text" (space-separated content units, e.g. phonemes), "speaker"}``; unit and
+        speaker inventories come from ``content_units`` / ``speakers`` of the data block (lists) or are collected from the manifest."""
+        if c is None or (c.get("manifest_filepath", None) is None and c.get("synthetic", None) is None):
+            return None
+        from ..data.audio_to_text import load_audio, read_manifest
+
+        sr = int(cfg_get(self._cfg, "sample_rate", 16000))
+        if c.get("synthetic", None) is not None:
+            syn = dict(c.synthetic)
+            g = torch.Generator().manual_seed(int(syn.get("seed", 0)))
+            items = [(0.1 * torch.randn(int(sr * 0.5), generator=g), torch.randint(0, self.num_phonemes, (4,), generator=g),
+                      int(torch.randint(0, self.num_speakers, (1,), generator=g))) for _ in range(int(syn.get("num_samples", 8)))]
+        else:
+            rows = read_manifest(c.manifest_filepath, max_duration=c.get("max_duration", None))
+            units = list(c.get("content_units", None) or sorted({u for r in rows for u in r["text"].split()}))
+            spks = list(c.get("speakers", None) or sorted({str(r["speaker"]) for r in rows}))
+            if len(units) > self.num_phonemes or len(spks) > self.num_speakers:
+                raise ValueError(f"{len(units)} content units / {len(spks)} speakers exceed num_phonemes={self.num_phonemes} / num_speakers={self.num_speakers}")
+            u2i, s2i = {u: i for i, u in enumerate(units)}, {s: i for i, s in enumerate(spks)}
+
+            class _DS(torch.utils.data.Dataset):
+                def __len__(self_inner):
+                    return len(rows)
+
+                def __getitem__(self_inner, i):
+                    r = rows[i]
+                    a = torch.as_tensor(load_audio(r["audio_filepath"], target_sr=sr, offset=float(r.get("offset", 0) or 0), duration=r.get("duration")), dtype=torch.float32)
+                    return a, torch.tensor([u2i[u] for u in r["text"].split()], dtype=torch.long), s2i[str(r["speaker"])]
+            items = _DS()
+
+        def collate(batch):
+            pad = torch.nn.utils.rnn.pad_sequence
+            a, p, s = zip(*batch)
+            return (pad(a, batch_first=True), torch.tensor([len(x) for x in a]), pad(p, batch_first=True), torch.tensor([len(x) for x in p]), torch.tensor(s))
+        return torch.utils.data.DataLoader(items, batch_size=int(c.get("batch_size", 8)), shuffle=bool(c.get("shuffle", False)), collate_fn=collate,
+                                           num_workers=int(c.get("num_workers", 0)))
 
     def setup_training_data(self, c):
-        self._train_dl = None
+        self._train_dl = self._loader(c)
 
     def setup_validation_data(self, c):
-        self._validation_dl = None
+        self._validation_dl = self._loader(c)
+
+    def validation_step(self, batch, batch_idx, dataloader_idx=0):
+        with torch.no_grad():
+            return {"val_loss": self.training_step(batch, batch_idx)["loss"]}
 
     def forward(self, input_signal, input_signal_length):
         feats, flen = self.preprocessor(input_signal=input_signal, length=input_signal_length)

@@ -271,3 +271,73 @@ def test_hybrid_conversion_evaluation_finetune_and_speaker_examples(tmp_path):
             f"model_path={spk}", f"data.enrollment_manifest={tmp_path / 'enroll.json'}", f"data.test_manifest={tmp_path / 'spk_test.json'}",
             f"data.out_manifest={tmp_path / ('id_' + backend + '.json')}", f"backend.backend_model={backend}", "cuda=-1"], str(tmp_path))
         assert "accuracy:" in out and len(open(tmp_path / ("id_" + backend + ".json")).read().splitlines()) == 2
+
+
+def test_voice_agent_stream_parsers_and_websocket_url():
+    import importlib.util
+
+    def load(rel):
+        spec = importlib.util.spec_from_file_location(os.path.basename(rel)[:-3], os.path.join(REPO, rel))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod
+
+    rp = load("examples/voice_agent/server/parsers/reasoning_parser.py")
+    text = "<think>the user greets me</think>Hello! <think>short</think>How are you?"
+    for size in (1, 3, 7, len(text)):                      # any chunking, tags cut in the middle included
+        p = rp.StreamingReasoningParser()
+        r = c = ""
+        for i in range(0, len(text), size):
+            d = p.feed(text[i:i + size])
+            r, c = r + d.reasoning, c + d.content
+        d = p.flush()
+        assert (r + d.reasoning, c + d.content) == ("the user greets meshort", "Hello! How are you?"), size
+    assert rp.split_reasoning("planning...</think>Answer") == ("planning...", "Answer")       # closing tag without an opening one
+    assert rp.split_reasoning("a < b and x <thin air") == (None, "a < b and x <thin air")
+    tp = load("examples/voice_agent/server/parsers/toolcall_parser_streaming.py")
+    text = 'Let me check. <TOOLCALL>[{"name": "weather", "arguments": {"city": "Paris {FR}", "note": "say \\"hi\\""}}, {"name": "time", "arguments": "{\\"tz\\": \\"CET\\"}"}]</TOOLCALL> Done.'
+    for size in (1, 5, 11, len(text)):
+        p = tp.StreamingToolCallParser()
+        content, calls, first_call_at = "", [], None
+        for i in range(0, len(text), size):
+            d = p.feed(text[i:i + size])
+            content += d.content
+            if d.tool_calls and first_call_at is None:
+                first_call_at = i
+            calls += d.tool_calls
+        d = p.flush()
+        content += d.content
+        assert content == "Let me check.  Done." and [c["function"]["name"] for c in calls] == ["weather", "time"], size
+        assert calls[0]["function"]["arguments"] == {"city": "Paris {FR}", "note": 'say "hi"'} and calls[1]["function"]["arguments"] == {"tz": "CET"}
+        assert [c["id"] for c in calls] == ["call_0", "call_1"]
+        if size == 1:
+            assert first_call_at < text.index('{"name": "time"')          # the first call is out before the second one is complete
+    p = tp.StreamingToolCallParser()
+    p.feed('<TOOLCALL>[{"name": "x", "arguments": {"a": 1')
+    assert p.flush().errors
+    wu = load("examples/voice_agent/server/websocket_url.py")
+    assert wu.websocket_url("0.0.0.0", 7860) == "ws://localhost:7860/ws"
+    assert wu.websocket_url("0.0.0.0", 7860, headers={"Host": "demo.example.com", "X-Forwarded-Proto": "https", "X-Forwarded-Prefix": "/agent/"}) == "wss://demo.example.com/agent/ws"
+    assert wu.websocket_url("::1", 9000, path="/audio") == "ws://[::1]:9000/audio"
+    assert wu.websocket_url("0.0.0.0", 1, public_url="https://x.example.org/base") == "wss://x.example.org/base/ws"
+
+
+def test_g2p_and_ssl_tts_examples(tmp_path):
+    lex = [("cat", "k æ t"), ("tack", "t æ k"), ("act", "æ k t"), ("box", "b ɑ k s"), ("tax", "t æ k s"), ("cab", "k æ b")]
+    (tmp_path / "train.json").write_text("\n".join(json.dumps({"text_graphemes": g_, "text": p}, ensure_ascii=False) for g_, p in lex), encoding="utf-8")
+    (tmp_path / "phones.txt").write_text("\n".join(sorted({x for _, p in lex for x in p.split()})), encoding="utf-8")
+    ds = "{manifest_filepath: " + str(tmp_path / "train.json") + ", batch_size: 6}"
+    log = _run("examples/tts/g2p/g2p_train_and_evaluate.py", ["model_type=ctc", f"model.phonemes={tmp_path / 'phones.txt'}", f"model.train_ds={ds}", f"model.validation_ds={ds}",
+                                                               f"model.test_ds={ds}", "do_testing=true", "model.d_model=32", "model.n_layers=1", "model.n_heads=2",
+                                                               "model.optim.lr=0.005", "trainer.max_epochs=150", "trainer.accelerator=cpu", f"exp_manager.exp_dir={tmp_path / 'exp'}"],
+               str(tmp_path))
+    assert "test PER" in log
+    nemo = glob.glob(str(tmp_path / "exp" / "**" / "*.nemo"), recursive=True)[0]
+    log = _run("examples/tts/g2p/g2p_inference.py", [f"pretrained_model={nemo}", f"manifest_filepath={tmp_path / 'train.json'}", f"output_file={tmp_path / 'out.json'}"],
+               str(tmp_path))
+    assert "PER:" in log and float(log.split("PER:")[1].split()[0]) < 0.2
+    assert "pred_text" in json.loads(open(tmp_path / "out.json", encoding="utf-8").readline())
+    _run("examples/tts/ssl_tts.py", ["+model.train_ds.synthetic={num_samples: 4}", "model.train_ds.manifest_filepath=null", "model.train_ds.batch_size=2",
+                                     "model.train_ds.num_workers=0", "model.encoder.n_layers=1", "model.encoder.d_model=32", "model.encoder.n_heads=2", "model.encoder_dim=32",
+                                     "model.encoder.subsampling_conv_channels=16", "trainer.max_steps=2", "trainer.max_epochs=null", "trainer.accelerator=cpu", "trainer.devices=1",
+                                     "trainer.strategy=auto", f"exp_manager.exp_dir={tmp_path / 'ssl'}", "exp_manager.create_tensorboard_logger=false"], str(tmp_path))
