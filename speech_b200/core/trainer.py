@@ -604,8 +604,24 @@ class Trainer:
                 sd[n] = p._mp_gather(sd[n])
         return {k: v.cpu() for k, v in sd.items()}
 
-    def save_checkpoint(self, filepath: str, weights_only: bool = False):
+    def save_checkpoint(self, filepath: str, weights_only: bool = False, checkpoint_format: Optional[str] = None):
+        """``checkpoint_format="dcp"`` (or a path ending in ``.dcp``) writes a distributed-checkpoint directory: the model tensors in
+        PyTorch's DCP layout, written cooperatively by all ranks, plus ``trainer_state.pt`` (optimizers, schedulers, counters) from
+        rank 0.  The default is one ``.ckpt`` file from rank 0."""
         ckpt = self.dump_checkpoint(weights_only)
+        if (checkpoint_format or getattr(self, "checkpoint_format", None)) == "dcp" or str(filepath).endswith(".dcp"):
+            from ..utils.dcp_io import DCPCheckpointIO
+
+            tensors = {k: v for k, v in ckpt["state_dict"].items() if torch.is_tensor(v)}
+            DCPCheckpointIO().save_checkpoint(tensors, filepath, extra={"global_step": self.global_step, "epoch": self.current_epoch})
+            if self.is_global_zero:
+                rest = {k: v for k, v in ckpt.items() if k != "state_dict"}
+                rest["state_dict_extra"] = {k: v for k, v in ckpt["state_dict"].items() if not torch.is_tensor(v)}
+                torch.save(rest, os.path.join(filepath, "trainer_state.pt.tmp"))
+                os.replace(os.path.join(filepath, "trainer_state.pt.tmp"), os.path.join(filepath, "trainer_state.pt"))
+            if self.world_size > 1 and dist.is_initialized():
+                dist.barrier()
+            return
         if self.is_global_zero:
             os.makedirs(os.path.dirname(os.path.abspath(filepath)), exist_ok=True)
             tmp = filepath + ".tmp"
@@ -615,7 +631,14 @@ class Trainer:
             dist.barrier()
 
     def _restore_checkpoint(self, path: str, weights_only: bool = False):
-        ckpt = torch.load(path, map_location="cpu", weights_only=False)
+        if os.path.isdir(path):
+            from ..utils.dcp_io import DCPCheckpointIO
+
+            state, _ = DCPCheckpointIO().load_checkpoint(path)
+            ckpt = torch.load(os.path.join(path, "trainer_state.pt"), map_location="cpu", weights_only=False)
+            ckpt["state_dict"] = dict(state, **ckpt.pop("state_dict_extra", {}))
+        else:
+            ckpt = torch.load(path, map_location="cpu", weights_only=False)
         sharded = [o for o in (getattr(self, "optimizers", []) or []) if hasattr(o, "load_full_params")]
         if sharded:
             # sharded parameters are taken slice-wise by their optimizer; the module only loads what the optimizer does not own

@@ -355,3 +355,48 @@ def test_trainer_manual_optimization_updates_each_optimizer_from_its_own_loss():
     tr.fit(m)
     # b moved by -lr * a = 0.9 (its own loss only: the gradient that a's loss left on b was never applied); a moved by +lr * b
     assert tr.global_step == 1 and m.seen[0][1] == pytest.approx(0.9) and m.seen[0][0] == pytest.approx(1.0 + 0.1 * 0.9)
+
+
+def test_trainer_resumes_bit_identically_from_a_dcp_directory(tmp_path):
+    import torch
+    from speech_b200.core.config import OmegaConf
+    from speech_b200.core.modelpt import ModelPT
+    from speech_b200.core.trainer import Trainer
+
+    class Tiny(ModelPT):
+        def __init__(self, cfg, trainer=None):
+            super().__init__(cfg=cfg, trainer=trainer)
+            torch.manual_seed(0)
+            self.net = torch.nn.Sequential(torch.nn.Linear(4, 8), torch.nn.Tanh(), torch.nn.Linear(8, 1))
+
+        def setup_training_data(self, c):
+            g = torch.Generator().manual_seed(1)
+            data = [(torch.randn(4, generator=g), torch.randn(1, generator=g)) for _ in range(12)]
+            self._train_dl = torch.utils.data.DataLoader(data, batch_size=2, shuffle=False)
+
+        def setup_validation_data(self, c):
+            self._validation_dl = None
+
+        def configure_optimizers(self):
+            return torch.optim.Adam(self.net.parameters(), lr=1e-2)
+
+        def training_step(self, batch, batch_idx):
+            x, y = batch
+            return {"loss": (self.net(x) - y).pow(2).mean()}
+
+    def run(steps, ckpt=None):
+        m = Tiny(OmegaConf.create({}))
+        m.setup_training_data(None)
+        tr = Trainer(max_steps=steps, accelerator="cpu", devices=1, enable_checkpointing=False, logger=False)
+        tr.fit(m, ckpt_path=ckpt)
+        return m, tr
+
+    whole, _ = run(5)
+    half, tr = run(3)
+    path = str(tmp_path / "step3.dcp")
+    tr.save_checkpoint(path)
+    assert os.path.exists(os.path.join(path, ".metadata")) and os.path.exists(os.path.join(path, "trainer_state.pt"))
+    resumed, tr2 = run(5, ckpt=path)
+    assert tr2.global_step == 5
+    for a, b in zip(whole.parameters(), resumed.parameters()):
+        assert torch.equal(a, b)

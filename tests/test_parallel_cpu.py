@@ -522,3 +522,44 @@ def test_trainer_with_parallel_strategy_trains_salm_on_a_mesh_and_resumes_four_r
                          capture_output=True, text=True, timeout=900, env=dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2"))
     assert out.returncode == 0, out.stderr[-4000:]
     assert out.stdout.count("RESULT ok") == 4
+
+
+DCP_SCRIPT = textwrap.dedent("""
+    import os, sys, torch, torch.distributed as dist
+    sys.path.insert(0, {repo!r})
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from speech_b200.utils.dcp_io import DCPCheckpointIO
+    path = {path!r}
+    torch.manual_seed(0)
+    table = torch.arange(10 * 3, dtype=torch.float32).view(10, 3)          # a row-sharded embedding: rank 0 holds 6 rows, rank 1 holds 4
+    split = [(0, 6), (6, 4)][rank]
+    replicated = torch.full((4,), 5.0)
+    io = DCPCheckpointIO()
+    io.save_checkpoint({{"emb": table[split[0]: split[0] + split[1]].clone(), "bias": replicated, "step": torch.tensor(11)}}, path,
+                       sharded={{"emb": (split[0], 10)}}, extra={{"note": "two ranks"}})
+    dist.barrier()
+    # restore on the same two ranks with ANOTHER split (3 / 7 rows): every rank gets its new rows
+    new = [(0, 3), (3, 7)][rank]
+    tmpl = {{"emb": torch.zeros(new[1], 3), "bias": torch.zeros(4), "step": torch.tensor(0)}}
+    out, extra = io.load_checkpoint(path, template=tmpl, sharded={{"emb": (new[0], 10)}})
+    assert torch.equal(out["emb"], table[new[0]: new[0] + new[1]]) and torch.equal(out["bias"], replicated) and int(out["step"]) == 11
+    assert extra == {{"note": "two ranks"}}
+    dist.barrier()
+    print("DCP_OK", rank)
+""")
+
+
+def test_dcp_checkpoint_written_by_two_ranks_reloads_with_another_sharding_and_on_one_rank(tmp_path):
+    import torch
+
+    from speech_b200.utils.dcp_io import DCPCheckpointIO
+
+    script = tmp_path / "dcp_script.py"
+    path = str(tmp_path / "ckpt")
+    script.write_text(DCP_SCRIPT.format(repo=REPO, path=path))
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29641",
+                          str(script)], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and out.stdout.count("DCP_OK") == 2, out.stderr[-3000:]
+    state, extra = DCPCheckpointIO().load_checkpoint(path)                    # a single process reads the whole thing
+    assert torch.equal(state["emb"], torch.arange(30, dtype=torch.float32).view(10, 3)) and int(state["step"]) == 11 and extra["note"] == "two ranks"

@@ -475,3 +475,31 @@ def test_vad_postprocessing_scoring_and_threshold_tuning(tmp_path):
     fp = V.generate_vad_frame_pred(Toy(), audio, window_length_in_sec=0.1, shift_length_in_sec=0.02)
     seg = V.generate_vad_segment_table(fp, {"onset": 0.7, "offset": 0.7})
     assert seg.shape == (1, 2) and abs(float(seg[0, 0]) - 0.25) < 0.08 and abs(float(seg[0, 1]) - 0.75) < 0.12
+
+
+def test_dcp_checkpoint_io_single_process_and_conversion(tmp_path):
+    from speech_b200.utils.dcp_io import DCPCheckpointIO, dcp_to_single_file, is_dcp_checkpoint, load_dcp_into_model, single_file_to_dcp
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(6, 4), torch.nn.Linear(4, 2))
+    io = DCPCheckpointIO(async_save=True)
+    d = str(tmp_path / "ckpt")
+    io.save_checkpoint(dict(model.state_dict(), step=torch.tensor(7)), d, extra={"epoch": 3})
+    io.finalize()
+    assert is_dcp_checkpoint(d)
+    state, extra = io.load_checkpoint(d)
+    assert extra == {"epoch": 3} and int(state["step"]) == 7 and torch.equal(state["0.weight"], model[0].weight)
+    other = torch.nn.Sequential(torch.nn.Linear(6, 4), torch.nn.Linear(4, 2))
+    with pytest.raises(RuntimeError):
+        load_dcp_into_model(other, d, strict=True)                              # "step" is not a parameter
+    missing, unexpected = load_dcp_into_model(other, d, strict=False)
+    assert missing == [] and unexpected == ["step"] and torch.equal(other[1].bias, model[1].bias)
+    dcp_to_single_file(d, str(tmp_path / "one.pt"))
+    single_file_to_dcp(str(tmp_path / "one.pt"), str(tmp_path / "back"))
+    again, extra2 = io.load_checkpoint(str(tmp_path / "back"))
+    assert extra2 == {"epoch": 3} and torch.equal(again["1.weight"], model[1].weight)
+    tmpl = {k: torch.zeros_like(v) for k, v in model.state_dict().items()}
+    io.load_checkpoint(d, template=tmpl)
+    assert torch.equal(tmpl["0.bias"], model[0].bias)
+    with pytest.raises(ValueError):
+        io.load_checkpoint(d, template={"0.weight": torch.zeros(3, 3)})
