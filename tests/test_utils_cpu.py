@@ -503,3 +503,50 @@ def test_dcp_checkpoint_io_single_process_and_conversion(tmp_path):
     assert torch.equal(tmpl["0.bias"], model[0].bias)
     with pytest.raises(ValueError):
         io.load_checkpoint(d, template={"0.weight": torch.zeros(3, 3)})
+
+
+def test_diarization_and_multispeaker_metrics():
+    from speech_b200.models.diarizers import nme_spectral_clustering
+    from speech_b200.utils.diar_metrics import (MultiBinaryAccuracy, cp_wer, diarization_error_rate, long_form_clustering, score_labels,
+                                                sot_speaker_alignment)
+
+    ref = [(0.0, 10.0, "A"), (10.0, 20.0, "B")]
+    # same segmentation with swapped names: the mapping absorbs the swap
+    r = diarization_error_rate(ref, [(0.0, 10.0, "x"), (10.0, 20.0, "y")], collar=0.0)
+    assert r["DER"] == 0.0 and r["mapping"] == {"x": "A", "y": "B"}
+    # boundary placed 2 s late: 2 s of confusion over 20 s; with a 0.25 s collar 0.25 s of it (and 1 s of reference) is not scored
+    r = diarization_error_rate(ref, [(0.0, 12.0, "x"), (12.0, 20.0, "y")], collar=0.0)
+    assert r["confusion"] == pytest.approx(0.1) and r["miss"] == 0.0 and r["false_alarm"] == 0.0
+    r = diarization_error_rate(ref, [(0.0, 12.0, "x"), (12.0, 20.0, "y")], collar=0.25)
+    assert r["total"] == pytest.approx(19.0) and r["confusion_time"] == pytest.approx(1.75)
+    # a missed stretch, a false alarm, and overlapped speech of which the hypothesis finds one speaker
+    ref2 = [(0.0, 10.0, "A"), (8.0, 12.0, "B")]
+    hyp2 = [(0.0, 9.0, "x"), (13.0, 14.0, "x")]
+    r = diarization_error_rate(ref2, hyp2, collar=0.0)
+    assert r["total"] == pytest.approx(14.0) and r["miss_time"] == pytest.approx(1.0 + 4.0) and r["false_alarm_time"] == pytest.approx(1.0)
+    r = diarization_error_rate(ref2, hyp2, collar=0.0, ignore_overlap=True)
+    assert r["total"] == pytest.approx(10.0) and r["miss_time"] == pytest.approx(2.0)                 # 10-12 s of B alone
+    pooled = score_labels({"a": ref, "b": ref2}, {"a": [(0.0, 10.0, "x"), (10.0, 20.0, "y")], "b": hyp2}, collar=0.0, ignore_overlap=False)
+    assert pooled["DER"] == pytest.approx(6.0 / 34.0) and pooled["items"]["a"] == 0.0
+    score, hyp_order, _ = cp_wer(["good morning all", "hello there my friend"], ["hello there friend", "good morning"])
+    assert score == pytest.approx(2 / 5) and hyp_order == ["hello there my friend", "good morning all"]
+    assert cp_wer(["a b", "c d", "e"], ["a b", "c d"])[0] == pytest.approx(1 / 4)                      # an extra speaker counts in full
+    acc = MultiBinaryAccuracy()
+    preds = torch.tensor([[[0.9, 0.1], [0.8, 0.7], [0.2, 0.9], [0.9, 0.9]]])
+    tgts = torch.tensor([[[1, 0], [1, 0], [0, 1], [0, 0]]]).float()
+    acc.update(preds, tgts, torch.tensor([3]))                                                          # the 4th frame is padding
+    f1, prec, rec = acc.compute()
+    assert prec == pytest.approx(3 / 4) and rec == 1.0 and acc.accuracy() == pytest.approx(5 / 6)
+    import numpy as np
+
+    rng = np.random.default_rng(0)
+    cents = rng.standard_normal((3, 16)) * 3
+    lab_true = rng.integers(0, 3, 600)
+    emb = cents[lab_true] + 0.3 * rng.standard_normal((600, 16))
+    cl = lambda aff, mx, oracle: nme_spectral_clustering(aff, mx, oracle)  # noqa: E731
+    lab = long_form_clustering(emb, cl, window=200, keep_per_cluster=20, max_num_speakers=4, oracle_num_speakers=3)
+    # same partition up to naming
+    pairs = {(int(a), int(b)) for a, b in zip(lab_true, lab)}
+    assert len(pairs) == 3 and len(set(lab.tolist())) == 3
+    score, by = sot_speaker_alignment("hello how are you <sc> fine thanks <sc> good to hear", ["hello how are you good to hear", "fine thanks"])
+    assert score == 0.0 and by == ["hello how are you good to hear", "fine thanks"]
