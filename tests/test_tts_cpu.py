@@ -643,3 +643,78 @@ def test_tts_data_stack_vocoder_magpie_featurizers_processors_trimming(tmp_path)
     assert float(np.abs(normalize_volume(sig, 0.5)).max()) == pytest.approx(0.5)
     p = BetaBinomialInterpolator()(37, 12)
     assert p.shape == (37, 12) and int(p[0].argmax()) == 0 and int(p[-1].argmax()) == 11
+
+
+def test_seanet_codec_and_residual_vector_quantisers():
+    from speech_b200.tts.encodec_modules import EuclideanCodebook, GroupResidualVectorQuantizer, ResidualVectorQuantizer, SEANetDecoder, SEANetEncoder
+
+    torch.manual_seed(0)
+    enc = SEANetEncoder(down_sample_rates=(2, 4), base_channels=4, encoded_dim=8, rnn_layers=1)
+    dec = SEANetDecoder(up_sample_rates=(4, 2), base_channels=16, encoded_dim=8, rnn_layers=1)
+    audio, alen = torch.randn(2, 160), torch.tensor([160, 120])
+    z, zl = enc(audio, alen)
+    assert z.shape == (2, 8, 20) and zl.tolist() == [20, 15] and float(z[1, :, 15:].abs().sum()) == 0.0
+    y, yl = dec(z, zl)
+    assert y.shape == (2, 160) and yl.tolist() == [160, 120] and float(y[1, 120:].abs().sum()) == 0.0
+    # padding does not change the valid part
+    z2, _ = enc(torch.cat([audio[1:, :120], torch.randn(1, 40)], 1), torch.tensor([120]))
+    assert torch.allclose(z2[0, :, :15], z[1, :, :15], atol=1e-5)
+    # codebook: k-means start on the first batch, EMA pull towards the data, dead codes re-seeded
+    cb = EuclideanCodebook(16, 4, decay=0.8, threshold_ema_dead_code=0.5, kmeans_iters=5).train()
+    cents = torch.randn(4, 4) * 5
+    x = (cents[torch.randint(0, 4, (2, 50))] + 0.05 * torch.randn(2, 50, 4)).transpose(1, 2)
+    lens = torch.tensor([50, 40])
+    for _ in range(10):
+        deq, idx, commit = cb(x, lens)
+    assert bool(cb.initialized) and float(commit) < 0.05 and idx.shape == (2, 50) and int(idx[1, 40:].abs().sum()) == 0
+    assert float((cb.decode(cb.encode(x, lens), lens) - x)[0].pow(2).mean()) < 0.05
+    xg = x.clone().requires_grad_(True)
+    cb(xg, lens)[0].sum().backward()
+    assert torch.allclose(xg.grad[0], torch.ones_like(xg.grad[0]))                     # straight-through
+    rvq = ResidualVectorQuantizer(num_codebooks=3, codebook_size=16, codebook_dim=4, kmeans_iters=3).train()
+    feats = torch.randn(2, 4, 30)
+    fl = torch.tensor([30, 20])
+    for _ in range(5):
+        q, ids = rvq(feats, fl)
+    assert ids.shape == (3, 2, 30) and float(rvq.commit_loss) > 0
+    rvq.eval()
+    ids = rvq.encode(feats, fl)
+    errs = [float((sum(b.decode(ids[k], fl) for k, b in enumerate(rvq.books[: n + 1])) - feats)[0].pow(2).mean()) for n in range(3)]
+    assert errs[0] > errs[1] > errs[2] and torch.allclose(rvq.decode(ids, fl), rvq(feats, fl)[0].detach(), atol=1e-5)
+    g = GroupResidualVectorQuantizer(num_codebooks=4, num_groups=2, codebook_size=16, codebook_dim=8, kmeans_iters=2).train()
+    q, ids = g(torch.randn(2, 8, 12), torch.tensor([12, 9]))
+    assert q.shape == (2, 8, 12) and ids.shape == (4, 2, 12) and g.decode(ids, torch.tensor([12, 9])).shape == (2, 8, 12)
+
+
+def test_magpie_helpers_special_tokens_frames_and_char_aware_encoder():
+    from speech_b200.tts.magpie_helpers import (CharAwareSubwordEncoder, EOSDetectionMethod, SpecialAudioToken, add_special_tokens, build_vocabs,
+                                                clear_forbidden_logits, cosine_schedule, pad_audio_codes, remove_special_tokens)
+
+    N = 100
+    assert SpecialAudioToken.get_index(SpecialAudioToken.AUDIO_EOS, N) == 101 and len(SpecialAudioToken.get_forbidden_tokens(N)) == 7
+    lg = clear_forbidden_logits(torch.zeros(1, 2, N + 8), N)
+    assert torch.isinf(lg[0, 0, 100]) and lg[0, 0, 101] == 0 and torch.isinf(lg[0, 1, 104:]).all()
+    assert torch.isinf(clear_forbidden_logits(torch.zeros(1, 1, N + 8), N, forbid_audio_eos=True)[0, 0, 101])
+    codes = torch.arange(1, 11).view(1, 2, 5).repeat(2, 1, 1)
+    lens = torch.tensor([5, 3])
+    with_tok, l2 = add_special_tokens(codes, lens, bos_id=100, eos_id=101)
+    assert l2.tolist() == [7, 5] and with_tok[0, 0].tolist() == [100, 1, 2, 3, 4, 5, 101] and with_tok[1, 1, :5].tolist() == [100, 6, 7, 8, 101]
+    back, l3 = remove_special_tokens(with_tok, l2)
+    assert l3.tolist() == [5, 3] and torch.equal(back[0], codes[0]) and back[1, 0, :3].tolist() == [1, 2, 3] and int(back[1, :, 3:].sum()) == 0
+    assert pad_audio_codes(codes, 4).shape == (2, 2, 8) and pad_audio_codes(codes, 5) is codes
+    assert float(cosine_schedule(torch.tensor(0.0))) == 1.0 and float(cosine_schedule(torch.tensor(1.0))) < 1e-6
+    am, sm = torch.tensor([[5, 101], [5, 5]]), torch.tensor([[5, 5], [101, 5]])
+    assert EOSDetectionMethod.ARGMAX_ANY.detect(am, sm, 101).tolist() == [True, False]
+    assert EOSDetectionMethod.ARGMAX_OR_MULTINOMIAL_ANY.detect(am, sm, 101).tolist() == [True, True]
+    assert EOSDetectionMethod.ARGMAX_OR_MULTINOMIAL_ZERO_CB.detect(am, sm, 101).tolist() == [False, True]
+    assert EOSDetectionMethod.ARGMAX_ALL.detect(am, sm, 101).tolist() == [False, False]
+    vocab = {"<pad>": 0, "▁the": 1, "▁then": 2, "ing": 3, "<bos>": 4, "▁zebra": 5}
+    table, chars = build_vocabs(vocab, 0)
+    assert table[1] == [chars[" "], chars["t"], chars["h"], chars["e"]] and table[4] == [chars["<bos>"]] and 0 not in table
+    torch.manual_seed(0)
+    enc = CharAwareSubwordEncoder(16, vocab, 0, n_layers=1, n_heads=2).eval()
+    ids = torch.tensor([[1, 2, 5, 0], [3, 1, 0, 0]])
+    e = enc(ids, ids != 0)
+    assert e.shape == (2, 4, 16) and float(e[0, 3].abs().sum()) == 0.0 and torch.allclose(e[0, 0], e[1, 1])
+    cos = torch.nn.functional.cosine_similarity
+    assert float(cos(e[0, 0], e[0, 1], dim=0)) > float(cos(e[0, 0], e[0, 2], dim=0))       # "the" is closer to "then" than to "zebra"
