@@ -1,6 +1,9 @@
 """TTS collection on CPU: FSQ round trip, codec training step, transformer KV cache, MoE routing, alignment prior / loss,
 MagpieTTS training and autoregressive inference."""
 import math
+import os
+
+import numpy as np
 
 import pytest
 import torch
@@ -718,3 +721,51 @@ def test_magpie_helpers_special_tokens_frames_and_char_aware_encoder():
     assert e.shape == (2, 4, 16) and float(e[0, 3].abs().sum()) == 0.0 and torch.allclose(e[0, 0], e[1, 1])
     cos = torch.nn.functional.cosine_similarity
     assert float(cos(e[0, 0], e[0, 1], dim=0)) > float(cos(e[0, 0], e[0, 2], dim=0))       # "the" is closer to "then" than to "zebra"
+
+
+def test_tts_logging_callback_writes_audio_and_images(tmp_path):
+    from speech_b200.tts.callbacks import AudioCodecArtifactGenerator, LoggingCallback, VocoderArtifactGenerator, create_id, write_pgm
+    from speech_b200.tts.classic import HifiGanModel
+
+    torch.manual_seed(0)
+    codec = AudioCodecModel(OmegaConf.create(CODEC_CFG))
+    audio, lens = torch.randn(2, 2048) * 0.1, torch.tensor([2048, 1536])
+    loader = [{"audio": audio, "audio_lens": lens, "audio_filepaths": ["spk1/a.wav", "spk2/b.wav"]}]
+
+    class FakeTrainer:
+        current_epoch, global_step, is_global_zero = 0, 10, True
+
+    class FakeBoard:
+        def __init__(self):
+            self.audio, self.images = [], []
+
+        def add_audio(self, tag, data, global_step, sample_rate):
+            self.audio.append((tag, global_step, sample_rate))
+
+        def add_image(self, tag, data, global_step):
+            self.images.append((tag, data.shape))
+
+    board = FakeBoard()
+    cb = LoggingCallback([AudioCodecArtifactGenerator(log_audio=True, log_encoding=True, log_dequantized=True)], loader, epoch_frequency=2,
+                         output_dir=str(tmp_path / "logs"), loggers=[board])
+    tr = FakeTrainer()
+    cb.on_train_epoch_end(tr, codec)
+    d = tmp_path / "logs" / "epoch_0"
+    names = sorted(os.listdir(d))
+    assert names == ["deq_spk1_a.pgm", "deq_spk2_b.pgm", "enc_spk1_a.pgm", "enc_spk2_b.pgm", "gt_spk1_a.wav", "gt_spk2_b.wav", "pred_spk1_a.wav", "pred_spk2_b.wav"]
+    assert open(d / "enc_spk1_a.pgm", "rb").read(2) == b"P5" and len(board.audio) == 4 and board.images[0][1][0] == 1 and codec.training
+    tr.current_epoch = 1
+    cb.on_train_epoch_end(tr, codec)                                   # off-frequency epoch: nothing
+    assert not (tmp_path / "logs" / "epoch_1").exists()
+    tr.current_epoch = 2
+    cb.on_train_epoch_end(tr, codec)                                   # later logs skip the ground truth
+    assert sorted(os.listdir(tmp_path / "logs" / "epoch_2")) == ["deq_spk1_a.pgm", "deq_spk2_b.pgm", "enc_spk1_a.pgm", "enc_spk2_b.pgm", "pred_spk1_a.wav", "pred_spk2_b.wav"]
+    voc = HifiGanModel(OmegaConf.create({"sample_rate": 8000, "generator": {"input_dim": 20, "up_sample_rates": [4, 4, 4], "base_channels": 16, "resblock_kernel_sizes": [3]},
+                                         "discriminator": {"periods": [2], "stft_resolutions": [[256, 64, 256]]}, "mel": {"n_fft": 256, "hop": 64, "win": 256}}))
+    cb2 = LoggingCallback([VocoderArtifactGenerator()], [(audio, lens)], log_epochs=[5], output_dir=str(tmp_path / "voc"))
+    tr.current_epoch = 5
+    cb2.on_train_epoch_end(tr, voc)
+    assert sorted(os.listdir(tmp_path / "voc" / "epoch_5")) == ["gt_item0.wav", "gt_item1.wav", "voc_item0.wav", "voc_item1.wav"]
+    assert create_id("/data/x/y.wav") == "data_x_y"
+    write_pgm(str(tmp_path / "flat.pgm"), np.zeros((3, 4)))
+    assert len(open(tmp_path / "flat.pgm", "rb").read()) == len(b"P5\n4 3\n255\n") + 12
