@@ -1,6 +1,7 @@
 """Audio (enhancement) collection on CPU: STFT round trip, SDR metrics, MVDR beamformer, mask-based, predictive and the
 three generative models (training step + sampler)."""
 import math
+import os
 
 import pytest
 import torch
@@ -264,3 +265,85 @@ def test_audio_metrics_wrapper_stoi_and_reference_free_estimates():
     assert 1.0 <= float(mos.compute()) <= 5.0 and mos.state_dict() == {}
     with pytest.raises(ValueError):
         SquimObjectiveMetric(16000, "mos")
+
+
+def test_audio_utils_coherence_alignment_targets_covariance():
+    import numpy as np
+
+    from speech_b200.audio import utils as U
+
+    rng = np.random.default_rng(0)
+    pos = np.array([[0, 0, 0], [0.05, 0, 0], [0.2, 0, 0]], dtype=float)
+    g = U.theoretical_coherence(pos, 16000, "spherical", 256)
+    assert g.shape == (129, 3, 3) and np.allclose(g[:, 0, 0], 1) and np.allclose(g[0], 1) and abs(g[100, 0, 2]) < abs(g[100, 0, 1])
+    assert U.theoretical_coherence(pos, 16000, "cylindrical", 256)[10, 0, 1] == pytest.approx(0.92, abs=0.01)          # J0(2 pi 625 Hz 0.05 m / c)
+    noise = rng.standard_normal((64000, 3))
+    field = U.generate_approximate_noise_field(pos, noise, 16000, "spherical", 256)
+    S = torch.stft(torch.tensor(field.T), 256, 64, 256, torch.hann_window(256, dtype=torch.float64), return_complex=True).numpy().transpose(1, 2, 0)
+    est = U.estimated_coherence(S)
+    lo = slice(5, 40)
+    assert np.abs(np.real(est[lo, 0, 1]) - g[lo, 0, 1]).mean() < 0.1 and np.abs(np.real(est[lo, 0, 2]) - g[lo, 0, 2]).mean() < 0.12
+    with pytest.raises(RuntimeError):
+        U.transform_to_match_coherence(np.stack([noise[:, 0]] * 3, 1), g, fft_length=256)
+    x = rng.standard_normal(4000)
+    assert U.get_segment_start(x, x[1234:1800]) == 1234
+    h = np.array([1.0, 0.5, -0.25])
+    M = U.convmtx_numpy(x[:50], 3)
+    assert np.allclose(M @ h, np.convolve(x[:50], h)[:50]) and np.allclose(U.convmtx_numpy(x[:50], 3, delay=2)[2:] @ h, (M @ h)[:-2])
+    assert U.convmtx_mc_numpy(np.stack([x[:50], x[50:100]], 1), 3).shape == (50, 6)
+    filtered = np.convolve(x, [0.8, 0.3, 0.1])[:4000]
+    assert U.calculate_sdr_numpy(filtered, x) < 12 and U.calculate_sdr_numpy(filtered, x, convolution_invariant=True, convolution_filter_length=8) > 40
+    assert U.calculate_sdr_numpy(3 * x, x, scale_invariant=True) > 60 and U.calculate_sdr_numpy(3 * x, x) < 0
+    assert U.calculate_sdr_numpy(x, x, sdr_max=20) == pytest.approx(20.0, abs=0.01)
+    assert float(U.mag2db(10.0)) == pytest.approx(20.0) and float(U.db2mag(-20.0)) == pytest.approx(0.1) and float(U.pow2db(100.0)) == pytest.approx(20.0)
+    t = U.toeplitz(torch.tensor([1.0 + 0j, 2 + 1j, 3 - 1j]))
+    assert t[1, 0] == 2 + 1j and t[0, 1] == 2 - 1j and t[2, 0] == 3 - 1j and torch.allclose(t, t.conj().T)
+    X = torch.randn(2, 3, 5, 40, dtype=torch.complex64)
+    C = U.covariance_matrix(X)
+    assert C.shape == (2, 5, 3, 3) and torch.allclose(C, C.conj().transpose(-1, -2), atol=1e-5)
+    m = torch.zeros(2, 5, 40)
+    m[..., :10] = 1
+    assert torch.allclose(U.covariance_matrix(X, m), U.covariance_matrix(X[..., :10]), atol=1e-5)
+    assert torch.allclose(U.wrap_to_pi(torch.tensor([3.5, -3.5, 0.5])), torch.tensor([3.5 - 2 * math.pi, -3.5 + 2 * math.pi, 0.5]), atol=1e-6)
+
+
+def test_array_geometry_and_room_mix_generator(tmp_path):
+    import json
+
+    import numpy as np
+
+    from speech_b200.audio.simulation import ArrayGeometry, RIRMixGenerator, calculate_drr, convolve_rir, scaled_disturbance, simultaneously_active_rms, wrap_to_180
+    from speech_b200.audio.utils import rms
+
+    arr = ArrayGeometry([[-0.05, 0, 0], [0.05, 0, 0], [0, 0.05, 0]])
+    assert arr.num_mics == 3 and arr.radius == pytest.approx(np.hypot(0.05, 1 / 60), abs=1e-6)
+    moved = arr.translate([2, 3, 1.5]).rotate(yaw=90)
+    assert np.allclose(moved.centroid, [2, 3, 1.5]) and np.allclose(moved.positions[1] - moved.positions[0], [0, 0.1, 0], atol=1e-9)
+    p = moved.new_point(1.0, 0.0, 0.0)                                  # "straight ahead" of an array turned by 90 degrees is +y
+    assert np.allclose(p, [2, 4, 1.5], atol=1e-9)
+    r, az, el = moved.spherical_relative_to_array([2, 3, 2.5])
+    assert (r, el) == (pytest.approx(1.0), pytest.approx(90.0)) and wrap_to_180(270) == -90.0
+    rir = np.zeros((1, 400))
+    rir[0, 20], rir[0, 200] = 1.0, 0.1
+    assert calculate_drr(rir, 16000)[0] == pytest.approx(20.0, abs=0.1)
+    sig = np.random.default_rng(0).standard_normal(2000)
+    assert np.allclose(convolve_rir(sig, rir)[:, 0], np.convolve(sig, rir[0])[:2000], atol=1e-9)
+    d = scaled_disturbance(sig, 5 * np.random.default_rng(1).standard_normal(2000), 10.0)
+    assert 20 * np.log10(rms(sig) / rms(d)) == pytest.approx(10.0, abs=1e-6)
+    gated = sig.copy()
+    gated[1000:] = 0
+    a, b = simultaneously_active_rms(gated, sig, 1000, window_len_ms=100)
+    assert a == pytest.approx(rms(sig[:1000]), rel=1e-6) and b == pytest.approx(rms(sig[:1000]), rel=1e-6)
+    rng = np.random.default_rng(2)
+    gen = RIRMixGenerator(arr, room_dim_range=((4, 5), (4, 5), (2.5, 3)), rt60_range=(0.2, 0.3), num_interferers=(1, 1), rsnr_range=(10, 10), rsir_range=(5, 5),
+                          sample_rate=8000, max_order=3, seed=3)
+    speech = lambda: (rng.standard_normal(8000) * (np.sin(np.arange(8000) / 400) > 0)).astype(np.float64)  # noqa: E731
+    out = gen.mix(speech(), [speech()], rng.standard_normal(8000))
+    assert out["mix"].shape == (8000, 3) and set(out) >= {"mix", "target_reverberant", "target_anechoic", "interference", "noise", "metadata"}
+    assert np.allclose(out["mix"], out["target_reverberant"] + out["interference"] + out["noise"], atol=1e-9)
+    assert 20 * np.log10(rms(out["target_reverberant"][:, 0]) / rms(out["noise"][:, 0])) == pytest.approx(10.0, abs=1e-6)
+    md = out["metadata"]
+    assert 0.5 <= md["target_range"] <= 2.5 and md["num_interferers"] == 1 and rms(out["target_anechoic"]) < rms(out["target_reverberant"])
+    man = gen.generate(str(tmp_path / "sim"), [speech(), speech()], [speech()], [rng.standard_normal(8000)])
+    rows = [json.loads(l) for l in open(man)]
+    assert len(rows) == 2 and os.path.exists(rows[1]["mix_filepath"]) and rows[0]["duration"] == 1.0
