@@ -21,6 +21,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 import torch.nn as nn
+import torch.nn.functional as F
 
 from ..core.config import DictConfig, cfg_get
 from ..core.instantiate import from_config_dict
@@ -364,3 +365,85 @@ class SchroedingerBridgeAudioToAudioModel(_GenerativeBase):
             if process == "sde" and i < steps - 1:
                 x = x + torch.sqrt((s2n * (1 - w)).clamp(min=0)) * _cnoise(x)
         return self._decode(x, lens, T) * n, input_length
+
+
+# ---------------------------------------------------------------------------------------------- time-domain denoiser
+class _Seasr(nn.Module):
+    """Learned analysis filterbank (strided convolution) -> three convolution stages, each summarised by a GRU -> a stack of
+    residual GRUs over the concatenated summaries -> a sigmoid mask on the analysis coefficients -> learned synthesis
+    (transposed convolution) with tanh."""
+
+    def __init__(self, hidden_nodes: int = 128, kernel_size: int = 320, f1: int = 1024, f2: int = 512, stride: int = 160, dropout: float = 0.0):
+        super().__init__()
+        f3 = 2 * hidden_nodes
+        self.kernel, self.stride = kernel_size, stride
+        self.analysis = nn.Conv1d(1, f1, kernel_size, stride=stride, bias=False)
+        self.bn0 = nn.BatchNorm1d(f1, eps=1e-3)
+        self.convs = nn.ModuleList([nn.Conv1d(f1, f2, 3, padding=1), nn.Conv1d(f2, f2, 3, padding=1), nn.Conv1d(f2, f2, 3, padding=1)])
+        self.bns = nn.ModuleList([nn.BatchNorm1d(f2, eps=1e-3) for _ in range(3)])
+        self.feat_gru = nn.ModuleList([nn.GRU(f1, f3, batch_first=True), nn.GRU(f2, f3, batch_first=True), nn.GRU(f2, f3, batch_first=True)])
+        self.den = nn.ModuleList([nn.GRU(3 * f3 + f2, f1, batch_first=True), nn.GRU(f1, f1, batch_first=True), nn.GRU(f1, f1, batch_first=True),
+                                  nn.GRU(f1, f1, batch_first=True)])
+        self.drop = nn.Dropout(dropout)
+        self.mask = nn.Linear(f1, f1)
+        self.synthesis = nn.ConvTranspose1d(f1, 1, kernel_size, stride=stride)
+
+    def forward(self, x0: torch.Tensor) -> torch.Tensor:
+        """[B, 1, T] -> [B, 1, T]."""
+        T = x0.shape[-1]
+        pad = (-(T - self.kernel)) % self.stride if T >= self.kernel else self.kernel - T
+        x0 = F.pad(x0, (0, pad))
+        a = F.relu(self.analysis(x0))
+        c0 = self.bn0(a)
+        c1 = self.bns[0](F.leaky_relu(self.convs[0](c0)))
+        c2 = self.bns[1](F.leaky_relu(self.convs[1](c1)))
+        c3 = self.bns[2](F.leaky_relu(self.convs[2](c2)))
+        g0, _ = self.feat_gru[0](c0.transpose(1, 2))
+        g1, _ = self.feat_gru[1](c1.transpose(1, 2))
+        g2, _ = self.feat_gru[2](c2.transpose(1, 2))
+        h, _ = self.den[0](torch.cat([g0, g1, g2, c3.transpose(1, 2)], dim=2))
+        h = self.drop(h) + c0.transpose(1, 2)
+        h1, _ = self.den[1](h)
+        h1 = self.drop(h1) + h
+        h2, _ = self.den[2](h1)
+        h, _ = self.den[3](h1 + self.drop(h2))
+        m = torch.sigmoid(self.mask(h)).transpose(1, 2)
+        return torch.tanh(self.synthesis(a * m))[..., :T]
+
+
+class BNR2(AudioToAudioModel):
+    """Background-noise removal in the time domain at 16 kHz with a combined loss (SI-SDR + spectral + recogniser features).
+    Reference: ``audio/models/maxine/bnr.py`` (``BNR2``)."""
+
+    def __init__(self, cfg: DictConfig, trainer=None, feature_extractor=None):
+        super().__init__(cfg=cfg, trainer=trainer)
+        from .losses import CombinedLoss
+
+        cfg = self._cfg
+        if int(self.sample_rate) != 16000:
+            raise ValueError("this model is defined for 16 kHz audio")
+        self.seasr = _Seasr(**{k: v for k, v in dict(cfg_get(cfg, "seasr", {}) or {}).items() if k != "_target_"})
+        self.loss = CombinedLoss(sample_rate=self.sample_rate, feature_extractor=feature_extractor,
+                                 **{k: v for k, v in dict(cfg_get(cfg, "loss", {}) or {}).items() if k != "_target_"})
+        self._ready = True
+        self._finish_init()
+
+    def forward(self, input_signal, input_length=None):
+        x = input_signal if input_signal.dim() == 3 else input_signal.unsqueeze(1)
+        if x.shape[1] != 1:
+            raise ValueError("single-channel input expected")
+        y = self.seasr(x)
+        if input_length is not None:
+            y = y * (torch.arange(y.shape[-1], device=y.device)[None, None, :] < input_length[:, None, None])
+        return y, input_length
+
+    def training_step(self, batch, batch_idx):
+        x, xl, y, yl = batch[:4]
+        est, _ = self.forward(x, xl)
+        n = min(est.shape[-1], y.shape[-1])
+        loss = self.loss(est[..., :n], y[..., :n] if y.dim() == 3 else y[:, None, :n], xl.clamp(max=n))
+        self.log_dict({"train_loss": loss.detach()})
+        return {"loss": loss}
+
+    def _eval_loss(self, est, tgt, lens):
+        return self.loss(est, tgt, lens)

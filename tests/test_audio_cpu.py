@@ -347,3 +347,43 @@ def test_array_geometry_and_room_mix_generator(tmp_path):
     man = gen.generate(str(tmp_path / "sim"), [speech(), speech()], [speech()], [rng.standard_normal(8000)])
     rows = [json.loads(l) for l in open(man)]
     assert len(rows) == 2 and os.path.exists(rows[1]["mix_filepath"]) and rows[0]["duration"] == 1.0
+
+
+def test_audio_losses_and_time_domain_denoiser():
+    from speech_b200.audio.losses import CombinedLoss, MAELoss, MSELoss, temporal_mean
+    from speech_b200.audio.models import BNR2
+
+    torch.manual_seed(0)
+    x = torch.tensor([[[1.0, 2.0, 3.0, 100.0]], [[2.0, 2.0, 2.0, 2.0]]])
+    assert temporal_mean(x, torch.tensor([3, 4])).flatten().tolist() == pytest.approx([2.0, 2.0])
+    est, tgt = torch.zeros(2, 2, 4), torch.ones(2, 2, 4)
+    tgt[:, 1] = 3.0
+    assert float(MSELoss()(est, tgt)) == pytest.approx(5.0) and float(MAELoss()(est, tgt)) == pytest.approx(2.0)
+    assert float(MSELoss(weight=[0.75, 0.25])(est, tgt)) == pytest.approx(3.0)
+    e2 = est.clone()
+    e2[0, :, 2:] = 50.0
+    assert float(MAELoss()(e2, tgt, input_length=torch.tensor([2, 4]))) == pytest.approx(2.0)         # the corrupted tail lies beyond the length
+    spec_e, spec_t = torch.zeros(1, 1, 3, 5, dtype=torch.complex64), torch.full((1, 1, 3, 5), 1 + 1j)
+    assert float(MSELoss(ndim=4)(spec_e, spec_t)) == pytest.approx(2.0)
+    with pytest.raises(ValueError):
+        MSELoss(weight=[0.5, 0.6])
+    feats = torch.nn.Conv1d(1, 4, 64, stride=32)
+    for p_ in feats.parameters():
+        p_.requires_grad_(False)
+    cl = CombinedLoss(16000, fft_length=256, hop_length=64, num_mels=20, feature_extractor=lambda a, l: feats(a.unsqueeze(1)))
+    clean = torch.sin(torch.arange(4000) * 0.05)[None].repeat(2, 1)
+    noisy = (clean + 0.3 * torch.randn(2, 4000)).requires_grad_(True)
+    l_noisy, l_clean = cl(noisy, clean), cl(clean + 1e-4 * torch.randn(2, 4000), clean)
+    assert float(l_clean) < float(l_noisy)
+    l_noisy.backward()
+    assert noisy.grad.abs().sum() > 0
+    m = BNR2(OmegaConf.create({"sample_rate": 16000, "seasr": {"hidden_nodes": 8, "kernel_size": 64, "f1": 32, "f2": 16, "stride": 32},
+                               "loss": {"fft_length": 256, "hop_length": 64, "num_mels": 20, "asr_loss_weight": 0.0}}))
+    lens = torch.tensor([4000, 3000])
+    out, _ = m(noisy.detach().unsqueeze(1), lens)
+    assert out.shape == (2, 1, 4000) and float(out[1, :, 3000:].abs().sum()) == 0.0 and float(out.abs().max()) <= 1.0
+    loss = m.training_step((noisy.detach().unsqueeze(1), lens, clean.unsqueeze(1), lens), 0)["loss"]
+    loss.backward()
+    assert torch.isfinite(loss) and m.seasr.analysis.weight.grad.abs().sum() > 0
+    with pytest.raises(ValueError):
+        BNR2(OmegaConf.create({"sample_rate": 8000}))
