@@ -26,6 +26,17 @@ from .perception import AudioPerceptionModule
 from .salm import SALM
 
 
+class _IdTokenizer:
+    """Stand-in when no tokenizer is attached (synthetic data): every character is its code point modulo a small range."""
+    pad_id, bos_id, eos_id = 0, 1, 2
+
+    def text_to_ids(self, text):
+        return [3 + (ord(c) % 29) for c in text if not c.isspace()]
+
+    def ids_to_text(self, ids):
+        return " ".join(str(i) for i in ids)
+
+
 class DuplexSTTModel(ModelPT):
     def __init__(self, cfg: DictConfig, trainer=None, llm: Optional[CausalLM] = None, tokenizer=None, perception: Optional[nn.Module] = None):
         super().__init__(cfg=cfg, trainer=trainer)
@@ -54,6 +65,13 @@ class DuplexSTTModel(ModelPT):
             self.asr_loss_weight = float(cfg_get(cfg, "asr_loss_weight", 1.0))
         else:
             self.predict_user_text = False
+        self._duplex_ready = True
+        if type(self) is DuplexSTTModel and not self._is_model_being_restored and self._train_dl is None:
+            self._setup_dataloaders_from_cfg()
+
+    def _setup_dataloaders_from_cfg(self):
+        if getattr(self, "_duplex_ready", False):                    # the base constructor calls this before the layers exist
+            super()._setup_dataloaders_from_cfg()
 
     @property
     def streaming_inference(self):
@@ -62,11 +80,25 @@ class DuplexSTTModel(ModelPT):
 
         return DuplexSTTStreamingInference(self)
 
+    def _loader(self, c):
+        from .duplex_data import build_duplex_dataloader
+
+        rank = self.global_rank if self._trainer is not None else 0
+        ws = self.world_size if self._trainer is not None else 1
+        return build_duplex_dataloader(c, self.tokenizer if self.tokenizer is not None else _IdTokenizer(), float(self.perception.token_equivalent_duration),
+                                       self.text_bos_id, self.text_eos_id, self.text_pad_id, num_codebooks=int(getattr(self, "_num_codebooks", 0) or 0),
+                                       codebook_size=int(getattr(self, "_codebook_size", 16) or 16), rank=rank, world_size=ws)
+
     def setup_training_data(self, c):
-        self._train_dl = None
+        self._train_dl = self._loader(c)
 
     def setup_validation_data(self, c):
-        self._validation_dl = None
+        self._validation_dl = self._loader(c)
+
+    def validation_step(self, batch, batch_idx, dataloader_idx=0):
+        with torch.no_grad():
+            l = self._losses(batch)
+        return {"val_loss": l["loss"].detach()}
 
     # ------------------------------------------------------------------ channels
     def _frame_inputs(self, source_emb: torch.Tensor, prev_text: torch.Tensor, prev_codes: Optional[torch.Tensor] = None,
@@ -179,6 +211,8 @@ class DuplexS2SModel(DuplexSTTModel):
         self.embed_audio_tokens = nn.ModuleList([nn.Embedding(self.speech_vocab_size, H) for _ in range(self._num_codebooks)])
         self.audio_head = nn.Linear(H, self.speech_vocab_size * self._num_codebooks)
         self.audio_loss_weight = float(cfg_get(cfg, "audio_loss_weight", 1.0))
+        if type(self) is DuplexS2SModel and not self._is_model_being_restored and self._train_dl is None:
+            self._setup_dataloaders_from_cfg()
 
     speech_vocab_size = property(lambda self: self._codebook_size + 3)
     speech_bos_id = property(lambda self: self._codebook_size)

@@ -590,3 +590,80 @@ def test_rvq_vae_codec_round_trip_streaming_decode_and_training():
     assert float(ProbabilisticRVQ(8, 4, 2).log_std) == 0.0
     audio, alen = m.decode(tokens=torch.stack(ids, dim=1), tokens_len=torch.tensor([20, 10]))
     assert torch.allclose(audio, full[:, 0]) and alen.tolist() == [320, 160] and m.rvq_codebooks.shape == (3, 32, 16)
+
+
+def test_duplex_token_channels_dataset_augmenter_and_chunked_perception():
+    from speech_b200.speechlm.duplex_data import (AudioAugmenter, DuplexConversationDataset, build_token_channel, configure_optimizers_exclude_norm_from_wd,
+                                                  delay_eos, encode_audio_with_optional_chunking, synthetic_duplex_conversations, text_with_timestamps_to_ids,
+                                                  tokens_to_str)
+
+    class Tok:
+        def text_to_ids(self, t):
+            return [10 + "abcdefgh".index(c) for c in t.replace(" ", "")]
+
+        def ids_to_text(self, ids):
+            return "".join("abcdefgh"[i - 10] for i in ids)
+
+    tok = Tok()
+    turns = [{"role": "user", "start": 0.0, "end": 0.8, "text": "ab"}, {"role": "agent", "start": 1.0, "end": 1.6, "text": "cde"},
+             {"role": "agent", "start": 2.0, "end": 2.3, "text": "fgh"}]
+    ch = build_token_channel(turns, {"agent"}, tok, 0.1, 30, bos_id=1, eos_id=2, pad_id=0)
+    assert ch[10:17].tolist() == [1, 12, 13, 14, 0, 0, 2] and ch[20:24].tolist() == [1, 15, 16, 2]          # the last turn is cut to fit before its end
+    usr = build_token_channel(turns, {"user"}, tok, 0.1, 30, 1, 2, 0)
+    assert usr[:9].tolist() == [1, 10, 11, 0, 0, 0, 0, 0, 2] and int(usr[9:].sum()) == 0
+    assert text_with_timestamps_to_ids("<|0.0|> a <|0.5|> bc", tok, 0.1) == [(0, [10]), (5, [11, 12])]
+    timed = build_token_channel([{"role": "agent", "start": 1.0, "end": 2.0, "text": "<|0.0|> a <|0.5|> bc"}], {"agent"}, tok, 0.1, 30, 1, 2, 0)
+    assert timed[10:21].tolist() == [1, 10, 0, 0, 0, 0, 11, 12, 0, 0, 2]
+    d = delay_eos(torch.tensor([[1, 5, 2, 0, 0, 0, 1, 6, 2, 0]]), 2, 0, shift=2)
+    assert d.tolist() == [[1, 5, 0, 0, 2, 0, 1, 6, 0, 2]]
+    assert tokens_to_str(torch.tensor([[1, 10, 11, 0, 2, 0]]), torch.tensor([6]), tok, 0, True, 1, 2) == ["<bos> ab <eos>"]
+    assert tokens_to_str(torch.tensor([[1, 10, 11, 0, 2, 0]]), torch.tensor([6]), tok, 0, False, 1, 2) == ["ab"]
+    ds = DuplexConversationDataset(synthetic_duplex_conversations(3, num_codebooks=2, duration=1.0), tok, frame_sec=0.08, eos_delay=1)
+    b = ds.collate_fn([ds[0], ds[1]])
+    assert b["source_audio"].shape == (2, 16000) and b["target_tokens"].shape == (2, 13) and b["target_codes"].shape == (2, 13, 2) and b["token_lens"].tolist() == [13, 13]
+    assert int((b["target_tokens"] == 1).sum()) == 2 and int((b["source_tokens"] == 1).sum()) == 2
+    x = torch.sin(torch.arange(16000) * 0.3) * 0.5
+    aug = AudioAugmenter(noise_prob=1.0, snr_range=(10, 10), gain_prob=0.0, lowpass_prob=0.0)
+    y = aug(x, 16000)
+    assert 10 * torch.log10(x.pow(2).mean() / (y - x).pow(2).mean()) == pytest.approx(10.0, abs=0.3)
+    lp = AudioAugmenter(lowpass_prob=1.0, lowpass_hz_range=(2000, 2000))(x + torch.sin(torch.arange(16000) * 2.5) * 0.5, 16000)
+    spec = torch.fft.rfft(lp).abs()
+    assert spec[int(0.3 / (2 * math.pi) * 16000)] > 50 * spec[int(2.5 / (2 * math.pi) * 16000)]               # 764 Hz passes, 6.4 kHz is removed
+
+    class Perc(torch.nn.Module):
+        calls = []
+
+        def forward(self, input_signal, input_signal_length):
+            Perc.calls.append(tuple(input_signal.shape))
+            e = input_signal.unfold(1, 160, 160).mean(-1, keepdim=True).repeat(1, 1, 4)
+            return e, input_signal_length // 160
+
+    audio, lens = torch.randn(2, 16000), torch.tensor([16000, 9000])
+    whole, wl = encode_audio_with_optional_chunking(Perc(), audio, lens)
+    parts, pl = encode_audio_with_optional_chunking(Perc(), audio, lens, chunk_size_seconds=0.25, min_chunk_seconds=0.1)
+    assert Perc.calls[-1] == (6, 5000) and pl.tolist() == wl.tolist() == [100, 56] and torch.allclose(parts[1, :56], whole[1, :56], atol=1e-6)
+    net = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.LayerNorm(4))
+    opt = configure_optimizers_exclude_norm_from_wd(net, lr=1e-3, weight_decay=0.1)
+    assert [len(g["params"]) for g in opt.param_groups] == [1, 3] and [g["weight_decay"] for g in opt.param_groups] == [0.1, 0.0]
+
+
+def test_duplex_models_train_from_their_config_data_blocks():
+    from speech_b200.core.trainer import Trainer
+    from speech_b200.speechlm.duplex import DuplexS2SModel, DuplexSTTModel
+
+    torch.manual_seed(0)
+    base = {"llm": {"vocab_size": 64, "hidden_size": 32, "intermediate_size": 64, "num_hidden_layers": 1, "num_attention_heads": 4, "num_key_value_heads": 2,
+                    "head_dim": 8}, "predict_user_text": True,
+            "perception": {"preprocessor": {"_target_": "speech_b200.modules.preprocessor.AudioToMelSpectrogramPreprocessor", "features": 16, "dither": 0.0},
+                           "encoder": {"_target_": "speech_b200.modules.conformer_encoder.ConformerEncoder", "feat_in": 16, "n_layers": 1, "d_model": 32,
+                                       "subsampling": "dw_striding", "subsampling_factor": 8, "subsampling_conv_channels": 16, "n_heads": 4},
+                           "modality_adapter": {"_target_": "speech_b200.speechlm.perception.IdentityConnector", "d_model": 32}},
+            "train_ds": {"synthetic": {"num_samples": 4, "duration": 1.0}, "batch_size": 2}, "optim": {"name": "adamw", "lr": 1e-3}}
+    for cls, extra in ((DuplexSTTModel, {}), (DuplexS2SModel, {"num_codebooks": 2, "codebook_size": 16})):
+        m = cls(OmegaConf.create(dict(base, **extra)))
+        assert m._train_dl is not None
+        batch = next(iter(m._train_dl))
+        assert ("target_codes" in batch) == (cls is DuplexS2SModel)
+        tr = Trainer(max_steps=2, accelerator="cpu", devices=1, enable_checkpointing=False, logger=False)
+        tr.fit(m)
+        assert tr.global_step == 2
