@@ -66,6 +66,11 @@ class DuplexSTTModel(ModelPT):
         else:
             self.predict_user_text = False
         self._duplex_ready = True
+        if not self._is_model_being_restored and any(cfg_get(cfg, k, None) for k in ("pretrained_s2s_model", "pretrained_perception_from_s2s", "init_from_checkpoint")):
+            from .pretrained import maybe_load_pretrained_models
+
+            if type(self) is DuplexSTTModel:                          # subclasses call it after they have added their own layers
+                maybe_load_pretrained_models(self)
         if type(self) is DuplexSTTModel and not self._is_model_being_restored and self._train_dl is None:
             self._setup_dataloaders_from_cfg()
 
@@ -211,6 +216,10 @@ class DuplexS2SModel(DuplexSTTModel):
         self.embed_audio_tokens = nn.ModuleList([nn.Embedding(self.speech_vocab_size, H) for _ in range(self._num_codebooks)])
         self.audio_head = nn.Linear(H, self.speech_vocab_size * self._num_codebooks)
         self.audio_loss_weight = float(cfg_get(cfg, "audio_loss_weight", 1.0))
+        if not self._is_model_being_restored and any(cfg_get(cfg, k, None) for k in ("pretrained_s2s_model", "pretrained_perception_from_s2s", "init_from_checkpoint")):
+            from .pretrained import maybe_load_pretrained_models
+
+            maybe_load_pretrained_models(self)
         if type(self) is DuplexS2SModel and not self._is_model_being_restored and self._train_dl is None:
             self._setup_dataloaders_from_cfg()
 

@@ -147,6 +147,11 @@ class SALM(ModelPT):
                     p.requires_grad_(False)
         freeze_and_subset(self.named_parameters(), cfg_get(cfg, "freeze_params", None), cfg_get(cfg, "prevent_freeze_params", None))
         self._prompt = None
+        if type(self).__name__ == "SALM" and not self._is_model_being_restored and any(
+                cfg_get(cfg, k, None) for k in ("pretrained_s2s_model", "pretrained_perception_from_s2s", "init_from_checkpoint")):
+            from .pretrained import maybe_load_pretrained_models
+
+            maybe_load_pretrained_models(self)
         if not self._is_model_being_restored and self._train_dl is None:
             self._setup_dataloaders_from_cfg()
 

@@ -1,6 +1,7 @@
 """Speech-LLM stack on CPU: native decoder-only LM (KV-cache decoding equals full recomputation, HF-directory round trip),
 placeholder splicing, LoRA, SALM training + generation, failure detection on the host."""
 import math
+import os
 
 import pytest
 import torch
@@ -667,3 +668,52 @@ def test_duplex_models_train_from_their_config_data_blocks():
         tr = Trainer(max_steps=2, accelerator="cpu", devices=1, enable_checkpointing=False, logger=False)
         tr.fit(m)
         assert tr.global_step == 2
+
+
+def test_speechlm_initialisation_from_checkpoints_of_several_kinds(tmp_path):
+    from safetensors.torch import save_file
+
+    from speech_b200.speechlm.pretrained import (init_from_training_checkpoint, init_model_from_checkpoint, init_perception_from_checkpoint, load_checkpoint,
+                                                 set_model_dict_for_partial_init)
+    from speech_b200.utils.dcp_io import DCPCheckpointIO
+
+    class Perc(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.encoder = torch.nn.Linear(4, 4)
+            self.proj = torch.nn.Linear(4, 6)
+
+    class LM(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.perception, self.llm = Perc(), torch.nn.Linear(6, 6)
+
+    torch.manual_seed(0)
+    a, b = LM(), LM()
+    sd = {k: v.clone() for k, v in a.state_dict().items()}
+    save_file(sd, str(tmp_path / "m.safetensors"))
+    torch.save({"state_dict": sd, "global_step": 3}, tmp_path / "m.ckpt")
+    os.makedirs(tmp_path / "hf")
+    keys = sorted(sd)
+    save_file({k: sd[k] for k in keys[:3]}, str(tmp_path / "hf" / "model-00001-of-00002.safetensors"))
+    save_file({k: sd[k] for k in keys[3:]}, str(tmp_path / "hf" / "model-00002-of-00002.safetensors"))
+    DCPCheckpointIO().save_checkpoint(sd, str(tmp_path / "dcp"))
+    for p in ("m.safetensors", "m.ckpt", "hf", "dcp"):
+        got = load_checkpoint(str(tmp_path / p))
+        assert set(got) == set(sd) and torch.equal(got["llm.weight"], sd["llm.weight"]), p
+    n_ok, n_skip = init_model_from_checkpoint(b, str(tmp_path / "m.safetensors"))
+    assert (n_ok, n_skip) == (6, 0) and torch.equal(b.llm.weight, a.llm.weight)
+    # an ASR-style checkpoint: encoder.* goes under perception., the rest is ignored
+    c = LM()
+    asr_sd = {"encoder.weight": torch.full((4, 4), 2.0), "encoder.bias": torch.zeros(4), "decoder.weight": torch.zeros(9, 4)}
+    torch.save(asr_sd, tmp_path / "asr.pt")
+    assert init_perception_from_checkpoint(c, str(tmp_path / "asr.pt")) == 2 and float(c.perception.encoder.weight[0, 0]) == 2.0
+    assert init_perception_from_checkpoint(c, str(tmp_path / "m.ckpt")) == 4 and torch.equal(c.perception.proj.weight, a.perception.proj.weight)
+    torch.save({"x": torch.zeros(1)}, tmp_path / "nothing.pt")
+    with pytest.raises(RuntimeError):
+        init_perception_from_checkpoint(c, str(tmp_path / "nothing.pt"))
+    _, taken, skipped = set_model_dict_for_partial_init({"model.llm.weight": torch.zeros(6, 6), "model.llm.bias": torch.zeros(5)}, b.state_dict(), strip_prefix="model.")
+    assert taken == ["llm.weight"] and "shape" in skipped[0]
+    assert init_from_training_checkpoint(LM(), str(tmp_path / "dcp")) == 6
+    with pytest.raises(RuntimeError):
+        init_from_training_checkpoint(torch.nn.Linear(2, 2), str(tmp_path / "m.ckpt"))
