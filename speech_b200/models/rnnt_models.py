@@ -43,7 +43,6 @@ class EncDecRNNTModel(ASRModel, ASRModuleMixin, TranscriptionMixin):
         loss_name, loss_kwargs = self.extract_rnnt_loss_cfg(cfg.get("loss", None))
         num_classes = cfg.joint.num_classes
         if loss_name == "tdt":
-            num_classes = num_classes - cfg.joint.get("num_extra_outputs", 0) if False else num_classes
             with open_dict(cfg):
                 cfg.joint.num_extra_outputs = len(loss_kwargs["durations"])
         elif loss_name == "multiblank_rnnt":
