@@ -383,3 +383,39 @@ def test_greedy_variants_agree_and_strategies_dispatch():
     per_t = GreedyRNNTInfer(mt.decoder, mt.joint, mt.decoding.blank_id, durations=mt.decoding.durations, max_symbols_per_step=10)(enc.transpose(1, 2), lens)[0]
     for b in range(3):
         assert per_t[b].y_sequence.tolist() == ref_t[b].y_sequence.tolist() and per_t[b].timestamp.tolist() == ref_t[b].timestamp.tolist()
+
+
+def test_host_context_graph_word_spotting_graph_and_merge():
+    import numpy as np
+
+    from speech_b200.decoding.context_biasing import WordSpotterHyp
+    from speech_b200.decoding.context_graph import CTCContextGraph, ContextGraph, merge_alignment_with_ws_hyps
+
+    g = ContextGraph(context_score=2.0).build([[1, 2, 3], [2, 3, 4, 5], [7]], phrases=["abc", "bcde", "g"])
+    assert g.num_nodes == 1 + 3 + 4 + 1
+    # a completed phrase keeps its boost; leaving a partly matched phrase gives the boost back
+    assert g.score_sequence([9, 1, 2, 3, 9]) == (6.0, ["abc"])
+    assert g.score_sequence([1, 2, 9]) == (0.0, [])
+    assert g.score_sequence([1, 2]) == (0.0, [])                               # unfinished at the end of the utterance
+    # failure links: after "a b c" the path continues into "b c d e" without starting over
+    total, found = g.score_sequence([1, 2, 3, 4, 5])
+    assert found == ["abc", "bcde"] and total == pytest.approx(6.0 + 8.0 - 6.0 + 6.0 - 6.0 + 0.0, abs=8.0) and total >= 8.0
+    s, st, m = g.forward_one_step(g.root, 7)
+    assert s == 2.0 and m is not None and m.phrase == "g" and g.finalize(st)[0] == 0.0
+    deep = ContextGraph(1.0, depth_scaling=2.0).build([[1, 2, 3]])
+    assert deep.score_sequence([1, 2, 3])[0] == 1 + 2 + 4
+    weighted = ContextGraph(1.0).build([[1, 2], [3]], scores=[5.0, 0.0])
+    assert weighted.score_sequence([1, 2, 3])[0] == 10.0 + 1.0
+    # CTC-topology search over posteriors: "b c" spoken at frames 3-7
+    V, blank = 6, 5
+    lp = np.full((12, V), np.log(0.02))
+    lp[:, blank] = np.log(0.9)
+    for t, tok in [(3, 2), (4, 2), (6, 3), (7, 3)]:
+        lp[t, blank], lp[t, tok] = np.log(0.02), np.log(0.9)
+    hits = CTCContextGraph({"bc": [2, 3], "zz": [0, 0]}, blank).search(lp, threshold=-1.0)
+    assert len(hits) == 1 and hits[0][0] == "bc" and 3 <= hits[0][2] <= 4 and 6 <= hits[0][3] <= 7 and hits[0][1] > -0.5
+    toks = {1: "▁the", 2: "▁cat", 3: "s", 4: "▁sat"}
+    ali = [5, 1, 1, 5, 2, 2, 3, 5, 5, 4, 4, 5]
+    text, words = merge_alignment_with_ws_hyps(ali, [WordSpotterHyp("kats", -0.2, 4, 6)], lambda i: toks[i], blank=5)
+    assert text == "the kats sat" and words[1] == ("kats", 4, 6)
+    assert merge_alignment_with_ws_hyps(ali, [], lambda i: toks[i], blank=5)[0] == "the cats sat"
