@@ -550,3 +550,46 @@ def test_diarization_and_multispeaker_metrics():
     assert len(pairs) == 3 and len(set(lab.tolist())) == 3
     score, by = sot_speaker_alignment("hello how are you <sc> fine thanks <sc> good to hear", ["hello how are you good to hear", "fine thanks"])
     assert score == 0.0 and by == ["hello how are you good to hear", "fine thanks"]
+
+
+def test_asr_evaluation_helpers(tmp_path):
+    import json
+
+    from speech_b200.decoding.rnnt_decoding import Hypothesis
+    from speech_b200.utils import asr_eval_utils as E
+
+    assert E.clean_label("Hello, [noise] World! It's 42.") == "hello world it's forty two" and E.convert_num_to_words("1205 7") == "one thousand two hundred five seven"
+    assert E.strip_spaces_before_punctuations("hi , there !") == "hi, there!" and E.remove_punctuations("a, b. c?") == "a b c"
+    man = tmp_path / "p.json"
+    man.write_text("\n".join(json.dumps(r) for r in [{"text": "the cat sat", "pred_text": "the cat sat down"}, {"text": "Good Day.", "pred_text": "good day"}]))
+    out, wer, ntok, n, rates = E.cal_write_wer(str(man), ignore_capitalization=True, ignore_punctuation=True)
+    assert wer == pytest.approx(1 / 5) and (ntok, n) == (5, 2) and rates["ins"] == pytest.approx(1 / 5) and json.loads(open(out).readline())["wer"] == pytest.approx(1 / 3)
+    assert E.cal_write_wer(str(man))[1] == pytest.approx(3 / 5)                                       # case and the full stop count
+    per = E.PunctuationErrorRate([".", ",", "?"])
+    per.update(["Hello, world. how are you", "yes."], ["Hello world. How are you?", "Yes, sure."])
+    r = per.compute()
+    assert r["."]["correct_rate"] == pytest.approx(0.5) and r[","]["sub_rate"] == pytest.approx(0.5) and r[","]["ins_rate"] == pytest.approx(0.5) and r["?"]["del_rate"] == 1.0
+    assert 0 < r["punct_er"] < 1
+    # latency: an oracle that emits token i right when 1/gamma more source arrived lags by its constant offset
+    assert E.compute_laal([2.0, 3.0, 4.0, 5.0], source_length=4.0, target_length=4) == pytest.approx(2.0)
+    assert E.compute_laal([10.0, 10.0], source_length=4.0, target_length=2) == 10.0
+    h1 = Hypothesis(score=-1.0, y_sequence=torch.tensor([1, 2]), text="a b", timestamp=[0, 3], token_confidence=[0.9, 0.8])
+    h2 = Hypothesis(score=-2.0, y_sequence=torch.tensor([3]), text="c", timestamp=[1], token_confidence=[0.7])
+    m = E.merge_parallel_chunks([h1, h2], [10, 8])
+    assert m.y_sequence.tolist() == [1, 2, 3] and m.timestamp == [0, 3, 11] and m.text == "a b c" and m.score == -3.0 and m.token_confidence == [0.9, 0.8, 0.7] and m.length == 18
+    g = E.merge_hypotheses_of_same_audio([("rec1-1", h2, 8), ("rec1-0", h1, 10), ("rec2_cut0", h2, 8)], decode_tokens_to_str=lambda ids: "".join(map(str, ids)))
+    assert g["rec1"].text == "123" and g["rec2"].y_sequence.tolist() == [3]
+    h = Hypothesis(score=0.0, y_sequence=[1], timestamp={"word": [{"word": "hi", "start_offset": 5, "end_offset": 9}]})
+    E.process_timestamp_outputs([h], subsampling_factor=8, window_stride=0.01)
+    assert h.timestamp["word"][0]["start"] == 0.4 and h.timestamp["word"][0]["end"] == 0.72
+    assert E.get_ctm_line("utt", 1, 0.5, 0.25, "hello", conf=0.9, speaker="spk1") == "utt 1 0.500 0.250 hello 0.900 lex spk1\n"
+    assert E.get_ctm_line("utt", 1, 0.5, 0.25, "hello").endswith("hello NA lex NA\n")
+    with pytest.raises(ValueError):
+        E.get_ctm_line("u", 1, -1.0, 0.1, "x")
+    assert E.get_subsegments(1.0, 2.0, 1.5, 0.75) == [(1.0, 1.5), (1.75, 1.25)]
+    rttm = tmp_path / "r.rttm"
+    rttm.write_text("SPEAKER r 1 0.0 2.0 <NA> <NA> A <NA> <NA>\nSPEAKER r 1 3.0 1.0 <NA> <NA> B <NA> <NA>\n")
+    (tmp_path / "in.json").write_text(json.dumps({"audio_filepath": "/x/r.wav", "rttm_filepath": str(rttm)}))
+    assert E.create_segment_manifest(str(tmp_path / "in.json"), str(tmp_path / "seg.json"), window=1.5, shift=0.75) == 3
+    d = E.get_subsegment_dict(str(tmp_path / "seg.json"), 1.5, 0.75)
+    assert d["r"]["ts"] == [[0.0, 1.5], [0.75, 2.0], [3.0, 4.0]] and d["r"]["json_dic"][2]["label"] == "B"
