@@ -43,6 +43,7 @@ class TranscribeConfig:
     timestamps: Optional[bool] = None
     verbose: bool = True
     partial_hypothesis: Optional[List[Any]] = None
+    chunk_duration_seconds: Optional[float] = None      # recordings longer than this are cut into chunks of this length and merged
 
 
 class ASRModel(ModelPT):
@@ -356,12 +357,13 @@ class TranscriptionMixin:
     def transcribe(self, audio: Union[str, List[str], np.ndarray, torch.Tensor, List[np.ndarray], List[torch.Tensor]],
                    batch_size: int = 4, return_hypotheses: bool = False, num_workers: int = 0,
                    channel_selector=None, augmentor=None, verbose: bool = False, timestamps: Optional[bool] = None,
-                   override_config: Optional[TranscribeConfig] = None, **kw):
+                   override_config: Optional[TranscribeConfig] = None, chunk_duration_seconds: Optional[float] = None, **kw):
         """Transcribe files / arrays.  Returns texts, or ``Hypothesis`` objects when ``return_hypotheses`` (or
-        ``timestamps``) is set."""
+        ``timestamps``) is set.  ``chunk_duration_seconds``: very long recordings are cut into non-overlapping chunks of that
+        length, the chunks are transcribed as a batch and merged back (tokens concatenated, frame indices shifted)."""
         cfg = override_config or TranscribeConfig(batch_size=batch_size, return_hypotheses=return_hypotheses,
                                                   num_workers=num_workers, channel_selector=channel_selector,
-                                                  timestamps=timestamps, verbose=verbose)
+                                                  timestamps=timestamps, verbose=verbose, chunk_duration_seconds=chunk_duration_seconds)
         if isinstance(audio, (str, np.ndarray)) or torch.is_tensor(audio) and audio.dim() == 1:
             audio = [audio]
         elif torch.is_tensor(audio):
@@ -371,7 +373,43 @@ class TranscriptionMixin:
             results.extend(out)
         return results
 
+    def _transcribe_chunked(self, audio, cfg: TranscribeConfig, sr: int):
+        """Every recording -> its chunks -> one flat list through the ordinary path -> merged per recording."""
+        import dataclasses
+
+        from ..utils.asr_eval_utils import merge_parallel_chunks
+
+        n = int(cfg.chunk_duration_seconds * sr)
+        flat, owner = [], []
+        for i, a in enumerate(audio):
+            w = torch.from_numpy(_data.load_audio(a, sr, channel_selector=cfg.channel_selector)) if isinstance(a, str) else torch.as_tensor(a, dtype=torch.float32).flatten()
+            pieces = list(w.split(n)) if w.numel() > n else [w]
+            if len(pieces) > 1 and pieces[-1].numel() < sr // 10:          # a sliver at the end joins the chunk before it
+                pieces[-2] = torch.cat([pieces[-2], pieces[-1]])
+                pieces.pop()
+            flat += pieces
+            owner += [i] * len(pieces)
+        inner = dataclasses.replace(cfg, chunk_duration_seconds=None, return_hypotheses=True)
+        hyps = [h for out in self.transcribe_generator(flat, inner) for h in out]
+        feat = getattr(getattr(self, "preprocessor", None), "featurizer", None)
+        hop = int(getattr(feat, "hop_length", 160))
+        sub = int(getattr(getattr(self, "encoder", None), "subsampling_factor", 1))
+        dec = getattr(self, "decoding", None) or getattr(self, "ctc_decoding", None)
+        to_text = getattr(dec, "decode_tokens_to_str", None)
+        merged = []
+        for i in range(len(audio)):
+            idx = [k for k, o in enumerate(owner) if o == i]
+            frames = [int(hyps[k].length) if int(hyps[k].length or 0) > 0 else -(-flat[k].numel() // (hop * sub)) for k in idx]
+            m = merge_parallel_chunks([hyps[k] for k in idx], frames, to_text) if len(idx) > 1 else hyps[idx[0]]
+            merged.append(m)
+        return merged
+
     def transcribe_generator(self, audio, cfg: TranscribeConfig):
+        sr = cfg_get(cfg_get(self._cfg, "preprocessor", {}), "sample_rate", 16000)
+        if getattr(cfg, "chunk_duration_seconds", None):
+            hyps = self._transcribe_chunked(audio, cfg, int(sr))
+            yield hyps if (cfg.return_hypotheses or cfg.timestamps) else [h.text for h in hyps]
+            return
         state = self._transcribe_on_begin(cfg)
         try:
             sr = cfg_get(cfg_get(self._cfg, "preprocessor", {}), "sample_rate", 16000)

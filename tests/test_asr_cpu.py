@@ -377,3 +377,22 @@ def test_model_level_adapters_strategies_save_load_and_restore(tmp_path):
     assert torch.equal(st(x, torch.nn.Linear(32, 32), module=host), x)
     with pytest.raises(ValueError, match="not one of"):
         m.add_adapter("vocoder:x", {"in_features": 176, "dim": 4})
+
+
+def test_transcribe_long_audio_in_chunks_merges_tokens_and_frame_indices():
+    from speech_b200.models import EncDecCTCModelBPE
+    from speech_b200.models.configs import fastconformer_ctc_config
+
+    torch.manual_seed(0)
+    m = EncDecCTCModelBPE(fastconformer_ctc_config("small", vocab_size=32, n_layers=1)).eval()
+    g = torch.Generator().manual_seed(0)
+    long_audio = (0.1 * torch.randn(16000 * 3 + 500, generator=g)).numpy()
+    short = long_audio[:8000]
+    chunked = m.transcribe([long_audio, short], batch_size=4, return_hypotheses=True, chunk_duration_seconds=1.0)
+    parts = m.transcribe([long_audio[:16000], long_audio[16000:32000], long_audio[32000:]], batch_size=4, return_hypotheses=True)
+    assert len(chunked) == 2
+    want = [int(t) for p in parts for t in (p.y_sequence.tolist() if torch.is_tensor(p.y_sequence) else p.y_sequence)]
+    assert [int(t) for t in chunked[0].y_sequence.tolist()] == want                 # the 500-sample sliver joined the third chunk
+    assert chunked[1].text == m.transcribe([short], batch_size=1)[0]
+    texts = m.transcribe([long_audio], batch_size=2, chunk_duration_seconds=1.0)
+    assert isinstance(texts[0], str)
