@@ -4,7 +4,6 @@ the middle of the word; output is a per-recording JSON with speaker-labelled sen
 python .../offline_diar_with_asr_infer.py diarizer.manifest_filepath=m.json diarizer.out_dir=out diarizer.asr.model_path=asr.nemo \
     diarizer.speaker_embeddings.model_path=titanet.nemo [diarizer.vad.model_path=vad.nemo]
 (reference script: ``examples/speaker_tasks/diarization/clustering_diarizer/offline_diar_with_asr_infer.py``)."""
-import json
 import os
 
 import torch
@@ -13,7 +12,8 @@ from speech_b200.core.config import OmegaConf, hydra_runner
 from speech_b200.data.audio_to_text import read_manifest
 from speech_b200.models.asr_model import ASRModel
 from speech_b200.models.diarizers import ClusteringDiarizer
-from speech_b200.models.multitalker import sentences_from_words, write_seglst
+from speech_b200.models.diar_with_asr import OfflineDiarWithASR
+from speech_b200.models.multitalker import write_seglst
 from speech_b200.utils.logging import logging
 
 
@@ -31,36 +31,26 @@ def words_with_times(model, path: str):
     return out
 
 
-def assign_speakers(words, segments):
-    """``segments``: ``(start, end, speaker)``; a word goes to the segment that holds its mid-point, else to the nearest one."""
-    out = []
-    for w in words:
-        mid = 0.5 * (w["start_time"] + w["end_time"])
-        best = min(segments, key=lambda s: 0.0 if s[0] <= mid <= s[1] else min(abs(mid - s[0]), abs(mid - s[1]))) if segments else (0, 0, "speaker_0")
-        out.append(dict(w, speaker=best[2]))
-    return out
-
-
 @hydra_runner(config_path="../conf", config_name="diar_infer_general")
 def main(cfg):
     d = cfg.diarizer
     os.makedirs(d.out_dir, exist_ok=True)
     diar = ClusteringDiarizer(cfg)
     asr = ASRModel.restore_from(d.asr.model_path, map_location="cuda" if torch.cuda.is_available() else "cpu").eval()
-    seglst = []
+    pipe = OfflineDiarWithASR(word_anchor=d.get("asr", {}).get("word_ts_anchor_pos", "mid") if d.get("asr") else "mid")
+    diar_labels, word_ts = {}, {}
     for it in read_manifest(d.manifest_filepath):
         uid = os.path.splitext(os.path.basename(it["audio_filepath"]))[0]
         segs = list(diar.diarize([it["audio_filepath"]], [it.get("num_speakers")]).values())[0]
-        words = assign_speakers(words_with_times(asr, it["audio_filepath"]), segs)
-        sents = []
-        for spk in sorted({w["speaker"] for w in words}):
-            sents += sentences_from_words([w for w in words if w["speaker"] == spk], uid, spk)
-        sents.sort(key=lambda s: s["start_time"])
-        with open(os.path.join(d.out_dir, uid + ".json"), "w", encoding="utf-8") as f:
-            json.dump({"session_id": uid, "speaker_count": len({s["speaker"] for s in sents}), "sentences": sents, "words": words}, f, indent=2)
-        seglst += sents
+        diar_labels[uid] = [f"{a:.3f} {b:.3f} {s}" for a, b, s in segs]
+        word_ts[uid] = words_with_times(asr, it["audio_filepath"])
+    result = pipe.get_transcript_with_speaker_labels(diar_labels, word_ts)
+    OfflineDiarWithASR.write_outputs(result, d.out_dir)
+    seglst = [{"session_id": uid, "speaker": s["speaker"], "start_time": round(s["start_time"], 3), "end_time": round(s["end_time"], 3), "words": s["text"]}
+              for uid, r in result.items() for s in r["sentences"]]
     write_seglst(os.path.join(d.out_dir, "all.seglst.json"), seglst)
     logging.info(f"{len(seglst)} sentences -> {d.out_dir}")
+    return result
 
 
 if __name__ == "__main__":

@@ -360,3 +360,45 @@ def test_speaker_tagged_asr_offline_streaming_and_speaker_target_data(tmp_path):
     assert torch.isfinite(out["loss"])
     asr.eval()
     assert "val_wer" in asr.validation_pass(batch, 0)
+
+
+def test_offline_diarization_with_asr_assignment_realignment_outputs_and_scores(tmp_path):
+    import json
+
+    from speech_b200.models import diar_with_asr as D
+
+    words = [{"word": w, "start_time": 0.5 * i, "end_time": 0.5 * i + 0.4} for i, w in enumerate("how are you today i am fine thanks".split())]
+    labels = ["0.000 1.800 speaker_0", "1.800 4.000 speaker_1"]                 # the change is placed one word early ("today" starts at 1.5)
+    plain = D.OfflineDiarWithASR(word_anchor="mid")
+    tagged = plain.assign_speakers(words, labels)
+    assert [w["speaker"] for w in tagged] == ["speaker_0"] * 4 + ["speaker_1"] * 4
+    early = ["0.000 1.300 speaker_0", "1.300 4.000 speaker_1"]
+    assert [w["speaker"] for w in plain.assign_speakers(words, early)][3] == "speaker_1"              # "today" lands on the wrong side
+    # a language model that likes the two fluent sentences moves the boundary back
+    good = {("how", "are", "you", "today"), ("i", "am", "fine", "thanks")}
+    lm = lambda ws: 0.0 if tuple(ws) in good else -float(len(ws))  # noqa: E731
+    fixed = D.OfflineDiarWithASR(realigning_lm=lm, max_shift=2).assign_speakers(words, early)
+    assert [w["speaker"] for w in fixed] == ["speaker_0"] * 4 + ["speaker_1"] * 4
+    res = plain.get_transcript_with_speaker_labels({"s1": labels}, {"s1": words})
+    assert res["s1"]["speaker_count"] == 2 and [s["text"] for s in res["s1"]["sentences"]] == ["how are you today", "i am fine thanks"]
+    D.OfflineDiarWithASR.write_outputs(res, str(tmp_path / "out"))
+    assert open(tmp_path / "out" / "s1.txt").readline().startswith("[00:00.00 - 00:01.90] speaker_0: how are you today")
+    assert len(open(tmp_path / "out" / "s1.ctm").read().splitlines()) == 8 and json.load(open(tmp_path / "out" / "s1.json"))["session_id"] == "s1"
+    rttm = D.labels_to_rttmfile(["0.000 2.000 A", "2.000 4.000 B"], "s1", str(tmp_path / "rttm"))
+    assert D.rttm_to_labels(rttm) == ["0.000 2.000 A", "2.000 4.000 B"]
+    ref_words = [(w["word"], "A" if i < 4 else "B") for i, w in enumerate(words)]
+    ev = D.OfflineDiarWithASR.evaluate(res, {"s1": rttm}, {"s1": ref_words}, {"s1": labels}, collar=0.0)["s1"]
+    assert ev["cpWER"] == 0.0 and ev["WDER"] == 0.0 and ev["WER"] == 0.0 and ev["DER"] == pytest.approx(0.05) and ev["CER"] == pytest.approx(0.05)
+    wrong = plain.get_transcript_with_speaker_labels({"s1": early}, {"s1": words})
+    ev2 = D.OfflineDiarWithASR.evaluate(wrong, None, {"s1": ref_words})["s1"]
+    assert ev2["WDER"] == pytest.approx(1 / 8) and ev2["cpWER"] == pytest.approx(2 / 8)
+    assert D.merge_float_intervals([[0, 1], [0.5, 2], [3, 4], [4.00001, 5]]) == [[0.0, 2.0], [3.0, 5.0]]
+    assert D.get_sub_range_list([1.0, 3.5], [[0, 2], [3, 4], [5, 6]]) == [[1.0, 2], [3, 3.5]] and not D.is_overlap([0, 1], [1, 2])
+    seg = [{"session_id": "s", "speaker": "A", "start_time": 8.0, "end_time": 12.0, "words": "a b c d"}, {"session_id": "s", "speaker": "B", "start_time": 13.0, "end_time": 14.0, "words": "e"}]
+    chunks = D.chunk_seglst(seg, 10.0)
+    assert [c["words"] for c in chunks[0]] == ["a b"] and [c["words"] for c in chunks[1]] == ["c d", "e"] and chunks[1][0]["start_time"] == 10.0
+    man = tmp_path / "m.json"
+    man.write_text(json.dumps({"audio_filepath": "/a/x.wav", "offset": 0, "duration": 3.0}) + "\n" + json.dumps({"audio_filepath": "/a/x.wav", "offset": 3.0, "duration": 3.0}))
+    assert list(D.audio_rttm_map(str(man), attach_dur=True)) == ["x_0_3000", "x_3000_3000"]
+    with pytest.raises(KeyError):
+        D.audio_rttm_map(str(man))
