@@ -593,3 +593,83 @@ def test_asr_evaluation_helpers(tmp_path):
     assert E.create_segment_manifest(str(tmp_path / "in.json"), str(tmp_path / "seg.json"), window=1.5, shift=0.75) == 3
     d = E.get_subsegment_dict(str(tmp_path / "seg.json"), 1.5, 0.75)
     assert d["r"]["ts"] == [[0.0, 1.5], [0.75, 2.0], [3.0, 4.0]] and d["r"]["json_dic"][2]["label"] == "B"
+
+
+def test_misc_extra_packing_datastore_dtypes_configs(tmp_path, monkeypatch):
+    import dataclasses
+    from argparse import ArgumentParser
+
+    from speech_b200.utils import misc_extra as X
+
+    assert X.first_fit([4, 3, 3, 2, 2], 6) == [[4, 2], [3, 3], [2]] and X.first_fit_decreasing([2, 5, 4, 1], 6) == [[5, 1], [4, 2]]
+    data = [{"input_ids": list(range(n + 1)), "loss_mask": [0] + [1] * n} for n in (3, 3, 2, 5, 1, 9)]
+    by_len, hist = X.create_hist(data, truncate_seq_len=6)
+    assert hist == [0, 1, 1, 2, 0, 1, 1] and len(by_len[6]) == 1                                     # the 9-token example was cut to 6
+    packs, meta = X.create_packing_strategy(hist, 6, "first_fit_decreasing")
+    assert sorted(map(sorted, packs)) == [[1, 5], [2], [3, 3], [6]] and meta["num_packs"] == 4 and meta["packing_factor"] == 1.5
+    filled = X.fill_packing_strategy(packs, by_len, 6)
+    assert sum(len(f["seq_start_id"]) for f in filled) == 6 and all(len(f["input_ids"]) == len(f["loss_mask"]) for f in filled)
+    two = next(f for f in filled if len(f["seq_start_id"]) == 2 and len(f["input_ids"]) == 8)       # lengths 5 and 1 -> 6 + 2 tokens
+    assert two["seq_start_id"] == [0, 6]
+    monkeypatch.setenv("NEMO_CACHE_DIR", str(tmp_path / "cache"))
+    assert X.is_datastore_path("s3://b/k/x.tar") and not X.is_datastore_path("/data/x.tar") and X.is_tarred_path("a/b.tar.gz")
+    assert X.bucket_and_object_from_uri("ais://bucket/dir/obj.wav") == ("bucket", "dir/obj.wav")
+    calls = []
+
+    def fetch(url, dest):
+        calls.append(url)
+        open(dest, "w").write("payload")
+
+    obj = X.DataStoreObject("s3://b/k/x.txt", fetch=fetch)
+    assert obj.local_path == str(tmp_path / "cache" / "datastore" / "s3" / "b" / "k" / "x.txt") and obj.local_path and len(calls) == 1
+    assert X.open_best("s3://b/k/x.txt", "r", fetch=fetch).read() == "payload" and len(calls) == 1    # cached
+    with pytest.raises(RuntimeError):
+        X.DataStoreObject("gs://nobody/registered").get()
+    assert X.str_to_dtype("bf16-mixed") is torch.bfloat16 and X.str_to_dtype(16) is torch.float16 and X.str_to_dtype(torch.float64) is torch.float64
+    with pytest.raises(ValueError):
+        X.str_to_dtype("int3")
+    m = X.CastToFloat(torch.nn.Softmax(dim=-1))
+    y = m(torch.randn(2, 5, dtype=torch.bfloat16))
+    assert y.dtype == torch.bfloat16
+    out = X.CastToFloatAll(torch.nn.Bilinear(3, 3, 2))(torch.randn(4, 3, dtype=torch.float16), torch.randn(4, 3, dtype=torch.float16))
+    assert out.dtype == torch.float16
+    with X.monkeypatched(torch, "is_tensor", lambda x: "patched"):
+        assert torch.is_tensor(1) == "patched"
+    assert torch.is_tensor(torch.zeros(1)) is True and X.maybe_cast_to_type("3", int) == 3 and X.maybe_cast_to_type(None, int) is None
+
+    @dataclasses.dataclass
+    class Schema:
+        sample_rate: int = 16000
+        train_ds: dict = dataclasses.field(default_factory=lambda: {"batch_size": 8, "shuffle": True})
+        validation_ds: dict = dataclasses.field(default_factory=lambda: {"batch_size": 8})
+
+    cfg = X.update_model_config(Schema(), {"sample_rate": 8000, "train_ds": {"batch_size": 4, "extra": 1}})
+    assert cfg.sample_rate == 8000 and cfg.train_ds.batch_size == 4 and cfg.train_ds.shuffle and cfg.train_ds.extra == 1 and "validation_ds" not in cfg
+
+    class Mod:
+        def __init__(self, sample_rate, hidden, legacy=None):
+            pass
+
+    @dataclasses.dataclass
+    class ModCfg:
+        sample_rate: int = 1
+        width: int = 2
+
+    assert X.assert_dataclass_signature_match(Mod, ModCfg, ignore_args=["legacy"], remap_args={"hidden": "width"}) == (True, None, None)
+    assert X.assert_dataclass_signature_match(Mod, ModCfg)[1] == {"hidden", "legacy"}
+    src = tmp_path / "a.txt"
+    src.write_text("x")
+    fails = {"n": 0}
+
+    def flaky(s, d):
+        fails["n"] += 1
+        if fails["n"] < 3:
+            raise OSError("stale handle")
+        import shutil
+
+        shutil.copy2(s, d)
+
+    assert X.robust_copy(src, tmp_path / "b.txt", retries=3, backoff=0.0, copy_fn=flaky).endswith("b.txt") and fails["n"] == 3
+    p = X.add_asr_args(X.add_scheduler_args(X.add_optimizer_args(ArgumentParser(), default_lr=1e-3)))
+    a = p.parse_args(["--asr_model", "m", "--train_dataset", "t", "--eval_dataset", "e", "--opt_args", "betas=0.9,0.98"])
+    assert a.lr == 1e-3 and a.opt_args == ["betas=0.9,0.98"] and a.min_lr == 0.0
