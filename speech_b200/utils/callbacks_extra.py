@@ -385,3 +385,27 @@ class HuggingFaceFileIO:
         with tempfile.TemporaryDirectory() as d:
             self.save_pretrained(d)
             return HfApi().upload_folder(repo_id=repo_id, folder_path=d, **kw)
+
+
+class IPLEpochStopper(Callback):
+    """Stops training at the end of every ``stop_every_n_epochs``-th epoch when ``enable_stop`` is set.  Iterative pseudo-labelling
+    alternates training with re-labelling of the unlabelled data: the trainer stops here, labels are regenerated with the current
+    model, and training resumes from the checkpoint (reference: ``common/callbacks/ipl_epoch_stopper.py``)."""
+
+    def __init__(self, enable_stop: bool = False, stop_every_n_epochs: int = 1):
+        self.enable_stop, self.every = bool(enable_stop), int(stop_every_n_epochs)
+        self._left = self.every
+
+    def on_train_epoch_end(self, trainer, model):
+        if not self.enable_stop:
+            return
+        self._left -= 1
+        if self._left <= 0:
+            trainer.should_stop = True
+            self._left = self.every
+
+    def state_dict(self):
+        return {"left": self._left}
+
+    def load_state_dict(self, sd):
+        self._left = int(sd.get("left", self.every))

@@ -158,3 +158,61 @@ class GlobalAverageLossMetric:
             dist.all_reduce(t)
             s, n = t[0].cpu(), t[1].cpu()
         return (s / n).float() if n > 0 else torch.tensor(float("nan"))
+
+
+class TopKClassificationAccuracy:
+    """``update(logits [N, C], labels [N])`` accumulates, for every k, how often the label is among the k best classes;
+    ``compute()`` -> list of accuracies in the order of ``top_k``.  Counts are summed over ranks when a process group exists."""
+
+    def __init__(self, top_k: Sequence[int] = (1,)):
+        self.top_k = sorted(set(int(k) for k in top_k))
+        self.reset()
+
+    def reset(self):
+        self.correct = torch.zeros(len(self.top_k), dtype=torch.float64)
+        self.total = 0.0
+
+    @torch.no_grad()
+    def update(self, logits: torch.Tensor, labels: torch.Tensor):
+        kmax = min(max(self.top_k), logits.shape[-1])
+        pred = logits.topk(kmax, dim=-1).indices
+        hit = pred == labels.view(-1, 1)
+        for i, k in enumerate(self.top_k):
+            self.correct[i] += float(hit[:, : min(k, kmax)].any(dim=1).sum())
+        self.total += labels.numel()
+
+    def compute(self) -> List[float]:
+        c, t = self.correct.clone(), torch.tensor([self.total], dtype=torch.float64)
+        if torch.distributed.is_available() and torch.distributed.is_initialized():
+            dev = "cuda" if torch.distributed.get_backend() == "nccl" else "cpu"
+            c, t = c.to(dev), t.to(dev)
+            torch.distributed.all_reduce(c)
+            torch.distributed.all_reduce(t)
+            c, t = c.cpu(), t.cpu()
+        return [float(x / t.clamp(min=1)) for x in c]
+
+
+class Perplexity:
+    """Mean perplexity of a stream of distributions: ``update(probs=...)`` or ``update(logits=...)`` ([..., V]); the entropy of
+    every distribution is exponentiated and averaged (``validate_args`` checks that probabilities sum to one)."""
+
+    def __init__(self, validate_args: bool = True):
+        self.validate = validate_args
+        self.reset()
+
+    def reset(self):
+        self.sum, self.n = 0.0, 0
+
+    @torch.no_grad()
+    def update(self, probs: Optional[torch.Tensor] = None, logits: Optional[torch.Tensor] = None):
+        if (probs is None) == (logits is None):
+            raise ValueError("give probs or logits, not both")
+        if probs is not None and self.validate and not torch.allclose(probs.sum(-1), torch.ones_like(probs.sum(-1)), atol=1e-4):
+            raise ValueError("probabilities do not sum to one")
+        logp = torch.log_softmax(logits.float(), -1) if logits is not None else torch.log(probs.float().clamp(min=1e-30))
+        ent = -(logp.exp() * logp).sum(-1)
+        self.sum += float(ent.exp().sum())
+        self.n += ent.numel()
+
+    def compute(self) -> float:
+        return self.sum / max(1, self.n)

@@ -400,3 +400,81 @@ def test_trainer_resumes_bit_identically_from_a_dcp_directory(tmp_path):
     assert tr2.global_step == 5
     for a, b in zip(whole.parameters(), resumed.parameters()):
         assert torch.equal(a, b)
+
+
+def test_common_losses_datasets_and_metrics():
+    import numpy as np
+    import torch
+
+    from speech_b200.data.concat import CodeSwitchedDataset, ConcatDataset, ConcatMapDataset, FallbackDataset
+    from speech_b200.losses.extra import LatentSpeakerSupervisionLoss, MultiSimilarityLoss, SpanningLoss
+    from speech_b200.utils.metrics import Perplexity, TopKClassificationAccuracy
+
+    # speaker tokens 10, 11; words 1..5; pad 0
+    labels = torch.tensor([[10, 1, 2, 11, 3, 10, 4, 0]])
+    lss = LatentSpeakerSupervisionLoss([10, 11], pad_id=0, per_speaker_normalization=False)
+    assert lss.active_speakers(labels).tolist() == [[0, 0, 0, 1, 1, 0, 0, 0]]
+    V = 12
+    good = torch.full((1, 8, V), -10.0)
+    for t, s in enumerate([10, 10, 10, 11, 11, 10, 10, 10]):
+        good[0, t, s] = 0.0
+    bad = good.clone()
+    bad[0, 4, 11], bad[0, 4, 10] = -10.0, 0.0                                # the word after <spk1> leans to speaker 0
+    lg, lb = float(lss(torch.log_softmax(good, -1), labels)), float(lss(torch.log_softmax(bad, -1), labels))
+    assert lg < 1e-3 and lb == pytest.approx(10.0 / 4, rel=1e-3)             # one of four word positions is wrong
+    per = LatentSpeakerSupervisionLoss([10, 11], pad_id=0, per_speaker_normalization=True)
+    assert float(per(torch.log_softmax(bad, -1), labels)) == pytest.approx(10.0 / 2, rel=1e-3)        # speaker 1 has one word: its error weighs a half
+    with_ce = LatentSpeakerSupervisionLoss([10, 11], pad_id=0, include_ce_loss=True)
+    assert float(with_ce(torch.log_softmax(good, -1), labels)) > lg
+    torch.manual_seed(0)
+    emb = torch.nn.Parameter(torch.randn(8, 4))
+    y = torch.tensor([0, 0, 1, 1, 2, 2, 3, 3])
+    ms = MultiSimilarityLoss()
+    opt = torch.optim.Adam([emb], 0.05)
+    first = float(ms(emb, y))
+    for _ in range(60):
+        opt.zero_grad()
+        ms(emb, y).backward()
+        opt.step()
+    e = torch.nn.functional.normalize(emb.detach(), dim=-1)
+    assert float(ms(emb, y)) < first and float((e[0] * e[1]).sum()) > float((e[0] * e[2]).sum())
+    span_logits = torch.zeros(2, 5, 2)
+    span_logits[0, 1, 0], span_logits[0, 3, 1] = 5.0, 5.0
+    loss, s_, e_ = SpanningLoss()(span_logits, torch.tensor([1, 99]), torch.tensor([3, 99]))
+    assert float(loss) < 0.1 and s_.shape == (2, 5)
+    a, b = list(range(100, 110)), list(range(200, 203))
+    rr = ConcatMapDataset([a, b], sampling_technique="round-robin")
+    assert len(rr) == 20 and [rr[i] for i in range(4)] == [100, 200, 101, 201] and rr[7] == 200                 # the short one wraps around
+    tmp = ConcatMapDataset([a, b], sampling_technique="temperature", sampling_temperature=1.0, seed=1)
+    assert len(tmp) == 13 and 4 <= sum(x >= 200 for x in [tmp[i] for i in range(13)]) + 4 <= 12
+    rnd = ConcatMapDataset([a, b], sampling_technique="random", sampling_probabilities=[0.0, 1.0])
+    assert all(rnd[i] >= 200 for i in range(len(rnd)))
+    parts = [list(ConcatDataset([a, b], sampling_technique="round-robin", global_rank=r, world_size=2)) for r in range(2)]
+    assert len(parts[0]) == len(parts[1]) == 10 and sorted(parts[0] + parts[1]) == sorted([rr[i] for i in range(20)])
+    mk = lambda base, n: [(torch.full((8000,), 0.01 * (base + 1)), torch.tensor(8000), torch.tensor([base, base]), torch.tensor(2)) for _ in range(n)]  # noqa: E731
+    cs = CodeSwitchedDataset([mk(0, 6), mk(1, 6)], min_duration=1.0, max_duration=2.0, min_monolingual=0.0, pause_join=0.1, sample_rate=16000, return_lang_ids=True, seed=3)
+    items = list(cs)
+    assert items and all(1.0 <= (x[0].numel() / 16000) <= 2.3 for x in items[:-1]) and {int(v) for it in items for v in it[4]} == {0, 1}
+    x0 = items[0]
+    assert x0[2].numel() == x0[4].numel() and float(x0[0][:8000].pow(2).mean().sqrt()) == pytest.approx(10 ** (-25 / 20), rel=1e-3)
+
+    class Flaky(torch.utils.data.Dataset):
+        def __len__(self):
+            return 4
+
+        def __getitem__(self, i):
+            if i == 2:
+                raise OSError("corrupt")
+            return i
+
+    fb = FallbackDataset(Flaky())
+    assert [fb[i] for i in range(4)] == [0, 1, 1, 3] and fb.failures == 1
+    acc = TopKClassificationAccuracy(top_k=[1, 2])
+    acc.update(torch.tensor([[0.1, 0.7, 0.2], [0.5, 0.3, 0.2], [0.2, 0.3, 0.5]]), torch.tensor([1, 1, 0]))
+    assert acc.compute() == [pytest.approx(1 / 3), pytest.approx(2 / 3)]
+    ppl = Perplexity()
+    ppl.update(probs=torch.full((2, 4), 0.25))
+    ppl.update(logits=torch.tensor([[100.0, 0.0, 0.0, 0.0]]))
+    assert ppl.compute() == pytest.approx((4 + 4 + 1) / 3, rel=1e-4)
+    with pytest.raises(ValueError):
+        Perplexity().update(probs=torch.full((1, 4), 0.3))
