@@ -95,6 +95,11 @@ def build_text_tokenizer(cfg):
     if cfg is None:
         return None
     get = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: getattr(cfg, k, d))
+    if get("_target_", None):
+        # a tokenizer class by path (e.g. speech_b200.tokenizers.tts.IPATokenizer) with a nested ``g2p`` block built first
+        from ..core.instantiate import instantiate
+
+        return instantiate(cfg)
     kind = get("type", "char")
     if kind == "char":
         from ..tokenizers import CharTokenizer

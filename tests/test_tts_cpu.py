@@ -2,6 +2,7 @@
 MagpieTTS training and autoregressive inference."""
 import math
 import os
+import re
 
 import numpy as np
 
@@ -769,3 +770,47 @@ def test_tts_logging_callback_writes_audio_and_images(tmp_path):
     assert create_id("/data/x/y.wav") == "data_x_y"
     write_pgm(str(tmp_path / "flat.pgm"), np.zeros((3, 4)))
     assert len(open(tmp_path / "flat.pgm", "rb").read()) == len(b"P5\n4 3\n255\n") + 12
+
+
+def test_tts_text_tokenizers():
+    from speech_b200.tokenizers.tts import (AggregatedTTSTokenizer, ArabicCharsTokenizer, EnglishCharsTokenizer, EnglishPhonemesTokenizer, FrenchCharsTokenizer,
+                                            GermanCharsTokenizer, HindiCharsTokenizer, IPATokenizer, SpanishCharsTokenizer, english_text_preprocessing,
+                                            get_grapheme_character_set, get_ipa_punctuation_list)
+    from speech_b200.tts.g2p import IpaG2p
+
+    assert english_text_preprocessing("Café “naïve”… ok") == 'cafe "naive"... ok'
+    assert "Ñ" in get_grapheme_character_set("es-ES") and "ñ" in get_grapheme_character_set("es-ES", "mixed") and "¿" in get_ipa_punctuation_list("es-ES")
+    with pytest.raises(ValueError):
+        get_grapheme_character_set("xx-XX")
+    en = EnglishCharsTokenizer(pad_with_space=True, add_blank_at="last_but_one")
+    ids = en("Hello,   Wörld§!")
+    assert en.decode(ids) == " hello, world! " and en.pad == len(en.tokens) - 3 and en.blank == en.pad + 1 and en.oov == en.pad + 2
+    last = EnglishCharsTokenizer(add_blank_at="last")
+    assert last.blank == len(last.tokens) - 1 and last.oov == len(last.tokens) - 2
+    nop = EnglishCharsTokenizer(punct=False)
+    assert nop.decode(nop("hi, there!")) == "hi there"
+    assert GermanCharsTokenizer().decode(GermanCharsTokenizer()("Straße und Öl")) == "Straße und Öl"
+    assert SpanishCharsTokenizer().decode(SpanishCharsTokenizer()("¿Qué Niño?")) == "¿qué niño?"
+    assert FrenchCharsTokenizer().decode(FrenchCharsTokenizer()("Ça va, garçon")) == "ça va, garçon"
+    assert HindiCharsTokenizer().decode(HindiCharsTokenizer()("नमस्ते।")) == "नमस्ते।" and len(ArabicCharsTokenizer()("مرحبا؟")) == 6
+    arpa = {"hello": ["HH", "AH0", "L", "OW1"], "world": ["W", "ER1", "L", "D"]}
+
+    def g2p(text):
+        out = []
+        for tok in re.findall(r"\w+|[^\w\s]|\s+", text):
+            out += [" "] if tok.isspace() else arpa.get(tok.lower(), list(tok.lower()) if tok.isalpha() else [tok])
+        return out
+
+    ph = EnglishPhonemesTokenizer(g2p, stresses=True, chars=True)
+    ids = ph("Hello xyz, world")
+    assert ph.decode(ids) == "HH|AH0|L|OW1| |x|y|z|,| |W|ER1|L|D"
+    ns = EnglishPhonemesTokenizer(g2p, stresses=False)
+    assert ns.decode(ns("hello world")) == "HH|AH|L|OW| |W|ER|L|D" and ns.vocab_size < ph.vocab_size
+    ipa_g2p = IpaG2p({"hello": ["həˈloʊ"], "world": ["ˈwɝld"]}, use_chars=True, grapheme_prefix="#")
+    ipa = IPATokenizer(ipa_g2p, locale="en-US")
+    assert ipa.decode(ipa("hello xy world!")) == "həˈloʊ #X#Y ˈwɝld!" and "#Q" in ipa.tokens
+    fixed = IPATokenizer(IpaG2p({"hello": ["həˈloʊ"], "yes": ["jɛs"]}, use_chars=True, grapheme_prefix="#"), locale=None, fixed_vocab=list("həˈloʊ") + ["#Y", "#E", "#S"])
+    assert fixed.decode(fixed("hello yes")) == "həˈloʊ #Y#E#S"                  # "jɛs" uses symbols outside the fixed inventory: spelled instead
+    agg = AggregatedTTSTokenizer([en, ipa], ["english_chars", "english_ipa"])
+    a, b = agg.encode("hello", "english_chars"), agg.encode("hello", "english_ipa")
+    assert max(a) < en.vocab_size <= min(b) and agg.vocab_size == en.vocab_size + ipa.vocab_size and agg.decode(b, "english_ipa") == "həˈloʊ"
