@@ -320,3 +320,143 @@ def test_extra_data_tools(tmp_path):
     out = T.write_transcribed_files(str(tmp_path / "pred_rank*.json"), [str(tmp_path / "src.json")])
     merged = read_manifest(out[0])
     assert len(merged) == 1 and merged[0]["text"] == "new zero" and merged[0]["orig_text"] == "old"
+
+
+def test_asr_dataset_factories_tarred_noise_feature_and_record_datasets(tmp_path):
+    """Tarred audio with scatter / replicate sharding and a shuffle buffer, bucket chains, config factories, audio+noise items,
+    feature manifests gated by RTTM, record datasets and the prediction writer."""
+    import json
+    import tarfile
+
+    import numpy as np
+    import torch
+
+    from speech_b200.data import asr_datasets_extra as X
+    from speech_b200.data.audio_to_text import save_wav
+
+    labels = list(" abcdefghijklmnopqrstuvwxyz'")
+    rng = np.random.RandomState(0)
+    entries, tars = [], []
+    for s in range(2):
+        tar = tmp_path / f"audio_{s}.tar"
+        with tarfile.open(tar, "w") as tf:
+            for k in range(3):
+                name = f"utt{s}{k}.wav"
+                p = tmp_path / name
+                save_wav(str(p), (rng.randn(1600 * (k + 2)) * 0.1).astype(np.float32))
+                tf.add(p, arcname=name)
+                entries.append({"audio_filepath": name, "duration": 0.1 * (k + 2), "text": "ab" * (k + 1), "label": "x" if k else "y"})
+        tars.append(str(tar))
+    man = tmp_path / "tarred.json"
+    man.write_text("".join(json.dumps(e) + "\n" for e in entries))
+    brace = str(tmp_path / "audio__OP_0..1_CL_.tar")
+
+    ds = X.TarredAudioToCharDataset(brace, str(man), labels=labels, return_sample_id=True)
+    got = list(ds)
+    assert len(got) == 6 and [g[3] for g in got] == [2, 4, 6, 2, 4, 6] and got[1][0].shape[0] == 4800
+    r0 = list(X.TarredAudioToCharDataset(brace, str(man), labels=labels, world_size=2, global_rank=0, return_sample_id=True))
+    r1 = list(X.TarredAudioToCharDataset(brace, str(man), labels=labels, world_size=2, global_rank=1, return_sample_id=True))
+    assert sorted(g[4] for g in r0) == [0, 1, 2] and sorted(g[4] for g in r1) == [3, 4, 5]
+    rep = X.TarredAudioToCharDataset(brace, str(man), labels=labels, world_size=2, global_rank=1, shard_strategy="replicate")
+    assert len(list(rep)) == 6 and len(rep) == 6
+    sh = X.TarredAudioToCharDataset(brace, str(man), labels=labels, shuffle_n=4, return_sample_id=True)
+    order = [g[4] for g in sh]
+    assert sorted(order) == list(range(6)) and order != list(range(6))
+    a, al, t, tl = ds.collate_fn([g[:4] for g in got[:3]])
+    assert a.shape == (3, 6400) and t.shape == (3, 6)
+    with pytest.raises(ValueError):
+        X.shard_filepaths(tars, "scatter", world_size=3, global_rank=0)
+
+    cl = X.TarredAudioToSpeechLabelDataset(brace, str(man), labels=["x", "y"], window_length_in_sec=0.1, shift_length_in_sec=0.1)
+    xs, xl, ys, yl = cl.collate_fn(list(cl)[:2])
+    assert xs.shape == (2 + 3, 1600) and ys.tolist() == [1, 1, 0, 0, 0]
+
+    # buckets ---------------------------------------------------------------------------------------------------------
+    assert X.convert_to_config_list("a,b") == [["a", "b"]] and X.convert_to_config_list([["a"], ["b"]]) == [["a"], ["b"]]
+    with pytest.raises(ValueError):
+        X.convert_to_config_list([])
+    assert X.calc_bucketing_batch_sizes({"bucketing_batch_size": 2, "batch_size": 1}, 3) == [6, 4, 2]
+    assert X.calc_bucketing_batch_sizes({"bucketing_batch_size": [8, 4], "batch_size": 1, "bucketing_weights": [2, 1]}, 3) == [8, 8, 4]
+    with pytest.raises(ValueError):
+        X.calc_bucketing_batch_sizes({"bucketing_batch_size": 2, "batch_size": 4}, 3)
+    cfg = {"tarred_audio_filepaths": [[tars[0]], [tars[1]]], "manifest_filepath": [[str(man)], [str(man)]], "labels": labels, "batch_size": 1,
+           "bucketing_batch_size": 1, "bucketing_strategy": "fixed_order", "is_tarred": True, "shuffle": False}
+    chain = X.get_audio_to_text_char_dataset_from_config(cfg)
+    groups = list(chain)
+    assert [len(g) for g in groups] == [2, 1, 1, 1, 1]            # bucket 0 in pairs, bucket 1 one by one
+    assert chain.datasets[0].collate_fn([groups[0]])[0].shape[0] == 2
+    rnd = X.get_chain_dataset([ds, ds, ds], {"bucketing_strategy": "synced_randomized", "batch_size": 1})
+    assert isinstance(rnd, X.RandomizedChainDataset) and len(list(rnd)) == 18
+    with pytest.raises(ValueError):
+        X.get_chain_dataset([ds, ds], {"bucketing_strategy": "nope", "batch_size": 1})
+
+    # plain / concat factories -----------------------------------------------------------------------------------------
+    plain = tmp_path / "plain.json"
+    plain.write_text("".join(json.dumps({**e, "audio_filepath": str(tmp_path / e["audio_filepath"])}) + "\n" for e in entries))
+    d = X.get_audio_to_text_char_dataset_from_config({"manifest_filepath": str(plain), "labels": labels, "return_sample_id": True})
+    assert len(d) == 6 and d[2][3] == 6
+    cc = X.get_audio_to_text_char_dataset_from_config({"manifest_filepath": [str(plain), str(plain)], "labels": labels, "is_concat": True,
+                                                       "concat_sampling_technique": "round-robin"})
+    assert len(list(cc)) == 12
+    assert X.get_audio_to_text_char_dataset_from_config({"manifest_filepath": None, "labels": labels}) is None
+    mc, dc = {"sample_rate": 8000, "labels": None}, {"sample_rate": 16000}
+    X.inject_dataloader_value_from_model_config(mc, dc, "sample_rate")
+    X.inject_dataloader_value_from_model_config(mc, dc, "labels")
+    assert dc == {"sample_rate": 8000}
+
+    # prediction writer -------------------------------------------------------------------------------------------------
+    w = X.ASRPredictionWriter(d, str(tmp_path / "pred.json"))
+    w.write_on_batch_end(prediction=[(0, "hello"), (2, type("H", (), {"text": "world", "timestamp": None, "token_confidence": None})())])
+    assert w.close_output_file() == 2
+    lines = [json.loads(l) for l in open(tmp_path / "pred.json")]
+    assert lines[0]["pred_text"] == "hello" and lines[1]["pred_text"] == "world" and lines[1]["text"] == "ababab"
+
+    # audio + noise ------------------------------------------------------------------------------------------------------
+    nz = X.AudioNoiseDataset(manifest_filepath=str(plain), noise_manifest=str(plain), min_audio_len_secs=0.3)
+    item = nz[0]
+    assert len(item.audio) == 4800 and torch.equal(item.audio[3200:], item.audio[:1600])
+    assert torch.allclose(item.noisy_audio, item.audio + item.noise) and float(item.noise.abs().sum()) > 0
+    batch = nz.collate_fn([nz[0], nz[2]])
+    assert batch.audio.shape == (2, 6400) and batch.noisy_audio_len.tolist() == [4800, 6400]
+    silent = X.AudioNoiseDataset(manifest_filepath=str(plain))[1]
+    assert float(silent.noise.abs().sum()) == 0.0
+    x = torch.arange(3.0)
+    assert X.pad_audio(x, 7, "repeat").tolist() == [0, 1, 2, 0, 1, 2, 0] and X.pad_audio(x, 5, "zero").tolist() == [0, 1, 2, 0, 0]
+    wn, wl = X.load_noise_audio({"audio_filepath": str(tmp_path / "missing.wav"), "duration": 1.0}, 16000, 800)
+    assert wn.shape == (800,) and 0 < float(wn.abs().max()) < 0.05
+    tn = list(X.get_audio_noise_dataset_from_config({"manifest_filepath": str(man), "tarred_audio_filepaths": brace, "is_tarred": True,
+                                                     "noise_manifest": str(plain), "batch_size": 1}))
+    assert len(tn) == 6 and isinstance(tn[0], X.AudioNoiseItem)
+
+    # feature manifests with RTTM gating -----------------------------------------------------------------------------------
+    feat = torch.arange(80.0).reshape(1, 80).repeat(4, 1)
+    np.save(tmp_path / "f.npy", feat.numpy())
+    (tmp_path / "f.rttm").write_text("SPEAKER f 1 0.10 0.20 <NA> <NA> s <NA> <NA>\nSPEAKER f 1 0.50 0.10 <NA> <NA> s <NA> <NA>\n")
+    fm = tmp_path / "feat.json"
+    fm.write_text(json.dumps({"feature_file": str(tmp_path / "f.npy"), "rttm_filepath": str(tmp_path / "f.rttm"), "duration": 0.8, "text": "abc"}) + "\n")
+    fd = X.get_feature_char_dataset({"manifest_filepath": str(fm), "labels": labels, "use_rttm": True, "rttm_mode": "drop"})
+    f, fl, y, yl = fd[0]
+    assert fl == 30 and f[0, :20].tolist() == list(range(10, 30)) and f[0, 20:].tolist() == list(range(50, 60)) and y.tolist() == [1, 2, 3]
+    fmask = X.FeatureToCharDataset(str(fm), labels=labels, use_rttm=True, rttm_mode="mask")[0][0]
+    assert fmask.shape == (4, 80) and float(fmask[0, 0]) == pytest.approx(-16.635) and float(fmask[0, 15]) == 15.0
+    F, FL, Y, YL = fd.collate_fn([fd[0], fd[0]])
+    assert F.shape == (2, 4, 30) and Y.shape == (2, 3)
+
+    # record datasets ---------------------------------------------------------------------------------------------------------
+    recs = [{"audio": {"array": rng.randn(8000).astype(np.float32), "sampling_rate": 8000}, "text": "Ab, c!", "id": f"r{k}"} for k in range(5)]
+    hd = X.get_hf_audio_to_text_char_dataset({"labels": labels, "normalize_text": True, "return_sample_id": True, "id_key": "id"}, records=recs)
+    a0 = hd[1]
+    assert a0[0].shape[0] == 16000 and a0[2].tolist() == [1, 2, 0, 3] and a0[4] == "r1"
+    assert X.get_nested_dict_value(recs[0], "audio.sampling_rate") == 8000
+    it0 = list(X.get_hf_audio_to_text_char_dataset({"labels": labels, "streaming": True, "return_sample_id": True}, world_size=2, global_rank=0, records=recs))
+    it1 = list(X.get_hf_audio_to_text_char_dataset({"labels": labels, "streaming": True, "return_sample_id": True}, world_size=2, global_rank=1, records=recs))
+    assert [s[4] for s in it0] == [0, 2, 4] and [s[4] for s in it1] == [1, 3]
+
+    class Tok:
+        bos_id, eos_id = 1, 2
+
+        def text_to_ids(self, t):
+            return [10 + len(w) for w in t.split()]
+
+    hb = X.get_hf_audio_to_text_bpe_dataset({"use_start_end_token": True}, Tok(), records=recs)
+    assert hb[0][2].tolist() == [1, 13, 12, 2]
