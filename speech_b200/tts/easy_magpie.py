@@ -6,7 +6,7 @@
   chunk: inside a chunk as a masked, decay-weighted ``(C B^T)`` product (GEMM-shaped work), between chunks through the carried
   state; ``step`` is the O(1) recurrence for decoding with a (convolution window, state) cache.  Both give the same numbers.
 * ``NemotronHDecoder`` — a stack described by a pattern string: ``M`` = Mamba-2 block, ``*`` = causal self-attention (rotary,
-  grouped KV heads), ``-`` = gated MLP; every block is pre-normalised with a residual connection.
+  grouped KV heads), ``-`` = gated MLP, ``E`` = mixture-of-experts block (``NemotronHMoE``); every block is pre-normalised with a residual connection.
 * ``EasyMagpieTTSModel`` — one sequence ``[text tokens | audio frames]``: text tokens use the text embedding table, an audio
   frame is the sum of its per-codebook embeddings; the backbone is a ``CausalLM`` transformer or the hybrid decoder; one linear
   head per codebook predicts the next frame.  Training: cross-entropy on the audio positions; inference: autoregressive sampling
@@ -110,8 +110,69 @@ class Mamba2Block(nn.Module):
         return self.out_proj(self.norm(y * F.silu(z)))
 
 
+class NemotronHMoE(nn.Module):
+    """Mixture-of-experts feed-forward block of the hybrid decoder (pattern letter ``E``).  The router scores every expert with a
+    sigmoid; experts are arranged in ``n_group`` groups, a group's score is the sum of its two best (bias-corrected) experts, only
+    the ``topk_group`` best groups stay eligible and the ``top_k`` best eligible experts are chosen.  The mixing weights are the
+    uncorrected sigmoid scores of the chosen experts, optionally normalised to sum to one, times ``routed_scaling_factor``.  Experts
+    are plain two-layer MLPs (``down(act(up(x)))``) kept as stacked weights so that the tokens of one expert, after a sort by
+    expert, are one GEMM; a shared expert sees every token.
+    Reference: ``tts/modules/nemotron_h_decoder.py`` (``NemotronHTopkRouter``, ``NemotronHMOE``)."""
+
+    def __init__(self, hidden_size: int, n_routed_experts: int = 8, num_experts_per_tok: int = 2, moe_intermediate_size: int = 1024,
+                 moe_shared_expert_intermediate_size: int = 2048, n_group: int = 1, topk_group: int = 1, routed_scaling_factor: float = 1.0,
+                 norm_topk_prob: bool = True, mlp_hidden_act: str = "silu", initializer_range: float = 0.02):
+        super().__init__()
+        if n_routed_experts % n_group:
+            raise ValueError(f"{n_routed_experts} experts do not split into {n_group} groups")
+        self.E, self.k, self.n_group, self.topk_group = n_routed_experts, num_experts_per_tok, n_group, topk_group
+        self.scale, self.norm_topk_prob = routed_scaling_factor, norm_topk_prob
+        self.act = {"silu": F.silu, "gelu": F.gelu, "relu": F.relu, "relu2": lambda v: F.relu(v).square()}[mlp_hidden_act]
+        self.router = nn.Parameter(torch.empty(n_routed_experts, hidden_size).normal_(std=initializer_range))
+        self.register_buffer("e_score_correction_bias", torch.zeros(n_routed_experts))
+        self.up = nn.Parameter(torch.empty(n_routed_experts, moe_intermediate_size, hidden_size).normal_(std=initializer_range))
+        self.down = nn.Parameter(torch.empty(n_routed_experts, hidden_size, moe_intermediate_size).normal_(std=initializer_range))
+        self.shared_up = nn.Linear(hidden_size, moe_shared_expert_intermediate_size, bias=False)
+        self.shared_down = nn.Linear(moe_shared_expert_intermediate_size, hidden_size, bias=False)
+
+    def route(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """x [N, H] → (expert indices [N, k], mixing weights [N, k])."""
+        scores = F.linear(x.float(), self.router.float()).sigmoid()
+        with torch.no_grad():
+            choice = scores + self.e_score_correction_bias
+            if self.n_group > 1:
+                per = self.E // self.n_group
+                g = choice.view(-1, self.n_group, per).topk(min(2, per), dim=-1)[0].sum(-1)
+                keep = torch.zeros_like(g).scatter_(1, g.topk(self.topk_group, dim=-1)[1], 1.0)
+                choice = choice.masked_fill(keep.unsqueeze(-1).expand(-1, -1, per).reshape(-1, self.E) == 0, 0.0)
+            idx = choice.topk(self.k, dim=-1)[1]
+        w = scores.gather(1, idx)
+        if self.norm_topk_prob:
+            w = w / (w.sum(-1, keepdim=True) + 1e-20)
+        return idx, w * self.scale
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        h = x.reshape(-1, shape[-1])
+        idx, w = self.route(h)
+        flat = idx.reshape(-1)
+        order = flat.argsort(stable=True)
+        token = order // self.k
+        counts = torch.bincount(flat, minlength=self.E).tolist()
+        rows = h[token]
+        out = torch.zeros_like(h, dtype=torch.float32)
+        o = 0
+        for e, n in enumerate(counts):
+            if n:
+                y = F.linear(self.act(F.linear(rows[o:o + n], self.up[e].to(h.dtype))), self.down[e].to(h.dtype))
+                out.index_add_(0, token[o:o + n], y.float() * w.reshape(-1)[order[o:o + n]].unsqueeze(-1))
+                o += n
+        out = out.to(h.dtype) + self.shared_down(self.act(self.shared_up(h)))
+        return out.view(shape)
+
+
 class _HybridLayer(nn.Module):
-    def __init__(self, kind: str, cfg: LLMConfig, mamba: Dict[str, Any]):
+    def __init__(self, kind: str, cfg: LLMConfig, mamba: Dict[str, Any], moe: Optional[Dict[str, Any]] = None):
         super().__init__()
         self.kind = kind
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
@@ -121,8 +182,10 @@ class _HybridLayer(nn.Module):
             self.mixer = Attention(cfg)
         elif kind == "-":
             self.mixer = MLP(cfg)
+        elif kind == "E":
+            self.mixer = NemotronHMoE(cfg.hidden_size, **dict(moe or {}))
         else:
-            raise ValueError(f"unknown block '{kind}' in the hybrid pattern (use M, * and -)")
+            raise ValueError(f"unknown block '{kind}' in the hybrid pattern (use M, *, - and E)")
 
     def forward(self, x, cos, sin, mask, cache):
         h = self.norm(x)
@@ -136,11 +199,14 @@ class _HybridLayer(nn.Module):
 class NemotronHDecoder(nn.Module):
     """``forward(inputs_embeds, cache)`` -> hidden states; ``cache`` is a list with one dict per block."""
 
-    def __init__(self, cfg: Any, pattern: str = "M-M*-", mamba: Optional[Dict[str, Any]] = None):
+    def __init__(self, cfg: Any, pattern: str = "M-M*-", mamba: Optional[Dict[str, Any]] = None, moe: Optional[Dict[str, Any]] = None,
+                 num_layers: Optional[int] = None):
         super().__init__()
         self.config = cfg if isinstance(cfg, LLMConfig) else LLMConfig(**dict(cfg))
+        if num_layers is not None and len(pattern) != num_layers:       # the pattern repeats (or is cut) to the layer count
+            pattern = (pattern * (num_layers // len(pattern) + 1))[:num_layers]
         self.pattern = pattern
-        self.layers = nn.ModuleList(_HybridLayer(k, self.config, dict(mamba or {})) for k in pattern)
+        self.layers = nn.ModuleList(_HybridLayer(k, self.config, dict(mamba or {}), dict(moe or {})) for k in pattern)
         self.norm = RMSNorm(self.config.hidden_size, self.config.rms_norm_eps)
 
     def new_cache(self) -> List[dict]:
@@ -173,7 +239,8 @@ class EasyMagpieTTSModel(ModelPT):
         self.backbone_type = str(cfg_get(cfg, "backbone_type", "transformer"))
         lcfg = dict(cfg.backbone)
         if self.backbone_type == "nemotron_h":
-            self.backbone = NemotronHDecoder(LLMConfig(**lcfg), str(cfg_get(cfg, "hybrid_pattern", "M-M*-")), dict(cfg_get(cfg, "mamba", {}) or {}))
+            self.backbone = NemotronHDecoder(LLMConfig(**lcfg), str(cfg_get(cfg, "hybrid_pattern", "M-M*-")), dict(cfg_get(cfg, "mamba", {}) or {}),
+                                             dict(cfg_get(cfg, "moe", {}) or {}))
             hidden, text_vocab = self.backbone.config.hidden_size, self.backbone.config.vocab_size
         elif self.backbone_type == "transformer":
             self.backbone = CausalLM.from_config(lcfg)

@@ -814,3 +814,49 @@ def test_tts_text_tokenizers():
     agg = AggregatedTTSTokenizer([en, ipa], ["english_chars", "english_ipa"])
     a, b = agg.encode("hello", "english_chars"), agg.encode("hello", "english_ipa")
     assert max(a) < en.vocab_size <= min(b) and agg.vocab_size == en.vocab_size + ipa.vocab_size and agg.decode(b, "english_ipa") == "həˈloʊ"
+
+
+def test_hybrid_decoder_moe_block_routes_by_group_and_matches_dense_evaluation():
+    """The mixture-of-experts block of the hybrid decoder: group-limited sigmoid routing, the sorted-by-expert evaluation equal to a
+    per-token dense evaluation, incremental decoding equal to the full pass."""
+    import torch
+    import torch.nn.functional as F
+
+    from speech_b200.speechlm.llm import LLMConfig
+    from speech_b200.tts.easy_magpie import NemotronHDecoder, NemotronHMoE
+
+    torch.manual_seed(0)
+    moe = NemotronHMoE(16, n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=12, moe_shared_expert_intermediate_size=20, n_group=4,
+                       topk_group=1, routed_scaling_factor=1.5, initializer_range=0.5, mlp_hidden_act="relu2")
+    x = torch.randn(3, 5, 16)
+    idx, w = moe.route(x.reshape(-1, 16))
+    assert idx.shape == (15, 2) and bool((idx[:, 0] // 2 == idx[:, 1] // 2).all())      # one eligible group of two experts → both from it
+    assert torch.allclose(w.sum(-1), torch.full((15,), 1.5), atol=1e-5)
+    scores = F.linear(x.reshape(-1, 16), moe.router).sigmoid()
+    best_group = scores.view(15, 4, 2).sum(-1).argmax(-1)
+    assert torch.equal(best_group, idx[:, 0] // 2)
+    y = moe(x)
+    ref = torch.zeros(15, 16)
+    h = x.reshape(-1, 16)
+    for n in range(15):
+        for j in range(2):
+            e = int(idx[n, j])
+            ref[n] += w[n, j] * F.linear(F.relu(F.linear(h[n], moe.up[e])).square(), moe.down[e])
+    ref = ref + moe.shared_down(F.relu(moe.shared_up(h)).square())
+    assert torch.allclose(y.reshape(15, 16), ref, atol=1e-4)
+    moe.e_score_correction_bias[5] = 10.0                          # the load-balancing bias steers the choice, not the weight
+    idx2, w2 = moe.route(h)
+    assert bool((idx2 == 5).any(-1).all()) and torch.allclose(w2.sum(-1), torch.full((15,), 1.5), atol=1e-5)
+    y.sum().backward()
+    assert moe.router.grad is not None and moe.up.grad.abs().sum() > 0
+
+    tiny = dict(vocab_size=32, hidden_size=16, intermediate_size=32, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1)
+    dec = NemotronHDecoder(LLMConfig(**tiny), "ME*", {"d_state": 8, "head_dim": 8}, {"n_routed_experts": 4, "moe_intermediate_size": 8,
+                                                                                  "moe_shared_expert_intermediate_size": 8}, num_layers=5).eval()
+    assert dec.pattern == "ME*ME"
+    z = torch.randn(2, 6, 16)
+    with torch.no_grad():
+        full = dec(z)
+        cache = dec.new_cache()
+        steps = torch.cat([dec(z[:, t:t + 1], cache) for t in range(6)], dim=1)
+    assert torch.allclose(full, steps, atol=1e-4)
