@@ -460,3 +460,73 @@ def test_asr_dataset_factories_tarred_noise_feature_and_record_datasets(tmp_path
 
     hb = X.get_hf_audio_to_text_bpe_dataset({"use_start_end_token": True}, Tok(), records=recs)
     assert hb[0][2].tolist() == [1, 13, 12, 2]
+
+
+def test_manifest_collections_parse_filter_and_index(tmp_path):
+    import json
+
+    from speech_b200.data import collections as C
+
+    (tmp_path / "a.wav").write_bytes(b"")
+    (tmp_path / "t.txt").write_text("from file\n")
+    (tmp_path / "s.rttm").write_text("SPEAKER s 1 0.0 1.0 <NA> <NA> bob <NA> <NA>\nSPEAKER s 1 1.0 1.0 <NA> <NA> amy <NA> <NA>\nSPEAKER s 1 2.0 1.0 <NA> <NA> bob <NA> <NA>\n")
+    man = tmp_path / "m.json"
+    rows = [{"audio_filepath": "a.wav", "duration": 3.0, "text": "hello", "lang": "en", "offset": 1.0},
+            {"audio_filename": "/abs/b.wav", "duration": 0.2, "text": "short"},
+            {"audio_filepath": "c.wav", "duration": 2.0, "text_filepath": "t.txt", "speaker": 7},
+            {"audio_filepath": "d.wav", "duration": 1.0, "normalized_text": "norm", "token_labels": [4, 5]}]
+    man.write_text("".join(json.dumps(r) + "\n" for r in rows))
+    parser = lambda t: [ord(c) - 96 for c in t if c.isalpha()]  # noqa: E731
+    col = C.ASRAudioText(str(man), parser=parser, min_duration=0.5, do_sort_by_duration=True)
+    assert [e.duration for e in col] == [1.0, 2.0, 3.0]
+    assert col[2].audio_file == str(tmp_path / "a.wav") and col[2].text_tokens == [8, 5, 12, 12, 15] and col[2].lang == "en" and col[2].offset == 1.0
+    assert col[1].text_raw == "from file" and col[1].speaker == 7 and col[0].text_tokens == [4, 5] and col[0].text_raw == "norm"
+    idx = C.ASRAudioText(str(man), parser=parser, index_by_file_id=True, max_number=3)
+    assert len(idx) == 3 and idx.mapping["c"] == [2]
+    with pytest.raises(ValueError):
+        C.parse_item(json.dumps({"text": "x", "duration": 1.0}), str(man))
+    assert C.get_full_path("a.wav", str(man)) == str(tmp_path / "a.wav") and C.get_full_path("zz.wav", str(man)) == "zz.wav"
+    assert [e.tokens for e in C.FromFileText(str(tmp_path / "t.txt"), parser)] == [[6, 18, 15, 13, 6, 9, 12, 5]]
+
+    lm = tmp_path / "l.json"
+    lm.write_text("".join(json.dumps(r) + "\n" for r in [{"audio_filepath": "a.wav", "duration": 1.0, "label": "yes"}, {"audio_filepath": "b.wav", "duration": 2.0, "command": "no"},
+                                                       {"audio_filepath": "c.wav", "duration": 9.0, "target": "yes"}]))
+    sl = C.ASRSpeechLabel(str(lm), max_duration=5.0, cal_labels_occurrence=True)
+    assert [e.label for e in sl] == ["yes", "no"] and sl.uniq_labels == ["no", "yes"] and sl.labels_occurrence == {"yes": 2, "no": 1}
+    reg = tmp_path / "r.json"
+    reg.write_text(json.dumps({"audio_filepath": "a.wav", "duration": 1.0, "label": "0.5"}) + "\n")
+    assert C.ASRSpeechLabel(str(reg), is_regression_task=True)[0].label == 0.5
+
+    assert C.FeatureSequenceLabel.relative_speaker_parser("c a c b") == [0, 1, 0, 2]
+    fm = tmp_path / "f.json"
+    fm.write_text(json.dumps({"feature_filepath": "x.npy", "seq_label": "s2 s1 s2", "label": "0 1 1", "duration": 0.3, "text": "ab", "rttm_filepath": "s.rttm"}) + "\n")
+    assert C.ASRFeatureSequenceLabel(str(fm))[0].seq_label == [0, 1, 0]
+    fl = C.ASRFeatureLabel(str(fm), cal_labels_occurrence=True, delimiter=" ")
+    assert fl[0].label == "0 1 1" and fl.labels_occurrence == {"0": 1, "1": 2}
+    ft = C.ASRFeatureText(str(fm), parser=parser)
+    assert ft[0].feature_file == "x.npy" and ft[0].rttm_file == str(tmp_path / "s.rttm") and ft[0].text_tokens == [1, 2]
+
+    dm = tmp_path / "d.json"
+    dm.write_text(json.dumps({"audio_filepath": "/x/s.wav", "duration": 3.0, "rttm_filepath": str(tmp_path / "s.rttm"), "offset": 1.5}) + "\n")
+    tr = C.DiarizationSpeechLabel(str(dm))
+    assert len(tr) == 1 and tr[0].target_spks == (0, 1) and tr[0].sess_spk_dict == {0: "bob", 1: "amy"} and tr[0].rttm_spk_digits == [0, 1]
+    inf = C.DiarizationSpeechLabel(str(dm), clus_label_dict={"s": ["0 1 speaker_0", "1 2 speaker_1", "2 3 speaker_2"]}, pairwise_infer=True)
+    assert [e.target_spks for e in inf] == [(0, 1), (0, 2), (1, 2)] and inf[0].clus_spk_digits == [0, 1, 2]
+    e2e = C.EndtoEndDiarizationSpeechLabel(str(dm))
+    assert e2e[0].uniq_id == "s_1500_3000" and e2e[0].rttm_file == str(tmp_path / "s.rttm")
+
+    am = tmp_path / "au.json"
+    am.write_text(json.dumps({"noisy": "n.wav", "clean": ["c1.wav", "c2.wav"], "extra": "e.wav", "duration": 2.0}) + "\n")
+    ac = C.AudioCollection(str(am), {"input_signal": "noisy", "target_signal": "clean,extra"})
+    assert ac[0].audio_files == {"input_signal": "n.wav", "target_signal": ["c1.wav", "c2.wav", "e.wav"]} and ac[0].offset == 0.0
+    with pytest.raises(KeyError):
+        C.AudioCollection(str(am), {"input_signal": "nope"})
+
+    qm = tmp_path / "q.json"
+    qm.write_text("".join(json.dumps(r) + "\n" for r in [{"audio_filepath": "a.wav", "duration": 1.0, "context": "transcribe", "answer": "hi"},
+                                                       {"audio_filepath": "b.wav", "duration": 2.0, "text": "yo"},
+                                                       {"context": "text only", "context_duration": 0.5, "answer": "ok"}]))
+    q = C.SpeechLLMAudioTextCollection(str(qm))
+    assert [(e.context, e.answer) for e in q] == [("transcribe", "hi"), ("what does this audio mean", "yo"), ("text only", "ok")] and q[2].audio_file is None
+    (tmp_path / "ctx.txt").write_text("describe it\n")
+    assert C.SpeechLLMAudioTextCollection(str(qm), context_file=str(tmp_path / "ctx.txt"), max_num_samples=2)[0].context == "describe it"
