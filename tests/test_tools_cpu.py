@@ -530,3 +530,84 @@ def test_manifest_collections_parse_filter_and_index(tmp_path):
     assert [(e.context, e.answer) for e in q] == [("transcribe", "hi"), ("what does this audio mean", "yo"), ("text only", "ok")] and q[2].audio_file is None
     (tmp_path / "ctx.txt").write_text("describe it\n")
     assert C.SpeechLLMAudioTextCollection(str(qm), context_file=str(tmp_path / "ctx.txt"), max_num_samples=2)[0].context == "describe it"
+
+
+def test_text_adapters_typed_examples_prompt_formats_and_tar_writer(tmp_path):
+    import json
+
+    import numpy as np
+    import torch
+
+    from speech_b200.data import text_adapters as T
+    from speech_b200.data.audio_to_text import save_wav
+    from speech_b200.data.cuts import Cut
+    from speech_b200.prompts import PromptFormatter
+
+    class Tok:
+        bos_id, eos_id, pad_id = 1, 2, 0
+
+        def text_to_ids(self, t):
+            return [3 + (ord(c) % 50) for c in t]
+
+        def token_to_id(self, t):
+            return 60
+
+    prompt = PromptFormatter.resolve("plain")(Tok())
+    (tmp_path / "a.txt").write_text("hello\nworld\n")
+    (tmp_path / "b.txt").write_text("hallo\nwelt\n")
+    (tmp_path / "q.txt").write_text("translate:\n")
+    ex = list(T.LhotseTextAdapter(str(tmp_path / "a.txt"), language="en"))
+    assert [e.text for e in ex] == ["hello", "world"] and ex[0].tokenize(Tok()).num_tokens == 5
+    ex[0].apply_prompt_format(prompt)
+    assert ex[0].input_length == 0 and ex[0].output_length == ex[0].total_length == 6 and bool(ex[0].mask.all())
+    (tmp_path / "j.jsonl").write_text(json.dumps({"content": "abc", "k": 1}) + "\n")
+    je = list(T.LhotseTextJsonlAdapter(str(tmp_path / "j.jsonl"), text_field="content"))
+    assert je[0].text == "abc" and je[0].custom["k"] == 1
+
+    pairs = list(T.LhotseTextPairAdapter(str(tmp_path / "a.txt"), str(tmp_path / "b.txt"), "en", "de", questions_path=str(tmp_path / "q.txt")))
+    assert pairs[1].source.text == "world" and pairs[1].target.text == "welt" and pairs[1].question.text == "translate:" and pairs[1].target.language == "de"
+    pairs[0].apply_prompt_format(prompt)
+    assert pairs[0].output_length >= 5 and pairs[0].input_length >= len("translate: hello") and pairs[0].total_length == pairs[0].input_length + pairs[0].output_length
+    with pytest.raises(ValueError):
+        T.LhotseTextPairAdapter([str(tmp_path / "a.txt"), str(tmp_path / "b.txt")], str(tmp_path / "b.txt"))
+
+    (tmp_path / "sft.jsonl").write_text(json.dumps({"system": "", "mask": "User", "conversations": [{"from": "User", "value": "hi"}, {"from": "Assistant", "value": "yo"}]}) + "\n")
+    sft = list(T.NeMoSFTJsonlAdapter(str(tmp_path / "sft.jsonl")))[0]
+    sft.apply_prompt_format(prompt)
+    assert sft.data["conversations"][1]["value"] == "yo" and int(sft.mask.sum()) == sft.output_length and sft.input_length > 0
+
+    # conversations: write tar shards, read them back ---------------------------------------------------------------
+    rng = np.random.RandomState(0)
+    for n in ("u1", "u2", "u3"):
+        save_wav(str(tmp_path / f"{n}.wav"), (rng.randn(8000) * 0.1).astype(np.float32))
+    convs = [T.NeMoMultimodalConversation(f"c{k}", [T.TextTurn("transcribe", "user"), T.AudioTurn(Cut(n, str(tmp_path / f"{n}.wav"), 0.25, offset=0.1), "user"),
+                                                   T.TextTurn(f"answer {k}", "assistant")], token_equivalent_duration=0.08) for k, n in enumerate(("u1", "u2", "u3"))]
+    assert convs[0].has_audio_turns and convs[0].has_text_turns and not convs[0].is_text_only and len(convs[0].list_cuts()) == 1
+    assert convs[0].to_dict()["conversations"][1] == {"type": "audio", "from": "User", "duration": 0.25, "value": str(tmp_path / "u1.wav"), "offset": 0.1}
+    convs[0].apply_prompt_format(prompt)
+    n_audio = int(np.ceil(0.25 / 0.08)) - 1
+    assert convs[0].total_length == len(convs[0].input_ids) + n_audio and convs[0].input_length == len(convs[0].context_ids) + n_audio
+    assert convs[0].output_length == len(convs[0].answer_ids)
+    out = tmp_path / "shards"
+    with T.NeMoMultimodalConversationTarWriter(str(out), shard_size=2) as w:
+        for c in convs:
+            w.write(c)
+    assert sorted(p.name for p in out.iterdir()) == ["audio_0.tar", "audio_1.tar", "manifest_0.jsonl", "manifest_1.jsonl"] and w.total == 3
+    assert [n for n, _ in T.TarIterator(str(out / "audio_0.tar"))] == ["u1.wav", "u2.wav"]
+    back = list(T.NeMoMultimodalConversationJsonlAdapter(str(out / "manifest__OP_0..1_CL_.jsonl"), tarred_audio_filepaths=str(out / "audio__OP_0..1_CL_.tar"),
+                                                         token_equivalent_duration=0.08))
+    assert [b.id for b in back] == ["c0", "c1", "c2"] and back[2].turns[2].value == "answer 2"
+    a = back[1].turns[1]
+    assert isinstance(a, T.AudioTurn) and a.cut.duration == pytest.approx(0.25) and len(a.cut.load_audio()) == 4000
+    audio, lens, kept = T.collate_conversation_audio_fault_tolerant(back)
+    assert audio.shape == (3, 4000) and len(kept) == 3
+    bad = T.NeMoMultimodalConversation("bad", [T.AudioTurn(Cut("x", str(tmp_path / "missing.wav"), 1.0), "user")])
+    audio, lens, kept = T.collate_conversation_audio_fault_tolerant([bad, back[0]])
+    assert audio.shape == (1, 4000) and [k.id for k in kept] == ["c0"]
+
+    (tmp_path / "sg.jsonl").write_text(json.dumps({"id": "s0", "sound": str(tmp_path / "u1.wav"), "duration": 0.5,
+                                                    "conversations": [{"from": "human", "value": "what is said <sound> here"}, {"from": "gpt", "value": "words"}]}) + "\n")
+    sg = list(T.NeMoMultimodalConversationShareGPTJsonlAdapter(str(tmp_path / "sg.jsonl")))[0]
+    assert [type(t).__name__ for t in sg.turns] == ["TextTurn", "AudioTurn", "TextTurn", "TextTurn"] and sg.turns[3].role == "assistant"
+    ids = T.default_multimodal_conversation_prompt_format_fn(sg, prompt)
+    assert int(ids["mask"].sum()) == len(ids["answer_ids"])
