@@ -16,7 +16,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..core.config import DictConfig, cfg_get
+from ..core.config import DictConfig, cfg_get, to_container
 from ..core.modelpt import ModelPT
 from .audio_codec import Discriminator, HiFiGANDecoder, MelLoss, discriminator_loss, feature_matching_loss, gan_update, generator_adv_loss
 from .magpietts import ForwardSumLoss, beta_binomial_prior
@@ -237,6 +237,12 @@ class FastPitchModel(ModelPT):
         self.forward_sum = ForwardSumLoss()
         n_spk = cfg_get(cfg, "n_speakers", 1)
         self.speaker_emb = nn.Embedding(n_spk, d) if n_spk > 1 else None
+        # optional speaker encoder (look-up table + global style tokens of a reference spectrogram + pre-computed embedding)
+        self.speaker_encoder = None
+        if cfg_get(cfg, "speaker_encoder", None):
+            from .submodules import SpeakerEncoder
+
+            self.speaker_encoder = SpeakerEncoder.from_config(to_container(cfg_get(cfg, "speaker_encoder"), resolve=True), d)
         self.mel = MelLoss(cfg_get(cfg, "sample_rate", 22050), self.n_mel, cfg_get(cfg, "n_fft", 1024), cfg_get(cfg, "hop_length", 256),
                            cfg_get(cfg, "win_length", 1024))
         self.w = {"dur": cfg_get(cfg, "dur_loss_scale", 0.1), "pitch": cfg_get(cfg, "pitch_loss_scale", 0.1), "align": cfg_get(cfg, "align_loss_scale", 1.0)}
@@ -275,11 +281,17 @@ class FastPitchModel(ModelPT):
         f0 = sr / (idx + lo).float()
         return torch.where(peak > 0.3 * ac[..., 0].clamp(min=1e-8), f0, torch.zeros_like(f0))
 
-    def forward(self, text, text_len, mel=None, mel_len=None, pitch=None, speaker=None, pace: float = 1.0):
+    def forward(self, text, text_len, mel=None, mel_len=None, pitch=None, speaker=None, pace: float = 1.0, reference_spec=None, reference_spec_lens=None):
         mask = torch.arange(text.shape[1], device=text.device)[None] < text_len[:, None]
         x = self.embedding(text)
         if self.speaker_emb is not None and speaker is not None:
             x = x + self.speaker_emb(speaker).unsqueeze(1)
+        if self.speaker_encoder is not None:
+            if reference_spec is None and mel is not None and self.speaker_encoder.gst_module is not None:
+                reference_spec, reference_spec_lens = mel, mel_len          # training: the target utterance is its own style reference
+            cond = self.speaker_encoder(batch_size=text.shape[0], speaker=speaker, reference_spec=reference_spec, reference_spec_lens=reference_spec_lens)
+            if cond is not None:
+                x = x + cond.to(x.dtype)
         enc = self.encoder(x, mask)["output"].float()
         log_dur = self.duration_predictor(enc, mask)
         pitch_pred = self.pitch_predictor(enc, mask)
@@ -326,10 +338,10 @@ class FastPitchModel(ModelPT):
         return {"loss": loss}
 
     @torch.no_grad()
-    def generate_spectrogram(self, tokens: torch.Tensor, speaker=None, pace: float = 1.0) -> torch.Tensor:
+    def generate_spectrogram(self, tokens: torch.Tensor, speaker=None, pace: float = 1.0, reference_spec=None, reference_spec_lens=None) -> torch.Tensor:
         self.eval()
         lens = torch.tensor([tokens.shape[1]] * tokens.shape[0], device=tokens.device)
-        return self.forward(tokens, lens, speaker=speaker, pace=pace)["mel"]
+        return self.forward(tokens, lens, speaker=speaker, pace=pace, reference_spec=reference_spec, reference_spec_lens=reference_spec_lens)["mel"]
 
     def parse(self, text: str) -> torch.Tensor:
         return torch.tensor([self.tokenizer.text_to_ids(text)], dtype=torch.long, device=self.device)

@@ -860,3 +860,92 @@ def test_hybrid_decoder_moe_block_routes_by_group_and_matches_dense_evaluation()
         cache = dec.new_cache()
         steps = torch.cat([dec(z[:, t:t + 1], cache) for t in range(6)], dim=1)
     assert torch.allclose(full, steps, atol=1e-4)
+
+
+def test_tts_submodules_masking_conditioning_and_speaker_encoder():
+    import torch
+
+    from speech_b200.tts import submodules as S
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 4, 10)
+    mask = (torch.arange(10)[None, :] < torch.tensor([10, 6])[:, None]).unsqueeze(1).float()
+    norm = S.MaskedInstanceNorm1d(4)
+    y = norm(x, mask)
+    assert torch.allclose(y[1, :, :6].mean(-1), torch.zeros(4), atol=1e-5) and torch.allclose(y[1, :, :6].std(-1), torch.ones(4), atol=1e-4) and float(y[1, :, 6:].abs().sum()) == 0
+    y2 = norm(torch.cat([x[1:, :, :6], torch.full((1, 4, 4), 50.0)], dim=-1), mask[1:])       # padding values do not matter
+    assert torch.allclose(y2[0, :, :6], y[1, :, :6], atol=1e-5)
+
+    pc = S.PartialConv1d(4, 3, 3, padding=1)
+    full = pc(x[1:, :, :6], torch.ones(1, 1, 6))
+    part = pc(x[1:], mask[1:])
+    plain = torch.nn.functional.conv1d(x[1:, :, :6], pc.weight, pc.bias, padding=1)
+    assert torch.allclose(full[..., 1:5], plain[..., 1:5], atol=1e-5)                      # interior windows are an ordinary convolution
+    assert torch.allclose(part[..., :6], full, atol=1e-5) and float(part[..., 7:].abs().sum()) == 0
+    edge = (plain[..., 0] - pc.bias) * 1.5 + pc.bias                                        # 2 of 3 taps valid → scaled by 3/2
+    assert torch.allclose(full[..., 0], edge, atol=1e-5)
+
+    cn = S.ConvNorm(4, 5, 3, use_partial_padding=True, norm_fn=S.MaskedInstanceNorm1d)
+    assert cn(x, mask).shape == (2, 5, 10) and float(cn(x, mask)[1, :, 6:].abs().sum()) == 0
+    with pytest.raises(ValueError):
+        S.ConvNorm(4, 5, 4)
+
+    pre = S.Prenet(6, [8, 8], p_dropout=0.5).eval()
+    a, b = pre(torch.ones(3, 6)), pre(torch.ones(3, 6))
+    assert not torch.equal(a, b)                                                             # dropout stays on in eval mode
+    c = pre(torch.ones(3, 6), inference=True)
+    assert torch.equal(c[0], c[1])                                                            # one mask for the batch
+
+    att = S.Attention(7, 5, 6, 4, 3)
+    mem = torch.randn(2, 9, 5)
+    pad = torch.arange(9)[None, :] >= torch.tensor([9, 4])[:, None]
+    ctx, w = att(torch.randn(2, 7), mem, att.memory_layer(mem), torch.rand(2, 2, 9), pad)
+    assert ctx.shape == (2, 5) and torch.allclose(w.sum(1), torch.ones(2), atol=1e-5) and float(w[1, 4:].sum()) == 0
+
+    cond = torch.randn(2, 1, 3)
+    h = torch.randn(2, 5, 8)
+    cln = S.ConditionalLayerNorm(8, 3, ["layernorm"])
+    assert torch.allclose(cln(h, cond), torch.nn.functional.layer_norm(h, (8,)), atol=1e-6)  # identity at initialisation
+    with pytest.raises(ValueError):
+        cln(h)
+    assert torch.equal(S.ConditionalInput(8, 3, [])(h), h)
+    ci = S.ConditionalInput(8, 3, ["add", "concat"])
+    assert ci(h, cond).shape == h.shape
+    with pytest.raises(ValueError):
+        S.ConditionalInput(8, 3, ["multiply"])
+
+    ref = S.ReferenceEncoder(n_mels=16, cnn_filters=[4, 8], dropout=0.0, gru_hidden=12)
+    mel = torch.randn(2, 16, 20)
+    lens = torch.tensor([20, 11])
+    r = ref(mel, lens)
+    r_short = ref(mel[1:, :, :11], lens[1:])
+    assert r.shape == (2, 12) and torch.allclose(r[1], r_short[0], atol=1e-5)               # padding does not change the summary
+    gst = S.GlobalStyleToken(ref, gst_size=12, n_style_token=5, n_style_attn_head=3)
+    assert gst(mel, lens).shape == (2, 12)
+    enc = S.SpeakerEncoder(S.SpeakerLookupTable(4, 12), gst)
+    both = enc(speaker=torch.tensor([1, 3]), reference_spec=mel, reference_spec_lens=lens)
+    only = enc(speaker=torch.tensor([1, 3]))
+    assert both.shape == (2, 1, 12) and torch.allclose(both - only, gst(mel, lens).unsqueeze(1), atol=1e-5) and enc() is None
+    enc.overwrite_precomputed_emb(torch.arange(12.0))
+    assert torch.equal(enc(batch_size=3)[2, 0], torch.arange(12.0))
+
+
+def test_fastpitch_with_speaker_encoder_conditions_on_reference():
+    import torch
+
+    from speech_b200.core.config import OmegaConf
+    from speech_b200.tts.classic import FastPitchModel
+
+    torch.manual_seed(0)
+    cfg = OmegaConf.create({"n_symbols": 20, "symbols_embedding_dim": 16, "n_mel_channels": 16, "d_inner": 32, "encoder_layers": 1, "decoder_layers": 1, "sample_rate": 8000,
+                            "n_fft": 128, "hop_length": 32, "win_length": 128,
+                            "speaker_encoder": {"lookup_module": {"n_speakers": 3}, "gst_module": {"n_mels": 16, "cnn_filters": [4, 4], "n_style_token": 4, "n_style_attn_head": 2}}})
+    m = FastPitchModel(cfg).eval()
+    toks = torch.randint(1, 20, (1, 7))
+    lens = torch.tensor([7])
+    ref_a, ref_b = torch.randn(1, 16, 30), torch.randn(1, 16, 30)
+    with torch.no_grad():
+        e0 = m.speaker_encoder(batch_size=1, speaker=torch.tensor([0]), reference_spec=ref_a, reference_spec_lens=torch.tensor([30]))
+        e1 = m.speaker_encoder(batch_size=1, speaker=torch.tensor([2]), reference_spec=ref_b, reference_spec_lens=torch.tensor([30]))
+        out = m(toks, lens, speaker=torch.tensor([0]), reference_spec=ref_a, reference_spec_lens=torch.tensor([30]))
+    assert e0.shape == (1, 1, 16) and not torch.allclose(e0, e1) and out["mel"].shape[1] == 16
