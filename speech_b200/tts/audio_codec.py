@@ -16,7 +16,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..core.config import DictConfig, OmegaConf, cfg_get
+from ..core.config import DictConfig, OmegaConf, cfg_get, to_container
 from ..core.modelpt import ModelPT
 
 
@@ -315,11 +315,21 @@ class AudioCodecModel(ModelPT):
         enc = dict(cfg_get(cfg, "audio_encoder", {}) or {})
         dec = dict(cfg_get(cfg, "audio_decoder", {}) or {})
         vq = dict(cfg_get(cfg, "vector_quantizer", {}) or {})
-        for d in (enc, dec, vq):
+        from . import audio_codec_encoders as E
+
+        enc_kind, dec_kind = str(enc.get("_target_", "")).rsplit(".", 1)[-1], str(dec.get("_target_", "")).rsplit(".", 1)[-1]
+        enc = to_container(cfg_get(cfg, "audio_encoder"), resolve=True) if enc_kind in E.ENCODERS else enc
+        for d in (dec, vq):
             d.pop("_target_", None)
-        self.audio_encoder = HiFiGANEncoder(**enc)
+        if enc_kind in E.ENCODERS:                                   # spectral / causal encoders named by class
+            self.audio_encoder = E.build_encoder(enc)
+        else:
+            enc.pop("_target_", None)
+            self.audio_encoder = HiFiGANEncoder(**enc)
         self.vector_quantizer = GroupFiniteScalarQuantizer(**vq) if vq else None
-        if dec.pop("causal", False):
+        if dec_kind in E.DECODERS:
+            self.audio_decoder = E.DECODERS[dec_kind](**{k: (list(v) if hasattr(v, "__iter__") and not isinstance(v, str) else v) for k, v in dec.items()})
+        elif dec.pop("causal", False):
             from .audio_codec_extra import CausalHiFiGANDecoder
 
             self.audio_decoder = CausalHiFiGANDecoder(**dec)

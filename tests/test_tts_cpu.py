@@ -949,3 +949,80 @@ def test_fastpitch_with_speaker_encoder_conditions_on_reference():
         e1 = m.speaker_encoder(batch_size=1, speaker=torch.tensor([2]), reference_spec=ref_b, reference_spec_lens=torch.tensor([30]))
         out = m(toks, lens, speaker=torch.tensor([0]), reference_spec=ref_a, reference_spec_lens=torch.tensor([30]))
     assert e0.shape == (1, 1, 16) and not torch.allclose(e0, e1) and out["mel"].shape[1] == 16
+
+
+def test_codec_spectral_encoders_resnet_decoder_and_codec_model_with_them():
+    import torch
+
+    from speech_b200.core.config import OmegaConf
+    from speech_b200.tts import audio_codec_encoders as E
+    from speech_b200.tts.audio_codec import AudioCodecModel
+
+    torch.manual_seed(0)
+    audio = torch.randn(2, 4096) * 0.1
+    lens = torch.tensor([4096, 3000])
+    audio[1, 3000:] = 0
+
+    act = E.CodecActivation("half_snake", 6)
+    z = torch.randn(1, 6, 5)
+    assert torch.allclose(act(z)[:, :3], z[:, :3] + torch.sin(z[:, :3]).square(), atol=1e-5) and torch.allclose(act(z)[:, 3:], torch.nn.functional.leaky_relu(z[:, 3:], 0.01))
+    pre = E.PreEmphasis(0.5)(torch.tensor([[1.0, 2.0, 4.0]]))
+    assert pre.tolist() == [[0.0, 1.5, 3.0]]
+
+    stft = E.STFTProcessor(256, 256, 64)
+    s, sl = stft(audio, lens)
+    assert s.shape == (2, 129, 64) and sl.tolist() == [64, 46] and float(s[1, :, 46:].abs().sum()) == 0
+    melp = E.MelSpectrogramProcessor(16000, 256, 64, mel_dim=20)
+    m, ml = melp(audio, lens)
+    assert m.shape == (2, 20, 64) and ml.tolist() == [64, 46] and bool((m[0] >= 0).all())     # log(1 + mel) ≥ 0
+
+    with pytest.raises(ValueError):
+        E.MultiBandMelEncoder([(0, 8), (10, 20)], melp, out_channels=4)
+    mb = E.MultiBandMelEncoder([(0, 8), (8, 20)], melp, out_channels=4, num_layers=1, hidden_channels=8, filters=16)
+    enc, el = mb(audio, lens)
+    assert enc.shape == (2, 8, 64) and el.tolist() == [64, 46] and mb.total_stride == 64 and float(enc[1, :, 46:].abs().sum()) == 0
+    fb = E.FullBandMelEncoder(melp, E.ResNetEncoder(20, 6, num_layers=1, hidden_channels=8, filters=16))
+    assert fb(audio, lens)[0].shape == (2, 6, 64)
+
+    with pytest.raises(ValueError):
+        E.MultiResolutionSTFTEncoder(8, [(128, 32, 128), (256, 96, 256)], [8, 8])
+    mr = E.MultiResolutionSTFTEncoder(8, [(128, 32, 128), (256, 64, 256), (512, 128, 512)], [8, 12, 16], down_sample_filter_list=[16], down_sample_rate_list=[2])
+    enc, el = mr(audio, lens)
+    assert mr.total_stride == 256 and enc.shape == (2, 8, 16) and el.tolist() == [16, 11]
+
+    ce = E.CausalHiFiGANEncoder(6, down_sample_rates=(2, 4), base_channels=4, resblock_kernel_sizes=(3,), resblock_dilation_sizes=(1, 2))
+    a, al = ce(audio[:1, :512], torch.tensor([512]))
+    a2, _ = ce(torch.cat([audio[:1, :256], torch.randn(1, 256)], dim=1), torch.tensor([512]))
+    assert a.shape == (1, 6, 64) and torch.allclose(a[..., :32], a2[..., :32], atol=1e-5)        # no look-ahead
+
+    dec = E.ResNetDecoder(8, 12, [2], [10], 2, 16, [4, 2], [8, 4], resblock_up_sample_kernel_size=5)
+    y, yl = dec(torch.randn(2, 8, 10), torch.tensor([10, 7]))
+    assert dec.total_stride == 16 and y.shape == (2, 160) and yl.tolist() == [160, 112] and float(y[1, 112:].abs().sum()) == 0 and float(y.abs().max()) <= 1
+    cdec = E.ResNetDecoder(8, 12, [2], [10], 1, 16, [4], [6], is_causal=True).eval()
+    x = torch.randn(1, 8, 12)
+    x2 = torch.cat([x[..., :6], torch.randn(1, 8, 6)], dim=-1)
+    with torch.no_grad():
+        y1, _ = cdec(x, torch.tensor([12]))
+        y2, _ = cdec(x2, torch.tensor([12]))
+    assert torch.allclose(y1[:, :48], y2[:, :48], atol=1e-5) and not torch.allclose(y1[:, 48:], y2[:, 48:])
+    mr.post_conv.remove_weight_norm()
+    assert not torch.nn.utils.parametrize.is_parametrized(mr.post_conv.conv)
+
+    mpd = E.MultiPeriodDiscriminator((2, 3))
+    sr, sg, fr, fg = mpd(audio[:, :600], audio[:, :600] * 0.5)
+    assert len(sr) == len(sg) == 2 and len(fr[0]) == len(fg[0])
+
+    cfg = OmegaConf.create({"sample_rate": 16000, "train_discriminator": False, "mel_loss": {"n_mels": 16, "n_fft": 256, "hop": 64, "win": 256},
+                            "audio_encoder": {"_target_": "speech_b200.tts.audio_codec_encoders.MultiBandMelEncoder", "mel_bands": [[0, 8], [8, 16]], "out_channels": 4,
+                                              "num_layers": 1, "hidden_channels": 8, "filters": 8,
+                                              "mel_processor": {"sample_rate": 16000, "win_length": 256, "hop_length": 64, "mel_dim": 16}},
+                            "vector_quantizer": {"num_groups": 2, "num_levels_per_group": [4, 4, 4, 4]},
+                            "audio_decoder": {"_target_": "speech_b200.tts.audio_codec_encoders.ResNetDecoder", "input_dim": 8, "input_filters": 8, "pre_up_sample_rates": [2],
+                                              "pre_up_sample_filters": [8], "n_hidden_layers": 1, "hidden_filters": 8, "resblock_up_sample_rates": [8, 4],
+                                              "resblock_up_sample_filters": [6, 4]}})
+    model = AudioCodecModel(cfg).eval()
+    assert model.samples_per_frame == 64
+    with torch.no_grad():
+        toks, tl = model.encode(audio, lens)
+        rec, rl = model.decode(toks, tl)
+    assert toks.shape == (2, 2, 64) and tl.tolist() == [64, 46] and rec.shape == (2, 4096) and rl.tolist() == [4096, 2944]
