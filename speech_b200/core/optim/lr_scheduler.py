@@ -370,6 +370,10 @@ def register_scheduler(name: str, scheduler, scheduler_params=None):
     if name in AVAILABLE_SCHEDULERS:
         raise ValueError(f"Cannot register duplicate scheduler ({name})")
     AVAILABLE_SCHEDULERS[name] = scheduler
+    if scheduler_params is not None:                               # the typed record of its arguments, looked up as "<class name>Params"
+        from ..config_schemas import register_scheduler_params
+
+        register_scheduler_params(f"{scheduler.__name__}Params", scheduler_params)
 
 
 def get_scheduler(name: str, **kwargs):

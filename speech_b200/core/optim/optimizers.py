@@ -276,6 +276,10 @@ def register_optimizer(name: str, optimizer, optimizer_params=None):
     if name in AVAILABLE_OPTIMIZERS:
         raise ValueError(f"Cannot register duplicate optimizer ({name})")
     AVAILABLE_OPTIMIZERS[name] = optimizer
+    if optimizer_params is not None:                               # the typed record of its arguments, looked up as "<name>_params"
+        from ..config_schemas import register_optimizer_params
+
+        register_optimizer_params(f"{name}_params", optimizer_params)
 
 
 def parse_optimizer_args(optimizer_name: str, optimizer_kwargs: Any) -> Dict[str, Any]:

@@ -478,3 +478,67 @@ def test_common_losses_datasets_and_metrics():
     assert ppl.compute() == pytest.approx((4 + 4 + 1) / 3, rel=1e-4)
     with pytest.raises(ValueError):
         Perplexity().update(probs=torch.full((1, 4), 0.3))
+
+
+def test_optimizer_and_scheduler_param_records_and_config_builder():
+    from dataclasses import dataclass
+
+    import torch
+
+    from speech_b200.core import config_schemas as S
+    from speech_b200.core.optim.lr_scheduler import get_scheduler, register_scheduler
+    from speech_b200.core.optim.optimizers import get_optimizer, register_optimizer
+
+    cos = S.get_scheduler_config("CosineAnnealingParams", min_lr=1e-5)(max_steps=100, warmup_steps=10)
+    assert cos.min_lr == 1e-5 and cos.max_steps == 100 and cos.last_epoch == -1
+    w = torch.nn.Parameter(torch.zeros(2))
+    opt = get_optimizer("novograd", **S.params_to_dict(S.get_optimizer_config("novograd", lr=0.1, weight_decay=0.01)))([w])
+    assert opt.defaults["lr"] == 0.1 and tuple(opt.defaults["betas"]) == (0.95, 0.98)
+    sched = get_scheduler("CosineAnnealing", **S.params_to_dict(cos))(opt)
+    lrs = []
+    for _ in range(12):
+        opt.step(); sched.step(); lrs.append(sched.get_last_lr()[0])
+    assert max(lrs) <= 0.1 + 1e-9 and lrs[0] < lrs[5] < lrs[9]
+    assert "lr" not in S.params_to_dict(S.AdamParams()) and S.params_to_dict(S.AdamParams(lr=1.0))["betas"] == [0.9, 0.999]
+    with pytest.raises(ValueError):
+        S.get_scheduler_config("NopeParams")
+    with pytest.raises(ValueError):
+        S.get_optimizer_config("nope")
+    assert S.get_optimizer_config(None, lr=1) == {"lr": 1}
+
+    @dataclass
+    class MySchedParams(S.SchedulerParams):
+        k: int = 3
+
+    class MySched(torch.optim.lr_scheduler.LRScheduler):
+        def __init__(self, optimizer, k=3, last_epoch=-1):
+            self.k = k
+            super().__init__(optimizer, last_epoch)
+
+        def get_lr(self):
+            return [b / self.k for b in self.base_lrs]
+
+    register_scheduler("MySchedForTest", MySched, MySchedParams)
+    assert S.get_scheduler_config("MySchedParams", k=5)().k == 5
+    with pytest.raises(ValueError):
+        register_scheduler("MySchedForTest", MySched, MySchedParams)
+
+    @dataclass
+    class MyOptParams(S.OptimizerParams):
+        momentum: float = 0.5
+
+    register_optimizer("my_sgd_for_test", torch.optim.SGD, MyOptParams)
+    assert S.params_to_dict(S.get_optimizer_config("my_sgd_for_test", lr=0.2)) == {"lr": 0.2, "momentum": 0.5}
+
+    class Builder(S.ModelConfigBuilder):
+        def _finalize_cfg(self):
+            if self.model_cfg.train_ds is not None and self.model_cfg.validation_ds is None:
+                self.model_cfg.validation_ds = S.DatasetConfig(batch_size=self.model_cfg.train_ds.batch_size, shuffle=False)
+
+    b = Builder(S.ModelConfig())
+    b.set_train_ds(S.DatasetConfig(batch_size=8, shuffle=True))
+    b.set_optim(S.NovogradParams(lr=0.05), S.SchedConfig(name="CosineAnnealing", min_lr=1e-6))
+    cfg = b.build()
+    assert cfg.validation_ds.batch_size == 8 and cfg.optim.name == "novograd" and cfg.optim.lr == 0.05 and cfg.optim.sched.name == "CosineAnnealing"
+    top = S.to_dictconfig(S.NemoConfig(name="exp", model=cfg))
+    assert top.model.optim.sched.min_lr == 1e-6 and top.trainer.strategy == "ddp" and top.model.train_ds.shuffle is True and list(top.model.optim.betas) == [0.95, 0.98]
