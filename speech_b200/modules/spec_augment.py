@@ -99,3 +99,84 @@ class SpectrogramAugmentation(NeuralModule):
         if self.spec_augment is not None:
             x = self.spec_augment(x, length)
         return x
+
+
+class MaskedPatchAugmentation(NeuralModule):
+    """Zeroes whole time patches of ``patch_size`` frames.  ``mask_patches >= 1`` is a patch count, ``< 1`` the fraction of the shortest
+    utterance's frames to cover (rounded up to whole patches); every utterance of the batch loses the same number of patches, drawn
+    without replacement among the patches that lie inside its own length.  The choice is made for the whole batch at once (random scores
+    per patch, the lowest-scoring valid ones are masked), so no host loop runs over the batch.  Optional frequency masks follow.
+    Reference: ``asr/modules/audio_preprocessing.py`` ``MaskedPatchAugmentation``."""
+
+    def __init__(self, patch_size: int = 48, mask_patches: float = 10.0, freq_masks: int = 0, freq_width: int = 0):
+        super().__init__()
+        if mask_patches < 0:
+            raise ValueError("mask_patches cannot be negative")
+        self.patch_size = int(patch_size)
+        self.mask_patches = int(mask_patches) if mask_patches >= 1 else None
+        self._mask_fraction = float(mask_patches) if mask_patches < 1 else None
+        self.spec_augment = SpecAugment(freq_masks, 0, freq_width, 0) if freq_masks > 0 else None
+
+    @property
+    def input_types(self):
+        return {"input_spec": NeuralType(("B", "D", "T"), SpectrogramType()), "length": NeuralType(("B",), LengthsType())}
+
+    @property
+    def output_types(self):
+        return {"augmented_spec": NeuralType(("B", "D", "T"), SpectrogramType())}
+
+    @typecheck()
+    def forward(self, input_spec, length):
+        B, _, T = input_spec.shape
+        P = self.patch_size
+        min_len = int(length.min())
+        if self.mask_patches is None:
+            cover = int(min_len * self._mask_fraction)
+            n = -(-cover // P)
+        else:
+            n = self.mask_patches
+        n = min(n, min_len // P)
+        x = input_spec
+        if n > 0:
+            n_patches = -(-T // P)
+            valid = torch.arange(n_patches, device=x.device)[None, :] < (length // P)[:, None]          # patches fully inside the utterance
+            score = torch.rand(B, n_patches, device=x.device).masked_fill(~valid, 2.0)
+            chosen = torch.zeros(B, n_patches, dtype=torch.bool, device=x.device).scatter_(1, score.topk(n, dim=1, largest=False)[1], True) & valid
+            x = x.masked_fill(chosen.repeat_interleave(P, dim=1)[:, None, :T], 0.0)
+        if self.spec_augment is not None:
+            x = self.spec_augment(x, length)
+        return x
+
+
+class CropOrPadSpectrogramAugmentation(NeuralModule):
+    """Every spectrogram of the batch gets exactly ``audio_length`` frames: longer inputs are cropped at a random offset per utterance,
+    shorter ones zero-padded on both sides (the extra frame of an odd difference goes to the right).  All returned lengths equal
+    ``audio_length``.  Reference: ``asr/modules/audio_preprocessing.py`` ``CropOrPadSpectrogramAugmentation``."""
+
+    def __init__(self, audio_length: int):
+        super().__init__()
+        if audio_length < 0:
+            raise ValueError("audio_length must be non-negative")
+        self.audio_length = int(audio_length)
+
+    @property
+    def input_types(self):
+        return {"input_signal": NeuralType(("B", "D", "T"), SpectrogramType()), "length": NeuralType(("B",), LengthsType())}
+
+    @property
+    def output_types(self):
+        return {"processed_signal": NeuralType(("B", "D", "T"), SpectrogramType()), "processed_length": NeuralType(("B",), LengthsType())}
+
+    @typecheck()
+    @torch.no_grad()
+    def forward(self, input_signal, length):
+        B, _, T = input_signal.shape
+        L = self.audio_length
+        if T > L:
+            off = torch.randint(0, T - L + 1, (B,), device=input_signal.device)
+            idx = off[:, None] + torch.arange(L, device=input_signal.device)[None, :]
+            out = torch.gather(input_signal, 2, idx[:, None, :].expand(-1, input_signal.shape[1], -1))
+        else:
+            left = (L - T) // 2
+            out = torch.nn.functional.pad(input_signal, (left, L - T - left))
+        return out, torch.full_like(length, L)

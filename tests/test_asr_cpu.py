@@ -396,3 +396,47 @@ def test_transcribe_long_audio_in_chunks_merges_tokens_and_frame_indices():
     assert chunked[1].text == m.transcribe([short], batch_size=1)[0]
     texts = m.transcribe([long_audio], batch_size=2, chunk_duration_seconds=1.0)
     assert isinstance(texts[0], str)
+
+
+def test_masked_patch_and_crop_or_pad_augmentations_and_front_end_config_records():
+    import torch
+
+    from speech_b200.core.config_schemas import to_dictconfig
+    from speech_b200.core.instantiate import instantiate
+    from speech_b200.modules import configs as C
+    from speech_b200.modules.spec_augment import CropOrPadSpectrogramAugmentation, MaskedPatchAugmentation
+
+    torch.manual_seed(0)
+    x = torch.ones(3, 4, 50)
+    lens = torch.tensor([50, 33, 20])
+    y = MaskedPatchAugmentation(patch_size=5, mask_patches=3)(input_spec=x.clone(), length=lens)
+    zero = (y == 0).all(1)
+    assert zero.sum(1).tolist() == [15, 15, 15]                                        # the same amount masked in every utterance
+    for b in range(3):
+        cols = zero[b].nonzero().flatten()
+        assert int(cols.max()) < int(lens[b]) // 5 * 5 and all(int(zero[b, s:s + 5].sum()) in (0, 5) for s in range(0, 50, 5))   # whole patches, inside the length
+    frac = MaskedPatchAugmentation(patch_size=5, mask_patches=0.3)(input_spec=x.clone(), length=lens)
+    assert (frac == 0).all(1).sum(1).tolist() == [10, 10, 10]                          # 30 % of the shortest (20) = 6 frames → 2 patches
+    many = MaskedPatchAugmentation(patch_size=5, mask_patches=9)(input_spec=x.clone(), length=lens)
+    assert (many == 0).all(1).sum(1).tolist() == [20, 20, 20]                          # capped by the shortest utterance
+    fm = MaskedPatchAugmentation(patch_size=5, mask_patches=1, freq_masks=1, freq_width=2)(input_spec=x.clone(), length=lens)
+    assert fm.shape == x.shape
+    with pytest.raises(ValueError):
+        MaskedPatchAugmentation(mask_patches=-1)
+
+    ramp = torch.arange(50.0).expand(2, 3, 50).contiguous()
+    crop, cl = CropOrPadSpectrogramAugmentation(20)(input_signal=ramp, length=torch.tensor([50, 40]))
+    assert crop.shape == (2, 3, 20) and cl.tolist() == [20, 20] and bool((crop[:, :, 1:] - crop[:, :, :-1] == 1).all())
+    pad, pl = CropOrPadSpectrogramAugmentation(55)(input_signal=ramp + 1, length=torch.tensor([50, 40]))
+    assert pad.shape == (2, 3, 55) and pl.tolist() == [55, 55] and float(pad[0, 0, :2].sum()) == 0 and float(pad[0, 0, 2]) == 1 and float(pad[0, 0, 52:].sum()) == 0
+
+    pre = instantiate(to_dictconfig(C.AudioToMelSpectrogramPreprocessorConfig(features=32, dither=0.0)))
+    feats, fl = pre(input_signal=torch.randn(2, 3200), length=torch.tensor([3200, 1600]))
+    assert feats.shape[1] == 32 and fl.tolist() == [20, 10]
+    aug = instantiate(to_dictconfig(C.MaskedPatchAugmentationConfig(patch_size=4, mask_patches=2)))
+    assert isinstance(aug, MaskedPatchAugmentation) and aug.patch_size == 4
+    assert instantiate(to_dictconfig(C.CropOrPadSpectrogramAugmentationConfig(audio_length=16))).audio_length == 16
+    mfcc = instantiate(to_dictconfig(C.AudioToMFCCPreprocessorConfig(n_mfcc=13, n_mels=24)))
+    assert mfcc(input_signal=torch.randn(1, 3200), length=torch.tensor([3200]))[0].shape[1] == 13
+    sa = instantiate(to_dictconfig(C.SpectrogramAugmentationConfig(freq_masks=1, freq_width=3)))
+    assert sa(input_spec=torch.ones(1, 8, 10), length=torch.tensor([10])).shape == (1, 8, 10)
