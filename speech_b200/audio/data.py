@@ -79,6 +79,10 @@ class SyntheticNoisyDataset(Dataset):
 def build_audio_to_target_dataloader(config, rank: int = 0, world_size: int = 1):
     get = config.get if hasattr(config, "get") else (lambda k, d=None: getattr(config, k, d))
     syn = get("synthetic", None)
+    if syn is None and any(get(k, None) is not None for k in ("input_channel_selector", "target_channel_selector", "normalization_signal", "reference_key", "embedding_key")):
+        from .data_extra import get_audio_dataset_from_config          # multi-file signals, channel selection, peak normalisation, reference / embedding
+
+        return get_dataloader_from_config(config, get_audio_dataset_from_config(config), rank, world_size)
     ds = SyntheticNoisyDataset(**dict(syn)) if syn is not None else AudioToTargetDataset(
         get("manifest_filepath"), get("sample_rate", 16000), get("input_key", "input_filepath"), get("target_key", "target_filepath"),
         get("audio_duration", None), get("random_offset", False))

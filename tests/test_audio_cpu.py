@@ -387,3 +387,66 @@ def test_audio_losses_and_time_domain_denoiser():
     assert torch.isfinite(loss) and m.seasr.analysis.weight.grad.abs().sum() > 0
     with pytest.raises(ValueError):
         BNR2(OmegaConf.create({"sample_rate": 8000}))
+
+
+def test_multi_signal_audio_datasets_sync_async_embedding_and_channel_selection(tmp_path):
+    import json
+
+    import numpy as np
+    import torch
+
+    from speech_b200.audio import data_extra as D
+    from speech_b200.data.audio_to_text import save_wav
+
+    sr = 8000
+    t = np.arange(sr * 2) / sr
+    clean = (0.5 * np.sin(2 * np.pi * 5 * t)).astype(np.float32)               # slow sine: sample index is recoverable from the phase
+    noisy2 = np.stack([clean * 0.5, -clean * 0.5], axis=1).astype(np.float32)  # two channels
+    from scipy.io import wavfile
+
+    wavfile.write(str(tmp_path / "noisy.wav"), sr, noisy2)
+    save_wav(str(tmp_path / "clean.wav"), clean, sr)
+    save_wav(str(tmp_path / "extra.wav"), clean * 0.25, sr)
+    save_wav(str(tmp_path / "ref.wav"), np.linspace(-0.5, 0.5, sr * 3).astype(np.float32), sr)
+    np.save(tmp_path / "emb.npy", np.arange(6, dtype=np.float32))
+    man = tmp_path / "m.json"
+    rows = [{"noisy": "noisy.wav", "clean": "clean.wav", "both": ["clean.wav", "extra.wav"], "ref": "ref.wav", "emb": "emb.npy", "duration": 2.0},
+            {"noisy": "noisy.wav", "clean": "clean.wav", "both": ["clean.wav", "extra.wav"], "ref": "ref.wav", "emb": "emb.npy", "duration": 2.0, "offset": 0.5}]
+    man.write_text("".join(json.dumps(r) + "\n" for r in rows))
+
+    ds = D.AudioToTargetDataset(str(man), sr, "noisy", "clean")
+    ex = ds[0]
+    assert ex["input_signal"].shape == (2, 2 * sr) and ex["target_signal"].shape == (1, 2 * sr) and ds.num_channels("input_signal") == 2
+    assert torch.allclose(ex["input_signal"][0] * 2, ex["target_signal"][0], atol=1e-3)
+    sel = D.AudioToTargetDataset(str(man), sr, "noisy", "both", input_channel_selector=1, target_channel_selector="average", normalization_signal="input_signal")[0]
+    assert sel["input_signal"].shape == (1, 2 * sr) and float(sel["input_signal"].abs().max()) == pytest.approx(1.0, abs=1e-3)
+    assert torch.allclose(sel["target_signal"][0], -sel["input_signal"][0] * (0.625 / 0.5), atol=1e-2)           # mean of (1, 0.25) × clean vs −0.5 × clean, same scale
+
+    rnd = D.AudioToTargetDataset(str(man), sr, "noisy", "clean", audio_duration=0.5, random_offset=True, seed=3)
+    a, b = rnd[0], rnd[0]
+    assert a["input_signal"].shape == (2, sr // 2) and torch.allclose(a["input_signal"][0] * 2, a["target_signal"][0], atol=1e-3)     # input and target stay aligned
+    assert not torch.equal(a["target_signal"], b["target_signal"])                                                                 # a new segment each time
+    fixed = D.AudioToTargetDataset(str(man), sr, "noisy", "clean", audio_duration=0.25)[1]
+    assert torch.allclose(fixed["target_signal"][0], torch.from_numpy(clean[sr // 2: sr // 2 + sr // 4]), atol=1e-3)                # the manifest offset
+
+    batch = ds.collate_fn([ds[0], rnd[0]])
+    assert batch.input_signal.shape == (2, 2, 2 * sr) and batch.input_length.tolist() == [2 * sr, sr // 2] and batch.target_signal.shape == (2, 1, 2 * sr)
+
+    ref = D.AudioToTargetWithReferenceDataset(str(man), sr, "noisy", "clean", "ref", reference_is_synchronized=False, reference_duration=1.0, seed=1)
+    r = ref[0]
+    assert r["reference_signal"].shape == (1, sr) and r["input_signal"].shape == (2, 2 * sr)
+    ramp = r["reference_signal"][0]
+    assert float(ramp[1000] - ramp[0]) == pytest.approx(1000.0 / (3 * sr), rel=0.01) and float(ramp[0]) > -0.5                            # a random stretch of the ramp
+    rb = ref.collate_fn([ref[0], ref[1]])
+    assert rb.reference_signal.shape == (2, 1, sr) and rb.reference_length.tolist() == [sr, sr]
+    sync = D.get_audio_dataset_from_config({"manifest_filepath": str(man), "sample_rate": sr, "input_key": "noisy", "target_key": "clean", "reference_key": "clean",
+                                            "audio_duration": 0.5, "random_offset": True})
+    s0 = sync[0]
+    assert isinstance(sync, D.AudioToTargetWithReferenceDataset) and torch.equal(s0["reference_signal"], s0["target_signal"])
+
+    emb = D.get_audio_dataset_from_config({"manifest_filepath": str(man), "sample_rate": sr, "input_key": "noisy", "target_key": "clean", "embedding_key": "emb"})
+    eb = emb.collate_fn([emb[0], emb[1]])
+    assert eb.embedding_vector.shape == (2, 6) and eb.embedding_length.tolist() == [6, 6] and eb.embedding_vector[0].tolist() == [0, 1, 2, 3, 4, 5]
+    assert D.get_audio_dataset_from_config({"manifest_filepath": None}) is None
+    with pytest.raises(RuntimeError):
+        D.ASRAudioProcessor.list_to_multichannel([np.zeros((10, 1)), np.zeros((12, 1))])
