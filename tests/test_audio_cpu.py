@@ -450,3 +450,51 @@ def test_multi_signal_audio_datasets_sync_async_embedding_and_channel_selection(
     assert D.get_audio_dataset_from_config({"manifest_filepath": None}) is None
     with pytest.raises(RuntimeError):
         D.ASRAudioProcessor.list_to_multichannel([np.zeros((10, 1)), np.zeros((12, 1))])
+
+
+def test_audio_transforms_spectrogram_mel_db_mfcc_resample():
+    import math
+
+    import numpy as np
+    import torch
+    from scipy.signal import resample_poly
+
+    from speech_b200.audio import transforms as T
+
+    torch.manual_seed(0)
+    sr = 16000
+    t = torch.arange(sr) / sr
+    x = torch.sin(2 * math.pi * 1000 * t)[None, :]
+    spec = T.Spectrogram(n_fft=512, hop_length=128)(x)
+    assert spec.shape == (1, 257, 126) and int(spec[0, :, 60].argmax()) == 32                        # 1 kHz → bin 1000 / (16000 / 512)
+    cplx = T.Spectrogram(n_fft=512, hop_length=128, power=None)(x)
+    assert cplx.is_complex() and torch.allclose(cplx.abs() ** 2, spec, rtol=1e-4, atol=1e-3)
+    fb = T.melscale_fbanks(257, 0.0, 8000.0, 40, sr)
+    assert fb.shape == (257, 40) and bool((fb >= 0).all()) and bool((fb.sum(0) > 0).all())
+    peaks = fb.argmax(0)
+    assert bool((peaks[1:] > peaks[:-1]).all())                                                        # centre frequencies increase
+    slaney = T.melscale_fbanks(257, 0.0, 8000.0, 40, sr, norm="slaney", mel_scale="slaney")
+    assert float(slaney[:, 0].max()) > float(slaney[:, -1].max())                                      # unit area: narrow low filters are taller
+    mel = T.MelSpectrogram(sr, n_fft=512, hop_length=128, n_mels=40)(x)
+    assert mel.shape == (1, 40, 126) and torch.allclose(mel, T.MelScale(40, sr, n_stft=257)(spec), atol=1e-4)
+    db = T.AmplitudeToDB("power", top_db=60.0)(mel)
+    assert float(db.max() - db.min()) <= 60.0 + 1e-4 and float(db.max()) == pytest.approx(10 * math.log10(float(mel.max())), abs=1e-3)
+    assert torch.allclose(T.AmplitudeToDB("magnitude")(torch.tensor([[10.0, 1.0]])), torch.tensor([[20.0, 0.0]]))
+    dct = T.create_dct(13, 40)
+    assert torch.allclose(dct.t() @ dct, torch.eye(13), atol=1e-5)                                     # orthonormal rows
+    mf = T.MFCC(sr, n_mfcc=13, melkwargs={"n_fft": 512, "hop_length": 128, "n_mels": 40})(x)
+    assert mf.shape == (1, 13, 126)
+    with pytest.raises(ValueError):
+        T.MFCC(sr, n_mfcc=50, melkwargs={"n_mels": 40})
+
+    sig = torch.sin(2 * math.pi * 440 * t) + 0.5 * torch.sin(2 * math.pi * 3000 * t)
+    down = T.Resample(16000, 8000)(sig[None])
+    ref = resample_poly(sig.numpy().astype(np.float64), 1, 2)
+    assert down.shape == (1, 8000) and float((down[0, 200:-200] - torch.from_numpy(ref[200:-200]).float()).abs().max()) < 0.02
+    sharp_down = T.Resample(16000, 8000, lowpass_filter_width=64)(sig[None])
+    up = T.Resample(8000, 16000, resampling_method="sinc_interp_kaiser", lowpass_filter_width=64)(sharp_down)
+    assert up.shape == (1, 16000) and float((up[0, 400:-400] - sig[400:-400]).abs().max()) < 0.03    # both tones are below 4 kHz: with sharp filters the round trip is near-lossless
+    odd = T.Resample(16000, 22050)(sig[None, :1600])
+    assert odd.shape == (1, 2205) and T.Resample(16000, 16000)(sig[None]) is not None
+    batch = T.Resample(16000, 8000)(torch.stack([sig, -sig]).reshape(2, 1, -1))
+    assert batch.shape == (2, 1, 8000) and torch.allclose(batch[0], -batch[1], atol=1e-6)
