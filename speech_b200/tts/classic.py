@@ -18,6 +18,7 @@ import torch.nn.functional as F
 
 from ..core.config import DictConfig, cfg_get, to_container
 from ..core.modelpt import ModelPT
+from .base import SpectrogramGenerator, Vocoder
 from .audio_codec import Discriminator, HiFiGANDecoder, MelLoss, discriminator_loss, feature_matching_loss, gan_update, generator_adv_loss
 from .magpietts import ForwardSumLoss, beta_binomial_prior
 from .transformer_2501 import Transformer
@@ -215,11 +216,12 @@ class TemporalPredictor(nn.Module):
         return self.fc(h).squeeze(-1) * mask
 
 
-class FastPitchModel(ModelPT):
+class FastPitchModel(SpectrogramGenerator):
     def __init__(self, cfg: DictConfig, trainer=None, tokenizer=None):
         super().__init__(cfg=cfg, trainer=trainer)
         cfg = self._cfg
         self.tokenizer = tokenizer if tokenizer is not None else build_text_tokenizer(cfg_get(cfg, "text_tokenizer", None))
+        self._setup_normalizer(cfg)
         # the datasets append <bos> / <eos> as vocab_size and vocab_size + 1
         n_sym = cfg_get(cfg, "n_symbols", None) or (self.tokenizer.vocab_size + 2 if self.tokenizer is not None else 128)
         d = cfg_get(cfg, "symbols_embedding_dim", 384)
@@ -343,11 +345,13 @@ class FastPitchModel(ModelPT):
         lens = torch.tensor([tokens.shape[1]] * tokens.shape[0], device=tokens.device)
         return self.forward(tokens, lens, speaker=speaker, pace=pace, reference_spec=reference_spec, reference_spec_lens=reference_spec_lens)["mel"]
 
-    def parse(self, text: str) -> torch.Tensor:
+    def parse(self, text: str, normalize: bool = True, **kwargs) -> torch.Tensor:
+        if normalize:
+            text = self.normalize_text(text)
         return torch.tensor([self.tokenizer.text_to_ids(text)], dtype=torch.long, device=self.device)
 
 
-class HifiGanModel(ModelPT):
+class HifiGanModel(Vocoder):
     """Vocoder: mel spectrogram → waveform (generator = ``HiFiGANDecoder``; multi-period + STFT discriminators)."""
 
     def __init__(self, cfg: DictConfig, trainer=None):
@@ -386,7 +390,8 @@ class HifiGanModel(ModelPT):
         lens = torch.full((spec.shape[0],), spec.shape[2], device=spec.device, dtype=torch.long)
         return self.generator(spec, lens)[0]
 
-    convert_spectrogram_to_audio = forward
+    def convert_spectrogram_to_audio(self, spec: torch.Tensor, **kwargs) -> torch.Tensor:
+        return self.forward(spec)
 
     def configure_optimizers(self):
         lr = cfg_get(cfg_get(self._cfg, "optim", {}), "lr", 2e-4)

@@ -1026,3 +1026,40 @@ def test_codec_spectral_encoders_resnet_decoder_and_codec_model_with_them():
         toks, tl = model.encode(audio, lens)
         rec, rl = model.decode(toks, tl)
     assert toks.shape == (2, 2, 64) and tl.tolist() == [64, 46] and rec.shape == (2, 4096) and rl.tolist() == [4096, 2944]
+
+
+def test_tts_base_kinds_text_normaliser_hook_and_griffin_lim_vocoder():
+    import math
+
+    import numpy as np
+    import torch
+
+    from speech_b200.core.config import OmegaConf
+    from speech_b200.modules.preprocessor import mel_filterbank
+    from speech_b200.tts.base import GriffinLimVocoder, SpectrogramGenerator, Vocoder
+    from speech_b200.tts.classic import FastPitchModel, HifiGanModel
+
+    assert issubclass(FastPitchModel, SpectrogramGenerator) and issubclass(HifiGanModel, Vocoder)
+    with pytest.raises(TypeError):
+        SpectrogramGenerator(OmegaConf.create({}))                                          # abstract: parse / generate_spectrogram missing
+    cfg = OmegaConf.create({"n_symbols": 40, "symbols_embedding_dim": 16, "n_mel_channels": 16, "d_inner": 32, "encoder_layers": 1, "decoder_layers": 1,
+                            "sample_rate": 8000, "n_fft": 128, "hop_length": 32, "win_length": 128})
+    m = FastPitchModel(cfg, tokenizer=type("Tok", (), {"text_to_ids": staticmethod(lambda t: [1 + (ord(c) % 30) for c in t])})())
+    raw = m.parse("ab 12")
+    m.text_normalizer_call = lambda t, verbose=False: t.replace("12", "twelve")
+    m.text_normalizer_call_kwargs = {"verbose": False}
+    assert m.parse("ab 12").shape[1] == raw.shape[1] + 4 and m.parse("ab 12", normalize=False).shape == raw.shape
+
+    sr, n_fft, hop = 8000, 512, 128
+    t = torch.arange(sr) / sr
+    x = 0.5 * torch.sin(2 * math.pi * 440 * t)
+    win = torch.hann_window(n_fft)
+    mag = torch.stft(x, n_fft, hop, n_fft, win, return_complex=True).abs()
+    fb = torch.as_tensor(np.asarray(mel_filterbank(sr, n_fft, 64, 0.0, None)), dtype=torch.float32)
+    logmel = torch.log(torch.matmul(fb, mag).clamp(min=1e-5))[None]
+    voc = GriffinLimVocoder(sr, n_fft, hop, n_mels=64, n_iters=16)
+    y = voc.convert_spectrogram_to_audio(logmel)
+    assert y.shape[0] == 1 and abs(y.shape[1] - sr) <= hop
+    spec_y = torch.stft(y[0], n_fft, hop, n_fft, win, return_complex=True).abs().mean(-1)
+    assert abs(int(spec_y.argmax()) - round(440 / (sr / n_fft))) <= 1                      # the tone survives the mel → waveform inversion
+    assert float(y[0, 1000:-1000].pow(2).mean().sqrt()) == pytest.approx(0.5 / math.sqrt(2), rel=0.3)
