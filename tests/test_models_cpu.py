@@ -402,3 +402,46 @@ def test_offline_diarization_with_asr_assignment_realignment_outputs_and_scores(
     assert list(D.audio_rttm_map(str(man), attach_dur=True)) == ["x_0_3000", "x_3000_3000"]
     with pytest.raises(KeyError):
         D.audio_rttm_map(str(man))
+
+
+def test_model_config_records_diarizer_preset_and_matchboxnet_builder():
+    import torch
+
+    from speech_b200.core.config_schemas import to_dictconfig
+    from speech_b200.models import config_records as R
+    from speech_b200.models.classification_models import EncDecClassificationModel
+    from speech_b200.models.diarizers import ClusteringDiarizer
+
+    inf = R.NeuralDiarizerInferenceConfig.init_config(diar_model_path=None, vad_model_path="vad.nemo", map_location="cpu")
+    assert inf.diarizer.vad.model_path == "vad.nemo" and inf.diarizer.clustering.parameters.max_num_speakers == 8
+    assert inf.diarizer.speaker_embeddings.parameters.get("window_length_in_sec")[0] == 1.5 and "collar" in list(inf.diarizer)
+    dc = inf.to_dictconfig()
+    assert dc.diarizer.vad.parameters.onset == 0.1 and list(dc.diarizer.speaker_embeddings.parameters.shift_length_in_sec)[-1] == 0.25
+    d = ClusteringDiarizer(dc)
+    assert d.windows == [1.5, 1.25, 1.0, 0.75, 0.5] and d.max_num_speakers == 8 and d.sparse_search_volume == 30
+
+    b = R.EncDecClassificationModelConfigBuilder("matchboxnet_3x1x64")
+    b.set_labels(["yes", "no", "up"])
+    b.set_sample_rate(8000)
+    b.set_repeat(2)
+    b.set_dropout(0.1)
+    b.set_timesteps(64)
+    cfg = b.build()
+    assert cfg.decoder["num_classes"] == 3 and cfg.decoder["feat_in"] == 128 and cfg.encoder["feat_in"] == 64 and cfg.preprocessor.sample_rate == 8000
+    assert [blk["repeat"] for blk in cfg.encoder["jasper"]] == [1, 2, 2, 2, 1, 1] and cfg.encoder["jasper"][-1]["dropout"] == 0.0 and cfg.encoder["jasper"][0]["dropout"] == 0.1
+    assert cfg.train_ds.labels == ["yes", "no", "up"] and cfg.validation_ds.sample_rate == 8000 and cfg.crop_or_pad_augment.audio_length == 64
+    with pytest.raises(ValueError):
+        R.EncDecClassificationModelConfigBuilder("resnet")
+    mc = to_dictconfig(cfg)
+    mc.train_ds = None
+    mc.validation_ds = None
+    mc.test_ds = None
+    mc.optim = {"name": "adamw", "lr": 1e-3}
+    model = EncDecClassificationModel(mc).eval()
+    with torch.no_grad():
+        logits = model.forward(input_signal=torch.randn(2, 8000), input_signal_length=torch.tensor([8000, 6000]))
+    assert logits.shape == (2, 3)
+    vad = R.EncDecClassificationModelConfigBuilder("matchboxnet_3x1x64_vad").build()
+    assert vad.labels == ["background", "speech"] and vad.decoder["num_classes"] == 2 and vad.crop_or_pad_augment is None
+    top = to_dictconfig(R.EncDecCTCModelConfig(name="ctc"))
+    assert top.model.optim.name == "novograd" and top.model.preprocessor.features == 64 and top.model.train_ds.shuffle is True
