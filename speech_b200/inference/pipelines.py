@@ -431,7 +431,9 @@ class PipelineBuilder:
             from ..models.asr_model import ASRModel
 
             asr_model = ASRModel.restore_from(_get(cfg, "asr.model_name"), map_location=_get(cfg, "asr.device", None))
-        kind = str(_get(cfg, "pipeline_type", "cache_aware")).lower()
+        from .enums import PipelineType
+
+        kind = PipelineType.from_str(_get(cfg, "pipeline_type", "cache_aware")).name.lower()      # rejects unknown names with the list of choices
         dtype = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": None, None: None}[
             _get(cfg, "asr.compute_dtype", None) if _get(cfg, "asr.compute_dtype", None) in ("bfloat16", "float16") else None]
         device = _get(cfg, "asr.device", None)

@@ -423,3 +423,12 @@ def test_streaming_transducer_inference_with_left_and_right_context():
     assert len(hyps) == 2 and all(h is not None for h in hyps)
     ts = [int(t) for t in (hyps[0].timestamp.tolist() if torch.is_tensor(hyps[0].timestamp) else hyps[0].timestamp)]
     assert ts == sorted(ts)
+
+
+def test_inference_option_enums_parse_config_strings():
+    from speech_b200.inference.enums import ASRDecodingType, FeatureBufferPaddingMode, MergingStrategy, PipelineType, RequestType
+
+    assert PipelineType.from_str("Cache_Aware") is PipelineType.CACHE_AWARE and MergingStrategy.from_str("lcsubstr") is MergingStrategy.LCSUBSTR
+    assert FeatureBufferPaddingMode.from_str("left") is FeatureBufferPaddingMode.LEFT and RequestType.FRAME is not RequestType.FEATURE_BUFFER
+    with pytest.raises(ValueError, match="ctc"):
+        ASRDecodingType.from_str("transducer")
