@@ -419,3 +419,36 @@ def test_host_context_graph_word_spotting_graph_and_merge():
     text, words = merge_alignment_with_ws_hyps(ali, [WordSpotterHyp("kats", -0.2, 4, 6)], lambda i: toks[i], blank=5)
     assert text == "the kats sat" and words[1] == ("kats", 4, 6)
     assert merge_alignment_with_ws_hyps(ali, [], lambda i: toks[i], blank=5)[0] == "the cats sat"
+
+
+def test_exported_transducer_graphs_reproduce_framework_greedy_decoding(tmp_path):
+    import torch
+
+    from speech_b200.decoding.exported_rnnt import ONNXGreedyBatchedRNNTInfer, TorchscriptGreedyBatchedRNNTInfer, export_transducer_subnets
+    from speech_b200.models.configs import fastconformer_transducer_config
+    from speech_b200.models.rnnt_models import EncDecRNNTBPEModel
+
+    torch.manual_seed(3)
+    for loss in ("rnnt", "tdt"):
+        cfg = fastconformer_transducer_config("small", vocab_size=24, n_layers=2, loss=loss, dropout=0.0)
+        cfg.joint.fuse_loss_wer = False
+        model = EncDecRNNTBPEModel(cfg).eval()
+        with torch.no_grad():
+            model.joint.joint_net[-1].bias[:-1 if loss == "rnnt" else -6] += 1.5          # make non-blank tokens likely so that the loop really emits
+        enc_path, dj_path = export_transducer_subnets(model, str(tmp_path / loss), feat_frames=48)
+        durations = list(getattr(model.decoding, "durations", None) or [])
+        infer = TorchscriptGreedyBatchedRNNTInfer(enc_path, dj_path, blank_id=model.decoding.blank_id, pred_layers=model.decoder.pred_rnn_layers,
+                                                  pred_hidden=model.decoder.pred_hidden, max_symbols_per_step=3, durations=durations)
+        feats = torch.randn(3, 80, 120)
+        flen = torch.tensor([120, 90, 57])
+        got = infer(feats, flen)
+        with torch.no_grad():
+            enc, enc_len = model.encoder(audio_signal=feats, length=flen)
+        model.change_decoding_strategy({"strategy": "greedy_batch", "greedy": {"max_symbols": 3}})
+        ref = model.decoding.rnnt_decoder_predictions_tensor(enc, enc_len, return_hypotheses=True)
+        ref_ids = [[int(t) for t in h.y_sequence] for h in ref]
+        assert got == ref_ids and sum(len(g) for g in got) > 0
+    with pytest.raises(RuntimeError, match="onnxruntime"):
+        ONNXGreedyBatchedRNNTInfer("e.onnx", "d.onnx", 24, 1, 320)
+    with pytest.raises(FileNotFoundError):
+        TorchscriptGreedyBatchedRNNTInfer(str(tmp_path / "no.ts"), dj_path, 24, 1, 320)
