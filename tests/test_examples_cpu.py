@@ -341,3 +341,28 @@ def test_g2p_and_ssl_tts_examples(tmp_path):
                                      "model.train_ds.num_workers=0", "model.encoder.n_layers=1", "model.encoder.d_model=32", "model.encoder.n_heads=2", "model.encoder_dim=32",
                                      "model.encoder.subsampling_conv_channels=16", "trainer.max_steps=2", "trainer.max_epochs=null", "trainer.accelerator=cpu", "trainer.devices=1",
                                      "trainer.strategy=auto", f"exp_manager.exp_dir={tmp_path / 'ssl'}", "exp_manager.create_tensorboard_logger=false"], str(tmp_path))
+
+
+def test_adapter_sweep_scoring_picks_constrained_and_unconstrained_winners(tmp_path):
+    import importlib.util
+    import itertools
+    import json
+
+    import pandas as pd
+
+    spec = importlib.util.spec_from_file_location("scoring_and_analysis", os.path.join(REPO, "examples", "asr", "asr_adapters", "scoring_and_analysis.py"))
+    sa = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sa)
+    rows = []
+    for pos, dim, g in itertools.product(["encoder", "decoder"], [32, 64], ["a", "b"]):
+        rows.append({"Adapter Position": pos, "Adapter Dimensions": dim, "Adapter Dropout": 0.1, "Stochastic Depth": 0.0, "Train Steps": 1000, "Dataset": g,
+                     "WER: Test": 10 - (2 if dim == 64 else 1) - (1 if pos == "encoder" else 0), "WER: Original Test": 5 + (4 if dim == 64 else 0.5)})
+    pd.DataFrame(rows).to_csv(tmp_path / "sweep.csv", index=False)
+    (tmp_path / "base.json").write_text(json.dumps({"original": 5.0, "adapted": {"a": 10.0, "b": 10.0}}))
+    best = sa.main(["--csv", str(tmp_path / "sweep.csv"), "--dataset_type_column", "Dataset", "--baselines", str(tmp_path / "base.json")])
+    assert [b["Adapter Dimensions"] for b in best] == [64, 64, 32, 32]     # lowest WER wins unconstrained; the run that ruins the original domain scores 0
+    df = pd.read_csv(tmp_path / "sweep.csv")
+    assert abs(df[(df["Adapter Dimensions"] == 32) & (df["Adapter Position"] == "encoder")]["Score"].iloc[0] - (2.5 / 3) * 0.2) < 1e-3
+    only = sa.main(["--csv", str(tmp_path / "sweep.csv"), "--dataset_type_column", "Dataset", "--baselines", str(tmp_path / "base.json"), "-uargs", "Adapter Dimensions", "32"])
+    assert only[0]["Adapter Dimensions"] == 32
+    assert sa.original_scale(9.0, 5.0, 3.0) == 0.0 and sa.adapt_werr(12.0, 10.0) == 0.0
