@@ -1063,3 +1063,38 @@ def test_tts_base_kinds_text_normaliser_hook_and_griffin_lim_vocoder():
     spec_y = torch.stft(y[0], n_fft, hop, n_fft, win, return_complex=True).abs().mean(-1)
     assert abs(int(spec_y.argmax()) - round(440 / (sr / n_fft))) <= 1                      # the tone survives the mel → waveform inversion
     assert float(y[0, 1000:-1000].pow(2).mean().sqrt()) == pytest.approx(0.5 / math.sqrt(2), rel=0.3)
+
+
+def test_heteronym_disambiguation_picks_the_pronunciation_the_audio_supports():
+    import torch
+
+    from speech_b200.tts.heteronym_aligner import alignment_score, disambiguate_heteronyms
+
+    symbols = [" ", "r", "iy", "eh", "d", "ay", "b", "uh", "k"]
+    sid = {s: k for k, s in enumerate(symbols)}
+
+    def aligner(spec, spec_len, text, text_len):
+        """Frames are (noisy) one-hot symbol indicators: the log-probability of token u at frame t is the log-softmax over tokens of their match."""
+        sim = spec[0].t()[:, text[0]] * 8.0                                  # [T, U]
+        logp = torch.log_softmax(sim, dim=-1)[None, None]
+        return logp.exp(), logp
+
+    def render(seq, per=4):
+        frames = torch.zeros(len(symbols), len(seq) * per)
+        for k, s in enumerate(seq):
+            frames[sid[s], k * per:(k + 1) * per] = 1.0
+        return frames[None] + 0.05 * torch.randn(1, len(symbols), len(seq) * per, generator=torch.Generator().manual_seed(0))
+
+    encode = lambda syms: [sid[s] for s in syms]  # noqa: E731
+    prons = {"read": [["r", "iy", "d"], ["r", "eh", "d"]], "i": [["ay"]], "book": [["b", "uh", "k"]]}
+    words = ["i", "read", "book"]
+    for truth, want in ((["ay", " ", "r", "eh", "d", " ", "b", "uh", "k"], 1), (["ay", " ", "r", "iy", "d", " ", "b", "uh", "k"], 0)):
+        spec = render(truth)
+        slen = torch.tensor([spec.shape[-1]])
+        chosen, dec = disambiguate_heteronyms(aligner, spec, slen, words, prons, encode)
+        assert len(dec) == 1 and dec[0]["word"] == "read" and dec[0]["choice"] == want and dec[0]["confidence"] > 0
+        assert chosen[1] == prons["read"][want] and chosen[0] == ["ay"]
+        good, bad = alignment_score(aligner, spec, slen, encode(truth)), alignment_score(aligner, spec, slen, encode(truth[:3] + ["k"] + truth[4:]))
+        assert good > bad
+    unsure, dec = disambiguate_heteronyms(aligner, spec, slen, words, prons, encode, min_confidence=1e9)
+    assert dec[0]["choice"] is None and unsure[1] == prons["read"][0]
