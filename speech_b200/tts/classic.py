@@ -18,6 +18,7 @@ import torch.nn.functional as F
 
 from ..core.config import DictConfig, cfg_get, to_container
 from ..core.modelpt import ModelPT
+from ..core.adapters import AdapterModelPTMixin
 from .base import SpectrogramGenerator, Vocoder
 from .audio_codec import Discriminator, HiFiGANDecoder, MelLoss, discriminator_loss, feature_matching_loss, gan_update, generator_adv_loss
 from .magpietts import ForwardSumLoss, beta_binomial_prior
@@ -216,7 +217,10 @@ class TemporalPredictor(nn.Module):
         return self.fc(h).squeeze(-1) * mask
 
 
-class FastPitchModel(SpectrogramGenerator):
+class FastPitchModel(SpectrogramGenerator, AdapterModelPTMixin):
+    adapter_module_names = ("encoder", "decoder")
+    default_adapter_module_name = "encoder"
+
     def __init__(self, cfg: DictConfig, trainer=None, tokenizer=None):
         super().__init__(cfg=cfg, trainer=trainer)
         cfg = self._cfg
@@ -249,6 +253,7 @@ class FastPitchModel(SpectrogramGenerator):
                            cfg_get(cfg, "win_length", 1024))
         self.w = {"dur": cfg_get(cfg, "dur_loss_scale", 0.1), "pitch": cfg_get(cfg, "pitch_loss_scale", 0.1), "align": cfg_get(cfg, "align_loss_scale", 1.0)}
         self.bin_loss_start = cfg_get(cfg, "bin_loss_warmup_epochs", 100)
+        self.restore_adapters_from_cfg()
         if not self._is_model_being_restored and self._train_dl is None:
             self._setup_dataloaders_from_cfg()
 

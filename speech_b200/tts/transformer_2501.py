@@ -15,6 +15,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
+from ..core.module import AdapterModuleMixin
 
 
 class ConvolutionLayer(nn.Module):
@@ -170,7 +171,7 @@ class Attention(nn.Module):
         return ops.linear(y, self.o_net.weight, None), probs
 
 
-class TransformerLayer(nn.Module):
+class TransformerLayer(nn.Module, AdapterModuleMixin):
     def __init__(self, d_model, d_ffn, sa_n_heads, kernel_size, p_dropout, has_xattn, xa_d_memory=None, xa_n_heads=None,
                  is_causal=True, apply_norm_to_cond=True, use_moe=False, num_experts=4, top_k_experts=2, routing_strategy="top_k",
                  router_jitter_noise=0.0):
@@ -199,7 +200,10 @@ class TransformerLayer(nn.Module):
                                             cache=None if cache is None else cache.setdefault("cross", {}))
             x = (x + a) * m
         ff = self.pos_ff(self.norm_pos_ff(x), x_mask) if self.use_moe else self.pos_ff(self.norm_pos_ff(x))
-        return (x + ff) * m, probs
+        x = (x + ff) * m
+        if self.is_adapter_available():                              # adapters sit at the end of the layer, merged by their strategy (residual add)
+            x = self.forward_enabled_adapters(x) * m
+        return x, probs
 
 
 class Transformer(nn.Module):
@@ -227,6 +231,37 @@ class Transformer(nn.Module):
 
     def new_cache(self) -> List[dict]:
         return [dict() for _ in self.layers]
+
+    # ------------------------------------------------------------------ adapters (every layer hosts a copy)
+    def add_adapter(self, name: str, cfg) -> None:
+        for layer in self.layers:
+            layer.add_adapter(name, cfg)
+
+    def is_adapter_available(self) -> bool:
+        return any(layer.is_adapter_available() for layer in self.layers)
+
+    @property
+    def adapter_cfg(self) -> dict:
+        """Names and configs of the hosted adapters (the layers hold identical sets)."""
+        return next((layer.adapter_cfg for layer in self.layers if layer.is_adapter_available()), {})
+
+    def set_enabled_adapters(self, name=None, enabled: bool = True) -> None:
+        for layer in self.layers:
+            if layer.is_adapter_available():
+                layer.set_enabled_adapters(name, enabled)
+
+    def get_enabled_adapters(self) -> List[str]:
+        names: List[str] = []
+        for layer in self.layers:
+            for n in layer.get_enabled_adapters():
+                if n not in names:
+                    names.append(n)
+        return names
+
+    def unfreeze_enabled_adapters(self, freeze_batchnorm: bool = True) -> None:
+        for layer in self.layers:
+            if layer.is_adapter_available():
+                layer.unfreeze_enabled_adapters(freeze_batchnorm)
 
     def moe_aux_losses(self) -> Dict[str, torch.Tensor]:
         out: Dict[str, torch.Tensor] = {}

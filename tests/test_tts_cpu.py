@@ -1098,3 +1098,49 @@ def test_heteronym_disambiguation_picks_the_pronunciation_the_audio_supports():
         assert good > bad
     unsure, dec = disambiguate_heteronyms(aligner, spec, slen, words, prons, encode, min_confidence=1e9)
     assert dec[0]["choice"] is None and unsure[1] == prons["read"][0]
+
+
+def test_fastpitch_adapters_train_alone_and_round_trip(tmp_path):
+    import torch
+
+    from speech_b200.core.config import OmegaConf
+    from speech_b200.tts.classic import FastPitchModel
+
+    torch.manual_seed(0)
+    cfg = OmegaConf.create({"n_symbols": 20, "symbols_embedding_dim": 16, "n_mel_channels": 16, "d_inner": 32, "encoder_layers": 2, "decoder_layers": 1, "sample_rate": 8000,
+                            "n_fft": 128, "hop_length": 32, "win_length": 128})
+    m = FastPitchModel(cfg).eval()
+    toks, lens = torch.randint(1, 20, (2, 7)), torch.tensor([7, 5])
+    with torch.no_grad():
+        base = m(toks, lens)["mel"]
+    acfg = {"in_features": 16, "dim": 8, "activation": "swish", "norm_position": "pre"}
+    m.add_adapter("encoder:spk", acfg)
+    m.add_adapter("decoder:spk", acfg)
+    assert m.get_enabled_adapters() == ["encoder:spk", "decoder:spk"] and len(m.encoder.layers[1].adapter_layer) == 1
+    with torch.no_grad():
+        fresh = m(toks, lens)["mel"]
+    assert torch.allclose(fresh, base, atol=1e-5)                                 # a new adapter starts as the identity
+    n = m.freeze_base_and_train_adapters()
+    trainable = [k for k, p in m.named_parameters() if p.requires_grad]
+    assert n > 0 and all(".adapter_layer." in k for k in trainable) and not m.embedding.weight.requires_grad
+    with torch.no_grad():
+        for k, p in m.named_parameters():
+            if ".adapter_layer." in k:
+                p.add_(0.05 * torch.randn_like(p))
+        changed = m.eval()(toks, lens)["mel"]
+    assert not torch.allclose(changed, base, atol=1e-4)
+    m.set_enabled_adapters(enabled=False)
+    with torch.no_grad():
+        assert torch.allclose(m(toks, lens)["mel"], base, atol=1e-5)              # disabled adapters leave the base model intact
+    m.set_enabled_adapters(enabled=True)
+    m.save_adapters(str(tmp_path / "spk.pt"))
+    torch.manual_seed(0)
+    m2 = FastPitchModel(cfg).eval()
+    m2.load_state_dict({k: v for k, v in m.state_dict().items() if ".adapter_layer." not in k})
+    m2.load_adapters(str(tmp_path / "spk.pt"))
+    with torch.no_grad():
+        assert torch.allclose(m2(toks, lens)["mel"], changed, atol=1e-5)
+    m3 = FastPitchModel(m2.cfg).eval()                                             # the config remembers the adapters: a rebuilt model has them
+    assert m3.get_enabled_adapters() == ["encoder:spk", "decoder:spk"]
+    with pytest.raises(ValueError):
+        m.add_adapter("aligner:spk", acfg)
