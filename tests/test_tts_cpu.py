@@ -1144,3 +1144,36 @@ def test_fastpitch_adapters_train_alone_and_round_trip(tmp_path):
     assert m3.get_enabled_adapters() == ["encoder:spk", "decoder:spk"]
     with pytest.raises(ValueError):
         m.add_adapter("aligner:spk", acfg)
+
+
+def test_fastpitch_ssl_trains_on_features_and_swaps_speakers():
+    import torch
+
+    from speech_b200.core.config import OmegaConf
+    from speech_b200.core.trainer import Trainer
+    from speech_b200.tts.base import GriffinLimVocoder
+    from speech_b200.tts.fastpitch_ssl import FastPitchModel_SSL
+
+    torch.manual_seed(0)
+    cfg = OmegaConf.create({"n_mel_channels": 16, "content_emb_indim": 12, "speaker_emb_indim": 10, "symbols_embedding_dim": 16, "d_inner": 32, "encoder_layers": 1,
+                            "decoder_layers": 1, "dropout": 0.0, "train_ds": {"synthetic": {"num_samples": 8}, "batch_size": 4},
+                            "validation_ds": {"synthetic": {"num_samples": 4}, "batch_size": 4}, "optim": {"name": "adamw", "lr": 1e-2}})
+    voc = GriffinLimVocoder(8000, 128, 32, n_mels=16, n_iters=2, log_input=False)
+    model = FastPitchModel_SSL(cfg, vocoder=voc)
+    batch = next(iter(model._train_dl))
+    first = float(model._losses(batch)[0])
+    Trainer(max_steps=12, accelerator="cpu", logger=False, enable_checkpointing=False, log_every_n_steps=100).fit(model)
+    model.eval()
+    assert float(model._losses(batch)[0]) < first
+    ce, cl, spk, mel, ml, dur, pitch = batch
+    out, out_len = model.synthesize_spectrogram(ce, spk, cl, durations=dur, pitch=pitch)
+    assert out.shape[:2] == (4, 16) and out_len.tolist() == dur.sum(1).long().tolist()                # given durations fix the output length
+    other, _ = model.synthesize_spectrogram(ce, spk.flip(0), cl, durations=dur, pitch=pitch)
+    assert not torch.allclose(out, other, atol=1e-4)                                                   # another speaker embedding → another voice
+    slow, slow_len = model.synthesize_spectrogram(ce, spk, cl, durations=dur, pitch=pitch, pace=0.5)
+    assert slow_len.tolist() == (2 * dur.sum(1)).long().tolist()
+    free, free_len = model.synthesize_spectrogram(ce, spk, cl)                                         # predicted durations and pitch
+    assert free.shape[0] == 4 and int(free_len.min()) >= 0
+    wavs = model.generate_wav(ce, spk, cl, durations=dur, pitch=pitch)
+    assert len(wavs) == 4 and wavs[0].shape[0] == int(out_len[0]) * (wavs[0].shape[0] // int(out_len[0]))
+    assert "vocoder" not in dict(model.named_modules())
